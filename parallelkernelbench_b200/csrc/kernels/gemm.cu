@@ -1,0 +1,79 @@
+// Host launchers of the tcgen05 GEMM (kernel template in pkb/gemm_umma.cuh).
+#include "pkb/api.h"
+#include "pkb/gemm_umma.cuh"
+#include "pkb/host.h"
+
+namespace pkb {
+
+template <int BN, int EPI, bool OUT_F32>
+static int launch_plain(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                        int num_ctas, cudaStream_t stream) {
+  auto kern = gemm_umma_kernel<BN, EPI, OUT_F32, false, false>;
+  constexpr int smem = GemmSmem<BN>::kTotal;
+  static bool configured = false;  // per instantiation; attribute is per device but idempotent
+  if (!configured) {
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+  }
+  kern<<<num_ctas, kGemmThreads, smem, stream>>>(ta, tb, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+template <int BN, bool OUT_F32>
+static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                        int num_ctas, cudaStream_t stream) {
+  switch (epi) {
+    case kEpiNone: return launch_plain<BN, kEpiNone, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiSilu: return launch_plain<BN, kEpiSilu, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiBias: return launch_plain<BN, kEpiBias, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiBiasSilu: return launch_plain<BN, kEpiBiasSilu, OUT_F32>(ta, tb, p, num_ctas, stream);
+  }
+  set_last_error("unknown epilogue");
+  return kApiBadArgument;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+extern "C" int pkb_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* c,
+                             long long ldc, int M, int N, int K, const void* bias, float alpha,
+                             int epilogue, int out_f32, int block_n, int num_ctas, void* stream) {
+  PKB_CHECK_ARG(M > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && K % 8 == 0, "lda, ldb, K must be multiples of 8");
+  PKB_CHECK_ARG((epilogue & 2) == 0 || bias != nullptr, "bias epilogue without bias");
+  if (block_n == 0) block_n = (N >= 256 && (long long)M * N >= 128ll * 256 * 64) ? 256 : 128;
+  PKB_CHECK_ARG(block_n == 128 || block_n == 256, "block_n must be 128 or 256");
+
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
+                          kGemmBlockK, kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK,
+                      (uint32_t)block_n, kSwizzle128);
+  if (rc) return rc;
+
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.C = c; p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.group_m = 16;
+  p.kernel_id = 100;
+  p.world = 1;
+
+  const int num_m = (M + kGemmBlockM - 1) / kGemmBlockM;
+  const int num_n = (N + block_n - 1) / block_n;
+  const int tiles = num_m * num_n;
+  int ctas = num_ctas > 0 ? num_ctas : sm_count();
+  if (ctas > tiles) ctas = tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block_n == 256)
+    return out_f32 ? dispatch_epi<256, true>(epilogue, ta, tb, p, ctas, s)
+                   : dispatch_epi<256, false>(epilogue, ta, tb, p, ctas, s);
+  return out_f32 ? dispatch_epi<128, true>(epilogue, ta, tb, p, ctas, s)
+                 : dispatch_epi<128, false>(epilogue, ta, tb, p, ctas, s);
+}

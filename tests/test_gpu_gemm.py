@@ -1,0 +1,73 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, w, bias=None, act="none", alpha=1.0):
+    y = alpha * (a.float() @ w.float().t())
+    if bias is not None:
+        y = y + bias.float()
+    if act.endswith("silu"):
+        y = torch.nn.functional.silu(y)
+    return y
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (128, 256, 64), (256, 512, 256), (1024, 1024, 1024),
+                                    (100, 72, 40), (129, 257, 136), (1, 128, 64), (2048, 3584, 512)])
+@pytest.mark.parametrize("block_n", [128, 256])
+def test_gemm_matches_fp32_reference(M, N, K, block_n):
+    from parallelkernelbench_b200.ops import gemm_bf16
+
+    g = torch.Generator(device="cuda").manual_seed(1234 + M + N + K)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=g)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16, generator=g) * 0.05
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm_bf16(a, w, out=out, block_n=block_n)
+    ref = _ref(a, w)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("epilogue", ["none", "silu", "bias", "bias_silu"])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_epilogues(epilogue, out_dtype):
+    from parallelkernelbench_b200.ops import gemm_bf16
+
+    M, N, K = 384, 640, 320
+    g = torch.Generator(device="cuda").manual_seed(7)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=g)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16, generator=g) * 0.05
+    bias = torch.randn(N, device="cuda", dtype=torch.bfloat16, generator=g) if "bias" in epilogue else None
+    out = gemm_bf16(a, w, bias=bias, epilogue=epilogue, alpha=0.5, out_dtype=out_dtype)
+    ref = _ref(a, w, bias, epilogue, 0.5)
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+
+
+def test_gemm_is_deterministic_and_leaves_guard_bands_alone():
+    from parallelkernelbench_b200.ops import gemm_bf16
+
+    M, N, K = 300, 520, 1024
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    # output embedded in a larger buffer whose border must stay untouched
+    buf = torch.full((M + 16, N + 16), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = buf[8:8 + M, 8:8 + N]
+    gemm_bf16(a, w, out=out)
+    first = out.clone()
+    for _ in range(10):
+        gemm_bf16(a, w, out=out)
+        assert torch.equal(out, first)
+    border = buf.clone()
+    border[8:8 + M, 8:8 + N] = 7.0
+    assert torch.all(border == 7.0)
+
+
+def test_large_k_accumulation():
+    from parallelkernelbench_b200.ops import gemm_bf16
+
+    M, N, K = 256, 256, 8192
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
+    out = gemm_bf16(a, w)
+    torch.testing.assert_close(out.float(), _ref(a, w), atol=3e-2, rtol=2e-2)
