@@ -1,0 +1,60 @@
+// C view of the symmetric-heap context and the collective entry points (collectives.cu).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Mirrors pkb::SymmCtx minus the device-only fields. Filled by the Python side (ctypes.Structure).
+typedef struct pkb_symm_ctx {
+  uint64_t base;
+  uint64_t stride;
+  uint64_t mc_base;
+  int32_t rank;
+  int32_t world;
+  int32_t gsize;
+  int32_t grank;
+  int32_t members[16];
+  int32_t channel;
+  int32_t _pad;
+  uint64_t budget_ns;  // 0 = library default
+} pkb_symm_ctx;
+
+// dtype: 0 bf16, 1 fp32, 2 fp64, 3 fp16, 4 int32, 5 int64. op: 0 sum, 1 max, 2 min.
+int pkb_coll_barrier(const pkb_symm_ctx* h, int blocks, void* stream);
+int pkb_coll_reduce(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long stage_elems,
+                    unsigned long long stage_off, long long in_base, long long n, void* out, int active,
+                    double scale, int max_blocks, void* stream);
+int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes,
+                    unsigned long long stage_off, unsigned int src_mask, long long in_base,
+                    long long in_member_stride, long long seg_bytes, void* out, long long out_stride,
+                    int active, int max_blocks, void* stream);
+int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n,
+                               unsigned long long stage_off, unsigned long long result_off, void* out,
+                               int src_in_heap, double scale, int max_blocks, void* stream);
+int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n,
+                            unsigned long long stage_off, unsigned long long result_off, void* out,
+                            int src_in_heap, int max_blocks, void* stream);
+int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_rows, long long row_bytes,
+                          const void* send_counts, const void* send_offsets, unsigned long long stage_off,
+                          unsigned long long meta_off, void* out, long long out_capacity_rows,
+                          void* recv_counts, void* recv_total, int max_blocks, void* stream);
+
+// symmetric heap (symm_heap.cu)
+int pkb_heap_multicast_supported();
+long long pkb_heap_round_size(long long bytes, int world, int with_multicast);
+int pkb_heap_create(long long bytes, int rank, int world, int* out_fd);
+int pkb_heap_import_peer(int heap, int peer, int fd);
+unsigned long long pkb_heap_base(int heap);
+unsigned long long pkb_heap_stride(int heap);
+unsigned long long pkb_heap_mc_base(int heap);
+int pkb_heap_mc_create(int heap, int* out_fd);
+int pkb_heap_mc_import(int heap, int fd);
+int pkb_heap_mc_add_device(int heap);
+int pkb_heap_mc_bind(int heap);
+int pkb_heap_destroy(int heap);
+
+#ifdef __cplusplus
+}
+#endif

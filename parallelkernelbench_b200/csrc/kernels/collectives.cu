@@ -1,0 +1,522 @@
+// Collectives over the symmetric heap: every kernel stages its input into this rank's heap
+// (unless it already lives there), crosses one in-kernel barrier, and then reads its peers'
+// memory directly over NVLink with 16-byte loads. There are no rings: NVSwitch gives every pair
+// full bandwidth, so each rank talks to all peers at once.
+//
+//   reduce family  (all-reduce one-shot, reduce-scatter, reduce-to-root): sum/max/min in fp32/fp64
+//                  in a fixed member order, so every rank computes bit-identical results
+//   gather family  (all-gather, all-to-all, broadcast, scatter, gather-to-root): byte copies
+//   two-shot all-reduce: reduce own slice, publish it, gather the other slices
+//   NVLS all-reduce: multimem.ld_reduce of the own slice, multimem.st of the result to everyone
+//   all-to-all-v: per-destination counts and offsets travel through the heap; nothing returns
+//                 to the host
+// They replace the NCCL calls of the reference's collective problems
+// (reference: reference/1_allreduce.py:8 ... reference/8_alltoall.py:8) and the example kernels
+// (reference: kernelgen/solution_new_add_cuda.py:16-26,
+//  kernelgen/solutions_new_allreduce_parallelkittens.py:31-69).
+#include "pkb/api.h"
+#include "pkb/collectives_api.h"
+#include "pkb/host.h"
+#include "pkb/symm.cuh"
+
+namespace pkb {
+
+constexpr int kCollThreads = 512;
+
+enum CollDtype : int { kCollBf16 = 0, kCollF32 = 1, kCollF64 = 2, kCollF16 = 3, kCollI32 = 4, kCollI64 = 5 };
+enum CollOp : int { kCollSum = 0, kCollMax = 1, kCollMin = 2 };
+
+template <int OP, typename A>
+__device__ __forceinline__ A combine(A a, A b) {
+  if constexpr (OP == kCollSum) return a + b;
+  else if constexpr (OP == kCollMax) return a > b ? a : b;
+  else return a < b ? a : b;
+}
+
+// ---- 16-byte packs per dtype: unpack to an accumulator array, combine, pack ------------------
+template <int DT> struct Pack;
+template <> struct Pack<kCollBf16> {
+  using Acc = float; static constexpr int kN = 8; static constexpr int kElem = 2;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) {
+    float2 f;
+    f = unpack_bf16x2(u.x); a[0] = f.x; a[1] = f.y;
+    f = unpack_bf16x2(u.y); a[2] = f.x; a[3] = f.y;
+    f = unpack_bf16x2(u.z); a[4] = f.x; a[5] = f.y;
+    f = unpack_bf16x2(u.w); a[6] = f.x; a[7] = f.y;
+  }
+  static __device__ __forceinline__ U4 pack(const Acc* a) {
+    return U4{pack_bf16x2(a[0], a[1]), pack_bf16x2(a[2], a[3]), pack_bf16x2(a[4], a[5]),
+              pack_bf16x2(a[6], a[7])};
+  }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) {
+    return __bfloat162float(static_cast<const __nv_bfloat16*>(p)[i]);
+  }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) {
+    static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+  }
+};
+template <> struct Pack<kCollF16> {
+  using Acc = float; static constexpr int kN = 8; static constexpr int kElem = 2;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { float2 f = __half22float2(h[i]); a[2 * i] = f.x; a[2 * i + 1] = f.y; }
+  }
+  static __device__ __forceinline__ U4 pack(const Acc* a) {
+    U4 u; __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(a[2 * i], a[2 * i + 1]);
+    return u;
+  }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) {
+    return __half2float(static_cast<const __half*>(p)[i]);
+  }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) {
+    static_cast<__half*>(p)[i] = __float2half_rn(v);
+  }
+};
+template <> struct Pack<kCollF32> {
+  using Acc = float; static constexpr int kN = 4; static constexpr int kElem = 4;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) {
+    a[0] = __uint_as_float(u.x); a[1] = __uint_as_float(u.y);
+    a[2] = __uint_as_float(u.z); a[3] = __uint_as_float(u.w);
+  }
+  static __device__ __forceinline__ U4 pack(const Acc* a) {
+    return U4{__float_as_uint(a[0]), __float_as_uint(a[1]), __float_as_uint(a[2]), __float_as_uint(a[3])};
+  }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) { return static_cast<const float*>(p)[i]; }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) { static_cast<float*>(p)[i] = v; }
+};
+template <> struct Pack<kCollF64> {
+  using Acc = double; static constexpr int kN = 2; static constexpr int kElem = 8;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) {
+    a[0] = __hiloint2double((int)u.y, (int)u.x); a[1] = __hiloint2double((int)u.w, (int)u.z);
+  }
+  static __device__ __forceinline__ U4 pack(const Acc* a) {
+    return U4{(uint32_t)__double2loint(a[0]), (uint32_t)__double2hiint(a[0]),
+              (uint32_t)__double2loint(a[1]), (uint32_t)__double2hiint(a[1])};
+  }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) { return static_cast<const double*>(p)[i]; }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) { static_cast<double*>(p)[i] = v; }
+};
+template <> struct Pack<kCollI32> {
+  using Acc = int; static constexpr int kN = 4; static constexpr int kElem = 4;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) { a[0] = u.x; a[1] = u.y; a[2] = u.z; a[3] = u.w; }
+  static __device__ __forceinline__ U4 pack(const Acc* a) { return U4{(uint32_t)a[0], (uint32_t)a[1], (uint32_t)a[2], (uint32_t)a[3]}; }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) { return static_cast<const int*>(p)[i]; }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) { static_cast<int*>(p)[i] = v; }
+};
+template <> struct Pack<kCollI64> {
+  using Acc = long long; static constexpr int kN = 2; static constexpr int kElem = 8;
+  static __device__ __forceinline__ void unpack(const U4& u, Acc* a) {
+    a[0] = (long long)(((unsigned long long)u.y << 32) | u.x); a[1] = (long long)(((unsigned long long)u.w << 32) | u.z);
+  }
+  static __device__ __forceinline__ U4 pack(const Acc* a) {
+    return U4{(uint32_t)a[0], (uint32_t)((unsigned long long)a[0] >> 32), (uint32_t)a[1], (uint32_t)((unsigned long long)a[1] >> 32)};
+  }
+  static __device__ __forceinline__ Acc load1(const void* p, long long i) { return static_cast<const long long*>(p)[i]; }
+  static __device__ __forceinline__ void store1(void* p, long long i, Acc v) { static_cast<long long*>(p)[i] = v; }
+};
+
+// Copy `bytes` from src to dst with the whole grid (16-byte body, byte tail). Both 16-aligned or not.
+__device__ __forceinline__ void grid_copy_bytes(void* dst, const void* src, long long bytes) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
+    const long long nvec = bytes >> 4;
+    for (long long i = tid; i < nvec; i += nthreads)
+      st_global_v4(static_cast<uint8_t*>(dst) + (i << 4), ld_global_v4(static_cast<const uint8_t*>(src) + (i << 4)));
+    for (long long i = (nvec << 4) + tid; i < bytes; i += nthreads)
+      static_cast<uint8_t*>(dst)[i] = static_cast<const uint8_t*>(src)[i];
+  } else {
+    for (long long i = tid; i < bytes; i += nthreads)
+      static_cast<uint8_t*>(dst)[i] = static_cast<const uint8_t*>(src)[i];
+  }
+}
+
+// ================================================================================================
+// reduce family
+// ================================================================================================
+struct ReduceArgs {
+  const void* src;        // local input (any device memory); staged into the heap if stage_elems > 0
+  long long stage_elems;  // elements to copy from src to heap[stage_off]; 0: input already in heap
+  uint64_t stage_off;     // heap offset of the (staged) input on every rank
+  long long in_base;      // first element (in the peers' staged input) this rank reduces
+  long long n;            // elements this rank reduces
+  void* out;              // local output
+  int active;             // 0: take part in the barriers only (non-root of a reduce-to-root)
+  double scale;           // applied after the reduction (1/W for a mean)
+};
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(kCollThreads)
+coll_reduce_kernel(const SymmCtx c, const ReduceArgs a) {
+  using P = Pack<DT>;
+  using Acc = typename P::Acc;
+  if (a.stage_elems > 0)
+    grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_elems * P::kElem);
+  if (!symm_block_barrier(c, 200, 1)) return;
+  if (a.active) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long nthreads = (long long)gridDim.x * blockDim.x;
+    const uint64_t in_off = a.stage_off + (uint64_t)a.in_base * P::kElem;
+    const bool vec_ok = ((in_off | (uintptr_t)a.out) & 15) == 0;
+    const long long nvec = vec_ok ? a.n / P::kN : 0;
+    for (long long i = tid; i < nvec; i += nthreads) {
+      Acc acc[P::kN];
+      P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[0], in_off) + (i << 4)), acc);
+      for (int g = 1; g < c.gsize; ++g) {
+        Acc v[P::kN];
+        P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[g], in_off) + (i << 4)), v);
+#pragma unroll
+        for (int j = 0; j < P::kN; ++j) acc[j] = combine<OP>(acc[j], v[j]);
+      }
+      if (a.scale != 1.0) {
+#pragma unroll
+        for (int j = 0; j < P::kN; ++j) acc[j] = (Acc)(acc[j] * (Acc)a.scale);
+      }
+      st_global_v4(static_cast<uint8_t*>(a.out) + (i << 4), P::pack(acc));
+    }
+    for (long long i = nvec * P::kN + tid; i < a.n; i += nthreads) {
+      Acc acc = P::load1(symm_ptr<uint8_t>(c, c.members[0], in_off), i);
+      for (int g = 1; g < c.gsize; ++g)
+        acc = combine<OP>(acc, P::load1(symm_ptr<uint8_t>(c, c.members[g], in_off), i));
+      if (a.scale != 1.0) acc = (Acc)(acc * (Acc)a.scale);
+      P::store1(a.out, i, acc);
+    }
+  }
+  symm_block_barrier(c, 200, 2);
+}
+
+// ================================================================================================
+// gather family
+// ================================================================================================
+struct GatherArgs {
+  const void* src;
+  long long stage_bytes;  // bytes to stage from src; 0: already in heap
+  uint64_t stage_off;
+  uint32_t src_mask;      // bit g set: read from group member g
+  long long in_base;      // byte offset inside the member's staged buffer
+  long long in_member_stride;  // extra byte offset per *reading* rank (all-to-all: chunk index = my grank)
+  long long seg_bytes;    // bytes read from each selected member
+  void* out;              // local output; segment k (k-th selected member) goes to out + k*out_stride
+  long long out_stride;
+  int active;
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_gather_kernel(const SymmCtx c, const GatherArgs a) {
+  if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
+  if (!symm_block_barrier(c, 201, 1)) return;
+  if (a.active) {
+    int k = 0;
+    for (int g = 0; g < c.gsize; ++g) {
+      if (!((a.src_mask >> g) & 1u)) continue;
+      const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + a.in_base +
+                            a.in_member_stride * c.grank;
+      grid_copy_bytes(static_cast<uint8_t*>(a.out) + (long long)k * a.out_stride, from, a.seg_bytes);
+      ++k;
+    }
+  }
+  symm_block_barrier(c, 201, 2);
+}
+
+// ================================================================================================
+// two-shot all-reduce: reduce own slice -> publish -> gather all slices
+// ================================================================================================
+struct TwoShotArgs {
+  const void* src;
+  long long n;          // total elements (every rank holds n)
+  uint64_t stage_off;   // staged inputs
+  uint64_t result_off;  // n elements: slice g is produced by member g in its own heap
+  void* out;
+  int src_in_heap;
+  double scale;
+};
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(kCollThreads)
+coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
+  using P = Pack<DT>;
+  using Acc = typename P::Acc;
+  if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  if (!symm_block_barrier(c, 202, 1)) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  // slices in units of 16-byte vectors; the last member also takes the ragged tail
+  const long long nvec_total = a.n / P::kN;
+  const long long per = (nvec_total + c.gsize - 1) / c.gsize;
+  const long long v0 = min(per * c.grank, nvec_total), v1 = min(v0 + per, nvec_total);
+  for (long long i = v0 + tid; i < v1; i += nthreads) {
+    Acc acc[P::kN];
+    P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[0], a.stage_off) + (i << 4)), acc);
+    for (int g = 1; g < c.gsize; ++g) {
+      Acc v[P::kN];
+      P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + (i << 4)), v);
+#pragma unroll
+      for (int j = 0; j < P::kN; ++j) acc[j] = combine<OP>(acc[j], v[j]);
+    }
+    if (a.scale != 1.0) {
+#pragma unroll
+      for (int j = 0; j < P::kN; ++j) acc[j] = (Acc)(acc[j] * (Acc)a.scale);
+    }
+    st_global_v4(symm_local<uint8_t>(c, a.result_off) + (i << 4), P::pack(acc));
+  }
+  if (c.grank == c.gsize - 1) {
+    for (long long i = nvec_total * P::kN + tid; i < a.n; i += nthreads) {
+      Acc acc = P::load1(symm_ptr<uint8_t>(c, c.members[0], a.stage_off), i);
+      for (int g = 1; g < c.gsize; ++g)
+        acc = combine<OP>(acc, P::load1(symm_ptr<uint8_t>(c, c.members[g], a.stage_off), i));
+      if (a.scale != 1.0) acc = (Acc)(acc * (Acc)a.scale);
+      P::store1(symm_local<uint8_t>(c, a.result_off), i, acc);
+    }
+  }
+  if (!symm_block_barrier(c, 202, 2)) return;
+  for (int g = 0; g < c.gsize; ++g) {
+    const long long s0 = min(per * g, nvec_total), s1 = min(s0 + per, nvec_total);
+    const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.result_off);
+    for (long long i = s0 + tid; i < s1; i += nthreads)
+      st_global_v4(static_cast<uint8_t*>(a.out) + (i << 4), ld_global_v4(from + (i << 4)));
+    if (g == c.gsize - 1)
+      for (long long i = nvec_total * P::kN + tid; i < a.n; i += nthreads)
+        P::store1(a.out, i, P::load1(from, i));
+  }
+  symm_block_barrier(c, 202, 3);
+}
+
+// ================================================================================================
+// NVLS all-reduce (bf16 / fp32 sum): in-switch reduction through the multicast mapping
+// ================================================================================================
+template <int DT>
+__global__ void __launch_bounds__(kCollThreads)
+coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
+  using P = Pack<DT>;
+  if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  if (!symm_block_barrier(c, 203, 1)) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long nvec_total = (a.n + P::kN - 1) / P::kN;  // staging buffers are padded to 16 bytes
+  const long long per = (nvec_total + c.gsize - 1) / c.gsize;
+  const long long v0 = min(per * c.grank, nvec_total), v1 = min(v0 + per, nvec_total);
+  for (long long i = v0 + tid; i < v1; i += nthreads) {
+    U4 v;
+    if constexpr (DT == kCollBf16) v = multimem_ld_reduce_bf16x8(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
+    else v = multimem_ld_reduce_f32x4(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
+    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), v);
+  }
+  if (!symm_block_barrier(c, 203, 2)) return;
+  if (a.out != nullptr) grid_copy_bytes(a.out, symm_local<uint8_t>(c, a.result_off), a.n * P::kElem);
+  symm_block_barrier(c, 203, 3);
+}
+
+// ================================================================================================
+// all-to-all-v: rows of row_bytes; send_counts/send_offsets (in rows, int64, device) per destination
+// ================================================================================================
+struct A2AVArgs {
+  const void* src;            // local rows, already grouped by destination
+  long long src_rows;         // rows to stage
+  long long row_bytes;
+  const long long* send_counts;   // [gsize] rows for each destination (device memory)
+  const long long* send_offsets;  // [gsize] first row for each destination
+  uint64_t stage_off;         // staged rows
+  uint64_t meta_off;          // 2*kSymmMaxWorld int64: counts then offsets, as seen by the sender
+  void* out;                  // received rows, grouped by source in member order
+  long long out_capacity_rows;
+  long long* recv_counts;     // [gsize] rows received from each source (device memory, may be null)
+  long long* recv_total;      // [1]
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_a2av_kernel(const SymmCtx c, const A2AVArgs a) {
+  grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.src_rows * a.row_bytes);
+  if (blockIdx.x == 0 && (int)threadIdx.x < c.gsize) {
+    long long* meta = symm_local<long long>(c, a.meta_off);
+    meta[threadIdx.x] = a.send_counts[threadIdx.x];
+    meta[kSymmMaxWorld + threadIdx.x] = a.send_offsets[threadIdx.x];
+  }
+  if (!symm_block_barrier(c, 204, 1)) return;
+  long long out_row = 0;
+  for (int g = 0; g < c.gsize; ++g) {
+    const long long* meta = symm_ptr<long long>(c, c.members[g], a.meta_off);
+    const long long cnt = meta[c.grank];
+    const long long off = meta[kSymmMaxWorld + c.grank];
+    long long take = cnt;
+    if (out_row + take > a.out_capacity_rows) take = max(0ll, a.out_capacity_rows - out_row);
+    grid_copy_bytes(static_cast<uint8_t*>(a.out) + out_row * a.row_bytes,
+                    symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + off * a.row_bytes,
+                    take * a.row_bytes);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && a.recv_counts) a.recv_counts[g] = cnt;
+    out_row += cnt;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && a.recv_total) *a.recv_total = out_row;
+  symm_block_barrier(c, 204, 2);
+}
+
+// A barrier and nothing else (used by tests and to fence phases of composite ops).
+__global__ void coll_barrier_kernel(const SymmCtx c) { symm_block_barrier(c, 205, 1); }
+
+static SymmCtx to_ctx(const pkb_symm_ctx* h) {
+  SymmCtx c;
+  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
+  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
+  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
+  c.channel = h->channel;
+  c.status = status_block_device_ptr();
+  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
+  return c;
+}
+
+static int check_ctx(const pkb_symm_ctx* h) {
+  PKB_CHECK_ARG(h != nullptr && h->base != 0 && h->stride != 0, "symmetric heap not initialised");
+  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kSymmMaxWorld && h->grank >= 0 && h->grank < h->gsize, "bad group");
+  PKB_CHECK_ARG(h->channel >= 0 && h->channel < kSymmChannels, "bad channel");
+  return kApiOk;
+}
+
+static int grid_for(long long bytes, int max_blocks) {
+  long long per_block = (long long)kCollThreads * 16 * 4;
+  long long b = (bytes + per_block - 1) / per_block;
+  if (b < 1) b = 1;
+  int cap = max_blocks > 0 ? max_blocks : 2 * sm_count();
+  if (cap > kSymmMaxBlocks) cap = kSymmMaxBlocks;
+  return (int)(b > cap ? cap : b);
+}
+
+template <int DT>
+static int launch_reduce_op(int op, const SymmCtx& c, const ReduceArgs& a, int grid, cudaStream_t s) {
+  switch (op) {
+    case kCollSum: coll_reduce_kernel<DT, kCollSum><<<grid, kCollThreads, 0, s>>>(c, a); break;
+    case kCollMax: coll_reduce_kernel<DT, kCollMax><<<grid, kCollThreads, 0, s>>>(c, a); break;
+    case kCollMin: coll_reduce_kernel<DT, kCollMin><<<grid, kCollThreads, 0, s>>>(c, a); break;
+    default: set_last_error("unknown reduce op"); return kApiBadArgument;
+  }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+static int elem_size(int dt) {
+  switch (dt) {
+    case kCollBf16: case kCollF16: return 2;
+    case kCollF32: case kCollI32: return 4;
+    case kCollF64: case kCollI64: return 8;
+  }
+  return 0;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+extern "C" {
+
+int pkb_coll_barrier(const pkb_symm_ctx* h, int blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(blocks >= 1 && blocks <= kSymmMaxBlocks, "blocks out of range");
+  coll_barrier_kernel<<<blocks, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h));
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_reduce(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long stage_elems,
+                    unsigned long long stage_off, long long in_base, long long n, void* out, int active,
+                    double scale, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(elem_size(dtype) > 0, "unknown dtype");
+  PKB_CHECK_ARG((stage_off & 15) == 0, "stage offset must be 16-byte aligned");
+  ReduceArgs a{src, stage_elems, stage_off, in_base, n, out, active, scale};
+  const long long work = (stage_elems > n * h->gsize ? stage_elems : n * h->gsize) * elem_size(dtype);
+  const int grid = grid_for(work, max_blocks);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SymmCtx c = to_ctx(h);
+  switch (dtype) {
+    case kCollBf16: return launch_reduce_op<kCollBf16>(op, c, a, grid, s);
+    case kCollF16: return launch_reduce_op<kCollF16>(op, c, a, grid, s);
+    case kCollF32: return launch_reduce_op<kCollF32>(op, c, a, grid, s);
+    case kCollF64: return launch_reduce_op<kCollF64>(op, c, a, grid, s);
+    case kCollI32: return launch_reduce_op<kCollI32>(op, c, a, grid, s);
+    case kCollI64: return launch_reduce_op<kCollI64>(op, c, a, grid, s);
+  }
+  return kApiBadArgument;
+}
+
+int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes,
+                    unsigned long long stage_off, unsigned int src_mask, long long in_base,
+                    long long in_member_stride, long long seg_bytes, void* out, long long out_stride,
+                    int active, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG((stage_off & 15) == 0, "stage offset must be 16-byte aligned");
+  GatherArgs a{src, stage_bytes, stage_off, src_mask, in_base, in_member_stride, seg_bytes, out, out_stride, active};
+  const long long work = stage_bytes > seg_bytes * h->gsize ? stage_bytes : seg_bytes * h->gsize;
+  const int grid = grid_for(work, max_blocks);
+  coll_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n,
+                               unsigned long long stage_off, unsigned long long result_off, void* out,
+                               int src_in_heap, double scale, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(((stage_off | result_off) & 15) == 0, "heap offsets must be 16-byte aligned");
+  PKB_CHECK_ARG(((uintptr_t)out & 15) == 0, "output must be 16-byte aligned");
+  TwoShotArgs a{src, n, stage_off, result_off, out, src_in_heap, scale};
+  const int grid = grid_for(n * elem_size(dtype) * 2, max_blocks);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SymmCtx c = to_ctx(h);
+#define PKB_TWOSHOT(DT)                                                                         \
+  switch (op) {                                                                                 \
+    case kCollSum: coll_allreduce_twoshot_kernel<DT, kCollSum><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    case kCollMax: coll_allreduce_twoshot_kernel<DT, kCollMax><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    case kCollMin: coll_allreduce_twoshot_kernel<DT, kCollMin><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    default: set_last_error("unknown reduce op"); return kApiBadArgument;                       \
+  }
+  switch (dtype) {
+    case kCollBf16: PKB_TWOSHOT(kCollBf16); break;
+    case kCollF16: PKB_TWOSHOT(kCollF16); break;
+    case kCollF32: PKB_TWOSHOT(kCollF32); break;
+    case kCollF64: PKB_TWOSHOT(kCollF64); break;
+    case kCollI32: PKB_TWOSHOT(kCollI32); break;
+    case kCollI64: PKB_TWOSHOT(kCollI64); break;
+    default: set_last_error("unknown dtype"); return kApiBadArgument;
+  }
+#undef PKB_TWOSHOT
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n,
+                            unsigned long long stage_off, unsigned long long result_off, void* out,
+                            int src_in_heap, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(h->mc_base != 0, "NVLS multicast mapping not available");
+  PKB_CHECK_ARG(h->gsize == h->world, "NVLS all-reduce runs on the whole heap group only");
+  PKB_CHECK_ARG(((stage_off | result_off) & 15) == 0, "heap offsets must be 16-byte aligned");
+  TwoShotArgs a{src, n, stage_off, result_off, out, src_in_heap, 1.0};
+  const int grid = grid_for(n * elem_size(dtype), max_blocks);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SymmCtx c = to_ctx(h);
+  if (dtype == kCollBf16) coll_allreduce_nvls_kernel<kCollBf16><<<grid, kCollThreads, 0, s>>>(c, a);
+  else if (dtype == kCollF32) coll_allreduce_nvls_kernel<kCollF32><<<grid, kCollThreads, 0, s>>>(c, a);
+  else { set_last_error("NVLS all-reduce supports bf16 and fp32"); return kApiUnsupported; }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_rows, long long row_bytes,
+                          const void* send_counts, const void* send_offsets, unsigned long long stage_off,
+                          unsigned long long meta_off, void* out, long long out_capacity_rows,
+                          void* recv_counts, void* recv_total, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(row_bytes > 0, "row_bytes must be positive");
+  PKB_CHECK_ARG(((stage_off | meta_off) & 15) == 0, "heap offsets must be 16-byte aligned");
+  A2AVArgs a{src, src_rows, row_bytes, static_cast<const long long*>(send_counts),
+             static_cast<const long long*>(send_offsets), stage_off, meta_off, out, out_capacity_rows,
+             static_cast<long long*>(recv_counts), static_cast<long long*>(recv_total)};
+  int cap = max_blocks > 0 ? max_blocks : sm_count();
+  if (cap > kSymmMaxBlocks) cap = kSymmMaxBlocks;
+  coll_a2av_kernel<<<cap, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // extern "C"

@@ -1,0 +1,224 @@
+"""Collectives over the symmetric heap (kernels: csrc/kernels/collectives.cu).
+
+Each function is one kernel launch: stage (unless the input already lives in the heap) -> in-kernel
+barrier -> direct peer loads -> in-kernel barrier. Algorithm choice for all-reduce is by message
+size: one-shot below ``ONE_SHOT_MAX_BYTES`` (latency bound: one barrier + one remote read of every
+peer), NVLS in-switch reduction above it when the multicast mapping exists, otherwise two-shot.
+
+They cover the bare-collective workloads of the reference (reference: reference/1_allreduce.py ...
+reference/8_alltoall.py) and are the building blocks the composite ops call.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as nv
+from ..parallel.symm_heap import SymmGroup, SymmTensor
+
+ONE_SHOT_MAX_BYTES = 512 * 1024
+_DT = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2, torch.float16: 3, torch.int32: 4, torch.int64: 5}
+_OP = {"sum": 0, "max": 1, "min": 2}
+
+
+def _lib():
+    return nv.cuda_lib()
+
+
+def _stage(group: SymmGroup, key: str, x: torch.Tensor, min_bytes: int = 0) -> tuple[int, int]:
+    """Heap offset for ``x`` and how many bytes must be staged (0 when ``x`` is already in the heap)."""
+    off = group.heap.contains(x)
+    if off is not None and off % 16 == 0:
+        return off, 0
+    nbytes = max(x.numel() * x.element_size(), min_bytes)
+    cap = 1 << max(12, (max(nbytes, 1) - 1).bit_length())
+    buf = group.heap.named((key, group.channel), (cap,), torch.uint8)
+    return buf.offset, x.numel() * x.element_size()
+
+
+def _check(x: torch.Tensor) -> torch.Tensor:
+    if not x.is_cuda:
+        raise ValueError("symmetric-heap collectives need CUDA tensors")
+    return x if x.is_contiguous() else x.contiguous()
+
+
+def barrier(group: SymmGroup, blocks: int = 1) -> None:
+    nv.check(_lib().pkb_coll_barrier(group.ref, blocks, nv.current_stream()), "pkb_coll_barrier")
+    nv.count_launch()
+
+
+def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Tensor | None = None,
+               algo: str = "auto", scale: float = 1.0, max_blocks: int = 0) -> torch.Tensor:
+    x = _check(x)
+    if x.dtype not in _DT:
+        raise TypeError(f"unsupported dtype {x.dtype}")
+    if out is None:
+        out = torch.empty_like(x)
+    n = x.numel()
+    nbytes = n * x.element_size()
+    nvls_ok = (group.heap.mc_base != 0 and group.is_whole_heap and op == "sum" and scale == 1.0
+               and x.dtype in (torch.bfloat16, torch.float32))
+    if algo == "auto":
+        algo = "oneshot" if nbytes <= ONE_SHOT_MAX_BYTES or group.size == 1 else ("nvls" if nvls_ok else "twoshot")
+    off, stage_bytes = _stage(group, "ar_in", x)
+    lib = _lib()
+    if algo == "oneshot":
+        nv.check(lib.pkb_coll_reduce(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x),
+                                     nv.c_ll(n if stage_bytes else 0), ctypes.c_ulonglong(off), nv.c_ll(0),
+                                     nv.c_ll(n), nv.ptr(out), 1, ctypes.c_double(scale), max_blocks,
+                                     nv.current_stream()), "pkb_coll_reduce")
+    elif algo == "twoshot":
+        res = group.heap.named(("ar_res", group.channel), (1 << max(12, (nbytes - 1).bit_length()),), torch.uint8)
+        nv.check(lib.pkb_coll_allreduce_twoshot(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x), nv.c_ll(n),
+                                                ctypes.c_ulonglong(off), ctypes.c_ulonglong(res.offset),
+                                                nv.ptr(out), 0 if stage_bytes else 1, ctypes.c_double(scale),
+                                                max_blocks, nv.current_stream()), "pkb_coll_allreduce_twoshot")
+    elif algo == "nvls":
+        if not nvls_ok:
+            raise RuntimeError("NVLS all-reduce not available for this call (needs multicast, sum, bf16/fp32, whole job)")
+        res = group.heap.named(("ar_res", group.channel), (1 << max(12, (nbytes - 1).bit_length()),), torch.uint8)
+        nv.check(lib.pkb_coll_allreduce_nvls(group.ref, _DT[x.dtype], nv.ptr(x), nv.c_ll(n),
+                                             ctypes.c_ulonglong(off), ctypes.c_ulonglong(res.offset), nv.ptr(out),
+                                             0 if stage_bytes else 1, max_blocks, nv.current_stream()),
+                 "pkb_coll_allreduce_nvls")
+    else:
+        raise ValueError(f"unknown all-reduce algorithm {algo!r}")
+    nv.count_launch()
+    return out
+
+
+def reduce_scatter(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Tensor | None = None,
+                   scale: float = 1.0) -> torch.Tensor:
+    """``x`` is ``[W * n, ...]``; rank g receives the reduction of chunk g."""
+    x = _check(x)
+    W = group.size
+    if x.shape[0] % W != 0:
+        raise ValueError("leading dimension must be divisible by the group size")
+    n = x.numel() // W
+    if out is None:
+        out = torch.empty((x.shape[0] // W, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    off, stage_bytes = _stage(group, "rs_in", x)
+    nv.check(_lib().pkb_coll_reduce(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x),
+                                    nv.c_ll(x.numel() if stage_bytes else 0), ctypes.c_ulonglong(off),
+                                    nv.c_ll(n * group.rank_in_group), nv.c_ll(n), nv.ptr(out), 1,
+                                    ctypes.c_double(scale), 0, nv.current_stream()), "pkb_coll_reduce")
+    nv.count_launch()
+    return out
+
+
+def reduce(x: torch.Tensor, group: SymmGroup, dst: int = 0, op: str = "sum") -> torch.Tensor:
+    """Sum to group member ``dst``; other members get their input back unchanged."""
+    x = _check(x)
+    is_root = group.rank_in_group == dst
+    out = torch.empty_like(x) if is_root else x
+    off, stage_bytes = _stage(group, "red_in", x)
+    nv.check(_lib().pkb_coll_reduce(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x),
+                                    nv.c_ll(x.numel() if stage_bytes else 0), ctypes.c_ulonglong(off), nv.c_ll(0),
+                                    nv.c_ll(x.numel()), nv.ptr(out), 1 if is_root else 0, ctypes.c_double(1.0), 0,
+                                    nv.current_stream()), "pkb_coll_reduce")
+    nv.count_launch()
+    return out
+
+
+def _gather_call(group, x, mask, in_base, member_stride, seg_bytes, out, out_stride, active, key):
+    off, stage_bytes = _stage(group, key, x)
+    nv.check(_lib().pkb_coll_gather(group.ref, nv.ptr(x), nv.c_ll(stage_bytes), ctypes.c_ulonglong(off),
+                                    ctypes.c_uint(mask), nv.c_ll(in_base), nv.c_ll(member_stride),
+                                    nv.c_ll(seg_bytes), nv.ptr(out), nv.c_ll(out_stride), 1 if active else 0, 0,
+                                    nv.current_stream()), "pkb_coll_gather")
+    nv.count_launch()
+
+
+def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Returns ``[W, *x.shape]`` (member order)."""
+    x = _check(x)
+    W = group.size
+    if out is None:
+        out = torch.empty((W, *x.shape), dtype=x.dtype, device=x.device)
+    nb = x.numel() * x.element_size()
+    _gather_call(group, x, (1 << W) - 1, 0, 0, nb, out, nb, True, "ag_in")
+    return out
+
+
+def all_to_all(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x`` is ``[W, ...]``; ``out[g] = x_of_member_g[my index]``."""
+    x = _check(x)
+    W = group.size
+    if x.shape[0] != W:
+        raise ValueError("leading dimension must equal the group size")
+    if out is None:
+        out = torch.empty_like(x)
+    chunk = x[0].numel() * x.element_size()
+    _gather_call(group, x, (1 << W) - 1, 0, chunk, chunk, out, chunk, True, "a2a_in")
+    return out
+
+
+def broadcast(x: torch.Tensor, group: SymmGroup, src: int = 0) -> torch.Tensor:
+    x = _check(x)
+    out = torch.empty_like(x)
+    nb = x.numel() * x.element_size()
+    _gather_call(group, x, 1 << src, 0, 0, nb, out, nb, True, "bc_in")
+    return out
+
+
+def scatter(x: torch.Tensor, group: SymmGroup, src: int = 0) -> torch.Tensor:
+    """Member ``src`` holds ``[W, ...]``; every member receives its chunk. All members pass a
+    tensor of the full shape (only the root's content is used)."""
+    x = _check(x)
+    out = torch.empty_like(x[0])
+    chunk = x[0].numel() * x.element_size()
+    _gather_call(group, x, 1 << src, 0, chunk, chunk, out, chunk, True, "sc_in")
+    return out
+
+
+def gather(x: torch.Tensor, group: SymmGroup, dst: int = 0) -> torch.Tensor:
+    """Member ``dst`` receives ``[W, *x.shape]``; the others get their input back."""
+    x = _check(x)
+    is_root = group.rank_in_group == dst
+    W = group.size
+    out = torch.empty((W, *x.shape), dtype=x.dtype, device=x.device) if is_root else x
+    nb = x.numel() * x.element_size()
+    _gather_call(group, x, (1 << W) - 1, 0, 0, nb, out, nb, is_root, "ga_in")
+    return out
+
+
+def all_to_all_v(x: torch.Tensor, send_counts: torch.Tensor, group: SymmGroup, out_capacity_rows: int,
+                 send_offsets: torch.Tensor | None = None, max_send_rows: int | None = None):
+    """Variable all-to-all of rows. ``x`` is ``[rows, ...]`` grouped by destination, ``send_counts``
+    an int64 device tensor ``[W]``. Returns ``(out[out_capacity_rows, ...], recv_counts[W], total[1])``;
+    counts stay on the device - there is no host round trip (the reference pays one ``.tolist()``
+    per exchange, reference: reference/31_fused_moe_fwd.py:60-101). ``out_capacity_rows`` and
+    ``max_send_rows`` (default: ``out_capacity_rows``) must be the same on every rank: they size the
+    symmetric staging buffer."""
+    x = _check(x)
+    W = group.size
+    if send_counts.dtype != torch.int64 or send_counts.numel() != W:
+        raise ValueError("send_counts must be int64 [W]")
+    if send_offsets is None:
+        send_offsets = torch.cumsum(send_counts, 0) - send_counts
+    rows = x.shape[0]
+    row_elems = 1
+    for d in x.shape[1:]:
+        row_elems *= int(d)
+    row_bytes = row_elems * x.element_size()
+    max_send_rows = out_capacity_rows if max_send_rows is None else max_send_rows
+    if rows > max_send_rows:
+        raise ValueError(f"{rows} rows to send exceed max_send_rows={max_send_rows}")
+    cap = 1 << max(12, (max(max_send_rows * row_bytes, 1) - 1).bit_length())
+    stage = group.heap.named(("a2av_in", group.channel), (cap,), torch.uint8)
+    meta = group.heap.named(("a2av_meta", group.channel), (2 * 16,), torch.int64)
+    out = torch.empty((out_capacity_rows, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    recv_counts = torch.empty(W, dtype=torch.int64, device=x.device)
+    total = torch.empty(1, dtype=torch.int64, device=x.device)
+    nv.check(_lib().pkb_coll_all_to_all_v(group.ref, nv.ptr(x), nv.c_ll(rows), nv.c_ll(row_bytes),
+                                          nv.ptr(send_counts), nv.ptr(send_offsets.contiguous()),
+                                          ctypes.c_ulonglong(stage.offset), ctypes.c_ulonglong(meta.offset),
+                                          nv.ptr(out), nv.c_ll(out_capacity_rows), nv.ptr(recv_counts),
+                                          nv.ptr(total), 0, nv.current_stream()), "pkb_coll_all_to_all_v")
+    nv.count_launch()
+    return out, recv_counts, total
+
+
+__all__ = ["barrier", "all_reduce", "reduce_scatter", "reduce", "all_gather", "all_to_all", "broadcast",
+           "scatter", "gather", "all_to_all_v", "SymmTensor", "SymmGroup"]

@@ -1,0 +1,169 @@
+"""Per-rank body of the multi-GPU collective tests (launched by torchrun, one rank per GPU).
+
+Every symmetric-heap collective is compared against torch.distributed (NCCL) on the same inputs.
+Prints one ``PASS``/``FAIL`` line per case and exits non-zero if anything failed.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from parallelkernelbench_b200 import _native as nv  # noqa: E402
+from parallelkernelbench_b200.ops import collectives as C  # noqa: E402
+from parallelkernelbench_b200.parallel import init_context  # noqa: E402
+
+
+def main() -> int:
+    ctx = init_context()
+    heap = ctx.heap()
+    g = heap.world_group
+    W, r = ctx.world, ctx.rank
+    dev = ctx.device
+    fails = 0
+
+    def report(name, ok, extra=""):
+        nonlocal fails
+        if not ok:
+            fails += 1
+        if r == 0 or not ok:
+            print(f"{'PASS' if ok else 'FAIL'} rank{r} {name} {extra}", flush=True)
+
+    if r == 0:
+        print(f"heap base={heap.base:#x} stride={heap.stride:#x} mc_base={heap.mc_base:#x} world={W}", flush=True)
+    gen = torch.Generator(device=dev).manual_seed(100 + r)
+    for dtype in (torch.bfloat16, torch.float32):
+        for n in (8, 1000, 4096, 65536 + 24, 1 << 20, (1 << 22) + 8):
+            x = torch.randn(n, device=dev, dtype=dtype, generator=gen)
+            ref = x.clone()
+            dist.all_reduce(ref)
+            tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+            algos = ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else [])
+            for algo in algos:
+                if algo != "oneshot" and n % 8 != 0:
+                    continue
+                y = C.all_reduce(x, g, algo=algo)
+                torch.cuda.synchronize()
+                ok = torch.allclose(y.float(), ref.float(), atol=tol * (W ** 0.5), rtol=tol)
+                report(f"all_reduce[{algo}] {dtype} n={n}", ok, f"maxerr={(y.float() - ref.float()).abs().max().item():.3g}")
+    # max / min / int
+    x = torch.randn(4099, device=dev, generator=gen)
+    for op, rop in (("max", dist.ReduceOp.MAX), ("min", dist.ReduceOp.MIN)):
+        ref = x.clone(); dist.all_reduce(ref, op=rop)
+        report(f"all_reduce {op}", torch.equal(C.all_reduce(x, g, op=op), ref))
+    xi = torch.randint(-1000, 1000, (777,), device=dev, dtype=torch.int64, generator=gen)
+    ref = xi.clone(); dist.all_reduce(ref)
+    report("all_reduce int64", torch.equal(C.all_reduce(xi, g), ref))
+    # exactly representable inputs -> bitwise equality expected (constant rank+1 pattern)
+    xc = torch.full((1024, 1024), float(r + 1), device=dev, dtype=torch.bfloat16)
+    ref = xc.clone(); dist.all_reduce(ref)
+    for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []):
+        report(f"all_reduce[{algo}] constant 2MiB bitwise", torch.equal(C.all_reduce(xc, g, algo=algo), ref))
+
+    # all_gather
+    x = torch.randn(513, 64, device=dev, dtype=torch.bfloat16, generator=gen)
+    ref = torch.empty(W, 513, 64, device=dev, dtype=torch.bfloat16)
+    dist.all_gather_into_tensor(ref.view(W * 513, 64), x)
+    report("all_gather", torch.equal(C.all_gather(x, g), ref))
+    # reduce_scatter
+    x = torch.randn(W * 300, 40, device=dev, dtype=torch.float32, generator=gen)
+    ref = torch.empty(300, 40, device=dev)
+    dist.reduce_scatter_tensor(ref, x)
+    y = C.reduce_scatter(x, g)
+    report("reduce_scatter", torch.allclose(y, ref, atol=1e-5, rtol=1e-5))
+    # all_to_all
+    x = torch.randn(W, 1000, device=dev, dtype=torch.bfloat16, generator=gen)
+    ref = torch.empty_like(x)
+    dist.all_to_all_single(ref, x)
+    report("all_to_all", torch.equal(C.all_to_all(x, g), ref))
+    # broadcast / scatter / gather / reduce
+    x = torch.randn(3000, device=dev, generator=gen)
+    ref = x.clone(); dist.broadcast(ref, src=W - 1)
+    report("broadcast", torch.equal(C.broadcast(x, g, src=W - 1), ref))
+    x = torch.randn(W, 129, device=dev, generator=gen)
+    ref = torch.empty(129, device=dev)
+    dist.scatter(ref, list(x.unbind(0)) if r == 0 else None, src=0)
+    report("scatter", torch.equal(C.scatter(x, g, src=0), ref))
+    x = torch.randn(257, device=dev, generator=gen)
+    got = C.gather(x, g, dst=0)
+    lst = [torch.empty_like(x) for _ in range(W)] if r == 0 else None
+    dist.gather(x, lst, dst=0)
+    report("gather", torch.equal(got, torch.stack(lst)) if r == 0 else torch.equal(got, x))
+    ref = x.clone(); dist.reduce(ref, dst=0)
+    got = C.reduce(x, g, dst=0)
+    report("reduce", torch.allclose(got, ref, atol=1e-5) if r == 0 else torch.equal(got, x))
+    # all_to_all_v with uneven, rank-dependent counts (including a zero)
+    counts = torch.tensor([(3 * r + 5 * d) % 7 for d in range(W)], device=dev, dtype=torch.int64)
+    counts[(r + 1) % W] = 0 if W > 1 else counts[0]
+    rows = int(counts.sum().item())
+    x = torch.randn(rows, 24, device=dev, dtype=torch.bfloat16, generator=gen)
+    all_counts = torch.empty(W, W, device=dev, dtype=torch.int64)
+    dist.all_gather_into_tensor(all_counts, counts)
+    recv = all_counts[:, r].tolist()
+    ref = torch.empty(sum(recv), 24, device=dev, dtype=torch.bfloat16)
+    dist.all_to_all_single(ref, x, output_split_sizes=recv, input_split_sizes=counts.tolist())
+    out, rc, total = C.all_to_all_v(x, counts, g, out_capacity_rows=64)
+    torch.cuda.synchronize()
+    ok = int(total.item()) == sum(recv) and rc.tolist() == recv and torch.equal(out[:sum(recv)], ref)
+    report("all_to_all_v", ok)
+
+    # sub-groups: pairs (0,1), (2,3), ... on their own channels
+    if W >= 4:
+        pair = [r - r % 2, r - r % 2 + 1]
+        pgs = [dist.new_group([2 * i, 2 * i + 1]) for i in range(W // 2)]
+        sg = None
+        for i in range(W // 2):
+            gi = heap.group([2 * i, 2 * i + 1])
+            if r in (2 * i, 2 * i + 1):
+                sg = gi
+        x = torch.randn(5000, device=dev, generator=gen)
+        ref = x.clone(); dist.all_reduce(ref, group=pgs[r // 2])
+        report("all_reduce sub-group", torch.allclose(C.all_reduce(x, sg), ref, atol=1e-5))
+
+    # repeat-run determinism (cheap race detector)
+    x = torch.randn(1 << 18, device=dev, dtype=torch.bfloat16, generator=gen)
+    first = C.all_reduce(x, g, algo="twoshot").clone()
+    same = all(torch.equal(C.all_reduce(x, g, algo="twoshot"), first) for _ in range(20))
+    report("all_reduce twoshot determinism x20", same)
+
+    # quick timing vs NCCL (device time, max over ranks)
+    def timeit(fn, n=30, warm=10):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+    for nbytes in (4096, 65536, 1 << 20, 1 << 24, 1 << 27):
+        x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
+        y = torch.empty_like(x)
+        t_nccl = timeit(lambda: dist.all_reduce(y))
+        line = f"PERF all_reduce {nbytes}B nccl={t_nccl * 1e3:.1f}us"
+        for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []):
+            if algo == "oneshot" and nbytes > (1 << 24):
+                continue
+            t = timeit(lambda: C.all_reduce(x, g, algo=algo, out=y))
+            line += f" {algo}={t * 1e3:.1f}us"
+        if r == 0:
+            print(line, flush=True)
+
+    torch.cuda.synchronize()
+    st = nv.read_status()
+    report("device status clean", st[0] == 0, str(st[:8]))
+    tot = torch.tensor([fails], device=dev)
+    dist.all_reduce(tot)
+    ctx.finalize()
+    if r == 0:
+        print("TOTAL_FAILS", int(tot.item()), flush=True)
+    return 1 if tot.item() else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
