@@ -62,10 +62,12 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + align slack
 };
 
+// Body of one GEMM CTA. `cta` / `num_ctas` are this CTA's index and the number of CTAs that share
+// the tile loop (a fused kernel may reserve some of its grid for communication roles).
 template <int BN, int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
-__global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+__device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                              const GemmParams& p, const int cta,
+                                              const int num_ctas) {
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   constexpr uint32_t kTmemCols = 2 * BN;  // two accumulator buffers (power of two: 256 or 512)
@@ -135,7 +137,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
         int m_blk, n_blk;
         tile_coords(tile, m_blk, n_blk);
         if constexpr (A_READY) {
@@ -177,7 +179,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) {
           record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
           break;
@@ -219,7 +221,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int q = warp & 3;  // TMEM lane quadrant this warp may access
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    for (int tile = cta; tile < num_tiles; tile += num_ctas) {
       int m_blk, n_blk;
       tile_coords(tile, m_blk, n_blk);
       bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_budget_ns);
@@ -333,6 +335,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+template <int BN, int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                 const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma_cta<BN, EPI, OUT_F32, A_READY, RS_SCATTER>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
 }
 
 }  // namespace pkb

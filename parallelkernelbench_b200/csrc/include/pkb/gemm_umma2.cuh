@@ -1,0 +1,300 @@
+// CTA-pair variant of the persistent tcgen05 GEMM: two CTAs of a cluster share one 256 x 256
+// output tile (tcgen05.mma.cta_group::2, M = 256). Each CTA loads its own 128 rows of A and its own
+// 128 rows (output features) of B, so every operand byte crosses L2 -> shared memory once per pair
+// instead of once per CTA, and the smaller per-CTA stage (32 KiB) leaves room for a six-deep ring.
+//   warp 0 (both CTAs): TMA producer; completion bytes of both CTAs land on the leader's barrier
+//   warp 1 (leader)   : MMA issuer; commits arrive on both CTAs' barriers
+//   warps 2-5 (both)  : epilogue of the CTA's own 128 accumulator rows
+// Hooks (a_ready flags, row-block scatter) and bounded waits are the same as in gemm_umma.cuh.
+#pragma once
+#include "pkb/gemm_umma.cuh"
+
+namespace pkb {
+
+constexpr int kGemm2TileM = 256;
+constexpr int kGemm2TileN = 256;
+constexpr int kGemm2Stages = 6;
+constexpr int kGemm2ABytes = 128 * kGemmBlockK * 2;   // this CTA's half of A
+constexpr int kGemm2BBytes = 128 * kGemmBlockK * 2;   // this CTA's half of B
+constexpr int kGemm2StageBytes = kGemm2ABytes + kGemm2BBytes;
+constexpr int kGemm2SmemTotal = kGemm2Stages * kGemm2StageBytes + 256 + 1024;
+
+template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
+__device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                                               const GemmParams& p, const int pair,
+                                               const int num_pairs) {
+  constexpr int kStages = kGemm2Stages;
+  constexpr int BN = kGemm2TileN;
+  constexpr uint32_t kTmemCols = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * kGemm2StageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_holder =
+      reinterpret_cast<uint32_t*>(smem_gen + kStages * kGemm2StageBytes + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+
+  const int num_m = (p.M + kGemm2TileM - 1) / kGemm2TileM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_k = (p.K + kGemmBlockK - 1) / kGemmBlockK;
+  const int group_m = p.group_m > 0 ? p.group_m : 8;
+
+  auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+    const int tiles_per_group = group_m * num_n;
+    const int g = tile / tiles_per_group;
+    const int first_m = g * group_m;
+    const int gm = min(group_m, num_m - first_m);
+    const int local = tile - g * tiles_per_group;
+    n_blk = local / gm;
+    m_blk = first_m + (local - n_blk * gm) + p.m_block_rotation;
+    if (m_blk >= num_m) m_blk -= num_m;
+  };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full_bar(s), 1);   // leader's producer arrives (expect_tx of both CTAs' bytes)
+      mbar_init(empty_bar(s), 1);  // one commit arrival, delivered to both CTAs
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);  // four epilogue warps of each CTA
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_holder), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both CTAs) ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int m_blk, n_blk;
+        tile_coords(tile, m_blk, n_blk);
+        const int row0 = m_blk * kGemm2TileM + (int)cta_rank * 128;
+        const int col0 = n_blk * BN + (int)cta_rank * 128;
+        if constexpr (A_READY) {
+          int chunk = row0 / p.a_chunk_rows;
+          const int last_chunk = (p.M - 1) / p.a_chunk_rows;
+          if (chunk > last_chunk) chunk = last_chunk;
+          if (!wait_flag_ge(p.a_ready + chunk, p.a_ready_epoch, p.wait_budget_ns)) {
+            *abort_flag = 1;
+            record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
+            ok = false;
+            break;
+          }
+          fence_proxy_async_all();
+        }
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_budget_ns)) {
+            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 11, tile);
+            ok = false;
+            break;
+          }
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * kGemm2StageBytes);
+          const uint32_t sa = smem_base + stage * kGemm2StageBytes;
+          tma_load_2d_pair(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+          tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc(kGemm2TileM, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) {
+          record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.wait_budget_ns)) {
+            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 21, tile);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_base + stage * kGemm2StageBytes;
+          const uint64_t da = make_smem_desc_sw128_kmajor(sa);
+          const uint64_t db = make_smem_desc_sw128_kmajor(sa + kGemm2ABytes);
+#pragma unroll
+          for (int k = 0; k < kGemmBlockK / 16; ++k)
+            umma_f16_ss_pair(tmem_d, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit_pair(empty_bar(stage), 0x3);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc), 0x3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ epilogue (warps 2..5, both CTAs) ------------------------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t leader_tempty0 = mapa_shared(tempty_bar(0), 0);
+    const uint32_t leader_tempty1 = mapa_shared(tempty_bar(1), 0);
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      int m_blk, n_blk;
+      tile_coords(tile, m_blk, n_blk);
+      bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0)
+          record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 30, tile);
+        break;
+      }
+      tc_fence_after_sync();
+      const int row_blk0 = m_blk * kGemm2TileM + (int)cta_rank * 128;
+      const int row = row_blk0 + q * 32 + lane;
+      const int n0 = n_blk * BN;
+      uint8_t* out_row;
+      constexpr int kOutBytes = OUT_F32 ? 4 : 2;
+      if constexpr (RS_SCATTER) {
+        const int owner = row / p.rs_rows_per_rank;
+        const int r_in = row - owner * p.rs_rows_per_rank;
+        out_row = static_cast<uint8_t*>(p.rs_out[owner < p.world ? owner : 0]) +
+                  static_cast<long long>(r_in) * p.ldc * kOutBytes;
+      } else {
+        out_row = static_cast<uint8_t*>(p.C) + static_cast<long long>(row) * p.ldc * kOutBytes;
+      }
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                               static_cast<uint32_t>(acc * BN + c * 32);
+        tmem_ld_32x32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+          if constexpr (EPI == kEpiBias || EPI == kEpiBiasSilu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+          }
+          if constexpr (EPI == kEpiSilu || EPI == kEpiBiasSilu) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
+          }
+          if constexpr (OUT_F32) {
+            float* o = reinterpret_cast<float*>(out_row) + col0;
+            if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                U4 u{__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]),
+                     __float_as_uint(v[j + 3])};
+                st_global_v4(o + j, u);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) o[j] = v[j];
+            }
+          } else {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + col0;
+            if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                U4 u{pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                     pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7])};
+                st_global_v4(o + j, u);
+              }
+            } else {
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc == 0 ? leader_tempty0 : leader_tempty1);
+
+      if constexpr (RS_SCATTER) {
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) {
+          const int owner = row_blk0 / p.rs_rows_per_rank;
+          if (owner < p.world && row_blk0 < p.M) {
+            const int blk_in_rank = (row_blk0 - owner * p.rs_rows_per_rank) / kGemmBlockM;
+            red_release_sys_add(p.rs_done[owner] + blk_in_rank, 1u);
+          }
+        }
+      }
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  // neither CTA may leave (or free TMEM) while the other can still signal its barriers
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_umma2_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma2_cta<EPI, OUT_F32, A_READY, RS_SCATTER>(tmap_a, tmap_b, p, blockIdx.x >> 1,
+                                                    gridDim.x >> 1);
+}
+
+}  // namespace pkb

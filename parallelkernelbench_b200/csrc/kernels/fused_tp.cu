@@ -1,0 +1,325 @@
+// Fused tensor-parallel kernels: the collective runs inside the GEMM kernel, over peer memory.
+//
+//  tp_ag_gemm       all-gather -> GEMM (+SiLU). A few CTAs of the persistent grid are communication
+//                   CTAs: they push this rank's activation shard into every peer's gather buffer
+//                   with 16-byte P2P stores, sub-block by sub-block, and publish one flag per
+//                   sub-block with a system-scope release. The other CTAs are the tcgen05 GEMM; its
+//                   TMA producer waits (bounded) for the flag of the rows it is about to load and
+//                   starts with the local shard, so the transfer hides behind the math.
+//  tp_gemm_rs_rmsnorm  GEMM -> reduce-scatter -> RMSNorm. The GEMM walks row blocks in destination
+//                   order (rank+1 first, own rows last); its epilogue stores each partial tile
+//                   straight into the owner's receive slot and bumps a per-row-block counter there.
+//                   After its tiles, every CTA turns into a consumer: it waits for the counters of
+//                   its rows, adds the W partial slots in rank order in fp32, applies RMSNorm and
+//                   writes bf16 - the reduced tensor never exists un-normalised in memory.
+//
+// Reference behaviour being replaced: all_gather + matmul + silu, matmul + reduce_scatter, and
+// reduce_scatter + RMSNorm as separate NCCL / cuBLAS / elementwise launches
+// (reference: reference/15_combined_sharded_gemms.py:17-31, reference/16_gemm_reducescatter.py:19-22,
+//  reference/45_reducescatter_fused_rmsnorm.py:23-29).
+#include "pkb/api.h"
+#include "pkb/collectives_api.h"
+#include "pkb/gemm_umma.cuh"
+#include "pkb/host.h"
+#include "pkb/symm.cuh"
+
+namespace pkb {
+
+struct TpAgArgs {
+  SymmCtx ctx;
+  const uint8_t* x_local;  // this rank's shard, rows x K bf16, contiguous
+  uint64_t gather_off;     // heap offset of the gather buffer [gsize * rows, K]
+  uint64_t flags_off;      // heap offset of the readiness flags [gsize * sub_per_shard] (uint32)
+  long long sub_bytes;     // bytes of one sub-block (a_chunk_rows * K * 2)
+  int sub_per_shard;
+  uint32_t epoch;
+  int local_in_place;      // x_local already is the local slice of the gather buffer
+  int comm_ctas;
+};
+
+__device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
+  const SymmCtx& c = a.ctx;
+  // every rank has entered this call, so every rank has finished reading the previous gather
+  if (!symm_block_barrier(c, 300, 1)) return;
+  const int W = c.gsize;
+  const int total_items = W * a.sub_per_shard;
+  for (int item = blockIdx.x; item < total_items; item += a.comm_ctas) {
+    const int step = item / a.sub_per_shard;
+    const int sb = item - step * a.sub_per_shard;
+    int dest_g = c.grank - step;
+    if (dest_g < 0) dest_g += W;
+    const int dest = c.members[dest_g];
+    const int chunk = c.grank * a.sub_per_shard + sb;
+    if (!(step == 0 && a.local_in_place)) {
+      const uint8_t* src = a.x_local + (long long)sb * a.sub_bytes;
+      uint8_t* dst = symm_ptr<uint8_t>(c, dest, a.gather_off) + (long long)chunk * a.sub_bytes;
+      const long long nvec = a.sub_bytes >> 4;
+      long long i = threadIdx.x;
+      // four independent 16-byte loads in flight per thread
+      for (; i + 3ll * blockDim.x < nvec; i += 4ll * blockDim.x) {
+        U4 v0 = ld_global_nc_v4(src + (i << 4));
+        U4 v1 = ld_global_nc_v4(src + ((i + blockDim.x) << 4));
+        U4 v2 = ld_global_nc_v4(src + ((i + 2ll * blockDim.x) << 4));
+        U4 v3 = ld_global_nc_v4(src + ((i + 3ll * blockDim.x) << 4));
+        st_global_v4(dst + (i << 4), v0);
+        st_global_v4(dst + ((i + blockDim.x) << 4), v1);
+        st_global_v4(dst + ((i + 2ll * blockDim.x) << 4), v2);
+        st_global_v4(dst + ((i + 3ll * blockDim.x) << 4), v3);
+      }
+      for (; i < nvec; i += blockDim.x) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      st_release_sys(symm_ptr<uint32_t>(c, dest, a.flags_off) + chunk, a.epoch);
+    }
+  }
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p, const TpAgArgs a) {
+  if ((int)blockIdx.x < a.comm_ctas) {
+    ag_push_role(a);
+    return;
+  }
+  gemm_umma_cta<BN, EPI, false, true, false>(tmap_a, tmap_b, p, blockIdx.x - a.comm_ctas,
+                                             gridDim.x - a.comm_ctas);
+}
+
+struct TpRsArgs {
+  SymmCtx ctx;
+  uint64_t recv_off;     // heap offset of the receive slots [gsize][rows_per_rank, N] bf16
+  uint64_t done_off;     // heap offset of the per-row-block arrival counters (uint32)
+  uint32_t done_target;  // cumulative arrivals expected per row block once this call is complete
+  const __nv_bfloat16* gamma;
+  __nv_bfloat16* out;    // [rows_per_rank, N]
+  float eps;
+  float scale;
+  int N;
+  int rows_per_rank;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                          const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
+                          const TpRsArgs a) {
+  const SymmCtx& c = a.ctx;
+  // all ranks have entered this call => all ranks have consumed the previous call's receive slots
+  if (!symm_block_barrier(c, 301, 1)) return;
+  gemm_umma_cta<BN, kEpiNone, false, false, true>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
+  __syncthreads();
+
+  // ---- consumer phase: reduce the W partial slots of my rows and normalise --------------------
+  extern __shared__ uint8_t smem_raw[];
+  float* rowbuf = reinterpret_cast<float*>(smem_raw);
+  __shared__ float red[8];
+  __shared__ int s_ok;
+  const uint32_t* done = symm_local<uint32_t>(c, a.done_off);
+  const __nv_bfloat16* slots = symm_local<__nv_bfloat16>(c, a.recv_off);
+  const long long slot_stride = (long long)a.rows_per_rank * a.N;
+  int waited_blk = -1;
+  const int nthreads = blockDim.x;
+  for (int row = blockIdx.x; row < a.rows_per_rank; row += gridDim.x) {
+    const int blk = row / kGemmBlockM;
+    if (blk != waited_blk) {
+      if (threadIdx.x == 0) {
+        s_ok = wait_flag_ge(done + blk, a.done_target, c.budget_ns) ? 1 : 0;
+        if (!s_ok) record_status(c.status, kStatusPeerTimeout, 301, c.rank, blk, 2, row);
+      }
+      __syncthreads();
+      if (!s_ok) return;
+      waited_blk = blk;
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int g = 0; g < c.gsize; ++g) {
+        // peers wrote these rows with plain stores followed by a release; read them coherently
+        U4 u = ld_global_relaxed_v4(slots + g * slot_stride + (long long)row * a.N + i);
+        float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+               f3 = unpack_bf16x2(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j] *= a.scale;
+        rowbuf[i + j] = acc[j];
+        ss += acc[j] * acc[j];
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.f;
+    for (int w = 0; w < (nthreads >> 5); ++w) total += red[w];
+    const float rstd = rsqrtf(total / (float)a.N + a.eps);
+    __nv_bfloat16* yrow = a.out + (long long)row * a.N;
+    for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
+      U4 g = ld_global_v4(a.gamma + i);
+      float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z),
+             g3 = unpack_bf16x2(g.w);
+      U4 o;
+      o.x = pack_bf16x2(rowbuf[i] * rstd * g0.x, rowbuf[i + 1] * rstd * g0.y);
+      o.y = pack_bf16x2(rowbuf[i + 2] * rstd * g1.x, rowbuf[i + 3] * rstd * g1.y);
+      o.z = pack_bf16x2(rowbuf[i + 4] * rstd * g2.x, rowbuf[i + 5] * rstd * g2.y);
+      o.w = pack_bf16x2(rowbuf[i + 6] * rstd * g3.x, rowbuf[i + 7] * rstd * g3.y);
+      st_global_v4(yrow + i, o);
+    }
+    __syncthreads();
+  }
+}
+
+static SymmCtx ctx_from(const pkb_symm_ctx* h) {
+  SymmCtx c;
+  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
+  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
+  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
+  c.channel = h->channel;
+  c.status = status_block_device_ptr();
+  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
+  return c;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+extern "C" {
+
+// C[gsize*rows, N] = epi( allgather(x_local)[gsize*rows, K] @ w[N, K]^T ), C local bf16.
+// gather_off / flags_off: heap offsets of the gather buffer (gsize*rows*K bf16) and of
+// gsize * (rows / a_chunk_rows) uint32 flags. `epoch` must grow by one on every call (same value
+// on all ranks). comm_ctas CTAs of the grid push the shard to the peers.
+int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
+                   unsigned long long gather_off, unsigned long long flags_off, int a_chunk_rows,
+                   unsigned int epoch, const void* w, long long ldb, void* c, long long ldc, int N,
+                   int epilogue, int comm_ctas, void* stream) {
+  PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
+  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kGemmMaxWorld, "group size must be 1..8");
+  PKB_CHECK_ARG(rows > 0 && K % 8 == 0 && N > 0, "bad shapes");
+  PKB_CHECK_ARG(a_chunk_rows % kGemmBlockM == 0 && rows % a_chunk_rows == 0,
+                "a_chunk_rows must be a multiple of 128 that divides rows");
+  PKB_CHECK_ARG(epilogue == kEpiNone || epilogue == kEpiSilu, "epilogue must be none or silu");
+  PKB_CHECK_ARG((gather_off & 1023) == 0 && (flags_off & 15) == 0, "heap offsets misaligned");
+  const int W = h->gsize;
+  const int M = W * rows;
+  SymmCtx ctx = ctx_from(h);
+  uint8_t* g_local = reinterpret_cast<uint8_t*>(h->base + (uint64_t)h->rank * h->stride + gather_off);
+
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, g_local, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
+                          kGemmBlockK, kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 256,
+                      kSwizzle128);
+  if (rc) return rc;
+
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.C = c; p.ldc = ldc; p.alpha = 1.0f;
+  p.status = ctx.status; p.wait_budget_ns = ctx.budget_ns;
+  p.kernel_id = 300;
+  p.rank = h->rank; p.world = W;
+  p.a_ready = reinterpret_cast<const uint32_t*>(h->base + (uint64_t)h->rank * h->stride + flags_off);
+  p.a_ready_epoch = epoch;
+  p.a_chunk_rows = a_chunk_rows;
+  const int blocks_per_shard = rows / kGemmBlockM;
+  p.group_m = blocks_per_shard < 16 ? blocks_per_shard : 16;
+  // keep whole shards inside rasterisation groups when possible
+  while (blocks_per_shard % p.group_m != 0) --p.group_m;
+  p.m_block_rotation = h->grank * blocks_per_shard;  // local rows first, then rank+1, ...
+
+  TpAgArgs a;
+  a.ctx = ctx;
+  a.x_local = static_cast<const uint8_t*>(x_local);
+  a.gather_off = gather_off; a.flags_off = flags_off;
+  a.sub_bytes = (long long)a_chunk_rows * K * 2;
+  a.sub_per_shard = rows / a_chunk_rows;
+  a.epoch = epoch;
+  a.local_in_place = (x_local == g_local + (long long)h->grank * rows * K * 2) ? 1 : 0;
+  if (comm_ctas <= 0) comm_ctas = W > 1 ? 16 : 1;
+  const int sms = sm_count();
+  PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");
+  a.comm_ctas = comm_ctas;
+
+  constexpr int smem = GemmSmem<256>::kTotal;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (epilogue == kEpiSilu) {
+    auto k = tp_ag_gemm_kernel<256, kEpiSilu>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, p, a);
+  } else {
+    auto k = tp_ag_gemm_kernel<256, kEpiNone>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, p, a);
+  }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// out[rows_per_rank, N] = RMSNorm( reduce_scatter( a[gsize*rows_per_rank, K] @ w[N, K]^T ) * scale )
+// recv_off: heap offset of gsize receive slots of rows_per_rank*N bf16; done_off: heap offset of
+// rows_per_rank/128 uint32 counters; call_index counts calls on these buffers starting at 1.
+int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long lda, const void* w,
+                           long long ldb, int rows_per_rank, int N, int K,
+                           unsigned long long recv_off, unsigned long long done_off,
+                           unsigned int call_index, const void* gamma, void* out, float eps,
+                           float scale, void* stream) {
+  PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
+  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kGemmMaxWorld, "group size must be 1..8");
+  PKB_CHECK_ARG(rows_per_rank % kGemmBlockM == 0, "rows_per_rank must be a multiple of 128");
+  PKB_CHECK_ARG(N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "N, K, lda, ldb must be multiples of 8");
+  PKB_CHECK_ARG(N * 4 <= GemmSmem<256>::kTotal, "row too long for the shared-memory row buffer");
+  PKB_CHECK_ARG((recv_off & 15) == 0 && (done_off & 15) == 0, "heap offsets misaligned");
+  const int W = h->gsize;
+  const int M = W * rows_per_rank;
+  SymmCtx ctx = ctx_from(h);
+
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a_mat, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
+                          kGemmBlockK, kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 256,
+                      kSwizzle128);
+  if (rc) return rc;
+
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = N; p.alpha = 1.0f;
+  p.status = ctx.status; p.wait_budget_ns = ctx.budget_ns;
+  p.kernel_id = 301;
+  p.rank = h->rank; p.world = W;
+  p.rs_rows_per_rank = rows_per_rank;
+  const long long slot_bytes = (long long)rows_per_rank * N * 2;
+  for (int g = 0; g < W; ++g) {
+    const uint64_t peer = h->base + (uint64_t)h->members[g] * h->stride;
+    p.rs_out[g] = reinterpret_cast<void*>(peer + recv_off + (uint64_t)h->grank * slot_bytes);
+    p.rs_done[g] = reinterpret_cast<uint32_t*>(peer + done_off);
+  }
+  const int blocks_per_rank = rows_per_rank / kGemmBlockM;
+  p.group_m = blocks_per_rank < 16 ? blocks_per_rank : 16;
+  while (blocks_per_rank % p.group_m != 0) --p.group_m;
+  p.m_block_rotation = ((h->grank + 1) % W) * blocks_per_rank;  // rank+1's rows first, own rows last
+
+  const int num_n = (N + 255) / 256;
+  TpRsArgs a;
+  a.ctx = ctx;
+  a.recv_off = recv_off; a.done_off = done_off;
+  a.done_target = call_index * (uint32_t)(W * num_n * 4);
+  a.gamma = static_cast<const __nv_bfloat16*>(gamma);
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.eps = eps; a.scale = scale; a.N = N; a.rows_per_rank = rows_per_rank;
+
+  constexpr int smem = GemmSmem<256>::kTotal;
+  auto k = tp_gemm_rs_rmsnorm_kernel<256>;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int grid = sm_count();
+  if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
+  k<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, p, a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // extern "C"

@@ -1,6 +1,6 @@
 // Host launchers of the tcgen05 GEMM (kernel template in pkb/gemm_umma.cuh).
 #include "pkb/api.h"
-#include "pkb/gemm_umma.cuh"
+#include "pkb/gemm_umma2.cuh"
 #include "pkb/host.h"
 
 namespace pkb {
@@ -33,9 +33,67 @@ static int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, c
   return kApiBadArgument;
 }
 
+template <int EPI, bool OUT_F32>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                       int num_ctas, cudaStream_t stream) {
+  auto kern = gemm_umma2_kernel<EPI, OUT_F32, false, false>;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kGemm2SmemTotal));
+  kern<<<num_ctas, kGemmThreads, kGemm2SmemTotal, stream>>>(ta, tb, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+template <bool OUT_F32>
+static int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                         int num_ctas, cudaStream_t stream) {
+  switch (epi) {
+    case kEpiNone: return launch_pair<kEpiNone, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiSilu: return launch_pair<kEpiSilu, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiBias: return launch_pair<kEpiBias, OUT_F32>(ta, tb, p, num_ctas, stream);
+    case kEpiBiasSilu: return launch_pair<kEpiBiasSilu, OUT_F32>(ta, tb, p, num_ctas, stream);
+  }
+  set_last_error("unknown epilogue");
+  return kApiBadArgument;
+}
+
 }  // namespace pkb
 
 using namespace pkb;
+
+// CTA-pair form: 256 x 256 tiles on clusters of two CTAs (see pkb/gemm_umma2.cuh).
+extern "C" int pkb_gemm_bf16_pair(const void* a, long long lda, const void* b, long long ldb,
+                                  void* c, long long ldc, int M, int N, int K, const void* bias,
+                                  float alpha, int epilogue, int out_f32, int num_ctas,
+                                  void* stream) {
+  PKB_CHECK_ARG(M > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && K % 8 == 0, "lda, ldb, K must be multiples of 8");
+  PKB_CHECK_ARG((epilogue & 2) == 0 || bias != nullptr, "bias epilogue without bias");
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
+                          kGemmBlockK, 128, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK,
+                      128, kSwizzle128);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K;
+  p.C = c; p.ldc = ldc;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.alpha = alpha;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.group_m = 8;
+  p.kernel_id = 101;
+  p.world = 1;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int ctas = num_ctas > 0 ? num_ctas : sm_count();
+  ctas &= ~1;
+  if (ctas > 2 * tiles) ctas = 2 * tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return out_f32 ? dispatch_pair<true>(epilogue, ta, tb, p, ctas, s)
+                 : dispatch_pair<false>(epilogue, ta, tb, p, ctas, s);
+}
 
 extern "C" int pkb_gemm_bf16(const void* a, long long lda, const void* b, long long ldb, void* c,
                              long long ldc, int M, int N, int K, const void* bias, float alpha,

@@ -19,7 +19,8 @@ EPILOGUES = {"none": 0, "silu": 1, "bias": 2, "bias_silu": 3}
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = None,
               bias: torch.Tensor | None = None, epilogue: str = "none", alpha: float = 1.0,
-              out_dtype: torch.dtype = torch.bfloat16, block_n: int = 0, num_ctas: int = 0) -> torch.Tensor:
+              out_dtype: torch.dtype = torch.bfloat16, block_n: int = 0, num_ctas: int = 0,
+              mode: str = "auto") -> torch.Tensor:
     """``out[M, N] = epilogue(alpha * a[M, K] @ w[N, K].T + bias)`` with fp32 accumulation."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise TypeError("gemm_bf16 expects bf16 operands")
@@ -38,6 +39,16 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, *, out: torch.Tensor | None = No
         if bias.dtype != torch.bfloat16 or bias.numel() != N:
             raise ValueError("bias must be bf16 [N]")
     lib = nv.cuda_lib()
+    if mode == "auto":
+        mode = "pair" if (block_n == 0 and M >= 512 and N >= 256) else "single"
+    if mode == "pair":
+        nv.check(lib.pkb_gemm_bf16_pair(nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(w.stride(0)),
+                                        nv.ptr(out), nv.c_ll(out.stride(0)), M, N, K, nv.ptr(bias),
+                                        nv.c_float(alpha), EPILOGUES[epilogue],
+                                        1 if out.dtype == torch.float32 else 0, num_ctas, nv.current_stream()),
+                 "pkb_gemm_bf16_pair")
+        nv.count_launch()
+        return out
     nv.check(lib.pkb_gemm_bf16(nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(w.stride(0)), nv.ptr(out),
                                nv.c_ll(out.stride(0)), M, N, K, nv.ptr(bias), nv.c_float(alpha),
                                EPILOGUES[epilogue], 1 if out.dtype == torch.float32 else 0, block_n, num_ctas,

@@ -1,0 +1,89 @@
+"""Fused tensor-parallel GEMM + collective ops (kernels: csrc/kernels/fused_tp.cu).
+
+``AllGatherGemm``    all-gather(x) @ w.T (+SiLU) in one launch: communication CTAs push the shard to
+                     the peers while the tcgen05 GEMM consumes row chunks as their flags arrive.
+``GemmReduceScatterRMSNorm``  (a @ w.T) reduce-scattered over rows, then RMSNorm, in one launch: the
+                     GEMM epilogue stores partial tiles into the owner's receive slots over NVLink.
+
+Both keep their symmetric buffers between calls (steady-state calls allocate nothing), like the
+module-level buffer caches of the reference's example solutions
+(reference: kernelgen/solution_new_add_cuda.py:70-84) but owned by an object instead of globals.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as nv
+from ..parallel.symm_heap import SymmGroup
+
+
+class AllGatherGemm:
+    def __init__(self, group: SymmGroup, rows: int, k: int, chunk_rows: int = 256, comm_ctas: int = 0):
+        if rows % 128 != 0:
+            raise ValueError("rows per rank must be a multiple of 128")
+        while rows % chunk_rows != 0:
+            chunk_rows //= 2
+        self.group, self.rows, self.k, self.chunk_rows, self.comm_ctas = group, rows, k, chunk_rows, comm_ctas
+        W = group.size
+        heap = group.heap
+        self.gather = heap.empty((W * rows, k), torch.bfloat16)
+        self.flags = heap.empty((W * (rows // chunk_rows),), torch.int32)
+        self.flags.local.zero_()
+        self.epoch = 0
+
+    @property
+    def x_slot(self) -> torch.Tensor:
+        """This rank's rows of the gather buffer: fill it directly to skip the local copy."""
+        r = self.group.rank_in_group
+        return self.gather.local[r * self.rows:(r + 1) * self.rows]
+
+    def __call__(self, x_local: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None,
+                 epilogue: str = "none") -> torch.Tensor:
+        W = self.group.size
+        if x_local.shape != (self.rows, self.k) or x_local.dtype != torch.bfloat16 or not x_local.is_contiguous():
+            raise ValueError("x_local must be a contiguous bf16 [rows, k] tensor")
+        if w.dtype != torch.bfloat16 or w.shape[1] != self.k or w.stride(1) != 1:
+            raise ValueError("w must be bf16 [N, k], contiguous along k")
+        n = w.shape[0]
+        if out is None:
+            out = torch.empty((W * self.rows, n), dtype=torch.bfloat16, device=x_local.device)
+        self.epoch += 1
+        nv.check(nv.cuda_lib().pkb_tp_ag_gemm(
+            self.group.ref, nv.ptr(x_local), self.rows, self.k, ctypes.c_ulonglong(self.gather.offset),
+            ctypes.c_ulonglong(self.flags.offset), self.chunk_rows, ctypes.c_uint(self.epoch), nv.ptr(w),
+            nv.c_ll(w.stride(0)), nv.ptr(out), nv.c_ll(out.stride(0)), n, {"none": 0, "silu": 1}[epilogue],
+            self.comm_ctas, nv.current_stream()), "pkb_tp_ag_gemm")
+        nv.count_launch()
+        return out
+
+
+class GemmReduceScatterRMSNorm:
+    def __init__(self, group: SymmGroup, rows_per_rank: int, n: int):
+        if rows_per_rank % 128 != 0:
+            raise ValueError("rows per rank must be a multiple of 128")
+        self.group, self.rows, self.n = group, rows_per_rank, n
+        heap = group.heap
+        self.recv = heap.empty((group.size, rows_per_rank, n), torch.bfloat16)
+        self.done = heap.empty((max(rows_per_rank // 128, 4),), torch.int32)
+        self.done.local.zero_()
+        self.calls = 0
+
+    def __call__(self, a: torch.Tensor, w: torch.Tensor, gamma: torch.Tensor, eps: float = 1e-6,
+                 scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+        W = self.group.size
+        if a.shape[0] != W * self.rows or a.dtype != torch.bfloat16 or a.stride(1) != 1:
+            raise ValueError("a must be bf16 [W * rows_per_rank, K]")
+        if w.shape != (self.n, a.shape[1]) or w.stride(1) != 1:
+            raise ValueError("w must be [N, K]")
+        if out is None:
+            out = torch.empty((self.rows, self.n), dtype=torch.bfloat16, device=a.device)
+        self.calls += 1
+        nv.check(nv.cuda_lib().pkb_tp_gemm_rs_rmsnorm(
+            self.group.ref, nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(w.stride(0)), self.rows, self.n,
+            a.shape[1], ctypes.c_ulonglong(self.recv.offset), ctypes.c_ulonglong(self.done.offset),
+            ctypes.c_uint(self.calls), nv.ptr(gamma), nv.ptr(out), nv.c_float(eps), nv.c_float(scale),
+            nv.current_stream()), "pkb_tp_gemm_rs_rmsnorm")
+        nv.count_launch()
+        return out

@@ -1,0 +1,85 @@
+"""Per-rank body of the tensor-parallel MLP test: fused kernels vs the PyTorch+NCCL reference."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from parallelkernelbench_b200 import _native as nv  # noqa: E402
+from parallelkernelbench_b200.models import TPMLPBlock, TPMLPConfig  # noqa: E402
+from parallelkernelbench_b200.parallel import init_context  # noqa: E402
+from parallelkernelbench_b200.refs.tp_mlp import TPMLPReference  # noqa: E402
+
+
+def main() -> int:
+    full = "--full" in sys.argv
+    ctx = init_context()
+    heap = ctx.heap()
+    g = heap.world_group
+    W, r, dev = ctx.world, ctx.rank, ctx.device
+    fails = 0
+    shapes = [(256, 512, 1024 * W), (384, 1024, 512 * W)]
+    if full:
+        shapes.append((2048, 8192, 28672))
+    for rows, hidden, ffn in shapes:
+        cfg = TPMLPConfig(rows_per_rank=rows, hidden=hidden, ffn=ffn)
+        w1, w2, gamma = TPMLPBlock.random_weights(cfg, W, r, dev)
+        gamma = (1 + 0.1 * torch.randn(hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(5))).to(torch.bfloat16)
+        mark = heap.mark()
+        blk = TPMLPBlock(g, cfg, w1, w2, gamma)
+        ref = TPMLPReference(W, rows, hidden, w1, w2, gamma, cfg.eps)
+        for trial in range(3):
+            x = torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16,
+                            generator=torch.Generator(device=dev).manual_seed(77 + trial * 10 + r))
+            y = blk(x).clone()
+            y_ref = ref(x)
+            torch.cuda.synchronize()
+            err = (y.float() - y_ref.float()).abs().max().item()
+            ok = torch.allclose(y.float(), y_ref.float(), atol=3e-2, rtol=3e-2)
+            fails += 0 if ok else 1
+            print(f"{'PASS' if ok else 'FAIL'} rank{r} tp_mlp rows={rows} hidden={hidden} ffn={ffn} trial={trial} maxerr={err:.4g}", flush=True)
+        # zero-copy input path + determinism
+        blk.x_slot.copy_(x)
+        y2 = blk(blk.x_slot).clone()
+        same = torch.equal(y2, y)
+        fails += 0 if same else 1
+        print(f"{'PASS' if same else 'FAIL'} rank{r} tp_mlp in-place input bitwise equal", flush=True)
+
+        def timeit(fn, n=20, warm=5):
+            for _ in range(warm):
+                fn()
+            torch.cuda.synchronize(); dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(n):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / n], device=dev)
+            if W > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+        t_ours = timeit(lambda: blk(x))
+        t_ref = timeit(lambda: ref(x))
+        if r == 0:
+            fl = 4.0 * rows * W * hidden * (ffn // W)
+            print(f"PERF tp_mlp rows={rows} hidden={hidden} ffn={ffn} W={W}: ours {t_ours:.3f} ms ({fl / t_ours / 1e9:.0f} TF/s/gpu) ref {t_ref:.3f} ms speedup {t_ref / t_ours:.2f}x", flush=True)
+        del blk, ref
+        heap.release(mark)
+    torch.cuda.synchronize()
+    st = nv.read_status()
+    if st[0] != 0:
+        fails += 1
+        print(f"FAIL rank{r} device status {st[:8]}", flush=True)
+    tot = torch.tensor([fails], device=dev)
+    if W > 1:
+        dist.all_reduce(tot)
+    ctx.finalize()
+    if r == 0:
+        print("TOTAL_FAILS", int(tot.item()), flush=True)
+    return 1 if tot.item() else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
