@@ -17,12 +17,21 @@ constexpr int kGemm2Stages = 6;
 constexpr int kGemm2ABytes = 128 * kGemmBlockK * 2;   // this CTA's half of A
 constexpr int kGemm2BBytes = 128 * kGemmBlockK * 2;   // this CTA's half of B
 constexpr int kGemm2StageBytes = kGemm2ABytes + kGemm2BBytes;
-constexpr int kGemm2SmemTotal = kGemm2Stages * kGemm2StageBytes + 256 + 1024;
+constexpr int kGemm2StoreBytes = 4 * 2 * 4096;      // per epilogue warp: two 32 x 128-byte buffers
+constexpr int kGemm2SmemTotal = kGemm2Stages * kGemm2StageBytes + kGemm2StoreBytes + 256 + 1024;
 
-template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
+// Tensor maps of the output for the TMA-store epilogue: one map for a local C, or one per
+// destination rank for the reduce-scatter form (box = 64 bf16 columns x 32 rows, 128-byte swizzle).
+struct alignas(64) GemmOutMaps {
+  CUtensorMap m[kGemmMaxWorld];
+};
+
+template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false>
 __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const int pair,
-                                               const int num_pairs) {
+                                               const int num_pairs,
+                                               const GemmOutMaps* out_maps = nullptr) {
+  static_assert(!(TMA_STORE && OUT_F32), "the TMA-store epilogue writes bf16");
   constexpr int kStages = kGemm2Stages;
   constexpr int BN = kGemm2TileN;
   constexpr uint32_t kTmemCols = 512;
@@ -30,13 +39,14 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
-  const uint32_t bar_base = smem_base + kStages * kGemm2StageBytes;
+  const uint32_t store_base = smem_base + kStages * kGemm2StageBytes;
+  const uint32_t bar_base = store_base + kGemm2StoreBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * kStages + a); };
   auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * kStages + 2 + a); };
-  uint32_t* tmem_holder =
-      reinterpret_cast<uint32_t*>(smem_gen + kStages * kGemm2StageBytes + 8 * (2 * kStages + 4));
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(
+      smem_gen + kStages * kGemm2StageBytes + kGemm2StoreBytes + 8 * (2 * kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -201,53 +211,122 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
       } else {
         out_row = static_cast<uint8_t*>(p.C) + static_cast<long long>(row) * p.ldc * kOutBytes;
       }
-      const bool row_ok = row < p.M;
+      if constexpr (TMA_STORE) {
+        // ---- staged epilogue: registers -> swizzled shared memory -> TMA store (128-byte rows,
+        // issued by one lane, so the destination sees full-line bursts even over NVLink) ----
+        const uint32_t stg = store_base + static_cast<uint32_t>(warp - 2) * 8192u;
+        int map_idx = 0;
+        int row_coord = row_blk0 + q * 32;
+        if constexpr (RS_SCATTER) {
+          const int owner = row_blk0 / p.rs_rows_per_rank;
+          map_idx = owner < p.world ? owner : 0;
+          row_coord -= owner * p.rs_rows_per_rank;
+        }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
-                               static_cast<uint32_t>(acc * BN + c * 32);
-        tmem_ld_32x32(taddr, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
-          float v[32];
+        for (int c = 0; c < BN / 64; ++c) {
+          const uint32_t buf = stg + static_cast<uint32_t>(c & 1) * 4096u;
+          if (lane == 0) tma_store_wait_read<1>();  // the store that last used this buffer was read
+          __syncwarp();
+          uint32_t r0[32], r1[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                 static_cast<uint32_t>(acc * BN + c * 64);
+          tmem_ld_32x32(taddr, r0);
+          tmem_ld_32x32(taddr + 32, r1);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 64;
+          uint32_t w[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-          if constexpr (EPI == kEpiBias || EPI == kEpiBiasSilu) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
-          }
-          if constexpr (EPI == kEpiSilu || EPI == kEpiBiasSilu) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
-          }
-          if constexpr (OUT_F32) {
-            float* o = reinterpret_cast<float*>(out_row) + col0;
-            if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                U4 u{__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]),
-                     __float_as_uint(v[j + 3])};
-                st_global_v4(o + j, u);
+          for (int j = 0; j < 32; j += 2) {
+            float a0 = __uint_as_float(r0[j]) * p.alpha, a1 = __uint_as_float(r0[j + 1]) * p.alpha;
+            float b0 = __uint_as_float(r1[j]) * p.alpha, b1 = __uint_as_float(r1[j + 1]) * p.alpha;
+            if constexpr (EPI == kEpiBias || EPI == kEpiBiasSilu) {
+              if (col0 + j + 1 < p.N) {
+                a0 += __bfloat162float(p.bias[col0 + j]);
+                a1 += __bfloat162float(p.bias[col0 + j + 1]);
               }
-            } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) o[j] = v[j];
+              if (col0 + 32 + j + 1 < p.N) {
+                b0 += __bfloat162float(p.bias[col0 + 32 + j]);
+                b1 += __bfloat162float(p.bias[col0 + 32 + j + 1]);
+              }
             }
-          } else {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + col0;
-            if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+            if constexpr (EPI == kEpiSilu || EPI == kEpiBiasSilu) {
+              a0 = silu_f(a0); a1 = silu_f(a1); b0 = silu_f(b0); b1 = silu_f(b1);
+            }
+            w[j >> 1] = pack_bf16x2(a0, a1);
+            w[16 + (j >> 1)] = pack_bf16x2(b0, b1);
+          }
+          // row `lane` of the 32 x 128-byte buffer; 16-byte chunk j lands at chunk (j ^ (row & 7))
+          const uint32_t row_addr = buf + static_cast<uint32_t>(lane) * 128u;
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                U4 u{pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                     pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7])};
-                st_global_v4(o + j, u);
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + (static_cast<uint32_t>(j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[4 * j]),
+                         "r"(w[4 * j + 1]), "r"(w[4 * j + 2]), "r"(w[4 * j + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && col0 < p.N && row_blk0 + q * 32 < p.M) {
+            tma_store_2d(&out_maps->m[map_idx], buf, col0, row_coord);
+            tma_store_commit();
+          }
+        }
+        if constexpr (RS_SCATTER) {
+          // the owner may only be told once the stores have been performed, not merely read
+          if (lane == 0) {
+            tma_store_wait_all<0>();
+            fence_proxy_async_all();
+          }
+        }
+      } else {
+      const bool row_ok = row < p.M;
+  #pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
+                                 static_cast<uint32_t>(acc * BN + c * 32);
+          tmem_ld_32x32(taddr, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row_ok && col0 < p.N) {
+            float v[32];
+  #pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+            if constexpr (EPI == kEpiBias || EPI == kEpiBiasSilu) {
+  #pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] += __bfloat162float(p.bias[col0 + j]);
+            }
+            if constexpr (EPI == kEpiSilu || EPI == kEpiBiasSilu) {
+  #pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
+            }
+            if constexpr (OUT_F32) {
+              float* o = reinterpret_cast<float*>(out_row) + col0;
+              if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  U4 u{__float_as_uint(v[j]), __float_as_uint(v[j + 1]), __float_as_uint(v[j + 2]),
+                       __float_as_uint(v[j + 3])};
+                  st_global_v4(o + j, u);
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) o[j] = v[j];
               }
             } else {
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + col0;
+              if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  U4 u{pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                       pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7])};
+                  st_global_v4(o + j, u);
+                }
+              } else {
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+              }
             }
           }
         }
@@ -272,6 +351,10 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
         acc_phase ^= 1u;
       }
     }
+    if constexpr (TMA_STORE) {
+      if (lane == 0) tma_store_wait_all<0>();  // staging memory and stores are done before exit
+      __syncwarp();
+    }
   }
 
   tc_fence_before_sync();
@@ -295,6 +378,16 @@ gemm_umma2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   gemm_umma2_cta<EPI, OUT_F32, A_READY, RS_SCATTER>(tmap_a, tmap_b, p, blockIdx.x >> 1,
                                                     gridDim.x >> 1);
+}
+
+// bf16 output through the TMA-store epilogue
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_umma2_tma_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ GemmOutMaps out_maps, const GemmParams p) {
+  gemm_umma2_cta<EPI, false, false, false, true>(tmap_a, tmap_b, p, blockIdx.x >> 1,
+                                                 gridDim.x >> 1, &out_maps);
 }
 
 }  // namespace pkb

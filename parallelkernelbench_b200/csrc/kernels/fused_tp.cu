@@ -19,7 +19,7 @@
 //  reference/45_reducescatter_fused_rmsnorm.py:23-29).
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
-#include "pkb/gemm_umma.cuh"
+#include "pkb/gemm_umma2.cuh"
 #include "pkb/host.h"
 #include "pkb/symm.cuh"
 
@@ -76,16 +76,18 @@ __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
   }
 }
 
-template <int BN, int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p, const TpAgArgs a) {
+                  const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
+                  const TpAgArgs a) {
   if ((int)blockIdx.x < a.comm_ctas) {
     ag_push_role(a);
     return;
   }
-  gemm_umma_cta<BN, EPI, false, true, false>(tmap_a, tmap_b, p, blockIdx.x - a.comm_ctas,
-                                             gridDim.x - a.comm_ctas);
+  gemm_umma2_cta<EPI, false, true, false, true>(tmap_a, tmap_b, p, (blockIdx.x - a.comm_ctas) >> 1,
+                                                (gridDim.x - a.comm_ctas) >> 1, &out_maps);
 }
 
 struct TpRsArgs {
@@ -101,15 +103,16 @@ struct TpRsArgs {
   int rows_per_rank;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                          const __grid_constant__ CUtensorMap tmap_b, const GemmParams p,
+                          const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
                           const TpRsArgs a) {
   const SymmCtx& c = a.ctx;
   // all ranks have entered this call => all ranks have consumed the previous call's receive slots
   if (!symm_block_barrier(c, 301, 1)) return;
-  gemm_umma_cta<BN, kEpiNone, false, false, true>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
+  gemm_umma2_cta<kEpiNone, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1,
+                                                     gridDim.x >> 1, &out_maps);
   __syncthreads();
 
   // ---- consumer phase: reduce the W partial slots of my rows and normalise --------------------
@@ -203,6 +206,7 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   PKB_CHECK_ARG(rows > 0 && K % 8 == 0 && N > 0, "bad shapes");
   PKB_CHECK_ARG(a_chunk_rows % kGemmBlockM == 0 && rows % a_chunk_rows == 0,
                 "a_chunk_rows must be a multiple of 128 that divides rows");
+  PKB_CHECK_ARG(rows % kGemm2TileM == 0, "rows per rank must be a multiple of 256");
   PKB_CHECK_ARG(epilogue == kEpiNone || epilogue == kEpiSilu, "epilogue must be none or silu");
   PKB_CHECK_ARG((gather_off & 1023) == 0 && (flags_off & 15) == 0, "heap offsets misaligned");
   const int W = h->gsize;
@@ -214,7 +218,14 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   int rc = encode_tmap_2d(&ta, kTmapBf16, g_local, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
                           kGemmBlockK, kGemmBlockM, kSwizzle128);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 256,
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 128,
+                      kSwizzle128);
+  if (rc) return rc;
+
+  PKB_CHECK_ARG(ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0,
+                "output must be 16-byte aligned with ldc a multiple of 8");
+  GemmOutMaps om;
+  rc = encode_tmap_2d(&om.m[0], kTmapBf16, c, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 32,
                       kSwizzle128);
   if (rc) return rc;
 
@@ -226,8 +237,8 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   p.a_ready = reinterpret_cast<const uint32_t*>(h->base + (uint64_t)h->rank * h->stride + flags_off);
   p.a_ready_epoch = epoch;
   p.a_chunk_rows = a_chunk_rows;
-  const int blocks_per_shard = rows / kGemmBlockM;
-  p.group_m = blocks_per_shard < 16 ? blocks_per_shard : 16;
+  const int blocks_per_shard = rows / kGemm2TileM;
+  p.group_m = blocks_per_shard < 8 ? blocks_per_shard : 8;
   // keep whole shards inside rasterisation groups when possible
   while (blocks_per_shard % p.group_m != 0) --p.group_m;
   p.m_block_rotation = h->grank * blocks_per_shard;  // local rows first, then rank+1, ...
@@ -240,21 +251,22 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   a.sub_per_shard = rows / a_chunk_rows;
   a.epoch = epoch;
   a.local_in_place = (x_local == g_local + (long long)h->grank * rows * K * 2) ? 1 : 0;
-  if (comm_ctas <= 0) comm_ctas = W > 1 ? 16 : 1;
-  const int sms = sm_count();
+  if (comm_ctas <= 0) comm_ctas = W > 1 ? 8 : 2;
+  comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
+  const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");
   a.comm_ctas = comm_ctas;
 
-  constexpr int smem = GemmSmem<256>::kTotal;
+  constexpr int smem = kGemm2SmemTotal;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (epilogue == kEpiSilu) {
-    auto k = tp_ag_gemm_kernel<256, kEpiSilu>;
+    auto k = tp_ag_gemm_kernel<kEpiSilu>;
     PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, p, a);
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, om, p, a);
   } else {
-    auto k = tp_ag_gemm_kernel<256, kEpiNone>;
+    auto k = tp_ag_gemm_kernel<kEpiNone>;
     PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, p, a);
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, om, p, a);
   }
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
@@ -270,9 +282,9 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
                            float scale, void* stream) {
   PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
   PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kGemmMaxWorld, "group size must be 1..8");
-  PKB_CHECK_ARG(rows_per_rank % kGemmBlockM == 0, "rows_per_rank must be a multiple of 128");
+  PKB_CHECK_ARG(rows_per_rank % kGemm2TileM == 0, "rows_per_rank must be a multiple of 256");
   PKB_CHECK_ARG(N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "N, K, lda, ldb must be multiples of 8");
-  PKB_CHECK_ARG(N * 4 <= GemmSmem<256>::kTotal, "row too long for the shared-memory row buffer");
+  PKB_CHECK_ARG(N * 4 <= kGemm2SmemTotal, "row too long for the shared-memory row buffer");
   PKB_CHECK_ARG((recv_off & 15) == 0 && (done_off & 15) == 0, "heap offsets misaligned");
   const int W = h->gsize;
   const int M = W * rows_per_rank;
@@ -282,10 +294,11 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
   int rc = encode_tmap_2d(&ta, kTmapBf16, a_mat, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
                           kGemmBlockK, kGemmBlockM, kSwizzle128);
   if (rc) return rc;
-  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 256,
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 128,
                       kSwizzle128);
   if (rc) return rc;
 
+  GemmOutMaps om;
   GemmParams p = {};
   p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = N; p.alpha = 1.0f;
   p.status = ctx.status; p.wait_budget_ns = ctx.budget_ns;
@@ -297,9 +310,12 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
     const uint64_t peer = h->base + (uint64_t)h->members[g] * h->stride;
     p.rs_out[g] = reinterpret_cast<void*>(peer + recv_off + (uint64_t)h->grank * slot_bytes);
     p.rs_done[g] = reinterpret_cast<uint32_t*>(peer + done_off);
+    rc = encode_tmap_2d(&om.m[g], kTmapBf16, p.rs_out[g], (uint64_t)N, (uint64_t)rows_per_rank,
+                        (uint64_t)N * 2, 64, 32, kSwizzle128);
+    if (rc) return rc;
   }
-  const int blocks_per_rank = rows_per_rank / kGemmBlockM;
-  p.group_m = blocks_per_rank < 16 ? blocks_per_rank : 16;
+  const int blocks_per_rank = rows_per_rank / kGemm2TileM;
+  p.group_m = blocks_per_rank < 8 ? blocks_per_rank : 8;
   while (blocks_per_rank % p.group_m != 0) --p.group_m;
   p.m_block_rotation = ((h->grank + 1) % W) * blocks_per_rank;  // rank+1's rows first, own rows last
 
@@ -312,12 +328,12 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
   a.out = static_cast<__nv_bfloat16*>(out);
   a.eps = eps; a.scale = scale; a.N = N; a.rows_per_rank = rows_per_rank;
 
-  constexpr int smem = GemmSmem<256>::kTotal;
-  auto k = tp_gemm_rs_rmsnorm_kernel<256>;
+  constexpr int smem = kGemm2SmemTotal;
+  auto k = tp_gemm_rs_rmsnorm_kernel;
   PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  int grid = sm_count();
+  int grid = sm_count() & ~1;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
-  k<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, p, a);
+  k<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, om, p, a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

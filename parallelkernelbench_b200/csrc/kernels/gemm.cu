@@ -44,6 +44,30 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return kApiOk;
 }
 
+template <int EPI>
+static int launch_pair_tma(const CUtensorMap& ta, const CUtensorMap& tb, const GemmOutMaps& om,
+                           const GemmParams& p, int num_ctas, cudaStream_t stream) {
+  auto kern = gemm_umma2_tma_kernel<EPI>;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kGemm2SmemTotal));
+  kern<<<num_ctas, kGemmThreads, kGemm2SmemTotal, stream>>>(ta, tb, om, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+static int dispatch_pair_tma(int epi, const CUtensorMap& ta, const CUtensorMap& tb,
+                             const GemmOutMaps& om, const GemmParams& p, int num_ctas,
+                             cudaStream_t stream) {
+  switch (epi) {
+    case kEpiNone: return launch_pair_tma<kEpiNone>(ta, tb, om, p, num_ctas, stream);
+    case kEpiSilu: return launch_pair_tma<kEpiSilu>(ta, tb, om, p, num_ctas, stream);
+    case kEpiBias: return launch_pair_tma<kEpiBias>(ta, tb, om, p, num_ctas, stream);
+    case kEpiBiasSilu: return launch_pair_tma<kEpiBiasSilu>(ta, tb, om, p, num_ctas, stream);
+  }
+  set_last_error("unknown epilogue");
+  return kApiBadArgument;
+}
+
 template <bool OUT_F32>
 static int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
                          int num_ctas, cudaStream_t stream) {
@@ -91,6 +115,13 @@ extern "C" int pkb_gemm_bf16_pair(const void* a, long long lda, const void* b, l
   ctas &= ~1;
   if (ctas > 2 * tiles) ctas = 2 * tiles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (!out_f32 && ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0) {
+    GemmOutMaps om;
+    rc = encode_tmap_2d(&om.m[0], kTmapBf16, c, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64, 32,
+                        kSwizzle128);
+    if (rc) return rc;
+    return dispatch_pair_tma(epilogue, ta, tb, om, p, ctas, s);
+  }
   return out_f32 ? dispatch_pair<true>(epilogue, ta, tb, p, ctas, s)
                  : dispatch_pair<false>(epilogue, ta, tb, p, ctas, s);
 }

@@ -21,8 +21,8 @@ from ..parallel.symm_heap import SymmGroup
 
 class AllGatherGemm:
     def __init__(self, group: SymmGroup, rows: int, k: int, chunk_rows: int = 256, comm_ctas: int = 0):
-        if rows % 128 != 0:
-            raise ValueError("rows per rank must be a multiple of 128")
+        if rows % 256 != 0:
+            raise ValueError("rows per rank must be a multiple of 256 (one CTA-pair tile)")
         while rows % chunk_rows != 0:
             chunk_rows //= 2
         self.group, self.rows, self.k, self.chunk_rows, self.comm_ctas = group, rows, k, chunk_rows, comm_ctas
@@ -61,8 +61,8 @@ class AllGatherGemm:
 
 class GemmReduceScatterRMSNorm:
     def __init__(self, group: SymmGroup, rows_per_rank: int, n: int):
-        if rows_per_rank % 128 != 0:
-            raise ValueError("rows per rank must be a multiple of 128")
+        if rows_per_rank % 256 != 0:
+            raise ValueError("rows per rank must be a multiple of 256 (one CTA-pair tile)")
         self.group, self.rows, self.n = group, rows_per_rank, n
         heap = group.heap
         self.recv = heap.empty((group.size, rows_per_rank, n), torch.bfloat16)

@@ -20,7 +20,7 @@ def main() -> int:
     g = heap.world_group
     W, r, dev = ctx.world, ctx.rank, ctx.device
     fails = 0
-    shapes = [(256, 512, 1024 * W), (384, 1024, 512 * W)]
+    shapes = [(256, 512, 1024 * W), (512, 1024, 512 * W)]
     if full:
         shapes.append((2048, 8192, 28672))
     for rows, hidden, ffn in shapes:
@@ -30,16 +30,36 @@ def main() -> int:
         mark = heap.mark()
         blk = TPMLPBlock(g, cfg, w1, w2, gamma)
         ref = TPMLPReference(W, rows, hidden, w1, w2, gamma, cfg.eps)
+
+        def exact(x_local):
+            """fp32 restatement: gather, fp32 GEMMs (bf16-rounded hidden, as both pipelines store it), fp32 reduce."""
+            xs = [torch.empty_like(x_local) for _ in range(W)]
+            if W > 1:
+                dist.all_gather(xs, x_local)
+            else:
+                xs = [x_local]
+            xf = torch.cat(xs).float()
+            hmid = torch.nn.functional.silu(xf @ w1.float().t()).to(torch.bfloat16).float()
+            part = hmid @ w2.float().t()
+            if W > 1:
+                dist.all_reduce(part)
+            yv = part[r * rows:(r + 1) * rows]
+            return yv * torch.rsqrt(yv.pow(2).mean(-1, keepdim=True) + cfg.eps) * gamma.float()
+
         for trial in range(3):
             x = torch.randn(rows, hidden, device=dev, dtype=torch.bfloat16,
                             generator=torch.Generator(device=dev).manual_seed(77 + trial * 10 + r))
             y = blk(x).clone()
             y_ref = ref(x)
+            y_true = exact(x)
             torch.cuda.synchronize()
-            err = (y.float() - y_ref.float()).abs().max().item()
-            ok = torch.allclose(y.float(), y_ref.float(), atol=3e-2, rtol=3e-2)
+            err = (y.float() - y_true).abs().max().item()
+            err_ref = (y_ref.float() - y_true).abs().max().item()
+            # both are bf16 pipelines with different summation orders: judge each against the fp32 result
+            ok = torch.allclose(y.float(), y_true, atol=4e-2, rtol=2e-2) and err <= max(2.0 * err_ref, 4e-2)
             fails += 0 if ok else 1
-            print(f"{'PASS' if ok else 'FAIL'} rank{r} tp_mlp rows={rows} hidden={hidden} ffn={ffn} trial={trial} maxerr={err:.4g}", flush=True)
+            print(f"{'PASS' if ok else 'FAIL'} rank{r} tp_mlp rows={rows} hidden={hidden} ffn={ffn} trial={trial} "
+                  f"maxerr={err:.4g} (nccl+cublas reference: {err_ref:.4g})", flush=True)
         # zero-copy input path + determinism
         blk.x_slot.copy_(x)
         y2 = blk(blk.x_slot).clone()
