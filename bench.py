@@ -1,0 +1,210 @@
+#!/usr/bin/env python3
+"""Headline benchmark: the tensor-parallel MLP block (all-gather -> GEMM -> SiLU -> GEMM ->
+reduce-scatter -> RMSNorm) on N GPUs of one node, bf16, synthetic data, random-init weights.
+
+Per rank the activations are [2048, 8192]; the FFN dimension 28672 is sharded over the N ranks, so
+the work per GPU is the same at every N (weak scaling) and N = 8 is exactly the named 8-rank
+configuration. One step = one forward of the block = two fused kernel launches.
+
+    python bench.py --gpus 1 --steps 50 --warmup 10
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 50 --warmup 10
+
+Rank 0 prints ONE JSON line. ``value`` is rows (tokens) per second summed over all GPUs, device
+timed with CUDA events as the max over ranks. The same line carries the time of the PyTorch + NCCL
++ cuBLAS implementation of the block measured in the same process with the same protocol
+(``ref_ms_per_step``, ``speedup_vs_ref``), the fraction of the compute roofline, an end-to-end
+number that includes the host->device copy of every step's input and a device->host read of a
+result metric, the clocks seen during the timed region, and the number of our kernels launched.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS_PER_RANK = 2048
+HIDDEN = 8192
+FFN = 28672
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-ref", action="store_true", help="skip timing the in-repo PyTorch+NCCL implementation")
+    ap.add_argument("--comm-ctas", type=int, default=0)
+    return ap.parse_args()
+
+
+def reference_arm() -> int:
+    # The upstream tree is a flat collection of scripts without installable packages: the offline
+    # `pip install --target baseline/_ref` stops in metadata generation (setuptools refuses
+    # automatic discovery over several top-level packages), with and without --no-deps and from a
+    # writable copy. Nothing of it is importable from baseline/_ref, so this arm cannot run.
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    why = ("reference is not pip-installable offline: setuptools metadata generation fails on its flat "
+           "multi-package layout (no build configuration), so baseline/_ref is empty")
+    if os.path.isdir(ref_dir) and any(os.scandir(ref_dir)):
+        why = "baseline/_ref exists but the reference ships no importable package or benchmark entry point for this config"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    args = parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    import torch.distributed as dist
+
+    from parallelkernelbench_b200 import _native as nv
+    from parallelkernelbench_b200.models import TPMLPBlock, TPMLPConfig
+    from parallelkernelbench_b200.parallel import init_context
+    from parallelkernelbench_b200.refs.tp_mlp import TPMLPReference
+    from parallelkernelbench_b200.utils.clocks import ClockSampler
+    from parallelkernelbench_b200.utils.env import measured_peaks
+
+    os.environ.setdefault("PKB_HEAP_GIB", "1")
+    ctx = init_context()
+    W, rank, dev = ctx.world, ctx.rank, ctx.device
+    if W != args.gpus and rank == 0:
+        print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE={W}; using {W}", file=sys.stderr)
+    heap = ctx.heap()
+    group = heap.world_group
+
+    cfg = TPMLPConfig(rows_per_rank=ROWS_PER_RANK, hidden=HIDDEN, ffn=FFN)
+    w1, w2, gamma = TPMLPBlock.random_weights(cfg, W, rank, dev)
+    block = TPMLPBlock(group, cfg, w1, w2, gamma, comm_ctas=args.comm_ctas)
+
+    # a rotation of input buffers (the per-step working set, weights + activations, is already far
+    # larger than the 126 MB L2; rotating the inputs additionally defeats any reuse across steps)
+    n_inputs = 4
+    gen = torch.Generator(device=dev).manual_seed(4242 + rank)
+    xs = [torch.randn(ROWS_PER_RANK, HIDDEN, device=dev, dtype=torch.bfloat16, generator=gen) for _ in range(n_inputs)]
+
+    def timed(fn, steps: int, warmup: int):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        ctx.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = nv.launches()
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        torch.cuda.synchronize()
+        ctx.barrier()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        if W > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), nv.launches() - launches0
+
+    # ---------------------------------------------------------------- device-timed headline
+    sampler = ClockSampler(gpu_index=ctx.local_rank).start() if rank == 0 else None
+    ms_ours, launches = timed(lambda i: block(xs[i % n_inputs]), args.steps, args.warmup)
+    if sampler is not None:
+        time.sleep(0.25)
+        sampler.stop()
+        clocks = sampler.summary()
+    else:
+        clocks = None
+    nv.raise_on_status(sync=True)
+
+    # ---------------------------------------------------------------- end to end through the public API
+    # every step: H2D copy of the step's input from pinned host memory (copy stream, double
+    # buffered so it overlaps the previous step's kernels), forward, a scalar result metric, and its
+    # D2H read into pinned memory.
+    host_x = [torch.randn(ROWS_PER_RANK, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty(ROWS_PER_RANK, HIDDEN, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+    host_metric = torch.zeros(1, dtype=torch.float32).pin_memory()
+    copy_stream = torch.cuda.Stream(device=dev)
+    h2d_done = [torch.cuda.Event() for _ in range(2)]
+    compute_done = [torch.cuda.Event() for _ in range(2)]
+    main_stream = torch.cuda.current_stream()
+    for ev in compute_done:
+        ev.record(main_stream)
+
+    def e2e_step(i: int):
+        b = i & 1
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(compute_done[b])
+            dev_x[b].copy_(host_x[b], non_blocking=True)
+            h2d_done[b].record(copy_stream)
+        main_stream.wait_event(h2d_done[b])
+        y = block(dev_x[b])
+        metric = y.float().pow(2).mean().reshape(1)
+        host_metric.copy_(metric, non_blocking=True)
+        compute_done[b].record(main_stream)
+
+    ms_e2e, _ = timed(e2e_step, args.steps, max(3, args.warmup // 2))
+    nv.raise_on_status(sync=True)
+    h2d_bytes = ROWS_PER_RANK * HIDDEN * 2
+    d2h_bytes = 4
+
+    # ---------------------------------------------------------------- PyTorch + NCCL + cuBLAS implementation
+    ms_ref = None
+    if not args.no_ref:
+        time.sleep(float(os.environ.get("PKB_COOLDOWN_SEC", "0.5")))
+        ref = TPMLPReference(W, ROWS_PER_RANK, HIDDEN, w1, w2, gamma, cfg.eps)
+        ms_ref, _ = timed(lambda i: ref(xs[i % n_inputs]), args.steps, args.warmup)
+
+    peaks = measured_peaks()
+    flops_per_gpu = 4.0 * (W * ROWS_PER_RANK) * HIDDEN * (FFN // W)
+    tflops = flops_per_gpu / (ms_ours * 1e-3) / 1e12
+    peak = float(peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops"))
+    # per GPU and per direction: (W-1) activation shards gathered + (W-1) partial row blocks scattered
+    nvlink_bytes_per_dir = 2.0 * (W - 1) * ROWS_PER_RANK * HIDDEN * 2
+    roofline_ms = max(flops_per_gpu / (peak * 1e12), nvlink_bytes_per_dir / 770e9) * 1e3
+    tokens = W * ROWS_PER_RANK
+    out = {
+        "metric": "tp_mlp_block_tokens_per_s",
+        "value": tokens / (ms_ours * 1e-3),
+        "unit": "tokens/s",
+        "n_gpus": W,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": ms_ours,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic (N(0,1) activations, N(0,0.02) random-init weights)",
+        "impl": "ours",
+        "config": {"model": "tp_mlp_block(AG->GEMM->SiLU->GEMM->RS->RMSNorm)", "global_batch": tokens,
+                   "seq_len": ROWS_PER_RANK, "hidden": HIDDEN, "ffn": FFN, "parallelism": f"tp{W}",
+                   "l2_policy": "inputs larger than L2 (weights+activations per step >> 126 MB) and 4 rotating input buffers"},
+        "tflops_per_gpu": tflops,
+        "pct_roofline": 100.0 * roofline_ms / ms_ours,
+        "roofline_ms": roofline_ms,
+        "roofline_peak": {"bf16_tflops": peak, "source": peaks.get("source"), "kind": "sustained cuBLAS bf16 (of measured)"},
+        "ref_ms_per_step": ms_ref,
+        "speedup_vs_ref": (ms_ref / ms_ours) if ms_ref else None,
+        "ref_impl": "in-repo PyTorch + NCCL + cuBLAS implementation of the same block, same timing protocol",
+        "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d_bytes * W, "d2h_bytes_per_step": d2h_bytes * W},
+        "gpu_launches": launches,
+        "clocks": clocks,
+    }
+    ctx.finalize()
+    if rank == 0:
+        print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

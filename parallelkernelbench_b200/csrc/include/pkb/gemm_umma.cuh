@@ -40,6 +40,10 @@ struct GemmParams {
   const uint32_t* a_ready;
   uint32_t a_ready_epoch;
   int a_chunk_rows;
+  // Rows [a_local_row0, a_local_row0 + a_local_rows) of A are this rank's own shard: they are read
+  // through a second tensor map straight from the caller's tensor, with no flag to wait for.
+  int a_local_row0;
+  int a_local_rows;
   // ---- GEMM -> reduce-scatter hook ----------------------------------------------------------
   // Output row m belongs to rank m / rs_rows_per_rank; it is stored at
   // rs_out[rank_of_m] + (m % rs_rows_per_rank) * ldc, and when a tile of that row block is done

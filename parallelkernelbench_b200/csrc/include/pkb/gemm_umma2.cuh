@@ -30,7 +30,8 @@ template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE =
 __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const int pair,
                                                const int num_pairs,
-                                               const GemmOutMaps* out_maps = nullptr) {
+                                               const GemmOutMaps* out_maps = nullptr,
+                                               const CUtensorMap* tmap_a_local = nullptr) {
   static_assert(!(TMA_STORE && OUT_F32), "the TMA-store epilogue writes bf16");
   constexpr int kStages = kGemm2Stages;
   constexpr int BN = kGemm2TileN;
@@ -106,7 +107,18 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
         tile_coords(tile, m_blk, n_blk);
         const int row0 = m_blk * kGemm2TileM + (int)cta_rank * 128;
         const int col0 = n_blk * BN + (int)cta_rank * 128;
+        const CUtensorMap* map_a = &tmap_a;
+        int a_row = row0;
+        bool a_is_local = false;
         if constexpr (A_READY) {
+          if (tmap_a_local != nullptr && row0 >= p.a_local_row0 &&
+              row0 < p.a_local_row0 + p.a_local_rows) {
+            map_a = tmap_a_local;
+            a_row = row0 - p.a_local_row0;
+            a_is_local = true;
+          }
+        }
+        if (A_READY && !a_is_local) {
           int chunk = row0 / p.a_chunk_rows;
           const int last_chunk = (p.M - 1) / p.a_chunk_rows;
           if (chunk > last_chunk) chunk = last_chunk;
@@ -126,7 +138,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           }
           if (leader) mbar_expect_tx(full_bar(stage), 2 * kGemm2StageBytes);
           const uint32_t sa = smem_base + stage * kGemm2StageBytes;
-          tma_load_2d_pair(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+          tma_load_2d_pair(sa, map_a, full_bar(stage), kb * kGemmBlockK, a_row);
           tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0);
           if (++stage == kStages) {
             stage = 0;

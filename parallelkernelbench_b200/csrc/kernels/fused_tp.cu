@@ -43,14 +43,15 @@ __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
   if (!symm_block_barrier(c, 300, 1)) return;
   const int W = c.gsize;
   const int total_items = W * a.sub_per_shard;
-  for (int item = blockIdx.x; item < total_items; item += a.comm_ctas) {
+  // the local shard is read in place by the GEMM (its own tensor map): only remote pushes here
+  for (int item = a.sub_per_shard + blockIdx.x; item < total_items; item += a.comm_ctas) {
     const int step = item / a.sub_per_shard;
     const int sb = item - step * a.sub_per_shard;
     int dest_g = c.grank - step;
     if (dest_g < 0) dest_g += W;
     const int dest = c.members[dest_g];
     const int chunk = c.grank * a.sub_per_shard + sb;
-    if (!(step == 0 && a.local_in_place)) {
+    {
       const uint8_t* src = a.x_local + (long long)sb * a.sub_bytes;
       uint8_t* dst = symm_ptr<uint8_t>(c, dest, a.gather_off) + (long long)chunk * a.sub_bytes;
       const long long nvec = a.sub_bytes >> 4;
@@ -80,6 +81,7 @@ template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ CUtensorMap tmap_a_local,
                   const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
                   const TpAgArgs a) {
   if ((int)blockIdx.x < a.comm_ctas) {
@@ -87,7 +89,8 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     return;
   }
   gemm_umma2_cta<EPI, false, true, false, true>(tmap_a, tmap_b, p, (blockIdx.x - a.comm_ctas) >> 1,
-                                                (gridDim.x - a.comm_ctas) >> 1, &out_maps);
+                                                (gridDim.x - a.comm_ctas) >> 1, &out_maps,
+                                                &tmap_a_local);
 }
 
 struct TpRsArgs {
@@ -221,6 +224,11 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 128,
                       kSwizzle128);
   if (rc) return rc;
+  PKB_CHECK_ARG((reinterpret_cast<uintptr_t>(x_local) & 15) == 0, "x_local must be 16-byte aligned");
+  CUtensorMap tal;
+  rc = encode_tmap_2d(&tal, kTmapBf16, x_local, (uint64_t)K, (uint64_t)rows, (uint64_t)K * 2, kGemmBlockK,
+                      kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
 
   PKB_CHECK_ARG(ldc % 8 == 0 && (reinterpret_cast<uintptr_t>(c) & 15) == 0,
                 "output must be 16-byte aligned with ldc a multiple of 8");
@@ -237,6 +245,8 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   p.a_ready = reinterpret_cast<const uint32_t*>(h->base + (uint64_t)h->rank * h->stride + flags_off);
   p.a_ready_epoch = epoch;
   p.a_chunk_rows = a_chunk_rows;
+  p.a_local_row0 = h->grank * rows;
+  p.a_local_rows = rows;
   const int blocks_per_shard = rows / kGemm2TileM;
   p.group_m = blocks_per_shard < 8 ? blocks_per_shard : 8;
   // keep whole shards inside rasterisation groups when possible
@@ -262,11 +272,11 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   if (epilogue == kEpiSilu) {
     auto k = tp_ag_gemm_kernel<kEpiSilu>;
     PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, om, p, a);
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, tal, om, p, a);
   } else {
     auto k = tp_ag_gemm_kernel<kEpiNone>;
     PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, om, p, a);
+    k<<<sms, kGemmThreads, smem, s>>>(ta, tb, tal, om, p, a);
   }
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;

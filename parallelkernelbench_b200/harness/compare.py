@@ -1,0 +1,132 @@
+"""Per-rank output comparison.
+
+An op returns a Tensor, a tuple/list (saved as ``{'output_0': ..}``) or a dict; ``save_output`` moves
+it to CPU and writes ``rank_<r>.pt``. ``compare_dirs`` loads the reference and candidate files of
+every rank and walks them recursively: dict keys must agree, sequences must have equal length,
+tensor leaves are upcast to fp32 (fp64 stays fp64) and compared with ``allclose(atol, rtol)`` plus a
+shape check, other leaves with ``==``. The result carries ``ok``, a ``kind`` (``match``,
+``tensor_mismatch``, ``path_mismatch``, ``load_error``, ``missing_artifacts``), the first errors and
+per-file max / mean absolute differences - the same semantics and vocabulary as the reference's
+comparison core (reference: utils/problem_id.py:113-275, utils/input_output_tensors.py:15-45).
+"""
+from __future__ import annotations
+
+import os
+import re
+from typing import Any
+
+import torch
+
+_RANK_FILE = re.compile(r"^rank_(\d+)\.pt$")
+
+
+def normalize_output(y: Any) -> Any:
+    """Tensor stays a tensor, tuple/list becomes ``{'output_i': ...}``, dicts are walked; all on CPU."""
+    if isinstance(y, torch.Tensor):
+        return y.detach().to("cpu")
+    if isinstance(y, (tuple, list)):
+        return {f"output_{i}": normalize_output(v) for i, v in enumerate(y)}
+    if isinstance(y, dict):
+        return {str(k): normalize_output(v) for k, v in y.items()}
+    if isinstance(y, torch.Size):
+        return list(y)
+    return y
+
+
+def save_output(y: Any, logs_dir: str, rank: int) -> str:
+    os.makedirs(logs_dir, exist_ok=True)
+    path = os.path.join(logs_dir, f"rank_{rank}.pt")
+    torch.save(normalize_output(y), path)
+    return path
+
+
+def rank_files(d: str) -> dict[int, str]:
+    out = {}
+    if os.path.isdir(d):
+        for f in os.listdir(d):
+            m = _RANK_FILE.match(f)
+            if m:
+                out[int(m.group(1))] = os.path.join(d, f)
+    return out
+
+
+def _compare_leaf(a: Any, b: Any, path: str, atol: float, rtol: float, errors: list, stats: dict) -> bool:
+    if isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor):
+        if a.shape != b.shape:
+            errors.append(f"{path}: shape {tuple(a.shape)} vs {tuple(b.shape)}")
+            return False
+        if a.numel() == 0:
+            return True
+        if a.is_complex() or b.is_complex():
+            a, b = torch.view_as_real(a.to(torch.complex128)), torch.view_as_real(b.to(torch.complex128))
+        up = torch.float64 if (a.dtype == torch.float64 or b.dtype == torch.float64) else torch.float32
+        af, bf = a.to(up), b.to(up)
+        diff = (af - bf).abs()
+        finite = torch.isfinite(diff)
+        mx = float(diff[finite].max()) if finite.any() else 0.0
+        stats["max_abs_diff"] = max(stats.get("max_abs_diff", 0.0), mx)
+        stats["mean_abs_diff"] = max(stats.get("mean_abs_diff", 0.0), float(diff[finite].mean()) if finite.any() else 0.0)
+        if not torch.allclose(af, bf, atol=atol, rtol=rtol, equal_nan=True):
+            bad = int((~torch.isclose(af, bf, atol=atol, rtol=rtol, equal_nan=True)).sum())
+            errors.append(f"{path}: {bad}/{a.numel()} elements differ (max abs diff {mx:.4g}, atol {atol}, rtol {rtol})")
+            return False
+        return True
+    if isinstance(a, dict) and isinstance(b, dict):
+        if set(a.keys()) != set(b.keys()):
+            errors.append(f"{path}: keys {sorted(a.keys())} vs {sorted(b.keys())}")
+            return False
+        ok = True
+        for k in sorted(a.keys()):
+            ok = _compare_leaf(a[k], b[k], f"{path}.{k}", atol, rtol, errors, stats) and ok
+        return ok
+    if isinstance(a, (list, tuple)) and isinstance(b, (list, tuple)):
+        if len(a) != len(b):
+            errors.append(f"{path}: length {len(a)} vs {len(b)}")
+            return False
+        ok = True
+        for i, (x, y) in enumerate(zip(a, b)):
+            ok = _compare_leaf(x, y, f"{path}[{i}]", atol, rtol, errors, stats) and ok
+        return ok
+    if type(a) is not type(b) and not (isinstance(a, (int, float)) and isinstance(b, (int, float))):
+        errors.append(f"{path}: type {type(a).__name__} vs {type(b).__name__}")
+        return False
+    if a != b:
+        errors.append(f"{path}: value {a!r} vs {b!r}")
+        return False
+    return True
+
+
+def compare_objects(a: Any, b: Any, atol: float = 1e-2, rtol: float = 1e-2) -> dict:
+    errors: list[str] = []
+    stats: dict = {}
+    ok = _compare_leaf(a, b, "out", atol, rtol, errors, stats)
+    return {"ok": ok, "errors": errors[:16], **stats}
+
+
+def compare_dirs(ref_dir: str, cand_dir: str, atol: float = 1e-2, rtol: float = 1e-2, expected_ranks: int | None = None) -> dict:
+    """Compare ``rank_<r>.pt`` of two job directories. Never raises."""
+    ref, cand = rank_files(ref_dir), rank_files(cand_dir)
+    if not ref or not cand or (expected_ranks is not None and (len(ref) < expected_ranks or len(cand) < expected_ranks)):
+        return {"ok": False, "kind": "missing_artifacts", "errors": [f"reference files: {sorted(ref)}, candidate files: {sorted(cand)}"],
+                "per_file": []}
+    if set(ref) != set(cand):
+        return {"ok": False, "kind": "path_mismatch", "errors": [f"rank sets differ: {sorted(ref)} vs {sorted(cand)}"], "per_file": []}
+    per_file, errors, all_ok, kind = [], [], True, "match"
+    for r in sorted(ref):
+        try:
+            a = torch.load(ref[r], map_location="cpu", weights_only=False)
+            b = torch.load(cand[r], map_location="cpu", weights_only=False)
+        except Exception as e:  # corrupt or truncated artifact
+            per_file.append({"file": f"rank_{r}.pt", "ok": False, "detail": f"load error: {e}"})
+            errors.append(f"rank {r}: load error: {e}")
+            all_ok, kind = False, "load_error"
+            continue
+        res = compare_objects(a, b, atol, rtol)
+        per_file.append({"file": f"rank_{r}.pt", "ok": res["ok"], "max_abs_diff": res.get("max_abs_diff"),
+                         "mean_abs_diff": res.get("mean_abs_diff"), "detail": "; ".join(res["errors"][:3])})
+        if not res["ok"]:
+            all_ok = False
+            if kind == "match":
+                kind = "tensor_mismatch"
+            errors.extend(f"rank {r}: {e}" for e in res["errors"][:4])
+    return {"ok": all_ok, "kind": kind if not all_ok else "match", "errors": errors[:16], "per_file": per_file}

@@ -1,0 +1,333 @@
+"""Launcher CLI: run one implementation, evaluate ours against the reference, sweep ops x world
+sizes, list the registry, and inspect stored results.
+
+    python -m parallelkernelbench_b200.harness.launch list
+    python -m parallelkernelbench_b200.harness.launch run   --op allreduce --impl ours --nproc 2
+    python -m parallelkernelbench_b200.harness.launch eval  --op tp_mlp --nproc 8 --measure-perf
+    python -m parallelkernelbench_b200.harness.launch eval  --op plumbing --nproc 2 --backend gloo --atol 1e-5 --rtol 1e-5
+    python -m parallelkernelbench_b200.harness.launch sweep --ops allreduce,allgather --worlds 1,2,4,8 --resume
+    python -m parallelkernelbench_b200.harness.launch inspect --op allreduce
+    python -m parallelkernelbench_b200.harness.launch perf-diff --op allreduce
+
+``eval`` runs, for every trial, the reference job, a cool-down, the candidate job, then compares the
+per-rank dumps and (with ``--measure-perf``) reports ``ref_max_ms / ours_max_ms`` and the fraction
+of roofline; it stops at the first failing trial and ends with one machine-readable line
+``EVAL_JSON:{...}``. Exit codes: 0 all trials match, 1 mismatch or failure, 130 interrupted.
+One torchrun job per (implementation, trial), one process per GPU, rendezvous on 127.0.0.1 with a
+random port so back-to-back jobs never collide (same orchestration role as reference:
+run_local.py:72-482).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import random
+import shutil
+import signal
+import subprocess
+import sys
+import time
+
+from ..utils import env
+from . import compare, hygiene, report
+
+LOGS_ROOT = os.environ.get("PKB_LOGS_DIR", os.path.join(str(env.REPO_ROOT), "logs"))
+
+
+def _job_dir(op: str, impl: str, trial: int) -> str:
+    d = os.path.join(LOGS_ROOT, "pkb200_worker", f"{op}_{impl}_t{trial}_{random.randrange(1 << 30):08x}")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
+def final_dir(op: str, impl: str, trial: int, world: int) -> str:
+    return os.path.join(LOGS_ROOT, f"op_{op}", f"w{world}", impl, f"trial_{trial}")
+
+
+def run_job(op: str, impl: str, nproc: int, trial: int = 0, config: str = "default", overrides=None, dtype="bfloat16",
+            backend=None, measure_perf=False, warmup=500, iters=100, graph=False, profile=False, timeout_s=1800.0,
+            extra_worker_args=None, pg_timeout_s=None) -> dict:
+    """Start one torchrun job and wait for it. Never raises; the dict says what happened."""
+    job_dir = _job_dir(op, impl, trial)
+    port = random.randint(29500, 39500)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           "-m", "parallelkernelbench_b200.harness.worker", "--op", op, "--impl", impl, "--logs-dir", job_dir,
+           "--config", config, "--dtype", dtype, "--trial", str(trial)]
+    for k, v in (overrides or {}).items():
+        cmd += ["--set", f"{k}={v}"]
+    if backend:
+        cmd += ["--backend", backend]
+    if measure_perf:
+        cmd += ["--measure-perf", "--warmup", str(warmup), "--iters", str(iters)]
+        if graph:
+            cmd.append("--graph")
+    if profile:
+        cmd.append("--profile")
+    cmd += list(extra_worker_args or [])
+    child_env = dict(os.environ)
+    child_env["TORCHELASTIC_ERROR_FILE"] = os.path.join(job_dir, "torch_elastic_error.json")
+    child_env["PYTHONPATH"] = str(env.REPO_ROOT) + os.pathsep + child_env.get("PYTHONPATH", "")
+    child_env.setdefault("OMP_NUM_THREADS", "1")
+    if pg_timeout_s is not None:
+        child_env["PKB_PG_TIMEOUT_SEC"] = str(pg_timeout_s)
+    if env.verbose():
+        print(" ".join(cmd), flush=True)
+    t0 = time.time()
+    interrupted = False
+    timed_out = False
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=child_env,
+                            cwd=str(env.REPO_ROOT), start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        timed_out = True
+        out, err = _stop_group(proc)
+    except KeyboardInterrupt:
+        interrupted = True
+        out, err = _stop_group(proc)
+        with open(os.path.join(job_dir, "interrupted.txt"), "w") as fh:
+            fh.write("interrupted by the user\n")
+    artifacts = sorted(f for f in os.listdir(job_dir) if f.startswith("rank_") and f.endswith(".pt"))
+    elastic = sorted(f for f in os.listdir(job_dir) if f.startswith("torch_elastic_error"))
+    return {"op": op, "impl": impl, "trial": trial, "nproc": nproc, "returncode": proc.returncode if not timed_out else -9,
+            "timed_out": timed_out, "interrupted": interrupted, "seconds": time.time() - t0, "job_dir": job_dir,
+            "artifact_names": artifacts, "artifact_count": len(artifacts), "elastic_error_files": elastic,
+            "stdout": out or "", "stderr": err or ""}
+
+
+def _stop_group(proc) -> tuple[str, str]:
+    """SIGTERM, then SIGKILL, the exact process group this launcher started."""
+    try:
+        os.killpg(proc.pid, signal.SIGTERM)
+    except ProcessLookupError:
+        pass
+    try:
+        return proc.communicate(timeout=10)
+    except subprocess.TimeoutExpired:
+        try:
+            os.killpg(proc.pid, signal.SIGKILL)
+        except ProcessLookupError:
+            pass
+        return proc.communicate()
+
+
+def _keep(job: dict, world: int) -> str:
+    """Move a finished job's artifacts to their final place; failed jobs stay where they are."""
+    dst = final_dir(job["op"], job["impl"], job["trial"], world)
+    if os.path.isdir(dst):
+        shutil.rmtree(dst)
+    os.makedirs(os.path.dirname(dst), exist_ok=True)
+    shutil.move(job["job_dir"], dst)
+    job["job_dir"] = dst
+    return dst
+
+
+def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rtol: float | None = None, measure_perf=False,
+            cooldown: float | None = None, **job_kw) -> dict:
+    from ..workloads import registry
+
+    spec = registry.get(op)
+    atol = spec.atol if atol is None else atol
+    rtol = spec.rtol if rtol is None else rtol
+    cooldown = env.cooldown_sec() if cooldown is None else cooldown
+    results, all_ok, interrupted, env_failed = [], True, False, False
+    for t in range(trials):
+        hygiene.between_jobs()
+        ref_job = run_job(spec.name, "reference", nproc, trial=t, measure_perf=measure_perf, **job_kw)
+        time.sleep(cooldown)
+        cand_job = run_job(spec.name, "ours", nproc, trial=t, measure_perf=measure_perf, **job_kw)
+        cmp = None
+        if ref_job["artifact_count"] and cand_job["artifact_count"]:
+            cmp = compare.compare_dirs(ref_job["job_dir"], cand_job["job_dir"], atol, rtol, expected_ranks=nproc)
+        verdict = report.classify_trial(ref_job, cand_job, cmp)
+        ref_perf = report.summarize_perf(ref_job["job_dir"]) if measure_perf else None
+        cand_perf = report.summarize_perf(cand_job["job_dir"]) if measure_perf else None
+        print(report.trial_line(t, verdict, ref_perf, cand_perf), flush=True)
+        ok = verdict["result"] == "match"
+        entry = {"trial": t, **verdict, "compare": cmp, "reference_returncode": ref_job["returncode"],
+                 "ours_returncode": cand_job["returncode"], "reference_artifact_names": ref_job["artifact_names"],
+                 "ours_artifact_names": cand_job["artifact_names"], "reference_perf": ref_perf, "ours_perf": cand_perf}
+        if ref_perf and cand_perf:
+            entry["speedup"] = ref_perf["wall_time_ms_max"] / cand_perf["wall_time_ms_max"]
+        if not ok:
+            for name, job in (("reference_job", ref_job), ("ours_job", cand_job)):
+                if job["returncode"] != 0 or job["artifact_count"] == 0:
+                    entry[name] = {"returncode": job["returncode"], "artifact_count": job["artifact_count"],
+                                   "elastic_error_files": job["elastic_error_files"], "worker_logs_dir": job["job_dir"],
+                                   **report.bounded_output(job["stdout"], job["stderr"])}
+                    print(f"--- {job['impl']} job failed (rc={job['returncode']}), logs kept in {job['job_dir']}", flush=True)
+                    print(job["stderr"][-2000:], flush=True)
+        else:
+            _keep(ref_job, nproc)
+            _keep(cand_job, nproc)
+        results.append(entry)
+        interrupted = interrupted or verdict["result"] == "interrupted"
+        env_failed = env_failed or verdict["result"] == "harness_environment"
+        if not ok:
+            all_ok = False
+            entry["early_stop"] = True
+            break
+    summary = {"version": 1, "backend": "local", "mode": "eval", "op": spec.name, "problem_ids": list(spec.problem_ids),
+               "all_ok": all_ok, "interrupted": interrupted, "harness_environment_failed": env_failed,
+               "trials": results, "nproc_per_node": nproc, "atol": atol, "rtol": rtol, "git_sha": env.git_sha()}
+    print("all trials match" if all_ok else "mismatch", flush=True)
+    print("EVAL_JSON:" + json.dumps(summary), flush=True)
+    return summary
+
+
+def cmd_list(_args) -> int:
+    from ..workloads import registry
+
+    for s in registry.all_ops():
+        impl = "ours+ref" if s.ours is not None else "ref only"
+        print(f"{s.name:32s} group={s.group:12s} problems={','.join(map(str, s.problem_ids)) or '-':12s} {impl:8s} configs={','.join(s.configs)}")
+    cov = registry.coverage()
+    print(f"{len(registry.all_ops())} ops; reference problems covered: {len(cov)}/87")
+    return 0
+
+
+def cmd_run(a) -> int:
+    from ..workloads import registry
+
+    job = run_job(registry.get(a.op).name, a.impl, a.nproc, trial=a.trial, config=a.config,
+                  overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, measure_perf=a.measure_perf,
+                  warmup=a.warmup, iters=a.iters, graph=a.graph, profile=a.profile, timeout_s=a.timeout)
+    ok = job["returncode"] == 0 and job["artifact_count"] == a.nproc
+    if ok:
+        perf = report.summarize_perf(job["job_dir"])
+        _keep(job, a.nproc)
+        print(f"dry run ok: {job['artifact_count']} rank files in {job['job_dir']}")
+        if perf:
+            print(f"Perf: max wall time (across ranks) {perf['wall_time_ms_max']:.4f} ms (mean {perf['wall_time_ms_mean']:.4f} ms, ranks={perf['n_ranks']})")
+        return 0
+    hint = report.environment_hint(job["stdout"] + job["stderr"])
+    print(f"job failed rc={job['returncode']} artifacts={job['artifact_count']} logs={job['job_dir']}" + (f" environment: {hint}" if hint else ""))
+    print(job["stderr"][-4000:])
+    return 130 if job["interrupted"] else 1
+
+
+def cmd_eval(a) -> int:
+    from ..workloads import registry
+
+    s = eval_op(a.op, a.nproc, trials=a.trials, atol=a.atol, rtol=a.rtol, measure_perf=a.measure_perf, config=a.config,
+                overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
+                graph=a.graph, profile=a.profile, timeout_s=a.timeout)
+    if s["interrupted"]:
+        return 130
+    return 0 if s["all_ok"] else 1
+
+
+def cmd_sweep(a) -> int:
+    """ops x world sizes; one JSON line per cell appended to the ledger, finished cells skipped with --resume."""
+    from ..workloads import registry
+
+    ops = [s.name for s in registry.all_ops() if s.ours is not None] if a.ops == "all" else a.ops.split(",")
+    worlds = [int(w) for w in a.worlds.split(",")]
+    ledger = a.ledger or os.path.join(LOGS_ROOT, "results.jsonl")
+    os.makedirs(os.path.dirname(ledger), exist_ok=True)
+    done = set()
+    if a.resume and os.path.exists(ledger):
+        with open(ledger) as fh:
+            for line in fh:
+                try:
+                    d = json.loads(line)
+                    if d.get("git_sha") == env.git_sha() or a.any_sha:
+                        done.add((d["op"], d["world"], d.get("config", "default")))
+                except ValueError:
+                    pass
+    rc = 0
+    for op in ops:
+        for w in worlds:
+            if (op, w, a.config) in done:
+                print(f"skip {op} w={w} (already in {ledger})")
+                continue
+            s = eval_op(op, w, trials=a.trials, measure_perf=a.measure_perf, config=a.config, backend=a.backend,
+                        warmup=a.warmup, iters=a.iters, timeout_s=a.timeout)
+            last = s["trials"][-1] if s["trials"] else {}
+            cell = {"op": op, "world": w, "config": a.config, "all_ok": s["all_ok"], "git_sha": s["git_sha"],
+                    "result": last.get("result"), "speedup": last.get("speedup"),
+                    "ref_ms": (last.get("reference_perf") or {}).get("wall_time_ms_max"),
+                    "ours_ms": (last.get("ours_perf") or {}).get("wall_time_ms_max"),
+                    "pct_of_roofline": (last.get("ours_perf") or {}).get("pct_of_roofline"),
+                    "limiter": (last.get("ours_perf") or {}).get("limiter"), "time": time.time()}
+            with open(ledger, "a") as fh:
+                fh.write(json.dumps(cell) + "\n")
+            rc = rc or (0 if s["all_ok"] else 1)
+    return rc
+
+
+def cmd_inspect(a) -> int:
+    from . import inspect_outputs
+
+    return inspect_outputs.main_compare(a)
+
+
+def cmd_perf_diff(a) -> int:
+    from . import inspect_outputs
+
+    return inspect_outputs.main_perf(a)
+
+
+def _common(sp, need_impl=False):
+    sp.add_argument("--op", required=True)
+    if need_impl:
+        sp.add_argument("--impl", default="ours", choices=["reference", "ours"])
+    sp.add_argument("--nproc", "--nproc-per-node", dest="nproc", type=int, default=1)
+    sp.add_argument("--config", default="default")
+    sp.add_argument("--set", action="append", default=[])
+    sp.add_argument("--dtype", default="bfloat16")
+    sp.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
+    sp.add_argument("--measure-perf", action="store_true")
+    sp.add_argument("--warmup", type=int, default=500)
+    sp.add_argument("--iters", type=int, default=100)
+    sp.add_argument("--graph", action="store_true")
+    sp.add_argument("--profile", action="store_true")
+    sp.add_argument("--timeout", type=float, default=1800.0)
+    sp.add_argument("--trial", type=int, default=0)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="parallelkernelbench_b200.harness.launch", description=__doc__,
+                                 formatter_class=argparse.RawDescriptionHelpFormatter)
+    sub = ap.add_subparsers(dest="verb", required=True)
+    sub.add_parser("list").set_defaults(fn=cmd_list)
+    sp = sub.add_parser("run"); _common(sp, need_impl=True); sp.set_defaults(fn=cmd_run)
+    sp = sub.add_parser("eval"); _common(sp)
+    sp.add_argument("--trials", type=int, default=5)
+    sp.add_argument("--atol", type=float, default=None)
+    sp.add_argument("--rtol", type=float, default=None)
+    sp.set_defaults(fn=cmd_eval)
+    sp = sub.add_parser("sweep")
+    sp.add_argument("--ops", default="all")
+    sp.add_argument("--worlds", default="1,2,4,8")
+    sp.add_argument("--config", default="default")
+    sp.add_argument("--trials", type=int, default=1)
+    sp.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
+    sp.add_argument("--measure-perf", action="store_true")
+    sp.add_argument("--warmup", type=int, default=500)
+    sp.add_argument("--iters", type=int, default=100)
+    sp.add_argument("--timeout", type=float, default=1800.0)
+    sp.add_argument("--ledger", default=None)
+    sp.add_argument("--resume", action="store_true")
+    sp.add_argument("--any-sha", action="store_true", help="with --resume: accept cells recorded at another commit")
+    sp.set_defaults(fn=cmd_sweep)
+    for name, fn in (("inspect", cmd_inspect), ("perf-diff", cmd_perf_diff)):
+        sp = sub.add_parser(name)
+        sp.add_argument("--op", required=True)
+        sp.add_argument("--world", type=int, default=None)
+        sp.add_argument("--trial", type=int, default=0)
+        sp.add_argument("--atol", type=float, default=1e-2)
+        sp.add_argument("--rtol", type=float, default=1e-2)
+        sp.add_argument("--max-print", type=int, default=8)
+        sp.set_defaults(fn=fn)
+    args = ap.parse_args(argv)
+    try:
+        return args.fn(args)
+    except KeyboardInterrupt:
+        return 130
+
+
+if __name__ == "__main__":
+    sys.exit(main())

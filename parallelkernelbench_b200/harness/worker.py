@@ -1,0 +1,134 @@
+"""Per-rank worker, started once per GPU (or CPU rank) by torchrun.
+
+Flow: bind the rank, create the process group -> build the op's seeded inputs -> run the chosen
+implementation once -> synchronise and barrier -> save ``rank_<r>.pt`` -> optionally time it
+(500 warm-up / 100 timed by default) into ``rank_<r>_perf.json`` -> optionally record a
+torch-profiler trace -> tear the group down in ``finally``. The native library is prebuilt, so no
+rank compiles anything (the reference JIT-compiles per rank and isolates extension caches to
+avoid races: reference: scripts/worker.py:49-55,118-237).
+
+    torchrun --nproc-per-node N -m parallelkernelbench_b200.harness.worker --op allreduce \
+        --impl ours --logs-dir DIR [--config default] [--set m=2048] [--dtype bfloat16] [--trial 0] \
+        [--measure-perf --warmup 500 --iters 100 --graph] [--profile] [--backend gloo]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+
+def parse_args(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--op", required=True)
+    ap.add_argument("--impl", required=True, choices=["reference", "ours"])
+    ap.add_argument("--logs-dir", required=True)
+    ap.add_argument("--config", default="default")
+    ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--trial", type=int, default=0)
+    ap.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
+    ap.add_argument("--measure-perf", action="store_true")
+    ap.add_argument("--warmup", type=int, default=500)
+    ap.add_argument("--iters", type=int, default=100)
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the op")
+    ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--fail-rank", type=int, default=-1, help="test hook: this rank raises before the first collective")
+    ap.add_argument("--exit-rank", type=int, default=-1, help="test hook: this rank exits non-zero before the first collective")
+    return ap.parse_args(argv)
+
+
+def run_worker(args) -> int:
+    from ..parallel import init_context
+    from ..workloads import registry
+    from . import compare, timing
+    from .roofline import estimate
+
+    if "RANK" not in os.environ and int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        print("worker must be started by torchrun", file=sys.stderr)
+        return 2
+    rank_env = int(os.environ.get("RANK", "0"))
+    if args.fail_rank == rank_env:
+        raise RuntimeError(f"injected failure on rank {rank_env} (test hook)")
+    if args.exit_rank == rank_env:
+        return 3
+    ctx = init_context(backend=args.backend, timeout_s=float(os.environ.get("PKB_PG_TIMEOUT_SEC", "600")))
+    rc = 0
+    try:
+        spec = registry.get(args.op)
+        cfg = spec.config(args.config, registry.parse_overrides(args.set))
+        dtype = registry.DTYPES[args.dtype]
+        run = registry.RunCtx(ctx, spec.name, trial=args.trial, dtype=dtype)
+        impl = spec.reference if args.impl == "reference" else spec.ours
+        if impl is None:
+            raise NotImplementedError(f"op {spec.name} has no '{args.impl}' implementation")
+        if args.impl == "ours" and spec.ours_needs_cuda and not ctx.is_cuda:
+            raise RuntimeError(f"op {spec.name}: our implementation is a CUDA kernel and needs a GPU")
+        print(f"[Rank {ctx.rank}/{ctx.world}] {spec.name} impl={args.impl} cfg={cfg} dtype={args.dtype} "
+              f"device={ctx.device} backend={ctx.backend}", flush=True)
+        inputs = spec.make_inputs(run, cfg)
+        with torch.no_grad():
+            y = impl(run, *inputs)
+        if ctx.is_cuda:
+            torch.cuda.synchronize()
+            if args.impl == "ours":
+                from .. import _native as nv
+
+                nv.raise_on_status(sync=False)
+        ctx.barrier()
+        compare.save_output(y, args.logs_dir, ctx.rank)
+
+        if args.measure_perf:
+            with torch.no_grad():
+                perf = timing.measure(lambda *a: impl(run, *a), inputs, warmup=args.warmup, iters=args.iters,
+                                      device=ctx.device, use_graph=args.graph)
+            if spec.cost is not None:
+                perf.update(estimate(spec.cost(cfg, ctx.world), perf["wall_time_ms"]))
+            perf.update({"op": spec.name, "impl": args.impl, "world": ctx.world, "rank": ctx.rank, "config": cfg,
+                         "dtype": args.dtype})
+            with open(os.path.join(args.logs_dir, f"rank_{ctx.rank}_perf.json"), "w") as fh:
+                json.dump(perf, fh)
+            print(f"[Rank {ctx.rank}] {perf['wall_time_ms']:.4f} +- {perf['wall_time_std_ms']:.4f} ms "
+                  f"(min {perf['min_time_ms']:.4f}, {perf['iterations']} iters after {perf['warmup_iterations']} warm-up)",
+                  flush=True)
+
+        if args.profile and ctx.is_cuda:
+            from torch.profiler import ProfilerActivity, profile
+
+            os.makedirs(os.path.join(args.logs_dir, "traces"), exist_ok=True)
+            with torch.no_grad():
+                for _ in range(3):
+                    impl(run, *inputs)
+                torch.cuda.synchronize()
+                with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
+                    for _ in range(10):
+                        with torch.cuda.nvtx.range(f"{spec.name}:{args.impl}"):
+                            impl(run, *inputs)
+                    torch.cuda.synchronize()
+            prof.export_chrome_trace(os.path.join(args.logs_dir, "traces", f"rank_{ctx.rank}.json"))
+    except Exception:
+        rc = 1
+        traceback.print_exc()
+        err = os.environ.get("TORCHELASTIC_ERROR_FILE")
+        if err:
+            try:
+                with open(err + f".rank{ctx.rank}", "w") as fh:
+                    fh.write(traceback.format_exc())
+            except OSError:
+                pass
+    finally:
+        ctx.finalize()
+    return rc
+
+
+def main(argv=None) -> int:
+    return run_worker(parse_args(argv))
+
+
+if __name__ == "__main__":
+    sys.exit(main())

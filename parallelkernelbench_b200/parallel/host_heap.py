@@ -102,7 +102,7 @@ class HostHeap:
         raise RuntimeError(f"{what} failed (code {rc}): {msg}")
 
     def _scratch(self, nbytes: int) -> int:
-        key = "_scratch"
+        key = "_scratch_buf"
         cur = getattr(self, key, None)
         if cur is None or cur[1] < nbytes:
             cap = 1 << max(12, (max(nbytes, 1) - 1).bit_length())

@@ -9,6 +9,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200 box)")
     config.addinivalue_line("markers", "multigpu: needs more than one CUDA device")
+    config.addinivalue_line("markers", "expect_status: the test provokes a device status word on purpose")
 
 
 @pytest.fixture(autouse=True)

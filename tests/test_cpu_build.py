@@ -1,0 +1,32 @@
+"""The build entry point works on a machine without a GPU and leaves loadable libraries in-tree."""
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def test_build_entry_point_and_symbols():
+    import __graft_entry__ as g
+
+    g.build()
+    from parallelkernelbench_b200 import _native as nv
+
+    lib = nv.cuda_lib()
+    for sym in ("pkb_gemm_bf16", "pkb_gemm_bf16_pair", "pkb_rmsnorm_bf16", "pkb_coll_reduce", "pkb_coll_gather",
+                "pkb_coll_allreduce_nvls", "pkb_tp_ag_gemm", "pkb_tp_gemm_rs_rmsnorm", "pkb_heap_create"):
+        assert hasattr(lib, sym), sym
+    assert nv.host_lib().pkbh_ctrl_bytes() == 1 << 20
+
+
+def test_missing_library_raises_loudly(monkeypatch, tmp_path):
+    from parallelkernelbench_b200 import _native as nv
+
+    monkeypatch.setattr(nv, "_LIB_DIR", tmp_path)
+    monkeypatch.setattr(nv, "_cuda", None)
+    try:
+        nv.cuda_lib()
+    except nv.NativeLibraryError as e:
+        assert "Build it" in str(e)
+    else:
+        raise AssertionError("a missing kernel library must not be silently ignored")

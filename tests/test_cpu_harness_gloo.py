@@ -1,0 +1,63 @@
+"""End-to-end harness runs with no GPU: torchrun + gloo ranks, ours = shared-memory twin."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _launch(*args, timeout=300):
+    env = dict(os.environ, PKB_LOGS_DIR=os.path.join(ROOT, "logs", "pytest"), PKB_COOLDOWN_SEC="0")
+    r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", *args], cwd=ROOT, env=env,
+                       capture_output=True, text=True, timeout=timeout)
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("EVAL_JSON:")]
+    return r, (json.loads(line[-1][len("EVAL_JSON:"):]) if line else None)
+
+
+def test_plumbing_config_world2_matches_gloo_to_1e5():
+    r, js = _launch("eval", "--op", "plumbing", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "2",
+                    "--atol", "1e-5", "--rtol", "1e-5")
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert js["all_ok"] and len(js["trials"]) == 2 and js["trials"][0]["result"] == "match"
+    assert js["trials"][0]["ours_artifact_names"] == ["rank_0.pt", "rank_1.pt"]
+
+
+@pytest.mark.parametrize("op", ["allreduce", "allgather", "reducescatter", "alltoall", "broadcast", "reduce", "scatter", "gather"])
+def test_collectives_world2_gloo(op):
+    r, js = _launch("eval", "--op", op, "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
+                    "--config", "small")
+    assert r.returncode == 0 and js["all_ok"], r.stdout[-1500:] + r.stderr[-1500:]
+
+
+def test_perf_artifacts_and_speedup_line():
+    r, js = _launch("eval", "--op", "allreduce", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
+                    "--config", "small", "--measure-perf", "--warmup", "3", "--iters", "5")
+    assert r.returncode == 0
+    t = js["trials"][0]
+    assert t["reference_perf"]["n_ranks"] == 2 and t["ours_perf"]["wall_time_ms_max"] > 0 and t["speedup"] > 0
+    assert "speedup" in r.stdout
+
+
+def test_rank_that_raises_is_reported_not_hung():
+    from parallelkernelbench_b200.harness import launch
+
+    job = launch.run_job("allreduce", "ours", 2, backend="gloo", dtype="float32", config="small",
+                         extra_worker_args=["--fail-rank", "1"], timeout_s=120, pg_timeout_s=20)
+    assert job["returncode"] != 0 and job["artifact_count"] == 0 and not job["timed_out"]
+    assert "injected failure on rank 1" in job["stderr"]
+
+
+def test_rank_that_exits_nonzero_is_reported():
+    from parallelkernelbench_b200.harness import launch
+
+    job = launch.run_job("allreduce", "reference", 2, backend="gloo", dtype="float32", config="small",
+                         extra_worker_args=["--exit-rank", "0"], timeout_s=120, pg_timeout_s=20)
+    assert job["returncode"] != 0 and job["artifact_count"] == 0
+
+
+def test_unknown_op_is_a_clean_failure():
+    r, js = _launch("run", "--op", "no_such_op", "--nproc", "1", "--backend", "gloo")
+    assert r.returncode != 0

@@ -1,0 +1,44 @@
+import torch
+
+from parallelkernelbench_b200.parallel import mesh
+from parallelkernelbench_b200.utils.seeding import seed_for
+from parallelkernelbench_b200.workloads import registry
+
+
+def test_registry_loads_and_every_op_is_complete():
+    ops = registry.all_ops()
+    assert len(ops) >= 9
+    for s in ops:
+        assert s.reference is not None and callable(s.make_inputs) and "default" in s.configs or s.configs
+        assert s.atol > 0 and s.rtol > 0
+    assert registry.get("1").name == "allreduce"
+    assert registry.parse_overrides(["m=4", "x=1.5", "flag=true", "s=abc"]) == {"m": 4, "x": 1.5, "flag": True, "s": "abc"}
+
+
+def test_seeds_differ_by_rank_trial_and_op():
+    seeds = {seed_for(op, r, t) for op in ("a", "b") for r in range(8) for t in range(5)}
+    assert len(seeds) == 80
+
+
+def test_mesh_groups_megatron_order():
+    assert mesh.inner_groups(8, 2) == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert mesh.outer_groups(8, 2) == [[0, 2, 4, 6], [1, 3, 5, 7]]
+    m = mesh.Mesh2D.build(8, 4, rank=6, create_groups=False)
+    assert (m.outer, m.inner_rank, m.outer_rank) == (2, 2, 1)
+    assert m.inner_ranks == [4, 5, 6, 7] and m.outer_ranks == [2, 6]
+    assert mesh.factor_two_level(8, 2) == (4, 2) and mesh.factor_two_level(3, 2) == (3, 1)
+
+
+def test_input_factories_are_deterministic_on_cpu():
+    class FakeDist:
+        rank, world, device = 1, 4, torch.device("cpu")
+        is_cuda = False
+    spec = registry.get("alltoall")
+    a = spec.make_inputs(registry.RunCtx(FakeDist(), spec.name, trial=0, dtype=torch.float32), spec.config("small"))
+    b = spec.make_inputs(registry.RunCtx(FakeDist(), spec.name, trial=0, dtype=torch.float32), spec.config("small"))
+    assert torch.equal(a[0], b[0]) and a[0][2, 0, 0] == 12.0
+    rc0 = registry.RunCtx(FakeDist(), "x", trial=0, dtype=torch.float32)
+    rc1 = registry.RunCtx(FakeDist(), "x", trial=1, dtype=torch.float32)
+    assert not torch.equal(rc0.randn(8), rc1.randn(8))
+    assert torch.equal(registry.RunCtx(FakeDist(), "x", 0, torch.float32).randn(8, shared=True),
+                       registry.RunCtx(type("D", (), {"rank": 3, "world": 4, "device": torch.device("cpu")})(), "x", 0, torch.float32).randn(8, shared=True))

@@ -29,6 +29,21 @@ def test_gemm_matches_fp32_reference(M, N, K, block_n):
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 1024), (300, 520, 136), (1000, 72, 40), (2048, 3584, 512)])
+def test_pair_gemm_matches_reference_and_single_cta_kernel(M, N, K):
+    from parallelkernelbench_b200.ops import gemm_bf16
+
+    g = torch.Generator(device="cuda").manual_seed(99 + M)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16, generator=g)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16, generator=g) * 0.05
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    gemm_bf16(a, w, out=out, mode="pair")
+    torch.testing.assert_close(out.float(), _ref(a, w), atol=2e-2, rtol=2e-2)
+    assert torch.equal(out, gemm_bf16(a, w, mode="single"))
+    out32 = gemm_bf16(a, w, mode="pair", out_dtype=torch.float32, epilogue="silu")
+    torch.testing.assert_close(out32, _ref(a, w, act="silu"), atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("epilogue", ["none", "silu", "bias", "bias_silu"])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_epilogues(epilogue, out_dtype):
