@@ -1,0 +1,401 @@
+// Memory-bound kernels around the GEMMs: RoPE, fp8 1x128 block quantise / dequantise, fused
+// Adam / AdamW, vocab-parallel cross-entropy statistics, column reductions for the LayerNorm
+// backward, and a tensor-parallel RMSNorm whose cross-rank sum runs inside the kernel.
+// All use 16-byte global accesses and fp32 arithmetic.
+//
+// Reference behaviour: reference/17_rope_allgather.py:10-37, reference/19_blocked_fp8_quantize.py:7-23,
+// reference/20_blocked_fp8_dequantize.py:6-16, reference/43_fused_adam_grad_unshard_allgather.py:28-40,
+// reference/47_fsdp_step_e2e.py:52-65, reference/73_vocab_parallel_cross_entropy_loss.py:21-42,
+// reference/9_layernorm_backward.py:6-11, reference/18_tp_rms_norm.py:9-19.
+#include <cuda_fp8.h>
+
+#include "pkb/api.h"
+#include "pkb/collectives_api.h"
+#include "pkb/host.h"
+#include "pkb/symm.cuh"
+
+namespace pkb {
+
+// ================================================================================================
+// RoPE (rotate-half): x is [tokens, heads, dim]; cos/sin are [tokens, dim] (the two halves of a row
+// of cos/sin normally repeat). out[.., :d/2] = x1*cos1 - x2*sin1 ; out[.., d/2:] = x2*cos2 + x1*sin2
+// ================================================================================================
+template <typename T>
+__global__ void rope_kernel(const T* __restrict__ x, const T* __restrict__ cs, const T* __restrict__ sn,
+                            T* __restrict__ out, long long tokens, int heads, int dim) {
+  const int half = dim >> 1;
+  const long long total = tokens * heads * half;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % half);
+    const long long th = i / half;
+    const long long t = th / heads;
+    const T* xr = x + th * dim;
+    const float x1 = (float)xr[j], x2 = (float)xr[j + half];
+    const float c1 = (float)cs[t * dim + j], c2 = (float)cs[t * dim + j + half];
+    const float s1 = (float)sn[t * dim + j], s2 = (float)sn[t * dim + j + half];
+    out[th * dim + j] = (T)(x1 * c1 - x2 * s1);
+    out[th * dim + j + half] = (T)(x2 * c2 + x1 * s2);
+  }
+}
+
+// ================================================================================================
+// fp8 e4m3 quantise with one fp32 scale per 128 consecutive elements: s = amax/448 (1 if amax = 0),
+// y = sat(x / s). One warp handles one block: 4 elements per lane.
+// ================================================================================================
+template <typename T>
+__global__ void fp8_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, float* __restrict__ scales,
+                                 long long nblocks, int pow2_scales) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long b = warp; b < nblocks; b += nwarps) {
+    const T* p = x + b * 128 + lane * 4;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = (float)p[j];
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = warp_max(amax);
+    float s = amax / 448.0f;
+    if (pow2_scales && s > 0.f) s = exp2f(ceilf(log2f(s)));  // power-of-two scale (exact to undo)
+    if (s == 0.f) s = 1.0f;
+    const float inv = 1.0f / s;
+    __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+    __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+    reinterpret_cast<uint32_t*>(y + b * 128)[lane] = (uint32_t)lo | ((uint32_t)hi << 16);
+    if (lane == 0) scales[b] = s;
+  }
+}
+
+template <typename T>
+__global__ void fp8_dequant_kernel(const uint8_t* __restrict__ y, const float* __restrict__ scales,
+                                   T* __restrict__ x, long long nblocks) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long b = warp; b < nblocks; b += nwarps) {
+    const uint32_t packed = reinterpret_cast<const uint32_t*>(y + b * 128)[lane];
+    const float s = scales[b];
+    __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed & 0xffffu), __NV_E4M3);
+    __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed >> 16), __NV_E4M3);
+    float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
+    float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+    T* o = x + b * 128 + lane * 4;
+    o[0] = (T)(f0.x * s); o[1] = (T)(f0.y * s); o[2] = (T)(f1.x * s); o[3] = (T)(f1.y * s);
+  }
+}
+
+// ================================================================================================
+// Adam / AdamW on fp32 master weights. grad is fp32 or bf16 and is multiplied by grad_scale first.
+// decoupled = 1: AdamW (p *= 1 - lr*wd before the update); 0: L2 folded into the gradient.
+// Optionally writes a bf16 copy of the new parameters (what the next forward consumes).
+// ================================================================================================
+struct AdamArgs {
+  float lr, beta1, beta2, eps, weight_decay, grad_scale, bias_c1, bias_c2;
+  int decoupled;
+};
+
+template <typename G>
+__global__ void adam_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                            const G* __restrict__ g, __nv_bfloat16* __restrict__ p_bf16, long long n, AdamArgs a) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float grad = (float)g[i] * a.grad_scale;
+    float w = p[i];
+    if (a.decoupled) w *= (1.0f - a.lr * a.weight_decay);
+    else grad += a.weight_decay * w;
+    const float mi = a.beta1 * m[i] + (1.0f - a.beta1) * grad;
+    const float vi = a.beta2 * v[i] + (1.0f - a.beta2) * grad * grad;
+    const float mhat = mi / a.bias_c1;
+    const float vhat = vi / a.bias_c2;
+    w -= a.lr * mhat / (sqrtf(vhat) + a.eps);
+    p[i] = w; m[i] = mi; v[i] = vi;
+    if (p_bf16) p_bf16[i] = __float2bfloat16_rn(w);
+  }
+}
+
+// ================================================================================================
+// Vocab-parallel cross-entropy, local pass: per row of this rank's logit shard emit
+// {local max, sum exp(x - local max), target logit (0 if the target lives on another rank)}.
+// The three values of all ranks are then combined (tiny all-gather) by ce_finalize_kernel.
+// ================================================================================================
+template <typename T>
+__global__ void ce_stats_kernel(const T* __restrict__ logits, const long long* __restrict__ target,
+                                float* __restrict__ stats, int rows, int vocab_local, long long vocab_start) {
+  __shared__ float red[32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* lr = logits + (long long)row * vocab_local;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < vocab_local; i += blockDim.x) mx = fmaxf(mx, (float)lr[i]);
+    mx = warp_max(mx);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = -INFINITY;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float se = 0.f;
+    for (int i = threadIdx.x; i < vocab_local; i += blockDim.x) se += __expf((float)lr[i] - mx);
+    se = warp_sum(se);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = se;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+      const long long t = target[row] - vocab_start;
+      stats[row * 3 + 0] = mx;
+      stats[row * 3 + 1] = tot;
+      stats[row * 3 + 2] = (t >= 0 && t < vocab_local) ? (float)lr[t] : 0.f;
+    }
+    __syncthreads();
+  }
+}
+
+// stats_all is [W, rows, 3]; loss[row] = log(sum_w se_w * exp(mx_w - gmax)) + gmax - sum_w tgt_w
+__global__ void ce_finalize_kernel(const float* __restrict__ stats_all, float* __restrict__ loss, int rows, int world) {
+  for (int row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
+    float gmax = -INFINITY;
+    for (int w = 0; w < world; ++w) gmax = fmaxf(gmax, stats_all[((long long)w * rows + row) * 3]);
+    float se = 0.f, tgt = 0.f;
+    for (int w = 0; w < world; ++w) {
+      const float* s = stats_all + ((long long)w * rows + row) * 3;
+      se += s[1] * __expf(s[0] - gmax);
+      tgt += s[2];
+    }
+    loss[row] = logf(se) + gmax - tgt;
+  }
+}
+
+// ================================================================================================
+// Column reductions of the LayerNorm backward: dgamma[c] = sum_r dY[r,c] * Xhat[r,c], dbeta[c] = sum_r dY[r,c]
+// One block per 32-column strip; 32 x 8 threads walk the rows, shared-memory finish. fp32 output.
+// ================================================================================================
+template <typename T>
+__global__ void ln_bwd_colreduce_kernel(const T* __restrict__ xhat, const T* __restrict__ dy,
+                                        float* __restrict__ dgamma, float* __restrict__ dbeta, int rows, int cols) {
+  __shared__ float sg[8][33], sb[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
+  float g = 0.f, b = 0.f;
+  if (c < cols) {
+    for (int r = threadIdx.y; r < rows; r += 8) {
+      const float d = (float)dy[(long long)r * cols + c];
+      g += d * (float)xhat[(long long)r * cols + c];
+      b += d;
+    }
+  }
+  sg[threadIdx.y][threadIdx.x] = g;
+  sb[threadIdx.y][threadIdx.x] = b;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < cols) {
+    for (int k = 1; k < 8; ++k) { g += sg[k][threadIdx.x]; b += sb[k][threadIdx.x]; }
+    dgamma[c] = g;
+    dbeta[c] = b;
+  }
+}
+
+// ================================================================================================
+// Tensor-parallel RMSNorm (hidden dimension sharded): every block owns a set of rows on every rank,
+// publishes their local sums of squares in the symmetric heap, crosses ONE in-kernel barrier with the
+// same-index blocks of the peers, adds the peers' partial sums and normalises. One launch, no NCCL.
+// ================================================================================================
+struct TpRmsArgs {
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* gamma;
+  __nv_bfloat16* y;
+  int rows, cols_local;
+  long long cols_total;
+  float eps;
+  uint64_t sums_off;  // heap offset of fp32 [rows] partial sums
+};
+
+__global__ void __launch_bounds__(256) tp_rmsnorm_kernel(const SymmCtx c, const TpRmsArgs a) {
+  __shared__ float red[8];
+  float* my_sums = symm_local<float>(c, a.sums_off);
+  const int rows_per_block = (a.rows + gridDim.x - 1) / gridDim.x;
+  const int r0 = blockIdx.x * rows_per_block;
+  const int r1 = min(a.rows, r0 + rows_per_block);
+  for (int row = r0; row < r1; ++row) {
+    const __nv_bfloat16* xr = a.x + (long long)row * a.cols_local;
+    float ss = 0.f;
+    for (int i = threadIdx.x * 8; i < a.cols_local; i += blockDim.x * 8) {
+      U4 u = ld_global_v4(xr + i);
+      float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+      ss += f0.x * f0.x + f0.y * f0.y + f1.x * f1.x + f1.y * f1.y + f2.x * f2.x + f2.y * f2.y + f3.x * f3.x + f3.y * f3.y;
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += red[w];
+      my_sums[row] = t;
+    }
+    __syncthreads();
+  }
+  if (!symm_block_barrier(c, 400, 1)) return;
+  for (int row = r0; row < r1; ++row) {
+    float tot = 0.f;
+    for (int g = 0; g < c.gsize; ++g) tot += symm_ptr<float>(c, c.members[g], a.sums_off)[row];
+    const float rstd = rsqrtf(tot / (float)a.cols_total + a.eps);
+    const __nv_bfloat16* xr = a.x + (long long)row * a.cols_local;
+    __nv_bfloat16* yr = a.y + (long long)row * a.cols_local;
+    for (int i = threadIdx.x * 8; i < a.cols_local; i += blockDim.x * 8) {
+      U4 u = ld_global_v4(xr + i), g = ld_global_v4(a.gamma + i);
+      float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+      float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+      U4 o{pack_bf16x2(f0.x * rstd * g0.x, f0.y * rstd * g0.y), pack_bf16x2(f1.x * rstd * g1.x, f1.y * rstd * g1.y),
+           pack_bf16x2(f2.x * rstd * g2.x, f2.y * rstd * g2.y), pack_bf16x2(f3.x * rstd * g3.x, f3.y * rstd * g3.y)};
+      st_global_v4(yr + i, o);
+    }
+  }
+  // the sums buffer is rewritten by the next call: peers must have read it first
+  symm_block_barrier(c, 400, 2);
+}
+
+static int grid_1d(long long work_items, int threads, int max_blocks = 148 * 8) {
+  long long b = (work_items + threads - 1) / threads;
+  if (b < 1) b = 1;
+  return (int)(b > max_blocks ? max_blocks : b);
+}
+
+static SymmCtx ctx_of(const pkb_symm_ctx* h) {
+  SymmCtx c;
+  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
+  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
+  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
+  c.channel = h->channel;
+  c.status = status_block_device_ptr();
+  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
+  return c;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+extern "C" {
+
+// dtype: 0 bf16, 1 fp32
+int pkb_rope(const void* x, const void* cos_t, const void* sin_t, void* out, long long tokens, int heads,
+             int dim, int dtype, void* stream) {
+  PKB_CHECK_ARG(dim % 2 == 0 && tokens >= 0 && heads > 0, "bad RoPE shape");
+  if (tokens == 0) return kApiOk;
+  const long long total = tokens * heads * (dim / 2);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    rope_kernel<__nv_bfloat16><<<grid_1d(total, 256), 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(cos_t),
+        static_cast<const __nv_bfloat16*>(sin_t), static_cast<__nv_bfloat16*>(out), tokens, heads, dim);
+  else
+    rope_kernel<float><<<grid_1d(total, 256), 256, 0, s>>>(static_cast<const float*>(x), static_cast<const float*>(cos_t),
+                                                        static_cast<const float*>(sin_t), static_cast<float*>(out),
+                                                        tokens, heads, dim);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_fp8_quant_1x128(const void* x, void* y, void* scales, long long n, int dtype, int pow2_scales, void* stream) {
+  PKB_CHECK_ARG(n % 128 == 0, "element count must be a multiple of 128");
+  if (n == 0) return kApiOk;
+  const long long nb = n / 128;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_1d(nb * 32, 256);
+  if (dtype == 0)
+    fp8_quant_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(y),
+                                                        static_cast<float*>(scales), nb, pow2_scales);
+  else
+    fp8_quant_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), static_cast<uint8_t*>(y),
+                                                static_cast<float*>(scales), nb, pow2_scales);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_fp8_dequant_1x128(const void* y, const void* scales, void* x, long long n, int dtype, void* stream) {
+  PKB_CHECK_ARG(n % 128 == 0, "element count must be a multiple of 128");
+  if (n == 0) return kApiOk;
+  const long long nb = n / 128;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_1d(nb * 32, 256);
+  if (dtype == 0)
+    fp8_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(y), static_cast<const float*>(scales),
+                                                          static_cast<__nv_bfloat16*>(x), nb);
+  else
+    fp8_dequant_kernel<float><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(y), static_cast<const float*>(scales),
+                                                  static_cast<float*>(x), nb);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_adam(void* p, void* m, void* v, const void* g, void* p_bf16, long long n, int grad_dtype, float lr,
+             float beta1, float beta2, float eps, float weight_decay, float grad_scale, int step, int decoupled,
+             void* stream) {
+  PKB_CHECK_ARG(step >= 1, "step counts from 1");
+  if (n == 0) return kApiOk;
+  AdamArgs a{lr, beta1, beta2, eps, weight_decay, grad_scale, 1.0f - powf(beta1, (float)step),
+             1.0f - powf(beta2, (float)step), decoupled};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_1d(n, 256);
+  if (grad_dtype == 0)
+    adam_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<float*>(p), static_cast<float*>(m), static_cast<float*>(v),
+                                                   static_cast<const __nv_bfloat16*>(g),
+                                                   static_cast<__nv_bfloat16*>(p_bf16), n, a);
+  else
+    adam_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(p), static_cast<float*>(m), static_cast<float*>(v),
+                                           static_cast<const float*>(g), static_cast<__nv_bfloat16*>(p_bf16), n, a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_ce_stats(const void* logits, const void* target, void* stats, int rows, int vocab_local,
+                 long long vocab_start, int dtype, void* stream) {
+  if (rows == 0) return kApiOk;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  if (dtype == 0)
+    ce_stats_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(logits),
+                                                       static_cast<const long long*>(target),
+                                                       static_cast<float*>(stats), rows, vocab_local, vocab_start);
+  else
+    ce_stats_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(logits), static_cast<const long long*>(target),
+                                               static_cast<float*>(stats), rows, vocab_local, vocab_start);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_ce_finalize(const void* stats_all, void* loss, int rows, int world, void* stream) {
+  if (rows == 0) return kApiOk;
+  ce_finalize_kernel<<<grid_1d(rows, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(stats_all), static_cast<float*>(loss), rows, world);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_ln_bwd_colreduce(const void* xhat, const void* dy, void* dgamma, void* dbeta, int rows, int cols,
+                         int dtype, void* stream) {
+  if (cols == 0) return kApiOk;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 block(32, 8);
+  const int grid = (cols + 31) / 32;
+  if (dtype == 0)
+    ln_bwd_colreduce_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(static_cast<const __nv_bfloat16*>(xhat),
+                                                                 static_cast<const __nv_bfloat16*>(dy),
+                                                                 static_cast<float*>(dgamma), static_cast<float*>(dbeta),
+                                                                 rows, cols);
+  else
+    ln_bwd_colreduce_kernel<float><<<grid, block, 0, s>>>(static_cast<const float*>(xhat), static_cast<const float*>(dy),
+                                                         static_cast<float*>(dgamma), static_cast<float*>(dbeta), rows, cols);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_tp_rmsnorm(const pkb_symm_ctx* h, const void* x, const void* gamma, void* y, int rows, int cols_local,
+                   long long cols_total, float eps, unsigned long long sums_off, void* stream) {
+  PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
+  PKB_CHECK_ARG(cols_local % 8 == 0 && rows > 0, "cols_local must be a multiple of 8");
+  TpRmsArgs a{static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(gamma),
+              static_cast<__nv_bfloat16*>(y), rows, cols_local, cols_total, eps, sums_off};
+  int grid = rows < 148 ? rows : 148;
+  tp_rmsnorm_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ctx_of(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // extern "C"

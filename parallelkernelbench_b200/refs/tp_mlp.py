@@ -12,8 +12,8 @@ class TPMLPReference:
         self.world, self.rows, self.hidden, self.eps, self.group = world, rows_per_rank, hidden, eps, group
         self.w1, self.w2, self.gamma = w1, w2, gamma
         dev = w1.device
-        self.x_full = torch.empty((world * rows_per_rank, hidden), dtype=torch.bfloat16, device=dev)
-        self.y_local = torch.empty((rows_per_rank, hidden), dtype=torch.bfloat16, device=dev)
+        self.x_full = torch.empty((world * rows_per_rank, hidden), dtype=w1.dtype, device=dev)
+        self.y_local = torch.empty((rows_per_rank, hidden), dtype=w1.dtype, device=dev)
 
     def forward(self, x_local: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
@@ -29,6 +29,6 @@ class TPMLPReference:
         else:
             y = partial
         yf = y.float()
-        return (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + self.eps) * self.gamma.float()).to(torch.bfloat16)
+        return (yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + self.eps) * self.gamma.float()).to(x_local.dtype)
 
     __call__ = forward

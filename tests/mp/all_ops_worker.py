@@ -1,0 +1,77 @@
+"""Run every registered op (reference and ours) inside ONE process group and compare per rank.
+
+Used on CPU (gloo ranks, shared-memory transport) and on GPUs (NCCL + symmetric heap):
+    torchrun --nproc-per-node 2 tests/mp/all_ops_worker.py [--backend gloo] [--dtype float32] [--config small] [--ops a,b]
+Prints one PASS/FAIL line per op and ``TOTAL_FAILS n``; exits non-zero on any failure.
+"""
+import argparse
+import os
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from parallelkernelbench_b200.harness import compare  # noqa: E402
+from parallelkernelbench_b200.parallel import init_context  # noqa: E402
+from parallelkernelbench_b200.workloads import registry  # noqa: E402
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--backend", default=None)
+    ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--config", default="small", help="preferred config name; ops without it use 'default'")
+    ap.add_argument("--ops", default="all")
+    ap.add_argument("--skip", default="")
+    ap.add_argument("--trials", type=int, default=1)
+    args = ap.parse_args()
+    ctx = init_context(backend=args.backend)
+    names = [s.name for s in registry.all_ops()] if args.ops == "all" else args.ops.split(",")
+    skip = set(filter(None, args.skip.split(",")))
+    fails = 0
+    for name in names:
+        if name in skip:
+            continue
+        spec = registry.get(name)
+        if spec.ours is None or (spec.ours_needs_cuda and not ctx.is_cuda):
+            continue
+        cfg_name = args.config if args.config in spec.configs else "default"
+        for trial in range(args.trials):
+            ok, detail = False, ""
+            try:
+                cfg = spec.config(cfg_name)
+                rc_ref = registry.RunCtx(ctx, spec.name, trial=trial, dtype=registry.DTYPES[args.dtype])
+                rc_ours = registry.RunCtx(ctx, spec.name, trial=trial, dtype=registry.DTYPES[args.dtype])
+                with torch.no_grad():
+                    a = compare.normalize_output(spec.reference(rc_ref, *spec.make_inputs(rc_ref, cfg)))
+                    b = compare.normalize_output(spec.ours(rc_ours, *spec.make_inputs(rc_ours, cfg)))
+                if ctx.is_cuda:
+                    torch.cuda.synchronize()
+                    from parallelkernelbench_b200 import _native as nv
+
+                    st = nv.read_status()
+                    if st[0] != 0:
+                        nv.clear_status()
+                        raise RuntimeError(f"device status {st[:8]}")
+                res = compare.compare_objects(a, b, spec.atol, spec.rtol)
+                ok, detail = res["ok"], f"max_abs_diff={res.get('max_abs_diff')} " + "; ".join(res["errors"][:2])
+            except Exception as e:
+                detail = f"{type(e).__name__}: {e}\n{traceback.format_exc(limit=6)}"
+            flag = torch.tensor([0 if ok else 1], device=ctx.device)
+            if ctx.world > 1:
+                dist.all_reduce(flag)
+            if flag.item():
+                fails += 1
+            if ctx.rank == 0 or not ok:
+                print(f"{'PASS' if not flag.item() else 'FAIL'} rank{ctx.rank} {name} [{cfg_name}] trial={trial} {detail}", flush=True)
+    ctx.finalize()
+    if ctx.rank == 0:
+        print("TOTAL_FAILS", fails, flush=True)
+    return 1 if fails else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
