@@ -36,8 +36,8 @@ FFN = 28672
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ref", action="store_true", help="skip timing the in-repo PyTorch+NCCL implementation")
     ap.add_argument("--comm-ctas", type=int, default=0)
@@ -115,7 +115,7 @@ def main() -> int:
         return float(t.item()), nv.launches() - launches0
 
     # ---------------------------------------------------------------- device-timed headline
-    sampler = ClockSampler(gpu_index=ctx.local_rank).start() if rank == 0 else None
+    sampler = ClockSampler(gpu_index=ctx.local_rank, period_ms=50).start() if rank == 0 else None
     ms_ours, launches = timed(lambda i: block(xs[i % n_inputs]), args.steps, args.warmup)
     if sampler is not None:
         time.sleep(0.25)

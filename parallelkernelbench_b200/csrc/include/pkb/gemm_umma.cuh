@@ -22,7 +22,14 @@ constexpr int kGemmBlockK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
 constexpr int kGemmMaxWorld = 8;
 
-enum GemmEpilogue : int { kEpiNone = 0, kEpiSilu = 1, kEpiBias = 2, kEpiBiasSilu = 3 };
+enum GemmEpilogue : int {
+  kEpiNone = 0,
+  kEpiSilu = 1,
+  kEpiBias = 2,
+  kEpiBiasSilu = 3,
+  kEpiSwiGLU = 4,  // columns come in (gate, up) pairs: out[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]
+};
+constexpr int kGemmMaxGroups = 256;
 
 struct GemmParams {
   int M, N, K;
@@ -54,6 +61,12 @@ struct GemmParams {
   // ---- rank / schedule ----------------------------------------------------------------------
   int rank, world;
   int m_block_rotation;  // logical m-block i is physical (i + rotation) % num_m_blocks
+  // ---- grouped (ragged) form ------------------------------------------------------------------
+  // A holds the rows of `grp_count` groups back to back: group e owns rows
+  // [grp_offsets[e], grp_offsets[e+1]) (device memory, so the host never learns the counts) and
+  // multiplies them with its own weight block B[e*N .. e*N+N, :].
+  const int* grp_offsets;
+  int grp_count;
 };
 
 template <int BN>
@@ -68,7 +81,7 @@ struct GemmSmem {
 
 // Body of one GEMM CTA. `cta` / `num_ctas` are this CTA's index and the number of CTAs that share
 // the tile loop (a fused kernel may reserve some of its grid for communication roles).
-template <int BN, int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER>
+template <int BN, int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool GROUPED = false>
 __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                               const GemmParams& p, const int cta,
                                               const int num_ctas) {
@@ -94,22 +107,54 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
 
   const int num_m = (p.M + kGemmBlockM - 1) / kGemmBlockM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
   const int num_k = (p.K + kGemmBlockK - 1) / kGemmBlockK;
   const int group_m = p.group_m > 0 ? p.group_m : 16;
 
-  // tile -> (m block, n block): groups of `group_m` m-blocks, n outer / m inner inside a group, so
-  // one wave of CTAs touches a near-square set of A and B panels that stays in L2.
-  auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
-    const int tiles_per_group = group_m * num_n;
-    const int g = tile / tiles_per_group;
-    const int first_m = g * group_m;
-    const int gm = min(group_m, num_m - first_m);
-    const int local = tile - g * tiles_per_group;
-    n_blk = local / gm;
-    int m_logical = first_m + (local - n_blk * gm);
-    m_blk = m_logical + p.m_block_rotation;
-    if (m_blk >= num_m) m_blk -= num_m;
+  // grouped form: prefix sums of the groups' m-tile counts, built once per CTA from device counts
+  __shared__ int s_tile_prefix[GROUPED ? kGemmMaxGroups + 1 : 1];
+  if constexpr (GROUPED) {
+    for (int e = threadIdx.x; e < p.grp_count; e += blockDim.x) {
+      const int cnt = p.grp_offsets[e + 1] - p.grp_offsets[e];
+      s_tile_prefix[e + 1] = (cnt + kGemmBlockM - 1) / kGemmBlockM;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_tile_prefix[0] = 0;
+      for (int e = 0; e < p.grp_count; ++e) s_tile_prefix[e + 1] += s_tile_prefix[e];
+    }
+    __syncthreads();
+  }
+  const int num_tiles = GROUPED ? s_tile_prefix[p.grp_count] * num_n : num_m * num_n;
+
+  // tile -> first row of A / C, row limit, n block, first row of B.
+  // dense: groups of `group_m` m-blocks, n outer / m inner inside a group, so one wave of CTAs
+  // touches a near-square set of A and B panels that stays in L2.
+  // grouped: group-major, then m-tile, n fastest (the 128 x K row panel is shared by a wave).
+  auto tile_coords = [&](int tile, int& row0, int& row_end, int& n_blk, int& b_row0) {
+    if constexpr (GROUPED) {
+      const int mi = tile / num_n;
+      n_blk = tile - mi * num_n;
+      int lo = 0, hi = p.grp_count;  // find e with prefix[e] <= mi < prefix[e+1]
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (s_tile_prefix[mid] <= mi) lo = mid; else hi = mid;
+      }
+      row0 = p.grp_offsets[lo] + (mi - s_tile_prefix[lo]) * kGemmBlockM;
+      row_end = p.grp_offsets[lo + 1];
+      b_row0 = lo * p.N + n_blk * BN;
+    } else {
+      const int tiles_per_group = group_m * num_n;
+      const int g = tile / tiles_per_group;
+      const int first_m = g * group_m;
+      const int gm = min(group_m, num_m - first_m);
+      const int local = tile - g * tiles_per_group;
+      n_blk = local / gm;
+      int m_blk = first_m + (local - n_blk * gm) + p.m_block_rotation;
+      if (m_blk >= num_m) m_blk -= num_m;
+      row0 = m_blk * kGemmBlockM;
+      row_end = p.M;
+      b_row0 = n_blk * BN;
+    }
   };
 
   if (threadIdx.x == 0) {
@@ -142,10 +187,10 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
-        int m_blk, n_blk;
-        tile_coords(tile, m_blk, n_blk);
+        int row0, row_end, n_blk, b_row0;
+        tile_coords(tile, row0, row_end, n_blk, b_row0);
         if constexpr (A_READY) {
-          const int chunk = (m_blk * kGemmBlockM) / p.a_chunk_rows;
+          const int chunk = row0 / p.a_chunk_rows;
           if (!wait_flag_ge(p.a_ready + chunk, p.a_ready_epoch, p.wait_budget_ns)) {
             *abort_flag = 1;
             record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
@@ -164,8 +209,8 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
           }
           mbar_expect_tx(full_bar(stage), S::kStageBytes);
           const uint32_t sa = smem_base + stage * S::kStageBytes;
-          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, m_blk * kGemmBlockM);
-          tma_load_2d(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, n_blk * BN);
+          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+          tma_load_2d(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, b_row0);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -226,8 +271,8 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = cta; tile < num_tiles; tile += num_ctas) {
-      int m_blk, n_blk;
-      tile_coords(tile, m_blk, n_blk);
+      int tile_row0, row_end, n_blk, b_row0;
+      tile_coords(tile, tile_row0, row_end, n_blk, b_row0);
       bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_budget_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -236,7 +281,7 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
         break;
       }
       tc_fence_after_sync();
-      const int row = m_blk * kGemmBlockM + q * 32 + lane;
+      const int row = tile_row0 + q * 32 + lane;
       const int n0 = n_blk * BN;
 
       // destination row pointer (local, or the owner's buffer for the reduce-scatter form)
@@ -250,7 +295,7 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
       } else {
         out_row = static_cast<uint8_t*>(p.C) + static_cast<long long>(row) * p.ldc * kOutBytes;
       }
-      const bool row_ok = row < p.M;
+      const bool row_ok = row < row_end;
 
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -286,6 +331,23 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
               for (int j = 0; j < 32; ++j)
                 if (col0 + j < p.N) o[j] = v[j];
             }
+          } else if constexpr (EPI == kEpiSwiGLU) {
+            // 32 accumulator columns = 16 (gate, up) pairs -> 16 outputs at column col0 / 2
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + (col0 >> 1);
+            float g[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) g[j] = silu_f(v[2 * j]) * v[2 * j + 1];
+            if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                U4 u{pack_bf16x2(g[j], g[j + 1]), pack_bf16x2(g[j + 2], g[j + 3]),
+                     pack_bf16x2(g[j + 4], g[j + 5]), pack_bf16x2(g[j + 6], g[j + 7])};
+                st_global_v4(o + j, u);
+              }
+            } else {
+              for (int j = 0; j < 16; ++j)
+                if (col0 + 2 * j + 1 < p.N) o[j] = __float2bfloat16_rn(g[j]);
+            }
           } else {
             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + col0;
             if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
@@ -312,7 +374,7 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
         __threadfence_system();
         __syncwarp();
         if (lane == 0) {
-          const int row0 = m_blk * kGemmBlockM;
+          const int row0 = tile_row0;
           const int owner = row0 / p.rs_rows_per_rank;
           if (owner < p.world) {
             const int blk_in_rank = (row0 - owner * p.rs_rows_per_rank) / kGemmBlockM;
@@ -346,6 +408,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   gemm_umma_cta<BN, EPI, OUT_F32, A_READY, RS_SCATTER>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
+}
+
+// ragged groups (MoE experts): A rows grouped by expert, B = [groups * N, K]
+template <int BN, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_umma_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma_cta<BN, EPI, false, false, false, true>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
 }
 
 }  // namespace pkb

@@ -166,3 +166,57 @@ extern "C" int pkb_gemm_bf16(const void* a, long long lda, const void* b, long l
   return out_f32 ? dispatch_epi<128, true>(epilogue, ta, tb, p, ctas, s)
                  : dispatch_epi<128, false>(epilogue, ta, tb, p, ctas, s);
 }
+
+// Grouped (ragged) GEMM: rows of A are grouped back to back, group e = rows
+// [offsets[e], offsets[e+1]) (int32 device array of groups + 1 entries, read on the device only) and
+// uses the weight block b[e*N : (e+1)*N, :]. C[total_rows, N] (or N/2 columns for the SwiGLU
+// epilogue). max_rows bounds offsets[groups]; rows at or beyond it are never touched.
+// epilogue: 0 none, 1 SiLU, 4 SwiGLU over interleaved (gate, up) weight rows.
+extern "C" int pkb_gemm_bf16_grouped(const void* a, long long lda, const void* b, long long ldb,
+                                     void* c, long long ldc, const void* offsets, int groups,
+                                     int max_rows, int N, int K, int epilogue, int block_n,
+                                     void* stream) {
+  PKB_CHECK_ARG(groups >= 1 && groups <= kGemmMaxGroups, "1..256 groups");
+  PKB_CHECK_ARG(max_rows > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && K % 8 == 0, "lda, ldb, K must be multiples of 8");
+  PKB_CHECK_ARG(epilogue == kEpiNone || epilogue == kEpiSilu || epilogue == kEpiSwiGLU, "unsupported epilogue");
+  if (block_n == 0) block_n = N >= 256 ? 256 : 128;
+  PKB_CHECK_ARG(block_n == 128 || block_n == 256, "block_n must be 128 or 256");
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)K, (uint64_t)max_rows, (uint64_t)lda * 2,
+                          kGemmBlockK, kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)K, (uint64_t)groups * N, (uint64_t)ldb * 2,
+                      kGemmBlockK, (uint32_t)block_n, kSwizzle128);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = max_rows; p.N = N; p.K = K;
+  p.C = c; p.ldc = ldc; p.alpha = 1.0f;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.kernel_id = 102;
+  p.world = 1;
+  p.grp_offsets = static_cast<const int*>(offsets);
+  p.grp_count = groups;
+  const int ctas = sm_count();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PKB_GROUPED(BN, EPI)                                                                        \
+  {                                                                                                 \
+    auto kern = gemm_umma_grouped_kernel<BN, EPI>;                                                  \
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                                        GemmSmem<BN>::kTotal));                                     \
+    kern<<<ctas, kGemmThreads, GemmSmem<BN>::kTotal, s>>>(ta, tb, p);                               \
+  }
+  if (block_n == 256) {
+    if (epilogue == kEpiNone) PKB_GROUPED(256, kEpiNone)
+    else if (epilogue == kEpiSilu) PKB_GROUPED(256, kEpiSilu)
+    else PKB_GROUPED(256, kEpiSwiGLU)
+  } else {
+    if (epilogue == kEpiNone) PKB_GROUPED(128, kEpiNone)
+    else if (epilogue == kEpiSilu) PKB_GROUPED(128, kEpiSilu)
+    else PKB_GROUPED(128, kEpiSwiGLU)
+  }
+#undef PKB_GROUPED
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}

@@ -1,0 +1,127 @@
+"""Expert-parallel MoE primitives (kernels: csrc/kernels/moe.cu, grouped GEMM in csrc/kernels/gemm.cu).
+
+Everything stays on the device: the per-expert counts are all-gathered as a tiny tensor, the plan
+kernel turns them into slot bases and grouped-GEMM offsets, the dispatch kernel writes rows straight
+into the destination ranks' receive buffers, and the combine kernel pulls expert outputs back over
+NVLink. The reference synchronises with the host three times per layer call
+(reference: reference/31_fused_moe_fwd.py:60-101).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as nv
+from ..parallel.symm_heap import SymmGroup
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, epilogue: str = "none",
+                 out: torch.Tensor | None = None, block_n: int = 0) -> torch.Tensor:
+    """Ragged GEMM: rows ``[offsets[e], offsets[e+1])`` of ``a[rows, K]`` times ``w[e]`` (``w`` is
+    ``[G, N, K]``). ``offsets`` is an int32 device tensor ``[G+1]`` that the host never reads.
+    ``epilogue="swiglu"`` expects interleaved (gate, up) rows in ``w`` and returns ``N/2`` columns."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 3:
+        raise TypeError("grouped_gemm expects bf16 a[rows, K] and w[G, N, K]")
+    G, N, K = w.shape
+    if a.shape[1] != K or a.stride(1) != 1 or not w.is_contiguous():
+        raise ValueError("shape mismatch or non-contiguous operand")
+    if offsets.dtype != torch.int32 or offsets.numel() != G + 1:
+        raise ValueError("offsets must be int32 [G + 1]")
+    n_out = N // 2 if epilogue == "swiglu" else N
+    if out is None:
+        out = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
+    epi = {"none": 0, "silu": 1, "swiglu": 4}[epilogue]
+    nv.check(nv.cuda_lib().pkb_gemm_bf16_grouped(nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(K), nv.ptr(out),
+                                                 nv.c_ll(out.stride(0)), nv.ptr(offsets), G, a.shape[0], N, K, epi, block_n,
+                                                 nv.current_stream()), "pkb_gemm_bf16_grouped")
+    nv.count_launch()
+    return out
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """``[..., I, H]`` gate and up weights -> ``[..., 2I, H]`` with rows (g0, u0, g1, u1, ...)."""
+    return torch.stack([w_gate, w_up], dim=-2).reshape(*w_gate.shape[:-2], 2 * w_gate.shape[-2], w_gate.shape[-1]).contiguous()
+
+
+class MoEExchange:
+    """Dispatch / combine state of one expert-parallel group (buffers live in the symmetric heap)."""
+
+    def __init__(self, group: SymmGroup, num_experts: int, hidden: int, max_tokens: int, top_k: int,
+                 capacity_factor: float = 2.0, fp8: bool = True):
+        W = group.size
+        if num_experts % W != 0:
+            raise ValueError("experts must divide evenly over the expert-parallel group")
+        if fp8 and hidden % 128 != 0:
+            raise ValueError("fp8 dispatch needs hidden % 128 == 0")
+        self.group, self.E, self.El, self.hidden, self.top_k, self.fp8 = group, num_experts, num_experts // W, hidden, top_k, fp8
+        self.capacity = int(max_tokens * top_k * capacity_factor + 127) // 128 * 128
+        heap = group.heap
+        self.payload_bytes = hidden if fp8 else hidden * 2
+        self.scale_bytes = ((hidden // 128) * 4 + 15) // 16 * 16 if fp8 else 0
+        self.recv_payload = heap.empty((self.capacity, self.payload_bytes), torch.uint8)
+        self.recv_scales = heap.empty((self.capacity, max(self.scale_bytes, 16)), torch.uint8)
+        self.y = heap.empty((self.capacity, hidden), torch.bfloat16)
+        dev = self.y.local.device
+        self.counts = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.seg_base = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.cursor = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.offsets = torch.zeros(self.El + 1, dtype=torch.int32, device=dev)
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.slots = None
+
+    # -- planning ------------------------------------------------------------------------------
+    def plan(self, expert_idx: torch.Tensor, comm) -> torch.Tensor:
+        """``expert_idx`` int32 ``[T * k]``. Returns the all-gathered count matrix ``[W, E]`` (device)."""
+        lib = nv.cuda_lib()
+        nv.check(lib.pkb_moe_histogram(nv.ptr(expert_idx), nv.c_ll(expert_idx.numel()), self.E, nv.ptr(self.counts),
+                                       nv.current_stream()), "pkb_moe_histogram")
+        nv.count_launch()
+        all_counts = comm.all_gather(self.counts, self.group) if self.group.size > 1 else self.counts.unsqueeze(0)
+        nv.check(lib.pkb_moe_plan(nv.ptr(all_counts), self.group.size, self.E, self.El, self.group.rank_in_group,
+                                  nv.ptr(self.seg_base), nv.ptr(self.offsets), nv.ptr(self.cursor), nv.current_stream()),
+                 "pkb_moe_plan")
+        nv.count_launch()
+        return all_counts
+
+    # -- dispatch ------------------------------------------------------------------------------
+    def dispatch(self, x: torch.Tensor, expert_idx: torch.Tensor) -> torch.Tensor:
+        """Send every (token, k) row to its expert's rank. Returns the received rows as bf16
+        ``[capacity, hidden]`` (rows ``[0, offsets[-1])`` are valid, expert-major)."""
+        from .elementwise import fp8_dequantize_1x128, fp8_quantize_1x128
+
+        T = x.shape[0]
+        self.slots = torch.empty(T * self.top_k, dtype=torch.int32, device=x.device)
+        if self.fp8:
+            payload, scales = fp8_quantize_1x128(x)
+            if self.scale_bytes != scales.shape[1] * 4:
+                pad = torch.zeros((T, self.scale_bytes // 4), dtype=torch.float32, device=x.device)
+                pad[:, :scales.shape[1]] = scales
+                scales = pad
+        else:
+            payload, scales = x.contiguous(), None
+        nv.check(nv.cuda_lib().pkb_moe_dispatch(
+            self.group.ref, nv.ptr(payload), nv.ptr(scales), self.payload_bytes, self.scale_bytes, nv.ptr(expert_idx),
+            nv.c_ll(T * self.top_k), self.top_k, self.El, nv.ptr(self.seg_base), nv.ptr(self.cursor), nv.ptr(self.slots),
+            ctypes.c_ulonglong(self.recv_payload.offset), ctypes.c_ulonglong(self.recv_scales.offset), self.capacity,
+            nv.ptr(self.overflow), nv.current_stream()), "pkb_moe_dispatch")
+        nv.count_launch()
+        if self.fp8:
+            nblk = self.hidden // 128
+            s = self.recv_scales.local.view(torch.float32)[:, :nblk]
+            if s.shape[1] * 4 != self.scale_bytes:
+                s = s.contiguous()
+            return fp8_dequantize_1x128(self.recv_payload.local, s, torch.bfloat16)
+        return self.recv_payload.local.view(torch.bfloat16)
+
+    # -- combine -------------------------------------------------------------------------------
+    def combine(self, expert_idx: torch.Tensor, gates: torch.Tensor, num_tokens: int) -> torch.Tensor:
+        """``out[t] = sum_j gates[t, j] * y_owner[slot[t, j]]`` pulled over NVLink; ``self.y`` holds
+        this rank's expert outputs."""
+        out = torch.empty((num_tokens, self.hidden), dtype=torch.bfloat16, device=gates.device)
+        nv.check(nv.cuda_lib().pkb_moe_combine(self.group.ref, ctypes.c_ulonglong(self.y.offset), nv.ptr(expert_idx),
+                                               nv.ptr(self.slots), nv.ptr(gates.contiguous().float()), nv.ptr(out),
+                                               nv.c_ll(num_tokens), self.top_k, self.hidden, self.El, nv.current_stream()),
+                 "pkb_moe_combine")
+        nv.count_launch()
+        return out

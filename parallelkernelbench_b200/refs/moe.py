@@ -1,0 +1,68 @@
+"""PyTorch + NCCL reference of the expert-parallel MoE layer (oracle and timed baseline).
+
+Classic formulation: sort assignments by expert, exchange per-rank counts, ``all_to_all_single`` with
+host-side split sizes, loop over local experts with ``F.linear``, send results back, weighted
+``index_add_``. The fp8 dispatch is modelled by applying the same 1x128 quantise/dequantise to the
+tokens before they are sent, so that only the accumulation order differs from the kernels.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+import torch.nn.functional as F
+
+
+def fp8_round_trip_1x128(x: torch.Tensor) -> torch.Tensor:
+    xb = x.float().reshape(-1, 128)
+    s = xb.abs().amax(-1, keepdim=True) / 448.0
+    s = torch.where(s == 0, torch.ones_like(s), s)
+    return ((xb / s).to(torch.float8_e4m3fn).float() * s).reshape(x.shape).to(x.dtype)
+
+
+def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: int, top_k: int, group=None,
+                  fp8_dispatch: bool = False, gates_idx=None):
+    """``w_gate``/``w_up``: [E_local, I, H], ``w_down``: [E_local, H, I]. Returns [T, H]."""
+    W = dist.get_world_size(group) if dist.is_initialized() else 1
+    r = dist.get_rank(group) if dist.is_initialized() else 0
+    el = num_experts // W
+    T, H = x.shape
+    if gates_idx is None:
+        logits = F.linear(x, w_router, router_bias).float()
+        gates, idx = torch.topk(torch.softmax(logits, dim=-1), top_k, dim=-1)
+    else:
+        gates, idx = gates_idx
+    flat_e = idx.reshape(-1).long()
+    order = torch.argsort(flat_e, stable=True)
+    tok = (order // top_k)
+    xs = fp8_round_trip_1x128(x) if fp8_dispatch else x
+    send = xs[tok]
+    counts = torch.bincount(flat_e, minlength=num_experts)
+    if W > 1:
+        all_counts = torch.empty(W, num_experts, dtype=counts.dtype, device=x.device)
+        dist.all_gather_into_tensor(all_counts.view(-1), counts, group=group)
+        in_splits = counts.view(W, el).sum(1).tolist()
+        out_splits = all_counts[:, r * el:(r + 1) * el].sum(1).tolist()
+        recv = x.new_empty((sum(out_splits), H))
+        dist.all_to_all_single(recv, send.contiguous(), output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+        per_src = all_counts[:, r * el:(r + 1) * el]                      # [W, el] rows from source s for local expert e
+    else:
+        recv, per_src = send, counts.view(1, el)
+    # received rows are source-major, expert-minor: process each (source, expert) chunk with its expert
+    out_rows = torch.empty_like(recv)
+    pos = 0
+    for s in range(per_src.shape[0]):
+        for e in range(el):
+            n = int(per_src[s, e])
+            if n:
+                seg = recv[pos:pos + n]
+                h = F.silu(F.linear(seg, w_gate[e])) * F.linear(seg, w_up[e])
+                out_rows[pos:pos + n] = F.linear(h, w_down[e])
+                pos += n
+    if W > 1:
+        back = x.new_empty((send.shape[0], H))
+        dist.all_to_all_single(back, out_rows, output_split_sizes=in_splits, input_split_sizes=out_splits, group=group)
+    else:
+        back = out_rows
+    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    out.index_add_(0, tok, back.float() * gates.reshape(-1)[order].unsqueeze(1).float())
+    return out.to(x.dtype)

@@ -33,7 +33,7 @@ def test_fp8_quant_dequant_round_trip(dtype):
     assert (y.view(torch.float8_e4m3fn).float() - y_ref.float()).abs().max() <= 32.0   # at most one fp8 ulp at the top
     assert (y.view(torch.float8_e4m3fn).float() != y_ref.float()).float().mean() < 0.01
     back = fp8_dequantize_1x128(y, s, torch.float32)
-    torch.testing.assert_close(back, x.float(), atol=0.0, rtol=0.07)
+    torch.testing.assert_close(back, x.float(), atol=2e-3, rtol=0.07)   # e4m3: 3 mantissa bits, subnormals near zero
     y2, s2 = fp8_quantize_1x128(x, pow2_scales=True)
     assert torch.all(torch.log2(s2) == torch.log2(s2).round())
 
