@@ -292,15 +292,32 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_kmajor(uint32_t smem_ad
   return d;
 }
 
+// Shared-memory descriptor of an MN-major tile (the MN index is contiguous in memory, e.g. a weight
+// stored [K, N] row-major or V stored [kv, d]): the tile is a sequence of "atoms" of 64 bf16 along
+// MN (one 128-byte swizzled row per K index). Inside an atom, groups of eight K rows are 1024 bytes
+// apart (stride byte offset); consecutive atoms along MN are `atom_stride_bytes` apart (leading
+// byte offset). Stepping 16 along K moves the start address by 16 rows = 2048 bytes.
+__device__ __forceinline__ uint64_t make_smem_desc_sw128_mnmajor(uint32_t smem_addr,
+                                                                 uint32_t atom_stride_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((atom_stride_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;                            // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4, fp32 accumulate, both operands K-major.
 // a_fmt/b_fmt: f16 kinds 0 = fp16, 1 = bf16; f8f6f4 kinds 0 = e4m3, 1 = e5m2.
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n, uint32_t a_fmt,
-                                                  uint32_t b_fmt) {
+                                                  uint32_t b_fmt, uint32_t a_mn_major = 0,
+                                                  uint32_t b_mn_major = 0) {
   return (1u << 4)               // accumulator format: fp32
          | (a_fmt << 7)          // A format
          | (b_fmt << 10)         // B format
-         | (0u << 15)            // A K-major
-         | (0u << 16)            // B K-major
+         | (a_mn_major << 15)    // A: 0 K-major, 1 MN-major
+         | (b_mn_major << 16)    // B: 0 K-major, 1 MN-major
          | ((n >> 3) << 17)      // N / 8
          | ((m >> 4) << 24);     // M / 16
 }

@@ -220,3 +220,41 @@ extern "C" int pkb_gemm_bf16_grouped(const void* a, long long lda, const void* b
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
+
+// C[M,N] = epi(A[M,K] @ B[K,N]) with B row-major [K, N] (ldb elements between K rows, N % 8 == 0).
+// epilogue: 0 none, 1 SiLU. out_f32 selects fp32 output.
+extern "C" int pkb_gemm_bf16_bkn(const void* a, long long lda, const void* b, long long ldb, void* c,
+                                 long long ldc, int M, int N, int K, float alpha, int epilogue,
+                                 int out_f32, void* stream) {
+  PKB_CHECK_ARG(M > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && K % 8 == 0 && N % 8 == 0, "lda, ldb, K, N must be multiples of 8");
+  PKB_CHECK_ARG(epilogue == kEpiNone || epilogue == kEpiSilu, "epilogue must be none or silu");
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, kGemmBlockK,
+                          kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kGemmBlockK,
+                      kSwizzle128);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.C = c; p.ldc = ldc; p.alpha = alpha;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.group_m = 16; p.kernel_id = 103; p.world = 1;
+  const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
+  int ctas = sm_count();
+  if (ctas > tiles) ctas = tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr int smem = GemmSmem<128>::kTotal;
+#define PKB_BKN(EPI, F32)                                                                          \
+  {                                                                                                \
+    auto kern = gemm_umma_bkn_kernel<128, EPI, F32>;                                               \
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    kern<<<ctas, kGemmThreads, smem, s>>>(ta, tb, p);                                              \
+  }
+  if (epilogue == kEpiSilu) { if (out_f32) PKB_BKN(kEpiSilu, true) else PKB_BKN(kEpiSilu, false) }
+  else { if (out_f32) PKB_BKN(kEpiNone, true) else PKB_BKN(kEpiNone, false) }
+#undef PKB_BKN
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}

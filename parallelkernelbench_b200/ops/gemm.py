@@ -63,3 +63,23 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     lead = x.shape[:-1]
     y = gemm_bf16(x.reshape(-1, x.shape[-1]), weight, bias=bias, epilogue=activation)
     return y.reshape(*lead, weight.shape[0])
+
+
+def gemm_bf16_kn(a: torch.Tensor, b: torch.Tensor, *, out: torch.Tensor | None = None, epilogue: str = "none",
+                 alpha: float = 1.0, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``a[M, K] @ b[K, N]`` with ``b`` row-major (N contiguous): the tensor core reads B as an
+    MN-major operand, so a ``[K, N]`` weight needs no transposed copy."""
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or a.shape[1] != b.shape[0]:
+        raise ValueError("gemm_bf16_kn expects bf16 a[M, K] and b[K, N]")
+    if a.stride(1) != 1 or b.stride(1) != 1:
+        raise ValueError("operands must be contiguous along their last dimension")
+    M, K = a.shape
+    N = b.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    nv.check(nv.cuda_lib().pkb_gemm_bf16_bkn(nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(b), nv.c_ll(b.stride(0)), nv.ptr(out),
+                                             nv.c_ll(out.stride(0)), M, N, K, nv.c_float(alpha), EPILOGUES[epilogue],
+                                             1 if out.dtype == torch.float32 else 0, nv.current_stream()),
+             "pkb_gemm_bf16_bkn")
+    nv.count_launch()
+    return out

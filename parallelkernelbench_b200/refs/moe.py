@@ -27,7 +27,8 @@ def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: i
     el = num_experts // W
     T, H = x.shape
     if gates_idx is None:
-        logits = F.linear(x, w_router, router_bias).float()
+        # the router runs in fp32 (near-ties between experts must not flip with the rounding of bf16 logits)
+        logits = F.linear(x.float(), w_router.float(), None if router_bias is None else router_bias.float())
         gates, idx = torch.topk(torch.softmax(logits, dim=-1), top_k, dim=-1)
     else:
         gates, idx = gates_idx

@@ -86,3 +86,13 @@ def test_large_k_accumulation():
     w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02
     out = gemm_bf16(a, w)
     torch.testing.assert_close(out.float(), _ref(a, w), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (300, 200, 136)])
+def test_gemm_with_row_major_kn_weight(M, N, K):
+    from parallelkernelbench_b200.ops.gemm import gemm_bf16_kn
+
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.05
+    out = gemm_bf16_kn(a, b)
+    torch.testing.assert_close(out.float(), a.float() @ b.float(), atol=2e-2, rtol=2e-2)

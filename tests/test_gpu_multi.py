@@ -51,6 +51,23 @@ def test_tp_mlp_multi_rank(nproc):
     _assert_ok(_torchrun("tests/mp/tp_mlp_worker.py", nproc, port=29620 + nproc))
 
 
+def test_moe_single_rank():
+    _assert_ok(_torchrun("tests/mp/moe_worker.py", 1, port=29603))
+
+
+def test_all_ops_single_rank():
+    _assert_ok(_torchrun("tests/mp/all_ops_worker.py", 1, port=29604))
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_moe_and_all_ops_multi_rank(nproc):
+    if _ngpus() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _assert_ok(_torchrun("tests/mp/moe_worker.py", nproc, port=29630 + nproc))
+    _assert_ok(_torchrun("tests/mp/all_ops_worker.py", nproc, port=29640 + nproc))
+
+
 def test_harness_eval_on_gpu_single_rank():
     env = dict(os.environ, PKB_LOGS_DIR=os.path.join(ROOT, "logs", "pytest_gpu"), PKB_COOLDOWN_SEC="0")
     r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "eval", "--op", "allreduce",
