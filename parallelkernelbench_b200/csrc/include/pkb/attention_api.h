@@ -1,0 +1,37 @@
+// C view of the attention problem description (attention.cu).
+#pragma once
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct pkb_attn_desc {
+  int32_t batch, sq, skv;       // sequences, Q rows per sequence, rows of the KV buffer per sequence
+  int32_t hq, hkv, head_dim;    // query heads, KV heads (hq % hkv == 0), 64 or 128
+  int32_t causal;
+  float scale;                  // softmax scale (1/sqrt(d) usually)
+  // Q rows come in runs of q_seg_rows rows; run i starts at global position q_seg_pos[i]
+  int32_t q_seg_rows, num_q_segs;
+  int32_t q_seg_pos[16];
+  // KV buffer segments: rows [row0, row0 + len) hold global positions [pos0, pos0 + len)
+  int32_t num_kv_segs;
+  int32_t kv_seg_row0[16], kv_seg_pos0[16], kv_seg_len[16];
+  // optional: segment s may be read once kv_seg_ready[s] >= ready_epoch (device memory)
+  const uint32_t* kv_seg_ready;
+  uint32_t ready_epoch;
+  uint32_t _pad;
+  uint64_t budget_ns;           // bound of device-side waits, 0 = default
+  // optional trace buffer (int64): word 0 = record count, records of 4 words start at word 4
+  void* trace;
+  int32_t trace_capacity;
+  int32_t _pad2;
+} pkb_attn_desc;
+
+// q: [batch*sq, hq, d], k/v: [batch*skv, hkv, d] bf16; out like q; lse: [batch, hq, sq] fp32 or NULL
+int pkb_flash_attn_fwd(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, void* out,
+                       void* lse, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

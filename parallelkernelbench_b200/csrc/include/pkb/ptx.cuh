@@ -105,17 +105,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // microseconds); tests that exercise the time-out path pass a few milliseconds instead.
 constexpr uint64_t kDefaultWaitBudgetNs = 4000000000ull;
 
+// Budgets are given in nanoseconds but measured with the SM-local cycle counter (reading the
+// global timer costs on the order of a microsecond, far too much for a wait that normally succeeds
+// within a few polls). 2 cycles per nanosecond over-estimates the clock a little, so a wait gives
+// up slightly late rather than early.
+__device__ __forceinline__ long long budget_cycles(uint64_t budget_ns) {
+  return static_cast<long long>(budget_ns) * 2;
+}
+
 // Bounded mbarrier wait. `abort_flag` lives in shared memory and is shared by all roles of the
 // CTA: the first role whose budget expires raises it, every other wait sees it within ~1k polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t budget_ns = kDefaultWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xffu) == 0u) {
+    if ((++spins & 0x3ffu) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > budget_ns) {
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > budget_cycles(budget_ns)) {
         *abort_flag = 1;
         return false;
       }
@@ -355,12 +366,14 @@ __device__ __forceinline__ void fence_acq_rel_sys() {
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target,
                                              uint64_t budget_ns = kDefaultWaitBudgetNs) {
   if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
     if ((++spins & 0x3fu) == 0u) {
-      if (globaltimer_ns() - t0 > budget_ns) return false;
-      __nanosleep(64);
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_cycles(budget_ns)) return false;
+      __nanosleep(32);
     }
   }
   return true;
@@ -452,6 +465,12 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+// 2^x on the special-function unit (one MUFU instruction; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 }  // namespace pkb
 

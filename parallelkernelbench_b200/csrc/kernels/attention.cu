@@ -1,0 +1,487 @@
+// Flash-attention forward on tcgen05 / TMEM (never materialises the score matrix).
+//
+// One CTA owns one 128-row Q tile of one head and walks the KV tiles it is allowed to see:
+//   warp 0      TMA producer: Q once, then K and V tiles through two-stage rings
+//   warp 1      MMA issuer:   S = Q K^T (128 x 128 x D) into a TMEM S buffer, and O_j = P V
+//                             (128 x D x 128) into a TMEM O buffer; S of tile j+1 is issued before
+//                             P V of tile j so the tensor core works while the softmax runs
+//   warps 4-7   softmax:      thread = row. Two passes over the S row in TMEM (maximum, then
+//                             base-2 exponentials and row sum), mask, write P as bf16 into
+//                             128-byte-swizzled shared memory (the A operand of the P V MMA),
+//                             publish the rescale factor alpha
+//   warps 8-15  accumulate:   thread = row, two warpgroups take half of the D columns each.
+//                             o = o * alpha + O_j read back from TMEM; at the end divide by the row
+//                             sum and store bf16
+// K is the K-major B operand of the first MMA; V, stored [kv, d], is the MN-major B operand of the
+// second one - both arrive through the same TMA tile shape.
+//
+// Sequence layout is described by segments, so the same kernel serves plain attention, GQA, causal
+// masks and context-parallel layouts: Q rows come in `num_q_segs` runs of `q_seg_rows` rows whose
+// global positions start at q_seg_pos[i] (a zigzag rank owns two runs); the KV buffer is a list of
+// segments (buffer row, global position, length), and a segment may carry a readiness flag that the
+// producer waits for (bounded) - that is how the ring / all-gather of KV blocks from other ranks
+// overlaps with the math. The mask compares GLOBAL positions, and tiles that lie entirely in the
+// masked future are skipped.
+//
+// Reference behaviour replaced: materialised fp32 scores + logsumexp merge per ring step
+// (reference: reference/54_ring_attention.py:61-100) and SDPA calls (reference/77_magi1_cso_async_attention.py:108).
+#include "pkb/api.h"
+#include "pkb/attention_api.h"
+#include "pkb/host.h"
+#include "pkb/ptx.cuh"
+
+namespace pkb {
+
+constexpr int kFaThreads = 512;  // four warpgroups: {producer, MMA, 2 idle}, softmax, accumulate x 2
+constexpr int kFaTile = 128;  // q rows per CTA and kv rows per step
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct FaParams {
+  pkb_attn_desc d;
+  __nv_bfloat16* out;  // [batch * sq, hq, D]
+  float* lse;          // [batch, hq, sq] natural-log LSE (may be null)
+  uint32_t* status;
+  uint64_t budget_ns;
+  // optional device-side trace: CTA (0,0,0) records (role, event, tile, clock64) as four int64 per
+  // record, so the overlap of the roles can be plotted without a profiler
+  long long* trace;
+  int trace_capacity;  // records
+};
+
+__device__ __forceinline__ void fa_trace(const FaParams& p, int role, int event, int tile) {
+  if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0) return;
+  const unsigned long long slot = atomicAdd(reinterpret_cast<unsigned long long*>(p.trace), 1ull);
+  if (slot < (unsigned long long)p.trace_capacity) {
+    long long* r = p.trace + 4 + slot * 4;
+    r[0] = role; r[1] = event; r[2] = tile; r[3] = clock64();
+  }
+}
+
+template <int D>
+struct FaSmem {
+  static constexpr int kTileBytes = kFaTile * D * 2;       // Q, K, V tile
+  static constexpr int kPBytes = kFaTile * kFaTile * 2;    // P tile
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;               // 2 stages
+  static constexpr int kV = kK + 2 * kTileBytes;           // 2 stages
+  static constexpr int kP = kV + 2 * kTileBytes;           // 2 buffers
+  static constexpr int kAlpha = kP + 2 * kPBytes;          // [2][128] fp32
+  static constexpr int kStats = kAlpha + 2 * kFaTile * 4;  // l[128], m[128] fp32
+  static constexpr int kBars = kStats + 2 * kFaTile * 4;
+  static constexpr int kTotal = kBars + 256;
+};
+
+// Calls body(j, buffer_row, global_pos, valid_rows, segment) for every KV tile this Q tile touches.
+template <typename F>
+__device__ __forceinline__ int for_each_kv_tile(const pkb_attn_desc& d, int q_pos_last, F&& body) {
+  int j = 0;
+  for (int seg = 0; seg < d.num_kv_segs; ++seg) {
+    const int len = d.kv_seg_len[seg];
+    for (int t0 = 0; t0 < len; t0 += kFaTile) {
+      const int kp = d.kv_seg_pos0[seg] + t0;
+      if (d.causal && kp > q_pos_last) break;  // positions only grow inside a segment
+      body(j, d.kv_seg_row0[seg] + t0, kp, min(kFaTile, len - t0), seg);
+      ++j;
+    }
+  }
+  return j;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+              const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  using S = FaSmem<D>;
+  constexpr int kAtoms = D / 64;          // 64-column (128-byte) swizzle atoms per tile row
+  constexpr int kAtomBytes = kFaTile * 128;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = smem_u32(smem);
+  const pkb_attn_desc& d = p.d;
+
+  const uint32_t bar0 = sb + S::kBars;
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int b) { return bar0 + 8u * (9 + b); };
+  auto s_empty = [&](int b) { return bar0 + 8u * (11 + b); };
+  auto p_full = [&](int b) { return bar0 + 8u * (13 + b); };
+  auto p_empty = [&](int b) { return bar0 + 8u * (15 + b); };
+  auto o_full = [&](int b) { return bar0 + 8u * (17 + b); };
+  auto o_empty = [&](int b) { return bar0 + 8u * (19 + b); };
+  auto a_empty = [&](int b) { return bar0 + 8u * (21 + b); };
+  const uint32_t stats_full = bar0 + 8u * 23;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 24);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* alpha_s = reinterpret_cast<float*>(smem + S::kAlpha);
+  float* stats_s = reinterpret_cast<float*>(smem + S::kStats);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late, causal) tiles first
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (d.hq / d.hkv);
+  const int q_row0 = q_tile * kFaTile;  // row inside this batch's sequence
+  const int q_seg = q_row0 / d.q_seg_rows;
+  const int q_pos0 = d.q_seg_pos[q_seg] + (q_row0 - q_seg * d.q_seg_rows);
+  const int q_pos_last = q_pos0 + kFaTile - 1;
+  const int q_tok0 = batch * d.sq + q_row0;       // token coordinate in the Q / O tensors
+  const int kv_tok_base = batch * d.skv;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if ((sb & 1023u) != 0) {
+      *abort_flag = 1;
+      record_status(p.status, kStatusBadArgument, 600, 0, 0, 1, 0);
+    }
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1);
+      mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
+      mbar_init(s_full(s), 1); mbar_init(s_empty(s), 4);
+      mbar_init(p_full(s), 4); mbar_init(p_empty(s), 1);
+      mbar_init(o_full(s), 1); mbar_init(o_empty(s), 8);
+      mbar_init(a_empty(s), 8);
+    }
+    mbar_init(stats_full, 4);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;        // two S buffers of 128 columns
+  const uint32_t tmem_o = tmem_base + 256;  // two O buffers of D columns
+  const bool bad = *abort_flag != 0;
+
+  if (bad) {
+    // fall through to the common exit
+  } else if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, S::kTileBytes);
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a)
+        tma_load_3d(sb + S::kQ + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0);
+      bool ok = true;
+      int last_seg = -1;
+      for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
+        if (!ok) return;
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (seg != last_seg) {
+          last_seg = seg;
+          if (d.kv_seg_ready != nullptr) {
+            if (!wait_flag_ge(d.kv_seg_ready + seg, d.ready_epoch, p.budget_ns)) {
+              *abort_flag = 1;
+              record_status(p.status, kStatusPeerTimeout, 600, 0, seg, 10, j);
+              ok = false;
+              return;
+            }
+            fence_proxy_async_all();
+          }
+        }
+        if (!mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+        fa_trace(p, 0, 0, j);  // K(j) load issue
+        mbar_expect_tx(k_full(st), S::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+          tma_load_3d(sb + S::kK + st * S::kTileBytes + a * kAtomBytes, &tmap_k, k_full(st), a * 64, kv_head,
+                      kv_tok_base + row);
+        if (!mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+        mbar_expect_tx(v_full(st), S::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+          tma_load_3d(sb + S::kV + st * S::kTileBytes + a * kAtomBytes, &tmap_v, v_full(st), a * 64, kv_head,
+                      kv_tok_base + row);
+      });
+      if (!ok) record_status(p.status, kStatusMbarTimeout, 600, 0, 0, 11, 0);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const int n = for_each_kv_tile(d, q_pos_last, [](int, int, int, int, int) {});
+      constexpr uint32_t idesc_s = make_idesc(kFaTile, kFaTile, 1, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(kFaTile, D, 1, 1, 0, 1);  // V is MN-major
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.budget_ns);
+      auto issue_s = [&](int j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(k_full(st), ph, abort_flag, p.budget_ns)) return false;
+        if (!mbar_wait(s_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) return false;
+        tc_fence_after_sync();
+        fa_trace(p, 1, 0, j);  // S(j) issue
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          umma_f16_ss(tmem_s + st * 128, make_smem_desc_sw128_kmajor(sb + S::kQ + off),
+                      make_smem_desc_sw128_kmajor(sb + S::kK + st * S::kTileBytes + off), idesc_s, k != 0);
+        }
+        umma_commit(k_empty(st));
+        umma_commit(s_full(st));
+        return true;
+      };
+      if (ok && n > 0) ok = issue_s(0);
+      for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) ok = issue_s(j + 1);
+        if (!ok) break;
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(p_full(st), ph, abort_flag, p.budget_ns) || !mbar_wait(v_full(st), ph, abort_flag, p.budget_ns) ||
+            !mbar_wait(o_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        fa_trace(p, 1, 1, j);  // PV(j) issue
+#pragma unroll
+        for (int k = 0; k < kFaTile / 16; ++k) {
+          const uint32_t poff = (k >> 2) * kAtomBytes + (k & 3) * 32;  // P: K-major, two 64-kv atoms
+          const uint64_t dv = make_smem_desc_sw128_mnmajor(sb + S::kV + st * S::kTileBytes + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_o + st * D, make_smem_desc_sw128_kmajor(sb + S::kP + st * S::kPBytes + poff), dv, idesc_o,
+                      k != 0);
+        }
+        umma_commit(v_empty(st));
+        umma_commit(p_empty(st));
+        umma_commit(o_full(st));
+      }
+      if (!ok) record_status(p.status, kStatusMbarTimeout, 600, 0, 0, 20, 0);
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // idle warps of the first warpgroup
+  } else if (warp < 8) {
+    // ------------------------------ softmax (thread = row) ------------------------------
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const int my_pos = q_pos0 + row;
+    const float scale2 = d.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for_each_kv_tile(d, q_pos_last, [&](int j, int /*rowbuf*/, int kp, int valid, int /*seg*/) {
+      if (!ok) return;
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(s_full(b), ph, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      tc_fence_after_sync();
+      if (row == 0) fa_trace(p, 2, 0, j);  // S(j) visible to the softmax
+      // pass 1: row maximum (32 columns at a time; the row stays in TMEM, not in registers)
+      const uint32_t s_row = tmem_s + (static_cast<uint32_t>(q4 * 32) << 16) + b * 128;
+      const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_row + c * 32, r);
+        tmem_ld_wait();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            if (!(col >= valid || (d.causal && kp + col > my_pos))) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        }
+      }
+      mx *= scale2;  // scale2 > 0, so the maximum commutes with the scaling
+      const float m_new = fmaxf(m_run, mx);
+      const bool dead = m_new == -INFINITY;  // nothing visible yet for this row
+      const float alpha = dead ? 1.f : fast_exp2(m_run - m_new);
+      const float m_use = dead ? 0.f : m_new;
+      // P[b] and alpha[b] are free once P V of tile j-2 has read P and the accumulators read alpha
+      ok = mbar_wait(p_empty(b), ph ^ 1u, abort_flag, p.budget_ns) && mbar_wait(a_empty(b), ph ^ 1u, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) return;
+      if (row == 0) fa_trace(p, 2, 1, j);  // pass 1 done, P buffer free
+      // pass 2: exponentials, row sum, P as bf16 into the swizzled A-operand tile
+      const uint32_t prow = sb + S::kP + b * S::kPBytes + static_cast<uint32_t>(row) * 128u;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_row + c * 32, r);
+        tmem_ld_wait();
+        float pv[32];
+        if (need_mask || dead) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            const bool masked = dead || col >= valid || (d.causal && kp + col > my_pos);
+            pv[i] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(r[i]), scale2, -m_use));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, -m_use));
+        }
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[i & 3] += pv[i];
+        sum += (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // 16-byte chunk = kv columns 32c + 8g .. + 7
+          const int chunk = c * 4 + g;
+          const uint32_t atom = (chunk >> 3) * kAtomBytes;
+          const uint32_t dst = prow + atom + (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16x2(pv[8 * g], pv[8 * g + 1])),
+                       "r"(pack_bf16x2(pv[8 * g + 2], pv[8 * g + 3])), "r"(pack_bf16x2(pv[8 * g + 4], pv[8 * g + 5])),
+                       "r"(pack_bf16x2(pv[8 * g + 6], pv[8 * g + 7]))
+                       : "memory");
+        }
+      }
+      if (row == 0) fa_trace(p, 2, 3, j);  // pass 2 loop done
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty(b));
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      alpha_s[b * kFaTile + row] = alpha;
+      if (row == 0) fa_trace(p, 2, 4, j);  // before the proxy fence
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(b));
+      if (row == 0) fa_trace(p, 2, 2, j);  // P(j) published
+    });
+    if (ok) {
+      stats_s[row] = l_run;
+      stats_s[kFaTile + row] = m_run;
+      if (p.lse != nullptr && q_row0 + row < d.sq)
+        p.lse[(static_cast<long long>(batch) * d.hq + head) * d.sq + q_row0 + row] =
+            (l_run > 0.f) ? (m_run + log2f(l_run)) * kLn2 : -INFINITY;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stats_full);
+    } else if (lane == 0) {
+      record_status(p.status, kStatusMbarTimeout, 600, 0, 0, 30, 0);
+    }
+  } else {
+    // ------------------------------ accumulate (thread = row) ------------------------------
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    constexpr int DH = D / 2;                 // columns per accumulate warpgroup
+    const int col0 = (warp >= 12) ? DH : 0;   // warps 8-11: first half, warps 12-15: second half
+    float o[DH];
+#pragma unroll
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
+    const int n = for_each_kv_tile(d, q_pos_last, [](int, int, int, int, int) {});
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const int b = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      ok = mbar_wait(p_full(b), ph, abort_flag, p.budget_ns) && mbar_wait(o_full(b), ph, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      if (row == 0 && col0 == 0) fa_trace(p, 3, 0, j);  // O(j) visible to the accumulators
+      const float alpha = alpha_s[b * kFaTile + row];
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_o + (static_cast<uint32_t>(q4 * 32) << 16) + b * D + col0 + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(r[i]);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(o_empty(b));
+        mbar_arrive(a_empty(b));
+      }
+    }
+    if (ok) ok = mbar_wait(stats_full, 0, abort_flag, p.budget_ns);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const float l = stats_s[row];
+      const float inv = l > 0.f ? 1.0f / l : 0.f;
+      if (q_row0 + row < d.sq) {
+        __nv_bfloat16* dst = p.out + (static_cast<long long>(q_tok0 + row) * d.hq + head) * D + col0;
+#pragma unroll
+        for (int i = 0; i < DH; i += 8) {
+          U4 u{pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
+               pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv)};
+          st_global_v4(dst + i, u);
+        }
+      }
+    } else if (lane == 0) {
+      record_status(p.status, kStatusMbarTimeout, 600, 0, 0, 40, 0);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, void* out, void* lse,
+                     cudaStream_t stream) {
+  const pkb_attn_desc& d = *desc;
+  CUtensorMap tq, tk, tv;
+  // (d, head, token) views: d contiguous, head stride D*2 bytes, token stride heads*D*2 bytes
+  int rc = encode_tmap_3d(&tq, kTmapBf16, q, D, d.hq, (uint64_t)d.batch * d.sq, (uint64_t)D * 2, (uint64_t)d.hq * D * 2, 64,
+                          1, kFaTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tk, kTmapBf16, k, D, d.hkv, (uint64_t)d.batch * d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1,
+                      kFaTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tv, kTmapBf16, v, D, d.hkv, (uint64_t)d.batch * d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1,
+                      kFaTile, kSwizzle128);
+  if (rc) return rc;
+  FaParams p;
+  p.d = d;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = static_cast<float*>(lse);
+  p.status = status_block_device_ptr();
+  p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
+  p.trace = reinterpret_cast<long long*>(d.trace);
+  p.trace_capacity = d.trace_capacity;
+  auto kern = fa_fwd_kernel<D>;
+  constexpr int smem = FaSmem<D>::kTotal;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid((d.sq + kFaTile - 1) / kFaTile, d.hq, d.batch);
+  kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+extern "C" int pkb_flash_attn_fwd(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, void* out,
+                                  void* lse, void* stream) {
+  PKB_CHECK_ARG(desc != nullptr, "null descriptor");
+  const pkb_attn_desc& d = *desc;
+  PKB_CHECK_ARG(d.head_dim == 64 || d.head_dim == 128, "head_dim must be 64 or 128");
+  PKB_CHECK_ARG(d.hq % d.hkv == 0 && d.batch >= 1 && d.sq >= 1 && d.skv >= 1, "bad attention shape");
+  PKB_CHECK_ARG(d.num_q_segs >= 1 && d.num_q_segs <= 16 && d.num_kv_segs >= 1 && d.num_kv_segs <= 16, "1..16 segments");
+  PKB_CHECK_ARG(d.q_seg_rows % kFaTile == 0 || d.num_q_segs == 1, "q segments must be multiples of 128 rows");
+  for (int s = 0; s < d.num_kv_segs; ++s)
+    PKB_CHECK_ARG(d.kv_seg_row0[s] >= 0 && d.kv_seg_len[s] >= 0 && d.kv_seg_row0[s] + d.kv_seg_len[s] <= d.skv,
+                  "kv segment outside the buffer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d.head_dim == 128) return launch_fa<128>(desc, q, k, v, out, lse, s);
+  return launch_fa<64>(desc, q, k, v, out, lse, s);
+}
