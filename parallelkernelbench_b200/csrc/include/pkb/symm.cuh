@@ -57,8 +57,10 @@ __device__ __forceinline__ T* symm_mc(const SymmCtx& c, uint64_t off) {
 // Barrier between the same-index blocks of all group members. Every thread of the block calls it.
 // Returns false (on every thread) if a peer did not arrive within the budget; the status block
 // then names the kernel, this rank and the peer that was missing.
-__device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, int kernel_id, int site) {
-  __shared__ uint32_t s_epoch;
+// `s_epoch_slot` is one uint32 of shared memory used to broadcast the epoch inside the block.
+__device__ __forceinline__ bool symm_block_barrier_at(const SymmCtx& c, int kernel_id, int site,
+                                                      volatile uint32_t* s_epoch_slot) {
+  volatile uint32_t& s_epoch = *s_epoch_slot;
   const int b = blockIdx.x;
   const uint64_t chan_off = (uint64_t)c.channel * kSymmChannelBytes;
   __syncthreads();
@@ -82,6 +84,11 @@ __device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, int kernel_
     }
   }
   return __syncthreads_and(ok) != 0;
+}
+
+__device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, int kernel_id, int site) {
+  __shared__ uint32_t s_epoch_static;
+  return symm_block_barrier_at(c, kernel_id, site, &s_epoch_static);
 }
 
 }  // namespace pkb

@@ -28,7 +28,8 @@
 #include "pkb/api.h"
 #include "pkb/attention_api.h"
 #include "pkb/host.h"
-#include "pkb/ptx.cuh"
+#include "pkb/collectives_api.h"
+#include "pkb/symm.cuh"
 
 namespace pkb {
 
@@ -89,9 +90,9 @@ __device__ __forceinline__ int for_each_kv_tile(const pkb_attn_desc& d, int q_po
 }
 
 template <int D>
-__global__ void __launch_bounds__(kFaThreads, 1)
-fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-              const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+__device__ __forceinline__ void fa_fwd_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                           const CUtensorMap& tmap_v, const FaParams& p, const int q_tile,
+                                           const int head, const int batch) {
   using S = FaSmem<D>;
   constexpr int kAtoms = D / 64;          // 64-column (128-byte) swizzle atoms per tile row
   constexpr int kAtomBytes = kFaTile * 128;
@@ -120,9 +121,6 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_tile = gridDim.x - 1 - blockIdx.x;  // heavy (late, causal) tiles first
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
   const int kv_head = head / (d.hq / d.hkv);
   const int q_row0 = q_tile * kFaTile;  // row inside this batch's sequence
   const int q_seg = q_row0 / d.q_seg_rows;
@@ -181,8 +179,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         const uint32_t ph = (j >> 1) & 1;
         if (seg != last_seg) {
           last_seg = seg;
-          if (d.kv_seg_ready != nullptr) {
-            if (!wait_flag_ge(d.kv_seg_ready + seg, d.ready_epoch, p.budget_ns)) {
+          if (d.kv_seg_ready != nullptr && d.kv_seg_flag[seg] >= 0) {
+            if (!wait_flag_ge(d.kv_seg_ready + d.kv_seg_flag[seg], d.ready_epoch, p.budget_ns)) {
               *abort_flag = 1;
               record_status(p.status, kStatusPeerTimeout, 600, 0, seg, 10, j);
               ok = false;
@@ -435,6 +433,94 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 }
 
 template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+              const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  // heavy (late, causal) tiles first
+  fa_fwd_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// ---- context-parallel form: the KV exchange runs inside the attention kernel -------------------
+// The first `comm_blocks` CTAs push this rank's K and V chunks into every peer's gather buffer
+// (16-byte P2P stores) and count each finished piece on the peer's per-segment counter; the other
+// CTAs are attention CTAs whose TMA producer waits for the counter of a segment before loading it.
+// With NVSwitch every peer is one hop away, so the "ring" is only the order of the pushes.
+struct FaCommArgs {
+  SymmCtx ctx;
+  const uint8_t* k_local;     // [rows_local, hkv, D] bf16, rows_local = segs_per_rank * seg_rows
+  const uint8_t* v_local;
+  uint64_t k_gather_off;      // heap offsets of the gather buffers [gsize * rows_local, hkv, D]
+  uint64_t v_gather_off;
+  uint64_t flags_off;         // heap offset of gsize * segs_per_rank uint32 counters
+  long long seg_bytes;        // bytes of one segment of K (or V)
+  long long piece_bytes;      // a segment is pushed in pieces of this size
+  int segs_per_rank;
+  int comm_blocks;
+  int local_in_place;         // k_local / v_local already are this rank's slots of the gather buffers
+  int num_q_tiles, hq;
+};
+
+__device__ __forceinline__ void fa_push_role(const FaCommArgs& a) {
+  const SymmCtx& c = a.ctx;
+  // all ranks have entered this call => nobody still reads the previous call's gathered KV
+  // (the epoch slot lives in dynamic shared memory: this kernel has no room for static shared memory)
+  extern __shared__ __align__(1024) uint8_t smem_comm[];
+  if (!symm_block_barrier_at(c, 601, 1, reinterpret_cast<volatile uint32_t*>(smem_comm))) return;
+  const int W = c.gsize;
+  const int pieces = static_cast<int>((a.seg_bytes + a.piece_bytes - 1) / a.piece_bytes);
+  const int per_dest = a.segs_per_rank * 2 * pieces;  // (segment, K|V, piece)
+  const int first = a.local_in_place ? per_dest : 0;
+  for (int item = first + blockIdx.x; item < W * per_dest; item += a.comm_blocks) {
+    const int step = item / per_dest;          // 0 = local copy, then rank+1, rank+2, ...
+    int rem = item - step * per_dest;
+    const int seg = rem / (2 * pieces);
+    rem -= seg * 2 * pieces;
+    const int is_v = rem / pieces;
+    const int piece = rem - is_v * pieces;
+    int dest_g = c.grank + step;
+    if (dest_g >= W) dest_g -= W;
+    const int dest = c.members[dest_g];
+    const long long off = (long long)seg * a.seg_bytes + (long long)piece * a.piece_bytes;
+    const long long n = min(a.piece_bytes, a.seg_bytes - (long long)piece * a.piece_bytes);
+    const uint8_t* src = (is_v ? a.v_local : a.k_local) + off;
+    uint8_t* dst = symm_ptr<uint8_t>(c, dest, is_v ? a.v_gather_off : a.k_gather_off) +
+                   (long long)c.grank * a.segs_per_rank * a.seg_bytes + off;
+    const long long nvec = n >> 4;
+    long long i = threadIdx.x;
+    for (; i + 3ll * blockDim.x < nvec; i += 4ll * blockDim.x) {
+      U4 v0 = ld_global_nc_v4(src + (i << 4));
+      U4 v1 = ld_global_nc_v4(src + ((i + blockDim.x) << 4));
+      U4 v2 = ld_global_nc_v4(src + ((i + 2ll * blockDim.x) << 4));
+      U4 v3 = ld_global_nc_v4(src + ((i + 3ll * blockDim.x) << 4));
+      st_global_v4(dst + (i << 4), v0);
+      st_global_v4(dst + ((i + blockDim.x) << 4), v1);
+      st_global_v4(dst + ((i + 2ll * blockDim.x) << 4), v2);
+      st_global_v4(dst + ((i + 3ll * blockDim.x) << 4), v3);
+    }
+    for (; i < nvec; i += blockDim.x) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      red_release_sys_add(symm_ptr<uint32_t>(c, dest, a.flags_off) + c.grank * a.segs_per_rank + seg, 1u);
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const FaCommArgs a) {
+  if ((int)blockIdx.x < a.comm_blocks) {
+    fa_push_role(a);
+    return;
+  }
+  const int id = blockIdx.x - a.comm_blocks;
+  const int qt = a.num_q_tiles - 1 - id % a.num_q_tiles;
+  const int hb = id / a.num_q_tiles;
+  fa_fwd_cta<D>(tmap_q, tmap_k, tmap_v, p, qt, hb % a.hq, hb / a.hq);
+}
+
+template <int D>
 static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, void* out, void* lse,
                      cudaStream_t stream) {
   const pkb_attn_desc& d = *desc;
@@ -484,4 +570,95 @@ extern "C" int pkb_flash_attn_fwd(const pkb_attn_desc* desc, const void* q, cons
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (d.head_dim == 128) return launch_fa<128>(desc, q, k, v, out, lse, s);
   return launch_fa<64>(desc, q, k, v, out, lse, s);
+}
+
+namespace pkb {
+
+template <int D>
+static int launch_fa_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, const void* q, const void* k_local,
+                          const void* v_local, unsigned long long k_off, unsigned long long v_off,
+                          unsigned long long flags_off, int segs_per_rank, int seg_rows, int comm_blocks, void* out,
+                          void* lse, cudaStream_t stream) {
+  pkb_attn_desc d = *desc;
+  const uint64_t local_base = h->base + (uint64_t)h->rank * h->stride;
+  const void* kg = reinterpret_cast<const void*>(local_base + k_off);
+  const void* vg = reinterpret_cast<const void*>(local_base + v_off);
+  CUtensorMap tq, tk, tv;
+  int rc = encode_tmap_3d(&tq, kTmapBf16, q, D, d.hq, (uint64_t)d.batch * d.sq, (uint64_t)D * 2, (uint64_t)d.hq * D * 2, 64,
+                          1, kFaTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tk, kTmapBf16, kg, D, d.hkv, (uint64_t)d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1, kFaTile,
+                      kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tv, kTmapBf16, vg, D, d.hkv, (uint64_t)d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1, kFaTile,
+                      kSwizzle128);
+  if (rc) return rc;
+
+  FaCommArgs a;
+  a.ctx.base = h->base; a.ctx.stride = h->stride; a.ctx.mc_base = h->mc_base;
+  a.ctx.rank = h->rank; a.ctx.world = h->world; a.ctx.gsize = h->gsize; a.ctx.grank = h->grank;
+  for (int i = 0; i < kSymmMaxWorld; ++i) a.ctx.members[i] = h->members[i];
+  a.ctx.channel = h->channel;
+  a.ctx.status = status_block_device_ptr();
+  a.ctx.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
+  a.k_local = static_cast<const uint8_t*>(k_local);
+  a.v_local = static_cast<const uint8_t*>(v_local);
+  a.k_gather_off = k_off; a.v_gather_off = v_off; a.flags_off = flags_off;
+  a.seg_bytes = (long long)seg_rows * d.hkv * D * 2;
+  a.piece_bytes = 1ll << 20;
+  if (a.piece_bytes > a.seg_bytes) a.piece_bytes = a.seg_bytes;
+  a.segs_per_rank = segs_per_rank;
+  a.comm_blocks = comm_blocks;
+  const long long rank_bytes = a.seg_bytes * segs_per_rank;
+  a.local_in_place = (k_local == static_cast<const uint8_t*>(kg) + (long long)h->grank * rank_bytes &&
+                      v_local == static_cast<const uint8_t*>(vg) + (long long)h->grank * rank_bytes) ? 1 : 0;
+  a.num_q_tiles = (d.sq + kFaTile - 1) / kFaTile;
+  a.hq = d.hq;
+  const int pieces = (int)((a.seg_bytes + a.piece_bytes - 1) / a.piece_bytes);
+  d.kv_seg_ready = reinterpret_cast<const uint32_t*>(local_base + flags_off);
+  d.ready_epoch = desc->ready_epoch * (uint32_t)(2 * pieces);
+  if (!a.local_in_place) {
+    // the local rows are copied by the communication CTAs as well: they get a counter like the rest
+  }
+
+  FaParams p;
+  p.d = d;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.lse = static_cast<float*>(lse);
+  p.status = a.ctx.status;
+  p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
+  p.trace = nullptr;
+  p.trace_capacity = 0;
+  auto kern = fa_fwd_ring_kernel<D>;
+  constexpr int smem = FaSmem<D>::kTotal;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int grid = comm_blocks + a.num_q_tiles * d.hq * d.batch;
+  kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // namespace pkb
+
+extern "C" int pkb_flash_attn_fwd_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, const void* q,
+                                       const void* k_local, const void* v_local, unsigned long long k_gather_off,
+                                       unsigned long long v_gather_off, unsigned long long flags_off,
+                                       int segs_per_rank, int seg_rows, int comm_blocks, void* out, void* lse,
+                                       void* stream) {
+  PKB_CHECK_ARG(desc != nullptr && h != nullptr && h->base != 0, "null descriptor or heap");
+  const pkb_attn_desc& d = *desc;
+  PKB_CHECK_ARG(d.head_dim == 64 || d.head_dim == 128, "head_dim must be 64 or 128");
+  PKB_CHECK_ARG(d.batch == 1, "the context-parallel form takes one sequence");
+  PKB_CHECK_ARG(d.hq % d.hkv == 0 && d.sq >= 1, "bad attention shape");
+  PKB_CHECK_ARG(segs_per_rank >= 1 && seg_rows >= 1 && h->gsize * segs_per_rank <= 16, "at most 16 KV segments");
+  PKB_CHECK_ARG(d.skv == h->gsize * segs_per_rank * seg_rows, "desc.skv must cover the gather buffer");
+  PKB_CHECK_ARG(comm_blocks >= 1 && comm_blocks <= kSymmMaxBlocks, "1..256 communication blocks");
+  PKB_CHECK_ARG((k_gather_off & 1023) == 0 && (v_gather_off & 1023) == 0 && (flags_off & 15) == 0, "heap offsets misaligned");
+  PKB_CHECK_ARG(((long long)seg_rows * d.hkv * d.head_dim * 2) % 16 == 0, "segment size must be a multiple of 16 bytes");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d.head_dim == 128)
+    return pkb::launch_fa_ring<128>(desc, h, q, k_local, v_local, k_gather_off, v_gather_off, flags_off, segs_per_rank,
+                                    seg_rows, comm_blocks, out, lse, s);
+  return pkb::launch_fa_ring<64>(desc, h, q, k_local, v_local, k_gather_off, v_gather_off, flags_off, segs_per_rank, seg_rows,
+                                 comm_blocks, out, lse, s);
 }

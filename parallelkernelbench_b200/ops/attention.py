@@ -19,7 +19,7 @@ class AttnDesc(ctypes.Structure):
                 ("hkv", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("causal", ctypes.c_int32), ("scale", ctypes.c_float),
                 ("q_seg_rows", ctypes.c_int32), ("num_q_segs", ctypes.c_int32), ("q_seg_pos", ctypes.c_int32 * 16),
                 ("num_kv_segs", ctypes.c_int32), ("kv_seg_row0", ctypes.c_int32 * 16), ("kv_seg_pos0", ctypes.c_int32 * 16),
-                ("kv_seg_len", ctypes.c_int32 * 16), ("kv_seg_ready", ctypes.c_void_p), ("ready_epoch", ctypes.c_uint32),
+                ("kv_seg_len", ctypes.c_int32 * 16), ("kv_seg_flag", ctypes.c_int32 * 16), ("kv_seg_ready", ctypes.c_void_p), ("ready_epoch", ctypes.c_uint32),
                 ("_pad", ctypes.c_uint32), ("budget_ns", ctypes.c_uint64), ("trace", ctypes.c_void_p),
                 ("trace_capacity", ctypes.c_int32), ("_pad2", ctypes.c_int32)]
 
@@ -51,6 +51,7 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
     d.num_kv_segs = len(kv_segments)
     for i, (row0, pos0, ln) in enumerate(kv_segments):
         d.kv_seg_row0[i], d.kv_seg_pos0[i], d.kv_seg_len[i] = row0, pos0, ln
+        d.kv_seg_flag[i] = i
     d.kv_seg_ready = kv_ready.data_ptr() if kv_ready is not None else None
     d.ready_epoch = ready_epoch
     if trace is not None:            # int64 buffer: [0] = record count, records of (role, event, tile, clock) from word 4
@@ -61,3 +62,89 @@ def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal:
                                               nv.current_stream()), "pkb_flash_attn_fwd")
     nv.count_launch()
     return out, lse
+
+
+def zigzag_positions(world: int, rank: int, chunk: int) -> list[int]:
+    """Global start positions of the two chunks a rank owns in the load-balanced causal layout:
+    the sequence is cut into ``2 * world`` chunks and rank r holds chunks r and 2*world-1-r."""
+    return [rank * chunk, (2 * world - 1 - rank) * chunk]
+
+
+class RingAttention:
+    """Context-parallel attention: every rank holds ``rows_local`` rows of one long sequence.
+
+    One launch per forward: communication CTAs of the attention kernel push this rank's K and V into
+    the peers' gather buffers while the attention CTAs start on the local rows and pick up remote
+    segments as their counters arrive (reference behaviour: a Python loop of isend/irecv steps around
+    a materialised-score attention, reference: reference/54_ring_attention.py:29-100).
+
+    ``layout="zigzag"`` (causal load balance: two chunks per rank) or ``"contiguous"``.
+    """
+
+    def __init__(self, group, rows_local: int, hq: int, hkv: int, head_dim: int, layout: str = "zigzag",
+                 comm_blocks: int = 8):
+        W = group.size
+        self.group, self.W, self.rows, self.hq, self.hkv, self.D = group, W, rows_local, hq, hkv, head_dim
+        self.layout, self.comm_blocks = layout, comm_blocks
+        self.segs = 2 if layout == "zigzag" else 1
+        if rows_local % (self.segs * 128) != 0:
+            raise ValueError("rows per rank must be a multiple of 128 per chunk")
+        if W * self.segs > 16:
+            raise ValueError("at most 16 KV segments (8 ranks in the zigzag layout)")
+        self.seg_rows = rows_local // self.segs
+        heap = group.heap
+        self.k_gather = heap.empty((W * rows_local, hkv, head_dim), torch.bfloat16)
+        self.v_gather = heap.empty((W * rows_local, hkv, head_dim), torch.bfloat16)
+        self.flags = heap.empty((max(W * self.segs, 4),), torch.int32)
+        self.flags.local.zero_()
+        self.calls = 0
+
+    def positions(self, rank_in_group: int) -> list[int]:
+        if self.layout == "zigzag":
+            return zigzag_positions(self.W, rank_in_group, self.seg_rows)
+        return [rank_in_group * self.rows]
+
+    @property
+    def kv_slots(self):
+        """Views of this rank's rows inside the gather buffers (write K, V there to skip the local copy)."""
+        r = self.group.rank_in_group
+        sl = slice(r * self.rows, (r + 1) * self.rows)
+        return self.k_gather.local[sl], self.v_gather.local[sl]
+
+    def forward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = True, scale: float | None = None):
+        """``q`` [rows, hq, d], ``k``/``v`` [rows, hkv, d] (this rank's rows). Returns ``(out, lse)``."""
+        W, r = self.W, self.group.rank_in_group
+        d = AttnDesc()
+        d.batch, d.sq, d.skv, d.hq, d.hkv, d.head_dim = 1, self.rows, W * self.rows, self.hq, self.hkv, self.D
+        d.causal = 1 if causal else 0
+        d.scale = float(scale if scale is not None else 1.0 / math.sqrt(self.D))
+        d.q_seg_rows, d.num_q_segs = self.seg_rows, self.segs
+        for i, pos in enumerate(self.positions(r)):
+            d.q_seg_pos[i] = pos
+        # consumption order: local rows first, then the ranks whose pushes reach us first
+        order = [(r - s) % W for s in range(W)]
+        n = 0
+        in_place = k.data_ptr() == self.kv_slots[0].data_ptr() and v.data_ptr() == self.kv_slots[1].data_ptr()
+        for src in order:
+            for sgi, pos in enumerate(self.positions(src)):
+                d.kv_seg_row0[n] = src * self.rows + sgi * self.seg_rows
+                d.kv_seg_pos0[n] = pos
+                d.kv_seg_len[n] = self.seg_rows
+                d.kv_seg_flag[n] = -1 if (src == r and in_place) else src * self.segs + sgi
+                n += 1
+        d.num_kv_segs = n
+        self.calls += 1
+        d.ready_epoch = self.calls
+        out = torch.empty((self.rows, self.hq, self.D), dtype=torch.bfloat16, device=q.device)
+        lse = torch.empty((1, self.hq, self.rows), dtype=torch.float32, device=q.device)
+        if not in_place and W > 0:
+            pass  # the communication CTAs copy the local rows into the gather buffers too
+        nv.check(nv.cuda_lib().pkb_flash_attn_fwd_ring(
+            ctypes.byref(d), self.group.ref, nv.ptr(q.contiguous()), nv.ptr(k.contiguous()), nv.ptr(v.contiguous()),
+            ctypes.c_ulonglong(self.k_gather.offset), ctypes.c_ulonglong(self.v_gather.offset),
+            ctypes.c_ulonglong(self.flags.offset), self.segs, self.seg_rows, self.comm_blocks, nv.ptr(out), nv.ptr(lse),
+            nv.current_stream()), "pkb_flash_attn_fwd_ring")
+        nv.count_launch()
+        return out, lse
+
+    __call__ = forward

@@ -1,0 +1,78 @@
+"""PyTorch (+NCCL) references for attention.
+
+``attention_positions_ref``  exact fp32 restatement with explicit global positions (small shapes).
+``cp_attention_reference``   the timed context-parallel baseline: NCCL all-gather of K and V, then the
+                             library flash kernel per Q chunk (past chunks un-masked, own chunk causal),
+                             merged by log-sum-exp.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+
+def attention_positions_ref(q, k, v, q_pos, kv_pos, causal: bool, scale: float):
+    """q [Sq,Hq,D], k/v [Skv,Hkv,D]; ``q_pos``/``kv_pos`` global positions. Returns (out fp32, lse)."""
+    Hq, Hkv = q.shape[1], k.shape[1]
+    qf = q.float().permute(1, 0, 2)
+    kf = k.float().permute(1, 0, 2).repeat_interleave(Hq // Hkv, dim=0)
+    vf = v.float().permute(1, 0, 2).repeat_interleave(Hq // Hkv, dim=0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * scale
+    if causal:
+        s = s.masked_fill((kv_pos[None, :] > q_pos[:, None])[None], float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.nan_to_num(torch.softmax(s, dim=-1))
+    return torch.einsum("hqk,hkd->hqd", p, vf).permute(1, 0, 2), lse
+
+
+def _flash(q, k, v, causal, scale):
+    """Library flash attention on [S,H,D] tensors with GQA; returns (out [S,H,D], lse [H,S])."""
+    Hq, Hkv = q.shape[1], k.shape[1]
+    qt = q.permute(1, 0, 2).unsqueeze(0)
+    kt = k.permute(1, 0, 2).unsqueeze(0).repeat_interleave(Hq // Hkv, dim=1)
+    vt = v.permute(1, 0, 2).unsqueeze(0).repeat_interleave(Hq // Hkv, dim=1)
+    res = torch.ops.aten._scaled_dot_product_flash_attention(qt, kt, vt, 0.0, causal, False, scale=scale)
+    return res[0][0].permute(1, 0, 2), res[1][0]
+
+
+def _merge(o1, l1, o2, l2):
+    lse = torch.logaddexp(l1, l2)
+    w1 = torch.exp(l1 - lse).t().unsqueeze(-1)
+    w2 = torch.exp(l2 - lse).t().unsqueeze(-1)
+    return (o1.float() * w1 + o2.float() * w2), lse
+
+
+def cp_attention_reference(q, k, v, positions_of, world: int, rank: int, causal: bool, scale: float | None = None, group=None):
+    """``q``/``k``/``v``: this rank's rows [rows, H, D] made of equal chunks whose global start positions
+    are ``positions_of(rank)``. Returns (out [rows, Hq, D] in q.dtype, lse [Hq, rows])."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    rows = q.shape[0]
+    if world > 1:
+        kg = torch.empty((world * rows, *k.shape[1:]), dtype=k.dtype, device=k.device)
+        vg = torch.empty_like(kg)
+        dist.all_gather_into_tensor(kg, k.contiguous(), group=group)
+        dist.all_gather_into_tensor(vg, v.contiguous(), group=group)
+    else:
+        kg, vg = k, v
+    nseg = len(positions_of(0))
+    C = rows // nseg
+    # global order of the gathered chunks
+    chunks = sorted((pos, src * rows + i * C) for src in range(world) for i, pos in enumerate(positions_of(src)))
+    kfull = torch.cat([kg[row0:row0 + C] for _, row0 in chunks])
+    vfull = torch.cat([vg[row0:row0 + C] for _, row0 in chunks])
+    outs, lses = [], []
+    for i, pos in enumerate(positions_of(rank)):
+        qc = q[i * C:(i + 1) * C]
+        if not causal:
+            o, l = _flash(qc, kfull, vfull, False, scale)
+        else:
+            o, l = _flash(qc, kfull[pos:pos + C], vfull[pos:pos + C], True, scale)
+            if pos > 0:
+                o0, l0 = _flash(qc, kfull[:pos], vfull[:pos], False, scale)
+                o, l = _merge(o0, l0, o, l)
+        outs.append(o.to(q.dtype))
+        lses.append(l)
+    return torch.cat(outs), torch.cat(lses, dim=1)

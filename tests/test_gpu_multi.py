@@ -68,6 +68,19 @@ def test_moe_and_all_ops_multi_rank(nproc):
     _assert_ok(_torchrun("tests/mp/all_ops_worker.py", nproc, port=29640 + nproc))
 
 
+def test_ring_attention_single_rank():
+    r = _torchrun("tests/mp/all_ops_worker.py", 1, "--ops", "ring_attention,flash_attention", port=29605)
+    _assert_ok(r)
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_ring_attention_multi_rank(nproc):
+    if _ngpus() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _assert_ok(_torchrun("tests/mp/all_ops_worker.py", nproc, "--ops", "ring_attention", "--config", "default", port=29650 + nproc))
+
+
 def test_harness_eval_on_gpu_single_rank():
     env = dict(os.environ, PKB_LOGS_DIR=os.path.join(ROOT, "logs", "pytest_gpu"), PKB_COOLDOWN_SEC="0")
     r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "eval", "--op", "allreduce",
