@@ -83,8 +83,9 @@ struct GemmSmem {
 // the tile loop (a fused kernel may reserve some of its grid for communication roles).
 // B_MN: B is given as [K, N] row-major (N contiguous) instead of [N, K]; its tiles are loaded as
 // BN/64 boxes of 64 x 64 and described to the tensor core as MN-major.
+// A_MN: A is given as [K, M] row-major (M contiguous), i.e. the kernel computes A^T B.
 template <int BN, int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool GROUPED = false,
-          bool B_MN = false>
+          bool B_MN = false, bool A_MN = false>
 __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                               const GemmParams& p, const int cta,
                                               const int num_ctas) {
@@ -212,7 +213,13 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
           }
           mbar_expect_tx(full_bar(stage), S::kStageBytes);
           const uint32_t sa = smem_base + stage * S::kStageBytes;
-          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kGemmBlockM / 64; ++j)
+              tma_load_2d(sa + j * 8192, &tmap_a, full_bar(stage), row0 + j * 64, kb * kGemmBlockK);
+          } else {
+            tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+          }
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
@@ -232,7 +239,7 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc(kGemmBlockM, BN, 1, 1, 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = make_idesc(kGemmBlockM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -253,14 +260,14 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
           }
           tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * S::kStageBytes;
-          const uint64_t da = make_smem_desc_sw128_kmajor(sa);
+          const uint64_t da = A_MN ? make_smem_desc_sw128_mnmajor(sa, 8192u) : make_smem_desc_sw128_kmajor(sa);
           const uint64_t db = B_MN ? make_smem_desc_sw128_mnmajor(sa + S::kABytes, 8192u)
                                    : make_smem_desc_sw128_kmajor(sa + S::kABytes);
 #pragma unroll
           for (int k = 0; k < kGemmBlockK / 16; ++k) {
             // K-major: 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (addr >> 4)
             // field. MN-major: 16 K rows of 128 bytes: +128.
-            umma_f16_ss(tmem_d, da + 2u * k, db + (B_MN ? 128u : 2u) * k, idesc,
+            umma_f16_ss(tmem_d, da + (A_MN ? 128u : 2u) * k, db + (B_MN ? 128u : 2u) * k, idesc,
                         (kb | k) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));  // smem stage reusable once these MMAs have read it
@@ -429,6 +436,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_umma_bkn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   gemm_umma_cta<BN, EPI, OUT_F32, false, false, false, true>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
+}
+
+// C = A^T B with A [K, M] and B [K, N], both row-major (weight gradients: dW = dY^T X)
+template <int BN, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_umma_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma_cta<BN, kEpiNone, OUT_F32, false, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x, gridDim.x);
 }
 
 // ragged groups (MoE experts): A rows grouped by expert, B = [groups * N, K]

@@ -258,3 +258,37 @@ extern "C" int pkb_gemm_bf16_bkn(const void* a, long long lda, const void* b, lo
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
+
+// C[M,N] = alpha * A^T B with A [K, M] and B [K, N] row-major (lda, ldb in elements; M, N, K % 8 == 0).
+// The natural form of a weight gradient (dW = dY^T X): no transposed copy of either operand.
+extern "C" int pkb_gemm_bf16_tn(const void* a, long long lda, const void* b, long long ldb, void* c,
+                                long long ldc, int M, int N, int K, float alpha, int out_f32, void* stream) {
+  PKB_CHECK_ARG(M > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && M % 8 == 0 && N % 8 == 0, "lda, ldb, M, N must be multiples of 8");
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, kGemmBlockK, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, kGemmBlockK, kSwizzle128);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.C = c; p.ldc = ldc; p.alpha = alpha;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.group_m = 16; p.kernel_id = 104; p.world = 1;
+  const int tiles = ((M + 127) / 128) * ((N + 255) / 256);
+  int ctas = sm_count();
+  if (ctas > tiles) ctas = tiles;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  constexpr int smem = GemmSmem<256>::kTotal;
+  if (out_f32) {
+    auto kern = gemm_umma_tn_kernel<256, true>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<ctas, kGemmThreads, smem, s>>>(ta, tb, p);
+  } else {
+    auto kern = gemm_umma_tn_kernel<256, false>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<ctas, kGemmThreads, smem, s>>>(ta, tb, p);
+  }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}

@@ -83,3 +83,22 @@ def gemm_bf16_kn(a: torch.Tensor, b: torch.Tensor, *, out: torch.Tensor | None =
              "pkb_gemm_bf16_bkn")
     nv.count_launch()
     return out
+
+
+def gemm_bf16_tn(a_km: torch.Tensor, b_kn: torch.Tensor, *, out: torch.Tensor | None = None, alpha: float = 1.0,
+                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``a_km.T @ b_kn`` for row-major ``a_km[K, M]`` and ``b_kn[K, N]`` (both MN-major operands): the
+    weight-gradient form ``dW = dY.T @ X`` without materialising a transpose."""
+    if a_km.dtype != torch.bfloat16 or b_kn.dtype != torch.bfloat16 or a_km.shape[0] != b_kn.shape[0]:
+        raise ValueError("gemm_bf16_tn expects bf16 a[K, M] and b[K, N]")
+    if a_km.stride(1) != 1 or b_kn.stride(1) != 1:
+        raise ValueError("operands must be contiguous along their last dimension")
+    K, M = a_km.shape
+    N = b_kn.shape[1]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a_km.device)
+    nv.check(nv.cuda_lib().pkb_gemm_bf16_tn(nv.ptr(a_km), nv.c_ll(a_km.stride(0)), nv.ptr(b_kn), nv.c_ll(b_kn.stride(0)),
+                                            nv.ptr(out), nv.c_ll(out.stride(0)), M, N, K, nv.c_float(alpha),
+                                            1 if out.dtype == torch.float32 else 0, nv.current_stream()), "pkb_gemm_bf16_tn")
+    nv.count_launch()
+    return out

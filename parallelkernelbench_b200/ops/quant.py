@@ -42,3 +42,18 @@ def dequant_sum(payload: torch.Tensor, scales: torch.Tensor, mode: str, block: i
                                            nv.current_stream()), "pkb_dequant_sum")
     nv.count_launch()
     return out
+
+
+def fsdp_adamw_fp8(payload: torch.Tensor, scales: torch.Tensor, p: torch.Tensor, m: torch.Tensor, v: torch.Tensor,
+                   q_out: torch.Tensor, s_out: torch.Tensor, *, lr: float, beta1: float, beta2: float, eps: float,
+                   weight_decay: float, grad_scale: float, step: int, p_bf16: torch.Tensor | None = None) -> None:
+    """Owner side of the fp8 gradient exchange: ``payload`` [W, n] e4m3 bytes + ``scales`` [W, n/128]
+    are dequantised, summed, scaled by ``grad_scale`` (1/W), applied with AdamW to the fp32 shard
+    ``p, m, v`` in place, and the new weights are written as e4m3 + 1x128 scales into ``q_out, s_out``."""
+    W, n = payload.shape
+    nv.check(nv.cuda_lib().pkb_fsdp_adamw_fp8(nv.ptr(payload.contiguous()), nv.ptr(scales.contiguous()), W, nv.c_ll(n),
+                                              nv.ptr(p), nv.ptr(m), nv.ptr(v), nv.ptr(q_out), nv.ptr(s_out), nv.ptr(p_bf16),
+                                              nv.c_float(lr), nv.c_float(beta1), nv.c_float(beta2), nv.c_float(eps),
+                                              nv.c_float(weight_decay), nv.c_float(grad_scale), int(step),
+                                              nv.current_stream()), "pkb_fsdp_adamw_fp8")
+    nv.count_launch()

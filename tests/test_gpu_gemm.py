@@ -96,3 +96,13 @@ def test_gemm_with_row_major_kn_weight(M, N, K):
     b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.05
     out = gemm_bf16_kn(a, b)
     torch.testing.assert_close(out.float(), a.float() @ b.float(), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 512, 1000), (4096, 1024, 4096)])
+def test_gemm_transposed_a_for_weight_gradients(M, N, K):
+    from parallelkernelbench_b200.ops import gemm_bf16_tn
+
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16) * 0.1
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.1
+    out = gemm_bf16_tn(a, b, out_dtype=torch.float32)
+    torch.testing.assert_close(out, a.float().t() @ b.float(), atol=3e-2, rtol=2e-2)
