@@ -36,6 +36,12 @@ int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const v
 int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n,
                             unsigned long long stage_off, unsigned long long result_off, void* out,
                             int src_in_heap, int max_blocks, void* stream);
+// Remote row gather over a table sharded by rows: out[i] = table_of_member(ids[i] / rows_per_member)[ids[i] % rows_per_member].
+// ids are int64; ids outside [0, gsize * rows_per_member) produce rows of zeros. With sync = 0 the shards must already
+// be resident at table_off on every member and unchanged since the last barrier.
+int pkb_coll_row_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long table_off,
+                        const void* ids, long long n, long long rows_per_member, long long row_bytes, void* out,
+                        int sync, int max_blocks, void* stream);
 int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_rows, long long row_bytes,
                           const void* send_counts, const void* send_offsets, unsigned long long stage_off,
                           unsigned long long meta_off, void* out, long long out_capacity_rows,

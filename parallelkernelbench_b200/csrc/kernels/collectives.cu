@@ -222,6 +222,47 @@ coll_gather_kernel(const SymmCtx c, const GatherArgs a) {
 }
 
 // ================================================================================================
+// remote row gather: out[i] = row (ids[i] % rows_per_member) of member (ids[i] / rows_per_member)
+// ================================================================================================
+struct RowGatherArgs {
+  const void* src;          // local table shard, staged into the heap when stage_bytes > 0
+  long long stage_bytes;
+  uint64_t table_off;       // heap offset of every member's shard
+  const long long* ids;     // [n] global row ids
+  long long n;
+  long long rows_per_member;
+  long long row_bytes;
+  void* out;                // [n, row_bytes]
+  int sync;                 // 0: the table is resident and unchanged, no barrier needed
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_row_gather_kernel(const SymmCtx c, const RowGatherArgs a) {
+  if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.table_off), a.src, a.stage_bytes);
+  if (a.sync && !symm_block_barrier(c, 205, 1)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const bool vec = ((a.row_bytes | a.table_off | (uintptr_t)a.out) & 15) == 0;
+  for (long long i = warp; i < a.n; i += nwarps) {
+    const long long id = a.ids[i];
+    long long g = id / a.rows_per_member;
+    uint8_t* dst = static_cast<uint8_t*>(a.out) + i * a.row_bytes;
+    if (id < 0 || g >= c.gsize) {                       // out-of-range id: a row of zeros, never a wild load
+      for (long long b = lane; b < a.row_bytes; b += 32) dst[b] = 0;
+      continue;
+    }
+    const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.table_off) + (id - g * a.rows_per_member) * a.row_bytes;
+    if (vec) {
+      for (long long b = (long long)lane << 4; b < a.row_bytes; b += 32 << 4) st_global_v4(dst + b, ld_global_v4(from + b));
+    } else {
+      for (long long b = lane; b < a.row_bytes; b += 32) dst[b] = from[b];
+    }
+  }
+  if (a.sync) symm_block_barrier(c, 205, 2);
+}
+
+// ================================================================================================
 // two-shot all-reduce: reduce own slice -> publish -> gather all slices
 // ================================================================================================
 struct TwoShotArgs {
@@ -449,6 +490,20 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
   const long long work = stage_bytes > seg_bytes * h->gsize ? stage_bytes : seg_bytes * h->gsize;
   const int grid = grid_for(work, max_blocks);
   coll_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_row_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long table_off,
+                        const void* ids, long long n, long long rows_per_member, long long row_bytes, void* out,
+                        int sync, int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(rows_per_member > 0 && row_bytes > 0 && n >= 0, "rows_per_member and row_bytes must be positive");
+  PKB_CHECK_ARG(stage_bytes == 0 || sync, "a staged table needs the barriers");
+  RowGatherArgs a{src, stage_bytes, table_off, static_cast<const long long*>(ids), n, rows_per_member, row_bytes, out, sync};
+  const long long work = stage_bytes > n * row_bytes ? stage_bytes : n * row_bytes;
+  const int grid = grid_for(work, max_blocks);
+  coll_row_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -183,6 +183,31 @@ def gather(x: torch.Tensor, group: SymmGroup, dst: int = 0) -> torch.Tensor:
     return out
 
 
+def row_gather(shard: torch.Tensor, ids: torch.Tensor, group: SymmGroup, resident: bool = False) -> torch.Tensor:
+    """Lookup in a table sharded by rows over the group: ``out[i] = table[ids[i]]`` where member ``g`` owns rows
+    ``[g * S, (g + 1) * S)`` and ``shard`` is this member's ``[S, ...]`` slice. Rows are fetched with direct peer loads,
+    so no request/reply exchange is needed (the reference does three all-to-alls: reference/10_embedding_lookup.py).
+    ``resident=True``: ``shard`` lives in the symmetric heap and has not changed since the last barrier - no staging,
+    no barriers."""
+    shard = _check(shard)
+    idc = ids.contiguous().view(-1).to(torch.int64)
+    S = shard.shape[0]
+    row_bytes = (shard.numel() // max(S, 1)) * shard.element_size()
+    if resident:
+        off = group.heap.contains(shard)
+        if off is None:
+            raise ValueError("resident=True needs a shard allocated in the symmetric heap")
+        stage_bytes = 0
+    else:
+        off, stage_bytes = _stage(group, "rowgather_in", shard)
+    out = torch.empty((idc.numel(), *shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+    nv.check(_lib().pkb_coll_row_gather(group.ref, nv.ptr(shard), nv.c_ll(stage_bytes), ctypes.c_ulonglong(off), nv.ptr(idc),
+                                        nv.c_ll(idc.numel()), nv.c_ll(S), nv.c_ll(row_bytes), nv.ptr(out), 0 if resident else 1,
+                                        0, nv.current_stream()), "pkb_coll_row_gather")
+    nv.count_launch()
+    return out.view(*ids.shape, *shard.shape[1:])
+
+
 def all_to_all_v(x: torch.Tensor, send_counts: torch.Tensor, group: SymmGroup, out_capacity_rows: int,
                  send_offsets: torch.Tensor | None = None, max_send_rows: int | None = None):
     """Variable all-to-all of rows. ``x`` is ``[rows, ...]`` grouped by destination, ``send_counts``

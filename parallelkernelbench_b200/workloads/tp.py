@@ -108,17 +108,9 @@ def _emb_ours(rc, idx, shard):
     if W == 1:
         return shard[idx]
     if rc.dist.is_cuda:
-        heap = rc.comm.heap
-        tbl = heap.named(("emb_table", tuple(shard.shape)), shard.shape, shard.dtype)
-        tbl.local.copy_(shard)
-        rc.comm.barrier()
-        out = torch.empty((idx.numel(), shard.shape[1]), dtype=shard.dtype, device=shard.device)
-        owner = idx // S
-        for p in range(W):
-            sel = (owner == p).nonzero(as_tuple=True)[0]
-            out[sel] = tbl.peer(p)[idx[sel] % S]          # direct P2P loads from the owner's shard
-        rc.comm.barrier()
-        return out
+        from ..ops.collectives import row_gather
+
+        return row_gather(shard, idx, rc.comm.group())
     table = rc.comm.all_gather(shard).reshape(W * S, -1)
     return table[idx]
 

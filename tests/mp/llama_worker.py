@@ -1,0 +1,73 @@
+"""Per-rank body of the FSDP Llama test: a small decoder trained for a few steps with our kernels and
+with the PyTorch+NCCL implementation from the same initial weights; losses must track each other."""
+import os
+import sys
+import time
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from parallelkernelbench_b200 import _native as nv  # noqa: E402
+from parallelkernelbench_b200.models.llama import FSDPLlama, LlamaConfig  # noqa: E402
+from parallelkernelbench_b200.parallel import init_context  # noqa: E402
+
+
+def main() -> int:
+    full = "--full" in sys.argv
+    os.environ.setdefault("PKB_HEAP_GIB", "8" if full else "1")
+    ctx = init_context()
+    W, r, dev = ctx.world, ctx.rank, ctx.device
+    if full:
+        cfg = LlamaConfig()
+        steps = 3
+    else:
+        cfg = LlamaConfig(layers=2, hidden=512, ffn=1024, heads=4, kv_heads=2, vocab=1024 * max(W, 1), seq=256)
+        steps = 4
+    g = torch.Generator(device=dev).manual_seed(99 + r)
+    toks = [torch.randint(0, cfg.vocab, (cfg.seq,), device=dev, generator=g) for _ in range(steps)]
+    tgts = [torch.randint(0, cfg.vocab, (cfg.seq,), device=dev, generator=g) for _ in range(steps)]
+    losses, times = {}, {}
+    impls = ["ours"] if full and "--ours-only" in sys.argv else ["ours", "torch"]
+    for impl in impls:
+        model = FSDPLlama(ctx, cfg, impl=impl)
+        ls, ts = [], []
+        for i in range(steps):
+            torch.cuda.synchronize()
+            if W > 1:
+                dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            loss = model.step(toks[i], tgts[i])
+            e1.record()
+            torch.cuda.synchronize()
+            ls.append(float(loss)); ts.append(e0.elapsed_time(e1))
+        losses[impl], times[impl] = ls, ts
+        del model
+        torch.cuda.empty_cache()
+    fails = 0
+    st = nv.read_status()
+    if st[0] != 0:
+        fails += 1
+    if r == 0:
+        for impl in impls:
+            print(f"{impl}: losses {['%.4f' % x for x in losses[impl]]} ms/step {['%.1f' % t for t in times[impl]]}", flush=True)
+    if len(impls) == 2:
+        for a, b in zip(losses["ours"], losses["torch"]):
+            if abs(a - b) > 0.05 * abs(b) + 0.05:
+                fails += 1
+    import math
+    if any(math.isnan(x) for x in losses["ours"]):
+        fails += 1
+    tot = torch.tensor([fails], device=dev)
+    if W > 1:
+        dist.all_reduce(tot)
+    ctx.finalize()
+    if r == 0:
+        print("status", st[:6]); print("TOTAL_FAILS", int(tot.item()), flush=True)
+    return 1 if tot.item() else 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -77,3 +77,36 @@ def test_layernorm_backward_column_reduce():
     dg, db = ln_bwd_colreduce(xh, dy)
     torch.testing.assert_close(dg, (dy.float() * xh.float()).sum(0), atol=1e-2, rtol=1e-3)
     torch.testing.assert_close(db, dy.float().sum(0), atol=1e-2, rtol=1e-3)
+
+
+def test_fsdp_adamw_fp8_matches_dequant_sum_then_adamw():
+    """fp8 slices + scales -> summed gradient -> AdamW -> re-quantised weights, against plain fp32 PyTorch."""
+    from parallelkernelbench_b200.ops import fp8_dequantize_1x128, fp8_quantize_1x128
+    from parallelkernelbench_b200.ops.quant import fsdp_adamw_fp8
+
+    torch.manual_seed(5)
+    W, n = 4, 128 * 257
+    grads = [torch.randn(n, device="cuda") * 0.01 for _ in range(W)]
+    qs = [fp8_quantize_1x128(g.view(-1, 128)) for g in grads]
+    payload = torch.stack([q.view(-1) for q, _ in qs])
+    scales = torch.stack([s.view(-1) for _, s in qs])
+    gsum = sum(fp8_dequantize_1x128(q, s, torch.float32).view(-1) for q, s in qs) / W
+    p = torch.randn(n, device="cuda") * 0.02
+    m, v = torch.randn(n, device="cuda") * 1e-3, torch.rand(n, device="cuda") * 1e-5
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    q_out = torch.empty(n, dtype=torch.uint8, device="cuda")
+    s_out = torch.empty(n // 128, device="cuda")
+    pb = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    lr, b1, b2, eps, wd, step = 1e-3, 0.9, 0.95, 1e-8, 0.1, 3
+    fsdp_adamw_fp8(payload, scales, p, m, v, q_out, s_out, lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                   grad_scale=1.0 / W, step=step, p_bf16=pb)
+    pr.mul_(1 - lr * wd)
+    mr.mul_(b1).add_(gsum, alpha=1 - b1)
+    vr.mul_(b2).addcmul_(gsum, gsum, value=1 - b2)
+    pr.addcdiv_(mr / (1 - b1 ** step), (vr / (1 - b2 ** step)).sqrt() + eps, value=-lr)
+    torch.testing.assert_close(p, pr, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(m, mr, rtol=1e-5, atol=1e-9)
+    torch.testing.assert_close(v, vr, rtol=1e-5, atol=1e-12)
+    torch.testing.assert_close(pb.float(), pr, rtol=1e-2, atol=1e-4)
+    back = fp8_dequantize_1x128(q_out.view(-1, 128), s_out.view(-1, 1), torch.float32).view(-1)
+    torch.testing.assert_close(back, pr, rtol=0.07, atol=2e-3)

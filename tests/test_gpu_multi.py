@@ -81,6 +81,18 @@ def test_ring_attention_multi_rank(nproc):
     _assert_ok(_torchrun("tests/mp/all_ops_worker.py", nproc, "--ops", "ring_attention", "--config", "default", port=29650 + nproc))
 
 
+def test_fsdp_llama_single_rank():
+    _assert_ok(_torchrun("tests/mp/llama_worker.py", 1, port=29606))
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_fsdp_llama_multi_rank(nproc):
+    if _ngpus() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _assert_ok(_torchrun("tests/mp/llama_worker.py", nproc, port=29660 + nproc))
+
+
 def test_harness_eval_on_gpu_single_rank():
     env = dict(os.environ, PKB_LOGS_DIR=os.path.join(ROOT, "logs", "pytest_gpu"), PKB_COOLDOWN_SEC="0")
     r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "eval", "--op", "allreduce",
