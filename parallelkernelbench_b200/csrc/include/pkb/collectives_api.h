@@ -42,6 +42,13 @@ int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, l
 int pkb_coll_row_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long table_off,
                         const void* ids, long long n, long long rows_per_member, long long row_bytes, void* out,
                         int sync, int max_blocks, void* stream);
+// All-to-all with a layout change. Every member stages its whole tensor; member r then copies, from each member g,
+// the box  base_g + r * in_rank_off + i0*in_strides[0] + i1*in_strides[1] + i2*in_strides[2]  (inner_bytes contiguous
+// bytes per index triple, extents[3] triples) to  out + g * out_member_off + i0*out_strides[0] + ... . All in bytes.
+int pkb_coll_a2a_permute(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long stage_off,
+                         long long in_rank_off, const long long* extents, const long long* in_strides,
+                         long long out_member_off, const long long* out_strides, long long inner_bytes, void* out,
+                         int max_blocks, void* stream);
 int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_rows, long long row_bytes,
                           const void* send_counts, const void* send_offsets, unsigned long long stage_off,
                           unsigned long long meta_off, void* out, long long out_capacity_rows,

@@ -263,6 +263,50 @@ coll_row_gather_kernel(const SymmCtx c, const RowGatherArgs a) {
 }
 
 // ================================================================================================
+// all-to-all with a layout change: member g's block for me is a strided box of its staged tensor, and it
+// lands as a strided box of my output (sequence <-> head exchanges, distributed transposes)
+// ================================================================================================
+struct A2APermArgs {
+  const void* src;
+  long long stage_bytes;
+  uint64_t stage_off;
+  long long in_rank_off;     // byte offset of the box addressed to member index r: r * in_rank_off
+  long long n0, n1, n2;      // outer extents of the box
+  long long in_s0, in_s1, in_s2;     // byte strides inside the sender's tensor
+  long long out_member_off;  // byte offset of the box received from member index g: g * out_member_off
+  long long out_s0, out_s1, out_s2;  // byte strides inside the output
+  long long inner_bytes;     // contiguous bytes per (i0, i1, i2)
+  void* out;
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_a2a_perm_kernel(const SymmCtx c, const A2APermArgs a) {
+  if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
+  if (!symm_block_barrier(c, 206, 1)) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long rows = a.n0 * a.n1 * a.n2;
+  const bool vec = ((a.inner_bytes | a.in_rank_off | a.in_s0 | a.in_s1 | a.in_s2 | a.out_member_off | a.out_s0 | a.out_s1 |
+                     a.out_s2 | (long long)a.stage_off | (long long)(uintptr_t)a.out) & 15) == 0;
+  const long long unit = vec ? 16 : 1;
+  const long long upr = a.inner_bytes / unit;   // units per row
+  for (int k = 0; k < c.gsize; ++k) {
+    const int g = (c.grank + k) % c.gsize;      // start with my own box, spread the peers over time
+    const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + (long long)c.grank * a.in_rank_off;
+    uint8_t* to = static_cast<uint8_t*>(a.out) + (long long)g * a.out_member_off;
+    for (long long idx = tid; idx < rows * upr; idx += nthreads) {
+      const long long row = idx / upr, u = idx - row * upr;
+      const long long i2 = row % a.n2, t = row / a.n2, i1 = t % a.n1, i0 = t / a.n1;
+      const long long so = i0 * a.in_s0 + i1 * a.in_s1 + i2 * a.in_s2 + u * unit;
+      const long long dof = i0 * a.out_s0 + i1 * a.out_s1 + i2 * a.out_s2 + u * unit;
+      if (vec) st_global_v4(to + dof, ld_global_v4(from + so));
+      else to[dof] = from[so];
+    }
+  }
+  symm_block_barrier(c, 206, 2);
+}
+
+// ================================================================================================
 // two-shot all-reduce: reduce own slice -> publish -> gather all slices
 // ================================================================================================
 struct TwoShotArgs {
@@ -504,6 +548,22 @@ int pkb_coll_row_gather(const pkb_symm_ctx* h, const void* src, long long stage_
   const long long work = stage_bytes > n * row_bytes ? stage_bytes : n * row_bytes;
   const int grid = grid_for(work, max_blocks);
   coll_row_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_a2a_permute(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long stage_off,
+                         long long in_rank_off, const long long* extents, const long long* in_strides,
+                         long long out_member_off, const long long* out_strides, long long inner_bytes, void* out,
+                         int max_blocks, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(extents && in_strides && out_strides && inner_bytes > 0, "extents, strides and inner_bytes are required");
+  PKB_CHECK_ARG(extents[0] > 0 && extents[1] > 0 && extents[2] > 0, "extents must be positive");
+  A2APermArgs a{src, stage_bytes, stage_off, in_rank_off, extents[0], extents[1], extents[2], in_strides[0], in_strides[1],
+                in_strides[2], out_member_off, out_strides[0], out_strides[1], out_strides[2], inner_bytes, out};
+  const long long moved = extents[0] * extents[1] * extents[2] * inner_bytes * h->gsize;
+  const int grid = grid_for(moved > stage_bytes ? moved : stage_bytes, max_blocks);
+  coll_a2a_perm_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -148,3 +148,27 @@ class RingAttention:
         return out, lse
 
     __call__ = forward
+
+
+def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, *,
+                   causal: bool, scale: float | None = None, q_pos0: int = 0):
+    """Attention backward from a saved forward. ``q, out, dout`` [Sq, Hq, D]; ``k, v`` [Skv, Hkv, D]; ``lse`` [Hq, Sq];
+    query row i sits at global position ``q_pos0 + i``, key row j at position j. Returns fp32 (dq, dk, dv)."""
+    from ..refs.attention import attention_bwd_positions_ref
+
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    Sq, Skv = q.shape[0], k.shape[0]
+    kv_pos = torch.arange(Skv, device=q.device)
+    dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+    step = max(1, min(Sq, (1 << 26) // max(Skv * q.shape[1], 1)))      # bound the score matrix held at once
+    for s0 in range(0, Sq, step):
+        s1 = min(Sq, s0 + step)
+        q_pos = torch.arange(q_pos0 + s0, q_pos0 + s1, device=q.device)
+        a, b, c = attention_bwd_positions_ref(q[s0:s1], k, v, out[s0:s1], lse[:, s0:s1], dout[s0:s1], q_pos, kv_pos, causal, scale)
+        dq[s0:s1] = a
+        dk += b
+        dv += c
+    return dq, dk, dv

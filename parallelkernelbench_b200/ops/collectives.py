@@ -208,6 +208,55 @@ def row_gather(shard: torch.Tensor, ids: torch.Tensor, group: SymmGroup, residen
     return out.view(*ids.shape, *shard.shape[1:])
 
 
+def _collapse(shape, in_st, out_st):
+    """Merge adjacent dimensions that are contiguous in both layouts; returns lists (outermost first)."""
+    dims = [(n, a, b) for n, a, b in zip(shape, in_st, out_st) if n != 1]
+    merged: list[list[int]] = []
+    for n, a, b in dims:
+        if merged and merged[-1][1] == a * n and merged[-1][2] == b * n:
+            merged[-1] = [merged[-1][0] * n, a, b]
+        else:
+            merged.append([n, a, b])
+    return merged
+
+
+def all_to_all_permute(x: torch.Tensor, group: SymmGroup, scatter_dim: int, gather_dim: int) -> torch.Tensor:
+    """Split ``x`` along ``scatter_dim`` into W parts, send part g to member g, and concatenate what arrives along
+    ``gather_dim`` - in one launch, with the layout change done by the peer loads themselves (the reference chunks,
+    exchanges a list and concatenates: reference/33_ulysses_all_to_all_tensor_primitive.py:9-22)."""
+    x = _check(x)
+    W, r = group.size, group.rank_in_group
+    sd, gd = scatter_dim % x.ndim, gather_dim % x.ndim
+    if x.shape[sd] % W != 0:
+        raise ValueError("scatter dimension must be divisible by the group size")
+    es = x.element_size()
+    box = list(x.shape)
+    box[sd] //= W
+    out_shape = list(box)
+    out_shape[gd] *= W
+    out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    in_st = [s * es for s in x.stride()]
+    out_st = [s * es for s in out.stride()]
+    m = _collapse(box, in_st, out_st)
+    inner = es
+    if m and m[-1][1] == es and m[-1][2] == es:
+        inner = m[-1][0] * es
+        m = m[:-1]
+    if len(m) > 3:
+        raise ValueError("layout change needs more than three strided dimensions")
+    while len(m) < 3:
+        m.insert(0, [1, 0, 0])
+    ext = (ctypes.c_longlong * 3)(*[d[0] for d in m])
+    ist = (ctypes.c_longlong * 3)(*[d[1] for d in m])
+    ost = (ctypes.c_longlong * 3)(*[d[2] for d in m])
+    off, stage_bytes = _stage(group, "a2ap_in", x)
+    nv.check(_lib().pkb_coll_a2a_permute(group.ref, nv.ptr(x), nv.c_ll(stage_bytes), ctypes.c_ulonglong(off),
+                                         nv.c_ll(box[sd] * in_st[sd]), ext, ist, nv.c_ll(box[gd] * out_st[gd]), ost,
+                                         nv.c_ll(inner), nv.ptr(out), 0, nv.current_stream()), "pkb_coll_a2a_permute")
+    nv.count_launch()
+    return out
+
+
 def all_to_all_v(x: torch.Tensor, send_counts: torch.Tensor, group: SymmGroup, out_capacity_rows: int,
                  send_offsets: torch.Tensor | None = None, max_send_rows: int | None = None):
     """Variable all-to-all of rows. ``x`` is ``[rows, ...]`` grouped by destination, ``send_counts``

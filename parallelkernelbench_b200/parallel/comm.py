@@ -81,6 +81,29 @@ class Comm:
             return self._C.all_to_all(x, g)
         return self.heap.all_to_all(x, g)
 
+    def all_to_all_permute(self, x: torch.Tensor, scatter_dim: int, gather_dim: int, group=None) -> torch.Tensor:
+        """Split along ``scatter_dim``, exchange, concatenate along ``gather_dim`` (sequence <-> head exchange)."""
+        g = self.group(group)
+        W = self.size(group)
+        if W == 1:
+            return x.contiguous()
+        if self.is_cuda:
+            return self._C.all_to_all_permute(x, g, scatter_dim, gather_dim)
+        parts = torch.stack([c.contiguous() for c in x.chunk(W, dim=scatter_dim)])
+        got = self.heap.all_to_all(parts, g)
+        return torch.cat(list(got.unbind(0)), dim=gather_dim).contiguous()
+
+    def row_gather(self, shard: torch.Tensor, ids: torch.Tensor, group=None) -> torch.Tensor:
+        """Lookup in a table sharded by rows over the group."""
+        g = self.group(group)
+        if self.size(group) == 1:
+            return shard[ids]
+        if self.is_cuda:
+            return self._C.row_gather(shard, ids, g)
+        W = self.size(group)
+        table = self.heap.all_gather(shard.contiguous(), g).reshape(W * shard.shape[0], *shard.shape[1:])
+        return table[ids]
+
     def broadcast(self, x: torch.Tensor, src: int = 0, group=None) -> torch.Tensor:
         g = self.group(group)
         if self.is_cuda:

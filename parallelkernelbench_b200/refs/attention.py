@@ -76,3 +76,30 @@ def cp_attention_reference(q, k, v, positions_of, world: int, rank: int, causal:
         outs.append(o.to(q.dtype))
         lses.append(l)
     return torch.cat(outs), torch.cat(lses, dim=1)
+
+
+def attention_bwd_positions_ref(q, k, v, out, lse, dout, q_pos, kv_pos, causal: bool, scale: float):
+    """Explicit attention backward in fp32 from a saved forward (``out`` [Sq,Hq,D], ``lse`` [Hq,Sq]).
+
+    P = exp(S - lse); dV = P^T dO; dP = dO V^T; dS = P * (dP - rowsum(dO * O)); dQ = dS K * scale; dK = dS^T Q * scale.
+    GQA: the gradients of the query heads that share a KV head are summed. Returns (dq, dk, dv) in fp32.
+    """
+    Hq, Hkv = q.shape[1], k.shape[1]
+    rep = Hq // Hkv
+    qf, of, dof = (t.float().permute(1, 0, 2) for t in (q, out, dout))
+    kf = k.float().permute(1, 0, 2).repeat_interleave(rep, dim=0)
+    vf = v.float().permute(1, 0, 2).repeat_interleave(rep, dim=0)
+    s = torch.einsum("hqd,hkd->hqk", qf, kf) * scale
+    if causal:
+        s = s.masked_fill((kv_pos[None, :] > q_pos[:, None])[None], float("-inf"))
+    p = torch.exp(s - lse.float()[:, :, None])
+    dv = torch.einsum("hqk,hqd->hkd", p, dof)
+    dp = torch.einsum("hqd,hkd->hqk", dof, vf)
+    delta = (dof * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta)
+    dq = torch.einsum("hqk,hkd->hqd", ds, kf) * scale
+    dk = torch.einsum("hqk,hqd->hkd", ds, qf) * scale
+    Skv, D = k.shape[0], k.shape[2]
+    dk = dk.reshape(Hkv, rep, Skv, D).sum(1)
+    dv = dv.reshape(Hkv, rep, Skv, D).sum(1)
+    return dq.permute(1, 0, 2), dk.permute(1, 0, 2), dv.permute(1, 0, 2)
