@@ -274,3 +274,491 @@ register(OpSpec(name="gsplat_projection", problem_ids=(61,), group="wild",
                          "large": {"n_local": 100000, "cams": 2, "width": 1920, "height": 1080}},
                 make_inputs=_gs_inputs, reference=_gs_ref, ours=_gs_ours, atol=1e-5, rtol=1e-5,
                 doc="projection + culling + ordered compaction + peer stores in three launches; pure arithmetic, no graphics API"))
+
+
+# =================================================================================================
+# 62: discrete-continuous convolution on the sphere over a polar x azimuth mesh
+# (reference/62_torchharmonics_spherical_convolution.py)
+# =================================================================================================
+def _disco_mesh(rc: RunCtx):
+    from ..parallel.mesh import Mesh2D
+
+    if "disco_mesh" not in rc.cache:
+        az = 2 if rc.world % 2 == 0 else 1
+        rc.cache["disco_mesh"] = Mesh2D.build(rc.world, az, rc.rank, inner_name="azimuth", outer_name="polar")
+    return rc.cache["disco_mesh"]
+
+
+def _disco_inputs(rc: RunCtx, cfg):
+    m = _disco_mesh(rc)
+    az, pol = m.inner, m.outer
+    B, C, Ksz = cfg["batch"], cfg["chans"], 3
+    nlat = -(-cfg["nlat"] // pol) * pol
+    nlon = -(-2 * nlat // az) * az
+    nlat_l, nlon_l = nlat // pol, nlon // az
+    x = rc.randn(B, C, nlat_l, nlon_l, dtype=torch.float32)
+    weight = rc.randn(C, C, Ksz, dtype=torch.float32, shared=True, salt=1)
+    bias = rc.randn(C, dtype=torch.float32, shared=True, salt=2)
+    # sparse filter: a few entries per (kernel, output latitude) row, columns inside this rank's latitude band
+    E = min(4, nlat_l * nlon)
+    k_idx = torch.arange(Ksz, device=rc.device).view(-1, 1, 1).expand(Ksz, nlat, E)
+    o_idx = torch.arange(nlat, device=rc.device).view(1, -1, 1).expand(Ksz, nlat, E)
+    e_idx = torch.arange(E, device=rc.device).view(1, 1, -1).expand(Ksz, nlat, E)
+    lat_l = (o_idx - m.outer_rank * nlat_l) % nlat_l
+    lon = (o_idx + e_idx * (k_idx + 1)) % nlon
+    cols = (lat_l * nlon + lon).reshape(-1).int()
+    vals = (torch.randn(Ksz * nlat * E, device=rc.device, generator=rc.gen(salt=3)) * 0.05)
+    row_ptr = (torch.arange(Ksz * nlat + 1, device=rc.device) * E).int()
+    return (x, row_ptr, cols, vals, weight, bias, nlat, nlon)
+
+
+def _disco_contract_torch(x, row_ptr, cols, vals, rows, nlon_out):
+    BC, nlat_in, nlon_in = x.shape
+    E = cols.numel() // rows
+    lat = (cols.long() // nlon_in).view(rows, E)
+    lon = (cols.long() % nlon_in).view(rows, E)
+    p = torch.arange(nlon_out, device=x.device) * (nlon_in // nlon_out)
+    y = torch.zeros((BC, rows, nlon_out), dtype=x.dtype, device=x.device)
+    for e in range(E):
+        idx = (lon[:, e, None] + p[None, :]) % nlon_in                   # [rows, P]
+        y += vals.view(rows, E)[:, e].view(1, rows, 1) * x[:, lat[:, e]].gather(2, idx.unsqueeze(0).expand(BC, -1, -1))
+    return y
+
+
+def _disco(rc, x, row_ptr, cols, vals, weight, bias, nlat, nlon, ours):
+    m = _disco_mesh(rc)
+    az, pol = m.inner, m.outer
+    B, C, nlat_l, nlon_l = x.shape
+    Ksz = weight.shape[2]
+    def a2a(t, sd, gd):
+        if az == 1:
+            return t
+        if ours:
+            return rc.comm.all_to_all_permute(t, sd, gd, group=m.inner_ranks)
+        ins = [c.contiguous() for c in t.chunk(az, dim=sd)]
+        outs = [torch.empty_like(ins[0]) for _ in range(az)]
+        if _is_gloo():
+            for i, src in enumerate(m.inner_ranks):
+                buf = torch.stack(ins) if src == rc.rank else torch.empty((az, *ins[0].shape), dtype=t.dtype, device=t.device)
+                dist.broadcast(buf, src, group=m.inner_group)
+                outs[i].copy_(buf[m.inner_rank])
+        else:
+            dist.all_to_all(outs, ins, group=m.inner_group)
+        return torch.cat(outs, dim=gd).contiguous()
+    xt = a2a(x, 1, 3)                                                      # [B, C/az, nlat_l, nlon]
+    Cl = xt.shape[1]
+    rows = Ksz * nlat
+    if ours and rc.dist.is_cuda:
+        from ..ops.wild import disco_contract
+
+        y = disco_contract(xt.reshape(B * Cl, nlat_l, nlon), row_ptr, cols, vals, rows, nlon)
+    else:
+        y = _disco_contract_torch(xt.reshape(B * Cl, nlat_l, nlon), row_ptr, cols, vals, rows, nlon)
+    y = y.view(B, Cl, Ksz, nlat, nlon)
+    if pol > 1:                                                             # sum the latitude-band contributions, keep my band
+        if ours:
+            yl = rc.comm.reduce_scatter(y.permute(3, 0, 1, 2, 4).contiguous(), group=m.outer_ranks).permute(1, 2, 3, 0, 4).contiguous()
+        else:
+            yf = y.contiguous()
+            dist.all_reduce(yf, group=m.outer_group)
+            yl = yf[:, :, :, m.outer_rank * nlat_l:(m.outer_rank + 1) * nlat_l].contiguous()
+    else:
+        yl = y
+    yl = a2a(yl, 4, 1)                                                      # [B, C, K, nlat_l, nlon/az]
+    out = torch.einsum("bckxy,ock->boxy", yl, weight)
+    return out + bias.view(1, -1, 1, 1)
+
+
+register(OpSpec(name="disco_s2_convolution", problem_ids=(62,), group="wild",
+                configs={"default": {"batch": 32, "chans": 8, "nlat": 128}, "small": {"batch": 2, "chans": 4, "nlat": 8}},
+                make_inputs=_disco_inputs, reference=lambda rc, *a: _disco(rc, *a, ours=False), ours=lambda rc, *a: _disco(rc, *a, ours=True),
+                atol=1e-3, rtol=1e-3))
+
+
+# =================================================================================================
+# 63: block Kalman-filter optimiser step in fp64 (reference/63_deepmd_kalman_filter_optimizer.py)
+# =================================================================================================
+def _kalman_inputs(rc: RunCtx, cfg):
+    nb, n = cfg["blocks"], cfg["block"]
+    H = rc.randn(nb, n, 1, dtype=torch.float64) * 0.01
+    w = rc.randn(nb, n, 1, dtype=torch.float64, salt=1)
+    P = torch.eye(n, dtype=torch.float64, device=rc.device).repeat(nb, 1, 1) + 0.01 * rc.randn(nb, n, n, dtype=torch.float64, salt=2)
+    P = 0.5 * (P + P.transpose(1, 2))
+    err = rc.randn(1, dtype=torch.float64, salt=3).reshape(())
+    return (H, err, w, P, 0.98, 0.9987)
+
+
+def _kalman(rc, H, err, w, P, lam, nue, ours):
+    """All blocks batched (the project loops over them); the scalar and the weights cross ranks."""
+    W = rc.world
+    K = torch.bmm(P, H)                                                   # [nb, n, 1]
+    tmp = (lam + torch.bmm(H.transpose(1, 2), K)).sum().reshape(1)
+    if W > 1:
+        tmp = rc.comm.all_reduce(tmp) if ours else _allreduce_ref(tmp)
+    A = 1.0 / tmp
+    w_new = w + A * err * K
+    P_new = (1.0 / lam) * (P - A * torch.bmm(K, K.transpose(1, 2)))
+    if W > 1:
+        allw = rc.comm.all_gather(w_new.contiguous()) if ours else _ag_ref(w_new.contiguous(), W)
+    else:
+        allw = w_new.unsqueeze(0)
+    lam_next = torch.tensor(nue * lam + 1 - nue, dtype=torch.float64, device=H.device)
+    return {"weights": allw.reshape(-1, w.shape[1], 1), "P": P_new, "lambda": lam_next}
+
+
+def _allreduce_ref(t):
+    t = t.clone()
+    dist.all_reduce(t)
+    return t
+
+
+register(OpSpec(name="kalman_filter_step", problem_ids=(63,), group="wild",
+                configs={"default": {"blocks": 8, "block": 1024}, "small": {"blocks": 2, "block": 16}},
+                make_inputs=_kalman_inputs, reference=lambda rc, *a: _kalman(rc, *a, ours=False), ours=lambda rc, *a: _kalman(rc, *a, ours=True),
+                atol=1e-9, rtol=1e-9))
+
+
+# =================================================================================================
+# graph workloads (64-69)
+# =================================================================================================
+def _a2av_ref(x: torch.Tensor, send_counts: torch.Tensor):
+    """Variable all-to-all over the world group with the host round trip the projects pay. Returns (rows, recv_counts)."""
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts)
+    rs, ss = recv_counts.tolist(), send_counts.tolist()
+    out = x.new_empty((sum(rs), *x.shape[1:]))
+    dist.all_to_all_single(out, x.contiguous(), output_split_sizes=rs, input_split_sizes=ss)
+    return out, recv_counts
+
+
+def _heap_copy(rc: RunCtx, name: str, t: torch.Tensor):
+    """A tensor that does not change during the job (graph structure, embedding table), placed in the symmetric heap
+    once so that peers can read it in place."""
+    key = (name, t.data_ptr(), tuple(t.shape))
+    if key not in rc.cache:
+        buf = rc.comm.heap.named((name, tuple(t.shape), str(t.dtype)), t.shape, t.dtype)
+        buf.local.copy_(t)
+        rc.comm.barrier()
+        rc.cache[key] = buf.local
+    return rc.cache[key]
+
+
+def _remote_rows(rc: RunCtx, name: str, table: torch.Tensor, owner: torch.Tensor, local_idx: torch.Tensor) -> torch.Tensor:
+    """``table_of_rank(owner[i])[local_idx[i]]`` for every i: direct peer loads on a GPU, a gather of the tables on CPU."""
+    n = table.shape[0]
+    if rc.world == 1:
+        return table[local_idx]
+    if rc.dist.is_cuda:
+        from ..ops.collectives import row_gather
+
+        return row_gather(_heap_copy(rc, name, table), owner * n + local_idx, rc.comm.group(), resident=True)
+    return rc.comm.row_gather(table, owner * n + local_idx)
+
+
+# ---- 64: two-hop neighbour sampling (reference/64_gnn_neighbor_sampling.py) -----------------------
+def _gnn_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    n = -(-cfg["nodes"] // W) * W
+    deg = cfg["degree"]
+    colptr = torch.arange(n + 1, device=rc.device, dtype=torch.int64) * deg
+    row = ((torch.arange(n, device=rc.device).unsqueeze(1) + torch.arange(1, deg + 1, device=rc.device).unsqueeze(0)) % n).reshape(-1)
+    node_to_rank = torch.arange(n, device=rc.device) % W
+    seeds = (torch.arange(cfg["seeds"], device=rc.device) + rc.rank * cfg["seeds"]) % n
+    return (seeds, list(cfg["fanouts"]), colptr, row.contiguous(), node_to_rank)
+
+
+def _first_seen_unique(node: torch.Tensor, out_node: torch.Tensor):
+    """Unique values of cat(node, out_node) in order of first appearance; also the new ones only."""
+    comb = torch.cat([node, out_node])
+    uniq, inv = torch.unique(comb, return_inverse=True)
+    first = torch.full((uniq.numel(),), comb.numel(), dtype=torch.int64, device=comb.device)
+    first.scatter_reduce_(0, inv, torch.arange(comb.numel(), device=comb.device), reduce="amin")
+    order = first.sort().values
+    allnodes = comb[order]
+    return allnodes[node.numel():], allnodes
+
+
+def _gnn_finish(node, node_dupl, dst_dupl, edges):
+    if node_dupl.numel() == 0:
+        return {"node": node, "row": node.new_empty(0), "col": node.new_empty(0), "edge": edges}
+    assoc = torch.full((int(node.max()) + 1,), -1, dtype=torch.int64, device=node.device)
+    assoc[node] = torch.arange(node.numel(), device=node.device)
+    return {"node": node, "row": assoc[node_dupl], "col": assoc[dst_dupl], "edge": edges}
+
+
+def _gnn_ref(rc, seeds, fanouts, colptr, row, node_to_rank):
+    """Requests routed to the owners, owners sample, replies routed back (five exchanges per hop with host syncs)."""
+    W = rc.world
+    src, node = seeds.clone(), seeds.clone()
+    nd, dd, ed = [seeds.new_empty(0)], [seeds.new_empty(0)], [seeds.new_empty(0)]
+    for k in fanouts:
+        owner = node_to_rank[src]
+        order = torch.argsort(owner, stable=True)
+        req = src[order]
+        if W > 1:
+            got, recv_counts = _a2av_ref(req, torch.bincount(owner, minlength=W))
+        else:
+            got, recv_counts = req, torch.tensor([req.numel()], device=req.device)
+        start = colptr[got]
+        take = torch.clamp(colptr[got + 1] - start, max=k)
+        j = torch.arange(k, device=src.device)[None, :]
+        valid = j < take[:, None]
+        eid = (start[:, None] + j)[valid]
+        nbr = row[eid]
+        if W > 1:
+            bounds = torch.cumsum(recv_counts, 0)
+            seg = torch.searchsorted(bounds, torch.arange(got.numel(), device=src.device), right=True)
+            per_dst = torch.zeros(W, dtype=torch.int64, device=src.device).index_add_(0, seg, take)
+            nbr_b, _ = _a2av_ref(nbr, per_dst)
+            eid_b, _ = _a2av_ref(eid, per_dst)
+            take_b, _ = _a2av_ref(take, recv_counts)
+        else:
+            nbr_b, eid_b, take_b = nbr, eid, take
+        # replies arrive grouped by owner in request order: put them back into the order of `src`
+        take_src = torch.empty_like(take_b)
+        take_src[order] = take_b
+        starts_sorted = torch.cumsum(take_b, 0) - take_b
+        starts_src = torch.empty_like(starts_sorted)
+        starts_src[order] = starts_sorted
+        jj = torch.arange(k, device=src.device)[None, :]
+        vsrc = jj < take_src[:, None]
+        pos = (starts_src[:, None] + jj)[vsrc]
+        out_node, out_edge = nbr_b[pos], eid_b[pos]
+        out_dst = src[:, None].expand(-1, k)[vsrc]
+        if out_node.numel() == 0:
+            break
+        src, node = _first_seen_unique(node, out_node)
+        nd.append(out_node); dd.append(out_dst); ed.append(out_edge)
+    return _gnn_finish(node, torch.cat(nd), torch.cat(dd), torch.cat(ed))
+
+
+def _gnn_ours(rc, seeds, fanouts, colptr, row, node_to_rank):
+    """The requester reads the owner's adjacency in place: per hop two remote row gathers (degree bounds, neighbours),
+    no request/reply exchange and no host round trip for split sizes."""
+    src, node = seeds.clone(), seeds.clone()
+    nd, dd, ed = [seeds.new_empty(0)], [seeds.new_empty(0)], [seeds.new_empty(0)]
+    for k in fanouts:
+        owner = node_to_rank[src]
+        bounds = _remote_rows(rc, "gnn_colptr", colptr, torch.cat([owner, owner]), torch.cat([src, src + 1]))
+        start, end = bounds[:src.numel()], bounds[src.numel():]
+        take = torch.clamp(end - start, max=k)
+        j = torch.arange(k, device=src.device)[None, :]
+        valid = j < take[:, None]
+        eid = (start[:, None] + j)[valid]
+        out_node = _remote_rows(rc, "gnn_row", row, owner[:, None].expand(-1, k)[valid], eid)
+        out_dst = src[:, None].expand(-1, k)[valid]
+        if out_node.numel() == 0:
+            break
+        src, node = _first_seen_unique(node, out_node)
+        nd.append(out_node); dd.append(out_dst); ed.append(eid)
+    return _gnn_finish(node, torch.cat(nd), torch.cat(dd), torch.cat(ed))
+
+
+register(OpSpec(name="gnn_neighbor_sampling", problem_ids=(64,), group="wild",
+                configs={"default": {"nodes": 10000, "degree": 16, "seeds": 512, "fanouts": (10, 5)},
+                         "small": {"nodes": 64, "degree": 4, "seeds": 8, "fanouts": (3, 2)}},
+                make_inputs=_gnn_inputs, reference=_gnn_ref, ours=_gnn_ours, atol=0, rtol=0))
+
+
+# ---- 65 / 66: feature exchange forward and backward -------------------------------------------------
+def _fx_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    R, Hd = cfg["rows_per_peer"], cfg["hidden"]
+    seed_size = max(1, R * W * 3 // 4)
+    return (rc.randn(seed_size, Hd), rc.randint(0, seed_size, (R * W,), salt=1), R)
+
+
+def _rot_dst(j, r, W):
+    return (j + r) % W          # chunk j of rank r goes to rank (j + r) % W and arrives as chunk (r_src - r_dst) % W
+
+
+def _fx_ref(rc, feats, ids, R):
+    W, r = rc.world, rc.rank
+    gathered = feats[ids]
+    if W == 1:
+        return gathered
+    chunks = list(gathered.split(R))
+    send = torch.stack([chunks[(d - r) % W] for d in range(W)])           # indexed by destination
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send)
+    return torch.cat([recv[(j + r) % W] for j in range(W)])               # chunk j came from rank (j + r) % W
+
+
+def _fx_ours(rc, feats, ids, R):
+    """Only the row ids travel ahead (a few KB); the rows are then read from the owners' feature tables straight into
+    their final place, so the gathered copy is never materialised at the source."""
+    W, r = rc.world, rc.rank
+    if W == 1:
+        return feats[ids]
+    all_ids = rc.comm.all_gather(ids.contiguous())                        # [W, W*R]
+    j = torch.arange(W, device=feats.device)
+    s = (j + r) % W                                                        # source of my chunk j
+    js = (r - s) % W                                                       # which of its chunks that is
+    want = all_ids[s[:, None], (js * R)[:, None] + torch.arange(R, device=feats.device)[None, :]]     # [W, R]
+    return rc.comm.row_gather(feats, (s[:, None] * feats.shape[0] + want).reshape(-1))
+
+
+register(OpSpec(name="gnn_feature_exchange", problem_ids=(65,), group="wild",
+                configs={"default": {"rows_per_peer": 128, "hidden": 128}, "small": {"rows_per_peer": 4, "hidden": 8},
+                         "large": {"rows_per_peer": 16384, "hidden": 256}},
+                make_inputs=_fx_inputs, reference=_fx_ref, ours=_fx_ours, atol=0, rtol=0,
+                cost=lambda cfg, W: Cost(nvlink_bytes=cfg["rows_per_peer"] * (W - 1) * cfg["hidden"] * 2)))
+
+
+def _fxb_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    R, Hd = cfg["rows_per_peer"], cfg["hidden"]
+    seed_size = max(1, R * W // 2)
+    return (rc.randn(R * W, Hd, dtype=torch.float32), rc.randint(0, seed_size, (R * W,), salt=1), seed_size, R)
+
+
+def _fxb(rc, grad, ids, seed_size, R, ours):
+    W, r = rc.world, rc.rank
+    if W > 1:
+        chunks = list(grad.split(R))
+        send = torch.stack([chunks[(d - r) % W] for d in range(W)])
+        if ours:
+            recv = rc.comm.all_to_all(send)
+        else:
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send)
+        got = torch.cat([recv[(j + r) % W] for j in range(W)])
+    else:
+        got = grad
+    return torch.zeros((seed_size, grad.shape[1]), dtype=grad.dtype, device=grad.device).index_add_(0, ids, got)
+
+
+register(OpSpec(name="gnn_feature_exchange_backward", problem_ids=(66,), group="wild",
+                configs={"default": {"rows_per_peer": 128, "hidden": 128}, "small": {"rows_per_peer": 4, "hidden": 8}},
+                make_inputs=_fxb_inputs, reference=lambda rc, *a: _fxb(rc, *a, ours=False), ours=lambda rc, *a: _fxb(rc, *a, ours=True),
+                atol=1e-4, rtol=1e-4))
+
+
+# ---- 67: route sparse (index, value) rows to the owner index % W ------------------------------------
+def _se_inputs(rc: RunCtx, cfg):
+    n = -(-cfg["nodes"] // rc.world) * rc.world
+    return (rc.randint(0, n, (cfg["nnz"],)), rc.randn(cfg["nnz"], cfg["hidden"], salt=1))
+
+
+def _se_ref(rc, idx, value):
+    W = rc.world
+    if W == 1:
+        return {"idx": idx, "value": value}
+    owner = idx % W
+    perm = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=W)
+    ri, _ = _a2av_ref(idx[perm], counts)
+    rv, _ = _a2av_ref(value[perm], counts)
+    return {"idx": ri, "value": rv}
+
+
+def _se_ours(rc, idx, value):
+    """Counts stay on the device; index and value rows travel in ONE variable exchange (the index rides in the row)."""
+    W = rc.world
+    if W == 1:
+        return {"idx": idx, "value": value}
+    owner = idx % W
+    perm = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=W)
+    vb = value[perm].contiguous().view(torch.uint8).view(idx.numel(), -1)
+    packed = torch.cat([idx[perm].view(-1, 1).view(torch.uint8).view(idx.numel(), 8), vb], 1).contiguous()
+    cap = idx.numel() * W
+    out, _recv, total = rc.comm.all_to_all_v(packed, counts, cap)
+    n = int(total.item())                                                  # only to trim the result for the comparison
+    out = out[:n]
+    return {"idx": out[:, :8].contiguous().view(torch.int64).view(-1), "value": out[:, 8:].contiguous().view(value.dtype).view(n, -1)}
+
+
+register(OpSpec(name="gnn_sparse_embedding_route", problem_ids=(67,), group="wild",
+                configs={"default": {"nodes": 100000, "nnz": 1024, "hidden": 128}, "small": {"nodes": 64, "nnz": 16, "hidden": 8}},
+                make_inputs=_se_inputs, reference=_se_ref, ours=_se_ours, atol=0, rtol=0))
+
+
+# ---- 68: fetch rows of a sharded table, then project -------------------------------------------------
+def _sf_inputs(rc: RunCtx, cfg):
+    W, S, E = rc.world, cfg["shard_rows"], cfg["dim"]
+    base = torch.arange(cfg["queries"], device=rc.device)
+    ids = ((base + rc.rank) % W) * S + (base * 7 + rc.rank) % S
+    return (rc.randn(S, E), ids, rc.randn(E, E, std=1.0 / math.sqrt(E), shared=True, salt=1))
+
+
+def _sf_ref(rc, shard, ids, proj):
+    W, r, S = rc.world, rc.rank, shard.shape[0]
+    if W == 1:
+        return shard[ids] @ proj
+    owner = (ids // S).clamp(max=W - 1)
+    order = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=W)
+    got, recv_counts = _a2av_ref(ids[order], counts)
+    rows = shard[got - r * S]
+    back, _ = _a2av_ref(rows, recv_counts)
+    return back[torch.argsort(order, stable=True)] @ proj
+
+
+def _sf_ours(rc, shard, ids, proj):
+    """Rows come straight from the owners' shards (the table sits in the symmetric heap for the whole job) and feed the
+    projection GEMM; no request/reply exchange."""
+    W, S = rc.world, shard.shape[0]
+    owner = (ids // S).clamp(max=W - 1)
+    emb = _remote_rows(rc, "sf_table", shard, owner, ids - owner * S)
+    if rc.dist.is_cuda and emb.dtype == torch.bfloat16:
+        key = ("sf_proj_t", proj.data_ptr())
+        if key not in rc.cache:
+            rc.cache[key] = proj.t().contiguous()
+        return _mm_nt(rc, emb, rc.cache[key])
+    return emb @ proj
+
+
+register(OpSpec(name="gnn_sparse_feature_fetch_projection", problem_ids=(68,), group="wild",
+                configs={"default": {"shard_rows": 1 << 20, "dim": 256, "queries": 20000}, "small": {"shard_rows": 64, "dim": 16, "queries": 32},
+                         "full": {"shard_rows": 13875000, "dim": 256, "queries": 20000}},
+                make_inputs=_sf_inputs, reference=_sf_ref, ours=_sf_ours, atol=5e-2, rtol=2e-2,
+                cost=lambda cfg, W: Cost(flops=2.0 * cfg["queries"] * cfg["dim"] ** 2, nvlink_bytes=cfg["queries"] * cfg["dim"] * 2 * (W - 1) / max(W, 1))))
+
+
+# ---- 69: rank of the positive among gathered negatives -----------------------------------------------
+def _ns_inputs(rc: RunCtx, cfg):
+    n = cfg["pos"] + rc.rank % 3
+    return (rc.randn(n), rc.randn(n, cfg["neg"], salt=1))
+
+
+def _ns_ref(rc, pos, neg):
+    W = rc.world
+    if W > 1:
+        sizes = torch.zeros(W, dtype=torch.int64, device=pos.device)
+        sizes[rc.rank] = pos.shape[0]
+        dist.all_reduce(sizes)
+        rs = sizes.tolist()
+        parts_p = [torch.empty(n, dtype=pos.dtype, device=pos.device) for n in rs]
+        parts_n = [torch.empty((n, neg.shape[1]), dtype=neg.dtype, device=pos.device) for n in rs]
+        for s in range(W):                                                 # sizes differ: one broadcast per member
+            if s == rc.rank:
+                parts_p[s].copy_(pos); parts_n[s].copy_(neg)
+            dist.broadcast(parts_p[s], s); dist.broadcast(parts_n[s], s)
+        pos, neg = torch.cat(parts_p), torch.cat(parts_n)
+    scores = torch.sigmoid(torch.cat([pos.view(-1, 1), neg], 1).float())
+    _, order = torch.sort(scores, dim=1, descending=True, stable=True)
+    return torch.nonzero(order == 0)[:, 1] + 1
+
+
+def _ns_ours(rc, pos, neg):
+    """Rank = 1 + number of negatives that beat the positive: counted where the rows live, only the ranks (8 bytes per
+    row instead of the whole score matrix) are gathered, with the row counts carried on the device."""
+    W = rc.world
+    local = 1 + (torch.sigmoid(neg.float()) > torch.sigmoid(pos.float()).view(-1, 1)).sum(1)
+    if W == 1:
+        return local
+    cap = rc.cache.get("ns_cap")
+    if cap is None:
+        cap = rc.cache["ns_cap"] = int(rc.comm.all_reduce(torch.tensor([pos.shape[0]], dtype=torch.int64, device=pos.device), op="max").item())
+    padded = torch.zeros(cap + 1, dtype=torch.int64, device=pos.device)
+    padded[:local.numel()] = local
+    padded[cap] = local.numel()
+    allr = rc.comm.all_gather(padded)                                      # [W, cap + 1]
+    keep = torch.arange(cap, device=pos.device)[None, :] < allr[:, cap:cap + 1]
+    return allr[:, :cap][keep]
+
+
+register(OpSpec(name="gnn_negative_scoring", problem_ids=(69,), group="wild",
+                configs={"default": {"pos": 128, "neg": 1000}, "small": {"pos": 5, "neg": 16}},
+                make_inputs=_ns_inputs, reference=_ns_ref, ours=_ns_ours, atol=0, rtol=0))
