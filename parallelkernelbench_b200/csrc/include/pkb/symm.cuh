@@ -19,10 +19,12 @@
 namespace pkb {
 
 constexpr int kSymmMaxWorld = 16;
-constexpr int kSymmMaxBlocks = 256;
+constexpr int kSymmTableBlocks = 256;  // rows of the per-channel tables
+constexpr int kSymmMaxBlocks = 240;    // largest block index that may take part in a barrier; the last epoch words
+                                       // of a channel hold the state of the grid-wide barrier
 constexpr int kSymmChannels = 32;
-constexpr uint64_t kSymmFlagBytes = (uint64_t)kSymmMaxBlocks * kSymmMaxWorld * 4;  // 16 KiB
-constexpr uint64_t kSymmEpochBytes = (uint64_t)kSymmMaxBlocks * 4;                 // 1 KiB
+constexpr uint64_t kSymmFlagBytes = (uint64_t)kSymmTableBlocks * kSymmMaxWorld * 4;  // 16 KiB
+constexpr uint64_t kSymmEpochBytes = (uint64_t)kSymmTableBlocks * 4;                 // 1 KiB
 constexpr uint64_t kSymmChannelBytes = kSymmFlagBytes + kSymmEpochBytes;
 constexpr uint64_t kSymmCtrlBytes = 1ull << 20;  // user allocations start at 1 MiB
 static_assert(kSymmChannels * kSymmChannelBytes <= kSymmCtrlBytes, "control space too small");
@@ -89,6 +91,73 @@ __device__ __forceinline__ bool symm_block_barrier_at(const SymmCtx& c, int kern
 __device__ __forceinline__ bool symm_block_barrier(const SymmCtx& c, int kernel_id, int site) {
   __shared__ uint32_t s_epoch_static;
   return symm_block_barrier_at(c, kernel_id, site, &s_epoch_static);
+}
+
+// Barrier between ALL blocks of ALL group members: use it when a block reads data that a different block index of a
+// peer wrote in the same launch (stage with a grid-stride loop, then read the peers' staged bytes with another mapping).
+// Every block arrives on a local counter; block 0 waits for the whole grid, does the cross-rank flag exchange of the
+// block barrier (row 0 of the flag table) and then advances a local release word that the other blocks wait on.
+// The whole grid must be resident at once (launch at most one block per SM). Three words at the end of the channel's
+// epoch table hold the state, so grids that use this barrier have at most kSymmGridMaxBlocks blocks.
+constexpr int kSymmGridMaxBlocks = kSymmMaxBlocks;
+constexpr int kSymmGridArriveSlot = 253, kSymmGridErrSlot = 254, kSymmGridReleaseSlot = 255;
+
+__device__ __forceinline__ bool symm_grid_barrier(const SymmCtx& c, int kernel_id, int site) {
+  __shared__ uint32_t s_word;
+  __shared__ int s_ok;
+  const uint64_t chan_off = (uint64_t)c.channel * kSymmChannelBytes;
+  uint32_t* epochs = symm_local<uint32_t>(c, chan_off + kSymmFlagBytes);
+  uint32_t* arrive = epochs + kSymmGridArriveSlot;
+  uint32_t* err = epochs + kSymmGridErrSlot;
+  uint32_t* release = epochs + kSymmGridReleaseSlot;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    s_word = ld_acquire_sys(release);     // cannot advance before this block has arrived
+    s_ok = 1;
+    __threadfence();
+    atomicAdd(arrive, 1u);
+  }
+  __syncthreads();
+  const uint32_t target = s_word + 1u;
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) {
+      if (!wait_flag_ge(arrive, gridDim.x, c.budget_ns)) {
+        s_ok = 0;
+        record_status(c.status, kStatusPeerTimeout, kernel_id, c.rank, c.rank, site, gridDim.x);
+      }
+      *reinterpret_cast<volatile uint32_t*>(arrive) = 0u;
+      const uint32_t e = epochs[0] + 1u;
+      epochs[0] = e;
+      s_word = e;
+    }
+    __syncthreads();
+    const uint32_t e = s_word;
+    if ((int)threadIdx.x < c.gsize && s_ok) {
+      const int peer = c.members[threadIdx.x];
+      fence_acq_rel_sys();
+      st_release_sys(symm_ptr<uint32_t>(c, peer, chan_off) + c.rank, e);
+      const uint32_t* mine = symm_local<uint32_t>(c, chan_off) + peer;
+      if (!wait_flag_ge(mine, e, c.budget_ns)) {
+        s_ok = 0;
+        record_status(c.status, kStatusPeerTimeout, kernel_id, c.rank, peer, site, e);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (!s_ok) *reinterpret_cast<volatile uint32_t*>(err) = target;
+      fence_acq_rel_sys();
+      st_release_sys(release, target);
+    }
+  } else if (threadIdx.x == 0) {
+    if (!wait_flag_ge(release, target, 2 * c.budget_ns)) {
+      s_ok = 0;
+      record_status(c.status, kStatusPeerTimeout, kernel_id, c.rank, c.rank, site + 100, target);
+    } else if (ld_acquire_sys(err) == target) {
+      s_ok = 0;
+    }
+  }
+  __syncthreads();
+  return s_ok != 0;
 }
 
 }  // namespace pkb

@@ -652,7 +652,7 @@ extern "C" int pkb_flash_attn_fwd_ring(const pkb_attn_desc* desc, const pkb_symm
   PKB_CHECK_ARG(d.hq % d.hkv == 0 && d.sq >= 1, "bad attention shape");
   PKB_CHECK_ARG(segs_per_rank >= 1 && seg_rows >= 1 && h->gsize * segs_per_rank <= 16, "at most 16 KV segments");
   PKB_CHECK_ARG(d.skv == h->gsize * segs_per_rank * seg_rows, "desc.skv must cover the gather buffer");
-  PKB_CHECK_ARG(comm_blocks >= 1 && comm_blocks <= kSymmMaxBlocks, "1..256 communication blocks");
+  PKB_CHECK_ARG(comm_blocks >= 1 && comm_blocks <= kSymmMaxBlocks, "1..240 communication blocks");
   PKB_CHECK_ARG((k_gather_off & 1023) == 0 && (v_gather_off & 1023) == 0 && (flags_off & 15) == 0, "heap offsets misaligned");
   PKB_CHECK_ARG(((long long)seg_rows * d.hkv * d.head_dim * 2) % 16 == 0, "segment size must be a multiple of 16 bytes");
   cudaStream_t s = static_cast<cudaStream_t>(stream);

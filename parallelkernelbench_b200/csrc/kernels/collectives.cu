@@ -155,7 +155,7 @@ coll_reduce_kernel(const SymmCtx c, const ReduceArgs a) {
   using Acc = typename P::Acc;
   if (a.stage_elems > 0)
     grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_elems * P::kElem);
-  if (!symm_block_barrier(c, 200, 1)) return;
+  if (!symm_grid_barrier(c, 200, 1)) return;
   if (a.active) {
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -207,7 +207,7 @@ struct GatherArgs {
 __global__ void __launch_bounds__(kCollThreads)
 coll_gather_kernel(const SymmCtx c, const GatherArgs a) {
   if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
-  if (!symm_block_barrier(c, 201, 1)) return;
+  if (!symm_grid_barrier(c, 201, 1)) return;
   if (a.active) {
     int k = 0;
     for (int g = 0; g < c.gsize; ++g) {
@@ -239,7 +239,7 @@ struct RowGatherArgs {
 __global__ void __launch_bounds__(kCollThreads)
 coll_row_gather_kernel(const SymmCtx c, const RowGatherArgs a) {
   if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.table_off), a.src, a.stage_bytes);
-  if (a.sync && !symm_block_barrier(c, 205, 1)) return;
+  if (a.sync && !symm_grid_barrier(c, 207, 1)) return;
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -259,7 +259,7 @@ coll_row_gather_kernel(const SymmCtx c, const RowGatherArgs a) {
       for (long long b = lane; b < a.row_bytes; b += 32) dst[b] = from[b];
     }
   }
-  if (a.sync) symm_block_barrier(c, 205, 2);
+  if (a.sync) symm_block_barrier(c, 207, 2);
 }
 
 // ================================================================================================
@@ -282,7 +282,7 @@ struct A2APermArgs {
 __global__ void __launch_bounds__(kCollThreads)
 coll_a2a_perm_kernel(const SymmCtx c, const A2APermArgs a) {
   if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
-  if (!symm_block_barrier(c, 206, 1)) return;
+  if (!symm_grid_barrier(c, 206, 1)) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const long long rows = a.n0 * a.n1 * a.n2;
@@ -325,7 +325,7 @@ coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
   using P = Pack<DT>;
   using Acc = typename P::Acc;
   if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
-  if (!symm_block_barrier(c, 202, 1)) return;
+  if (!symm_grid_barrier(c, 202, 1)) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   // slices in units of 16-byte vectors; the last member also takes the ragged tail
@@ -356,7 +356,7 @@ coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
       P::store1(symm_local<uint8_t>(c, a.result_off), i, acc);
     }
   }
-  if (!symm_block_barrier(c, 202, 2)) return;
+  if (!symm_grid_barrier(c, 202, 2)) return;
   for (int g = 0; g < c.gsize; ++g) {
     const long long s0 = min(per * g, nvec_total), s1 = min(s0 + per, nvec_total);
     const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.result_off);
@@ -377,7 +377,7 @@ __global__ void __launch_bounds__(kCollThreads)
 coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
   using P = Pack<DT>;
   if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
-  if (!symm_block_barrier(c, 203, 1)) return;
+  if (!symm_grid_barrier(c, 203, 1)) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const long long nvec_total = (a.n + P::kN - 1) / P::kN;  // staging buffers are padded to 16 bytes
@@ -389,7 +389,7 @@ coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
     else v = multimem_ld_reduce_f32x4(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
     multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), v);
   }
-  if (!symm_block_barrier(c, 203, 2)) return;
+  if (!symm_grid_barrier(c, 203, 2)) return;
   if (a.out != nullptr) grid_copy_bytes(a.out, symm_local<uint8_t>(c, a.result_off), a.n * P::kElem);
   symm_block_barrier(c, 203, 3);
 }
@@ -419,7 +419,7 @@ coll_a2av_kernel(const SymmCtx c, const A2AVArgs a) {
     meta[threadIdx.x] = a.send_counts[threadIdx.x];
     meta[kSymmMaxWorld + threadIdx.x] = a.send_offsets[threadIdx.x];
   }
-  if (!symm_block_barrier(c, 204, 1)) return;
+  if (!symm_grid_barrier(c, 204, 1)) return;
   long long out_row = 0;
   for (int g = 0; g < c.gsize; ++g) {
     const long long* meta = symm_ptr<long long>(c, c.members[g], a.meta_off);
@@ -462,7 +462,8 @@ static int grid_for(long long bytes, int max_blocks) {
   long long per_block = (long long)kCollThreads * 16 * 4;
   long long b = (bytes + per_block - 1) / per_block;
   if (b < 1) b = 1;
-  int cap = max_blocks > 0 ? max_blocks : 2 * sm_count();
+  int cap = sm_count();                       // the grid-wide barrier needs every block resident: one block per SM
+  if (max_blocks > 0 && max_blocks < cap) cap = max_blocks;
   if (cap > kSymmMaxBlocks) cap = kSymmMaxBlocks;
   return (int)(b > cap ? cap : b);
 }
@@ -627,7 +628,8 @@ int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_
   A2AVArgs a{src, src_rows, row_bytes, static_cast<const long long*>(send_counts),
              static_cast<const long long*>(send_offsets), stage_off, meta_off, out, out_capacity_rows,
              static_cast<long long*>(recv_counts), static_cast<long long*>(recv_total)};
-  int cap = max_blocks > 0 ? max_blocks : sm_count();
+  int cap = sm_count();
+  if (max_blocks > 0 && max_blocks < cap) cap = max_blocks;
   if (cap > kSymmMaxBlocks) cap = kSymmMaxBlocks;
   coll_a2av_kernel<<<cap, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());

@@ -762,3 +762,284 @@ def _ns_ours(rc, pos, neg):
 register(OpSpec(name="gnn_negative_scoring", problem_ids=(69,), group="wild",
                 configs={"default": {"pos": 128, "neg": 1000}, "small": {"pos": 5, "neg": 16}},
                 make_inputs=_ns_inputs, reference=_ns_ref, ours=_ns_ours, atol=0, rtol=0))
+
+
+# =================================================================================================
+# 70: redistribution of a keyed jagged tensor (reference/70_torchrec_kjt_all2all.py)
+# =================================================================================================
+def _kjt_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    key_splits = [1 + (d % 3) for d in range(W)]
+    F_, B = sum(key_splits), cfg["batch"]
+    lengths = rc.randint(5, 21, (F_ * B,))
+    values = rc.randint(0, 1000000, (int(lengths.sum()),), salt=1)
+    return (lengths, values, key_splits, B)
+
+
+def _segment_permute(data: torch.Tensor, seg_len: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
+    """Concatenate the segments of ``data`` (lengths ``seg_len``) in the order ``order`` - on the device, no Python loop."""
+    starts = torch.cumsum(seg_len, 0) - seg_len
+    new_len = seg_len[order]
+    total = int(new_len.sum())
+    seg_of = torch.repeat_interleave(torch.arange(order.numel(), device=data.device), new_len, output_size=total)
+    new_starts = torch.cumsum(new_len, 0) - new_len
+    return data[starts[order][seg_of] + (torch.arange(total, device=data.device) - new_starts[seg_of])]
+
+
+def _kjt(rc, lengths, values, key_splits, B, ours):
+    W, r = rc.world, rc.rank
+    dev = lengths.device
+    ks = torch.tensor(key_splits, device=dev)
+    len_counts = ks * B                                                    # lengths sent to each destination
+    feat_sum = lengths.view(-1, B).sum(1)                                  # values per feature
+    bounds = torch.cumsum(ks, 0)
+    val_counts = torch.stack([feat_sum[int(b - k):int(b)].sum() for b, k in zip(bounds.tolist(), key_splits)])
+    if W > 1:
+        if ours:
+            cap_l, cap_v = key_splits[r] * B * W, 21 * key_splits[r] * B * W
+            rl, _, tl = rc.comm.all_to_all_v(lengths.view(-1, 1).contiguous(), len_counts, cap_l)
+            rv, _, tv = rc.comm.all_to_all_v(values.view(-1, 1).contiguous(), val_counts, cap_v)
+            rl, rv = rl.view(-1)[:key_splits[r] * B * W], rv.view(-1)[:int(tv.item())]
+        else:
+            rl, _ = _a2av_ref(lengths, len_counts)
+            rv, _ = _a2av_ref(values, val_counts)
+    else:
+        rl, rv = lengths, values
+    local = key_splits[r]
+    # received order is (source rank, feature); the consumer wants (feature, source rank)
+    recat = torch.tensor([f + s * local for f in range(local) for s in range(W)], device=dev)
+    l2 = rl.view(W * local, B)
+    return {"lengths": l2[recat].reshape(-1), "values": _segment_permute(rv, l2.sum(1), recat),
+            "stride": torch.tensor(B * W, device=dev)}
+
+
+register(OpSpec(name="kjt_all_to_all", problem_ids=(70,), group="wild",
+                configs={"default": {"batch": 512}, "small": {"batch": 4}},
+                make_inputs=_kjt_inputs, reference=lambda rc, *a: _kjt(rc, *a, ours=False), ours=lambda rc, *a: _kjt(rc, *a, ours=True),
+                atol=0, rtol=0))
+
+
+# =================================================================================================
+# 71: depthwise causal conv1d with halos from the neighbours, zigzag layout
+# (reference/71_hyena_conv1d_boundary_exchange.py)
+# =================================================================================================
+def _h1_inputs(rc: RunCtx, cfg):
+    return (rc.randn(cfg["batch"], cfg["channels"], 2 * cfg["chunk"]), rc.randn(cfg["channels"], 1, cfg["ksize"], salt=1) * 0.3)
+
+
+def _h1_ref(rc, x, w):
+    W, r = rc.world, rc.rank
+    B, C, L2 = x.shape
+    L, P = L2 // 2, w.shape[-1] - 1
+    ch = x.view(B, C, 2, L)
+    tail_a, tail_b = ch[:, :, 0, L - P:].contiguous(), ch[:, :, 1, L - P:].contiguous()
+    prev_a, next_b = torch.zeros_like(tail_a), tail_a.clone()
+    ops = []
+    if r > 0:
+        ops += [dist.P2POp(dist.irecv, prev_a, r - 1), dist.P2POp(dist.isend, tail_b, r - 1)]
+    if r < W - 1:
+        ops += [dist.P2POp(dist.isend, tail_a, r + 1), dist.P2POp(dist.irecv, next_b, r + 1)]
+    if ops:
+        for q in dist.batch_isend_irecv(ops):
+            q.wait()
+    xs = ch.permute(2, 0, 1, 3).reshape(2 * B, C, L)
+    xp = torch.cat([torch.cat([prev_a, next_b], 0), xs], -1)
+    y = F.conv1d(xp.float(), w.float(), groups=C).to(x.dtype)
+    return y.view(2, B, C, L).permute(1, 2, 0, 3).reshape(B, C, L2)
+
+
+def _h1_ours(rc, x, w):
+    if rc.dist.is_cuda and x.dtype in (torch.bfloat16, torch.float32):
+        from ..ops.wild import halo_conv1d_zigzag
+
+        return halo_conv1d_zigzag(x, w, rc.comm.group())
+    W, r = rc.world, rc.rank
+    B, C, L2 = x.shape
+    L, P = L2 // 2, w.shape[-1] - 1
+    ch = x.view(B, C, 2, L)
+    tails = rc.comm.all_gather(ch[:, :, :, L - P:].contiguous()) if W > 1 else ch[:, :, :, L - P:].unsqueeze(0)
+    prev_a = tails[r - 1][:, :, 0] if r > 0 else torch.zeros_like(tails[0][:, :, 0])
+    next_b = tails[r + 1][:, :, 1] if r < W - 1 else tails[r][:, :, 0]
+    xs = ch.permute(2, 0, 1, 3).reshape(2 * B, C, L)
+    xp = torch.cat([torch.cat([prev_a, next_b], 0), xs], -1)
+    y = F.conv1d(xp.float(), w.float(), groups=C).to(x.dtype)
+    return y.view(2, B, C, L).permute(1, 2, 0, 3).reshape(B, C, L2)
+
+
+register(OpSpec(name="hyena_conv1d_halo", problem_ids=(71,), group="wild",
+                configs={"default": {"batch": 1, "channels": 1024, "chunk": 1024, "ksize": 7}, "small": {"batch": 2, "channels": 8, "chunk": 16, "ksize": 4}},
+                make_inputs=_h1_inputs, reference=_h1_ref, ours=_h1_ours, atol=3e-2, rtol=2e-2,
+                cost=lambda cfg, W: Cost(hbm_bytes=2 * cfg["batch"] * cfg["channels"] * 2 * cfg["chunk"] * 2)))
+
+
+# =================================================================================================
+# 72: Hyena long convolution, sequence <-> channel exchanges around an FFT convolution
+# (reference/72_hyena_forward_cp.py)
+# =================================================================================================
+def _hy_inputs(rc: RunCtx, cfg):
+    C, L, FL = cfg["channels"], cfg["local_seq"], cfg["filter"]
+    h = (torch.arange(C * FL, device=rc.device, dtype=torch.float32).reshape(C, FL) / (C * FL)).to(rc.dtype)
+    bias = (torch.arange(C, device=rc.device, dtype=torch.float32) / C).to(rc.dtype)
+    return (rc.randn(1, C, L), rc.randn(1, C, L, salt=1), rc.randn(1, C, L, salt=2), h, bias)
+
+
+def _zz_index(n: int, device, inverse: bool) -> torch.Tensor:
+    """Chunk order of the zigzag layout: rank r holds chunks (r, n-1-r); ``inverse`` gives natural order from rank order."""
+    half = n // 2
+    idx = torch.empty(n, dtype=torch.long, device=device)
+    idx[0::2] = torch.arange(half, device=device)
+    idx[1::2] = torch.arange(n - 1, half - 1, -1, device=device)
+    return torch.argsort(idx) if inverse else idx
+
+
+def _fftconv(u, kern, bias):
+    L = u.shape[-1]
+    n = 2 * L
+    kf = torch.fft.rfft(kern.float(), n=n) / n
+    y = torch.fft.irfft(torch.fft.rfft(u.float(), n=n) * kf.unsqueeze(0), n=n, norm="forward")[..., :L]
+    return (y + u.float() * bias.float().unsqueeze(-1)).to(u.dtype)
+
+
+def _hyena(rc, x1, x2, v, h, bias, ours):
+    W, r = rc.world, rc.rank
+    B, C, L = x1.shape
+    Cl = C // W
+    def to_full(ts):
+        if W == 1:
+            return list(ts)
+        if ours:                                                           # the three tensors ride in ONE exchange
+            full = rc.comm.all_to_all_permute(torch.stack(ts), 2, 3)      # [3, B, C/W, W*L] in rank order
+            outs = list(full.unbind(0))
+        else:
+            outs = [_a2a_ref(t, 1, 2, W) for t in ts]
+        idx = _zz_index(2 * W, x1.device, True)
+        return [o.reshape(B, Cl, 2 * W, L // 2).index_select(2, idx).reshape(B, Cl, W * L) for o in outs]
+    f1, f2, fv = to_full([x1, x2, v])
+    z = f1 * _fftconv(f2 * fv, h[r * Cl:(r + 1) * Cl, :], bias[r * Cl:(r + 1) * Cl])
+    if W > 1:
+        z = z.reshape(B, Cl, 2 * W, L // 2).index_select(2, _zz_index(2 * W, z.device, False)).reshape(B, Cl, W * L)
+        z = rc.comm.all_to_all_permute(z.contiguous(), 2, 1) if ours else _a2a_ref(z.contiguous(), 2, 1, W)
+    return z.transpose(1, 2).contiguous()
+
+
+register(OpSpec(name="hyena_forward_cp", problem_ids=(72,), group="wild",
+                configs={"default": {"channels": 1024, "local_seq": 2048, "filter": 4096}, "small": {"channels": 8, "local_seq": 16, "filter": 32}},
+                make_inputs=_hy_inputs, reference=lambda rc, *a: _hyena(rc, *a, ours=False), ours=lambda rc, *a: _hyena(rc, *a, ours=True),
+                atol=5e-2, rtol=3e-2))
+
+
+# =================================================================================================
+# 74 / 75: gated delta-rule attention (reference/74_fla_kimi_delta_attention_cp_tp.py,
+# reference/75_fla_gated_deltanet_cp.py)
+# =================================================================================================
+def _delta_recurrence_torch(q, k, v, decay, beta):
+    """q, k [BH,T,K]; v [BH,T,V]; decay [BH,T,K or 1]; beta [BH,T]; the step-by-step form."""
+    BH, T, K = q.shape
+    S = torch.zeros(BH, K, v.shape[-1], dtype=torch.float32, device=q.device)
+    out = torch.empty(BH, T, v.shape[-1], dtype=torch.float32, device=q.device)
+    for t in range(T):
+        S = decay[:, t].unsqueeze(-1) * S
+        u = (v[:, t] - torch.bmm(k[:, t].unsqueeze(1), S).squeeze(1)) * beta[:, t].unsqueeze(-1)
+        S = S + k[:, t].unsqueeze(-1) * u.unsqueeze(1)
+        out[:, t] = torch.bmm(q[:, t].unsqueeze(1), S).squeeze(1)
+    return out
+
+
+def _delta_run(rc, q, k, v, decay, beta, ours):
+    """Inputs [B, T, H, *] -> output [B, T, H, V]."""
+    B, T, H, K = q.shape
+    bh = lambda t: t.float().permute(0, 2, 1, 3).reshape(B * H, T, t.shape[-1]).contiguous()  # noqa: E731
+    args = (bh(q), bh(k), bh(v), bh(decay), beta.float().permute(0, 2, 1).reshape(B * H, T).contiguous())
+    if ours and rc.dist.is_cuda and K in (32, 64, 128, 256):
+        from ..ops.wild import delta_rule_scan
+
+        o = delta_rule_scan(*args)
+    else:
+        o = _delta_recurrence_torch(*args)
+    return o.view(B, H, T, -1).permute(0, 2, 1, 3).contiguous()
+
+
+def _kda_inputs(rc: RunCtx, cfg):
+    T, H, K, V = cfg["local_seq"], cfg["heads"], cfg["k"], cfg["v"]
+    a_log = torch.linspace(-0.1, 0.1, H, device=rc.device).to(rc.dtype)
+    dt_bias = torch.linspace(-0.1, 0.1, H * K, device=rc.device).to(rc.dtype)
+    return (rc.randn(1, T, H, K), rc.randn(1, T, H, K, salt=1), rc.randn(1, T, H, V, salt=2), rc.randn(1, T, H, K, salt=3),
+            rc.randn(1, T, H, salt=4), a_log, dt_bias)
+
+
+def _kda_prep(q, k, g, beta, a_log, dt_bias):
+    H, K = q.shape[2], q.shape[3]
+    decay = torch.exp(-5.0 * torch.sigmoid(a_log.float().exp().view(1, 1, H, 1) * (g.float() + dt_bias.float().view(H, K))))
+    return F.normalize(q.float(), dim=-1) * K ** -0.5, F.normalize(k.float(), dim=-1), decay, beta.float().sigmoid()
+
+
+def _kda_ref(rc, q, k, v, g, beta, a_log, dt_bias):
+    """Every rank gathers the whole sequence and runs the recurrence for all heads, then keeps its rows."""
+    W, r = rc.world, rc.rank
+    T = q.shape[1]
+    if W > 1:
+        gs = lambda t: _ag_ref(t, W).transpose(0, 1).reshape(t.shape[0], W * T, *t.shape[2:])  # noqa: E731
+        q, k, v, g, beta = gs(q), gs(k), gs(v), gs(g), gs(beta)
+    qn, kn, decay, bs = _kda_prep(q, k, g, beta, a_log, dt_bias)
+    out = _delta_run(rc, qn, kn, v, decay, bs, False).to(v.dtype)
+    return out[:, r * T:(r + 1) * T].contiguous()
+
+
+def _kda_ours(rc, q, k, v, g, beta, a_log, dt_bias):
+    """The recurrence is sequential in time but independent per head: one exchange gives every rank H/W heads of the
+    whole sequence (all five inputs packed), the scan kernel runs once per head instead of W times, one exchange back."""
+    W, r = rc.world, rc.rank
+    H, K, V = q.shape[2], q.shape[3], v.shape[3]
+    qn, kn, decay, bs = _kda_prep(q, k, g, beta, a_log, dt_bias)
+    packed = torch.cat([qn, kn, v.float(), decay, bs.unsqueeze(-1)], -1)     # [B, T, H, 3K + V + 1]
+    if W > 1:
+        packed = rc.comm.all_to_all_permute(packed.contiguous(), 2, 1)      # [B, W*T, H/W, .]
+    qn, kn, vv, decay, bs = packed.split([K, K, V, K, 1], -1)
+    out = _delta_run(rc, qn, kn, vv, decay, bs.squeeze(-1), True)
+    if W > 1:
+        out = rc.comm.all_to_all_permute(out.contiguous(), 1, 2)
+    return out.to(v.dtype)
+
+
+register(OpSpec(name="kimi_delta_attention_cp", problem_ids=(74,), group="wild",
+                configs={"default": {"local_seq": 64, "heads": 16, "k": 128, "v": 128}, "small": {"local_seq": 8, "heads": 8, "k": 32, "v": 16}},
+                make_inputs=_kda_inputs, reference=_kda_ref, ours=_kda_ours, atol=3e-2, rtol=3e-2))
+
+
+def _gdn_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    T, K, V = cfg["local_seq"], cfg["k"], cfg["v"]
+    H = -(-cfg["heads"] // W) * W
+    a_log = torch.linspace(-0.1, 0.1, H, device=rc.device).to(rc.dtype)
+    dt_bias = torch.linspace(-0.1, 0.1, H, device=rc.device).to(rc.dtype)
+    return (rc.randn(1, T, H, K), rc.randn(1, T, H, K, salt=1), rc.randn(1, T, H, V, salt=2), rc.randn(1, T, H, salt=3),
+            torch.sigmoid(rc.randn(1, T, H, salt=4).float()).to(rc.dtype), a_log, dt_bias)
+
+
+def _gdn(rc, q, k, v, gate, beta, a_log, dt_bias, ours):
+    W, r = rc.world, rc.rank
+    H, K, V = q.shape[2], q.shape[3], v.shape[3]
+    Hl = H // W
+    if W > 1:
+        if ours:                                                           # five tensors, one exchange
+            packed = torch.cat([q.float(), k.float(), v.float(), gate.float().unsqueeze(-1), beta.float().unsqueeze(-1)], -1)
+            packed = rc.comm.all_to_all_permute(packed.contiguous(), 2, 1)
+            q, k, v, gate, beta = packed.split([K, K, V, 1, 1], -1)
+            gate, beta = gate.squeeze(-1), beta.squeeze(-1)
+        else:
+            q, k, v = (_a2a_ref(t, 2, 1, W) for t in (q, k, v))
+            gate, beta = (_a2a_ref(t.unsqueeze(-1), 2, 1, W).squeeze(-1) for t in (gate, beta))
+    al, db = a_log[r * Hl:(r + 1) * Hl].float(), dt_bias[r * Hl:(r + 1) * Hl].float()
+    qn = F.normalize(q.float(), dim=-1, eps=1e-6) * K ** -0.5
+    kn = F.normalize(k.float(), dim=-1, eps=1e-6)
+    decay = torch.exp(-al.exp().view(1, 1, Hl) * F.softplus(gate.float() + db.view(1, 1, Hl))).unsqueeze(-1)
+    out = _delta_run(rc, qn, kn, v.float(), decay, beta.float(), ours)
+    if W > 1:
+        out = rc.comm.all_to_all_permute(out.contiguous(), 1, 2) if ours else _a2a_ref(out.contiguous(), 1, 2, W)
+    return out.to(v.dtype)
+
+
+register(OpSpec(name="gated_deltanet_cp", problem_ids=(75,), group="wild",
+                configs={"default": {"local_seq": 64, "heads": 6, "k": 256, "v": 512}, "small": {"local_seq": 8, "heads": 4, "k": 32, "v": 16}},
+                make_inputs=_gdn_inputs, reference=lambda rc, *a: _gdn(rc, *a, ours=False), ours=lambda rc, *a: _gdn(rc, *a, ours=True),
+                atol=3e-2, rtol=3e-2))
