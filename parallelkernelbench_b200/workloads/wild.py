@@ -1043,3 +1043,341 @@ register(OpSpec(name="gated_deltanet_cp", problem_ids=(75,), group="wild",
                 configs={"default": {"local_seq": 64, "heads": 6, "k": 256, "v": 512}, "small": {"local_seq": 8, "heads": 4, "k": 32, "v": 16}},
                 make_inputs=_gdn_inputs, reference=lambda rc, *a: _gdn(rc, *a, ours=False), ours=lambda rc, *a: _gdn(rc, *a, ours=True),
                 atol=3e-2, rtol=3e-2))
+
+
+# =================================================================================================
+# 76: conv3d with the input channels sharded, partial outputs summed over the ranks
+# (reference/76_opensora_conv3d_allreduce.py)
+# =================================================================================================
+def _c3_inputs(rc: RunCtx, cfg):
+    cin_l = cfg["cout"] // rc.world
+    x = rc.randn(1, cin_l, cfg["t"], cfg["h"], cfg["w"])
+    w = rc.randn(cfg["cout"], cin_l, 3, 3, 3, salt=1) * (1.0 / math.sqrt(27 * cfg["cout"]))
+    bias = torch.linspace(-0.1, 0.1, cfg["cout"], device=rc.device).to(rc.dtype)
+    return (x, w, bias)
+
+
+def _c3_ref(rc, x, w, bias):
+    out = F.conv3d(x, w)
+    if rc.world > 1:
+        dist.all_reduce(out)
+    return out + bias.view(1, -1, 1, 1, 1)
+
+
+def _c3_ours(rc, x, w, bias):
+    """The convolution as ONE tcgen05 GEMM over unfolded patches ([positions, Cin*27] x [Cout, Cin*27]^T, fp32 out), the
+    partial sums reduced by the all-reduce kernel (in-switch for large tensors) and the bias added on the way out."""
+    Cout, Cin = w.shape[:2]
+    _, _, T, H, Wd = x.shape
+    To, Ho, Wo = T - 2, H - 2, Wd - 2
+    if rc.dist.is_cuda and x.dtype == torch.bfloat16 and (Cin * 27) % 8 == 0:
+        patches = x[0].unfold(1, 3, 1).unfold(2, 3, 1).unfold(3, 3, 1)            # [Cin, To, Ho, Wo, 3, 3, 3]
+        a = patches.permute(1, 2, 3, 0, 4, 5, 6).reshape(To * Ho * Wo, Cin * 27).contiguous()
+        out = _mm_nt(rc, a, w.reshape(Cout, Cin * 27), out_f32=True)               # [positions, Cout]
+        if rc.world > 1:
+            out = rc.comm.all_reduce(out)
+        out = (out + bias.float().view(1, -1)).to(x.dtype)
+        return out.t().reshape(1, Cout, To, Ho, Wo).contiguous()
+    out = F.conv3d(x, w)
+    if rc.world > 1:
+        out = rc.comm.all_reduce(out.contiguous())
+    return out + bias.view(1, -1, 1, 1, 1)
+
+
+register(OpSpec(name="conv3d_allreduce", problem_ids=(76,), group="wild",
+                configs={"default": {"cout": 512, "t": 19, "h": 66, "w": 66}, "small": {"cout": 8, "t": 4, "h": 6, "w": 6}},
+                make_inputs=_c3_inputs, reference=_c3_ref, ours=_c3_ours, atol=5e-2, rtol=3e-2,
+                cost=lambda cfg, W: Cost(flops=2.0 * (cfg["t"] - 2) * (cfg["h"] - 2) * (cfg["w"] - 2) * cfg["cout"] * cfg["cout"] / max(W, 1) * 27,
+                                         nvlink_bytes=2.0 * (W - 1) / max(W, 1) * (cfg["t"] - 2) * (cfg["h"] - 2) * (cfg["w"] - 2) * cfg["cout"] * 2)))
+
+
+# =================================================================================================
+# 77: context-shuffled attention over ranges (reference/77_magi1_cso_async_attention.py)
+# =================================================================================================
+def _cso_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    ranges, spb, D = cfg["ranges"], cfg["spb"], cfg["d"]
+    Hq = -(-cfg["hq"] // W) * W
+    Hkv = cfg["hkv"] if (cfg["hkv"] % W == 0 or W % cfg["hkv"] == 0) else W
+    q = rc.randn(ranges * spb, Hq, D)
+    kv = torch.cat([rc.randn(ranges * spb, Hkv, D, salt=1), rc.randn(ranges * spb, Hkv, D, salt=2)], -1)
+    clip = cfg.get("clip") or W * spb
+    return (q, kv, ranges, min(clip, W * spb))
+
+
+def _cso(rc, q, kv, ranges, clip, ours):
+    W = rc.world
+    tokens, Hq, D = q.shape
+    spb = tokens // ranges
+    if kv.shape[1] < W:
+        kv = kv.repeat_interleave(W // kv.shape[1], dim=1)
+    q4, kv4 = q.view(ranges, spb, Hq, D), kv.reshape(ranges, spb, kv.shape[1], 2 * D)
+    if W > 1:
+        if ours:
+            q4, kv4 = rc.comm.all_to_all_permute(q4.contiguous(), 2, 1), rc.comm.all_to_all_permute(kv4.contiguous(), 2, 1)
+        else:
+            q4, kv4 = _a2a_ref(q4, 2, 1, W), _a2a_ref(kv4, 2, 1, W)
+    kv4 = kv4[:, :clip]
+    k, v = kv4[..., :D].contiguous(), kv4[..., D:].contiguous()
+    if ours and rc.dist.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128):
+        from ..ops.attention import flash_attn_fwd
+
+        o = flash_attn_fwd(q4.contiguous(), k, v, causal=False, scale=D ** -0.5, return_lse=False)[0]   # every range is one batch entry
+    else:
+        rep = q4.shape[2] // k.shape[2]
+        s = torch.einsum("rqhd,rkhd->rhqk", q4.float(), k.float().repeat_interleave(rep, 2)) * D ** -0.5
+        o = torch.einsum("rhqk,rkhd->rqhd", torch.softmax(s, -1), v.float().repeat_interleave(rep, 2)).to(q.dtype)
+    if W > 1:
+        o = rc.comm.all_to_all_permute(o.contiguous(), 1, 2) if ours else _a2a_ref(o.contiguous(), 1, 2, W)
+    return o.reshape(tokens, Hq, D)
+
+
+register(OpSpec(name="cso_range_attention", problem_ids=(77,), group="wild",
+                configs={"default": {"ranges": 4, "spb": 2700, "hq": 48, "hkv": 8, "d": 128}, "small": {"ranges": 2, "spb": 6, "hq": 4, "hkv": 2, "d": 16}},
+                make_inputs=_cso_inputs, reference=lambda rc, *a: _cso(rc, *a, ours=False), ours=lambda rc, *a: _cso(rc, *a, ours=True),
+                atol=3e-2, rtol=3e-2))
+
+
+# =================================================================================================
+# 78: tile-parallel decode with seam blending (reference/78_magi1_tile_parallel_vae_decode.py)
+# =================================================================================================
+def _vae_inputs(rc: RunCtx, cfg):
+    z = torch.randn(1, cfg["c"], cfg["t"], cfg["h"], cfg["w"], device=rc.device, generator=rc.gen(shared=True)).to(torch.bfloat16 if rc.dist.is_cuda else rc.dtype)
+    return (z, cfg["tile_t"], cfg["tile_hw"], cfg["tile_hw"], 0.25, 0.0, cfg["up_s"], cfg["up_t"])
+
+
+def _decode_tile(tile, up_s, up_t):
+    d = F.interpolate(tile.float(), scale_factor=(up_t, up_s, up_s), mode="trilinear", align_corners=False)
+    if d.shape[1] < 3:
+        d = d.repeat(1, -(-3 // d.shape[1]), 1, 1, 1)
+    return d[:, :3].to(tile.dtype)
+
+
+def _blend(prev, cur, extent, dim):
+    extent = min(prev.shape[dim], cur.shape[dim], extent)
+    if extent <= 0:
+        return cur
+    ratio = (torch.arange(extent, device=cur.device, dtype=torch.float32) / extent).view([-1 if i == dim else 1 for i in range(5)])
+    head = prev.narrow(dim, prev.shape[dim] - extent, extent).float() * (1.0 - ratio) + cur.narrow(dim, 0, extent).float() * ratio
+    cur.narrow(dim, 0, extent).copy_(head.to(cur.dtype))
+    return cur
+
+
+def _vae(rc, z, tl, th, tw, sp_ov, t_ov, up_s, up_t, ours):
+    W, r = rc.world, rc.rank
+    st, sh, sw = int(tl * (1 - t_ov)), int(th * (1 - sp_ov)), int(tw * (1 - sp_ov))
+    rt, rh, rw = tl * up_t, th * up_s, tw * up_s
+    bt, bh, bw = int(rt * t_ov), int(rh * sp_ov), int(rw * sp_ov)
+    nt, nh, nw = -(-z.shape[2] // st), -(-z.shape[3] // sh), -(-z.shape[4] // sw)
+    tiles = [(a, b, c) for a in range(nt) for b in range(nh) for c in range(nw)]
+    lat = [z[:, :, a * st:a * st + tl, b * sh:b * sh + th, c * sw:c * sw + tw] for a, b, c in tiles]
+    order = sorted(range(len(tiles)), key=lambda i: lat[i].numel(), reverse=True)
+    per_rank = [order[s::W] for s in range(W)]
+    def shape_dec(i):
+        return (1, 3, lat[i].shape[2] * up_t, lat[i].shape[3] * up_s, lat[i].shape[4] * up_s)
+    def gather(local, shapes_of):
+        """Every rank ends up with every tile. All sizes follow from the tiling, so no shape exchange is needed."""
+        if W == 1:
+            return {i: t for i, t in zip(per_rank[0], local)}
+        flat = torch.cat([t.reshape(-1) for t in local]) if local else z.new_empty(0)
+        sizes = [sum(math.prod(shapes_of(i)) for i in per_rank[s]) for s in range(W)]
+        cap = max(sizes)
+        buf = torch.zeros(cap, dtype=flat.dtype, device=flat.device)
+        buf[:flat.numel()] = flat
+        allb = rc.comm.all_gather(buf) if ours else _ag_ref(buf, W)
+        out = {}
+        for s in range(W):
+            o = 0
+            for i in per_rank[s]:
+                n = math.prod(shapes_of(i))
+                out[i] = allb[s, o:o + n].view(shapes_of(i))
+                o += n
+        return out
+    dec = gather([_decode_tile(lat[i], up_s, up_t) for i in per_rank[r]], shape_dec)
+    idx_of = {t: i for i, t in enumerate(tiles)}
+    blended = []
+    for i in per_rank[r]:
+        a, b, c = tiles[i]
+        cur = dec[i].clone()
+        if a > 0:
+            cur = _blend(dec[idx_of[(a - 1, b, c)]], cur, bt, 2)
+        if b > 0:
+            cur = _blend(dec[idx_of[(a, b - 1, c)]], cur, bh, 3)
+        if c > 0:
+            cur = _blend(dec[idx_of[(a, b, c - 1)]], cur, bw, 4)
+        blended.append(cur[:, :, :rt - bt, :rh - bh, :rw - bw].contiguous())
+    def shape_bl(i):
+        s = shape_dec(i)
+        return (1, 3, min(s[2], rt - bt), min(s[3], rh - bh), min(s[4], rw - bw))
+    allb = gather(blended, shape_bl)
+    return torch.cat([torch.cat([torch.cat([allb[idx_of[(a, b, c)]] for c in range(nw)], 4) for b in range(nh)], 3) for a in range(nt)], 2)
+
+
+register(OpSpec(name="tile_parallel_vae_decode", problem_ids=(78,), group="wild",
+                configs={"default": {"c": 16, "t": 6, "h": 90, "w": 90, "tile_t": 3, "tile_hw": 32, "up_s": 8, "up_t": 4},
+                         "small": {"c": 4, "t": 4, "h": 10, "w": 10, "tile_t": 2, "tile_hw": 4, "up_s": 2, "up_t": 2}},
+                make_inputs=_vae_inputs, reference=lambda rc, *a: _vae(rc, *a, ours=False), ours=lambda rc, *a: _vae(rc, *a, ours=True),
+                atol=2e-2, rtol=2e-2))
+
+
+# =================================================================================================
+# 79: distributed k-nearest-neighbour search (reference/79_dinov2_distributed_knn.py)
+# =================================================================================================
+def _knn_inputs(rc: RunCtx, cfg):
+    Q, N, D = cfg["queries"], cfg["train"], cfg["d"]
+    test = F.normalize(rc.randn(Q, D, dtype=torch.float32), dim=1).to(rc.dtype)
+    train = F.normalize(rc.randn(N, D, dtype=torch.float32, salt=1), dim=1).to(rc.dtype)
+    labels = (rc.rank * N + torch.arange(N, device=rc.device)) % cfg["classes"]
+    return (test, train.t().contiguous(), labels.view(1, N), min(cfg["k"], N), cfg["classes"])
+
+
+def _knn_votes(sims, labels, classes):
+    votes = torch.zeros((sims.shape[0], classes), dtype=torch.float32, device=sims.device)
+    votes.scatter_add_(1, labels, torch.ones_like(sims, dtype=torch.float32))
+    return {"sims": sims.float(), "votes": votes / sims.shape[1]}
+
+
+def _knn_ref(rc, test, train_t, labels, k, classes):
+    """One round per owner: broadcast its queries, local similarity + top-k everywhere, gather on the owner, merge."""
+    W, r = rc.world, rc.rank
+    result = None
+    for owner in range(W):
+        qs = test.clone()
+        if W > 1:
+            dist.broadcast(qs, owner)
+        sims, idx = (qs.float() @ train_t.float()).topk(k, dim=1)
+        lab = labels.expand(qs.shape[0], -1).gather(1, idx)
+        if W > 1:
+            gs = [torch.empty_like(sims) for _ in range(W)] if r == owner else None
+            gl = [torch.empty_like(lab) for _ in range(W)] if r == owner else None
+            dist.gather(sims, gs, dst=owner)
+            dist.gather(lab, gl, dst=owner)
+            if r == owner:
+                s_all, l_all = torch.cat(gs, 1), torch.cat(gl, 1)
+                top, ti = s_all.topk(k, dim=1)
+                result = (top, l_all.gather(1, ti))
+        else:
+            result = (sims, lab)
+    return _knn_votes(result[0], result[1], classes)
+
+
+def _knn_ours(rc, test, train_t, labels, k, classes):
+    """All queries of all ranks at once: one gather, ONE GEMM against the local shard, one top-k, one exchange that
+    hands every owner its W candidate lists (similarity and label packed together), one merge."""
+    W, r = rc.world, rc.rank
+    Q = test.shape[0]
+    allq = rc.comm.all_gather(test.contiguous()).reshape(W * Q, -1) if W > 1 else test
+    if rc.dist.is_cuda and test.dtype == torch.bfloat16:
+        from ..ops import gemm_bf16_kn
+
+        sim = gemm_bf16_kn(allq.contiguous(), train_t.contiguous(), out_dtype=torch.float32)
+    else:
+        sim = allq.float() @ train_t.float()
+    sims, idx = sim.topk(k, dim=1)
+    lab = labels.expand(sims.shape[0], -1).gather(1, idx)
+    if W > 1:
+        packed = torch.stack([sims.float(), lab.float()], -1).view(W, Q, k, 2).contiguous()
+        got = rc.comm.all_to_all(packed)                                      # [W(source), Q, k, 2] for my queries
+        s_all = got[..., 0].permute(1, 0, 2).reshape(Q, W * k)
+        l_all = got[..., 1].permute(1, 0, 2).reshape(Q, W * k).long()
+        sims, ti = s_all.topk(k, dim=1)
+        lab = l_all.gather(1, ti)
+    return _knn_votes(sims, lab, classes)
+
+
+register(OpSpec(name="distributed_knn", problem_ids=(79,), group="wild",
+                configs={"default": {"queries": 32, "train": 2048, "d": 384, "k": 200, "classes": 1000},
+                         "small": {"queries": 4, "train": 64, "d": 16, "k": 5, "classes": 10}},
+                make_inputs=_knn_inputs, reference=_knn_ref, ours=_knn_ours, atol=2e-2, rtol=2e-2))
+
+
+# =================================================================================================
+# 80: Sinkhorn-Knopp normalisation with the batch sharded (reference/80_dinov2_distributed_sinkhorn_knopp.py)
+# =================================================================================================
+def _sk_inputs(rc: RunCtx, cfg):
+    return (rc.randn(cfg["batch"], cfg["prototypes"], dtype=torch.float32) * 0.01, 0.07, 3)
+
+
+def _sk_ref(rc, t, temp, iters):
+    W = rc.world
+    ar = (lambda x: _allreduce_ref(x)) if W > 1 else (lambda x: x)
+    q = torch.exp(t.float() / temp).T.contiguous()
+    total_batch = ar(torch.tensor([float(t.shape[0])], device=t.device))
+    P = q.shape[0]
+    q /= ar(q.sum().reshape(1))
+    for _ in range(iters):
+        q /= ar(q.sum(dim=1, keepdim=True))
+        q /= P
+        q /= q.sum(dim=0, keepdim=True)
+        q /= total_batch
+    q *= total_batch
+    return q.T.contiguous()
+
+
+def _sk_ours(rc, t, temp, iters):
+    """The matrix is never rewritten: a row scale per prototype and a column scale per sample carry the iterations, each
+    of which is two matrix-vector passes over exp(t/temp) and one small all-reduce; the result is written once."""
+    W = rc.world
+    ar = (lambda x: rc.comm.all_reduce(x)) if W > 1 else (lambda x: x)
+    E = torch.exp(t.float() / temp)                                           # [B, P]
+    B, P = E.shape
+    head = ar(torch.stack([torch.tensor(float(B), device=t.device), E.sum()]))   # batch size and mass in one exchange
+    total_batch, mass = head[0], head[1]
+    r = torch.ones(P, device=t.device)
+    c = torch.full((B,), 1.0, device=t.device) / mass
+    for _ in range(iters):
+        R = ar((r * torch.mv(E.t(), c)).contiguous())
+        r = r / R / P
+        c = c / (c * torch.mv(E, r)) / total_batch
+    return E * r.view(1, P) * (c * total_batch).view(B, 1)
+
+
+register(OpSpec(name="sinkhorn_knopp", problem_ids=(80,), group="wild",
+                configs={"default": {"batch": 1024, "prototypes": 16384}, "small": {"batch": 8, "prototypes": 32}},
+                make_inputs=_sk_inputs, reference=_sk_ref, ours=_sk_ours, atol=1e-7, rtol=1e-3))
+
+
+# =================================================================================================
+# 81: gather of object masks and IoU suppression (reference/81_sam3_allgather_iou_suppression.py)
+# =================================================================================================
+def _sam_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    counts = [1 + ((i + rc.trial) % 3) for i in range(W)]
+    n, H, Wd = counts[rc.rank], cfg["h"], cfg["w"]
+    yy = torch.arange(H, device=rc.device).view(1, H, 1)
+    xx = torch.arange(Wd, device=rc.device).view(1, 1, Wd)
+    cc = torch.arange(n, device=rc.device).view(n, 1, 1)
+    masks = rc.randn(n, H, Wd) + (((yy + xx + cc + rc.rank) % 5 == 0).to(rc.dtype) * 4.0 - 1.0)
+    scores = torch.linspace(-5.0, 5.0, n, device=rc.device).to(rc.dtype)
+    last = (torch.arange(sum(counts), device=rc.device) % 5) - 1
+    return (masks, scores, counts, last, 0.7)
+
+
+def _sam(rc, masks, scores, counts, last, thr, ours):
+    W = rc.world
+    cap = max(counts)
+    def gv(t):
+        if W == 1:
+            return t.float()
+        pad = torch.zeros((cap, *t.shape[1:]), dtype=torch.float32, device=t.device)
+        pad[:t.shape[0]] = t.float()
+        allp = rc.comm.all_gather(pad) if ours else _ag_ref(pad, W)
+        return torch.cat([allp[s, :counts[s]] for s in range(W)])
+    mg, sg = gv(masks), gv(scores)
+    n = mg.shape[0]
+    b = (mg > 0).flatten(1).float()
+    inter = b @ b.t()
+    area = b.sum(1)
+    iou = inter / (area[:, None] + area[None, :] - inter).clamp_min(1.0)
+    over = torch.triu(iou >= thr, diagonal=1)
+    li, lj = last.view(n, 1), last.view(1, n)
+    sup = (over & (li > lj) & (lj > -1)).any(1) | (over & (lj > li) & (li > -1)).any(0)
+    mg = mg.clone()
+    mg[sup] = -10.0
+    return {"masks": mg, "scores": sg, "suppressed": sup}
+
+
+register(OpSpec(name="mask_iou_suppression", problem_ids=(81,), group="wild",
+                configs={"default": {"h": 256, "w": 256}, "small": {"h": 8, "w": 8}},
+                make_inputs=_sam_inputs, reference=lambda rc, *a: _sam(rc, *a, ours=False), ours=lambda rc, *a: _sam(rc, *a, ours=True),
+                atol=1e-5, rtol=1e-5))
