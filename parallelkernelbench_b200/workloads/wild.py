@@ -1709,3 +1709,51 @@ register(OpSpec(name="importance_sampling_loss", problem_ids=(25,), group="wild"
                 configs={"default": {"tokens": 1024, "hidden": 1024, "vocab": 32000}, "small": {"tokens": 32, "hidden": 16, "vocab": 64}},
                 make_inputs=_isl_inputs, reference=_isl_ref, ours=_isl_ours, atol=5e-2, rtol=5e-2,
                 cost=lambda cfg, W: Cost(flops=2.0 * cfg["tokens"] * cfg["hidden"] * cfg["vocab"])))
+
+
+# =================================================================================================
+# 73: vocabulary-parallel cross-entropy (reference/73_vocab_parallel_cross_entropy_loss.py)
+# =================================================================================================
+def _vce_inputs(rc: RunCtx, cfg):
+    W = rc.world
+    Vl = cfg["vocab"] // W
+    return (rc.randn(cfg["batch"], cfg["seq"], Vl), rc.randint(0, Vl * W, (cfg["batch"], cfg["seq"]), shared=True, salt=1))
+
+
+def _vce_ref(rc, logits, target):
+    """Three all-reduces (max, target logit, sum of exponentials), fp32 math on a copy of the logits."""
+    W, r = rc.world, rc.rank
+    lg = logits.float()
+    Vl = lg.shape[-1]
+    ar = (lambda t, op=dist.ReduceOp.SUM: (dist.all_reduce(t, op=op), t)[1]) if W > 1 else (lambda t, op=None: t)
+    mx = ar(lg.max(-1).values, dist.ReduceOp.MAX)
+    lg = lg - mx.unsqueeze(-1)
+    out_of_range = (target < r * Vl) | (target >= (r + 1) * Vl)
+    local_t = (target - r * Vl).masked_fill(out_of_range, 0)
+    pred = ar(lg.gather(-1, local_t.unsqueeze(-1)).squeeze(-1).masked_fill(out_of_range, 0.0))
+    return torch.log(ar(torch.exp(lg).sum(-1))) - pred
+
+
+def _vce_ours(rc, logits, target):
+    if rc.dist.is_cuda and logits.dtype in (torch.bfloat16, torch.float32):
+        from ..ops import vocab_parallel_cross_entropy
+
+        return vocab_parallel_cross_entropy(logits, target, rc.comm)
+    W, r = rc.world, rc.rank
+    lg = logits.float()
+    Vl = lg.shape[-1]
+    mx = lg.max(-1).values
+    se = torch.exp(lg - mx.unsqueeze(-1)).sum(-1)
+    out_of_range = (target < r * Vl) | (target >= (r + 1) * Vl)
+    tg = lg.gather(-1, (target - r * Vl).masked_fill(out_of_range, 0).unsqueeze(-1)).squeeze(-1).masked_fill(out_of_range, 0.0)
+    st = torch.stack([mx, se, tg], -1)
+    allst = rc.comm.all_gather(st.contiguous()) if W > 1 else st.unsqueeze(0)     # ONE packed exchange
+    gmax = allst[..., 0].max(0).values
+    return torch.log((allst[..., 1] * torch.exp(allst[..., 0] - gmax)).sum(0)) + gmax - allst[..., 2].sum(0)
+
+
+register(OpSpec(name="vocab_parallel_cross_entropy", problem_ids=(73,), group="wild",
+                configs={"default": {"batch": 8, "seq": 1024, "vocab": 512}, "small": {"batch": 2, "seq": 8, "vocab": 32},
+                         "llama": {"batch": 1, "seq": 4096, "vocab": 128256}},
+                make_inputs=_vce_inputs, reference=_vce_ref, ours=_vce_ours, atol=2e-2, rtol=2e-2,
+                cost=lambda cfg, W: Cost(hbm_bytes=cfg["batch"] * cfg["seq"] * cfg["vocab"] / max(W, 1) * 2)))

@@ -61,3 +61,22 @@ def test_rank_that_exits_nonzero_is_reported():
 def test_unknown_op_is_a_clean_failure():
     r, js = _launch("run", "--op", "no_such_op", "--nproc", "1", "--backend", "gloo")
     assert r.returncode != 0
+
+
+def test_project_derived_and_sequence_parallel_ops_world2_gloo():
+    """Every op of the 'ulysses' and 'wild' groups and the 2-D mesh attention blocks: ours (host shared-memory backend,
+    PyTorch math) against the process-group restatement, two CPU ranks, fp32."""
+    import subprocess
+    import sys
+
+    from parallelkernelbench_b200.workloads import registry
+
+    names = [s.name for s in registry.all_ops() if s.group in ("ulysses", "wild")] + ["ring_attention_tp", "ring_attention_pp",
+                                                                                       "ring_attention_backward_dp"]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29577", os.path.join(root, "tests", "mp", "all_ops_worker.py"), "--backend", "gloo", "--dtype", "float32",
+           "--ops", ",".join(names)]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
+    assert r.stdout.count("PASS rank0") >= len(names)
