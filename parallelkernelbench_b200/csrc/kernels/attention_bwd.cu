@@ -1,0 +1,503 @@
+// Flash-attention backward on tcgen05 / TMEM.
+//
+// One CTA owns one 128-row KV tile of one KV head and walks every (query head of the group, 128-row Q tile) pair
+// that can see it. Per pair, from the saved forward (O, log-sum-exp):
+//     S  = Q K^T                         (tensor core, TMEM)
+//     dP = dO V^T                        (tensor core, TMEM)
+//     P  = exp2(S * scale * log2e - lse2)            dS = P * (dP - delta) * scale     (softmax warps, thread = q row)
+//     dV += P^T dO     dK += dS^T Q      (tensor core, accumulate in TMEM over the whole walk - no atomics, GQA summed)
+//     dQ_partial = dS K                  (tensor core, into the TMEM columns S has just left) -> fp32 vector `red` into dQ
+// delta = rowsum(dO * O) and lse2 = lse * log2e come from a small pre-kernel.
+//
+//   warp 0      TMA producer: K_j, V_j once; Q_i and dO_i per step
+//   warp 1      MMA issuer
+//   warps 4-7   softmax / dS (thread = q row): read S and dP from TMEM, write P and dS as bf16 into 128-byte-swizzled
+//               shared memory; the same [q][kv] tiles serve as K-major A (dS for dQ) and as MN-major A (P^T, dS^T)
+//   warps 8-15  dQ drain (thread = q row, two warpgroups take half of the D columns each), and at the end dV, dK
+// K_j ([kv][d]) is the K-major B operand of S and the MN-major B operand of dQ; Q_i and dO_i are K-major A operands of
+// S / dP and MN-major B operands of dK / dV: every tile is loaded once and read through two descriptors.
+//
+// Positions follow the forward kernel's segment description, so causal masks in context-parallel (zigzag) layouts are
+// exact. Reference behaviour replaced: materialised fp32 scores and their softmax per ring step
+// (reference: reference/57_ring_attention_backward_dp.py:39-69).
+#include "pkb/api.h"
+#include "pkb/attention_api.h"
+#include "pkb/host.h"
+#include "pkb/ptx.cuh"
+
+namespace pkb {
+
+constexpr int kFbThreads = 512;
+constexpr int kFbTile = 128;
+constexpr float kFbLog2e = 1.4426950408889634f;
+
+struct FaBwdParams {
+  pkb_attn_desc d;
+  const float* lse2;    // [batch, hq, sq]  log-sum-exp in base-2 units
+  const float* delta;   // [batch, hq, sq]  rowsum(dO * O)
+  float* dq;            // [batch * sq, hq, D] fp32, zero-initialised by the caller
+  float* dk;            // [batch * skv, hkv, D] fp32
+  float* dv;            // [batch * skv, hkv, D] fp32
+  uint32_t* status;
+  uint64_t budget_ns;
+};
+
+template <int D>
+struct FbSmem {
+  static constexpr int kTileBytes = kFbTile * D * 2;
+  static constexpr int kPBytes = kFbTile * kFbTile * 2;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTileBytes;
+  static constexpr int kQ = kV + kTileBytes;
+  static constexpr int kDO = kQ + kTileBytes;
+  static constexpr int kP = kDO + kTileBytes;
+  static constexpr int kDS = kP + kPBytes;
+  static constexpr int kBars = kDS + kPBytes;
+  static constexpr int kTotal = kBars + 256;
+};
+
+// delta[b,h,s] = sum_d dO * O ; lse2 = lse * log2(e). One warp per (token, head).
+__global__ void __launch_bounds__(256)
+fa_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout, const float* __restrict__ lse,
+                   float* __restrict__ delta, float* __restrict__ lse2, int batch, int sq, int hq, int D) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const long long total = (long long)batch * sq * hq;
+  for (long long i = warp; i < total; i += nwarps) {
+    const int h = (int)(i % hq);
+    const long long tok = i / hq;                 // batch * sq + s
+    const __nv_bfloat16* op = o + (tok * hq + h) * D;
+    const __nv_bfloat16* dp = dout + (tok * hq + h) * D;
+    float acc = 0.f;
+    for (int c = lane; c < D; c += 32) acc += __bfloat162float(op[c]) * __bfloat162float(dp[c]);
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const int b = (int)(tok / sq), s = (int)(tok % sq);
+      const long long idx = ((long long)b * hq + h) * sq + s;
+      delta[idx] = acc;
+      lse2[idx] = lse[idx] * kFbLog2e;
+    }
+  }
+}
+
+__device__ __forceinline__ void red_add_v4_f32(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+// Position of Q row `row` (inside one batch entry) and whether the 128-row tile starting there can see kv position kp0.
+__device__ __forceinline__ int fb_q_pos(const pkb_attn_desc& d, int row) {
+  const int seg = row / d.q_seg_rows;
+  return d.q_seg_pos[seg] + (row - seg * d.q_seg_rows);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFbThreads, 1)
+fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+              const FaBwdParams p) {
+  using S = FbSmem<D>;
+  constexpr int kAtoms = D / 64;
+  constexpr int kAtomBytes = kFbTile * 128;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = smem_u32(smem);
+  const pkb_attn_desc& d = p.d;
+
+  const uint32_t bar0 = sb + S::kBars;
+  const uint32_t kv_full = bar0;
+  const uint32_t qdo_full = bar0 + 8;
+  const uint32_t qdo_empty = bar0 + 16;
+  const uint32_t sdp_full = bar0 + 24;    // S and dP in TMEM
+  const uint32_t pds_full = bar0 + 32;    // P and dS in shared memory (and S, dP read out of TMEM)
+  const uint32_t pds_empty = bar0 + 40;   // the MMAs that read P and dS are complete
+  const uint32_t dq_full = bar0 + 48;     // dQ partial in TMEM
+  const uint32_t dq_empty = bar0 + 56;    // dQ partial drained: the S columns may be overwritten
+  const uint32_t acc_full = bar0 + 64;    // dV and dK final
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 10);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rep = d.hq / d.hkv;
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+
+  // which KV tile: heavy tiles (early positions see the most queries under a causal mask) come first in launch order
+  int kv_row0 = 0, kv_pos0 = 0, kv_valid = 0;
+  {
+    int t = blockIdx.x;
+    bool found = false;
+    for (int seg = 0; seg < d.num_kv_segs && !found; ++seg) {
+      const int nt = (d.kv_seg_len[seg] + kFbTile - 1) / kFbTile;
+      if (t < nt) {
+        kv_row0 = d.kv_seg_row0[seg] + t * kFbTile;
+        kv_pos0 = d.kv_seg_pos0[seg] + t * kFbTile;
+        kv_valid = min(kFbTile, d.kv_seg_len[seg] - t * kFbTile);
+        found = true;
+      }
+      t -= nt;
+    }
+    if (!found) return;   // uniform over the CTA: nothing allocated yet
+  }
+  // Active Q tiles: inside a segment positions grow, so under a causal mask the tiles that can see this KV tile are a
+  // suffix of every segment. seg_first / seg_cnt (shared memory, filled below) turn a step index into a tile in O(segments).
+  int* seg_first = reinterpret_cast<int*>(smem + S::kBars + 8 * 12);
+  int* seg_cnt = seg_first + 16;
+  int* n_active_s = seg_cnt + 16;
+  const int tiles_per_seg = d.num_q_segs == 1 ? (d.sq + kFbTile - 1) / kFbTile : d.q_seg_rows / kFbTile;
+  const int rows_per_seg = d.num_q_segs == 1 ? d.sq : d.q_seg_rows;
+  if (threadIdx.x == 0) {
+    int total = 0;
+    for (int sg = 0; sg < d.num_q_segs; ++sg) {
+      int first = 0;
+      if (d.causal) {
+        while (first < tiles_per_seg && d.q_seg_pos[sg] + min(first * kFbTile + kFbTile, rows_per_seg) - 1 < kv_pos0) ++first;
+      }
+      seg_first[sg] = first;
+      seg_cnt[sg] = tiles_per_seg - first;
+      total += tiles_per_seg - first;
+    }
+    *n_active_s = total;
+  }
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if ((sb & 1023u) != 0) {
+      *abort_flag = 1;
+      record_status(p.status, kStatusBadArgument, 650, 0, 0, 1, 0);
+    }
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(pds_empty, 1);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_empty, 8);
+    mbar_init(acc_full, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const int n_active = *n_active_s;
+  const int n_steps = n_active * rep;
+  const uint32_t tmem_base = *tmem_holder;
+  const uint32_t tmem_s = tmem_base;          // S, then the dQ partial (128 / D columns)
+  const uint32_t tmem_dp = tmem_base + 128;
+  const uint32_t tmem_dv = tmem_base + 256;
+  const uint32_t tmem_dk = tmem_base + 256 + D;
+  const bool bad = *abort_flag != 0;
+  const int kv_tok0 = batch * d.skv + kv_row0;
+
+  // step -> (query head, q tile): heads outer, active tiles inner
+  auto step_coords = [&](int step, int& head, int& qt) {
+    head = kv_head * rep + step / n_active;
+    int k = step % n_active;
+    qt = 0;
+    for (int sg = 0; sg < d.num_q_segs; ++sg) {
+      if (k < seg_cnt[sg]) {
+        qt = sg * tiles_per_seg + seg_first[sg] + k;
+        break;
+      }
+      k -= seg_cnt[sg];
+    }
+  };
+
+  if (bad || n_steps == 0) {
+    // nothing to accumulate for this tile: its dK / dV rows keep the zeros the caller put there
+  } else if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * S::kTileBytes);
+#pragma unroll
+      for (int a = 0; a < kAtoms; ++a) {
+        tma_load_3d(sb + S::kK + a * kAtomBytes, &tmap_k, kv_full, a * 64, kv_head, kv_tok0);
+        tma_load_3d(sb + S::kV + a * kAtomBytes, &tmap_v, kv_full, a * 64, kv_head, kv_tok0);
+      }
+      bool ok = true;
+      for (int step = 0; step < n_steps && ok; ++step) {
+        int head, qt;
+        step_coords(step, head, qt);
+        if (!mbar_wait(qdo_empty, (step & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; break; }
+        const int q_tok0 = batch * d.sq + qt * kFbTile;
+        mbar_expect_tx(qdo_full, 2 * S::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a) {
+          tma_load_3d(sb + S::kQ + a * kAtomBytes, &tmap_q, qdo_full, a * 64, head, q_tok0);
+          tma_load_3d(sb + S::kDO + a * kAtomBytes, &tmap_do, qdo_full, a * 64, head, q_tok0);
+        }
+      }
+      if (!ok) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 11, 0);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kFbTile, kFbTile, 1, 1, 0, 0);   // S, dP: both operands K-major
+      constexpr uint32_t idesc_acc = make_idesc(kFbTile, D, 1, 1, 1, 1);       // dV, dK: A and B MN-major
+      constexpr uint32_t idesc_dq = make_idesc(kFbTile, D, 1, 1, 0, 1);        // dQ: A K-major, B MN-major
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.budget_ns);
+      for (int step = 0; step < n_steps && ok; ++step) {
+        const uint32_t ph = step & 1;
+        if (!mbar_wait(qdo_full, ph, abort_flag, p.budget_ns) || !mbar_wait(dq_empty, ph ^ 1u, abort_flag, p.budget_ns)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kQ + off), make_smem_desc_sw128_kmajor(sb + S::kK + off),
+                      idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          umma_f16_ss(tmem_dp, make_smem_desc_sw128_kmajor(sb + S::kDO + off), make_smem_desc_sw128_kmajor(sb + S::kV + off),
+                      idesc_s, k != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, ph, abort_flag, p.budget_ns)) { ok = false; break; }
+        tc_fence_after_sync();
+        // dV += P^T dO ; dK += dS^T Q   (K dimension = the 128 q rows, 16 per instruction = 2048 bytes of a [row][128 B] atom)
+#pragma unroll
+        for (int k = 0; k < kFbTile / 16; ++k) {
+          const uint64_t a_p = make_smem_desc_sw128_mnmajor(sb + S::kP + k * 2048, kAtomBytes);
+          const uint64_t b_do = make_smem_desc_sw128_mnmajor(sb + S::kDO + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_dv, a_p, b_do, idesc_acc, (step != 0) || (k != 0));
+        }
+#pragma unroll
+        for (int k = 0; k < kFbTile / 16; ++k) {
+          const uint64_t a_ds = make_smem_desc_sw128_mnmajor(sb + S::kDS + k * 2048, kAtomBytes);
+          const uint64_t b_q = make_smem_desc_sw128_mnmajor(sb + S::kQ + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_dk, a_ds, b_q, idesc_acc, (step != 0) || (k != 0));
+        }
+        // dQ partial = dS K_j  (K dimension = the 128 kv rows)
+#pragma unroll
+        for (int k = 0; k < kFbTile / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          const uint64_t b_k = make_smem_desc_sw128_mnmajor(sb + S::kK + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kDS + aoff), b_k, idesc_dq, k != 0);
+        }
+        umma_commit(qdo_empty);
+        umma_commit(pds_empty);
+        umma_commit(dq_full);
+      }
+      if (ok) umma_commit(acc_full);
+      else record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 20, 0);
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // idle
+  } else if (warp < 8) {
+    // ------------------------------ P and dS (thread = q row) ------------------------------
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const float scale2 = d.scale * kFbLog2e;
+    bool ok = true;
+    for (int step = 0; step < n_steps && ok; ++step) {
+      int head, qt;
+      step_coords(step, head, qt);
+      const uint32_t ph = step & 1;
+      const int q_row = qt * kFbTile + row;
+      const bool row_ok = q_row < d.sq;
+      const int my_pos = row_ok ? fb_q_pos(d, q_row) : -1;
+      const long long sidx = ((long long)batch * d.hq + head) * d.sq + q_row;
+      const float lse2 = row_ok ? p.lse2[sidx] : 0.f;
+      const float delta = row_ok ? p.delta[sidx] : 0.f;
+      const bool row_dead = !row_ok || lse2 == -INFINITY;
+      ok = mbar_wait(sdp_full, ph, abort_flag, p.budget_ns);
+      if (ok && step > 0) ok = mbar_wait(pds_empty, ph ^ 1u, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+      const uint32_t prow = sb + S::kP + static_cast<uint32_t>(row) * 128u;
+      const uint32_t dsrow = sb + S::kDS + static_cast<uint32_t>(row) * 128u;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tmem_s + lane_off + c * 32, rs);
+        tmem_ld_32x32(tmem_dp + lane_off + c * 32, rd);
+        tmem_ld_wait();
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c * 32 + i;
+          const bool masked = row_dead || col >= kv_valid || (d.causal && kv_pos0 + col > my_pos);
+          const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[i]), scale2, -lse2));
+          pv[i] = pe;
+          dsv[i] = pe * (__uint_as_float(rd[i]) - delta) * d.scale;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = c * 4 + g;
+          const uint32_t atom = (chunk >> 3) * kAtomBytes;
+          const uint32_t sw = (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + atom + sw), "r"(pack_bf16x2(pv[8 * g], pv[8 * g + 1])),
+                       "r"(pack_bf16x2(pv[8 * g + 2], pv[8 * g + 3])), "r"(pack_bf16x2(pv[8 * g + 4], pv[8 * g + 5])),
+                       "r"(pack_bf16x2(pv[8 * g + 6], pv[8 * g + 7]))
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dsrow + atom + sw), "r"(pack_bf16x2(dsv[8 * g], dsv[8 * g + 1])),
+                       "r"(pack_bf16x2(dsv[8 * g + 2], dsv[8 * g + 3])), "r"(pack_bf16x2(dsv[8 * g + 4], dsv[8 * g + 5])),
+                       "r"(pack_bf16x2(dsv[8 * g + 6], dsv[8 * g + 7]))
+                       : "memory");
+        }
+      }
+      tc_fence_before_sync();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+    }
+    if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 30, 0);
+  } else {
+    // ------------------------------ dQ drain, then dV / dK (thread = row) ------------------------------
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    constexpr int DH = D / 2;
+    const int col0 = (warp >= 12) ? DH : 0;
+    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    bool ok = !bad;
+    for (int step = 0; step < n_steps && ok; ++step) {
+      int head, qt;
+      step_coords(step, head, qt);
+      ok = mbar_wait(dq_full, step & 1, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int q_row = qt * kFbTile + row;
+      float* dst = p.dq + ((static_cast<long long>(batch) * d.sq + q_row) * d.hq + head) * D + col0;
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_s + lane_off + col0 + c * 32, r);
+        tmem_ld_wait();
+        if (q_row < d.sq) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4)
+            red_add_v4_f32(dst + c * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
+                           __uint_as_float(r[i + 3]));
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_empty);
+    }
+    if (ok && n_steps > 0) {
+      ok = mbar_wait(acc_full, 0, abort_flag, p.budget_ns);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) tc_fence_after_sync();
+    }
+    if (ok) {
+      // rows of dV / dK are the KV rows of this tile
+      const bool row_ok = row < kv_valid;
+      float* dvp = p.dv + ((static_cast<long long>(kv_tok0) + row) * d.hkv + kv_head) * D + col0;
+      float* dkp = p.dk + ((static_cast<long long>(kv_tok0) + row) * d.hkv + kv_head) * D + col0;
+#pragma unroll
+      for (int c = 0; c < DH / 32; ++c) {
+        uint32_t rv[32], rk[32];
+        if (n_steps > 0) {
+          tmem_ld_32x32(tmem_dv + lane_off + col0 + c * 32, rv);
+          tmem_ld_32x32(tmem_dk + lane_off + col0 + c * 32, rk);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { rv[i] = 0u; rk[i] = 0u; }
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            st_global_v4(dvp + c * 32 + i, U4{rv[i], rv[i + 1], rv[i + 2], rv[i + 3]});
+            st_global_v4(dkp + c * 32 + i, U4{rk[i], rk[i + 1], rk[i + 2], rk[i + 3]});
+          }
+        }
+      }
+    } else if (lane == 0 && !bad) {
+      record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 40, 0);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+static int launch_fa_bwd(const pkb_attn_desc& d, const void* q, const void* k, const void* v, const void* o, const void* dout,
+                         const void* lse, void* delta, void* lse2, void* dq, void* dk, void* dv, cudaStream_t stream) {
+  CUtensorMap tq, tk, tv, tdo;
+  int rc = encode_tmap_3d(&tq, kTmapBf16, q, D, d.hq, (uint64_t)d.batch * d.sq, (uint64_t)D * 2, (uint64_t)d.hq * D * 2, 64, 1,
+                          kFbTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tdo, kTmapBf16, dout, D, d.hq, (uint64_t)d.batch * d.sq, (uint64_t)D * 2, (uint64_t)d.hq * D * 2, 64, 1,
+                      kFbTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tk, kTmapBf16, k, D, d.hkv, (uint64_t)d.batch * d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1,
+                      kFbTile, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_3d(&tv, kTmapBf16, v, D, d.hkv, (uint64_t)d.batch * d.skv, (uint64_t)D * 2, (uint64_t)d.hkv * D * 2, 64, 1,
+                      kFbTile, kSwizzle128);
+  if (rc) return rc;
+  const long long rows = (long long)d.batch * d.sq * d.hq;
+  long long pblocks = (rows * 32 + 255) / 256;
+  if (pblocks > 148 * 16) pblocks = 148 * 16;
+  fa_bwd_prep_kernel<<<(int)pblocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout),
+                                                       static_cast<const float*>(lse), static_cast<float*>(delta),
+                                                       static_cast<float*>(lse2), d.batch, d.sq, d.hq, D);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  FaBwdParams p;
+  p.d = d;
+  p.lse2 = static_cast<const float*>(lse2);
+  p.delta = static_cast<const float*>(delta);
+  p.dq = static_cast<float*>(dq);
+  p.dk = static_cast<float*>(dk);
+  p.dv = static_cast<float*>(dv);
+  p.status = status_block_device_ptr();
+  p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
+  auto kern = fa_bwd_kernel<D>;
+  constexpr int smem = FbSmem<D>::kTotal;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int kv_tiles = 0;
+  for (int s = 0; s < d.num_kv_segs; ++s) kv_tiles += (d.kv_seg_len[s] + kFbTile - 1) / kFbTile;
+  dim3 grid(kv_tiles, d.hkv, d.batch);
+  kern<<<grid, kFbThreads, smem, stream>>>(tq, tk, tv, tdo, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+}  // namespace pkb
+
+using namespace pkb;
+
+// dq, dk and dv must be zero-filled by the caller (dq is accumulated into; KV tiles that no query can see are skipped).
+extern "C" int pkb_flash_attn_bwd(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, const void* o,
+                                  const void* dout, const void* lse, void* delta_scratch, void* lse2_scratch, void* dq,
+                                  void* dk, void* dv, void* stream) {
+  PKB_CHECK_ARG(desc != nullptr, "null descriptor");
+  const pkb_attn_desc& d = *desc;
+  PKB_CHECK_ARG(d.head_dim == 64 || d.head_dim == 128, "head_dim must be 64 or 128");
+  PKB_CHECK_ARG(d.hq % d.hkv == 0 && d.batch >= 1 && d.sq >= 1 && d.skv >= 1, "bad attention shape");
+  PKB_CHECK_ARG(d.num_q_segs >= 1 && d.num_q_segs <= 16 && d.num_kv_segs >= 1 && d.num_kv_segs <= 16, "1..16 segments");
+  PKB_CHECK_ARG(d.q_seg_rows % kFbTile == 0 || d.num_q_segs == 1, "q segments must be multiples of 128 rows");
+  PKB_CHECK_ARG(d.q_seg_rows >= 1, "q_seg_rows must be positive");
+  for (int s = 0; s < d.num_kv_segs; ++s)
+    PKB_CHECK_ARG(d.kv_seg_row0[s] >= 0 && d.kv_seg_len[s] >= 0 && d.kv_seg_row0[s] + d.kv_seg_len[s] <= d.skv,
+                  "kv segment outside the buffer");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d.head_dim == 128) return launch_fa_bwd<128>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, dk, dv, s);
+  return launch_fa_bwd<64>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, dk, dv, s);
+}

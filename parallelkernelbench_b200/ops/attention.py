@@ -151,24 +151,65 @@ class RingAttention:
 
 
 def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, *,
-                   causal: bool, scale: float | None = None, q_pos0: int = 0):
-    """Attention backward from a saved forward. ``q, out, dout`` [Sq, Hq, D]; ``k, v`` [Skv, Hkv, D]; ``lse`` [Hq, Sq];
-    query row i sits at global position ``q_pos0 + i``, key row j at position j. Returns fp32 (dq, dk, dv)."""
-    from ..refs.attention import attention_bwd_positions_ref
-
+                   causal: bool, scale: float | None = None, q_pos0: int = 0,
+                   q_segments: list[tuple[int, int]] | None = None, kv_segments: list[tuple[int, int, int]] | None = None):
+    """Attention backward from a saved forward. ``q, out, dout`` [Sq, Hq, D] (or [B, Sq, Hq, D]); ``k, v`` [Skv, Hkv, D]
+    (or with the batch dimension); ``lse`` [Hq, Sq] (or [B, Hq, Sq]), natural log. Positions are described as in
+    :func:`flash_attn_fwd`; without segment lists query row i sits at ``q_pos0 + i`` and key row j at j.
+    Returns fp32 ``(dq, dk, dv)`` shaped like q, k, v. bf16 inputs with head dimension 64 or 128 run on the tcgen05
+    kernel (dK/dV accumulate in TMEM, dQ by fp32 vector reductions); anything else takes the PyTorch restatement."""
     D = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    Sq, Skv = q.shape[0], k.shape[0]
-    kv_pos = torch.arange(Skv, device=q.device)
-    dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
-    dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-    dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
-    step = max(1, min(Sq, (1 << 26) // max(Skv * q.shape[1], 1)))      # bound the score matrix held at once
-    for s0 in range(0, Sq, step):
-        s1 = min(Sq, s0 + step)
-        q_pos = torch.arange(q_pos0 + s0, q_pos0 + s1, device=q.device)
-        a, b, c = attention_bwd_positions_ref(q[s0:s1], k, v, out[s0:s1], lse[:, s0:s1], dout[s0:s1], q_pos, kv_pos, causal, scale)
-        dq[s0:s1] = a
-        dk += b
-        dv += c
+    squeeze = q.dim() == 3
+    if squeeze:
+        q, k, v, out, dout, lse = (t.unsqueeze(0) for t in (q, k, v, out, dout, lse))
+    B, sq, hq, _ = q.shape
+    skv, hkv = k.shape[1], k.shape[2]
+    q_segments = q_segments or [(sq, q_pos0)]
+    kv_segments = kv_segments or [(0, 0, skv)]
+    use_kernel = q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128)
+    if not use_kernel:
+        from ..refs.attention import attention_bwd_positions_ref
+
+        q_pos = torch.cat([torch.arange(p0, p0 + r, device=q.device) for r, p0 in q_segments])
+        kv_rows = torch.cat([torch.arange(r0, r0 + ln, device=q.device) for r0, _, ln in kv_segments])
+        kv_pos = torch.cat([torch.arange(p0, p0 + ln, device=q.device) for _, p0, ln in kv_segments])
+        dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        step = max(1, min(sq, (1 << 26) // max(kv_rows.numel() * hq, 1)))        # bound the score matrix held at once
+        for b in range(B):
+            kb, vb = k[b][kv_rows], v[b][kv_rows]
+            for s0 in range(0, sq, step):
+                s1 = min(sq, s0 + step)
+                a, bb, c = attention_bwd_positions_ref(q[b, s0:s1], kb, vb, out[b, s0:s1], lse[b][:, s0:s1], dout[b, s0:s1],
+                                                       q_pos[s0:s1], kv_pos, causal, scale)
+                dq[b, s0:s1] = a
+                dk[b].index_add_(0, kv_rows, bb)
+                dv[b].index_add_(0, kv_rows, c)
+    else:
+        d = AttnDesc()
+        d.batch, d.sq, d.skv, d.hq, d.hkv, d.head_dim = B, sq, skv, hq, hkv, D
+        d.causal, d.scale = (1 if causal else 0), float(scale)
+        if len({r for r, _ in q_segments}) != 1:
+            raise ValueError("all q runs must have the same number of rows")
+        d.q_seg_rows, d.num_q_segs = q_segments[0][0], len(q_segments)
+        for i, (_, pos) in enumerate(q_segments):
+            d.q_seg_pos[i] = pos
+        d.num_kv_segs = len(kv_segments)
+        for i, (row0, pos0, ln) in enumerate(kv_segments):
+            d.kv_seg_row0[i], d.kv_seg_pos0[i], d.kv_seg_len[i] = row0, pos0, ln
+        qc, kc, vc, oc, doc = (t.contiguous() for t in (q, k, v, out, dout))
+        lsec = lse.float().contiguous()
+        delta = torch.empty_like(lsec)
+        lse2 = torch.empty_like(lsec)
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        nv.check(nv.cuda_lib().pkb_flash_attn_bwd(ctypes.byref(d), nv.ptr(qc), nv.ptr(kc), nv.ptr(vc), nv.ptr(oc), nv.ptr(doc), nv.ptr(lsec),
+                                                  nv.ptr(delta), nv.ptr(lse2), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.current_stream()),
+                 "pkb_flash_attn_bwd")
+        nv.count_launch(2)
+    if squeeze:
+        return dq[0], dk[0], dv[0]
     return dq, dk, dv

@@ -131,11 +131,14 @@ class Comm:
         full = self.heap.all_gather(x, g)
         return full if g.rank_in_group == dst else x
 
-    def all_to_all_v(self, x: torch.Tensor, send_counts: torch.Tensor, out_capacity_rows: int, group=None):
-        """Rows of ``x`` grouped by destination; returns ``(out, recv_counts, total)`` with device-side counts."""
+    def all_to_all_v(self, x: torch.Tensor, send_counts: torch.Tensor, out_capacity_rows: int, group=None,
+                     max_send_rows: int | None = None):
+        """Rows of ``x`` grouped by destination; returns ``(out, recv_counts, total)`` with device-side counts.
+        ``out_capacity_rows`` and ``max_send_rows`` (an upper bound of ``x.shape[0]`` over all ranks; default: the output
+        capacity) must be the same on every rank."""
         g = self.group(group)
         if self.is_cuda:
-            return self._C.all_to_all_v(x, send_counts.to(torch.int64), g, out_capacity_rows)
+            return self._C.all_to_all_v(x, send_counts.to(torch.int64), g, out_capacity_rows, max_send_rows=max_send_rows)
         # CPU twin: exchange the count matrix, then one padded all-to-all
         W = g.size
         counts = self.heap.all_gather(send_counts.to(torch.int64), g)          # [W, W]

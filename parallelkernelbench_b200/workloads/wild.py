@@ -796,9 +796,10 @@ def _kjt(rc, lengths, values, key_splits, B, ours):
     val_counts = torch.stack([feat_sum[int(b - k):int(b)].sum() for b, k in zip(bounds.tolist(), key_splits)])
     if W > 1:
         if ours:
-            cap_l, cap_v = key_splits[r] * B * W, 21 * key_splits[r] * B * W
-            rl, _, tl = rc.comm.all_to_all_v(lengths.view(-1, 1).contiguous(), len_counts, cap_l)
-            rv, _, tv = rc.comm.all_to_all_v(values.view(-1, 1).contiguous(), val_counts, cap_v)
+            # capacities are upper bounds that every rank computes alike (lengths are at most 20 per entry)
+            ksm, nf = max(key_splits), sum(key_splits)
+            rl, _, tl = rc.comm.all_to_all_v(lengths.view(-1, 1).contiguous(), len_counts, ksm * B * W, max_send_rows=nf * B)
+            rv, _, tv = rc.comm.all_to_all_v(values.view(-1, 1).contiguous(), val_counts, 20 * ksm * B * W, max_send_rows=20 * nf * B)
             rl, rv = rl.view(-1)[:key_splits[r] * B * W], rv.view(-1)[:int(tv.item())]
         else:
             rl, _ = _a2av_ref(lengths, len_counts)

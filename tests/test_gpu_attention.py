@@ -63,3 +63,57 @@ def test_flash_attention_segments_model_a_zigzag_rank():
     torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
     assert torch.equal(out, flash_attn_fwd(q, k, v, causal=True, q_segments=[(C, r * C), (C, (2 * W - 1 - r) * C)],
                                            kv_segments=[(i * C, c * C, C) for i, c in enumerate(order)])[0])
+
+
+@pytest.mark.parametrize("case", [
+    dict(B=1, sq=256, skv=256, hq=4, hkv=2, D=128, causal=False),
+    dict(B=1, sq=256, skv=256, hq=4, hkv=2, D=128, causal=True),
+    dict(B=2, sq=384, skv=384, hq=2, hkv=2, D=64, causal=True),
+    dict(B=1, sq=200, skv=333, hq=3, hkv=1, D=128, causal=False),
+    dict(B=1, sq=1024, skv=1024, hq=8, hkv=2, D=128, causal=True),
+])
+def test_flash_attention_backward_matches_fp32_reference(case):
+    """dq, dk, dv of the tcgen05 backward kernel against the explicit fp32 formula, from the forward kernel's own out / lse."""
+    from parallelkernelbench_b200.ops.attention import flash_attn_bwd, flash_attn_fwd
+    from parallelkernelbench_b200.refs.attention import attention_bwd_positions_ref
+
+    B, sq, skv, hq, hkv, D, causal = (case[k] for k in ("B", "sq", "skv", "hq", "hkv", "D", "causal"))
+    torch.manual_seed(3)
+    q = torch.randn(B, sq, hq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, skv, hkv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, skv, hkv, D, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn(B, sq, hq, D, device="cuda", dtype=torch.bfloat16)
+    out, lse = flash_attn_fwd(q, k, v, causal=causal)
+    dq, dk, dv = flash_attn_bwd(q, k, v, out, lse, dout, causal=causal)
+    torch.cuda.synchronize()
+    q_pos, kv_pos = torch.arange(sq, device="cuda"), torch.arange(skv, device="cuda")
+    for b in range(B):
+        rq, rk, rv = attention_bwd_positions_ref(q[b], k[b], v[b], out[b], lse[b], dout[b], q_pos, kv_pos, causal, D ** -0.5)
+        for name, got, ref in (("dq", dq[b], rq), ("dk", dk[b], rk), ("dv", dv[b], rv)):
+            err = (got - ref).abs().max().item()
+            tol = 2e-2 * max(ref.abs().max().item(), 1.0)
+            assert err <= tol, f"{name} batch {b}: max err {err} > {tol} ({case})"
+
+
+def test_flash_attention_backward_zigzag_segments():
+    """Two query runs at far-apart global positions and KV segments in a permuted buffer order (context-parallel layout)."""
+    from parallelkernelbench_b200.ops.attention import flash_attn_bwd, flash_attn_fwd
+    from parallelkernelbench_b200.refs.attention import attention_bwd_positions_ref
+
+    torch.manual_seed(4)
+    C, hq, hkv, D = 128, 4, 2, 128
+    q_segs = [(C, 1 * C), (C, 6 * C)]                                      # rank 1 of 4 in the zigzag layout
+    kv_segs = [(0, 1 * C, C), (C, 6 * C, C), (2 * C, 0, C), (3 * C, 7 * C, C), (4 * C, 2 * C, C), (5 * C, 5 * C, C),
+               (6 * C, 3 * C, C), (7 * C, 4 * C, C)]
+    q = torch.randn(1, 2 * C, hq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 8 * C, hkv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(1, 8 * C, hkv, D, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn(1, 2 * C, hq, D, device="cuda", dtype=torch.bfloat16)
+    out, lse = flash_attn_fwd(q, k, v, causal=True, q_segments=q_segs, kv_segments=kv_segs)
+    dq, dk, dv = flash_attn_bwd(q, k, v, out, lse, dout, causal=True, q_segments=q_segs, kv_segments=kv_segs)
+    q_pos = torch.cat([torch.arange(p, p + r, device="cuda") for r, p in q_segs])
+    kv_pos = torch.cat([torch.arange(p, p + n, device="cuda") for _, p, n in kv_segs])
+    rq, rk, rv = attention_bwd_positions_ref(q[0], k[0], v[0], out[0], lse[0], dout[0], q_pos, kv_pos, True, D ** -0.5)
+    for name, got, ref in (("dq", dq[0], rq), ("dk", dk[0], rk), ("dv", dv[0], rv)):
+        err = (got - ref).abs().max().item()
+        assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), f"{name}: {err}"
