@@ -124,10 +124,23 @@ __device__ __forceinline__ void grid_copy_bytes(void* dst, const void* src, long
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) {
     const long long nvec = bytes >> 4;
-    for (long long i = tid; i < nvec; i += nthreads)
-      st_global_v4(static_cast<uint8_t*>(dst) + (i << 4), ld_global_v4(static_cast<const uint8_t*>(src) + (i << 4)));
-    for (long long i = (nvec << 4) + tid; i < bytes; i += nthreads)
-      static_cast<uint8_t*>(dst)[i] = static_cast<const uint8_t*>(src)[i];
+    const uint8_t* s8 = static_cast<const uint8_t*>(src);
+    uint8_t* d8 = static_cast<uint8_t*>(dst);
+    // four independent 16-byte loads in flight per thread: a peer load takes microseconds, so bandwidth over NVLink
+    // is bytes in flight divided by that latency
+    long long i = tid;
+    for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+      const U4 a = ld_global_v4(s8 + (i << 4));
+      const U4 b = ld_global_v4(s8 + ((i + nthreads) << 4));
+      const U4 c = ld_global_v4(s8 + ((i + 2 * nthreads) << 4));
+      const U4 e = ld_global_v4(s8 + ((i + 3 * nthreads) << 4));
+      st_global_v4(d8 + (i << 4), a);
+      st_global_v4(d8 + ((i + nthreads) << 4), b);
+      st_global_v4(d8 + ((i + 2 * nthreads) << 4), c);
+      st_global_v4(d8 + ((i + 3 * nthreads) << 4), e);
+    }
+    for (; i < nvec; i += nthreads) st_global_v4(d8 + (i << 4), ld_global_v4(s8 + (i << 4)));
+    for (long long j = (nvec << 4) + tid; j < bytes; j += nthreads) d8[j] = s8[j];
   } else {
     for (long long i = tid; i < bytes; i += nthreads)
       static_cast<uint8_t*>(dst)[i] = static_cast<const uint8_t*>(src)[i];
@@ -383,12 +396,19 @@ coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
   const long long nvec_total = (a.n + P::kN - 1) / P::kN;  // staging buffers are padded to 16 bytes
   const long long per = (nvec_total + c.gsize - 1) / c.gsize;
   const long long v0 = min(per * c.grank, nvec_total), v1 = min(v0 + per, nvec_total);
-  for (long long i = v0 + tid; i < v1; i += nthreads) {
-    U4 v;
-    if constexpr (DT == kCollBf16) v = multimem_ld_reduce_bf16x8(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
-    else v = multimem_ld_reduce_f32x4(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
-    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), v);
+  auto ldr = [&](long long i) {
+    if constexpr (DT == kCollBf16) return multimem_ld_reduce_bf16x8(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
+    else return multimem_ld_reduce_f32x4(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
+  };
+  long long i = v0 + tid;
+  for (; i + 3 * nthreads < v1; i += 4 * nthreads) {   // four in-switch reductions in flight per thread
+    const U4 r0 = ldr(i), r1 = ldr(i + nthreads), r2 = ldr(i + 2 * nthreads), r3 = ldr(i + 3 * nthreads);
+    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), r0);
+    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + nthreads) << 4), r1);
+    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + 2 * nthreads) << 4), r2);
+    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + 3 * nthreads) << 4), r3);
   }
+  for (; i < v1; i += nthreads) multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), ldr(i));
   if (!symm_grid_barrier(c, 203, 2)) return;
   if (a.out != nullptr) grid_copy_bytes(a.out, symm_local<uint8_t>(c, a.result_off), a.n * P::kElem);
   symm_block_barrier(c, 203, 3);

@@ -100,6 +100,81 @@ def case_allreduce(iters):
     ctx.finalize()
 
 
+def case_fa_bwd(iters):
+    from ..ops.attention import flash_attn_bwd, flash_attn_fwd
+
+    q = torch.randn(1, 4096, 16, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(1, 4096, 4, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(1, 4096, 4, 128, device="cuda", dtype=torch.bfloat16)
+    do = torch.randn(1, 4096, 16, 128, device="cuda", dtype=torch.bfloat16)
+    out, lse = flash_attn_fwd(q, k, v, causal=True)
+    for _ in range(iters):
+        flash_attn_bwd(q, k, v, out, lse, do, causal=True)
+
+
+def case_fsdp_adamw(iters):
+    from ..ops import fp8_quantize_1x128
+    from ..ops.quant import fsdp_adamw_fp8
+
+    W, n = 8, 32 << 20
+    payload = torch.randint(0, 120, (W, n), device="cuda", dtype=torch.uint8)
+    scales = torch.rand(W, n // 128, device="cuda") * 1e-3
+    p, m, v = torch.randn(n, device="cuda") * 0.02, torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    q_out, s_out = fp8_quantize_1x128(p.view(-1, 128))
+    for i in range(iters):
+        fsdp_adamw_fp8(payload, scales, p, m, v, q_out.view(-1), s_out.view(-1), lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
+                       weight_decay=0.1, grad_scale=1.0 / W, step=i + 1)
+
+
+def case_moe_exchange(iters):
+    """Dispatch and combine kernels at one rank (the pushes and pulls stay on this GPU)."""
+    from ..models.moe_layer import EPMoELayer, MoEConfig
+    from ..parallel import init_context
+    from ..parallel.comm import Comm
+
+    ctx = init_context()
+    dev = ctx.device
+    cfg = MoEConfig(hidden=2048, inter=512, num_experts=32, top_k=8, tokens_per_rank=4096)
+    w_router = torch.randn(32, 2048, device=dev, dtype=torch.bfloat16) * 0.02
+    wg = torch.randn(32, 512, 2048, device=dev, dtype=torch.bfloat16) * 0.02
+    wu = torch.randn(32, 512, 2048, device=dev, dtype=torch.bfloat16) * 0.02
+    wd = torch.randn(32, 2048, 512, device=dev, dtype=torch.bfloat16) * 0.02
+    comm = Comm(ctx)
+    layer = EPMoELayer(comm.group(), comm, cfg, w_router, wg, wu, wd)
+    x = torch.randn(cfg.tokens_per_rank, cfg.hidden, device=dev, dtype=torch.bfloat16)
+    for _ in range(iters):
+        layer(x)
+    torch.cuda.synchronize()
+    ctx.finalize()
+
+
+def case_gsplat(iters):
+    from ..ops.gsplat import gsplat_project_exchange
+    from ..parallel import init_context
+
+    ctx = init_context()
+    n = 1 << 20
+    dev = ctx.device
+    means = torch.stack([(torch.rand(n, device=dev) - 0.5) * 1.5, (torch.rand(n, device=dev) - 0.5) * 1.5, torch.rand(n, device=dev) * 2 + 2], -1)
+    view = torch.eye(4, device=dev).reshape(1, 4, 4)
+    K = torch.tensor([[800.0, 0, 512], [0, 800.0, 512], [0, 0, 1]], device=dev).reshape(1, 3, 3)
+    for _ in range(iters):
+        gsplat_project_exchange(ctx.heap().world_group, means, torch.randn(n, 4, device=dev), torch.rand(n, 3, device=dev) * 0.02,
+                                torch.rand(n, device=dev), torch.rand(n, 3, device=dev), view, K, 1, 1024, 1024)
+    torch.cuda.synchronize()
+    ctx.finalize()
+
+
+def case_delta_scan(iters):
+    from ..ops.wild import delta_rule_scan
+
+    BH, T, K, V = 64, 2048, 128, 128
+    q, k = torch.randn(BH, T, K, device="cuda") * 0.1, torch.nn.functional.normalize(torch.randn(BH, T, K, device="cuda"), dim=-1)
+    v, decay, beta = torch.randn(BH, T, V, device="cuda"), torch.rand(BH, T, K, device="cuda") * 0.1 + 0.9, torch.rand(BH, T, device="cuda")
+    for _ in range(iters):
+        delta_rule_scan(q, k, v, decay, beta)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("case")

@@ -11,8 +11,7 @@ Two implementations share this file's structure:
 * ``impl="torch"``  the PyTorch + NCCL + cuBLAS baseline of the same step (bf16 all-gather,
   reduce-scatter, library attention, torch AdamW arithmetic).
 
-The attention backward of ``impl="ours"`` calls the library flash-attention backward on the outputs
-and log-sum-exp of our forward kernel; everything else in that path is ours.
+Attention forward and backward of ``impl="ours"`` are the tcgen05 flash-attention kernels.
 Reference ancestors: reference/47_fsdp_step_e2e.py, reference/52_fp8_reduce_scatter_grads.py,
 reference/53_fp8_allgather_params.py, reference/73_vocab_parallel_cross_entropy_loss.py,
 reference/17_rope_allgather.py, reference/18_tp_rms_norm.py.
@@ -132,18 +131,11 @@ class _FlashAttention(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout):
+        from ..ops.attention import flash_attn_bwd
+
         q, k, v, out, lse = ctx.saved_tensors
-        rep = q.shape[2] // k.shape[2]
-        t = lambda x: x.permute(0, 2, 1, 3)  # noqa: E731  [B,S,H,D] -> [B,H,S,D]
-        kt, vt = t(k).repeat_interleave(rep, dim=1), t(v).repeat_interleave(rep, dim=1)
-        S = q.shape[1]
-        zero = torch.zeros((), dtype=torch.int64, device=q.device)
-        dq, dk, dv = torch.ops.aten._scaled_dot_product_flash_attention_backward(
-            t(dout.contiguous()), t(q), kt, vt, t(out), lse, None, None, S, S, 0.0, True, zero, zero, scale=ctx.scale)
-        B, H, _, D = dq.shape
-        dk = dk.reshape(B, k.shape[2], rep, S, D).sum(2)
-        dv = dv.reshape(B, k.shape[2], rep, S, D).sum(2)
-        return t(dq).contiguous(), t(dk).contiguous().to(k.dtype), t(dv).contiguous().to(v.dtype), None
+        dq, dk, dv = flash_attn_bwd(q, k, v, out, lse, dout.contiguous(), causal=True, scale=ctx.scale)
+        return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None
 
 
 def rope_tables(cfg: LlamaConfig, device, dtype=torch.bfloat16):

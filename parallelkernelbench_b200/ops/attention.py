@@ -149,6 +149,29 @@ class RingAttention:
 
     __call__ = forward
 
+    def backward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor,
+                 causal: bool = True, scale: float | None = None):
+        """Gradients of :meth:`forward`. K and V of the whole group are gathered (one launch each), the backward kernel
+        walks them by segment with this rank's query positions - dQ is complete locally, dK/dV partials for every KV
+        row come out in fp32 - and one reduce-scatter per tensor sends the partial sums to the owners of the rows.
+        Returns ``(dq, dk, dv)`` in fp32 for this rank's rows."""
+        from . import collectives as C
+
+        W, r = self.W, self.group.rank_in_group
+        if W > 1:
+            kg = C.all_gather(k.contiguous(), self.group).view(W * self.rows, self.hkv, self.D)
+            vg = C.all_gather(v.contiguous(), self.group).view(W * self.rows, self.hkv, self.D)
+        else:
+            kg, vg = k, v
+        q_segments = [(self.seg_rows, pos) for pos in self.positions(r)]
+        kv_segments = [(src * self.rows + sgi * self.seg_rows, pos, self.seg_rows) for src in range(W)
+                       for sgi, pos in enumerate(self.positions(src))]
+        dq, dkf, dvf = flash_attn_bwd(q, kg, vg, out, lse.reshape(self.hq, self.rows), dout, causal=causal, scale=scale,
+                                      q_segments=q_segments, kv_segments=kv_segments)
+        if W > 1:
+            return dq, C.reduce_scatter(dkf, self.group), C.reduce_scatter(dvf, self.group)
+        return dq, dkf, dvf
+
 
 def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, *,
                    causal: bool, scale: float | None = None, q_pos0: int = 0,

@@ -103,3 +103,59 @@ def attention_bwd_positions_ref(q, k, v, out, lse, dout, q_pos, kv_pos, causal: 
     dk = dk.reshape(Hkv, rep, Skv, D).sum(1)
     dv = dv.reshape(Hkv, rep, Skv, D).sum(1)
     return dq.permute(1, 0, 2), dk.permute(1, 0, 2), dv.permute(1, 0, 2)
+
+
+def cp_attention_fwd_bwd_reference(q, k, v, dout, positions_of, world: int, rank: int, causal: bool, scale: float | None = None,
+                                   group=None, exact: bool = False):
+    """Forward and backward of context-parallel attention the PyTorch + process-group way: all-gather K and V, run the
+    library flash kernel per query chunk (or the exact fp32 restatement when ``exact``), let autograd produce dQ and the
+    gradients of the gathered K / V, and reduce-scatter those to their owners. Returns (out, dq, dk, dv) in q.dtype."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    rows = q.shape[0]
+    with torch.enable_grad():
+        ql = q.detach().clone().requires_grad_()
+        if world > 1:
+            kg = torch.empty((world * rows, *k.shape[1:]), dtype=k.dtype, device=k.device)
+            vg = torch.empty_like(kg)
+            dist.all_gather_into_tensor(kg, k.contiguous(), group=group)
+            dist.all_gather_into_tensor(vg, v.contiguous(), group=group)
+        else:
+            kg, vg = k.detach().clone(), v.detach().clone()
+        kg.requires_grad_()
+        vg.requires_grad_()
+        nseg = len(positions_of(0))
+        C = rows // nseg
+        chunks = sorted((pos, src * rows + i * C) for src in range(world) for i, pos in enumerate(positions_of(src)))
+        kfull = torch.cat([kg[row0:row0 + C] for _, row0 in chunks])
+        vfull = torch.cat([vg[row0:row0 + C] for _, row0 in chunks])
+        outs = []
+        for i, pos in enumerate(positions_of(rank)):
+            qc = ql[i * C:(i + 1) * C]
+            if exact:
+                q_pos = torch.arange(pos, pos + C, device=q.device)
+                kv_pos = torch.arange(kfull.shape[0], device=q.device)
+                o = attention_positions_ref(qc, kfull, vfull, q_pos, kv_pos, causal, scale)[0]
+            elif not causal:
+                o = _flash(qc, kfull, vfull, False, scale)[0]
+            else:
+                o, l = _flash(qc, kfull[pos:pos + C], vfull[pos:pos + C], True, scale)
+                if pos > 0:
+                    o0, l0 = _flash(qc, kfull[:pos], vfull[:pos], False, scale)
+                    o, _ = _merge(o0, l0, o, l)
+            outs.append(o)
+        out = torch.cat(outs)
+        out.backward(dout.to(out.dtype))
+    dkg, dvg = kg.grad.float(), vg.grad.float()
+    if world > 1:
+        if dist.get_backend(group) == "gloo":
+            dist.all_reduce(dkg, group=group)
+            dist.all_reduce(dvg, group=group)
+            dk, dv = dkg[rank * rows:(rank + 1) * rows], dvg[rank * rows:(rank + 1) * rows]
+        else:
+            dk, dv = torch.empty((rows, *k.shape[1:]), device=k.device), torch.empty((rows, *k.shape[1:]), device=k.device)
+            dist.reduce_scatter_tensor(dk, dkg, group=group)
+            dist.reduce_scatter_tensor(dv, dvg, group=group)
+    else:
+        dk, dv = dkg, dvg
+    return out.detach().to(q.dtype), ql.grad.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)

@@ -10,7 +10,7 @@ import math
 import torch
 
 from ..harness.roofline import Cost
-from ..refs.attention import attention_positions_ref, cp_attention_reference
+from ..refs.attention import attention_positions_ref, cp_attention_fwd_bwd_reference, cp_attention_reference
 from .registry import OpSpec, RunCtx, register
 
 
@@ -98,6 +98,45 @@ register(OpSpec(name="ring_attention", problem_ids=(54,), group="attention",
                          "cp131k": {"rows": 16384, "hq": 32, "hkv": 8, "d": 128, "causal": 1, "layout": "zigzag"}},
                 make_inputs=_ring_inputs, reference=_ring_ref, ours=_ring_ours, atol=2e-2, rtol=2e-2, ours_needs_cuda=True,
                 cost=_ring_cost, doc="zigzag context-parallel causal attention, KV exchange inside the attention kernel"))
+
+
+# ---- context-parallel attention, forward and backward -----------------------------------------------
+def _ringfb_inputs(rc: RunCtx, cfg):
+    rows, Hq, Hkv, D = cfg["rows"], cfg["hq"], cfg["hkv"], cfg["d"]
+    return (rc.randn(rows, Hq, D), rc.randn(rows, Hkv, D, salt=1), rc.randn(rows, Hkv, D, salt=2), rc.randn(rows, Hq, D, salt=3),
+            bool(cfg["causal"]), cfg["layout"])
+
+
+def _ringfb_ref(rc, q, k, v, dout, causal, layout):
+    W = rc.world
+    exact = q.shape[0] * W <= 4096 or not rc.dist.is_cuda
+    return cp_attention_fwd_bwd_reference(q, k, v, dout, _positions_fn(layout, W, q.shape[0]), W, rc.rank, causal, exact=exact)
+
+
+def _ringfb_ours(rc, q, k, v, dout, causal, layout):
+    from ..ops.attention import RingAttention
+
+    key = ("ring", q.shape, k.shape, layout)
+    if key not in rc.cache:
+        rc.cache[key] = RingAttention(rc.comm.group(), q.shape[0], q.shape[1], k.shape[1], q.shape[2], layout=layout)
+    ring = rc.cache[key]
+    out, lse = ring(q, k, v, causal=causal)
+    dq, dk, dv = ring.backward(q, k, v, out, lse, dout, causal=causal)
+    return out, dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype)
+
+
+def _ringfb_cost(cfg, W):
+    S = cfg["rows"] * W
+    fwd = 4.0 * S * S * cfg["d"] * cfg["hq"] * (0.5 if cfg["causal"] else 1.0) / W
+    return Cost(flops=3.5 * fwd, nvlink_bytes=(2.0 * 2 + 2.0 * 4) * (W - 1) * cfg["rows"] * cfg["hkv"] * cfg["d"])
+
+
+register(OpSpec(name="ring_attention_fwd_bwd", problem_ids=(54, 57), group="attention",
+                configs={"default": {"rows": 512, "hq": 8, "hkv": 2, "d": 128, "causal": 1, "layout": "zigzag"},
+                         "small": {"rows": 256, "hq": 4, "hkv": 2, "d": 64, "causal": 1, "layout": "zigzag"},
+                         "cp131k": {"rows": 16384, "hq": 32, "hkv": 8, "d": 128, "causal": 1, "layout": "zigzag"}},
+                make_inputs=_ringfb_inputs, reference=_ringfb_ref, ours=_ringfb_ours, atol=5e-2, rtol=5e-2, ours_needs_cuda=True,
+                cost=_ringfb_cost, doc="zigzag context-parallel causal attention, forward and backward (GQA)"))
 
 
 # =================================================================================================

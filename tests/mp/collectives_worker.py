@@ -154,6 +154,46 @@ def main() -> int:
         if r == 0:
             print(line, flush=True)
 
+    # the same comparison with both sides replayed from a CUDA graph (launch overhead of either host path removed),
+    # inputs and outputs living in the symmetric heap so that no staging copy is involved
+    def graph_time(fn, n=20):
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize(); dist.barrier()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(n):
+                fn()
+        torch.cuda.synchronize(); dist.barrier()
+        for _ in range(3):
+            gr.replay()
+        torch.cuda.synchronize(); dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            gr.replay()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / (5 * n)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+    if W > 1 and "--graphs" in sys.argv:
+        for nbytes in (4096, 1 << 20, 1 << 24, 1 << 27):
+            xs = heap.named(("perf_x", nbytes), (nbytes // 2,), torch.bfloat16)
+            xs.local.normal_()
+            y = torch.empty(nbytes // 2, device=dev, dtype=torch.bfloat16)
+            yn = xs.local.clone()
+            line = f"GRAPH all_reduce {nbytes}B nccl={graph_time(lambda: dist.all_reduce(yn)) * 1e3:.1f}us"
+            for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []):
+                if algo == "oneshot" and nbytes > (1 << 24):
+                    continue
+                line += f" {algo}={graph_time(lambda: C.all_reduce(xs.local, g, algo=algo, out=y)) * 1e3:.1f}us"
+            if r == 0:
+                print(line, flush=True)
+
     torch.cuda.synchronize()
     st = nv.read_status()
     report("device status clean", st[0] == 0, str(st[:8]))
