@@ -1414,7 +1414,10 @@ def _vlp_inputs(rc: RunCtx, cfg, with_grad=False):
     target = ((torch.arange(B * S, device=rc.device) * 17 + 3 + rc.trial) % V).view(B, S)
     gv = rc.rank * Vl + torch.arange(Vl, device=rc.device)
     logits = logits + (gv.view(1, 1, Vl) == target.unsqueeze(-1)).to(logits.dtype) * 8.0
-    out = [logits, target, cfg["top_k"], cfg["top_p"], cfg.get("chunk", 0)]
+    chunk = cfg.get("chunk", 0)
+    if chunk:                                  # tokens per chunk (batch * chunk) must split evenly over the ranks
+        chunk = -(-chunk // W) * W
+    out = [logits, target, cfg["top_k"], cfg["top_p"], chunk]
     if with_grad:
         out.insert(2, torch.linspace(-1.0, 1.0, B * S, device=rc.device).view(B, S).to(rc.dtype))
     return tuple(out)
