@@ -25,6 +25,8 @@
 //
 // Reference behaviour replaced: materialised fp32 scores + logsumexp merge per ring step
 // (reference: reference/54_ring_attention.py:61-100) and SDPA calls (reference/77_magi1_cso_async_attention.py:108).
+#include <cstdlib>
+
 #include "pkb/api.h"
 #include "pkb/attention_api.h"
 #include "pkb/host.h"
@@ -432,6 +434,420 @@ __device__ __forceinline__ void fa_fwd_cta(const CUtensorMap& tmap_q, const CUte
   }
 }
 
+// ================================================================================================
+// Two Q tiles per CTA. The softmax, not the tensor core, bounds the one-tile kernel above (ncu: tensor pipe busy
+// ~18 % of active cycles), so this form gives the tensor core two independent softmax warpgroups to wait for:
+//   warp 0       TMA producer: Q0, Q1 once; K and V tiles one at a time (a K tile is free again as soon as both S
+//                products are issued, a V tile as soon as both P V products are - the softmax in between hides the loads)
+//   warp 1       MMA issuer: S_t = Q_t K^T into TMEM, O_t += P_t V accumulated IN TMEM over all KV tiles
+//   warps 4-7    softmax of tile 0, warps 8-11 softmax of tile 1 (thread = row, two passes over S in TMEM as above)
+//   warps 12-15  correction: before P_t V of step j is issued, scale the TMEM accumulator O_t by alpha_t(j) (tcgen05.ld,
+//                multiply, tcgen05.st) - skipped for a warp whose 32 rows all kept their maximum
+// At the end each softmax warpgroup reads its O from TMEM, divides by the row sums and stores bf16.
+// K and V tiles are shared by the two Q tiles, so L2 -> shared-memory traffic per Q row halves as well.
+// ================================================================================================
+template <int D>
+struct Fa2Smem {
+  static constexpr int kTileBytes = kFaTile * D * 2;
+  static constexpr int kPBytes = kFaTile * kFaTile * 2;
+  static constexpr int kQ = 0;                              // two tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;
+  static constexpr int kV = kK + kTileBytes;
+  static constexpr int kP = kV + kTileBytes;                // two tiles
+  static constexpr int kAlpha = kP + 2 * kPBytes;           // [2][128] fp32
+  static constexpr int kBars = kAlpha + 2 * kFaTile * 4;
+  static constexpr int kTotal = kBars + 256;
+};
+
+template <int D>
+__device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                            const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
+                                            const int head, const int batch) {
+  using S = Fa2Smem<D>;
+  constexpr int kAtoms = D / 64;
+  constexpr int kAtomBytes = kFaTile * 128;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = smem_u32(smem);
+  const pkb_attn_desc& d = p.d;
+
+  const uint32_t bar0 = sb + S::kBars;
+  const uint32_t q_full = bar0;
+  const uint32_t k_full = bar0 + 8, k_empty = bar0 + 16, v_full = bar0 + 24, v_empty = bar0 + 32;
+  auto s_full = [&](int t) { return bar0 + 8u * (5 + t); };
+  auto p_full = [&](int t) { return bar0 + 8u * (7 + t); };
+  auto p_empty = [&](int t) { return bar0 + 8u * (9 + t); };
+  auto a_full = [&](int t) { return bar0 + 8u * (11 + t); };
+  auto a_empty = [&](int t) { return bar0 + 8u * (13 + t); };
+  auto o_scaled = [&](int t) { return bar0 + 8u * (15 + t); };
+  auto pv_done = [&](int t) { return bar0 + 8u * (17 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* alpha_s = reinterpret_cast<float*>(smem + S::kAlpha);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_head = head / (d.hq / d.hkv);
+  const int n_q_tiles = (d.sq + kFaTile - 1) / kFaTile;
+  const int qt0 = q_pair * 2;
+  const bool has1 = qt0 + 1 < n_q_tiles;
+  const int q_row0 = qt0 * kFaTile;
+  const int q_seg = q_row0 / d.q_seg_rows;
+  const int q_pos0 = d.q_seg_pos[q_seg] + (q_row0 - q_seg * d.q_seg_rows);   // both tiles lie in one segment
+  const int q_pos_last0 = q_pos0 + kFaTile - 1;
+  const int q_pos_last = q_pos_last0 + (has1 ? kFaTile : 0);                  // last position of the pair
+  const int q_tok0 = batch * d.sq + q_row0;
+  const int kv_tok_base = batch * d.skv;
+  // tile 1 sees every KV tile of the pair's walk; tile 0 only those that start at or before its last row
+  auto need0 = [&](int kp) { return !(d.causal && kp > q_pos_last0); };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if ((sb & 1023u) != 0) {
+      *abort_flag = 1;
+      record_status(p.status, kStatusBadArgument, 602, 0, 0, 1, 0);
+    }
+    mbar_init(q_full, 1);
+    mbar_init(k_full, 1); mbar_init(k_empty, 1); mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), 4); mbar_init(p_empty(t), 1);
+      mbar_init(a_full(t), 4); mbar_init(a_empty(t), 4);
+      mbar_init(o_scaled(t), 4); mbar_init(pv_done(t), 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  auto tmem_s = [&](int t) { return tmem_base + t * 128; };
+  auto tmem_o = [&](int t) { return tmem_base + 256 + t * D; };
+  const bool bad = *abort_flag != 0;
+
+  if (bad) {
+    // common exit
+  } else if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, (has1 ? 2 : 1) * S::kTileBytes);
+      for (int t = 0; t < (has1 ? 2 : 1); ++t)
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+          tma_load_3d(sb + S::kQ + t * S::kTileBytes + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0 + t * kFaTile);
+      bool ok = true;
+      int last_seg = -1;
+      for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
+        if (!ok) return;
+        const uint32_t ph = j & 1;
+        if (seg != last_seg) {
+          last_seg = seg;
+          if (d.kv_seg_ready != nullptr && d.kv_seg_flag[seg] >= 0) {
+            if (!wait_flag_ge(d.kv_seg_ready + d.kv_seg_flag[seg], d.ready_epoch, p.budget_ns)) {
+              *abort_flag = 1;
+              record_status(p.status, kStatusPeerTimeout, 602, 0, seg, 10, j);
+              ok = false;
+              return;
+            }
+            fence_proxy_async_all();
+          }
+        }
+        if (!mbar_wait(k_empty, ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+        mbar_expect_tx(k_full, S::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+          tma_load_3d(sb + S::kK + a * kAtomBytes, &tmap_k, k_full, a * 64, kv_head, kv_tok_base + row);
+        if (!mbar_wait(v_empty, ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+        mbar_expect_tx(v_full, S::kTileBytes);
+#pragma unroll
+        for (int a = 0; a < kAtoms; ++a)
+          tma_load_3d(sb + S::kV + a * kAtomBytes, &tmap_v, v_full, a * 64, kv_head, kv_tok_base + row);
+      });
+      if (!ok) record_status(p.status, kStatusMbarTimeout, 602, 0, 0, 11, 0);
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc(kFaTile, kFaTile, 1, 1, 0, 0);
+      constexpr uint32_t idesc_o = make_idesc(kFaTile, D, 1, 1, 0, 1);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.budget_ns);
+      int pv[2] = {0, 0};         // P V products issued per tile
+      auto issue_s = [&](int t) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          umma_f16_ss(tmem_s(t), make_smem_desc_sw128_kmajor(sb + S::kQ + t * S::kTileBytes + off),
+                      make_smem_desc_sw128_kmajor(sb + S::kK + off), idesc_s, k != 0);
+        }
+        umma_commit(s_full(t));
+      };
+      // P_t of step pv[t] is in shared memory, so S_t in TMEM has been read for the last time
+      auto wait_p = [&](int t) { return mbar_wait(p_full(t), pv[t] & 1, abort_flag, p.budget_ns); };
+      auto issue_pv = [&](int t) {
+        if (!mbar_wait(o_scaled(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int k = 0; k < kFaTile / 16; ++k) {
+          const uint32_t poff = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          const uint64_t dv = make_smem_desc_sw128_mnmajor(sb + S::kV + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_o(t), make_smem_desc_sw128_kmajor(sb + S::kP + t * S::kPBytes + poff), dv, idesc_o,
+                      (k != 0) || (pv[t] != 0));
+        }
+        umma_commit(p_empty(t));
+        umma_commit(pv_done(t));
+        ++pv[t];
+        return true;
+      };
+      // One walk over the KV tiles with a one-tile lookahead: when tile j is visited, the S products of tile j and the
+      // P V products of tile j-1 are issued. Per Q tile the next S goes out FIRST (its TMEM columns are free as soon as
+      // P is written), so a softmax warpgroup waits for one product, not two, before its next tile; the other Q tile's
+      // products fill the tensor core meanwhile.
+      int prev_kp = 0;
+      const int n = for_each_kv_tile(d, q_pos_last, [&](int j, int /*row*/, int kp, int /*valid*/, int /*seg*/) {
+        if (!ok) return;
+        if (!mbar_wait(k_full, j & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+        if (j == 0) {
+          if (need0(kp)) issue_s(0);
+          if (has1) issue_s(1);
+          umma_commit(k_empty);
+          prev_kp = kp;
+          return;
+        }
+        const bool pv0 = need0(prev_kp);
+        if (pv0 && !wait_p(0)) { ok = false; return; }
+        if (need0(kp)) issue_s(0);
+        if (!has1) umma_commit(k_empty);
+        if (!mbar_wait(v_full, (j - 1) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+        if (pv0 && !issue_pv(0)) { ok = false; return; }
+        if (has1) {
+          if (!wait_p(1)) { ok = false; return; }
+          issue_s(1);
+          umma_commit(k_empty);
+          if (!issue_pv(1)) { ok = false; return; }
+        }
+        umma_commit(v_empty);
+        prev_kp = kp;
+      });
+      if (ok && n > 0) {
+        ok = mbar_wait(v_full, (n - 1) & 1, abort_flag, p.budget_ns);
+        if (ok && need0(prev_kp)) ok = wait_p(0) && issue_pv(0);
+        if (ok && has1) ok = wait_p(1) && issue_pv(1);
+      }
+      if (!ok) record_status(p.status, kStatusMbarTimeout, 602, 0, 0, 20, 0);
+    }
+    __syncwarp();
+  } else if (warp < 4) {
+    // idle
+  } else if (warp < 12) {
+    // ------------------------------ softmax of tile t (thread = row) ------------------------------
+    const int t = (warp >= 8) ? 1 : 0;
+    if (t == 0 || has1) {
+      const int q4 = warp & 3;
+      const int row = q4 * 32 + lane;
+      const int my_pos = q_pos0 + t * kFaTile + row;
+      const int tile_row0 = q_row0 + t * kFaTile;
+      const float scale2 = d.scale * kLog2e;
+      float m_run = -INFINITY, l_run = 0.f;
+      bool ok = true;
+      int cnt = 0;
+      const uint32_t s_row = tmem_s(t) + (static_cast<uint32_t>(q4 * 32) << 16);
+      for_each_kv_tile(d, q_pos_last, [&](int /*j*/, int /*rowbuf*/, int kp, int valid, int /*seg*/) {
+        if (!ok) return;
+        if (t == 0 && !need0(kp)) return;
+        const uint32_t ph = cnt & 1;
+        ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after_sync();
+        const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_row + cc * 32, r);
+          tmem_ld_wait();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = cc * 32 + i;
+              if (!(col >= valid || (d.causal && kp + col > my_pos))) mx = fmaxf(mx, __uint_as_float(r[i]));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+          }
+        }
+        mx *= scale2;
+        // The offset used for the exponentials follows the row maximum lazily: it moves only when the maximum has grown
+        // by more than 8 (a factor 256 in the exponentials, harmless in fp32 sums and bf16 P), so rescaling the
+        // accumulator becomes rare; the row sum carries the same offset, which keeps O / l and the log-sum-exp exact.
+        const float m_new = (mx > m_run + 8.f) ? mx : m_run;
+        const bool dead = m_new == -INFINITY;
+        const float alpha = (dead || m_new == m_run) ? 1.f : fast_exp2(m_run - m_new);
+        const float m_use = dead ? 0.f : m_new;
+        // publish alpha for the correction warps as early as possible
+        ok = mbar_wait(a_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        alpha_s[t * kFaTile + row] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(t));
+        ok = mbar_wait(p_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        const uint32_t prow = sb + S::kP + t * S::kPBytes + static_cast<uint32_t>(row) * 128u;
+        float sum = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_row + cc * 32, r);
+          tmem_ld_wait();
+          float pvv[32];
+          if (need_mask || dead) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = cc * 32 + i;
+              const bool masked = dead || col >= valid || (d.causal && kp + col > my_pos);
+              pvv[i] = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(r[i]), scale2, -m_use));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pvv[i] = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, -m_use));
+          }
+          float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < 32; ++i) part[i & 3] += pvv[i];
+          sum += (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = cc * 4 + g;
+            const uint32_t atom = (chunk >> 3) * kAtomBytes;
+            const uint32_t dst = prow + atom + (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16x2(pvv[8 * g], pvv[8 * g + 1])),
+                         "r"(pack_bf16x2(pvv[8 * g + 2], pvv[8 * g + 3])), "r"(pack_bf16x2(pvv[8 * g + 4], pvv[8 * g + 5])),
+                         "r"(pack_bf16x2(pvv[8 * g + 6], pvv[8 * g + 7]))
+                         : "memory");
+          }
+        }
+        l_run = l_run * alpha + sum;
+        m_run = m_new;
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(t));
+        ++cnt;
+      });
+      // epilogue: O_t / l -> bf16
+      const bool row_ok = tile_row0 + row < d.sq;
+      if (ok && cnt > 0) {
+        ok = mbar_wait(pv_done(t), (cnt - 1) & 1, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        if (cnt > 0) tc_fence_after_sync();
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        if (p.lse != nullptr && row_ok)
+          p.lse[(static_cast<long long>(batch) * d.hq + head) * d.sq + tile_row0 + row] =
+              (l_run > 0.f) ? (m_run + log2f(l_run)) * kLn2 : -INFINITY;
+        __nv_bfloat16* dst = p.out + (static_cast<long long>(q_tok0 + t * kFaTile + row) * d.hq + head) * D;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t r[32];
+          if (cnt > 0) {
+            tmem_ld_32x32(tmem_o(t) + (static_cast<uint32_t>(q4 * 32) << 16) + cc * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              U4 u{pack_bf16x2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv),
+                   pack_bf16x2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv),
+                   pack_bf16x2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv),
+                   pack_bf16x2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv)};
+              st_global_v4(dst + cc * 32 + i, u);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        record_status(p.status, kStatusMbarTimeout, 602, 0, 0, 30 + t, 0);
+      }
+    }
+  } else {
+    // ------------------------------ correction (thread = row, both tiles) ------------------------------
+    const int q4 = warp & 3;
+    const int row = q4 * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+    int cnt[2] = {0, 0};
+    bool ok = true;
+    for_each_kv_tile(d, q_pos_last, [&](int /*j*/, int /*rowbuf*/, int kp, int /*valid*/, int /*seg*/) {
+      for (int t = 0; t < 2 && ok; ++t) {
+        if (t == 0 ? !need0(kp) : !has1) continue;
+        const uint32_t ph = cnt[t] & 1;
+        ok = mbar_wait(a_full(t), ph, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float alpha = alpha_s[t * kFaTile + row];
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_empty(t));
+        if (cnt[t] > 0) {
+          // the accumulator may only be touched once the previous P V product has landed in it
+          ok = mbar_wait(pv_done(t), (cnt[t] - 1) & 1, abort_flag, p.budget_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          if (__any_sync(0xffffffffu, alpha != 1.f)) {
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cc = 0; cc < D / 32; ++cc) {
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_o(t) + lane_off + cc * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(tmem_o(t) + lane_off + cc * 32, r);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_scaled(t));
+        ++cnt[t];
+      }
+    });
+    if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 602, 0, 0, 40, 0);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  fa_fwd2_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
 template <int D>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -521,6 +937,28 @@ fa_fwd_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd2_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const FaCommArgs a) {
+  if ((int)blockIdx.x < a.comm_blocks) {
+    fa_push_role(a);
+    return;
+  }
+  const int pairs = (a.num_q_tiles + 1) / 2;
+  const int id = blockIdx.x - a.comm_blocks;
+  const int qp = pairs - 1 - id % pairs;
+  const int hb = id / pairs;
+  fa_fwd2_cta<D>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
+}
+
+// The two-tile form needs both tiles of a pair in one position run; PKB_FA_ONE_TILE=1 forces the one-tile kernel.
+static bool fa_use_pairs(const pkb_attn_desc& d) {
+  static const bool forced_off = [] { const char* e = getenv("PKB_FA_ONE_TILE"); return e != nullptr && e[0] == '1'; }();
+  if (forced_off) return false;
+  return d.num_q_segs == 1 || d.q_seg_rows % (2 * kFaTile) == 0;
+}
+
+template <int D>
 static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, void* out, void* lse,
                      cudaStream_t stream) {
   const pkb_attn_desc& d = *desc;
@@ -543,11 +981,20 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
   p.trace = reinterpret_cast<long long*>(d.trace);
   p.trace_capacity = d.trace_capacity;
-  auto kern = fa_fwd_kernel<D>;
-  constexpr int smem = FaSmem<D>::kTotal;
-  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  dim3 grid((d.sq + kFaTile - 1) / kFaTile, d.hq, d.batch);
-  kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+  const int n_tiles = (d.sq + kFaTile - 1) / kFaTile;
+  if (fa_use_pairs(d) && p.trace == nullptr) {
+    auto kern = fa_fwd2_kernel<D>;
+    constexpr int smem = Fa2Smem<D>::kTotal;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+  } else {
+    auto kern = fa_fwd_kernel<D>;
+    constexpr int smem = FaSmem<D>::kTotal;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    dim3 grid(n_tiles, d.hq, d.batch);
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+  }
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -629,11 +1076,19 @@ static int launch_fa_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, cons
   p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
   p.trace = nullptr;
   p.trace_capacity = 0;
-  auto kern = fa_fwd_ring_kernel<D>;
-  constexpr int smem = FaSmem<D>::kTotal;
-  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  const int grid = comm_blocks + a.num_q_tiles * d.hq * d.batch;
-  kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+  if (fa_use_pairs(d)) {
+    auto kern = fa_fwd2_ring_kernel<D>;
+    constexpr int smem = Fa2Smem<D>::kTotal;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = comm_blocks + ((a.num_q_tiles + 1) / 2) * d.hq * d.batch;
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+  } else {
+    auto kern = fa_fwd_ring_kernel<D>;
+    constexpr int smem = FaSmem<D>::kTotal;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int grid = comm_blocks + a.num_q_tiles * d.hq * d.batch;
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+  }
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
