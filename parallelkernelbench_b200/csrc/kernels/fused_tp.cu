@@ -261,7 +261,9 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   a.sub_per_shard = rows / a_chunk_rows;
   a.epoch = epoch;
   a.local_in_place = (x_local == g_local + (long long)h->grank * rows * K * 2) ? 1 : 0;
-  if (comm_ctas <= 0) comm_ctas = W > 1 ? 8 : 2;
+  // pushing (W-1) copies of the shard must keep pace with the GEMM that consumes them: at 8 ranks 8 CTAs (~400 GB/s of
+  // 16-byte stores) fall behind, so more SMs go to the push
+  if (comm_ctas <= 0) comm_ctas = W >= 8 ? 16 : (W > 1 ? 8 : 2);
   comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
   const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");

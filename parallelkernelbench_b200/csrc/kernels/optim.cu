@@ -51,17 +51,28 @@ __global__ void __launch_bounds__(256) fsdp_adamw_fp8_kernel(const FsdpAdamArgs 
     }
     float wnew[4];
     float amax = 0.f;
+    // master weights and moments move as 16-byte vectors (i0 is a multiple of 4 elements)
+    const float4 p4 = *reinterpret_cast<const float4*>(a.p + i0);
+    const float4 m4 = *reinterpret_cast<const float4*>(a.m + i0);
+    const float4 v4 = *reinterpret_cast<const float4*>(a.v + i0);
+    const float pin[4] = {p4.x, p4.y, p4.z, p4.w}, min_[4] = {m4.x, m4.y, m4.z, m4.w}, vin[4] = {v4.x, v4.y, v4.z, v4.w};
+    float mo[4], vo[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float grad = g[j] * a.grad_scale;
-      float w = a.p[i0 + j] * (1.0f - a.lr * a.weight_decay);
-      const float mi = a.beta1 * a.m[i0 + j] + (1.0f - a.beta1) * grad;
-      const float vi = a.beta2 * a.v[i0 + j] + (1.0f - a.beta2) * grad * grad;
+      float w = pin[j] * (1.0f - a.lr * a.weight_decay);
+      const float mi = a.beta1 * min_[j] + (1.0f - a.beta1) * grad;
+      const float vi = a.beta2 * vin[j] + (1.0f - a.beta2) * grad * grad;
       w -= a.lr * (mi / a.bias_c1) / (sqrtf(vi / a.bias_c2) + a.eps);
-      a.p[i0 + j] = w; a.m[i0 + j] = mi; a.v[i0 + j] = vi;
+      mo[j] = mi; vo[j] = vi;
       wnew[j] = w;
       amax = fmaxf(amax, fabsf(w));
-      if (a.p_bf16) a.p_bf16[i0 + j] = __float2bfloat16_rn(w);
+    }
+    *reinterpret_cast<float4*>(a.p + i0) = make_float4(wnew[0], wnew[1], wnew[2], wnew[3]);
+    *reinterpret_cast<float4*>(a.m + i0) = make_float4(mo[0], mo[1], mo[2], mo[3]);
+    *reinterpret_cast<float4*>(a.v + i0) = make_float4(vo[0], vo[1], vo[2], vo[3]);
+    if (a.p_bf16) {
+      *reinterpret_cast<uint2*>(a.p_bf16 + i0) = make_uint2(pack_bf16x2(wnew[0], wnew[1]), pack_bf16x2(wnew[2], wnew[3]));
     }
     amax = warp_max(amax);
     float s = amax / 448.0f;
