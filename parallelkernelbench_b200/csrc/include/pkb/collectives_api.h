@@ -30,6 +30,13 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
                     unsigned long long stage_off, unsigned int src_mask, long long in_base,
                     long long in_member_stride, long long seg_bytes, void* out, long long out_stride,
                     int active, int max_blocks, void* stream);
+// Latency-optimised all-reduce (bf16 / fp32, at most cap_units 4-byte words): data and an epoch word travel in one
+// 8-byte store, no barrier. ll_off: header (16 bytes, zero at first use) + 2 * gsize * cap_units * 8 bytes in the heap.
+int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n, unsigned long long ll_off,
+                          long long cap_units, void* out, double scale, void* stream);
+// All-gather of `words` 4-byte words per member with the same no-barrier exchange; out is [gsize, words].
+int pkb_coll_allgather_ll(const pkb_symm_ctx* h, const void* src, long long words, unsigned long long ll_off,
+                          long long cap_units, void* out, void* stream);
 int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n,
                                unsigned long long stage_off, unsigned long long result_off, void* out,
                                int src_in_heap, double scale, int max_blocks, void* stream);

@@ -320,6 +320,151 @@ coll_a2a_perm_kernel(const SymmCtx c, const A2APermArgs a) {
 }
 
 // ================================================================================================
+// latency-optimised all-reduce for small messages: every 4 bytes of data travel with a 4-byte epoch word in ONE 8-byte
+// store straight into the receiver's slot for this sender, and the receiver polls the words it is about to reduce.
+// There is no barrier at all: the cost is one kernel launch plus one one-way NVLink store. Two slots alternate by the
+// parity of the epoch, which is enough because a rank can run at most one call ahead of any peer (it needs the peer's
+// data of the current call to finish it). The epoch lives in the heap and is advanced by the last block of each call.
+// Layout at ll_off: header {uint32 epoch, uint32 done_blocks, pad to 16 B}, then [2 parities][gsize sources][cap units] x 8 B.
+// ================================================================================================
+struct LLArgs {
+  const void* src;
+  long long n;          // elements
+  uint64_t ll_off;
+  long long cap_units;  // 4-byte data words per (parity, source) slot
+  void* out;
+  float scale;
+};
+
+__device__ __forceinline__ void st_volatile_v2(void* p, uint32_t a, uint32_t b) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(kCollThreads)
+coll_allreduce_ll_kernel(const SymmCtx c, const LLArgs a) {
+  uint32_t* hdr = symm_local<uint32_t>(c, a.ll_off);
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(hdr) + 1u;   // advanced only after every block has read it
+  const uint32_t parity = epoch & 1u;
+  const long long elems_per_word = DT == kCollF32 ? 1 : 2;
+  const long long units = (a.n + elems_per_word - 1) / elems_per_word;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const uint64_t slots = a.ll_off + 16;
+  const uint64_t my_slot = slots + (((uint64_t)parity * c.gsize + c.grank) * a.cap_units) * 8;
+  // send: my words into slot [parity][me] of every member (my own copy included: one code path, one rounding order)
+  for (long long i = tid; i < units; i += nthreads) {
+    uint32_t w;
+    if (DT == kCollF32) {
+      w = static_cast<const uint32_t*>(a.src)[i];
+    } else {
+      const uint16_t* s16 = static_cast<const uint16_t*>(a.src);
+      const uint32_t lo = s16[2 * i], hi = (2 * i + 1 < a.n) ? s16[2 * i + 1] : 0u;
+      w = lo | (hi << 16);
+    }
+    for (int g = 0; g < c.gsize; ++g) st_volatile_v2(symm_ptr<uint8_t>(c, c.members[g], my_slot) + i * 8, w, epoch);
+  }
+  // receive + reduce: poll the (data, epoch) pairs of every source in member order
+  bool ok = true;
+  for (long long i = tid; i < units && ok; i += nthreads) {
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int g = 0; g < c.gsize && ok; ++g) {
+      const uint8_t* p = symm_local<uint8_t>(c, slots + (((uint64_t)parity * c.gsize + g) * a.cap_units) * 8) + i * 8;
+      uint2 v = ld_volatile_v2(p);
+      if (v.y != epoch) {
+        const long long t0 = clock64();
+        while ((v = ld_volatile_v2(p)).y != epoch) {
+          if (clock64() - t0 > budget_cycles(c.budget_ns)) {
+            record_status(c.status, kStatusPeerTimeout, 208, c.rank, c.members[g], 1, epoch);
+            ok = false;
+            break;
+          }
+        }
+      }
+      float x0, x1 = 0.f;
+      if (DT == kCollF32) {
+        x0 = __uint_as_float(v.x);
+      } else {
+        const float2 f = unpack_bf16x2(v.x);
+        x0 = f.x; x1 = f.y;
+      }
+      if (g == 0) { acc0 = x0; acc1 = x1; }
+      else { acc0 = combine<OP>(acc0, x0); acc1 = combine<OP>(acc1, x1); }
+    }
+    if (!ok) break;
+    acc0 *= a.scale; acc1 *= a.scale;
+    if (DT == kCollF32) {
+      static_cast<float*>(a.out)[i] = acc0;
+    } else {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(a.out);
+      o[2 * i] = __float2bfloat16_rn(acc0);
+      if (2 * i + 1 < a.n) o[2 * i + 1] = __float2bfloat16_rn(acc1);
+    }
+  }
+  // the last block to finish advances the epoch for the next call (kernels of one stream do not overlap)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(hdr + 1, 1u) + 1u;
+    if (done == gridDim.x) {
+      hdr[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(hdr) = epoch;
+    }
+  }
+}
+
+// The same exchange without the reduction: out[g] = the words of member g (small all-gathers: counts, row statistics).
+__global__ void __launch_bounds__(kCollThreads)
+coll_allgather_ll_kernel(const SymmCtx c, const LLArgs a) {
+  uint32_t* hdr = symm_local<uint32_t>(c, a.ll_off);
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(hdr) + 1u;
+  const uint32_t parity = epoch & 1u;
+  const long long units = a.n;       // 4-byte words per member
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const uint64_t slots = a.ll_off + 16;
+  const uint64_t my_slot = slots + (((uint64_t)parity * c.gsize + c.grank) * a.cap_units) * 8;
+  for (long long i = tid; i < units; i += nthreads) {
+    const uint32_t w = static_cast<const uint32_t*>(a.src)[i];
+    for (int g = 0; g < c.gsize; ++g) st_volatile_v2(symm_ptr<uint8_t>(c, c.members[g], my_slot) + i * 8, w, epoch);
+  }
+  bool ok = true;
+  for (long long i = tid; i < units * c.gsize && ok; i += nthreads) {
+    const int g = (int)(i / units);
+    const long long u = i - (long long)g * units;
+    const uint8_t* p = symm_local<uint8_t>(c, slots + (((uint64_t)parity * c.gsize + g) * a.cap_units) * 8) + u * 8;
+    uint2 v = ld_volatile_v2(p);
+    if (v.y != epoch) {
+      const long long t0 = clock64();
+      while ((v = ld_volatile_v2(p)).y != epoch) {
+        if (clock64() - t0 > budget_cycles(c.budget_ns)) {
+          record_status(c.status, kStatusPeerTimeout, 209, c.rank, c.members[g], 1, epoch);
+          ok = false;
+          break;
+        }
+      }
+    }
+    if (ok) static_cast<uint32_t*>(a.out)[i] = v.x;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(hdr + 1, 1u) + 1u;
+    if (done == gridDim.x) {
+      hdr[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(hdr) = epoch;
+    }
+  }
+}
+
+// ================================================================================================
 // two-shot all-reduce: reduce own slice -> publish -> gather all slices
 // ================================================================================================
 struct TwoShotArgs {
@@ -585,6 +730,45 @@ int pkb_coll_a2a_permute(const pkb_symm_ctx* h, const void* src, long long stage
   const long long moved = extents[0] * extents[1] * extents[2] * inner_bytes * h->gsize;
   const int grid = grid_for(moved > stage_bytes ? moved : stage_bytes, max_blocks);
   coll_a2a_perm_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n, unsigned long long ll_off,
+                          long long cap_units, void* out, double scale, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG(dtype == kCollBf16 || dtype == kCollF32, "the latency-optimised all-reduce takes bf16 or fp32");
+  PKB_CHECK_ARG((ll_off & 15) == 0 && n >= 1, "heap offset misaligned or empty input");
+  const long long units = dtype == kCollF32 ? n : (n + 1) / 2;
+  PKB_CHECK_ARG(units <= cap_units, "message larger than the slot");
+  LLArgs a{src, n, ll_off, cap_units, out, (float)scale};
+  int grid = (int)((units + 4 * kCollThreads - 1) / (4 * kCollThreads));
+  if (grid < 1) grid = 1;
+  if (grid > 32) grid = 32;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SymmCtx c = to_ctx(h);
+#define PKB_LL(DT)                                                                              \
+  switch (op) {                                                                                 \
+    case kCollSum: coll_allreduce_ll_kernel<DT, kCollSum><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    case kCollMax: coll_allreduce_ll_kernel<DT, kCollMax><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    case kCollMin: coll_allreduce_ll_kernel<DT, kCollMin><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    default: set_last_error("unknown reduce op"); return kApiBadArgument;                       \
+  }
+  if (dtype == kCollBf16) { PKB_LL(kCollBf16); } else { PKB_LL(kCollF32); }
+#undef PKB_LL
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_allgather_ll(const pkb_symm_ctx* h, const void* src, long long words, unsigned long long ll_off,
+                          long long cap_units, void* out, void* stream) {
+  if (int rc = check_ctx(h)) return rc;
+  PKB_CHECK_ARG((ll_off & 15) == 0 && words >= 1 && words <= cap_units, "heap offset misaligned or message larger than the slot");
+  LLArgs a{src, words, ll_off, cap_units, out, 1.0f};
+  int grid = (int)((words * h->gsize + 4 * kCollThreads - 1) / (4 * kCollThreads));
+  if (grid < 1) grid = 1;
+  if (grid > 32) grid = 32;
+  coll_allgather_ll_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -18,6 +18,8 @@ from .. import _native as nv
 from ..parallel.symm_heap import SymmGroup, SymmTensor
 
 ONE_SHOT_MAX_BYTES = 512 * 1024
+LL_MAX_BYTES = 1024 * 1024        # data + epoch in one 8-byte store, no barrier (twice the bytes on the wire)
+LL_AUTO_BYTES = 256 * 1024        # chosen automatically up to here (measured: 6.8 us vs NCCL 14.2 at 4 KiB, 9.4 vs 17.9 at 64 KiB, 23.6 vs 20.5 at 1 MiB)
 _DT = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2, torch.float16: 3, torch.int32: 4, torch.int64: 5}
 _OP = {"sum": 0, "max": 1, "min": 2}
 
@@ -48,6 +50,19 @@ def barrier(group: SymmGroup, blocks: int = 1) -> None:
     nv.count_launch()
 
 
+def _ll_slots(group: SymmGroup, nbytes: int):
+    """Slots of the no-barrier exchange for messages of up to ``nbytes`` (three size classes, each with its own epoch)."""
+    cap_bytes = 64 * 1024 if nbytes <= 64 * 1024 else (256 * 1024 if nbytes <= 256 * 1024 else LL_MAX_BYTES)
+    cap_units = cap_bytes // 4
+    key = ("ll_slots", group.channel, cap_units)
+    fresh = key not in group.heap._named
+    buf = group.heap.named(key, (16 + 2 * group.size * cap_units * 8,), torch.uint8)
+    if fresh:                           # epoch words must start at zero everywhere before the first exchange
+        buf.local.zero_()
+        barrier(group)
+    return buf, cap_units
+
+
 def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Tensor | None = None,
                algo: str = "auto", scale: float = 1.0, max_blocks: int = 0) -> torch.Tensor:
     x = _check(x)
@@ -59,10 +74,21 @@ def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Te
     nbytes = n * x.element_size()
     nvls_ok = (group.heap.mc_base != 0 and group.is_whole_heap and op == "sum" and scale == 1.0
                and x.dtype in (torch.bfloat16, torch.float32))
+    ll_ok = nbytes <= LL_MAX_BYTES and x.dtype in (torch.bfloat16, torch.float32) and group.size > 1
     if algo == "auto":
-        algo = "oneshot" if nbytes <= ONE_SHOT_MAX_BYTES or group.size == 1 else ("nvls" if nvls_ok else "twoshot")
-    off, stage_bytes = _stage(group, "ar_in", x)
+        algo = "ll" if (ll_ok and nbytes <= LL_AUTO_BYTES) else ("oneshot" if nbytes <= ONE_SHOT_MAX_BYTES or group.size == 1
+                                   else ("nvls" if nvls_ok else "twoshot"))
     lib = _lib()
+    if algo == "ll":
+        if not ll_ok:
+            raise RuntimeError("the latency-optimised all-reduce takes bf16/fp32 messages of at most 1 MiB on 2+ ranks")
+        buf, cap_units = _ll_slots(group, nbytes)
+        nv.check(lib.pkb_coll_allreduce_ll(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x), nv.c_ll(n), ctypes.c_ulonglong(buf.offset),
+                                           nv.c_ll(cap_units), nv.ptr(out), ctypes.c_double(scale), nv.current_stream()),
+                 "pkb_coll_allreduce_ll")
+        nv.count_launch()
+        return out
+    off, stage_bytes = _stage(group, "ar_in", x)
     if algo == "oneshot":
         nv.check(lib.pkb_coll_reduce(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x),
                                      nv.c_ll(n if stage_bytes else 0), ctypes.c_ulonglong(off), nv.c_ll(0),
@@ -137,6 +163,12 @@ def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = Non
     if out is None:
         out = torch.empty((W, *x.shape), dtype=x.dtype, device=x.device)
     nb = x.numel() * x.element_size()
+    if W > 1 and 0 < nb <= LL_MAX_BYTES // 4 and nb % 4 == 0 and x.data_ptr() % 4 == 0 and out.is_contiguous():
+        buf, cap_units = _ll_slots(group, nb)
+        nv.check(_lib().pkb_coll_allgather_ll(group.ref, nv.ptr(x), nv.c_ll(nb // 4), ctypes.c_ulonglong(buf.offset), nv.c_ll(cap_units),
+                                              nv.ptr(out), nv.current_stream()), "pkb_coll_allgather_ll")
+        nv.count_launch()
+        return out
     _gather_call(group, x, (1 << W) - 1, 0, 0, nb, out, nb, True, "ag_in")
     return out
 

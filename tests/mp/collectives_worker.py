@@ -40,9 +40,9 @@ def main() -> int:
             ref = x.clone()
             dist.all_reduce(ref)
             tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
-            algos = ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else [])
+            algos = ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []) + (["ll"] if n * x.element_size() <= (1 << 20) and W > 1 else [])
             for algo in algos:
-                if algo != "oneshot" and n % 8 != 0:
+                if algo not in ("oneshot", "ll") and n % 8 != 0:
                     continue
                 y = C.all_reduce(x, g, algo=algo)
                 torch.cuda.synchronize()
@@ -67,6 +67,17 @@ def main() -> int:
     ref = torch.empty(W, 513, 64, device=dev, dtype=torch.bfloat16)
     dist.all_gather_into_tensor(ref.view(W * 513, 64), x)
     report("all_gather", torch.equal(C.all_gather(x, g), ref))
+    for rows in (1, 7, 4096):                     # no-barrier path (small), and the staged path (large)
+        x = torch.randn(rows, 96, device=dev, dtype=torch.float32, generator=gen)
+        ref = torch.empty(W, rows, 96, device=dev)
+        dist.all_gather_into_tensor(ref.view(W * rows, 96), x)
+        report(f"all_gather fp32 rows={rows}", torch.equal(C.all_gather(x, g), ref))
+    same = True
+    for i in range(30):                            # back-to-back calls of alternating sizes: epochs and slot parity
+        xi = torch.full((16 + (i % 3) * 5,), float(r * 100 + i), device=dev)
+        got = C.all_gather(xi, g)
+        same &= all(bool((got[s] == float(s * 100 + i)).all()) for s in range(W))
+    report("all_gather no-barrier path x30 alternating sizes", same)
     # reduce_scatter
     x = torch.randn(W * 300, 40, device=dev, dtype=torch.float32, generator=gen)
     ref = torch.empty(300, 40, device=dev)
@@ -146,7 +157,7 @@ def main() -> int:
         y = torch.empty_like(x)
         t_nccl = timeit(lambda: dist.all_reduce(y))
         line = f"PERF all_reduce {nbytes}B nccl={t_nccl * 1e3:.1f}us"
-        for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []):
+        for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []) + (["ll"] if nbytes <= (1 << 20) and W > 1 else []):
             if algo == "oneshot" and nbytes > (1 << 24):
                 continue
             t = timeit(lambda: C.all_reduce(x, g, algo=algo, out=y))
@@ -181,13 +192,13 @@ def main() -> int:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
     if W > 1 and "--graphs" in sys.argv:
-        for nbytes in (4096, 1 << 20, 1 << 24, 1 << 27):
+        for nbytes in (4096, 65536, 1 << 20, 1 << 24, 1 << 27):
             xs = heap.named(("perf_x", nbytes), (nbytes // 2,), torch.bfloat16)
             xs.local.normal_()
             y = torch.empty(nbytes // 2, device=dev, dtype=torch.bfloat16)
             yn = xs.local.clone()
             line = f"GRAPH all_reduce {nbytes}B nccl={graph_time(lambda: dist.all_reduce(yn)) * 1e3:.1f}us"
-            for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []):
+            for algo in ["oneshot", "twoshot"] + (["nvls"] if heap.mc_base else []) + (["ll"] if nbytes <= (1 << 20) else []):
                 if algo == "oneshot" and nbytes > (1 << 24):
                     continue
                 line += f" {algo}={graph_time(lambda: C.all_reduce(xs.local, g, algo=algo, out=y)) * 1e3:.1f}us"
