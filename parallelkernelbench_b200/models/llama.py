@@ -91,14 +91,29 @@ class _RMSNorm(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
+        from ..ops import rmsnorm_bwd
+
         x, gamma = ctx.saved_tensors
-        xf, g, dyf = x.float(), gamma.float().reshape(-1), dy.float()
-        rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + ctx.eps)
-        xhat = xf * rstd
-        dg = (dyf * xhat).sum(0, keepdim=True).reshape(gamma.shape)
-        dxhat = dyf * g
-        dx = rstd * (dxhat - xhat * (dxhat * xhat).mean(-1, keepdim=True))
-        return dx.to(x.dtype), dg.to(gamma.dtype), None
+        dx, dg = rmsnorm_bwd(x, gamma, dy.contiguous(), ctx.eps)
+        return dx, dg.to(gamma.dtype).reshape(gamma.shape), None
+
+
+class _SwiGLU(torch.autograd.Function):
+    """``silu(gate) * up`` over the packed [tokens, 2 * ffn] projection, forward and backward in one pass each."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        from ..ops import swiglu_fwd
+
+        ctx.save_for_backward(gu)
+        return swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, da):
+        from ..ops import swiglu_bwd
+
+        (gu,) = ctx.saved_tensors
+        return swiglu_bwd(gu, da.contiguous())
 
 
 class _Rope(torch.autograd.Function):
@@ -180,7 +195,7 @@ def layer_forward(cfg: LlamaConfig, p: dict, x: torch.Tensor, cos, sin, impl: st
     x = x + lin(att.reshape(S, Hq * d), p["wo"])
     h2 = norm(x, p["norm2"])
     gu = lin(h2, p["wgu"])
-    a = F.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]
+    a = _SwiGLU.apply(gu) if ours else F.silu(gu[:, :cfg.ffn]) * gu[:, cfg.ffn:]
     return x + lin(a.contiguous(), p["wdown"])
 
 
@@ -234,6 +249,11 @@ class _VocabParallelLoss(torch.autograd.Function):
     def backward(ctx, dloss):
         hidden_all, head_shard, logits, lse, targets = ctx.saved_tensors
         n = logits.shape[0]
+        if ctx.ours and logits.dtype == torch.bfloat16 and logits.shape[1] % 8 == 0:
+            from ..ops import ce_backward, gemm_bf16_kn, gemm_bf16_tn
+
+            dlog = ce_backward(logits, lse, targets, ctx.vocab_start, 1.0 / n, upstream=dloss)
+            return gemm_bf16_kn(dlog, head_shard), gemm_bf16_tn(dlog, hidden_all), None, None, None, None
         dlog = torch.exp(logits.float() - lse[:, None])
         t = targets - ctx.vocab_start
         inr = (t >= 0) & (t < logits.shape[1])

@@ -129,3 +129,51 @@ def tp_rmsnorm(x_local: torch.Tensor, gamma_local: torch.Tensor, eps: float, gro
                                           nv.current_stream()), "pkb_tp_rmsnorm")
     nv.count_launch()
     return y.view(x_local.shape)
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    """``gu`` [rows, 2F] bf16 (gate columns, then up columns) -> ``silu(gate) * up`` [rows, F], one pass."""
+    rows, F2 = gu.shape
+    guc = gu.contiguous()
+    out = torch.empty((rows, F2 // 2), dtype=gu.dtype, device=gu.device)
+    nv.check(nv.cuda_lib().pkb_swiglu_fwd(nv.ptr(guc), nv.ptr(out), nv.c_ll(rows), F2 // 2, nv.current_stream()), "pkb_swiglu_fwd")
+    nv.count_launch()
+    return out
+
+
+def swiglu_bwd(gu: torch.Tensor, da: torch.Tensor) -> torch.Tensor:
+    """Gradient of :func:`swiglu_fwd` with respect to ``gu`` ([rows, 2F]), one pass."""
+    rows, F2 = gu.shape
+    guc, dac = gu.contiguous(), da.contiguous()
+    dgu = torch.empty_like(guc)
+    nv.check(nv.cuda_lib().pkb_swiglu_bwd(nv.ptr(guc), nv.ptr(dac), nv.ptr(dgu), nv.c_ll(rows), F2 // 2, nv.current_stream()),
+             "pkb_swiglu_bwd")
+    nv.count_launch()
+    return dgu
+
+
+def rmsnorm_bwd(x: torch.Tensor, gamma: torch.Tensor, dy: torch.Tensor, eps: float):
+    """Backward of ``y = x * rsqrt(mean(x^2) + eps) * gamma`` for bf16 ``x, dy`` [rows, H]: returns (dx bf16, dgamma fp32)."""
+    rows, H = x.shape
+    xc, dyc, gc = x.contiguous(), dy.contiguous(), gamma.reshape(-1).contiguous()
+    dx = torch.empty_like(xc)
+    dg = torch.zeros(H, dtype=torch.float32, device=x.device)
+    nv.check(nv.cuda_lib().pkb_rmsnorm_bwd(nv.ptr(xc), nv.ptr(gc), nv.ptr(dyc), nv.ptr(dx), nv.ptr(dg), rows, H, nv.c_float(eps),
+                                           nv.current_stream()), "pkb_rmsnorm_bwd")
+    nv.count_launch()
+    return dx, dg
+
+
+def ce_backward(logits: torch.Tensor, lse: torch.Tensor, target: torch.Tensor, vocab_start: int, scale: float,
+                upstream: torch.Tensor | None = None) -> torch.Tensor:
+    """``(softmax - onehot) * scale`` over a vocabulary shard, from the global log-sum-exp of every row (bf16, one pass).
+    ``upstream`` is an optional fp32 device scalar multiplied in (the incoming gradient of the loss; no host read)."""
+    rows, V = logits.shape
+    lc = logits.contiguous()
+    out = torch.empty_like(lc)
+    nv.check(nv.cuda_lib().pkb_ce_bwd(nv.ptr(lc), nv.ptr(lse.float().contiguous()), nv.ptr(target.contiguous().view(-1).to(torch.int64)),
+                                      nv.ptr(out), nv.c_ll(rows), V, nv.c_ll(vocab_start), nv.c_float(scale),
+                                      nv.ptr(upstream.float().contiguous()) if upstream is not None else None, nv.current_stream()),
+             "pkb_ce_bwd")
+    nv.count_launch()
+    return out

@@ -44,15 +44,17 @@ def main() -> int:
             torch.cuda.synchronize()
             ls.append(float(loss)); ts.append(e0.elapsed_time(e1))
         losses[impl], times[impl] = ls, ts
+        if r == 0:
+            print(f"{impl}: losses {['%.4f' % x for x in ls]} ms/step {['%.1f' % t for t in ts]} peak memory {torch.cuda.max_memory_allocated() / 2**30:.1f} GiB", flush=True)
         del model
+        import gc
+        gc.collect()                      # the engine and its units reference each other
         torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
     fails = 0
     st = nv.read_status()
     if st[0] != 0:
         fails += 1
-    if r == 0:
-        for impl in impls:
-            print(f"{impl}: losses {['%.4f' % x for x in losses[impl]]} ms/step {['%.1f' % t for t in times[impl]]}", flush=True)
     if len(impls) == 2:
         for a, b in zip(losses["ours"], losses["torch"]):
             if abs(a - b) > 0.05 * abs(b) + 0.05:

@@ -110,3 +110,46 @@ def test_fsdp_adamw_fp8_matches_dequant_sum_then_adamw():
     torch.testing.assert_close(pb.float(), pr, rtol=1e-2, atol=1e-4)
     back = fp8_dequantize_1x128(q_out.view(-1, 128), s_out.view(-1, 1), torch.float32).view(-1)
     torch.testing.assert_close(back, pr, rtol=0.07, atol=2e-3)
+
+
+def test_swiglu_forward_backward_match_autograd():
+    from parallelkernelbench_b200.ops import swiglu_bwd, swiglu_fwd
+
+    torch.manual_seed(6)
+    gu = torch.randn(300, 2 * 1024, device="cuda", dtype=torch.bfloat16)
+    da = torch.randn(300, 1024, device="cuda", dtype=torch.bfloat16)
+    ref_in = gu.float().requires_grad_()
+    ref = torch.nn.functional.silu(ref_in[:, :1024]) * ref_in[:, 1024:]
+    ref.backward(da.float())
+    torch.testing.assert_close(swiglu_fwd(gu).float(), ref.detach(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(swiglu_bwd(gu, da).float(), ref_in.grad, rtol=2e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("H", [512, 4096, 8192])
+def test_rmsnorm_backward_matches_autograd(H):
+    from parallelkernelbench_b200.ops import rmsnorm_bwd
+
+    torch.manual_seed(7)
+    rows, eps = 777, 1e-5
+    x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+    g = (1.0 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+    dy = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+    xr, gr = x.float().requires_grad_(), g.float().requires_grad_()
+    y = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + eps) * gr
+    y.backward(dy.float())
+    dx, dg = rmsnorm_bwd(x, g, dy, eps)
+    torch.testing.assert_close(dx.float(), xr.grad, rtol=2e-2, atol=3e-2)
+    torch.testing.assert_close(dg, gr.grad, rtol=1e-2, atol=2e-1)
+
+
+def test_cross_entropy_backward_matches_autograd():
+    from parallelkernelbench_b200.ops import ce_backward
+
+    torch.manual_seed(8)
+    rows, V, start = 64, 1024, 512                      # this "rank" owns vocabulary [512, 1536) of 2048
+    full = torch.randn(rows, 2048, device="cuda")
+    tgt = torch.randint(0, 2048, (rows,), device="cuda")
+    lse = torch.logsumexp(full, -1)
+    ref = (torch.softmax(full, -1) - torch.nn.functional.one_hot(tgt, 2048).float())[:, start:start + V] / rows
+    got = ce_backward(full[:, start:start + V].to(torch.bfloat16), lse, tgt, start, 1.0 / rows)
+    torch.testing.assert_close(got.float(), ref, rtol=3e-2, atol=2e-4)
