@@ -30,7 +30,21 @@ import sys
 import time
 
 from ..utils import env
+
 from . import compare, hygiene, report
+
+def _free_port() -> int:
+    """A TCP port nobody listens on right now (asked from the kernel, so two back-to-back jobs never share one and a
+    port held by an unrelated process is never picked); falls back to a random high port."""
+    import socket
+
+    try:
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sk:
+            sk.bind(("127.0.0.1", 0))
+            return int(sk.getsockname()[1])
+    except OSError:
+        return random.randint(29500, 39500)
+
 
 LOGS_ROOT = os.environ.get("PKB_LOGS_DIR", os.path.join(str(env.REPO_ROOT), "logs"))
 
@@ -50,7 +64,7 @@ def run_job(op: str, impl: str, nproc: int, trial: int = 0, config: str = "defau
             extra_worker_args=None, pg_timeout_s=None) -> dict:
     """Start one torchrun job and wait for it. Never raises; the dict says what happened."""
     job_dir = _job_dir(op, impl, trial)
-    port = random.randint(29500, 39500)
+    port = _free_port()
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
            "-m", "parallelkernelbench_b200.harness.worker", "--op", op, "--impl", impl, "--logs-dir", job_dir,
