@@ -11,9 +11,10 @@
 //
 //   warp 0      TMA producer: K_j, V_j once; Q_i and dO_i per step
 //   warp 1      MMA issuer
-//   warps 4-7   softmax / dS (thread = q row): read S and dP from TMEM, write P and dS as bf16 into 128-byte-swizzled
-//               shared memory; the same [q][kv] tiles serve as K-major A (dS for dQ) and as MN-major A (P^T, dS^T)
-//   warps 8-15  dQ drain (thread = q row, two warpgroups take half of the D columns each), and at the end dV, dK
+//   warps 4-11  softmax / dS (thread = q row; warps 4-7 take KV columns 0-63, warps 8-11 columns 64-127): read S and dP
+//               from TMEM, write P and dS as bf16 into 128-byte-swizzled shared memory; the same [q][kv] tiles serve
+//               as K-major A (dS for dQ) and as MN-major A (P^T, dS^T)
+//   warps 12-15 dQ drain (thread = q row), and at the end dV, dK
 // K_j ([kv][d]) is the K-major B operand of S and the MN-major B operand of dQ; Q_i and dO_i are K-major A operands of
 // S / dP and MN-major B operands of dK / dV: every tile is loaded once and read through two descriptors.
 //
@@ -169,10 +170,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     mbar_init(qdo_full, 1);
     mbar_init(qdo_empty, 1);
     mbar_init(sdp_full, 1);
-    mbar_init(pds_full, 4);
+    mbar_init(pds_full, 8);
     mbar_init(pds_empty, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 8);
+    mbar_init(dq_empty, 4);
     mbar_init(acc_full, 1);
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
@@ -265,6 +266,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         umma_commit(sdp_full);
         if (!mbar_wait(pds_full, ph, abort_flag, p.budget_ns)) { ok = false; break; }
         tc_fence_after_sync();
+        // dQ partial = dS K_j  (K dimension = the 128 kv rows)
+#pragma unroll
+        for (int k = 0; k < kFbTile / 16; ++k) {
+          const uint32_t aoff = (k >> 2) * kAtomBytes + (k & 3) * 32;
+          const uint64_t b_k = make_smem_desc_sw128_mnmajor(sb + S::kK + k * 2048, kAtomBytes);
+          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kDS + aoff), b_k, idesc_dq, k != 0);
+        }
+        umma_commit(dq_full);      // the drain of dQ overlaps the two accumulating products below
         // dV += P^T dO ; dK += dS^T Q   (K dimension = the 128 q rows, 16 per instruction = 2048 bytes of a [row][128 B] atom)
 #pragma unroll
         for (int k = 0; k < kFbTile / 16; ++k) {
@@ -278,16 +287,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           const uint64_t b_q = make_smem_desc_sw128_mnmajor(sb + S::kQ + k * 2048, kAtomBytes);
           umma_f16_ss(tmem_dk, a_ds, b_q, idesc_acc, (step != 0) || (k != 0));
         }
-        // dQ partial = dS K_j  (K dimension = the 128 kv rows)
-#pragma unroll
-        for (int k = 0; k < kFbTile / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          const uint64_t b_k = make_smem_desc_sw128_mnmajor(sb + S::kK + k * 2048, kAtomBytes);
-          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kDS + aoff), b_k, idesc_dq, k != 0);
-        }
         umma_commit(qdo_empty);
         umma_commit(pds_empty);
-        umma_commit(dq_full);
       }
       if (ok) umma_commit(acc_full);
       else record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 20, 0);
@@ -295,9 +296,10 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     __syncwarp();
   } else if (warp < 4) {
     // idle
-  } else if (warp < 8) {
-    // ------------------------------ P and dS (thread = q row) ------------------------------
+  } else if (warp < 12) {
+    // ------------------------------ P and dS (thread = q row, half of the KV columns) ------------------------------
     const int q4 = warp & 3;
+    const int c_begin = (warp >= 8) ? 2 : 0;      // 32-column chunks handled by this warpgroup
     const int row = q4 * 32 + lane;
     const float scale2 = d.scale * kFbLog2e;
     bool ok = true;
@@ -321,7 +323,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       const uint32_t prow = sb + S::kP + static_cast<uint32_t>(row) * 128u;
       const uint32_t dsrow = sb + S::kDS + static_cast<uint32_t>(row) * 128u;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = c_begin + cc;
         uint32_t rs[32], rd[32];
         tmem_ld_32x32(tmem_s + lane_off + c * 32, rs);
         tmem_ld_32x32(tmem_dp + lane_off + c * 32, rd);
@@ -360,8 +363,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     // ------------------------------ dQ drain, then dV / dK (thread = row) ------------------------------
     const int q4 = warp & 3;
     const int row = q4 * 32 + lane;
-    constexpr int DH = D / 2;
-    const int col0 = (warp >= 12) ? DH : 0;
+    constexpr int DH = D;
+    const int col0 = 0;
     const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
     bool ok = !bad;
     for (int step = 0; step < n_steps && ok; ++step) {
