@@ -61,9 +61,19 @@ def final_dir(op: str, impl: str, trial: int, world: int) -> str:
 
 def run_job(op: str, impl: str, nproc: int, trial: int = 0, config: str = "default", overrides=None, dtype="bfloat16",
             backend=None, measure_perf=False, warmup=500, iters=100, graph=False, profile=False, timeout_s=1800.0,
-            extra_worker_args=None, pg_timeout_s=None) -> dict:
-    """Start one torchrun job and wait for it. Never raises; the dict says what happened."""
+            extra_worker_args=None, pg_timeout_s=None, solution: str | None = None) -> dict:
+    """Start one torchrun job and wait for it. Never raises; the dict says what happened.
+    ``impl="file"`` runs the candidate in ``solution`` (a copy staged into the job directory, so that the evaluated
+    source is kept with its outputs)."""
     job_dir = _job_dir(op, impl, trial)
+    if impl == "file":
+        staged = os.path.join(job_dir, "candidate_solution.py")
+        try:
+            shutil.copyfile(solution or "", staged)
+        except OSError as e:
+            return {"returncode": 2, "artifact_count": 0, "job_dir": job_dir, "stdout": "", "stderr": f"cannot stage solution: {e}",
+                    "timed_out": False, "interrupted": False, "elastic_error_files": [], "worker_logs_dir": job_dir, "seconds": 0.0}
+        extra_worker_args = list(extra_worker_args or []) + ["--solution", staged]
     port = _free_port()
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port),
@@ -139,7 +149,7 @@ def _keep(job: dict, world: int) -> str:
 
 
 def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rtol: float | None = None, measure_perf=False,
-            cooldown: float | None = None, **job_kw) -> dict:
+            cooldown: float | None = None, solution: str | None = None, **job_kw) -> dict:
     from ..workloads import registry
 
     spec = registry.get(op)
@@ -151,7 +161,8 @@ def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rto
         hygiene.between_jobs()
         ref_job = run_job(spec.name, "reference", nproc, trial=t, measure_perf=measure_perf, **job_kw)
         time.sleep(cooldown)
-        cand_job = run_job(spec.name, "ours", nproc, trial=t, measure_perf=measure_perf, **job_kw)
+        cand_job = run_job(spec.name, "file" if solution else "ours", nproc, trial=t, measure_perf=measure_perf,
+                           solution=solution, **job_kw)
         cmp = None
         if ref_job["artifact_count"] and cand_job["artifact_count"]:
             cmp = compare.compare_dirs(ref_job["job_dir"], cand_job["job_dir"], atol, rtol, expected_ranks=nproc)
@@ -227,7 +238,7 @@ def cmd_eval(a) -> int:
 
     s = eval_op(a.op, a.nproc, trials=a.trials, atol=a.atol, rtol=a.rtol, measure_perf=a.measure_perf, config=a.config,
                 overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
-                graph=a.graph, profile=a.profile, timeout_s=a.timeout)
+                graph=a.graph, profile=a.profile, timeout_s=a.timeout, solution=a.solution)
     if s["interrupted"]:
         return 130
     return 0 if s["all_ok"] else 1
@@ -310,6 +321,7 @@ def main(argv=None) -> int:
     sp = sub.add_parser("run"); _common(sp, need_impl=True); sp.set_defaults(fn=cmd_run)
     sp = sub.add_parser("eval"); _common(sp)
     sp.add_argument("--trials", type=int, default=5)
+    sp.add_argument("--solution", default=None, help="evaluate this file's solution(rc, *inputs) instead of the built-in implementation")
     sp.add_argument("--atol", type=float, default=None)
     sp.add_argument("--rtol", type=float, default=None)
     sp.set_defaults(fn=cmd_eval)

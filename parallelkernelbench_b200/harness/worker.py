@@ -26,7 +26,8 @@ import torch.distributed as dist
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--op", required=True)
-    ap.add_argument("--impl", required=True, choices=["reference", "ours"])
+    ap.add_argument("--impl", required=True, choices=["reference", "ours", "file"])
+    ap.add_argument("--solution", default=None, help="with --impl file: a Python file that defines solution(rc, *inputs)")
     ap.add_argument("--logs-dir", required=True)
     ap.add_argument("--config", default="default")
     ap.add_argument("--set", action="append", default=[], metavar="KEY=VALUE")
@@ -41,6 +42,23 @@ def parse_args(argv=None):
     ap.add_argument("--fail-rank", type=int, default=-1, help="test hook: this rank raises before the first collective")
     ap.add_argument("--exit-rank", type=int, default=-1, help="test hook: this rank exits non-zero before the first collective")
     return ap.parse_args(argv)
+
+
+def load_solution(path: str):
+    """Import a candidate implementation from a file: it must define ``solution(rc, *inputs)`` with the same inputs and
+    outputs as the op's reference (``rc`` is the :class:`RunCtx`: rank, world, device, ``rc.comm`` for the symmetric-heap
+    collectives). Same role as the solution loader of the reference's worker (reference: scripts/worker.py:109-115)."""
+    import importlib.util
+
+    if not path or not os.path.isfile(path):
+        raise FileNotFoundError(f"solution file not found: {path!r}")
+    spec = importlib.util.spec_from_file_location("pkb_candidate_solution", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    fn = getattr(mod, "solution", None)
+    if not callable(fn):
+        raise AttributeError(f"{path} does not define a callable `solution(rc, *inputs)`")
+    return fn
 
 
 def run_worker(args) -> int:
@@ -64,7 +82,10 @@ def run_worker(args) -> int:
         cfg = spec.config(args.config, registry.parse_overrides(args.set))
         dtype = registry.DTYPES[args.dtype]
         run = registry.RunCtx(ctx, spec.name, trial=args.trial, dtype=dtype)
-        impl = spec.reference if args.impl == "reference" else spec.ours
+        if args.impl == "file":
+            impl = load_solution(args.solution)
+        else:
+            impl = spec.reference if args.impl == "reference" else spec.ours
         if impl is None:
             raise NotImplementedError(f"op {spec.name} has no '{args.impl}' implementation")
         if args.impl == "ours" and spec.ours_needs_cuda and not ctx.is_cuda:

@@ -1,0 +1,58 @@
+"""Builds the task prompt for one op: what to compute, the reference implementation, the solution-file contract, the
+building blocks this package offers and the hardware the kernel will run on."""
+from __future__ import annotations
+
+import inspect
+import textwrap
+
+HARDWARE_PROFILES = {
+    "b200_8": textwrap.dedent("""\
+        8 x NVIDIA B200 (sm_100a) in one node, every pair connected at full NVLink 5 bandwidth through NVSwitch
+        (900 GB/s per direction per GPU, in-switch reduction through multimem instructions); 148 SMs, 227 KB shared
+        memory per CTA, 256 KB tensor memory per SM, 126 MB L2, 180 GB HBM3e at about 6.5 TB/s measured copy bandwidth;
+        dense bf16 about 1.4-1.6 PFLOP/s measured. Matrix products belong on tcgen05.mma with accumulators in tensor
+        memory and operands staged by TMA; never issue a TMA load with cluster multicast from another GPU's memory."""),
+    "cpu_gloo": "CPU ranks over gloo and a shared-memory twin of the symmetric heap: correctness of the host logic only.",
+}
+
+CONTRACT = textwrap.dedent("""\
+    Write ONE Python file that defines
+
+        def solution(rc, *inputs): ...
+
+    with the same inputs and the same outputs (types, shapes, dtypes, tuple/dict structure) as the reference below.
+    `rc` gives rc.rank, rc.world, rc.device, rc.dtype and rc.comm, whose collectives run on a symmetric heap that every
+    rank maps: all_reduce(x, op="sum", scale=1.0), all_gather(x) -> [W, ...], reduce_scatter(x), all_to_all(x[W, ...]),
+    all_to_all_v(rows, counts, capacity), all_to_all_permute(x, scatter_dim, gather_dim), row_gather(shard, ids),
+    broadcast / reduce / scatter / gather, barrier(); rc.comm.heap allocates tensors that peers can address.
+    Kernels of this package: ops.gemm_bf16 (a @ w.T on tcgen05), ops.gemm_bf16_kn, ops.gemm_bf16_tn, ops.rmsnorm,
+    ops.rope, ops.fp8_quantize_1x128 / fp8_dequantize_1x128, ops.attention.flash_attn_fwd / flash_attn_bwd /
+    RingAttention, ops.tp.AllGatherGemm / GemmReduceScatterRMSNorm, ops.moe.MoEExchange / grouped_gemm.
+    The file is evaluated with
+        python -m parallelkernelbench_b200.harness.launch eval --op {op} --nproc {nproc} --solution your_file.py --measure-perf
+    which compares every rank's output with the reference within atol={atol}, rtol={rtol} over seeded trials and reports
+    reference time / your time (device-timed, max over ranks). Aim for correctness first, then for the fewest launches and
+    the fewest bytes over NVLink.""")
+
+
+def build_prompt(op: str, hardware: str = "b200_8", nproc: int = 8, feedback: str | None = None) -> str:
+    from ..workloads import registry
+
+    spec = registry.get(op)
+    parts = [f"# Task: a fast multi-GPU implementation of `{spec.name}`"
+             + (f" (reference problems {', '.join(map(str, spec.problem_ids))})" if spec.problem_ids else ""),
+             spec.doc or "", "## Hardware", HARDWARE_PROFILES[hardware],
+             "## Contract", CONTRACT.format(op=spec.name, nproc=nproc, atol=spec.atol, rtol=spec.rtol),
+             "## Named shape configurations", "\n".join(f"- {k}: {v}" for k, v in spec.configs.items()),
+             "## Input factory", _source(spec.make_inputs), "## Reference implementation (PyTorch + process group)",
+             _source(spec.reference)]
+    if feedback:
+        parts += ["## Result of your previous attempt", feedback]
+    return "\n\n".join(p for p in parts if p)
+
+
+def _source(fn) -> str:
+    try:
+        return "```python\n" + textwrap.dedent(inspect.getsource(fn)).rstrip() + "\n```"
+    except (OSError, TypeError):
+        return f"(source of {getattr(fn, '__name__', fn)!r} is not available)"

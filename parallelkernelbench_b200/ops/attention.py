@@ -166,8 +166,14 @@ class RingAttention:
         q_segments = [(self.seg_rows, pos) for pos in self.positions(r)]
         kv_segments = [(src * self.rows + sgi * self.seg_rows, pos, self.seg_rows) for src in range(W)
                        for sgi, pos in enumerate(self.positions(src))]
+        dk_buf = dv_buf = None
+        if W > 1:      # partial sums for every KV row of the group live in the heap: the reduce-scatter reads them in place
+            heap = self.group.heap
+            shape = (W * self.rows, self.hkv, self.D)
+            dk_buf = heap.named(("ring_dk", self.group.channel, shape), shape, torch.float32).local
+            dv_buf = heap.named(("ring_dv", self.group.channel, shape), shape, torch.float32).local
         dq, dkf, dvf = flash_attn_bwd(q, kg, vg, out, lse.reshape(self.hq, self.rows), dout, causal=causal, scale=scale,
-                                      q_segments=q_segments, kv_segments=kv_segments)
+                                      q_segments=q_segments, kv_segments=kv_segments, dk_out=dk_buf, dv_out=dv_buf)
         if W > 1:
             return dq, C.reduce_scatter(dkf, self.group), C.reduce_scatter(dvf, self.group)
         return dq, dkf, dvf
@@ -175,10 +181,13 @@ class RingAttention:
 
 def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, *,
                    causal: bool, scale: float | None = None, q_pos0: int = 0,
-                   q_segments: list[tuple[int, int]] | None = None, kv_segments: list[tuple[int, int, int]] | None = None):
+                   q_segments: list[tuple[int, int]] | None = None, kv_segments: list[tuple[int, int, int]] | None = None,
+                   dk_out: torch.Tensor | None = None, dv_out: torch.Tensor | None = None):
     """Attention backward from a saved forward. ``q, out, dout`` [Sq, Hq, D] (or [B, Sq, Hq, D]); ``k, v`` [Skv, Hkv, D]
     (or with the batch dimension); ``lse`` [Hq, Sq] (or [B, Hq, Sq]), natural log. Positions are described as in
     :func:`flash_attn_fwd`; without segment lists query row i sits at ``q_pos0 + i`` and key row j at j.
+    ``dk_out`` / ``dv_out``: optional fp32 tensors shaped like k / v that receive the result (they are zero-filled here);
+    a caller that reduces them over ranks passes symmetric-heap tensors so that the collective needs no staging copy.
     Returns fp32 ``(dq, dk, dv)`` shaped like q, k, v. bf16 inputs with head dimension 64 or 128 run on the tcgen05
     kernel (dK/dV accumulate in TMEM, dQ by fp32 vector reductions); anything else takes the PyTorch restatement."""
     D = q.shape[-1]
@@ -198,8 +207,8 @@ def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch
         kv_rows = torch.cat([torch.arange(r0, r0 + ln, device=q.device) for r0, _, ln in kv_segments])
         kv_pos = torch.cat([torch.arange(p0, p0 + ln, device=q.device) for _, p0, ln in kv_segments])
         dq = torch.empty(q.shape, dtype=torch.float32, device=q.device)
-        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        dk = dk_out.view(k.shape).zero_() if dk_out is not None else torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = dv_out.view(v.shape).zero_() if dv_out is not None else torch.zeros(v.shape, dtype=torch.float32, device=q.device)
         step = max(1, min(sq, (1 << 26) // max(kv_rows.numel() * hq, 1)))        # bound the score matrix held at once
         for b in range(B):
             kb, vb = k[b][kv_rows], v[b][kv_rows]
@@ -227,8 +236,8 @@ def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch
         delta = torch.empty_like(lsec)
         lse2 = torch.empty_like(lsec)
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
-        dk = torch.zeros(k.shape, dtype=torch.float32, device=q.device)
-        dv = torch.zeros(v.shape, dtype=torch.float32, device=q.device)
+        dk = dk_out.view(k.shape).zero_() if dk_out is not None else torch.zeros(k.shape, dtype=torch.float32, device=q.device)
+        dv = dv_out.view(v.shape).zero_() if dv_out is not None else torch.zeros(v.shape, dtype=torch.float32, device=q.device)
         nv.check(nv.cuda_lib().pkb_flash_attn_bwd(ctypes.byref(d), nv.ptr(qc), nv.ptr(kc), nv.ptr(vc), nv.ptr(oc), nv.ptr(doc), nv.ptr(lsec),
                                                   nv.ptr(delta), nv.ptr(lse2), nv.ptr(dq), nv.ptr(dk), nv.ptr(dv), nv.current_stream()),
                  "pkb_flash_attn_bwd")

@@ -80,3 +80,17 @@ def test_project_derived_and_sequence_parallel_ops_world2_gloo():
     r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, r.stdout[-3000:] + r.stderr[-2000:]
     assert r.stdout.count("PASS rank0") >= len(names)
+
+
+def test_external_solution_file_is_evaluated_against_the_reference(tmp_path):
+    """A candidate written by a user of the harness: one file with solution(rc, *inputs), evaluated like the built-in one."""
+    good = tmp_path / "my_allreduce.py"
+    good.write_text("def solution(rc, x):\n    return rc.comm.all_reduce(x)\n")
+    r, js = _launch("eval", "--op", "allreduce", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
+                    "--config", "small", "--solution", str(good))
+    assert r.returncode == 0 and js["all_ok"], r.stdout[-1500:] + r.stderr[-1500:]
+    bad = tmp_path / "wrong.py"
+    bad.write_text("def solution(rc, x):\n    return x * 3\n")
+    r, js = _launch("eval", "--op", "allreduce", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
+                    "--config", "small", "--solution", str(bad))
+    assert r.returncode != 0 and not js["all_ok"] and js["trials"][0]["result"] != "match"

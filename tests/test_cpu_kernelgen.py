@@ -1,0 +1,26 @@
+"""Prompt assembly and the generate -> evaluate -> feedback loop (a recorded wrong candidate, then a right one)."""
+import os
+
+
+def test_prompt_contains_contract_reference_and_hardware():
+    from parallelkernelbench_b200.kernelgen import build_prompt
+
+    p = build_prompt("gemm_allreduce", nproc=8)
+    assert "def solution(rc, *inputs)" in p and "tcgen05" in p and "_gar_ref" in p and "--solution" in p
+    assert "Result of your previous attempt" not in p
+    assert "verdict: tensor_mismatch" in build_prompt("allreduce", feedback="verdict: tensor_mismatch")
+
+
+def test_loop_stops_at_first_matching_candidate(tmp_path):
+    from parallelkernelbench_b200.kernelgen import ReplayProposer, optimise
+
+    cands = tmp_path / "cands"
+    cands.mkdir()
+    (cands / "a_wrong.py").write_text("def solution(rc, x):\n    return x * 2\n")
+    (cands / "b_right.py").write_text("def solution(rc, x):\n    return rc.comm.all_reduce(x)\n")
+    (cands / "c_unused.py").write_text("def solution(rc, x):\n    raise RuntimeError('never evaluated')\n")
+    out = optimise("allreduce", ReplayProposer(str(cands)), str(tmp_path / "work"), nproc=2, max_iters=3, backend="gloo",
+                   dtype="float32", config="small", timeout_s=300)
+    assert out["solved"] and len(out["attempts"]) == 2
+    assert not out["attempts"][0]["all_ok"] and "verdict" in out["attempts"][0]["feedback"]
+    assert os.path.isfile(out["attempts"][1]["path"])
