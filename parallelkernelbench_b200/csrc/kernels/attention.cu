@@ -31,6 +31,7 @@
 #include "pkb/attention_api.h"
 #include "pkb/host.h"
 #include "pkb/collectives_api.h"
+#include "pkb/bulk_copy.cuh"
 #include "pkb/symm.cuh"
 
 namespace pkb {
@@ -881,6 +882,11 @@ __device__ __forceinline__ void fa_push_role(const FaCommArgs& a) {
   // all ranks have entered this call => nobody still reads the previous call's gathered KV
   // (the epoch slot lives in dynamic shared memory: this kernel has no room for static shared memory)
   extern __shared__ __align__(1024) uint8_t smem_comm[];
+  BulkRing ring;
+  if (threadIdx.x == 0) {
+    *reinterpret_cast<volatile int*>(smem_comm + 8) = 0;        // abort flag of the ring's waits
+    bulk_ring_init(ring, smem_u32(smem_comm) + 128);
+  }
   if (!symm_block_barrier_at(c, 601, 1, reinterpret_cast<volatile uint32_t*>(smem_comm))) return;
   const int W = c.gsize;
   const int pieces = static_cast<int>((a.seg_bytes + a.piece_bytes - 1) / a.piece_bytes);
@@ -901,19 +907,15 @@ __device__ __forceinline__ void fa_push_role(const FaCommArgs& a) {
     const uint8_t* src = (is_v ? a.v_local : a.k_local) + off;
     uint8_t* dst = symm_ptr<uint8_t>(c, dest, is_v ? a.v_gather_off : a.k_gather_off) +
                    (long long)c.grank * a.segs_per_rank * a.seg_bytes + off;
-    const long long nvec = n >> 4;
-    long long i = threadIdx.x;
-    for (; i + 3ll * blockDim.x < nvec; i += 4ll * blockDim.x) {
-      U4 v0 = ld_global_nc_v4(src + (i << 4));
-      U4 v1 = ld_global_nc_v4(src + ((i + blockDim.x) << 4));
-      U4 v2 = ld_global_nc_v4(src + ((i + 2ll * blockDim.x) << 4));
-      U4 v3 = ld_global_nc_v4(src + ((i + 3ll * blockDim.x) << 4));
-      st_global_v4(dst + (i << 4), v0);
-      st_global_v4(dst + ((i + blockDim.x) << 4), v1);
-      st_global_v4(dst + ((i + 2ll * blockDim.x) << 4), v2);
-      st_global_v4(dst + ((i + 3ll * blockDim.x) << 4), v3);
+    if (threadIdx.x == 0) {
+      // the piece moves as 16 KiB TMA requests through a shared-memory ring (this CTA does no attention work, so the
+      // kernel's dynamic shared memory is free for it)
+      if (!bulk_copy(ring, dst, src, n, reinterpret_cast<volatile int*>(smem_comm + 8), c.budget_ns)) {
+        record_status(c.status, kStatusMbarTimeout, 601, c.rank, dest, 2, item);
+        return;
+      }
+      fence_proxy_async_all();
     }
-    for (; i < nvec; i += blockDim.x) st_global_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
     __syncthreads();
     if (threadIdx.x == 0) {
       fence_acq_rel_sys();

@@ -17,6 +17,7 @@
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
 #include "pkb/host.h"
+#include "pkb/bulk_copy.cuh"
 #include "pkb/symm.cuh"
 
 namespace pkb {
@@ -219,18 +220,39 @@ struct GatherArgs {
 
 __global__ void __launch_bounds__(kCollThreads)
 coll_gather_kernel(const SymmCtx c, const GatherArgs a) {
-  if (a.stage_bytes > 0) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
+  // large, aligned pieces move through the TMA bulk ring (one request carries 16 KiB, so a few requests per SM fill
+  // NVLink); everything else with 16-byte loads
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  BulkRing ring;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    bulk_ring_init(ring, smem_u32(bulk_smem));
+  }
+  __syncthreads();
+  bool ok = true;
+  auto copy = [&](void* dst, const void* src, long long bytes) {
+    if (bulk_copy_eligible(dst, src, bytes)) {
+      if (!grid_bulk_copy(ring, dst, src, bytes, &s_abort, c.budget_ns)) ok = false;
+    } else {
+      grid_copy_bytes(dst, src, bytes);
+    }
+  };
+  if (a.stage_bytes > 0) copy(symm_local<uint8_t>(c, a.stage_off), a.src, a.stage_bytes);
+  if (threadIdx.x == 0) fence_proxy_async_all();   // bulk stores of the staging are visible before the release below
   if (!symm_grid_barrier(c, 201, 1)) return;
+  if (threadIdx.x == 0) fence_proxy_async_all();   // peers' writes are visible to the bulk loads issued below
   if (a.active) {
     int k = 0;
     for (int g = 0; g < c.gsize; ++g) {
       if (!((a.src_mask >> g) & 1u)) continue;
       const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + a.in_base +
                             a.in_member_stride * c.grank;
-      grid_copy_bytes(static_cast<uint8_t*>(a.out) + (long long)k * a.out_stride, from, a.seg_bytes);
+      copy(static_cast<uint8_t*>(a.out) + (long long)k * a.out_stride, from, a.seg_bytes);
       ++k;
     }
   }
+  if (threadIdx.x == 0 && !ok) record_status(c.status, kStatusMbarTimeout, 201, c.rank, c.rank, 3, 0);
   symm_block_barrier(c, 201, 2);
 }
 
@@ -699,7 +721,12 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
   GatherArgs a{src, stage_bytes, stage_off, src_mask, in_base, in_member_stride, seg_bytes, out, out_stride, active};
   const long long work = stage_bytes > seg_bytes * h->gsize ? stage_bytes : seg_bytes * h->gsize;
   const int grid = grid_for(work, max_blocks);
-  coll_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  static bool attr_set = false;
+  if (!attr_set) {
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(coll_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
+    attr_set = true;
+  }
+  coll_gather_kernel<<<grid, kCollThreads, kBulkSmemBytes, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

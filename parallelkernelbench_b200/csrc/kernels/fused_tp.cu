@@ -261,8 +261,8 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   a.sub_per_shard = rows / a_chunk_rows;
   a.epoch = epoch;
   a.local_in_place = (x_local == g_local + (long long)h->grank * rows * K * 2) ? 1 : 0;
-  // pushing (W-1) copies of the shard must keep pace with the GEMM that consumes them: at 8 ranks 8 CTAs (~400 GB/s of
-  // 16-byte stores) fall behind, so more SMs go to the push
+  // pushing (W-1) copies of the shard must keep pace with the GEMM that consumes them. Measured at 8 ranks
+  // (2048 x 8192 rows per rank, ms per TP-MLP block): 8 CTAs 2.24, 16 CTAs 1.95, 24 CTAs 2.03, 32 CTAs 2.13
   if (comm_ctas <= 0) comm_ctas = W >= 8 ? 16 : (W > 1 ? 8 : 2);
   comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
   const int sms = sm_count() & ~1;

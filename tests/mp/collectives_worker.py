@@ -165,6 +165,16 @@ def main() -> int:
         if r == 0:
             print(line, flush=True)
 
+    for nbytes in (1 << 20, 1 << 24, 1 << 27):
+        x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
+        yn = torch.empty(W * (nbytes // 2), device=dev, dtype=torch.bfloat16)
+        yo = torch.empty(W, nbytes // 2, device=dev, dtype=torch.bfloat16)
+        t_nccl = timeit(lambda: dist.all_gather_into_tensor(yn, x))
+        t_ours = timeit(lambda: C.all_gather(x, g, out=yo))
+        if r == 0:
+            print(f"PERF all_gather {nbytes}B/rank nccl={t_nccl * 1e3:.1f}us ours={t_ours * 1e3:.1f}us "
+                  f"({(W - 1) * nbytes / t_ours / 1e6:.0f} GB/s in per rank)", flush=True)
+
     # the same comparison with both sides replayed from a CUDA graph (launch overhead of either host path removed),
     # inputs and outputs living in the symmetric heap so that no staging copy is involved
     def graph_time(fn, n=20):
