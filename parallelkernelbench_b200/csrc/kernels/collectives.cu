@@ -148,6 +148,36 @@ __device__ __forceinline__ void grid_copy_bytes(void* dst, const void* src, long
   }
 }
 
+// Large aligned copies go through the TMA bulk ring (dynamic shared memory of kBulkSmemBytes), the rest through 16-byte
+// loads. Every thread of every block calls init() once and copy() for each piece.
+struct GridCopier {
+  BulkRing ring;
+  volatile int* abort_flag;
+  uint64_t budget_ns;
+  bool ok;
+  __device__ __forceinline__ void init(uint8_t* smem, volatile int* abort_slot, uint64_t budget) {
+    abort_flag = abort_slot;
+    budget_ns = budget;
+    ok = true;
+    if (threadIdx.x == 0) {
+      *abort_slot = 0;
+      bulk_ring_init(ring, smem_u32(smem));
+    }
+    __syncthreads();
+  }
+  __device__ __forceinline__ void copy(void* dst, const void* src, long long bytes) {
+    if (bulk_copy_eligible(dst, src, bytes)) {
+      if (!grid_bulk_copy(ring, dst, src, bytes, abort_flag, budget_ns)) ok = false;
+    } else {
+      grid_copy_bytes(dst, src, bytes);
+    }
+  }
+  // after copies whose result other ranks read behind a barrier / before bulk loads of data others wrote
+  __device__ __forceinline__ void proxy_fence() {
+    if (threadIdx.x == 0) fence_proxy_async_all();
+  }
+};
+
 // ================================================================================================
 // reduce family
 // ================================================================================================
@@ -504,7 +534,12 @@ __global__ void __launch_bounds__(kCollThreads)
 coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
   using P = Pack<DT>;
   using Acc = typename P::Acc;
-  if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  GridCopier cp;
+  cp.init(bulk_smem, &s_abort, c.budget_ns);
+  if (!a.src_in_heap) cp.copy(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  cp.proxy_fence();
   if (!symm_grid_barrier(c, 202, 1)) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -512,7 +547,35 @@ coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
   const long long nvec_total = a.n / P::kN;
   const long long per = (nvec_total + c.gsize - 1) / c.gsize;
   const long long v0 = min(per * c.grank, nvec_total), v1 = min(v0 + per, nvec_total);
-  for (long long i = v0 + tid; i < v1; i += nthreads) {
+  long long i0 = v0 + tid;
+  // four vectors per thread and iteration: 4 x gsize independent loads in flight
+  for (; i0 + 3 * nthreads < v1; i0 += 4 * nthreads) {
+    Acc acc[4][P::kN];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[0], a.stage_off) + ((i0 + u * nthreads) << 4)), acc[u]);
+    for (int g = 1; g < c.gsize; ++g) {
+      U4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) raw[u] = ld_global_v4(symm_ptr<uint8_t>(c, c.members[g], a.stage_off) + ((i0 + u * nthreads) << 4));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        Acc v[P::kN];
+        P::unpack(raw[u], v);
+#pragma unroll
+        for (int j = 0; j < P::kN; ++j) acc[u][j] = combine<OP>(acc[u][j], v[j]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (a.scale != 1.0) {
+#pragma unroll
+        for (int j = 0; j < P::kN; ++j) acc[u][j] = (Acc)(acc[u][j] * (Acc)a.scale);
+      }
+      st_global_v4(symm_local<uint8_t>(c, a.result_off) + ((i0 + u * nthreads) << 4), P::pack(acc[u]));
+    }
+  }
+  for (long long i = i0; i < v1; i += nthreads) {
     Acc acc[P::kN];
     P::unpack(ld_global_v4(symm_ptr<uint8_t>(c, c.members[0], a.stage_off) + (i << 4)), acc);
     for (int g = 1; g < c.gsize; ++g) {
@@ -537,11 +600,12 @@ coll_allreduce_twoshot_kernel(const SymmCtx c, const TwoShotArgs a) {
     }
   }
   if (!symm_grid_barrier(c, 202, 2)) return;
-  for (int g = 0; g < c.gsize; ++g) {
+  cp.proxy_fence();
+  for (int k = 0; k < c.gsize; ++k) {
+    const int g = (c.grank + k) % c.gsize;      // own slice first, then the peers in a rotated order
     const long long s0 = min(per * g, nvec_total), s1 = min(s0 + per, nvec_total);
     const uint8_t* from = symm_ptr<uint8_t>(c, c.members[g], a.result_off);
-    for (long long i = s0 + tid; i < s1; i += nthreads)
-      st_global_v4(static_cast<uint8_t*>(a.out) + (i << 4), ld_global_v4(from + (i << 4)));
+    cp.copy(static_cast<uint8_t*>(a.out) + (s0 << 4), from + (s0 << 4), (s1 - s0) << 4);
     if (g == c.gsize - 1)
       for (long long i = nvec_total * P::kN + tid; i < a.n; i += nthreads)
         P::store1(a.out, i, P::load1(from, i));
@@ -556,7 +620,12 @@ template <int DT>
 __global__ void __launch_bounds__(kCollThreads)
 coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
   using P = Pack<DT>;
-  if (!a.src_in_heap) grid_copy_bytes(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  GridCopier cp;
+  cp.init(bulk_smem, &s_abort, c.budget_ns);
+  if (!a.src_in_heap) cp.copy(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * P::kElem);
+  cp.proxy_fence();
   if (!symm_grid_barrier(c, 203, 1)) return;
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -577,7 +646,8 @@ coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
   }
   for (; i < v1; i += nthreads) multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), ldr(i));
   if (!symm_grid_barrier(c, 203, 2)) return;
-  if (a.out != nullptr) grid_copy_bytes(a.out, symm_local<uint8_t>(c, a.result_off), a.n * P::kElem);
+  cp.proxy_fence();
+  if (a.out != nullptr) cp.copy(a.out, symm_local<uint8_t>(c, a.result_off), a.n * P::kElem);
   symm_block_barrier(c, 203, 3);
 }
 
@@ -643,6 +713,13 @@ static int check_ctx(const pkb_symm_ctx* h) {
   PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kSymmMaxWorld && h->grank >= 0 && h->grank < h->gsize, "bad group");
   PKB_CHECK_ARG(h->channel >= 0 && h->channel < kSymmChannels, "bad channel");
   return kApiOk;
+}
+
+// Launch of a kernel that carries the bulk-copy ring in dynamic shared memory.
+template <typename K, typename A>
+static void launch_with_ring(K kernel, int grid, cudaStream_t s, const SymmCtx& c, const A& a) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes);
+  kernel<<<grid, kCollThreads, kBulkSmemBytes, s>>>(c, a);
 }
 
 static int grid_for(long long bytes, int max_blocks) {
@@ -812,9 +889,9 @@ int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const v
   SymmCtx c = to_ctx(h);
 #define PKB_TWOSHOT(DT)                                                                         \
   switch (op) {                                                                                 \
-    case kCollSum: coll_allreduce_twoshot_kernel<DT, kCollSum><<<grid, kCollThreads, 0, s>>>(c, a); break; \
-    case kCollMax: coll_allreduce_twoshot_kernel<DT, kCollMax><<<grid, kCollThreads, 0, s>>>(c, a); break; \
-    case kCollMin: coll_allreduce_twoshot_kernel<DT, kCollMin><<<grid, kCollThreads, 0, s>>>(c, a); break; \
+    case kCollSum: launch_with_ring(coll_allreduce_twoshot_kernel<DT, kCollSum>, grid, s, c, a); break; \
+    case kCollMax: launch_with_ring(coll_allreduce_twoshot_kernel<DT, kCollMax>, grid, s, c, a); break; \
+    case kCollMin: launch_with_ring(coll_allreduce_twoshot_kernel<DT, kCollMin>, grid, s, c, a); break; \
     default: set_last_error("unknown reduce op"); return kApiBadArgument;                       \
   }
   switch (dtype) {
@@ -842,8 +919,8 @@ int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, l
   const int grid = grid_for(n * elem_size(dtype), max_blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   SymmCtx c = to_ctx(h);
-  if (dtype == kCollBf16) coll_allreduce_nvls_kernel<kCollBf16><<<grid, kCollThreads, 0, s>>>(c, a);
-  else if (dtype == kCollF32) coll_allreduce_nvls_kernel<kCollF32><<<grid, kCollThreads, 0, s>>>(c, a);
+  if (dtype == kCollBf16) launch_with_ring(coll_allreduce_nvls_kernel<kCollBf16>, grid, s, c, a);
+  else if (dtype == kCollF32) launch_with_ring(coll_allreduce_nvls_kernel<kCollF32>, grid, s, c, a);
   else { set_last_error("NVLS all-reduce supports bf16 and fp32"); return kApiUnsupported; }
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;

@@ -76,8 +76,17 @@ def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Te
                and x.dtype in (torch.bfloat16, torch.float32))
     ll_ok = nbytes <= LL_MAX_BYTES and x.dtype in (torch.bfloat16, torch.float32) and group.size > 1
     if algo == "auto":
-        algo = "ll" if (ll_ok and nbytes <= LL_AUTO_BYTES) else ("oneshot" if nbytes <= ONE_SHOT_MAX_BYTES or group.size == 1
-                                   else ("nvls" if nvls_ok else "twoshot"))
+        # measured on B200 (device time under CUDA-graph replay, 2 ranks, NCCL in brackets): the no-barrier exchange 6.7 us
+        # at 4 KiB (13.8), 9.0 us at 64 KiB (17.2); one-shot 52.6 us at 16 MiB (59.0); two-shot 261 us at 128 MiB (285), the
+        # in-switch form 429 us there - with two ranks a peer read costs the same as the switch reduction, so NVLS is
+        # used from four ranks on, where one-shot would read (W-1) copies
+        one_shot_max = (32 << 20) if group.size == 2 else ONE_SHOT_MAX_BYTES
+        if ll_ok and nbytes <= LL_AUTO_BYTES:
+            algo = "ll"
+        elif nbytes <= one_shot_max or group.size == 1:
+            algo = "oneshot"
+        else:
+            algo = "nvls" if (nvls_ok and group.size >= 4) else "twoshot"
     lib = _lib()
     if algo == "ll":
         if not ll_ok:
