@@ -32,7 +32,7 @@
 #include "pkb/host.h"
 #include "pkb/collectives_api.h"
 #include "pkb/bulk_copy.cuh"
-#include "pkb/symm.cuh"
+#include "pkb/symm_host.h"
 
 namespace pkb {
 
@@ -1044,12 +1044,7 @@ static int launch_fa_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, cons
   if (rc) return rc;
 
   FaCommArgs a;
-  a.ctx.base = h->base; a.ctx.stride = h->stride; a.ctx.mc_base = h->mc_base;
-  a.ctx.rank = h->rank; a.ctx.world = h->world; a.ctx.gsize = h->gsize; a.ctx.grank = h->grank;
-  for (int i = 0; i < kSymmMaxWorld; ++i) a.ctx.members[i] = h->members[i];
-  a.ctx.channel = h->channel;
-  a.ctx.status = status_block_device_ptr();
-  a.ctx.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
+  a.ctx = symm_ctx_from_api(h);
   a.k_local = static_cast<const uint8_t*>(k_local);
   a.v_local = static_cast<const uint8_t*>(v_local);
   a.k_gather_off = k_off; a.v_gather_off = v_off; a.flags_off = flags_off;

@@ -18,7 +18,7 @@
 #include "pkb/collectives_api.h"
 #include "pkb/host.h"
 #include "pkb/bulk_copy.cuh"
-#include "pkb/symm.cuh"
+#include "pkb/symm_host.h"
 
 namespace pkb {
 
@@ -697,23 +697,7 @@ coll_a2av_kernel(const SymmCtx c, const A2AVArgs a) {
 // A barrier and nothing else (used by tests and to fence phases of composite ops).
 __global__ void coll_barrier_kernel(const SymmCtx c) { symm_block_barrier(c, 205, 1); }
 
-static SymmCtx to_ctx(const pkb_symm_ctx* h) {
-  SymmCtx c;
-  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
-  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
-  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
-  c.channel = h->channel;
-  c.status = status_block_device_ptr();
-  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
-  return c;
-}
 
-static int check_ctx(const pkb_symm_ctx* h) {
-  PKB_CHECK_ARG(h != nullptr && h->base != 0 && h->stride != 0, "symmetric heap not initialised");
-  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kSymmMaxWorld && h->grank >= 0 && h->grank < h->gsize, "bad group");
-  PKB_CHECK_ARG(h->channel >= 0 && h->channel < kSymmChannels, "bad channel");
-  return kApiOk;
-}
 
 // Launch of a kernel that carries the bulk-copy ring in dynamic shared memory.
 template <typename K, typename A>
@@ -760,9 +744,9 @@ using namespace pkb;
 extern "C" {
 
 int pkb_coll_barrier(const pkb_symm_ctx* h, int blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(blocks >= 1 && blocks <= kSymmMaxBlocks, "blocks out of range");
-  coll_barrier_kernel<<<blocks, 32, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h));
+  coll_barrier_kernel<<<blocks, 32, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h));
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -770,14 +754,14 @@ int pkb_coll_barrier(const pkb_symm_ctx* h, int blocks, void* stream) {
 int pkb_coll_reduce(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long stage_elems,
                     unsigned long long stage_off, long long in_base, long long n, void* out, int active,
                     double scale, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(elem_size(dtype) > 0, "unknown dtype");
   PKB_CHECK_ARG((stage_off & 15) == 0, "stage offset must be 16-byte aligned");
   ReduceArgs a{src, stage_elems, stage_off, in_base, n, out, active, scale};
   const long long work = (stage_elems > n * h->gsize ? stage_elems : n * h->gsize) * elem_size(dtype);
   const int grid = grid_for(work, max_blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  SymmCtx c = to_ctx(h);
+  SymmCtx c = symm_ctx_from_api(h);
   switch (dtype) {
     case kCollBf16: return launch_reduce_op<kCollBf16>(op, c, a, grid, s);
     case kCollF16: return launch_reduce_op<kCollF16>(op, c, a, grid, s);
@@ -793,7 +777,7 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
                     unsigned long long stage_off, unsigned int src_mask, long long in_base,
                     long long in_member_stride, long long seg_bytes, void* out, long long out_stride,
                     int active, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG((stage_off & 15) == 0, "stage offset must be 16-byte aligned");
   GatherArgs a{src, stage_bytes, stage_off, src_mask, in_base, in_member_stride, seg_bytes, out, out_stride, active};
   const long long work = stage_bytes > seg_bytes * h->gsize ? stage_bytes : seg_bytes * h->gsize;
@@ -803,7 +787,7 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
     PKB_CHECK_CUDA(cudaFuncSetAttribute(coll_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kBulkSmemBytes));
     attr_set = true;
   }
-  coll_gather_kernel<<<grid, kCollThreads, kBulkSmemBytes, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  coll_gather_kernel<<<grid, kCollThreads, kBulkSmemBytes, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -811,13 +795,13 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
 int pkb_coll_row_gather(const pkb_symm_ctx* h, const void* src, long long stage_bytes, unsigned long long table_off,
                         const void* ids, long long n, long long rows_per_member, long long row_bytes, void* out,
                         int sync, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(rows_per_member > 0 && row_bytes > 0 && n >= 0, "rows_per_member and row_bytes must be positive");
   PKB_CHECK_ARG(stage_bytes == 0 || sync, "a staged table needs the barriers");
   RowGatherArgs a{src, stage_bytes, table_off, static_cast<const long long*>(ids), n, rows_per_member, row_bytes, out, sync};
   const long long work = stage_bytes > n * row_bytes ? stage_bytes : n * row_bytes;
   const int grid = grid_for(work, max_blocks);
-  coll_row_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  coll_row_gather_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -826,21 +810,21 @@ int pkb_coll_a2a_permute(const pkb_symm_ctx* h, const void* src, long long stage
                          long long in_rank_off, const long long* extents, const long long* in_strides,
                          long long out_member_off, const long long* out_strides, long long inner_bytes, void* out,
                          int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(extents && in_strides && out_strides && inner_bytes > 0, "extents, strides and inner_bytes are required");
   PKB_CHECK_ARG(extents[0] > 0 && extents[1] > 0 && extents[2] > 0, "extents must be positive");
   A2APermArgs a{src, stage_bytes, stage_off, in_rank_off, extents[0], extents[1], extents[2], in_strides[0], in_strides[1],
                 in_strides[2], out_member_off, out_strides[0], out_strides[1], out_strides[2], inner_bytes, out};
   const long long moved = extents[0] * extents[1] * extents[2] * inner_bytes * h->gsize;
   const int grid = grid_for(moved > stage_bytes ? moved : stage_bytes, max_blocks);
-  coll_a2a_perm_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  coll_a2a_perm_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
 
 int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n, unsigned long long ll_off,
                           long long cap_units, void* out, double scale, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(dtype == kCollBf16 || dtype == kCollF32, "the latency-optimised all-reduce takes bf16 or fp32");
   PKB_CHECK_ARG((ll_off & 15) == 0 && n >= 1, "heap offset misaligned or empty input");
   const long long units = dtype == kCollF32 ? n : (n + 1) / 2;
@@ -850,7 +834,7 @@ int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* 
   if (grid < 1) grid = 1;
   if (grid > 32) grid = 32;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  SymmCtx c = to_ctx(h);
+  SymmCtx c = symm_ctx_from_api(h);
 #define PKB_LL(DT)                                                                              \
   switch (op) {                                                                                 \
     case kCollSum: coll_allreduce_ll_kernel<DT, kCollSum><<<grid, kCollThreads, 0, s>>>(c, a); break; \
@@ -866,13 +850,13 @@ int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* 
 
 int pkb_coll_allgather_ll(const pkb_symm_ctx* h, const void* src, long long words, unsigned long long ll_off,
                           long long cap_units, void* out, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG((ll_off & 15) == 0 && words >= 1 && words <= cap_units, "heap offset misaligned or message larger than the slot");
   LLArgs a{src, words, ll_off, cap_units, out, 1.0f};
   int grid = (int)((words * h->gsize + 4 * kCollThreads - 1) / (4 * kCollThreads));
   if (grid < 1) grid = 1;
   if (grid > 32) grid = 32;
-  coll_allgather_ll_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  coll_allgather_ll_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -880,13 +864,13 @@ int pkb_coll_allgather_ll(const pkb_symm_ctx* h, const void* src, long long word
 int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n,
                                unsigned long long stage_off, unsigned long long result_off, void* out,
                                int src_in_heap, double scale, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(((stage_off | result_off) & 15) == 0, "heap offsets must be 16-byte aligned");
   PKB_CHECK_ARG(((uintptr_t)out & 15) == 0, "output must be 16-byte aligned");
   TwoShotArgs a{src, n, stage_off, result_off, out, src_in_heap, scale};
   const int grid = grid_for(n * elem_size(dtype) * 2, max_blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  SymmCtx c = to_ctx(h);
+  SymmCtx c = symm_ctx_from_api(h);
 #define PKB_TWOSHOT(DT)                                                                         \
   switch (op) {                                                                                 \
     case kCollSum: launch_with_ring(coll_allreduce_twoshot_kernel<DT, kCollSum>, grid, s, c, a); break; \
@@ -911,14 +895,14 @@ int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const v
 int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n,
                             unsigned long long stage_off, unsigned long long result_off, void* out,
                             int src_in_heap, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(h->mc_base != 0, "NVLS multicast mapping not available");
   PKB_CHECK_ARG(h->gsize == h->world, "NVLS all-reduce runs on the whole heap group only");
   PKB_CHECK_ARG(((stage_off | result_off) & 15) == 0, "heap offsets must be 16-byte aligned");
   TwoShotArgs a{src, n, stage_off, result_off, out, src_in_heap, 1.0};
   const int grid = grid_for(n * elem_size(dtype), max_blocks);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  SymmCtx c = to_ctx(h);
+  SymmCtx c = symm_ctx_from_api(h);
   if (dtype == kCollBf16) launch_with_ring(coll_allreduce_nvls_kernel<kCollBf16>, grid, s, c, a);
   else if (dtype == kCollF32) launch_with_ring(coll_allreduce_nvls_kernel<kCollF32>, grid, s, c, a);
   else { set_last_error("NVLS all-reduce supports bf16 and fp32"); return kApiUnsupported; }
@@ -930,7 +914,7 @@ int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_
                           const void* send_counts, const void* send_offsets, unsigned long long stage_off,
                           unsigned long long meta_off, void* out, long long out_capacity_rows,
                           void* recv_counts, void* recv_total, int max_blocks, void* stream) {
-  if (int rc = check_ctx(h)) return rc;
+  if (int rc = symm_ctx_check(h)) return rc;
   PKB_CHECK_ARG(row_bytes > 0, "row_bytes must be positive");
   PKB_CHECK_ARG(((stage_off | meta_off) & 15) == 0, "heap offsets must be 16-byte aligned");
   A2AVArgs a{src, src_rows, row_bytes, static_cast<const long long*>(send_counts),
@@ -939,7 +923,7 @@ int pkb_coll_all_to_all_v(const pkb_symm_ctx* h, const void* src, long long src_
   int cap = sm_count();
   if (max_blocks > 0 && max_blocks < cap) cap = max_blocks;
   if (cap > kSymmMaxBlocks) cap = kSymmMaxBlocks;
-  coll_a2av_kernel<<<cap, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(to_ctx(h), a);
+  coll_a2av_kernel<<<cap, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -21,7 +21,7 @@
 #include "pkb/collectives_api.h"
 #include "pkb/gemm_umma2.cuh"
 #include "pkb/host.h"
-#include "pkb/symm.cuh"
+#include "pkb/symm_host.h"
 
 namespace pkb {
 
@@ -179,16 +179,6 @@ tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
-static SymmCtx ctx_from(const pkb_symm_ctx* h) {
-  SymmCtx c;
-  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
-  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
-  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
-  c.channel = h->channel;
-  c.status = status_block_device_ptr();
-  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
-  return c;
-}
 
 }  // namespace pkb
 
@@ -214,7 +204,7 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   PKB_CHECK_ARG((gather_off & 1023) == 0 && (flags_off & 15) == 0, "heap offsets misaligned");
   const int W = h->gsize;
   const int M = W * rows;
-  SymmCtx ctx = ctx_from(h);
+  SymmCtx ctx = symm_ctx_from_api(h);
   uint8_t* g_local = reinterpret_cast<uint8_t*>(h->base + (uint64_t)h->rank * h->stride + gather_off);
 
   CUtensorMap ta, tb;
@@ -300,7 +290,7 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
   PKB_CHECK_ARG((recv_off & 15) == 0 && (done_off & 15) == 0, "heap offsets misaligned");
   const int W = h->gsize;
   const int M = W * rows_per_rank;
-  SymmCtx ctx = ctx_from(h);
+  SymmCtx ctx = symm_ctx_from_api(h);
 
   CUtensorMap ta, tb;
   int rc = encode_tmap_2d(&ta, kTmapBf16, a_mat, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,

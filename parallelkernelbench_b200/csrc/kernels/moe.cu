@@ -19,7 +19,7 @@
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
 #include "pkb/host.h"
-#include "pkb/symm.cuh"
+#include "pkb/symm_host.h"
 
 namespace pkb {
 
@@ -168,16 +168,6 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const SymmCtx c, const
   symm_block_barrier(c, 501, 2);
 }
 
-static SymmCtx moe_ctx(const pkb_symm_ctx* h) {
-  SymmCtx c;
-  c.base = h->base; c.stride = h->stride; c.mc_base = h->mc_base;
-  c.rank = h->rank; c.world = h->world; c.gsize = h->gsize; c.grank = h->grank;
-  for (int i = 0; i < kSymmMaxWorld; ++i) c.members[i] = h->members[i];
-  c.channel = h->channel;
-  c.status = status_block_device_ptr();
-  c.budget_ns = h->budget_ns ? h->budget_ns : kDefaultWaitBudgetNs;
-  return c;
-}
 
 }  // namespace pkb
 
@@ -222,7 +212,7 @@ int pkb_moe_dispatch(const pkb_symm_ctx* h, const void* payload, const void* sca
                     recv_payload_off, recv_scale_off, capacity, static_cast<int*>(overflow)};
   int grid = sm_count() * 2;   // fixed: the same on every rank, the barrier pairs blocks by index
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
-  moe_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(moe_ctx(h), a);
+  moe_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -238,9 +228,9 @@ int pkb_moe_combine(const pkb_symm_ctx* h, unsigned long long y_off, const void*
   int grid = sm_count() * 2;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (top_k <= 2) moe_combine_kernel<2><<<grid, 256, 0, s>>>(moe_ctx(h), a);
-  else if (top_k <= 4) moe_combine_kernel<4><<<grid, 256, 0, s>>>(moe_ctx(h), a);
-  else moe_combine_kernel<8><<<grid, 256, 0, s>>>(moe_ctx(h), a);
+  if (top_k <= 2) moe_combine_kernel<2><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
+  else if (top_k <= 4) moe_combine_kernel<4><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
+  else moe_combine_kernel<8><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
