@@ -81,6 +81,10 @@ def run_worker(args) -> int:
         spec = registry.get(args.op)
         cfg = spec.config(args.config, registry.parse_overrides(args.set))
         dtype = registry.DTYPES[args.dtype]
+        if spec.heap_gib is not None:       # the heap is created on first use: an op with large exchange buffers sizes it
+            need = float(spec.heap_gib(cfg, ctx.world))
+            if need > float(os.environ.get("PKB_HEAP_GIB", "1")):
+                os.environ["PKB_HEAP_GIB"] = str(need)
         run = registry.RunCtx(ctx, spec.name, trial=args.trial, dtype=dtype)
         if args.impl == "file":
             impl = load_solution(args.solution)

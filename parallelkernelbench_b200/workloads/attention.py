@@ -85,6 +85,13 @@ def _ring_ours(rc, q, k, v, causal, layout):
     return rc.cache[key](q, k, v, causal=causal)[0]
 
 
+def _ring_heap_gib(cfg, W, backward: bool) -> float:
+    """Gather buffers for K and V (bf16) and, for the backward, fp32 partial dK / dV for every KV row of the group."""
+    per_row = cfg["hkv"] * cfg["d"]
+    b = 2 * W * cfg["rows"] * per_row * 2 + (2 * W * cfg["rows"] * per_row * 4 if backward else 0)
+    return max(1.0, math.ceil(1.5 * b / (1 << 30) + 0.25))
+
+
 def _ring_cost(cfg, W):
     S = cfg["rows"] * W
     return Cost(flops=4.0 * S * S * cfg["d"] * cfg["hq"] * (0.5 if cfg["causal"] else 1.0) / W,
@@ -97,7 +104,8 @@ register(OpSpec(name="ring_attention", problem_ids=(54,), group="attention",
                          "contiguous": {"rows": 512, "hq": 8, "hkv": 2, "d": 128, "causal": 0, "layout": "contiguous"},
                          "cp131k": {"rows": 16384, "hq": 32, "hkv": 8, "d": 128, "causal": 1, "layout": "zigzag"}},
                 make_inputs=_ring_inputs, reference=_ring_ref, ours=_ring_ours, atol=2e-2, rtol=2e-2, ours_needs_cuda=True,
-                cost=_ring_cost, doc="zigzag context-parallel causal attention, KV exchange inside the attention kernel"))
+                cost=_ring_cost, heap_gib=lambda cfg, W: _ring_heap_gib(cfg, W, False),
+                doc="zigzag context-parallel causal attention, KV exchange inside the attention kernel"))
 
 
 # ---- context-parallel attention, forward and backward -----------------------------------------------
@@ -136,7 +144,8 @@ register(OpSpec(name="ring_attention_fwd_bwd", problem_ids=(54, 57), group="atte
                          "small": {"rows": 256, "hq": 4, "hkv": 2, "d": 64, "causal": 1, "layout": "zigzag"},
                          "cp131k": {"rows": 16384, "hq": 32, "hkv": 8, "d": 128, "causal": 1, "layout": "zigzag"}},
                 make_inputs=_ringfb_inputs, reference=_ringfb_ref, ours=_ringfb_ours, atol=5e-2, rtol=5e-2, ours_needs_cuda=True,
-                cost=_ringfb_cost, doc="zigzag context-parallel causal attention, forward and backward (GQA)"))
+                cost=_ringfb_cost, heap_gib=lambda cfg, W: _ring_heap_gib(cfg, W, True),
+                doc="zigzag context-parallel causal attention, forward and backward (GQA)"))
 
 
 # =================================================================================================

@@ -75,6 +75,7 @@ class OpSpec:
     group: str = "misc"
     doc: str = ""
     mutates_inputs: bool = False            # inputs must be re-created for every timed call
+    heap_gib: Callable[[dict, int], float] | None = None   # symmetric-heap size this op needs (config, world) -> GiB
 
     def config(self, name: str = "default", overrides: dict | None = None) -> dict:
         if name not in self.configs:
