@@ -213,5 +213,5 @@ _MOE_CFG = {
 register(OpSpec(name="moe_layer", problem_ids=(28, 29, 31, 32, 49, 50, 51), group="moe", configs=_MOE_CFG, make_inputs=_moe_inputs,
                 reference=_moe_ref, ours=_moe_ours, atol=1e-1, rtol=3e-2, cost=_moe_cost, ours_needs_cuda=True,
                 # receive buffers (capacity factor 2 over tokens * topk rows of `hidden` bytes + scales) and expert outputs in bf16
-                heap_gib=lambda cfg, W: max(1.0, float(-(-int(2.0 * cfg["tokens"] * cfg["topk"] * cfg["hidden"] * 3.2) // (1 << 30)) + 1)),
+                heap_gib=lambda cfg, W: max(1.0, float(-(-int(2.0 * cfg["tokens"] * cfg["topk"] * cfg["hidden"] * 5.0) // (1 << 30)) + 1)),
                 doc="router -> fp8/bf16 dispatch (P2P push) -> grouped SwiGLU experts -> combine (P2P pull)"))
