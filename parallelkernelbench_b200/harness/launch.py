@@ -269,7 +269,7 @@ def cmd_sweep(a) -> int:
                 print(f"skip {op} w={w} (already in {ledger})")
                 continue
             s = eval_op(op, w, trials=a.trials, measure_perf=a.measure_perf, config=a.config, backend=a.backend,
-                        warmup=a.warmup, iters=a.iters, timeout_s=a.timeout)
+                        dtype=a.dtype, warmup=a.warmup, iters=a.iters, timeout_s=a.timeout)
             last = s["trials"][-1] if s["trials"] else {}
             cell = {"op": op, "world": w, "config": a.config, "all_ok": s["all_ok"], "git_sha": s["git_sha"],
                     "result": last.get("result"), "speedup": last.get("speedup"),
@@ -329,6 +329,7 @@ def main(argv=None) -> int:
     sp.add_argument("--ops", default="all")
     sp.add_argument("--worlds", default="1,2,4,8")
     sp.add_argument("--config", default="default")
+    sp.add_argument("--dtype", default="bfloat16")
     sp.add_argument("--trials", type=int, default=1)
     sp.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
     sp.add_argument("--measure-perf", action="store_true")

@@ -94,3 +94,23 @@ def test_external_solution_file_is_evaluated_against_the_reference(tmp_path):
     r, js = _launch("eval", "--op", "allreduce", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
                     "--config", "small", "--solution", str(bad))
     assert r.returncode != 0 and not js["all_ok"] and js["trials"][0]["result"] != "match"
+
+
+def test_list_sweep_resume_inspect_and_perf_diff(tmp_path):
+    """The remaining launcher subcommands on CPU: list, a one-cell sweep with its ledger, resume skipping the finished cell,
+    and the offline inspectors over the stored per-rank files."""
+    r, _ = _launch("list")
+    assert r.returncode == 0 and "allreduce" in r.stdout and "reference problems covered: 87/87" in r.stdout
+    ledger = str(tmp_path / "results.jsonl")
+    args = ["sweep", "--ops", "allreduce", "--worlds", "2", "--config", "small", "--backend", "gloo", "--dtype", "float32", "--trials", "1",
+            "--measure-perf", "--warmup", "2", "--iters", "3", "--ledger", ledger]
+    r, _ = _launch(*args)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    cells = [json.loads(ln) for ln in open(ledger)]
+    assert len(cells) == 1 and cells[0]["op"] == "allreduce" and cells[0]["world"] == 2 and cells[0]["all_ok"] and cells[0]["speedup"] > 0
+    r, _ = _launch(*args, "--resume")
+    assert r.returncode == 0 and "skip allreduce w=2" in r.stdout and len(open(ledger).readlines()) == 1
+    r, _ = _launch("inspect", "--op", "allreduce")
+    assert r.returncode == 0 and "verdict: match" in r.stdout
+    r, _ = _launch("perf-diff", "--op", "allreduce")
+    assert r.returncode == 0 and "speed" in r.stdout.lower()
