@@ -140,3 +140,101 @@ int pkb_dequant_sum(const void* payload, const void* scales, void* out, int W, l
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Gradient clipping by global norm without a host round trip: (1) sum of squares of up to eight tensors in one launch,
+// (2) [the all-reduce of that scalar], (3) every tensor scaled in place by min(1, max_norm / sqrt(total)) read from device
+// memory. The reference computes a norm per tensor, all-reduces, and branches on the host
+// (reference: reference/21_clip_grad_norm_no_ep.py:25-50).
+// ------------------------------------------------------------------------------------------------
+namespace pkb {
+
+constexpr int kClipMaxTensors = 8;
+struct ClipArgs {
+  void* ptr[kClipMaxTensors];
+  long long n[kClipMaxTensors];
+  float pre_scale[kClipMaxTensors];   // each tensor is multiplied by this before it is measured (and stays scaled)
+  int slot[kClipMaxTensors];          // which accumulator the tensor's sum of squares goes to
+  int count;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) clip_sumsq_kernel(const ClipArgs a, float* __restrict__ acc) {
+  __shared__ float red[8];
+  for (int t = 0; t < a.count; ++t) {
+    const T* p = static_cast<const T*>(a.ptr[t]);
+    const float ps = a.pre_scale[t];
+    float s = 0.f;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n[t]; i += (long long)gridDim.x * blockDim.x) {
+      const float v = (float)p[i] * ps;
+      s += v * v;
+    }
+    s = warp_sum(s);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int w = 0; w < 8; ++w) tot += red[w];
+      if (tot != 0.f) atomicAdd(acc + a.slot[t], tot);
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+clip_scale_kernel(const ClipArgs a, const float* __restrict__ total_sq, int n_slots, float max_norm, float* __restrict__ total_norm_out) {
+  float tot = 0.f;
+  for (int s = 0; s < n_slots; ++s) tot += total_sq[s];
+  const float norm = sqrtf(tot);
+  const float coef = fminf(max_norm / norm, 1.0f);
+  if (blockIdx.x == 0 && threadIdx.x == 0 && total_norm_out != nullptr) *total_norm_out = norm;
+  for (int t = 0; t < a.count; ++t) {
+    T* p = static_cast<T*>(a.ptr[t]);
+    const float f = coef * a.pre_scale[t];
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n[t]; i += (long long)gridDim.x * blockDim.x)
+      p[i] = (T)((float)p[i] * f);
+  }
+}
+
+static int fill_clip_args(ClipArgs& a, void* const* ptrs, const long long* ns, const float* pre_scale, const int* slots, int count) {
+  PKB_CHECK_ARG(count >= 1 && count <= kClipMaxTensors, "1..8 tensors per call");
+  a.count = count;
+  for (int i = 0; i < count; ++i) {
+    a.ptr[i] = ptrs[i];
+    a.n[i] = ns[i];
+    a.pre_scale[i] = pre_scale ? pre_scale[i] : 1.0f;
+    a.slot[i] = slots ? slots[i] : 0;
+  }
+  return kApiOk;
+}
+
+}  // namespace pkb
+
+// acc (fp32, zero-filled by the caller) receives sum((x * pre_scale)^2) per slot. dtype: 0 bf16, 1 fp32.
+extern "C" int pkb_clip_sumsq(void* const* ptrs, const long long* ns, const float* pre_scale, const int* slots, int count, int dtype,
+                              void* acc, void* stream) {
+  pkb::ClipArgs a;
+  if (int rc = pkb::fill_clip_args(a, ptrs, ns, pre_scale, slots, count)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0) pkb::clip_sumsq_kernel<__nv_bfloat16><<<148 * 4, 256, 0, s>>>(a, static_cast<float*>(acc));
+  else pkb::clip_sumsq_kernel<float><<<148 * 4, 256, 0, s>>>(a, static_cast<float*>(acc));
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return pkb::kApiOk;
+}
+
+// Every tensor is multiplied in place by pre_scale * min(1, max_norm / sqrt(sum of the n_slots totals)).
+extern "C" int pkb_clip_scale(void* const* ptrs, const long long* ns, const float* pre_scale, int count, int dtype, const void* total_sq,
+                              int n_slots, float max_norm, void* total_norm_out, void* stream) {
+  pkb::ClipArgs a;
+  if (int rc = pkb::fill_clip_args(a, ptrs, ns, pre_scale, nullptr, count)) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == 0)
+    pkb::clip_scale_kernel<__nv_bfloat16><<<148 * 4, 256, 0, s>>>(a, static_cast<const float*>(total_sq), n_slots, max_norm,
+                                                                 static_cast<float*>(total_norm_out));
+  else
+    pkb::clip_scale_kernel<float><<<148 * 4, 256, 0, s>>>(a, static_cast<const float*>(total_sq), n_slots, max_norm,
+                                                         static_cast<float*>(total_norm_out));
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return pkb::kApiOk;
+}

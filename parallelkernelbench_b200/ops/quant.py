@@ -1,6 +1,8 @@
 """Quantised-wire helpers (csrc/kernels/quant.cu): per-tensor fp8, block int8, dequantise-and-sum."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .. import _native as nv
@@ -57,3 +59,39 @@ def fsdp_adamw_fp8(payload: torch.Tensor, scales: torch.Tensor, p: torch.Tensor,
                                               nv.c_float(weight_decay), nv.c_float(grad_scale), int(step),
                                               nv.current_stream()), "pkb_fsdp_adamw_fp8")
     nv.count_launch()
+
+
+def clip_grad_norm_(tensors: list[torch.Tensor], max_norm: float, comm=None, group=None, pre_scale: list[float] | None = None):
+    """Clip by global L2 norm in place, nothing returns to the host: one launch sums the squares of all tensors, one small
+    all-reduce combines the ranks, one launch scales every tensor by ``min(1, max_norm / norm)`` read from device memory.
+    ``pre_scale[i]`` multiplies tensor i before it is measured (and the tensor stays scaled), which is how expert-parallel
+    gradients enter the norm. Returns the global norm as a device scalar."""
+    if not tensors:
+        raise ValueError("no tensors")
+    dt = tensors[0].dtype
+    if dt not in (torch.bfloat16, torch.float32) or any(t.dtype != dt or not t.is_contiguous() for t in tensors):
+        raise TypeError("contiguous tensors of one dtype (bf16 or fp32) expected")
+    dev = tensors[0].device
+    acc = torch.zeros(1, dtype=torch.float32, device=dev)
+    lib = nv.cuda_lib()
+    code = 0 if dt == torch.bfloat16 else 1
+
+    def pack(chunk, scales):
+        n = len(chunk)
+        return ((ctypes.c_void_p * n)(*[t.data_ptr() for t in chunk]), (ctypes.c_longlong * n)(*[t.numel() for t in chunk]),
+                (ctypes.c_float * n)(*scales), n)
+
+    ps = list(pre_scale) if pre_scale is not None else [1.0] * len(tensors)
+    for i in range(0, len(tensors), 8):
+        ptrs, ns, sc, n = pack(tensors[i:i + 8], ps[i:i + 8])
+        nv.check(lib.pkb_clip_sumsq(ptrs, ns, sc, None, n, code, nv.ptr(acc), nv.current_stream()), "pkb_clip_sumsq")
+        nv.count_launch()
+    if comm is not None and comm.size(group) > 1:
+        acc = comm.all_reduce(acc, group=group)
+    norm = torch.empty((), dtype=torch.float32, device=dev)
+    for i in range(0, len(tensors), 8):
+        ptrs, ns, sc, n = pack(tensors[i:i + 8], ps[i:i + 8])
+        nv.check(lib.pkb_clip_scale(ptrs, ns, sc, n, code, nv.ptr(acc), 1, nv.c_float(float(max_norm)), nv.ptr(norm),
+                                    nv.current_stream()), "pkb_clip_scale")
+        nv.count_launch()
+    return norm

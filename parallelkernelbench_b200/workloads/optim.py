@@ -43,6 +43,12 @@ def _clip_ref(rc, grads, max_norm, p):
 
 def _clip_ours(rc, grads, max_norm, p):
     grads = [g.clone() for g in grads]
+    if rc.dist.is_cuda and p == 2.0 and grads[0].dtype in (torch.bfloat16, torch.float32):
+        from ..ops.quant import clip_grad_norm_
+
+        # three launches (sum of squares of all tensors, the scalar all-reduce, the scaling), no host branch
+        total = clip_grad_norm_(grads, max_norm, rc.comm)
+        return {"total_norm": total, "grads": grads}
     acc = torch.stack([(g.float().abs() ** p).sum() for g in grads]).sum().reshape(1)
     total = rc.comm.all_reduce(acc) ** (1.0 / p)
     # branch-free: the coefficient is computed on the device, nothing returns to the host
@@ -93,6 +99,13 @@ def _clip_ep_ref(rc, non_ep, ep_grads, max_norm, p, ep_size):
 
 def _clip_ep_ours(rc, non_ep, ep_grads, max_norm, p, ep_size):
     m = _clip_ep_mesh(rc)
+    if rc.dist.is_cuda and p == 2.0 and non_ep[0].dtype in (torch.bfloat16, torch.float32):
+        from ..ops.quant import clip_grad_norm_
+
+        # expert gradients enter pre-scaled by 1/ep; both reductions (EP-FSDP then EP) together span the whole job
+        dense, experts = [g.clone() for g in non_ep], [g.clone() for g in ep_grads]
+        total = clip_grad_norm_(dense + experts, max_norm, rc.comm, pre_scale=[1.0] * len(dense) + [1.0 / ep_size] * len(experts))
+        return {"total_norm": total, "non_ep": dense, "ep": experts}
     non_ep = [g.clone() for g in non_ep]
     ep_grads = [g.clone() / ep_size for g in ep_grads]
     a = torch.stack([(g.float().abs() ** p).sum() for g in non_ep]).sum().reshape(1)

@@ -153,3 +153,21 @@ def test_cross_entropy_backward_matches_autograd():
     ref = (torch.softmax(full, -1) - torch.nn.functional.one_hot(tgt, 2048).float())[:, start:start + V] / rows
     got = ce_backward(full[:, start:start + V].to(torch.bfloat16), lse, tgt, start, 1.0 / rows)
     torch.testing.assert_close(got.float(), ref, rtol=3e-2, atol=2e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_clip_grad_norm_kernels_match_torch(dtype):
+    from parallelkernelbench_b200.ops.quant import clip_grad_norm_
+
+    torch.manual_seed(9)
+    grads = [torch.randn(n, device="cuda", dtype=dtype) for n in (1000, 77, 4096 * 33, 5, 1 << 20, 300, 12, 64, 999, 2048)]   # two batches
+    scales = [1.0, 0.5, 1.0, 1.0, 0.25, 1.0, 1.0, 2.0, 1.0, 1.0]
+    ref = [g.float() * s for g, s in zip(grads, scales)]
+    total = torch.sqrt(sum((r * r).sum() for r in ref))
+    for max_norm in (1.0, 1e9):
+        mine = [g.clone() for g in grads]
+        norm = clip_grad_norm_(mine, max_norm, pre_scale=scales)
+        coef = min(max_norm / float(total), 1.0)
+        torch.testing.assert_close(norm, total, rtol=2e-3, atol=1e-3)
+        for got, r in zip(mine, ref):
+            torch.testing.assert_close(got.float(), r * coef, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-6)
