@@ -4,7 +4,8 @@
 
 Each case allocates a few hundred MB at most (inputs larger than L2 where DRAM figures matter),
 launches the kernel a handful of times and exits, so a capture of one launch ends by itself.
-Cases: gemm_pair, gemm_single, tp_mlp, fa_fwd, fa_fwd_d64, grouped_gemm, rmsnorm, allreduce.
+Cases: gemm_pair, gemm_single, tp_mlp, fa_fwd, fa_fwd_d64, fa_bwd, grouped_gemm, grouped_gemm_fp8, rmsnorm, allreduce,
+fsdp_adamw, moe_exchange, gsplat, delta_scan.
 """
 from __future__ import annotations
 
@@ -76,6 +77,19 @@ def case_grouped_gemm(iters):
     w = torch.randn(32, 1024, 2048, device="cuda", dtype=torch.bfloat16) * 0.02
     for _ in range(iters):
         grouped_gemm(a, w, offs)
+
+
+def case_grouped_gemm_fp8(iters):
+    """The same ragged problem as ``grouped_gemm`` on e4m3 operands with block scales."""
+    from ..ops.gemm_fp8 import gemm_fp8_blockscaled
+    from ..refs.gemm_fp8 import quantize_rows_1x128, quantize_weight_128x128
+
+    counts = torch.full((32,), 512, dtype=torch.int32)
+    offs = torch.cat([torch.zeros(1, dtype=torch.int32), counts.cumsum(0).to(torch.int32)]).cuda()
+    a8, sa = quantize_rows_1x128(torch.randn(32 * 512, 2048, device="cuda"))
+    w8, sb = quantize_weight_128x128(torch.randn(32, 1024, 2048, device="cuda") * 0.02)
+    for _ in range(iters):
+        gemm_fp8_blockscaled(a8, sa, w8, sb, offsets=offs)
 
 
 def case_rmsnorm(iters):

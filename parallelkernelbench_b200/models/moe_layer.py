@@ -6,6 +6,11 @@ into the symmetric buffer the combine reads), combine (P2P pull, gate-weighted, 
 The router GEMM runs on the dense tcgen05 kernel; softmax and top-k over a few hundred experts are
 PyTorch ops. Reference behaviour: reference/31_fused_moe_fwd.py:254-315 (with shared expert weights;
 here every expert has its own).
+
+``fp8_experts`` keeps the received tokens in e4m3: the expert weights are quantised once to e4m3 with
+128 x 128 block scales, the gate/up GEMM runs block-scaled on the fp8 tokens with a SwiGLU + 1x128
+re-quantise epilogue and the down GEMM consumes that directly - no dequantise pass and no bf16 copy of
+the received tokens or of the hidden activations.
 """
 from __future__ import annotations
 
@@ -14,6 +19,7 @@ from dataclasses import dataclass
 import torch
 
 from ..ops.gemm import gemm_bf16
+from ..ops.gemm_fp8 import gemm_fp8_blockscaled
 from ..ops.moe import MoEExchange, grouped_gemm, interleave_gate_up
 
 
@@ -26,6 +32,7 @@ class MoEConfig:
     tokens_per_rank: int = 8192
     capacity_factor: float = 2.0
     fp8_dispatch: bool = True
+    fp8_experts: bool = False
     weight_std: float = 0.02
 
 
@@ -39,7 +46,19 @@ class EPMoELayer:
         self.w_down = w_down.contiguous()
         self.ex = MoEExchange(group, cfg.num_experts, cfg.hidden, cfg.tokens_per_rank, cfg.top_k, cfg.capacity_factor,
                               cfg.fp8_dispatch)
-        self.h = torch.empty((self.ex.capacity, cfg.inter), dtype=torch.bfloat16, device=w_router.device)
+        dev = w_router.device
+        if cfg.fp8_experts:
+            from ..refs.gemm_fp8 import quantize_weight_128x128
+
+            if not cfg.fp8_dispatch or cfg.hidden % 128 or cfg.inter % 128:
+                raise ValueError("fp8 experts need the fp8 dispatch and hidden, inter multiples of 128")
+            self.w8_gate_up, self.s_gate_up = quantize_weight_128x128(self.w_gate_up)
+            self.w8_down, self.s_down = quantize_weight_128x128(self.w_down)
+            self.w_gate_up = self.w_down = None
+            self.h8 = torch.empty((self.ex.capacity, cfg.inter), dtype=torch.uint8, device=dev)
+            self.h_scales = torch.empty((self.ex.capacity, cfg.inter // 128), dtype=torch.float32, device=dev)
+        else:
+            self.h = torch.empty((self.ex.capacity, cfg.inter), dtype=torch.bfloat16, device=dev)
 
     def route(self, x: torch.Tensor):
         logits = gemm_bf16(x, self.w_router, out_dtype=torch.float32, mode="single", block_n=128)
@@ -53,9 +72,16 @@ class EPMoELayer:
         gates, idx = self.route(x)
         flat_idx = idx.view(-1)
         self.ex.plan(flat_idx, self.comm)
-        xin = self.ex.dispatch(x, flat_idx)
-        grouped_gemm(xin, self.w_gate_up, self.ex.offsets, epilogue="swiglu", out=self.h)
-        grouped_gemm(self.h, self.w_down, self.ex.offsets, out=self.ex.y.local)
+        if self.cfg.fp8_experts:
+            x8, xs = self.ex.dispatch(x, flat_idx, dequantize=False)
+            gemm_fp8_blockscaled(x8, xs, self.w8_gate_up, self.s_gate_up, offsets=self.ex.offsets, epilogue="swiglu_quant",
+                                 out=self.h8, out_scales=self.h_scales)
+            gemm_fp8_blockscaled(self.h8, self.h_scales, self.w8_down, self.s_down, offsets=self.ex.offsets,
+                                 out=self.ex.y.local)
+        else:
+            xin = self.ex.dispatch(x, flat_idx)
+            grouped_gemm(xin, self.w_gate_up, self.ex.offsets, epilogue="swiglu", out=self.h)
+            grouped_gemm(self.h, self.w_down, self.ex.offsets, out=self.ex.y.local)
         return self.ex.combine(flat_idx, gates.view(-1), T)
 
     __call__ = forward

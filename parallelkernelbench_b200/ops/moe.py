@@ -85,9 +85,11 @@ class MoEExchange:
         return all_counts
 
     # -- dispatch ------------------------------------------------------------------------------
-    def dispatch(self, x: torch.Tensor, expert_idx: torch.Tensor) -> torch.Tensor:
+    def dispatch(self, x: torch.Tensor, expert_idx: torch.Tensor, dequantize: bool = True):
         """Send every (token, k) row to its expert's rank. Returns the received rows as bf16
-        ``[capacity, hidden]`` (rows ``[0, offsets[-1])`` are valid, expert-major)."""
+        ``[capacity, hidden]`` (rows ``[0, offsets[-1])`` are valid, expert-major); with
+        ``dequantize=False`` (fp8 dispatch only) the received e4m3 bytes ``[capacity, hidden]`` and their fp32
+        scales ``[capacity, >= hidden/128]`` instead, as views of the receive buffers."""
         from .elementwise import fp8_dequantize_1x128, fp8_quantize_1x128
 
         T = x.shape[0]
@@ -106,6 +108,10 @@ class MoEExchange:
             ctypes.c_ulonglong(self.recv_payload.offset), ctypes.c_ulonglong(self.recv_scales.offset), self.capacity,
             nv.ptr(self.overflow), nv.current_stream()), "pkb_moe_dispatch")
         nv.count_launch()
+        if self.fp8 and not dequantize:
+            return self.recv_payload.local, self.recv_scales.local.view(torch.float32)
+        if not dequantize:
+            raise ValueError("dequantize=False needs the fp8 dispatch")
         if self.fp8:
             nblk = self.hidden // 128
             s = self.recv_scales.local.view(torch.float32)[:, :nblk]

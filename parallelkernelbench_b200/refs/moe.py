@@ -20,8 +20,12 @@ def fp8_round_trip_1x128(x: torch.Tensor) -> torch.Tensor:
 
 
 def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: int, top_k: int, group=None,
-                  fp8_dispatch: bool = False, gates_idx=None):
-    """``w_gate``/``w_up``: [E_local, I, H], ``w_down``: [E_local, H, I]. Returns [T, H]."""
+                  fp8_dispatch: bool = False, gates_idx=None, fp8_experts: bool = False):
+    """``w_gate``/``w_up``: [E_local, I, H], ``w_down``: [E_local, H, I]. Returns [T, H].
+
+    ``fp8_experts`` models experts that compute on e4m3 operands: the weights go through the 128 x 128
+    block quantiser (gate and up interleaved row by row, as the fused gate/up weight is stored) and the
+    hidden activations through the 1x128 one after rounding to bf16."""
     W = dist.get_world_size(group) if dist.is_initialized() else 1
     r = dist.get_rank(group) if dist.is_initialized() else 0
     el = num_experts // W
@@ -32,6 +36,13 @@ def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: i
         gates, idx = torch.topk(torch.softmax(logits, dim=-1), top_k, dim=-1)
     else:
         gates, idx = gates_idx
+    if fp8_experts:
+        from .gemm_fp8 import dequantize_weight_128x128, quantize_weight_128x128
+
+        gu = torch.stack([w_gate, w_up], dim=-2).reshape(w_gate.shape[0], 2 * w_gate.shape[1], w_gate.shape[2])
+        gu = dequantize_weight_128x128(*quantize_weight_128x128(gu)).to(w_gate.dtype)
+        w_gate, w_up = gu[:, 0::2], gu[:, 1::2]
+        w_down = dequantize_weight_128x128(*quantize_weight_128x128(w_down)).to(w_down.dtype)
     flat_e = idx.reshape(-1).long()
     order = torch.argsort(flat_e, stable=True)
     tok = (order // top_k)
@@ -57,6 +68,8 @@ def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: i
             if n:
                 seg = recv[pos:pos + n]
                 h = F.silu(F.linear(seg, w_gate[e])) * F.linear(seg, w_up[e])
+                if fp8_experts:
+                    h = fp8_round_trip_1x128(h)
                 out_rows[pos:pos + n] = F.linear(h, w_down[e])
                 pos += n
     if W > 1:

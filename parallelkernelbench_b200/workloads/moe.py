@@ -149,7 +149,10 @@ def _moe_inputs(rc: RunCtx, cfg):
     if cfg.get("lora_rank"):
         r = cfg["lora_rank"]
         lora = [mk(el, r, H), mk(el, I, r), mk(el, r, H), mk(el, I, r), mk(el, r, I), mk(el, H, r)]
-    return (x, w_router, b_router, wg, wu, wd, E, cfg["topk"], members, bool(cfg.get("fp8", False)), lora)
+    # precision mode: 0 = bf16 on the wire, 1 = e4m3 + 1x128 scales on the wire, 2 = additionally e4m3 experts
+    # (128 x 128 block-scaled weights, re-quantised hidden activations)
+    fp8 = 2 if cfg.get("fp8_experts") else int(bool(cfg.get("fp8", False)))
+    return (x, w_router, b_router, wg, wu, wd, E, cfg["topk"], members, fp8, lora)
 
 
 def _merge_lora(wg, wu, wd, lora):
@@ -176,7 +179,8 @@ def _pg_for(rc, members):
 
 def _moe_ref(rc, x, w_router, b_router, wg, wu, wd, E, k, members, fp8, lora):
     wg, wu, wd = _merge_lora(wg, wu, wd, lora)
-    return moe_reference(x, w_router, b_router, wg, wu, wd, E, k, group=_pg_for(rc, members), fp8_dispatch=fp8)
+    return moe_reference(x, w_router, b_router, wg, wu, wd, E, k, group=_pg_for(rc, members), fp8_dispatch=fp8 >= 1,
+                         fp8_experts=fp8 >= 2)
 
 
 def _moe_ours(rc, x, w_router, b_router, wg, wu, wd, E, k, members, fp8, lora):
@@ -188,14 +192,15 @@ def _moe_ours(rc, x, w_router, b_router, wg, wu, wd, E, k, members, fp8, lora):
     key = ("moe_layer", x.shape, wg.data_ptr(), fp8)
     if key not in rc.cache:
         cfg = MoEConfig(hidden=x.shape[1], inter=wg.shape[1], num_experts=E, top_k=k, tokens_per_rank=x.shape[0],
-                        capacity_factor=float(len(members)) if x.shape[0] * k <= 8192 else 2.0, fp8_dispatch=fp8)
+                        capacity_factor=float(len(members)) if x.shape[0] * k <= 8192 else 2.0, fp8_dispatch=fp8 >= 1,
+                        fp8_experts=fp8 >= 2)
         rc.cache[key] = EPMoELayer(rc.comm.group(members), rc.comm, cfg, w_router, wg, wu, wd, router_bias=b_router)
     return rc.cache[key](x)
 
 
 def _moe_cost(cfg, W):
     T, H, I, k = cfg["tokens"], cfg["hidden"], cfg["inter"], cfg["topk"]
-    payload = H * (1 + 4 / 128) if cfg.get("fp8") else 2 * H
+    payload = H * (1 + 4 / 128) if (cfg.get("fp8") or cfg.get("fp8_experts")) else 2 * H
     return Cost(flops=6.0 * T * k * H * I, nvlink_bytes=T * k * (W - 1) / max(W, 1) * max(payload, 2 * H),
                 hbm_bytes=3.0 * 2 * H * I * max(cfg.get("experts", 8), W) / W)
 
@@ -209,6 +214,9 @@ _MOE_CFG = {
     "fp8": {"tokens": 1024, "hidden": 1024, "inter": 128, "experts": 8, "topk": 2, "fp8": True},
     "lora": {"tokens": 1024, "hidden": 1024, "inter": 128, "experts": 8, "topk": 2, "lora_rank": 8},
     "deepseek": {"tokens": 8192, "hidden": 7168, "inter": 2048, "experts": 256, "topk": 8, "fp8": True, "std": 0.02},
+    "fp8_experts": {"tokens": 1024, "hidden": 1024, "inter": 128, "experts": 8, "topk": 2, "fp8_experts": True},
+    "deepseek_fp8_experts": {"tokens": 8192, "hidden": 7168, "inter": 2048, "experts": 256, "topk": 8, "fp8_experts": True,
+                             "std": 0.02},
 }
 register(OpSpec(name="moe_layer", problem_ids=(28, 29, 31, 32, 49, 50, 51), group="moe", configs=_MOE_CFG, make_inputs=_moe_inputs,
                 reference=_moe_ref, ours=_moe_ours, atol=1e-1, rtol=3e-2, cost=_moe_cost, ours_needs_cuda=True,

@@ -126,3 +126,56 @@ def test_permuting_all_to_all_descriptor_reproduces_chunk_and_cat():
                             do = g * out_member_off + i0 * m[0][2] + i1 * m[1][2] + i2 * m[2][2]
                             ob[do:do + inner] = ib[so:so + inner]
             assert torch.equal(out, want[r]), (shape, sd, gd, r)
+
+
+def test_block_scaled_fp8_restatement():
+    """Quantisers invert within one e4m3 step, the block-scaled product equals the per-K-block scaled sum the kernel
+    forms, and the grouped form equals one dense product per group."""
+    from parallelkernelbench_b200.refs.gemm_fp8 import (dequantize_rows_1x128, dequantize_weight_128x128, gemm_fp8_blockscaled_ref,
+                                                        quantize_rows_1x128, quantize_weight_128x128)
+
+    torch.manual_seed(3)
+    M, N, K = 70, 256, 384
+    a, w = torch.randn(M, K) * 3, torch.randn(N, K) * 0.1
+    a[5, 128:256] = 0
+    a8, sa = quantize_rows_1x128(a)
+    w8, sb = quantize_weight_128x128(w)
+    assert a8.dtype == torch.uint8 and sa.shape == (M, K // 128) and sb.shape == (N // 128, K // 128) and sa[5, 1] == 1.0
+    torch.testing.assert_close(dequantize_rows_1x128(a8, sa), a, rtol=0.07, atol=3 * 448 * 2 ** -9 / 448)
+    torch.testing.assert_close(dequantize_weight_128x128(w8, sb), w, rtol=0.07, atol=1e-3)
+    assert dequantize_rows_1x128(a8, sa).abs().amax() <= a.abs().amax() * (1 + 1e-6)       # amax maps to +-448 exactly
+
+    # the sum the kernel forms: one unscaled e4m3 product per 128-deep K block, scaled and accumulated in fp32
+    af, wf = a8.view(torch.float8_e4m3fn).float(), w8.view(torch.float8_e4m3fn).float()
+    acc = torch.zeros(M, N)
+    for kb in range(K // 128):
+        part = af[:, kb * 128:(kb + 1) * 128] @ wf[:, kb * 128:(kb + 1) * 128].t()
+        acc += part * sa[:, kb:kb + 1] * sb[:, kb].repeat_interleave(128)[None, :]
+    ref = gemm_fp8_blockscaled_ref(a8, sa, w8, sb)
+    torch.testing.assert_close(ref.float(), acc.to(torch.bfloat16).float(), rtol=1e-2, atol=1e-2)
+
+    G = 3
+    wg8, sbg = quantize_weight_128x128(torch.randn(G, N, K) * 0.1)
+    offsets = torch.tensor([0, 20, 20, 64], dtype=torch.int32)
+    out = gemm_fp8_blockscaled_ref(a8, sa, wg8, sbg, offsets)
+    torch.testing.assert_close(out[:20], gemm_fp8_blockscaled_ref(a8[:20], sa[:20], wg8[0], sbg[0]))
+    torch.testing.assert_close(out[20:64], gemm_fp8_blockscaled_ref(a8[20:64], sa[20:64], wg8[2], sbg[2]))
+    assert out[64:].abs().max() == 0
+    h8, hs = gemm_fp8_blockscaled_ref(a8, sa, wg8, sbg, offsets, "swiglu_quant")
+    h = gemm_fp8_blockscaled_ref(a8, sa, wg8, sbg, offsets, "swiglu")
+    assert h8.shape == (M, N // 2) and hs.shape == (M, N // 256)
+    torch.testing.assert_close(dequantize_rows_1x128(h8, hs), h.float(), rtol=0.07, atol=1e-3 * h.float().abs().max().item() + 1e-6)
+
+
+def test_moe_reference_with_fp8_experts_stays_close_to_bf16_experts():
+    from parallelkernelbench_b200.refs.moe import moe_reference
+
+    torch.manual_seed(4)
+    T, H, I, E, k = 96, 256, 128, 4, 2
+    x = torch.randn(T, H).to(torch.bfloat16)
+    wr = (torch.randn(E, H) * 0.05).to(torch.bfloat16)
+    wg, wu, wd = [(torch.randn(*s) * 0.05).to(torch.bfloat16) for s in ((E, I, H), (E, I, H), (E, H, I))]
+    base = moe_reference(x, wr, None, wg, wu, wd, E, k, fp8_dispatch=True).float()
+    q = moe_reference(x, wr, None, wg, wu, wd, E, k, fp8_dispatch=True, fp8_experts=True).float()
+    err = (q - base).abs().max() / base.abs().max()
+    assert 0 < err < 0.1, err

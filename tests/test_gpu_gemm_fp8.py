@@ -1,0 +1,73 @@
+"""Block-scaled fp8 GEMM (dense, grouped, SwiGLU and re-quantising epilogues) against the fp32 PyTorch restatement
+of the same arithmetic on dequantised operands.
+
+These kernels have been compiled for sm_100a but not yet executed on hardware, so the module only runs when
+PKB_RUN_NEW_KERNELS=1 is set; the gate goes away with their first validated run."""
+import os
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("PKB_RUN_NEW_KERNELS") != "1", reason="set PKB_RUN_NEW_KERNELS=1 for kernels awaiting their first hardware run")]
+
+
+def _operands(M, N, K, groups=0, seed=0):
+    from parallelkernelbench_b200.refs.gemm_fp8 import quantize_rows_1x128, quantize_weight_128x128
+
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randn(M, K, device="cuda", generator=g) * torch.rand(M, 1, device="cuda", generator=g) * 4   # rows of different magnitude
+    w = torch.randn((groups, N, K) if groups else (N, K), device="cuda", generator=g) * 0.05
+    return quantize_rows_1x128(a), quantize_weight_128x128(w)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (300, 384, 512), (4096, 2048, 2048)])
+def test_dense_matches_dequantised_product(M, N, K):
+    from parallelkernelbench_b200.ops.gemm_fp8 import gemm_fp8_blockscaled
+    from parallelkernelbench_b200.refs.gemm_fp8 import gemm_fp8_blockscaled_ref
+
+    (a8, sa), (w8, sb) = _operands(M, N, K)
+    out = torch.full((M + 8, N), float("nan"), device="cuda", dtype=torch.bfloat16)      # rows past M must stay untouched
+    gemm_fp8_blockscaled(a8, sa, w8, sb, out=out[:M])
+    ref = gemm_fp8_blockscaled_ref(a8, sa, w8, sb)
+    torch.testing.assert_close(out[:M].float(), ref.float(), rtol=1e-2, atol=1e-2 * ref.float().abs().max().item())
+    assert torch.isnan(out[M:]).all()
+
+
+def test_grouped_swiglu_and_requantise_feed_a_second_gemm():
+    from parallelkernelbench_b200.ops.gemm_fp8 import gemm_fp8_blockscaled
+    from parallelkernelbench_b200.refs.gemm_fp8 import dequantize_rows_1x128, gemm_fp8_blockscaled_ref
+
+    G, H, I = 6, 512, 256
+    counts = torch.tensor([130, 0, 128, 5, 257, 64])
+    offsets = torch.zeros(G + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0)
+    M = int(offsets[-1]) + 40                                            # spare rows after the last group
+    (a8, sa), (w8, sb) = _operands(M, 2 * I, H, groups=G, seed=1)
+    off_d = offsets.cuda()
+
+    h_ref = gemm_fp8_blockscaled_ref(a8, sa, w8, sb, offsets, "swiglu")
+    h = gemm_fp8_blockscaled(a8, sa, w8, sb, offsets=off_d, epilogue="swiglu")
+    rows = int(offsets[-1])
+    torch.testing.assert_close(h[:rows].float(), h_ref[:rows].float(), rtol=2e-2, atol=2e-2 * h_ref.float().abs().max().item())
+
+    h8, hs = gemm_fp8_blockscaled(a8, sa, w8, sb, offsets=off_d, epilogue="swiglu_quant")
+    h8_ref, hs_ref = gemm_fp8_blockscaled_ref(a8, sa, w8, sb, offsets, "swiglu_quant")
+    back, back_ref = dequantize_rows_1x128(h8[:rows], hs[:rows]), dequantize_rows_1x128(h8_ref[:rows], hs_ref[:rows])
+    torch.testing.assert_close(back, back_ref, rtol=0.14, atol=2e-2 * back_ref.abs().max().item())   # one e4m3 step where bf16 rounding differs
+
+    (_, _), (w8d, sbd) = _operands(1, H, I, groups=G, seed=2)
+    y = gemm_fp8_blockscaled(h8, hs, w8d, sbd, offsets=off_d)
+    y_ref = gemm_fp8_blockscaled_ref(h8, hs, w8d, sbd, offsets)
+    torch.testing.assert_close(y[:rows].float(), y_ref[:rows].float(), rtol=1e-2, atol=1e-2 * y_ref.float().abs().max().item())
+
+
+def test_moe_layer_with_fp8_experts_matches_its_reference():
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=1", "--master-addr", "127.0.0.1",
+           "--master-port", "29671", os.path.join(root, "tests/mp/all_ops_worker.py"), "--ops", "moe_layer", "--config", "fp8_experts"]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
