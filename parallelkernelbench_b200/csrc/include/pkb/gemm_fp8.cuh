@@ -250,7 +250,7 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
       const bool row_ok = row < row_end;
       const int col0 = n_blk * BN + half * 128;        // first accumulator column of this thread
       const bool half_ok = col0 < p.N;
-      const float* sa_row = p.sa + (long long)(row_ok ? row : tile_row0) * p.sa_stride;
+      const float* sa_row = p.sa + (long long)(row_ok ? row : min(tile_row0, p.M - 1)) * p.sa_stride;
       const float* sb_row = p.sb + (long long)((b_row0 + (half_ok ? half * 128 : 0)) >> 7) * p.sb_stride;
 
       float acc[128];

@@ -12,11 +12,16 @@
 //                   After its tiles, every CTA turns into a consumer: it waits for the counters of
 //                   its rows, adds the W partial slots in rank order in fp32, applies RMSNorm and
 //                   writes bf16 - the reduced tensor never exists un-normalised in memory.
+//  tp_gemm_allreduce  GEMM -> all-reduce (row-parallel linear). The same scatter epilogue as above sends every partial
+//                   tile to the rank that owns its rows; the consumer phase adds the W partial slots of its rows in
+//                   rank order and stores the sum into the result buffer of EVERY rank: one `multimem.st` through
+//                   the switch when the group is the whole job and the heap has a multicast mapping, else one
+//                   16-byte P2P store per member. A closing barrier tells each rank that all rows have landed.
 //
-// Reference behaviour being replaced: all_gather + matmul + silu, matmul + reduce_scatter, and
-// reduce_scatter + RMSNorm as separate NCCL / cuBLAS / elementwise launches
+// Reference behaviour being replaced: all_gather + matmul + silu, matmul + reduce_scatter,
+// reduce_scatter + RMSNorm and matmul + all_reduce as separate NCCL / cuBLAS / elementwise launches
 // (reference: reference/15_combined_sharded_gemms.py:17-31, reference/16_gemm_reducescatter.py:19-22,
-//  reference/45_reducescatter_fused_rmsnorm.py:23-29).
+//  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20).
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
 #include "pkb/gemm_umma2.cuh"
@@ -179,6 +184,81 @@ tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 }
 
+struct TpArArgs {
+  SymmCtx ctx;
+  uint64_t recv_off;     // heap offset of the receive slots [gsize][rows_per_rank, N] bf16
+  uint64_t done_off;     // heap offset of the per-row-block arrival counters (uint32)
+  uint32_t done_target;  // cumulative arrivals expected per row block once this call is complete
+  uint64_t out_off;      // heap offset of the all-reduced result [gsize * rows_per_rank, N] bf16 (same on every rank)
+  float scale;
+  int N;
+  int rows_per_rank;
+  int use_mc;            // 1: broadcast the reduced rows with multimem.st (whole-job group with a multicast mapping)
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+tp_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
+                         const TpArArgs a) {
+  const SymmCtx& c = a.ctx;
+  // all ranks have entered this call => all ranks have consumed the previous call's receive slots and result
+  if (!symm_block_barrier(c, 302, 1)) return;
+  gemm_umma2_cta<kEpiNone, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1,
+                                                     gridDim.x >> 1, &out_maps);
+  __syncthreads();
+
+  // ---- consumer phase: reduce the W partial slots of my rows, store the sums on every rank ----
+  __shared__ int s_ok;
+  const uint32_t* done = symm_local<uint32_t>(c, a.done_off);
+  const __nv_bfloat16* slots = symm_local<__nv_bfloat16>(c, a.recv_off);
+  const long long slot_stride = (long long)a.rows_per_rank * a.N;
+  const long long my_row0 = (long long)c.grank * a.rows_per_rank;
+  int waited_blk = -1;
+  const int nthreads = blockDim.x;
+  for (int row = blockIdx.x; row < a.rows_per_rank; row += gridDim.x) {
+    const int blk = row / kGemmBlockM;
+    if (blk != waited_blk) {
+      if (threadIdx.x == 0) {
+        s_ok = wait_flag_ge(done + blk, a.done_target, c.budget_ns) ? 1 : 0;
+        if (!s_ok) record_status(c.status, kStatusPeerTimeout, 302, c.rank, blk, 2, row);
+      }
+      __syncthreads();
+      if (!s_ok) return;
+      waited_blk = blk;
+    }
+    for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int g = 0; g < c.gsize; ++g) {
+        // peers wrote these rows with TMA stores followed by a release; read them coherently
+        U4 u = ld_global_relaxed_v4(slots + g * slot_stride + (long long)row * a.N + i);
+        float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
+               f3 = unpack_bf16x2(u.w);
+        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
+        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
+      }
+      U4 o;
+      o.x = pack_bf16x2(acc[0] * a.scale, acc[1] * a.scale);
+      o.y = pack_bf16x2(acc[2] * a.scale, acc[3] * a.scale);
+      o.z = pack_bf16x2(acc[4] * a.scale, acc[5] * a.scale);
+      o.w = pack_bf16x2(acc[6] * a.scale, acc[7] * a.scale);
+      const long long eoff = (my_row0 + row) * a.N + i;
+      if (a.use_mc) {
+        multimem_st_v4(symm_mc<__nv_bfloat16>(c, a.out_off) + eoff, o);
+      } else {
+        for (int k = 0; k < c.gsize; ++k) {
+          int g = c.grank + k;       // own copy first, peers spread over time
+          if (g >= c.gsize) g -= c.gsize;
+          st_global_v4(symm_ptr<__nv_bfloat16>(c, c.members[g], a.out_off) + eoff, o);
+        }
+      }
+    }
+  }
+  // every same-index block of every rank has stored its rows once this barrier passes; the kernel ends on a rank
+  // only after all its blocks passed, i.e. after all rows of all ranks have landed here
+  symm_block_barrier(c, 302, 3);
+}
+
 
 }  // namespace pkb
 
@@ -332,6 +412,69 @@ int pkb_tp_gemm_rs_rmsnorm(const pkb_symm_ctx* h, const void* a_mat, long long l
 
   constexpr int smem = kGemm2SmemTotal;
   auto k = tp_gemm_rs_rmsnorm_kernel;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int grid = sm_count() & ~1;
+  if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
+  k<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, om, p, a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// result[gsize * rows_per_rank, N] (bf16, at heap offset out_off on every rank) = scale * all_reduce( a @ w^T ), with
+// a [gsize * rows_per_rank, K] and w [N, K] this rank's K-shard of a row-parallel linear layer. recv_off / done_off /
+// call_index as for pkb_tp_gemm_rs_rmsnorm. N % 8 == 0. The result is valid on this rank when the kernel has finished.
+int pkb_tp_gemm_allreduce(const pkb_symm_ctx* h, const void* a_mat, long long lda, const void* w, long long ldb,
+                          int rows_per_rank, int N, int K, unsigned long long recv_off, unsigned long long done_off,
+                          unsigned int call_index, unsigned long long out_off, float scale, int allow_multicast,
+                          void* stream) {
+  PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
+  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kGemmMaxWorld, "group size must be 1..8");
+  PKB_CHECK_ARG(rows_per_rank % kGemm2TileM == 0, "rows_per_rank must be a multiple of 256");
+  PKB_CHECK_ARG(N % 8 == 0 && K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "N, K, lda, ldb must be multiples of 8");
+  PKB_CHECK_ARG((recv_off & 15) == 0 && (done_off & 15) == 0 && (out_off & 15) == 0, "heap offsets misaligned");
+  const int W = h->gsize;
+  const int M = W * rows_per_rank;
+  SymmCtx ctx = symm_ctx_from_api(h);
+
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a_mat, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2,
+                          kGemmBlockK, kGemmBlockM, kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, kGemmBlockK, 128,
+                      kSwizzle128);
+  if (rc) return rc;
+
+  GemmOutMaps om;
+  GemmParams p = {};
+  p.M = M; p.N = N; p.K = K; p.C = nullptr; p.ldc = N; p.alpha = 1.0f;
+  p.status = ctx.status; p.wait_budget_ns = ctx.budget_ns;
+  p.kernel_id = 302;
+  p.rank = h->rank; p.world = W;
+  p.rs_rows_per_rank = rows_per_rank;
+  const long long slot_bytes = (long long)rows_per_rank * N * 2;
+  for (int g = 0; g < W; ++g) {
+    const uint64_t peer = h->base + (uint64_t)h->members[g] * h->stride;
+    p.rs_out[g] = reinterpret_cast<void*>(peer + recv_off + (uint64_t)h->grank * slot_bytes);
+    p.rs_done[g] = reinterpret_cast<uint32_t*>(peer + done_off);
+    rc = encode_tmap_2d(&om.m[g], kTmapBf16, p.rs_out[g], (uint64_t)N, (uint64_t)rows_per_rank,
+                        (uint64_t)N * 2, 64, 32, kSwizzle128);
+    if (rc) return rc;
+  }
+  const int blocks_per_rank = rows_per_rank / kGemm2TileM;
+  p.group_m = blocks_per_rank < 8 ? blocks_per_rank : 8;
+  while (blocks_per_rank % p.group_m != 0) --p.group_m;
+  p.m_block_rotation = ((h->grank + 1) % W) * blocks_per_rank;  // rank+1's rows first, own rows last
+
+  const int num_n = (N + 255) / 256;
+  TpArArgs a;
+  a.ctx = ctx;
+  a.recv_off = recv_off; a.done_off = done_off; a.out_off = out_off;
+  a.done_target = call_index * (uint32_t)(W * num_n * 4);
+  a.scale = scale; a.N = N; a.rows_per_rank = rows_per_rank;
+  a.use_mc = (allow_multicast && h->mc_base != 0 && h->gsize == h->world && W > 1) ? 1 : 0;
+
+  constexpr int smem = kGemm2SmemTotal;
+  auto k = tp_gemm_allreduce_kernel;
   PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int grid = sm_count() & ~1;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;

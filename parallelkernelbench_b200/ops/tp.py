@@ -4,8 +4,11 @@
                      the peers while the tcgen05 GEMM consumes row chunks as their flags arrive.
 ``GemmReduceScatterRMSNorm``  (a @ w.T) reduce-scattered over rows, then RMSNorm, in one launch: the
                      GEMM epilogue stores partial tiles into the owner's receive slots over NVLink.
+``GemmAllReduce``    (a @ w.T) summed over the ranks (row-parallel linear) in one launch: the same scatter epilogue,
+                     then each rank adds the partial slots of its rows and stores the sums on every rank
+                     (``multimem.st`` through the switch, or one P2P store per member), closed by a barrier.
 
-Both keep their symmetric buffers between calls (steady-state calls allocate nothing), like the
+All keep their symmetric buffers between calls (steady-state calls allocate nothing), like the
 module-level buffer caches of the reference's example solutions
 (reference: kernelgen/solution_new_add_cuda.py:70-84) but owned by an object instead of globals.
 """
@@ -87,3 +90,38 @@ class GemmReduceScatterRMSNorm:
             nv.current_stream()), "pkb_tp_gemm_rs_rmsnorm")
         nv.count_launch()
         return out
+
+
+class GemmAllReduce:
+    """Row-parallel linear layer with its all-reduce fused in (reference: reference/13_gemm_allreduce.py:17-20).
+
+    ``M = W * rows_per_rank`` rows; the result lives in the symmetric heap and is returned as a view that stays valid
+    until the next call of this object."""
+
+    def __init__(self, group: SymmGroup, rows_per_rank: int, n: int, multicast: bool = True):
+        if rows_per_rank % 256 != 0:
+            raise ValueError("rows per rank must be a multiple of 256 (one CTA-pair tile)")
+        if n % 8 != 0:
+            raise ValueError("n must be a multiple of 8")
+        self.group, self.rows, self.n, self.multicast = group, rows_per_rank, n, multicast
+        heap = group.heap
+        self.recv = heap.empty((group.size, rows_per_rank, n), torch.bfloat16)
+        self.done = heap.empty((max(rows_per_rank // 128, 4),), torch.int32)
+        self.out = heap.empty((group.size * rows_per_rank, n), torch.bfloat16)
+        self.done.local.zero_()
+        self.calls = 0
+
+    def __call__(self, a: torch.Tensor, w: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        W = self.group.size
+        if a.shape[0] != W * self.rows or a.dtype != torch.bfloat16 or a.stride(1) != 1:
+            raise ValueError("a must be bf16 [W * rows_per_rank, K_local]")
+        if w.shape != (self.n, a.shape[1]) or w.stride(1) != 1 or w.dtype != torch.bfloat16:
+            raise ValueError("w must be bf16 [N, K_local]")
+        self.calls += 1
+        nv.check(nv.cuda_lib().pkb_tp_gemm_allreduce(
+            self.group.ref, nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(w.stride(0)), self.rows, self.n, a.shape[1],
+            ctypes.c_ulonglong(self.recv.offset), ctypes.c_ulonglong(self.done.offset), ctypes.c_uint(self.calls),
+            ctypes.c_ulonglong(self.out.offset), nv.c_float(scale), 1 if self.multicast else 0, nv.current_stream()),
+            "pkb_tp_gemm_allreduce")
+        nv.count_launch()
+        return self.out.local

@@ -159,8 +159,26 @@ def _gar_ref(rc, a, b):
     return c
 
 
-register(OpSpec(name="gemm_allreduce", problem_ids=(13,), group="tp", configs=_GEMM_CFG, make_inputs=_gar_inputs,
-                reference=_gar_ref, ours=lambda rc, a, b: rc.comm.all_reduce(_mm(rc, a, b)), atol=1.0, rtol=3e-2,
+def _gar_ours(rc, a, b):
+    """Two launches (tcgen05 GEMM, symmetric-heap all-reduce), or the single fused kernel when PKB_FUSED_GEMM_AR=1 and
+    the shapes fit it (rows a multiple of 256 per rank, K and N multiples of 8)."""
+    import os
+
+    W, (M, K), N = rc.world, a.shape, b.shape[1]
+    if (os.environ.get("PKB_FUSED_GEMM_AR") == "1" and rc.dist.is_cuda and a.dtype == torch.bfloat16 and M % (256 * W) == 0
+            and K % 8 == 0 and N % 8 == 0):
+        from ..ops.tp import GemmAllReduce
+
+        key = ("gemm_ar", M, N, b.data_ptr())
+        if key not in rc.cache:
+            rc.cache[key] = (GemmAllReduce(rc.comm.group(), M // W, N), b.t().contiguous())
+        op, w = rc.cache[key]
+        return op(a.contiguous(), w).clone()
+    return rc.comm.all_reduce(_mm(rc, a, b))
+
+
+register(OpSpec(name="gemm_allreduce", problem_ids=(13,), group="tp", configs={**_GEMM_CFG, "large": {"m": 4096, "n": 8192, "k": 1024}},
+                make_inputs=_gar_inputs, reference=_gar_ref, ours=_gar_ours, atol=1.0, rtol=3e-2,
                 cost=lambda cfg, W: Cost(flops=2.0 * cfg["m"] * cfg["n"] * cfg["k"], nvlink_bytes=cfg["m"] * cfg["n"] * 2 * (W - 1) / max(W, 1))))
 
 

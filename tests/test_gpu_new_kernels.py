@@ -1,5 +1,5 @@
 """Block-scaled fp8 GEMM (dense, grouped, SwiGLU and re-quantising epilogues) against the fp32 PyTorch restatement
-of the same arithmetic on dequantised operands.
+of the same arithmetic on dequantised operands, and the fused GEMM + all-reduce against GEMM then sum.
 
 These kernels have been compiled for sm_100a but not yet executed on hardware, so the module only runs when
 PKB_RUN_NEW_KERNELS=1 is set; the gate goes away with their first validated run."""
@@ -71,3 +71,22 @@ def test_moe_layer_with_fp8_experts_matches_its_reference():
            "--master-port", "29671", os.path.join(root, "tests/mp/all_ops_worker.py"), "--ops", "moe_layer", "--config", "fp8_experts"]
     r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def _all_ops(nproc, port, *args, env=None):
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(root, "tests/mp/all_ops_worker.py"), *args]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=600, env={**os.environ, **(env or {})})
+    assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_fused_gemm_allreduce_matches_gemm_then_allreduce(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _all_ops(nproc, 29672 + nproc, "--ops", "gemm_allreduce", "--config", "default", env={"PKB_FUSED_GEMM_AR": "1"})
+    _all_ops(nproc, 29676 + nproc, "--ops", "gemm_allreduce", "--config", "large", env={"PKB_FUSED_GEMM_AR": "1"})
