@@ -2,6 +2,8 @@
 // and slots stay on the device (the reference pays three host syncs per layer call,
 // reference: reference/31_fused_moe_fwd.py:60-101).
 //
+//  moe_route       one warp per token: router logits (+ bias) -> softmax -> top-k (descending, ties to the lower
+//                  expert index) -> gates, expert indices and the per-expert histogram, in one pass over the row
 //  moe_histogram   per-expert assignment counts of this rank's tokens
 //  moe_plan        from the all-gathered count matrix [W, E]: where each (source, expert) segment starts
 //                  in its destination's receive buffer (expert-major, source-minor), this rank's own
@@ -31,6 +33,68 @@ __global__ void moe_histogram_kernel(const int* __restrict__ expert_idx, long lo
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const int e = expert_idx[i];
     if (e >= 0 && e < num_experts) atomicAdd(&hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
+    if (hist[e]) atomicAdd(&counts[e], hist[e]);
+}
+
+// Softmax over up to 256 experts and top-k selection, one warp per token. Lane l holds experts l, l + 32, ...
+// Selection = k rounds of a warp-wide arg-max on (probability, lower index wins ties), so the output is sorted by
+// descending probability like torch.topk. The histogram is accumulated per block in shared memory first.
+constexpr int kRouteMaxPerLane = 8;
+
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ bias, int num_tokens,
+                 int num_experts, int top_k, float* __restrict__ gates, int* __restrict__ idx, int* __restrict__ counts) {
+  extern __shared__ int hist[];
+  for (int e = threadIdx.x; e < num_experts; e += blockDim.x) hist[e] = 0;
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  for (long long t = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < num_tokens;
+       t += (long long)gridDim.x * warps_per_block) {
+    const float* row = logits + t * ld;
+    float v[kRouteMaxPerLane];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      const int e = j * 32 + lane;
+      v[j] = e < num_experts ? row[e] + (bias ? bias[e] : 0.f) : -INFINITY;
+      m = fmaxf(m, v[j]);
+    }
+    m = warp_max(m);
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRouteMaxPerLane; ++j) {
+      v[j] = (j * 32 + lane) < num_experts ? expf(v[j] - m) : -1.f;   // probabilities are >= 0: -1 marks "absent / taken"
+      sum += fmaxf(v[j], 0.f);
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int r = 0; r < top_k; ++r) {
+      float best = -1.f;
+      int best_e = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < kRouteMaxPerLane; ++j)
+        if (v[j] > best) { best = v[j]; best_e = j * 32 + lane; }   // ascending j: the lower index wins ties
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oe = __shfl_xor_sync(0xffffffffu, best_e, off);
+        if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+      }
+      if ((best_e & 31) == lane) {
+#pragma unroll
+        for (int j = 0; j < kRouteMaxPerLane; ++j)
+          if (j == (best_e >> 5)) v[j] = -1.f;
+      }
+      if (lane == 0) {
+        gates[t * top_k + r] = best * inv;
+        idx[t * top_k + r] = best_e;
+        atomicAdd(&hist[best_e], 1);
+      }
+    }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < num_experts; e += blockDim.x)
@@ -184,6 +248,24 @@ int pkb_moe_histogram(const void* expert_idx, long long n, int num_experts, void
   if (blocks > 148 * 4) blocks = 148 * 4;
   moe_histogram_kernel<<<(int)blocks, 256, num_experts * sizeof(int), s>>>(static_cast<const int*>(expert_idx), n,
                                                                           num_experts, static_cast<int*>(counts));
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// logits [T, E] fp32 (row pitch ld elements) + optional fp32 bias [E] -> gates [T, k] fp32 (softmax probabilities of the
+// chosen experts, descending), idx [T, k] int32, counts [E] int32 (zeroed here, then accumulated). E <= 256, k <= E.
+int pkb_moe_route(const void* logits, long long ld, const void* bias, int num_tokens, int num_experts, int top_k,
+                  void* gates, void* idx, void* counts, void* stream) {
+  PKB_CHECK_ARG(num_experts >= 1 && num_experts <= 32 * kRouteMaxPerLane, "1..256 experts");
+  PKB_CHECK_ARG(top_k >= 1 && top_k <= num_experts, "top_k must be in 1..experts");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PKB_CHECK_CUDA(cudaMemsetAsync(counts, 0, sizeof(int) * num_experts, s));
+  if (num_tokens == 0) return kApiOk;
+  long long blocks = ((long long)num_tokens + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  moe_route_kernel<<<(int)blocks, 256, num_experts * sizeof(int), s>>>(
+      static_cast<const float*>(logits), ld, static_cast<const float*>(bias), num_tokens, num_experts, top_k,
+      static_cast<float*>(gates), static_cast<int*>(idx), static_cast<int*>(counts));
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -20,7 +20,7 @@ import torch
 
 from ..ops.gemm import gemm_bf16
 from ..ops.gemm_fp8 import gemm_fp8_blockscaled
-from ..ops.moe import MoEExchange, grouped_gemm, interleave_gate_up
+from ..ops.moe import MoEExchange, grouped_gemm, interleave_gate_up, route_topk
 
 
 @dataclass
@@ -33,6 +33,7 @@ class MoEConfig:
     capacity_factor: float = 2.0
     fp8_dispatch: bool = True
     fp8_experts: bool = False
+    fused_router: bool = False      # softmax + top-k + histogram in one kernel instead of PyTorch ops + histogram kernel
     weight_std: float = 0.02
 
 
@@ -42,6 +43,9 @@ class EPMoELayer:
         """``w_router`` [E, H]; ``w_gate``/``w_up`` [E_local, I, H]; ``w_down`` [E_local, H, I] (all bf16)."""
         self.group, self.comm, self.cfg = group, comm, cfg
         self.w_router, self.router_bias = w_router.contiguous(), router_bias
+        self.router_bias_f32 = None if router_bias is None else router_bias.float().contiguous()
+        if cfg.fused_router and cfg.num_experts > 256:
+            raise ValueError("the fused router handles at most 256 experts")
         self.w_gate_up = interleave_gate_up(w_gate, w_up)
         self.w_down = w_down.contiguous()
         self.ex = MoEExchange(group, cfg.num_experts, cfg.hidden, cfg.tokens_per_rank, cfg.top_k, cfg.capacity_factor,
@@ -62,6 +66,9 @@ class EPMoELayer:
 
     def route(self, x: torch.Tensor):
         logits = gemm_bf16(x, self.w_router, out_dtype=torch.float32, mode="single", block_n=128)
+        if self.cfg.fused_router:
+            gates, idx, _ = route_topk(logits, self.router_bias_f32, self.cfg.top_k, counts=self.ex.counts)
+            return gates, idx
         if self.router_bias is not None:
             logits = logits + self.router_bias.float()
         gates, idx = torch.topk(torch.softmax(logits, dim=-1), self.cfg.top_k, dim=-1)
@@ -71,7 +78,7 @@ class EPMoELayer:
         T = x.shape[0]
         gates, idx = self.route(x)
         flat_idx = idx.view(-1)
-        self.ex.plan(flat_idx, self.comm)
+        self.ex.plan(flat_idx, self.comm, counts_ready=self.cfg.fused_router)
         if self.cfg.fp8_experts:
             x8, xs = self.ex.dispatch(x, flat_idx, dequantize=False)
             gemm_fp8_blockscaled(x8, xs, self.w8_gate_up, self.s_gate_up, offsets=self.ex.offsets, epilogue="swiglu_quant",

@@ -39,6 +39,29 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, epi
     return out
 
 
+def route_topk(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, counts: torch.Tensor | None = None):
+    """Softmax over the experts, top-k and the per-expert histogram in one kernel (one warp per token).
+
+    ``logits`` fp32 ``[T, E]`` (E <= 256), ``bias`` fp32 ``[E]`` or None. Returns ``(gates [T, k] fp32, idx [T, k] int32,
+    counts [E] int32)``, the gates in descending order with ties going to the lower expert index - what
+    ``torch.topk(torch.softmax(logits + bias, -1), k)`` returns (reference: reference/31_fused_moe_fwd.py:269-277)."""
+    if logits.dtype != torch.float32 or logits.dim() != 2 or logits.stride(1) != 1:
+        raise TypeError("logits must be fp32 [T, E] with unit inner stride")
+    T, E = logits.shape
+    if E > 256 or not 1 <= top_k <= E:
+        raise ValueError("at most 256 experts and 1 <= top_k <= E")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != E or not bias.is_contiguous()):
+        raise TypeError("bias must be contiguous fp32 [E]")
+    gates = torch.empty((T, top_k), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+    if counts is None:
+        counts = torch.empty(E, dtype=torch.int32, device=logits.device)
+    nv.check(nv.cuda_lib().pkb_moe_route(nv.ptr(logits), nv.c_ll(logits.stride(0)), nv.ptr(bias), T, E, top_k, nv.ptr(gates),
+                                         nv.ptr(idx), nv.ptr(counts), nv.current_stream()), "pkb_moe_route")
+    nv.count_launch()
+    return gates, idx, counts
+
+
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """``[..., I, H]`` gate and up weights -> ``[..., 2I, H]`` with rows (g0, u0, g1, u1, ...)."""
     return torch.stack([w_gate, w_up], dim=-2).reshape(*w_gate.shape[:-2], 2 * w_gate.shape[-2], w_gate.shape[-1]).contiguous()
@@ -71,12 +94,14 @@ class MoEExchange:
         self.slots = None
 
     # -- planning ------------------------------------------------------------------------------
-    def plan(self, expert_idx: torch.Tensor, comm) -> torch.Tensor:
-        """``expert_idx`` int32 ``[T * k]``. Returns the all-gathered count matrix ``[W, E]`` (device)."""
+    def plan(self, expert_idx: torch.Tensor, comm, counts_ready: bool = False) -> torch.Tensor:
+        """``expert_idx`` int32 ``[T * k]``. Returns the all-gathered count matrix ``[W, E]`` (device).
+        ``counts_ready``: ``self.counts`` already holds this rank's histogram (the fused router wrote it)."""
         lib = nv.cuda_lib()
-        nv.check(lib.pkb_moe_histogram(nv.ptr(expert_idx), nv.c_ll(expert_idx.numel()), self.E, nv.ptr(self.counts),
-                                       nv.current_stream()), "pkb_moe_histogram")
-        nv.count_launch()
+        if not counts_ready:
+            nv.check(lib.pkb_moe_histogram(nv.ptr(expert_idx), nv.c_ll(expert_idx.numel()), self.E, nv.ptr(self.counts),
+                                           nv.current_stream()), "pkb_moe_histogram")
+            nv.count_launch()
         all_counts = comm.all_gather(self.counts, self.group) if self.group.size > 1 else self.counts.unsqueeze(0)
         nv.check(lib.pkb_moe_plan(nv.ptr(all_counts), self.group.size, self.E, self.El, self.group.rank_in_group,
                                   nv.ptr(self.seg_base), nv.ptr(self.offsets), nv.ptr(self.cursor), nv.current_stream()),

@@ -90,3 +90,29 @@ def test_fused_gemm_allreduce_matches_gemm_then_allreduce(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     _all_ops(nproc, 29672 + nproc, "--ops", "gemm_allreduce", "--config", "default", env={"PKB_FUSED_GEMM_AR": "1"})
     _all_ops(nproc, 29676 + nproc, "--ops", "gemm_allreduce", "--config", "large", env={"PKB_FUSED_GEMM_AR": "1"})
+
+
+@pytest.mark.parametrize("E,k", [(8, 2), (64, 6), (256, 8), (100, 3)])
+def test_fused_router_matches_softmax_topk_bincount(E, k):
+    from parallelkernelbench_b200.ops.moe import route_topk
+
+    g = torch.Generator(device="cuda").manual_seed(E)
+    logits = torch.randn(777, E, device="cuda", generator=g) * 2
+    bias = torch.randn(E, device="cuda", generator=g) * 0.1
+    logits[5, :] = 0.25                                    # a row of exact ties: the lowest indices must win, in order
+    for b in (None, bias):
+        if b is not None:
+            logits[5, :] = 0.25 - b                        # keep the tie after the bias is added
+        gates, idx, counts = route_topk(logits, b, k)
+        ref_g, ref_i = torch.topk(torch.softmax(logits + (0 if b is None else b), dim=-1), k, dim=-1)
+        torch.testing.assert_close(gates, ref_g, rtol=1e-5, atol=1e-7)
+        rows = torch.ones(777, dtype=torch.bool, device="cuda")
+        rows[5] = False                                    # torch.topk leaves the order among exact ties unspecified
+        assert torch.equal(idx[rows].long(), ref_i[rows])
+        if b is None:
+            assert idx[5].tolist() == list(range(k))
+        assert torch.equal(counts.long(), torch.bincount(idx.view(-1).long(), minlength=E))
+
+
+def test_moe_layer_with_fused_router():
+    _all_ops(1, 29681, "--ops", "moe_layer", "--config", "default", env={"PKB_FUSED_ROUTER": "1"})
