@@ -61,6 +61,9 @@ struct GemmParams {
   // ---- rank / schedule ----------------------------------------------------------------------
   int rank, world;
   int m_block_rotation;  // logical m-block i is physical (i + rotation) % num_m_blocks
+  // ---- GEMM -> all-gather along N (broadcast epilogue of the CTA-pair kernel) ------------------
+  int rank_in_group;     // index of this rank among the `world` destination maps
+  int bcast_col0;        // first column of this rank's block in the gathered result
   // ---- grouped (ragged) form ------------------------------------------------------------------
   // A holds the rows of `grp_count` groups back to back: group e owns rows
   // [grp_offsets[e], grp_offsets[e+1]) (device memory, so the host never learns the counts) and

@@ -26,13 +26,16 @@ struct alignas(64) GemmOutMaps {
   CUtensorMap m[kGemmMaxWorld];
 };
 
-template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false>
+// BCAST (with TMA_STORE): every output tile is stored into the result of EVERY rank (maps m[0 .. world)), at column
+// p.bcast_col0 + its own column: the all-gather along N of a column-parallel GEMM happens in the epilogue.
+template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false, bool BCAST = false>
 __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const int pair,
                                                const int num_pairs,
                                                const GemmOutMaps* out_maps = nullptr,
                                                const CUtensorMap* tmap_a_local = nullptr) {
   static_assert(!(TMA_STORE && OUT_F32), "the TMA-store epilogue writes bf16");
+  static_assert(!BCAST || (TMA_STORE && !RS_SCATTER), "the broadcast epilogue is a TMA-store epilogue");
   constexpr int kStages = kGemm2Stages;
   constexpr int BN = kGemm2TileN;
   constexpr uint32_t kTmemCols = 512;
@@ -279,7 +282,15 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && col0 < p.N && row_blk0 + q * 32 < p.M) {
-            tma_store_2d(&out_maps->m[map_idx], buf, col0, row_coord);
+            if constexpr (BCAST) {
+              for (int k = 0; k < p.world; ++k) {
+                int g = p.rank_in_group + k;  // own copy first, the peers spread over time
+                if (g >= p.world) g -= p.world;
+                tma_store_2d(&out_maps->m[g], buf, p.bcast_col0 + col0, row_coord);
+              }
+            } else {
+              tma_store_2d(&out_maps->m[map_idx], buf, col0, row_coord);
+            }
             tma_store_commit();
           }
         }
@@ -364,7 +375,10 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
       }
     }
     if constexpr (TMA_STORE) {
-      if (lane == 0) tma_store_wait_all<0>();  // staging memory and stores are done before exit
+      if (lane == 0) {
+        tma_store_wait_all<0>();  // staging memory and stores are done before exit
+        if constexpr (BCAST) fence_proxy_async_all();  // ... and ordered before the barrier that publishes them
+      }
       __syncwarp();
     }
   }

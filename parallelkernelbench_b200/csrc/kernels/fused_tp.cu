@@ -17,11 +17,14 @@
 //                   rank order and stores the sum into the result buffer of EVERY rank: one `multimem.st` through
 //                   the switch when the group is the whole job and the heap has a multicast mapping, else one
 //                   16-byte P2P store per member. A closing barrier tells each rank that all rows have landed.
+//  tp_gemm_allgather  GEMM -> all-gather along N (column-parallel linear). The TMA-store epilogue stores every output
+//                   tile into the gathered result of every rank at this rank's column block; a closing barrier
+//                   tells each rank that all column blocks have landed.
 //
 // Reference behaviour being replaced: all_gather + matmul + silu, matmul + reduce_scatter,
 // reduce_scatter + RMSNorm and matmul + all_reduce as separate NCCL / cuBLAS / elementwise launches
 // (reference: reference/15_combined_sharded_gemms.py:17-31, reference/16_gemm_reducescatter.py:19-22,
-//  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20).
+//  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20, reference/14_gemm_allgather.py:17-22).
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
 #include "pkb/gemm_umma2.cuh"
@@ -260,6 +263,19 @@ tp_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+tp_gemm_allgather_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                         const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
+                         const __grid_constant__ SymmCtx c) {
+  // all ranks have entered this call => all ranks have consumed the previous call's gathered result
+  if (!symm_block_barrier(c, 303, 1)) return;
+  gemm_umma2_cta<EPI, false, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1, &out_maps);
+  // the same-index blocks of every rank have completed their stores once this barrier passes
+  symm_block_barrier(c, 303, 2);
+}
+
 }  // namespace pkb
 
 using namespace pkb;
@@ -479,6 +495,63 @@ int pkb_tp_gemm_allreduce(const pkb_symm_ctx* h, const void* a_mat, long long ld
   int grid = sm_count() & ~1;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
   k<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, om, p, a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// result[M, gsize * n_local] (bf16, at heap offset out_off on every rank) = all_gather along N of epi(a @ w^T + bias), with
+// a [M, K] (the same on every rank) and w [n_local, K] this rank's block of output features. n_local % 64 == 0.
+// epilogue: 0 none, 1 SiLU, 2 bias, 3 bias + SiLU. The result is valid on this rank when the kernel has finished.
+int pkb_tp_gemm_allgather(const pkb_symm_ctx* h, const void* a_mat, long long lda, const void* w, long long ldb, int M,
+                          int n_local, int K, const void* bias, int epilogue, unsigned long long out_off, void* stream) {
+  PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
+  PKB_CHECK_ARG(h->gsize >= 1 && h->gsize <= kGemmMaxWorld, "group size must be 1..8");
+  PKB_CHECK_ARG(M > 0 && n_local > 0 && n_local % 64 == 0, "n_local must be a positive multiple of 64");
+  PKB_CHECK_ARG(K % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0, "K, lda, ldb must be multiples of 8");
+  PKB_CHECK_ARG((out_off & 1023) == 0, "heap offset misaligned");
+  PKB_CHECK_ARG(epilogue >= kEpiNone && epilogue <= kEpiBiasSilu, "unknown epilogue");
+  PKB_CHECK_ARG((epilogue & 2) == 0 || bias != nullptr, "bias epilogue without bias");
+  const int W = h->gsize;
+  SymmCtx ctx = symm_ctx_from_api(h);
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a_mat, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, kGemmBlockK, kGemmBlockM,
+                          kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, w, (uint64_t)K, (uint64_t)n_local, (uint64_t)ldb * 2, kGemmBlockK, 128, kSwizzle128);
+  if (rc) return rc;
+  GemmOutMaps om;
+  const long long n_total = (long long)W * n_local;
+  for (int g = 0; g < W; ++g) {
+    void* dst = reinterpret_cast<void*>(h->base + (uint64_t)h->members[g] * h->stride + out_off);
+    rc = encode_tmap_2d(&om.m[g], kTmapBf16, dst, (uint64_t)n_total, (uint64_t)M, (uint64_t)n_total * 2, 64, 32, kSwizzle128);
+    if (rc) return rc;
+  }
+  GemmParams p = {};
+  p.M = M; p.N = n_local; p.K = K; p.C = nullptr; p.ldc = n_total; p.alpha = 1.0f;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.status = ctx.status; p.wait_budget_ns = ctx.budget_ns;
+  p.kernel_id = 303;
+  p.rank = h->rank; p.world = W;
+  p.rank_in_group = h->grank;
+  p.bcast_col0 = h->grank * n_local;
+  p.group_m = 8;
+  int grid = sm_count() & ~1;
+  if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
+  constexpr int smem = kGemm2SmemTotal;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PKB_GAG(EPI)                                                                             \
+  {                                                                                              \
+    auto k = tp_gemm_allgather_kernel<EPI>;                                                      \
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    k<<<grid, kGemmThreads, smem, s>>>(ta, tb, om, p, ctx);                                      \
+  }
+  switch (epilogue) {
+    case kEpiNone: PKB_GAG(kEpiNone) break;
+    case kEpiSilu: PKB_GAG(kEpiSilu) break;
+    case kEpiBias: PKB_GAG(kEpiBias) break;
+    default: PKB_GAG(kEpiBiasSilu) break;
+  }
+#undef PKB_GAG
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

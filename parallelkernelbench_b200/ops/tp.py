@@ -7,6 +7,8 @@
 ``GemmAllReduce``    (a @ w.T) summed over the ranks (row-parallel linear) in one launch: the same scatter epilogue,
                      then each rank adds the partial slots of its rows and stores the sums on every rank
                      (``multimem.st`` through the switch, or one P2P store per member), closed by a barrier.
+``GemmAllGather``    (a @ w.T) gathered along the output features (column-parallel linear) in one launch: the TMA-store
+                     epilogue writes every output tile into the gathered result of every rank.
 
 All keep their symmetric buffers between calls (steady-state calls allocate nothing), like the
 module-level buffer caches of the reference's example solutions
@@ -123,5 +125,32 @@ class GemmAllReduce:
             ctypes.c_ulonglong(self.recv.offset), ctypes.c_ulonglong(self.done.offset), ctypes.c_uint(self.calls),
             ctypes.c_ulonglong(self.out.offset), nv.c_float(scale), 1 if self.multicast else 0, nv.current_stream()),
             "pkb_tp_gemm_allreduce")
+        nv.count_launch()
+        return self.out.local
+
+
+class GemmAllGather:
+    """Column-parallel linear layer with its all-gather along N fused in (reference: reference/14_gemm_allgather.py:17-22).
+
+    The gathered result ``[M, W * n_local]`` lives in the symmetric heap and is returned as a view that stays valid until
+    the next call of this object."""
+
+    def __init__(self, group: SymmGroup, m: int, n_local: int):
+        if n_local % 64 != 0:
+            raise ValueError("n_local must be a multiple of 64 (one TMA-store box)")
+        self.group, self.m, self.n_local = group, m, n_local
+        self.out = group.heap.empty((m, group.size * n_local), torch.bfloat16)
+
+    def __call__(self, a: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, activation: str = "none") -> torch.Tensor:
+        if a.shape[0] != self.m or a.dtype != torch.bfloat16 or a.stride(1) != 1:
+            raise ValueError("a must be bf16 [M, K]")
+        if w.shape != (self.n_local, a.shape[1]) or w.stride(1) != 1 or w.dtype != torch.bfloat16:
+            raise ValueError("w must be bf16 [n_local, K]")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.n_local):
+            raise ValueError("bias must be bf16 [n_local]")
+        epi = {"none": 0, "silu": 1}[activation] | (2 if bias is not None else 0)
+        nv.check(nv.cuda_lib().pkb_tp_gemm_allgather(
+            self.group.ref, nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(w.stride(0)), self.m, self.n_local, a.shape[1],
+            nv.ptr(bias), epi, ctypes.c_ulonglong(self.out.offset), nv.current_stream()), "pkb_tp_gemm_allgather")
         nv.count_launch()
         return self.out.local

@@ -196,9 +196,25 @@ def _gag_ref(rc, a, b):
     return torch.cat(parts, dim=1)
 
 
-register(OpSpec(name="gemm_allgather", problem_ids=(14,), group="tp", configs=_GEMM_CFG, make_inputs=_gag_inputs,
-                reference=_gag_ref,
-                ours=lambda rc, a, b: rc.comm.all_gather_cat(_mm(rc, a, b), dim=1) if rc.world > 1 else _mm(rc, a, b),
+def _gag_ours(rc, a, b):
+    """Two launches (tcgen05 GEMM, symmetric-heap all-gather), or the single fused kernel when PKB_FUSED_GEMM_AG=1 and
+    the shapes fit it (local N a multiple of 64, K a multiple of 8)."""
+    import os
+
+    (M, K), nl = a.shape, b.shape[1]
+    if os.environ.get("PKB_FUSED_GEMM_AG") == "1" and rc.dist.is_cuda and a.dtype == torch.bfloat16 and nl % 64 == 0 and K % 8 == 0:
+        from ..ops.tp import GemmAllGather
+
+        key = ("gemm_ag", M, nl, b.data_ptr())
+        if key not in rc.cache:
+            rc.cache[key] = (GemmAllGather(rc.comm.group(), M, nl), b.t().contiguous())
+        op, w = rc.cache[key]
+        return op(a.contiguous(), w).clone()
+    return rc.comm.all_gather_cat(_mm(rc, a, b), dim=1) if rc.world > 1 else _mm(rc, a, b)
+
+
+register(OpSpec(name="gemm_allgather", problem_ids=(14,), group="tp", configs={**_GEMM_CFG, "large": {"m": 4096, "n": 8192, "k": 1024}},
+                make_inputs=_gag_inputs, reference=_gag_ref, ours=_gag_ours,
                 atol=0.5, rtol=2e-2,
                 cost=lambda cfg, W: Cost(flops=2.0 * cfg["m"] * cfg["n"] * cfg["k"] / W, nvlink_bytes=cfg["m"] * cfg["n"] * 2 * (W - 1) / max(W, 1))))
 

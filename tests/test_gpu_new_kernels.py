@@ -116,3 +116,11 @@ def test_fused_router_matches_softmax_topk_bincount(E, k):
 
 def test_moe_layer_with_fused_router():
     _all_ops(1, 29681, "--ops", "moe_layer", "--config", "default", env={"PKB_FUSED_ROUTER": "1"})
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_fused_gemm_allgather_matches_gemm_then_allgather(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _all_ops(nproc, 29684 + nproc, "--ops", "gemm_allgather", "--config", "default", env={"PKB_FUSED_GEMM_AG": "1"})
+    _all_ops(nproc, 29688 + nproc, "--ops", "gemm_allgather", "--config", "large", env={"PKB_FUSED_GEMM_AG": "1"})
