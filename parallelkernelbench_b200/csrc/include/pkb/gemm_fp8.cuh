@@ -37,6 +37,7 @@ enum GemmFp8Epilogue : int {
   kFp8EpiNone = 0,         // bf16 out [M, N]
   kFp8EpiSwiGLU = 1,       // bf16 out [M, N/2]
   kFp8EpiSwiGLUQuant = 2,  // e4m3 out [M, N/2] + fp32 scales [M, N/256]
+  kFp8EpiRowScatter = 3,   // bf16 row m -> row row_meta[m].y of the buffer scatter_out[row_meta[m].x] (maybe on a peer)
 };
 
 struct GemmFp8Params {
@@ -55,6 +56,8 @@ struct GemmFp8Params {
   int kernel_id;
   const int* grp_offsets;    // grouped form: [grp_count + 1] row offsets in device memory
   int grp_count;
+  const int2* row_meta;      // row-scatter epilogue: per row of A (index into scatter_out, destination row)
+  void* scatter_out[kGemmMaxWorld];
 };
 
 struct GemmFp8Smem {
@@ -289,10 +292,16 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
       if (!ok) break;
 
       // ---- epilogue from registers ----
-      if constexpr (EPI == kFp8EpiNone) {
+      if constexpr (EPI == kFp8EpiNone || EPI == kFp8EpiRowScatter) {
         if (row_ok && half_ok) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
-          if (col0 + 128 <= p.N && (p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(p.C) & 15) == 0) {
+          __nv_bfloat16* o;
+          if constexpr (EPI == kFp8EpiRowScatter) {
+            const int2 meta = p.row_meta[row];
+            o = static_cast<__nv_bfloat16*>(p.scatter_out[meta.x]) + (long long)meta.y * p.ldc + col0;
+          } else {
+            o = static_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col0;
+          }
+          if (col0 + 128 <= p.N && (p.ldc & 7) == 0 && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 128; j += 8) {
               U4 u{pack_bf16x2(acc[j] * p.alpha, acc[j + 1] * p.alpha), pack_bf16x2(acc[j + 2] * p.alpha, acc[j + 3] * p.alpha),

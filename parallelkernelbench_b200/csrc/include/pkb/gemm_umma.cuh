@@ -28,6 +28,7 @@ enum GemmEpilogue : int {
   kEpiBias = 2,
   kEpiBiasSilu = 3,
   kEpiSwiGLU = 4,  // columns come in (gate, up) pairs: out[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]
+  kEpiRowScatter = 5,  // row m goes to row row_meta[m].y of the buffer rs_out[row_meta[m].x] (possibly on another rank)
 };
 constexpr int kGemmMaxGroups = 256;
 
@@ -70,6 +71,8 @@ struct GemmParams {
   // multiplies them with its own weight block B[e*N .. e*N+N, :].
   const int* grp_offsets;
   int grp_count;
+  // ---- row-scatter epilogue (expert outputs pushed to the ranks their tokens came from) --------
+  const int2* row_meta;  // per row of A: (index into rs_out, destination row)
 };
 
 template <int BN>
@@ -315,6 +318,9 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
         const int r_in = row - owner * p.rs_rows_per_rank;
         out_row = static_cast<uint8_t*>(p.rs_out[owner < p.world ? owner : 0]) +
                   static_cast<long long>(r_in) * p.ldc * kOutBytes;
+      } else if constexpr (EPI == kEpiRowScatter) {
+        const int2 meta = row < row_end ? p.row_meta[row] : make_int2(0, 0);
+        out_row = static_cast<uint8_t*>(p.rs_out[meta.x]) + static_cast<long long>(meta.y) * p.ldc * kOutBytes;
       } else {
         out_row = static_cast<uint8_t*>(p.C) + static_cast<long long>(row) * p.ldc * kOutBytes;
       }

@@ -221,6 +221,56 @@ extern "C" int pkb_gemm_bf16_grouped(const void* a, long long lda, const void* b
   return kApiOk;
 }
 
+// Grouped GEMM whose output rows are scattered: row m of the product is stored as row row_meta[m].y (ldc elements per
+// row, bf16) of the buffer dest_ptrs[row_meta[m].x], which may live on another rank. row_meta is an int2 device array with
+// one entry per row of A; dest_ptrs is a HOST array of ndest <= 8 device addresses (16-byte aligned).
+extern "C" int pkb_gemm_bf16_grouped_scatter(const void* a, long long lda, const void* b, long long ldb, long long ldc,
+                                             const void* offsets, int groups, int max_rows, int N, int K, int block_n,
+                                             const void* row_meta, const unsigned long long* dest_ptrs, int ndest,
+                                             void* stream) {
+  PKB_CHECK_ARG(groups >= 1 && groups <= kGemmMaxGroups, "1..256 groups");
+  PKB_CHECK_ARG(max_rows > 0 && N > 0 && K > 0, "empty problem");
+  PKB_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && K % 8 == 0 && ldc % 8 == 0, "lda, ldb, ldc, K must be multiples of 8");
+  PKB_CHECK_ARG(row_meta != nullptr && dest_ptrs != nullptr && ndest >= 1 && ndest <= kGemmMaxWorld,
+                "row_meta and 1..8 destination buffers are required");
+  if (block_n == 0) block_n = N >= 256 ? 256 : 128;
+  PKB_CHECK_ARG(block_n == 128 || block_n == 256, "block_n must be 128 or 256");
+  CUtensorMap ta, tb;
+  int rc = encode_tmap_2d(&ta, kTmapBf16, a, (uint64_t)K, (uint64_t)max_rows, (uint64_t)lda * 2, kGemmBlockK, kGemmBlockM,
+                          kSwizzle128);
+  if (rc) return rc;
+  rc = encode_tmap_2d(&tb, kTmapBf16, b, (uint64_t)K, (uint64_t)groups * N, (uint64_t)ldb * 2, kGemmBlockK, (uint32_t)block_n,
+                      kSwizzle128);
+  if (rc) return rc;
+  GemmParams p = {};
+  p.M = max_rows; p.N = N; p.K = K;
+  p.C = nullptr; p.ldc = ldc; p.alpha = 1.0f;
+  p.status = status_block_device_ptr();
+  p.wait_budget_ns = kDefaultWaitBudgetNs;
+  p.kernel_id = 106;
+  p.world = 1;
+  p.grp_offsets = static_cast<const int*>(offsets);
+  p.grp_count = groups;
+  p.row_meta = static_cast<const int2*>(row_meta);
+  for (int g = 0; g < kGemmMaxWorld; ++g) {
+    PKB_CHECK_ARG((dest_ptrs[g < ndest ? g : 0] & 15) == 0, "destination buffers must be 16-byte aligned");
+    p.rs_out[g] = reinterpret_cast<void*>(static_cast<uintptr_t>(dest_ptrs[g < ndest ? g : 0]));
+  }
+  const int ctas = sm_count();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (block_n == 256) {
+    auto kern = gemm_umma_grouped_kernel<256, kEpiRowScatter>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<256>::kTotal));
+    kern<<<ctas, kGemmThreads, GemmSmem<256>::kTotal, s>>>(ta, tb, p);
+  } else {
+    auto kern = gemm_umma_grouped_kernel<128, kEpiRowScatter>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<128>::kTotal));
+    kern<<<ctas, kGemmThreads, GemmSmem<128>::kTotal, s>>>(ta, tb, p);
+  }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
 // C[M,N] = epi(A[M,K] @ B[K,N]) with B row-major [K, N] (ldb elements between K rows, N % 8 == 0).
 // epilogue: 0 none, 1 SiLU. out_f32 selects fp32 output.
 extern "C" int pkb_gemm_bf16_bkn(const void* a, long long lda, const void* b, long long ldb, void* c,

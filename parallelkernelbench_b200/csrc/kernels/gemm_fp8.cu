@@ -18,6 +18,9 @@ static int launch_fp8(const CUtensorMap& ta, const CUtensorMap& tb, const GemmFp
 //   b8 [N, K] (dense) or [groups * N, K] (grouped) e4m3; sb fp32, sb[(row of b8 / 128) * sb_stride + k / 128]
 //   epilogue 0: c bf16 [M, N];  1: SwiGLU over interleaved (gate, up) columns, c bf16 [M, N / 2];
 //            2: SwiGLU, then 1x128 re-quantisation: c e4m3 [M, N / 2], out_scales[row * os_stride + n / 256]
+//            3: row scatter: bf16 row m is stored as row row_meta[m].y (ldc elements per row) of the buffer
+//               dest_ptrs[row_meta[m].x], which may live on another rank (c is unused); row_meta is an int2 device array
+//               with one entry per row of A, dest_ptrs a HOST array of ndest <= 8 device addresses
 //   groups 0: dense. groups >= 1: rows [offsets[e], offsets[e + 1]) of A use weight block e; offsets is an
 //   int32 device array of groups + 1 entries that only the device reads, M bounds offsets[groups].
 // K % 128 == 0, N % 128 == 0 (N % 256 == 0 for epilogue 2), lda % 16 == 0, ldb % 16 == 0.
@@ -25,11 +28,13 @@ extern "C" int pkb_gemm_fp8_blockscaled(const void* a8, long long lda, const voi
                                         const void* b8, long long ldb, const void* sb, long long sb_stride, void* c,
                                         long long ldc, void* out_scales, long long os_stride, const void* offsets,
                                         int groups, int M, int N, int K, float alpha, int epilogue, int num_ctas,
-                                        void* stream) {
+                                        const void* row_meta, const unsigned long long* dest_ptrs, int ndest, void* stream) {
   PKB_CHECK_ARG(M > 0 && N > 0 && K > 0, "empty problem");
   PKB_CHECK_ARG(K % kFp8BlockK == 0 && N % 128 == 0, "K and N must be multiples of 128");
   PKB_CHECK_ARG(lda % 16 == 0 && ldb % 16 == 0, "lda and ldb must be multiples of 16");
-  PKB_CHECK_ARG(epilogue >= kFp8EpiNone && epilogue <= kFp8EpiSwiGLUQuant, "unknown epilogue");
+  PKB_CHECK_ARG(epilogue >= kFp8EpiNone && epilogue <= kFp8EpiRowScatter, "unknown epilogue");
+  PKB_CHECK_ARG(epilogue != kFp8EpiRowScatter || (row_meta != nullptr && dest_ptrs != nullptr && ndest >= 1 && ndest <= kGemmMaxWorld),
+                "the row-scatter epilogue needs row_meta and 1..8 destination buffers");
   PKB_CHECK_ARG(epilogue != kFp8EpiSwiGLUQuant || (out_scales != nullptr && N % 256 == 0),
                 "the re-quantising epilogue needs out_scales and N % 256 == 0");
   PKB_CHECK_ARG(groups >= 0 && groups <= kGemmMaxGroups, "0..256 groups");
@@ -54,6 +59,11 @@ extern "C" int pkb_gemm_fp8_blockscaled(const void* a8, long long lda, const voi
   p.kernel_id = 105;
   p.grp_offsets = static_cast<const int*>(offsets);
   p.grp_count = groups;
+  if (epilogue == kFp8EpiRowScatter) {
+    p.row_meta = static_cast<const int2*>(row_meta);
+    for (int g = 0; g < kGemmMaxWorld; ++g)
+      p.scatter_out[g] = reinterpret_cast<void*>(static_cast<uintptr_t>(dest_ptrs[g < ndest ? g : 0]));
+  }
   int ctas = num_ctas > 0 ? num_ctas : sm_count();
   if (groups == 0) {
     const int tiles = ((M + kFp8BlockM - 1) / kFp8BlockM) * ((N + kFp8BlockN - 1) / kFp8BlockN);
@@ -64,12 +74,14 @@ extern "C" int pkb_gemm_fp8_blockscaled(const void* a8, long long lda, const voi
     switch (epilogue) {
       case kFp8EpiNone: return launch_fp8<kFp8EpiNone, true>(ta, tb, p, ctas, s);
       case kFp8EpiSwiGLU: return launch_fp8<kFp8EpiSwiGLU, true>(ta, tb, p, ctas, s);
+      case kFp8EpiRowScatter: return launch_fp8<kFp8EpiRowScatter, true>(ta, tb, p, ctas, s);
       default: return launch_fp8<kFp8EpiSwiGLUQuant, true>(ta, tb, p, ctas, s);
     }
   }
   switch (epilogue) {
     case kFp8EpiNone: return launch_fp8<kFp8EpiNone, false>(ta, tb, p, ctas, s);
     case kFp8EpiSwiGLU: return launch_fp8<kFp8EpiSwiGLU, false>(ta, tb, p, ctas, s);
+    case kFp8EpiRowScatter: return launch_fp8<kFp8EpiRowScatter, false>(ta, tb, p, ctas, s);
     default: return launch_fp8<kFp8EpiSwiGLUQuant, false>(ta, tb, p, ctas, s);
   }
 }

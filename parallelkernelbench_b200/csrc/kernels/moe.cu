@@ -146,6 +146,7 @@ struct MoeDispatchArgs {
   uint64_t recv_payload_off, recv_scale_off;   // heap offsets of the receive buffers
   int capacity;             // rows of the receive buffers
   int* overflow;            // incremented when a row does not fit
+  uint64_t recv_meta_off;   // 0, or heap offset of int2 [capacity]: (sender's index in the group, assignment index) per row
 };
 
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const SymmCtx c, const MoeDispatchArgs a) {
@@ -174,7 +175,10 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const SymmCtx c, cons
       uint8_t* sd = symm_ptr<uint8_t>(c, dest, a.recv_scale_off) + (long long)slot * a.scale_bytes;
       for (int b = lane * 16; b < a.scale_bytes; b += 32 * 16) st_global_v4(sd + b, ld_global_v4(ss + b));
     }
-    if (lane == 0) a.slots[i] = slot;
+    if (lane == 0) {
+      a.slots[i] = slot;
+      if (a.recv_meta_off != 0) symm_ptr<int2>(c, dest, a.recv_meta_off)[slot] = make_int2(c.grank, (int)i);
+    }
   }
   // when this barrier has been crossed by every block of every rank, all rows have landed everywhere
   symm_block_barrier(c, 500, 1);
@@ -188,6 +192,7 @@ struct MoeCombineArgs {
   __nv_bfloat16* out;        // [T, hidden]
   long long num_tokens;
   int top_k, hidden, experts_per_rank;
+  int local_rows;            // 1: row (t, j) sits at row t * k + j of THIS rank's buffer (the experts pushed it there)
 };
 
 template <int MAXK>
@@ -208,7 +213,9 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const SymmCtx c, const
         const int e = a.expert_idx[t * a.top_k + j];
         const int slot = a.slots[t * a.top_k + j];
         if (slot >= 0) {
-          rows[j] = symm_ptr<__nv_bfloat16>(c, c.members[e / a.experts_per_rank], a.y_off) + (long long)slot * a.hidden;
+          rows[j] = a.local_rows
+                        ? symm_local<__nv_bfloat16>(c, a.y_off) + (t * a.top_k + j) * a.hidden
+                        : symm_ptr<__nv_bfloat16>(c, c.members[e / a.experts_per_rank], a.y_off) + (long long)slot * a.hidden;
           w[j] = a.gates[t * a.top_k + j];
         }
       }
@@ -281,17 +288,21 @@ int pkb_moe_plan(const void* all_counts, int world, int num_experts, int experts
   return kApiOk;
 }
 
-int pkb_moe_dispatch(const pkb_symm_ctx* h, const void* payload, const void* scales, int payload_bytes,
-                     int scale_bytes, const void* expert_idx, long long num_assign, int top_k, int experts_per_rank,
-                     const void* seg_base, void* cursor, void* slots, unsigned long long recv_payload_off,
-                     unsigned long long recv_scale_off, int capacity, void* overflow, void* stream) {
+// recv_meta_off: 0, or the heap offset of an int2 [capacity] array that receives, for every row written, the sender's
+// index in the group and the assignment index (token * k + j) - what an expert needs to send the row's result home.
+int pkb_moe_dispatch_meta(const pkb_symm_ctx* h, const void* payload, const void* scales, int payload_bytes,
+                          int scale_bytes, const void* expert_idx, long long num_assign, int top_k, int experts_per_rank,
+                          const void* seg_base, void* cursor, void* slots, unsigned long long recv_payload_off,
+                          unsigned long long recv_scale_off, int capacity, void* overflow,
+                          unsigned long long recv_meta_off, void* stream) {
   PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
   PKB_CHECK_ARG(payload_bytes % 16 == 0 && scale_bytes % 16 == 0, "row sizes must be multiples of 16 bytes");
   PKB_CHECK_ARG((recv_payload_off & 15) == 0 && (recv_scale_off & 15) == 0, "heap offsets misaligned");
   MoeDispatchArgs a{static_cast<const uint8_t*>(payload), static_cast<const uint8_t*>(scales), payload_bytes, scale_bytes,
                     static_cast<const int*>(expert_idx), num_assign, top_k, experts_per_rank,
                     static_cast<const int*>(seg_base), static_cast<int*>(cursor), static_cast<int*>(slots),
-                    recv_payload_off, recv_scale_off, capacity, static_cast<int*>(overflow)};
+                    recv_payload_off, recv_scale_off, capacity, static_cast<int*>(overflow), recv_meta_off};
+  PKB_CHECK_ARG((recv_meta_off & 7) == 0, "heap offsets misaligned");
   int grid = sm_count() * 2;   // fixed: the same on every rank, the barrier pairs blocks by index
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
   moe_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
@@ -299,14 +310,24 @@ int pkb_moe_dispatch(const pkb_symm_ctx* h, const void* payload, const void* sca
   return kApiOk;
 }
 
-int pkb_moe_combine(const pkb_symm_ctx* h, unsigned long long y_off, const void* expert_idx, const void* slots,
-                    const void* gates, void* out, long long num_tokens, int top_k, int hidden, int experts_per_rank,
-                    void* stream) {
+int pkb_moe_dispatch(const pkb_symm_ctx* h, const void* payload, const void* scales, int payload_bytes,
+                     int scale_bytes, const void* expert_idx, long long num_assign, int top_k, int experts_per_rank,
+                     const void* seg_base, void* cursor, void* slots, unsigned long long recv_payload_off,
+                     unsigned long long recv_scale_off, int capacity, void* overflow, void* stream) {
+  return pkb_moe_dispatch_meta(h, payload, scales, payload_bytes, scale_bytes, expert_idx, num_assign, top_k, experts_per_rank,
+                               seg_base, cursor, slots, recv_payload_off, recv_scale_off, capacity, overflow, 0ull, stream);
+}
+
+// local_rows = 0: pull row `slots[t, j]` of the expert outputs at y_off from the rank that owns expert idx[t, j].
+// local_rows = 1: the experts already pushed the result of assignment (t, j) to row t * k + j of THIS rank's buffer at y_off.
+int pkb_moe_combine_from(const pkb_symm_ctx* h, unsigned long long y_off, const void* expert_idx, const void* slots,
+                         const void* gates, void* out, long long num_tokens, int top_k, int hidden, int experts_per_rank,
+                         int local_rows, void* stream) {
   PKB_CHECK_ARG(h && h->base, "symmetric heap not initialised");
   PKB_CHECK_ARG(hidden % 8 == 0 && top_k >= 1 && top_k <= 8, "hidden % 8 == 0 and top_k <= 8");
   MoeCombineArgs a{y_off, static_cast<const int*>(expert_idx), static_cast<const int*>(slots),
                    static_cast<const float*>(gates), static_cast<__nv_bfloat16*>(out), num_tokens, top_k, hidden,
-                   experts_per_rank};
+                   experts_per_rank, local_rows};
   int grid = sm_count() * 2;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -315,6 +336,12 @@ int pkb_moe_combine(const pkb_symm_ctx* h, unsigned long long y_off, const void*
   else moe_combine_kernel<8><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
+}
+
+int pkb_moe_combine(const pkb_symm_ctx* h, unsigned long long y_off, const void* expert_idx, const void* slots,
+                    const void* gates, void* out, long long num_tokens, int top_k, int hidden, int experts_per_rank,
+                    void* stream) {
+  return pkb_moe_combine_from(h, y_off, expert_idx, slots, gates, out, num_tokens, top_k, hidden, experts_per_rank, 0, stream);
 }
 
 }  // extern "C"

@@ -4,7 +4,10 @@ Five of our kernels per forward besides the router: histogram, plan, dispatch (P
 with 1x128 scales), two grouped tcgen05 GEMMs (gate/up with the SwiGLU epilogue, then down, writing
 into the symmetric buffer the combine reads), combine (P2P pull, gate-weighted, deterministic order).
 The router GEMM runs on the dense tcgen05 kernel; softmax and top-k over a few hundred experts are
-PyTorch ops. Reference behaviour: reference/31_fused_moe_fwd.py:254-315 (with shared expert weights;
+PyTorch ops. ``push_combine`` moves the way home into the down GEMM: the dispatch delivers (sender, assignment index) with every row, the
+GEMM's epilogue stores each output row straight into the sender's buffer over NVLink, and the combine kernel only reads local
+memory after its barrier.
+Reference behaviour: reference/31_fused_moe_fwd.py:254-315 (with shared expert weights;
 here every expert has its own).
 
 ``fp8_experts`` keeps the received tokens in e4m3: the expert weights are quantised once to e4m3 with
@@ -20,7 +23,7 @@ import torch
 
 from ..ops.gemm import gemm_bf16
 from ..ops.gemm_fp8 import gemm_fp8_blockscaled
-from ..ops.moe import MoEExchange, grouped_gemm, interleave_gate_up, route_topk
+from ..ops.moe import MoEExchange, grouped_gemm, grouped_gemm_scatter, interleave_gate_up, route_topk
 
 
 @dataclass
@@ -33,6 +36,7 @@ class MoEConfig:
     capacity_factor: float = 2.0
     fp8_dispatch: bool = True
     fp8_experts: bool = False
+    push_combine: bool = False      # the down GEMM's epilogue stores each output row in its token owner's memory
     fused_router: bool = False      # softmax + top-k + histogram in one kernel instead of PyTorch ops + histogram kernel
     weight_std: float = 0.02
 
@@ -49,7 +53,7 @@ class EPMoELayer:
         self.w_gate_up = interleave_gate_up(w_gate, w_up)
         self.w_down = w_down.contiguous()
         self.ex = MoEExchange(group, cfg.num_experts, cfg.hidden, cfg.tokens_per_rank, cfg.top_k, cfg.capacity_factor,
-                              cfg.fp8_dispatch)
+                              cfg.fp8_dispatch, push_combine=cfg.push_combine)
         dev = w_router.device
         if cfg.fp8_experts:
             from ..refs.gemm_fp8 import quantize_weight_128x128
@@ -83,12 +87,21 @@ class EPMoELayer:
             x8, xs = self.ex.dispatch(x, flat_idx, dequantize=False)
             gemm_fp8_blockscaled(x8, xs, self.w8_gate_up, self.s_gate_up, offsets=self.ex.offsets, epilogue="swiglu_quant",
                                  out=self.h8, out_scales=self.h_scales)
-            gemm_fp8_blockscaled(self.h8, self.h_scales, self.w8_down, self.s_down, offsets=self.ex.offsets,
-                                 out=self.ex.y.local)
+            if self.cfg.push_combine:
+                gemm_fp8_blockscaled(self.h8, self.h_scales, self.w8_down, self.s_down, offsets=self.ex.offsets,
+                                     epilogue="row_scatter", row_meta=self.ex.recv_meta.local, dest_ptrs=self.ex.home_ptrs(),
+                                     dest_pitch=self.cfg.hidden)
+            else:
+                gemm_fp8_blockscaled(self.h8, self.h_scales, self.w8_down, self.s_down, offsets=self.ex.offsets,
+                                     out=self.ex.y.local)
         else:
             xin = self.ex.dispatch(x, flat_idx)
             grouped_gemm(xin, self.w_gate_up, self.ex.offsets, epilogue="swiglu", out=self.h)
-            grouped_gemm(self.h, self.w_down, self.ex.offsets, out=self.ex.y.local)
+            if self.cfg.push_combine:
+                grouped_gemm_scatter(self.h, self.w_down, self.ex.offsets, self.ex.recv_meta.local, self.ex.home_ptrs(),
+                                     self.cfg.hidden)
+            else:
+                grouped_gemm(self.h, self.w_down, self.ex.offsets, out=self.ex.y.local)
         return self.ex.combine(flat_idx, gates.view(-1), T)
 
     __call__ = forward

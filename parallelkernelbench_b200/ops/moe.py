@@ -39,6 +39,29 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, *, epi
     return out
 
 
+def grouped_gemm_scatter(a: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor, row_meta: torch.Tensor,
+                         dest_ptrs: list[int], dest_pitch: int, block_n: int = 0) -> None:
+    """Ragged GEMM like :func:`grouped_gemm` whose output row ``m`` is stored as row ``row_meta[m, 1]`` of the bf16 buffer at
+    address ``dest_ptrs[row_meta[m, 0]]`` (``dest_pitch`` elements per row) - the buffers may be peers' symmetric memory, so
+    the expert outputs travel home from the GEMM's epilogue."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 3:
+        raise TypeError("grouped_gemm_scatter expects bf16 a[rows, K] and w[G, N, K]")
+    G, N, K = w.shape
+    if a.shape[1] != K or a.stride(1) != 1 or not w.is_contiguous():
+        raise ValueError("shape mismatch or non-contiguous operand")
+    if offsets.dtype != torch.int32 or offsets.numel() != G + 1:
+        raise ValueError("offsets must be int32 [G + 1]")
+    if row_meta.dtype != torch.int32 or row_meta.shape[-1] != 2 or row_meta.shape[0] < a.shape[0] or not row_meta.is_contiguous():
+        raise ValueError("row_meta must be a contiguous int32 [>= rows, 2] device tensor")
+    if not dest_ptrs or len(dest_ptrs) > 8 or dest_pitch < N or dest_pitch % 8:
+        raise ValueError("1..8 destination addresses and a row pitch >= N that is a multiple of 8")
+    ptrs = (ctypes.c_ulonglong * len(dest_ptrs))(*dest_ptrs)
+    nv.check(nv.cuda_lib().pkb_gemm_bf16_grouped_scatter(nv.ptr(a), nv.c_ll(a.stride(0)), nv.ptr(w), nv.c_ll(K), nv.c_ll(dest_pitch),
+                                                         nv.ptr(offsets), G, a.shape[0], N, K, block_n, nv.ptr(row_meta), ptrs,
+                                                         len(dest_ptrs), nv.current_stream()), "pkb_gemm_bf16_grouped_scatter")
+    nv.count_launch()
+
+
 def route_topk(logits: torch.Tensor, bias: torch.Tensor | None, top_k: int, counts: torch.Tensor | None = None):
     """Softmax over the experts, top-k and the per-expert histogram in one kernel (one warp per token).
 
@@ -71,7 +94,7 @@ class MoEExchange:
     """Dispatch / combine state of one expert-parallel group (buffers live in the symmetric heap)."""
 
     def __init__(self, group: SymmGroup, num_experts: int, hidden: int, max_tokens: int, top_k: int,
-                 capacity_factor: float = 2.0, fp8: bool = True):
+                 capacity_factor: float = 2.0, fp8: bool = True, push_combine: bool = False):
         W = group.size
         if num_experts % W != 0:
             raise ValueError("experts must divide evenly over the expert-parallel group")
@@ -84,7 +107,16 @@ class MoEExchange:
         self.scale_bytes = ((hidden // 128) * 4 + 15) // 16 * 16 if fp8 else 0
         self.recv_payload = heap.empty((self.capacity, self.payload_bytes), torch.uint8)
         self.recv_scales = heap.empty((self.capacity, max(self.scale_bytes, 16)), torch.uint8)
-        self.y = heap.empty((self.capacity, hidden), torch.bfloat16)
+        # pull combine: the experts write their outputs to `y` (one row per received row) and the token owners pull them.
+        # push combine: the dispatch also delivers (sender, assignment index) per row, the down GEMM's epilogue stores each
+        # output row into row `assignment index` of the SENDER's `home` buffer, and the combine reads only local memory.
+        self.push_combine = push_combine
+        if push_combine:
+            self.home = heap.empty((max_tokens * top_k, hidden), torch.bfloat16)
+            self.recv_meta = heap.empty((self.capacity, 2), torch.int32)
+            self.y = self.home
+        else:
+            self.y = heap.empty((self.capacity, hidden), torch.bfloat16)
         dev = self.y.local.device
         self.counts = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self.seg_base = torch.zeros(num_experts, dtype=torch.int32, device=dev)
@@ -127,11 +159,12 @@ class MoEExchange:
                 scales = pad
         else:
             payload, scales = x.contiguous(), None
-        nv.check(nv.cuda_lib().pkb_moe_dispatch(
+        nv.check(nv.cuda_lib().pkb_moe_dispatch_meta(
             self.group.ref, nv.ptr(payload), nv.ptr(scales), self.payload_bytes, self.scale_bytes, nv.ptr(expert_idx),
             nv.c_ll(T * self.top_k), self.top_k, self.El, nv.ptr(self.seg_base), nv.ptr(self.cursor), nv.ptr(self.slots),
             ctypes.c_ulonglong(self.recv_payload.offset), ctypes.c_ulonglong(self.recv_scales.offset), self.capacity,
-            nv.ptr(self.overflow), nv.current_stream()), "pkb_moe_dispatch")
+            nv.ptr(self.overflow), ctypes.c_ulonglong(self.recv_meta.offset if self.push_combine else 0),
+            nv.current_stream()), "pkb_moe_dispatch_meta")
         nv.count_launch()
         if self.fp8 and not dequantize:
             return self.recv_payload.local, self.recv_scales.local.view(torch.float32)
@@ -145,14 +178,21 @@ class MoEExchange:
             return fp8_dequantize_1x128(self.recv_payload.local, s, torch.bfloat16)
         return self.recv_payload.local.view(torch.bfloat16)
 
+    def home_ptrs(self) -> list[int]:
+        """Addresses of every member's ``home`` buffer, in group order (what ``recv_meta[:, 0]`` indexes)."""
+        return [self.home.peer_ptr(r) for r in self.group.members]
+
     # -- combine -------------------------------------------------------------------------------
     def combine(self, expert_idx: torch.Tensor, gates: torch.Tensor, num_tokens: int) -> torch.Tensor:
         """``out[t] = sum_j gates[t, j] * y_owner[slot[t, j]]`` pulled over NVLink; ``self.y`` holds
         this rank's expert outputs."""
         out = torch.empty((num_tokens, self.hidden), dtype=torch.bfloat16, device=gates.device)
-        nv.check(nv.cuda_lib().pkb_moe_combine(self.group.ref, ctypes.c_ulonglong(self.y.offset), nv.ptr(expert_idx),
-                                               nv.ptr(self.slots), nv.ptr(gates.contiguous().float()), nv.ptr(out),
-                                               nv.c_ll(num_tokens), self.top_k, self.hidden, self.El, nv.current_stream()),
-                 "pkb_moe_combine")
+        if self.push_combine and num_tokens * self.top_k > self.home.local.shape[0]:
+            raise ValueError("more tokens than the home buffer was sized for")
+        nv.check(nv.cuda_lib().pkb_moe_combine_from(self.group.ref, ctypes.c_ulonglong(self.y.offset), nv.ptr(expert_idx),
+                                                    nv.ptr(self.slots), nv.ptr(gates.contiguous().float()), nv.ptr(out),
+                                                    nv.c_ll(num_tokens), self.top_k, self.hidden, self.El,
+                                                    1 if self.push_combine else 0, nv.current_stream()),
+                 "pkb_moe_combine_from")
         nv.count_launch()
         return out

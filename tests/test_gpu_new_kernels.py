@@ -124,3 +124,11 @@ def test_fused_gemm_allgather_matches_gemm_then_allgather(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     _all_ops(nproc, 29684 + nproc, "--ops", "gemm_allgather", "--config", "default", env={"PKB_FUSED_GEMM_AG": "1"})
     _all_ops(nproc, 29688 + nproc, "--ops", "gemm_allgather", "--config", "large", env={"PKB_FUSED_GEMM_AG": "1"})
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_moe_layer_with_expert_outputs_pushed_home_by_the_down_gemm(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _all_ops(nproc, 29692 + nproc, "--ops", "moe_layer", "--config", "default", env={"PKB_PUSH_COMBINE": "1"})
+    _all_ops(nproc, 29696 + nproc, "--ops", "moe_layer", "--config", "fp8_experts", env={"PKB_PUSH_COMBINE": "1"})
