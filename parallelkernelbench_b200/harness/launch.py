@@ -6,6 +6,7 @@ sizes, list the registry, and inspect stored results.
     python -m parallelkernelbench_b200.harness.launch eval  --op tp_mlp --nproc 8 --measure-perf
     python -m parallelkernelbench_b200.harness.launch eval  --op plumbing --nproc 2 --backend gloo --atol 1e-5 --rtol 1e-5
     python -m parallelkernelbench_b200.harness.launch sweep --ops allreduce,allgather --worlds 1,2,4,8 --resume
+    python -m parallelkernelbench_b200.harness.launch report --format markdown      # the sweep ledger as a table
     python -m parallelkernelbench_b200.harness.launch inspect --op allreduce
     python -m parallelkernelbench_b200.harness.launch perf-diff --op allreduce
 
@@ -283,6 +284,21 @@ def cmd_sweep(a) -> int:
     return rc
 
 
+def cmd_report(a) -> int:
+    """Print the sweep ledger as a markdown table or CSV."""
+    ledger = a.ledger or os.path.join(LOGS_ROOT, "results.jsonl")
+    if not os.path.exists(ledger):
+        print(f"no ledger at {ledger}", file=sys.stderr)
+        return 2
+    text = report.ledger_table(report.ledger_rows(ledger, latest_only=not a.all_lines), a.format)
+    if a.out:
+        with open(a.out, "w") as fh:
+            fh.write(text)
+    else:
+        sys.stdout.write(text)
+    return 0
+
+
 def cmd_inspect(a) -> int:
     from . import inspect_outputs
 
@@ -340,6 +356,12 @@ def main(argv=None) -> int:
     sp.add_argument("--resume", action="store_true")
     sp.add_argument("--any-sha", action="store_true", help="with --resume: accept cells recorded at another commit")
     sp.set_defaults(fn=cmd_sweep)
+    sp = sub.add_parser("report")
+    sp.add_argument("--ledger", default=None)
+    sp.add_argument("--format", default="markdown", choices=["markdown", "csv"])
+    sp.add_argument("--all-lines", action="store_true", help="every ledger line instead of the latest per (op, world, config)")
+    sp.add_argument("--out", default=None)
+    sp.set_defaults(fn=cmd_report)
     for name, fn in (("inspect", cmd_inspect), ("perf-diff", cmd_perf_diff)):
         sp = sub.add_parser(name)
         sp.add_argument("--op", required=True)

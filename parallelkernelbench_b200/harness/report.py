@@ -97,3 +97,69 @@ def trial_line(trial: int, verdict: dict, ref_perf: dict | None, cand_perf: dict
     if verdict.get("harness_hint"):
         s += f" | environment: {verdict['harness_hint']}"
     return s
+
+
+def ledger_rows(path: str, latest_only: bool = True) -> list[dict]:
+    """Cells of a sweep ledger (one JSON object per line). With ``latest_only`` a later line for the same
+    (op, world, config) replaces an earlier one, so a re-run after a fix supersedes the failed cell."""
+    import json
+
+    rows: dict[tuple, dict] | list = {} if latest_only else []
+    with open(path) as fh:
+        for line in fh:
+            line = line.strip()
+            if not line:
+                continue
+            try:
+                d = json.loads(line)
+            except ValueError:
+                continue
+            if "op" not in d or "world" not in d:
+                continue
+            if latest_only:
+                rows[(d["op"], d["world"], d.get("config", "default"))] = d
+            else:
+                rows.append(d)
+    out = list(rows.values()) if latest_only else rows
+    return sorted(out, key=lambda d: (d["op"], d.get("config", "default"), d["world"]))
+
+
+_COLUMNS = (("op", "op"), ("config", "config"), ("world", "GPUs"), ("result", "result"), ("ref_ms", "reference ms"),
+            ("ours_ms", "ours ms"), ("speedup", "speed-up"), ("pct_of_roofline", "% of roofline"), ("limiter", "limiter"),
+            ("git_sha", "commit"))
+
+
+def _cell(v) -> str:
+    if v is None:
+        return "-"
+    if isinstance(v, float):
+        return f"{v:.4g}"
+    return str(v)
+
+
+def ledger_table(rows: list[dict], fmt: str = "markdown") -> str:
+    """The sweep ledger as a markdown table or CSV (the reference only writes a per-problem JSON:
+    utils/compare_performance.py:151-163; a table over all problems and world sizes is what a results page needs)."""
+    if fmt == "csv":
+        import csv
+        import io
+
+        buf = io.StringIO()
+        w = csv.writer(buf)
+        w.writerow([k for k, _ in _COLUMNS])
+        for d in rows:
+            w.writerow(["" if d.get(k) is None else d.get(k) for k, _ in _COLUMNS])
+        return buf.getvalue()
+    if fmt != "markdown":
+        raise ValueError("fmt must be 'markdown' or 'csv'")
+    lines = ["| " + " | ".join(h for _, h in _COLUMNS) + " |", "|" + "---|" * len(_COLUMNS)]
+    for d in rows:
+        lines.append("| " + " | ".join(_cell(d.get(k, "default" if k == "config" else None)) for k, _ in _COLUMNS) + " |")
+    ok = sum(1 for d in rows if d.get("all_ok"))
+    sp = [d["speedup"] for d in rows if d.get("speedup")]
+    tail = f"\n{ok} of {len(rows)} cells match"
+    if sp:
+        import math
+
+        tail += f"; geometric-mean speed-up over {len(sp)} timed cells: {math.exp(sum(math.log(x) for x in sp) / len(sp)):.3g}x"
+    return "\n".join(lines) + tail + "\n"

@@ -15,11 +15,13 @@ import ctypes
 import torch
 
 from .. import _native as nv
+from .. import tuning
 from ..parallel.symm_heap import SymmGroup, SymmTensor
 
 ONE_SHOT_MAX_BYTES = 512 * 1024
 LL_MAX_BYTES = 1024 * 1024        # data + epoch in one 8-byte store, no barrier (twice the bytes on the wire)
-LL_AUTO_BYTES = 256 * 1024        # chosen automatically up to here (measured: 6.8 us vs NCCL 14.2 at 4 KiB, 9.4 vs 17.9 at 64 KiB, 23.6 vs 20.5 at 1 MiB)
+# the automatic choice stops earlier, at the table's ll_max_bytes (measured: 6.8 us vs NCCL 14.2 at 4 KiB, 9.4 vs 17.9 at 64 KiB,
+# 23.6 vs 20.5 at 1 MiB)
 _DT = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2, torch.float16: 3, torch.int32: 4, torch.int64: 5}
 _OP = {"sum": 0, "max": 1, "min": 2}
 
@@ -76,17 +78,11 @@ def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Te
                and x.dtype in (torch.bfloat16, torch.float32))
     ll_ok = nbytes <= LL_MAX_BYTES and x.dtype in (torch.bfloat16, torch.float32) and group.size > 1
     if algo == "auto":
-        # measured on B200 (device time under CUDA-graph replay, 2 ranks, NCCL in brackets): the no-barrier exchange 6.7 us
-        # at 4 KiB (13.8), 9.0 us at 64 KiB (17.2); one-shot 52.6 us at 16 MiB (59.0); two-shot 261 us at 128 MiB (285), the
-        # in-switch form 429 us there - with two ranks a peer read costs the same as the switch reduction, so NVLS is
-        # used from four ranks on, where one-shot would read (W-1) copies
-        one_shot_max = (32 << 20) if group.size == 2 else ONE_SHOT_MAX_BYTES
-        if ll_ok and nbytes <= LL_AUTO_BYTES:
-            algo = "ll"
-        elif nbytes <= one_shot_max or group.size == 1:
-            algo = "oneshot"
-        else:
-            algo = "nvls" if (nvls_ok and group.size >= 4) else "twoshot"
+        # thresholds come from the tuning table (tuning/collectives_b200.json). Measured on B200 (device time under CUDA-graph
+        # replay, 2 ranks, NCCL in brackets): the no-barrier exchange 6.7 us at 4 KiB (13.8), 9.0 us at 64 KiB (17.2); one-shot
+        # 52.6 us at 16 MiB (59.0); two-shot 261 us at 128 MiB (285), the in-switch form 429 us there - with two ranks a peer
+        # read costs the same as the switch reduction, so NVLS is used from four ranks on, where one-shot would read (W-1) copies
+        algo = tuning.all_reduce_algo(nbytes, group.size, ll_ok=ll_ok, nvls_ok=nvls_ok)
     lib = _lib()
     if algo == "ll":
         if not ll_ok:
@@ -172,7 +168,7 @@ def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = Non
     if out is None:
         out = torch.empty((W, *x.shape), dtype=x.dtype, device=x.device)
     nb = x.numel() * x.element_size()
-    if W > 1 and 0 < nb <= LL_MAX_BYTES // 4 and nb % 4 == 0 and x.data_ptr() % 4 == 0 and out.is_contiguous():
+    if W > 1 and 0 < nb <= tuning.all_gather_ll_max(W) and nb % 4 == 0 and x.data_ptr() % 4 == 0 and out.is_contiguous():
         buf, cap_units = _ll_slots(group, nb)
         nv.check(_lib().pkb_coll_allgather_ll(group.ref, nv.ptr(x), nv.c_ll(nb // 4), ctypes.c_ulonglong(buf.offset), nv.c_ll(cap_units),
                                               nv.ptr(out), nv.current_stream()), "pkb_coll_allgather_ll")

@@ -110,6 +110,10 @@ def test_list_sweep_resume_inspect_and_perf_diff(tmp_path):
     assert len(cells) == 1 and cells[0]["op"] == "allreduce" and cells[0]["world"] == 2 and cells[0]["all_ok"] and cells[0]["speedup"] > 0
     r, _ = _launch(*args, "--resume")
     assert r.returncode == 0 and "skip allreduce w=2" in r.stdout and len(open(ledger).readlines()) == 1
+    r, _ = _launch("report", "--ledger", ledger)
+    assert r.returncode == 0 and "| allreduce | small | 2 | match |" in r.stdout and "1 of 1 cells match" in r.stdout
+    r, _ = _launch("report", "--ledger", ledger, "--format", "csv")
+    assert r.returncode == 0 and r.stdout.splitlines()[0].startswith("op,config,world,result") and "allreduce,small,2,match" in r.stdout
     r, _ = _launch("inspect", "--op", "allreduce")
     assert r.returncode == 0 and "verdict: match" in r.stdout
     r, _ = _launch("perf-diff", "--op", "allreduce")
