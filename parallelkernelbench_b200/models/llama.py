@@ -313,6 +313,18 @@ class _Unit:
         else:
             self.bf16 = self.master.to(torch.bfloat16)
 
+    def state(self) -> dict:
+        """This rank's shard: fp32 master and Adam moments plus the wire-format copy (e4m3 bytes and 1x128 scales, or bf16)."""
+        d = {"master": self.master, "m": self.m, "v": self.v}
+        d.update({"q8": self.q8, "s8": self.s8} if self.eng.impl == "ours" else {"bf16": self.bf16})
+        return d
+
+    def load_state(self, d: dict) -> None:
+        for k, t in self.state().items():
+            if k not in d or d[k].shape != t.shape or d[k].dtype != t.dtype:
+                raise ValueError(f"checkpoint shard lacks {k!r} or has another shape / dtype (other world size or config?)")
+            t.copy_(d[k])
+
     def gather(self) -> torch.Tensor:
         eng = self.eng
         if eng.impl == "ours":
@@ -380,6 +392,52 @@ class FSDPLlama:
         self.final_gain = torch.ones(1, cfg.hidden, device=self.device, dtype=torch.bfloat16)
         self.cos, self.sin = rope_tables(cfg, self.device)
         self.steps = 0
+
+    # -- sharded checkpoint --------------------------------------------------------------------------
+    def save_sharded(self, directory: str) -> str:
+        """Write this rank's shard of the whole training state (every unit's fp32 master, Adam moments and wire-format
+        copy, the vocabulary-parallel head with its moments, the step count) to ``directory/rank_<r>_of_<W>.pt``.
+        Every rank calls it; nothing is gathered. Returns the file written."""
+        import os
+
+        os.makedirs(directory, exist_ok=True)
+        cpu = lambda d: {k: v.detach().cpu() for k, v in d.items()}  # noqa: E731
+        blob = {"format": 1, "world": self.W, "rank": self.rank, "impl": self.impl, "steps": self.steps,
+                "config": {k: getattr(self.cfg, k) for k in ("vocab", "hidden", "layers", "heads", "kv_heads", "ffn")
+                           if hasattr(self.cfg, k)},
+                "embed": cpu(self.embed.state()), "units": [cpu(u.state()) for u in self.units],
+                "head": cpu({"master": self.head_master, "m": self.head_m, "v": self.head_v, "bf16": self.head.data})}
+        path = os.path.join(directory, f"rank_{self.rank}_of_{self.W}.pt")
+        tmp = path + ".tmp"
+        torch.save(blob, tmp)
+        os.replace(tmp, path)          # a reader never sees a half-written file
+        return path
+
+    def load_sharded(self, directory: str) -> int:
+        """Restore what :meth:`save_sharded` wrote (same world size, implementation and config). Returns the step count."""
+        import os
+
+        path = os.path.join(directory, f"rank_{self.rank}_of_{self.W}.pt")
+        blob = torch.load(path, map_location=self.device)
+        if blob.get("format") != 1 or blob["world"] != self.W or blob["rank"] != self.rank or blob["impl"] != self.impl:
+            raise ValueError(f"{path}: written by rank {blob.get('rank')} of {blob.get('world')} with implementation "
+                             f"{blob.get('impl')!r}; this is rank {self.rank} of {self.W} with {self.impl!r}")
+        for k, v in blob["config"].items():
+            if getattr(self.cfg, k) != v:
+                raise ValueError(f"{path}: config mismatch on {k}: checkpoint {v}, model {getattr(self.cfg, k)}")
+        if len(blob["units"]) != len(self.units):
+            raise ValueError(f"{path}: {len(blob['units'])} layers in the checkpoint, {len(self.units)} in the model")
+        with torch.no_grad():
+            self.embed.load_state(blob["embed"])
+            for u, d in zip(self.units, blob["units"]):
+                u.load_state(d)
+            h = blob["head"]
+            self.head_master.copy_(h["master"])
+            self.head_m.copy_(h["m"])
+            self.head_v.copy_(h["v"])
+            self.head.data.copy_(h["bf16"])
+        self.steps = int(blob["steps"])
+        return self.steps
 
     # -- collectives over rows ---------------------------------------------------------------------
     def all_gather_rows(self, x):

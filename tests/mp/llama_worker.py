@@ -52,6 +52,31 @@ def main() -> int:
         torch.cuda.empty_cache()
         torch.cuda.reset_peak_memory_stats()
     fails = 0
+    if "--resume-check" in sys.argv and not full:
+        # train 2 steps, save the shards, train 2 more; a fresh engine restored from the shards must repeat those 2 steps
+        import shutil
+        import tempfile
+
+        ckpt = os.path.join(tempfile.gettempdir(), f"pkb_llama_ckpt_{os.environ.get('MASTER_PORT', '0')}")
+        a = FSDPLlama(ctx, cfg, impl="ours")
+        for i in range(2):
+            a.step(toks[i], tgts[i])
+        a.save_sharded(ckpt)
+        la = [float(a.step(toks[i], tgts[i])) for i in range(2, 4)]
+        b = FSDPLlama(ctx, cfg, impl="ours")
+        restored = b.load_sharded(ckpt)
+        lb = [float(b.step(toks[i], tgts[i])) for i in range(2, 4)]
+        same = restored == 2 and all(abs(x - y) <= 1e-3 * abs(x) for x, y in zip(la, lb))      # dQ sums use atomics: last bits may differ
+        same = same and torch.allclose(a.units[0].master, b.units[0].master, rtol=1e-3, atol=1e-5) and a.steps == b.steps == 4
+        if r == 0:
+            print(f"resume: continued {['%.5f' % x for x in la]} restored {['%.5f' % x for x in lb]} -> {'same' if same else 'DIFFERENT'}", flush=True)
+        fails += 0 if same else 1
+        torch.cuda.synchronize()
+        if W > 1:
+            dist.barrier()
+        if r == 0:
+            shutil.rmtree(ckpt, ignore_errors=True)
+        del a, b
     st = nv.read_status()
     if st[0] != 0:
         fails += 1

@@ -179,3 +179,38 @@ def test_moe_reference_with_fp8_experts_stays_close_to_bf16_experts():
     q = moe_reference(x, wr, None, wg, wu, wd, E, k, fp8_dispatch=True, fp8_experts=True).float()
     err = (q - base).abs().max() / base.abs().max()
     assert 0 < err < 0.1, err
+
+
+def test_fsdp_llama_sharded_checkpoint_round_trip_on_cpu():
+    """2 steps in one go against 1 step, save, restore into a fresh engine, 1 step: same losses and the same master weights
+    (PyTorch implementation of the engine, one CPU rank)."""
+    import tempfile
+
+    from parallelkernelbench_b200.models.llama import FSDPLlama, LlamaConfig
+    from parallelkernelbench_b200.parallel import init_context
+
+    ctx = init_context()
+    cfg = LlamaConfig(layers=2, hidden=64, ffn=128, heads=4, kv_heads=2, vocab=256, seq=32)
+    torch.manual_seed(0)
+    tok = [torch.randint(0, 256, (32,)) for _ in range(2)]
+    tgt = [torch.randint(0, 256, (32,)) for _ in range(2)]
+    a = FSDPLlama(ctx, cfg, impl="torch")
+    la = [float(a.step(tok[i], tgt[i])) for i in range(2)]
+    b = FSDPLlama(ctx, cfg, impl="torch")
+    lb0 = float(b.step(tok[0], tgt[0]))
+    with tempfile.TemporaryDirectory() as d:
+        path = b.save_sharded(d)
+        assert path.endswith("rank_0_of_1.pt")
+        c = FSDPLlama(ctx, cfg, impl="torch")
+        assert c.load_sharded(d) == 1
+        other = FSDPLlama(ctx, LlamaConfig(layers=2, hidden=64, ffn=256, heads=4, kv_heads=2, vocab=256, seq=32), impl="torch")
+        try:
+            other.load_sharded(d)
+        except ValueError as e:
+            assert "ffn" in str(e)
+        else:
+            raise AssertionError("a checkpoint of another config must be refused")
+    lc1 = float(c.step(tok[1], tgt[1]))
+    assert la[0] == lb0 and la[1] == lc1 and a.steps == c.steps == 2
+    assert torch.equal(a.units[1].master, c.units[1].master) and torch.equal(a.head_master, c.head_master)
+    assert torch.equal(a.embed.m, c.embed.m)

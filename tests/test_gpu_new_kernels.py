@@ -132,3 +132,15 @@ def test_moe_layer_with_expert_outputs_pushed_home_by_the_down_gemm(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     _all_ops(nproc, 29692 + nproc, "--ops", "moe_layer", "--config", "default", env={"PKB_PUSH_COMBINE": "1"})
     _all_ops(nproc, 29696 + nproc, "--ops", "moe_layer", "--config", "fp8_experts", env={"PKB_PUSH_COMBINE": "1"})
+
+
+def test_fsdp_llama_resumes_from_sharded_checkpoint():
+    """Not a kernel: the engine's per-rank checkpoint (fp32 master, Adam moments, fp8 wire copy, head, step count)."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=1", "--master-addr", "127.0.0.1",
+           "--master-port", "29699", os.path.join(root, "tests/mp/llama_worker.py"), "--resume-check"]
+    r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout and "-> same" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
