@@ -53,7 +53,9 @@ def cuda_lib():
     global _cuda
     with _lock:
         if _cuda is None:
-            lib = _load(_LIB_DIR / "libpkb200_cuda.so", "CUDA kernel library")
+            # PKB_JITTER=1 selects the timing-perturbation build (random pauses around signals and waits)
+            name = "libpkb200_cuda_jitter.so" if os.environ.get("PKB_JITTER") == "1" else "libpkb200_cuda.so"
+            lib = _load(_LIB_DIR / name, "CUDA kernel library")
             lib.pkb_last_error.restype = ctypes.c_char_p
             _cuda = lib
         return _cuda

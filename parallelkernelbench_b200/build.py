@@ -12,7 +12,7 @@ There is no JIT at run time: ranks load the prebuilt objects with ctypes, which 
 reference's per-rank ``load_inline`` cache juggling (reference: utils/cuda_helpers.py:14-47,
 scripts/worker.py:49-55).
 
-Usage: ``python -m parallelkernelbench_b200.build [--force] [--verbose] [--ptxas-info]``
+Usage: ``python -m parallelkernelbench_b200.build [--force] [--verbose] [--ptxas-info] [--jitter]``
 """
 from __future__ import annotations
 
@@ -31,6 +31,7 @@ OUT_DIR = PKG / "_lib"
 OBJ_DIR = PKG.parent / "build" / "obj"
 
 CUDA_LIB = OUT_DIR / "libpkb200_cuda.so"
+CUDA_LIB_JITTER = OUT_DIR / "libpkb200_cuda_jitter.so"   # -DPKB_JITTER: random pauses around signals and waits (PKB_JITTER=1 loads it)
 HOST_LIB = OUT_DIR / "libpkb200_host.so"
 
 NVCC_FLAGS = [
@@ -71,11 +72,12 @@ def _run(cmd: list[str], verbose: bool) -> str:
     return res.stdout + res.stderr
 
 
-def _compile_one(src: Path, obj: Path, force: bool, verbose: bool, ptxas_info: bool, hdr_mtime: float) -> str:
+def _compile_one(src: Path, obj: Path, force: bool, verbose: bool, ptxas_info: bool, hdr_mtime: float,
+                 defines: tuple[str, ...] = ()) -> str:
     if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_mtime):
         return ""
     if src.suffix == ".cu":
-        cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines], f"-I{INCLUDE}", "-c", str(src), "-o", str(obj)]
         if ptxas_info:
             cmd[1:1] = ["-Xptxas", "-v"]
     else:
@@ -113,13 +115,33 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = Fal
     return {"cuda": CUDA_LIB, "host": HOST_LIB}
 
 
+def build_jitter(force: bool = False, verbose: bool = False) -> Path:
+    """The timing-perturbation variant of the CUDA library (same sources, ``-DPKB_JITTER``)."""
+    OUT_DIR.mkdir(parents=True, exist_ok=True)
+    obj_dir = OBJ_DIR.parent / "obj_jitter"
+    obj_dir.mkdir(parents=True, exist_ok=True)
+    hdr_mtime = _headers_mtime()
+    jobs = [(s, obj_dir / (s.stem + "_cu.o")) for s in cuda_sources()]
+    with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        for f in [ex.submit(_compile_one, s, o, force, verbose, False, hdr_mtime, ("PKB_JITTER",)) for s, o in jobs]:
+            f.result()
+    objs = [str(o) for _, o in jobs]
+    newest = max(Path(o).stat().st_mtime for o in objs)
+    if force or not CUDA_LIB_JITTER.exists() or CUDA_LIB_JITTER.stat().st_mtime < newest:
+        _run([_nvcc(), "-shared", "-o", str(CUDA_LIB_JITTER), *objs, "-lcudart_static", "-ldl", "-lrt", "-lpthread"], verbose)
+    return CUDA_LIB_JITTER
+
+
 def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--jitter", action="store_true", help="also build libpkb200_cuda_jitter.so (random pauses around signals and waits)")
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
     args = ap.parse_args(argv)
     libs = build_all(force=args.force or args.ptxas_info, verbose=args.verbose, ptxas_info=args.ptxas_info)
+    if args.jitter:
+        libs["cuda_jitter"] = build_jitter(force=args.force, verbose=args.verbose)
     for k, v in libs.items():
         print(f"{k}: {v} ({'ok' if v.exists() else 'missing'})")
     return 0

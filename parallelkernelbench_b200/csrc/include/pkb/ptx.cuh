@@ -369,13 +369,29 @@ __device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
   asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// Timing-perturbation build (-DPKB_JITTER, `python -m parallelkernelbench_b200.build --jitter`): a pseudo-random pause of up
+// to ~4 us before every system-scope signal and after every successful wait shifts the ranks against each other from call to
+// call, so an ordering that only holds by luck (a missing fence, a flag published before its data) shows up as a wrong
+// result in the ordinary tests instead of once in a long run. The release build compiles the pause away.
+#ifdef PKB_JITTER
+__device__ __forceinline__ void jitter_pause() {
+  uint32_t h = static_cast<uint32_t>(clock64()) * 2654435761u;
+  h ^= threadIdx.x * 40503u + blockIdx.x * 9176u;
+  __nanosleep((h >> 19) & 0xfffu);
+}
+#else
+__device__ __forceinline__ void jitter_pause() {}
+#endif
+
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  jitter_pause();
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void red_release_sys_add(uint32_t* p, uint32_t v) {
+  jitter_pause();
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
@@ -388,7 +404,10 @@ __device__ __forceinline__ void fence_acq_rel_sys() {
 // Bounded wait until *flag >= target (flags are monotonically increasing epoch counters).
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target,
                                              uint64_t budget_ns = kDefaultWaitBudgetNs) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) return true;
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - target) >= 0) {
+    jitter_pause();
+    return true;
+  }
   long long t0 = 0;
   uint32_t spins = 0;
   while (static_cast<int32_t>(ld_acquire_sys(flag) - target) < 0) {
@@ -399,6 +418,7 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t targ
       __nanosleep(32);
     }
   }
+  jitter_pause();
   return true;
 }
 

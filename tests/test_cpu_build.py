@@ -30,3 +30,24 @@ def test_missing_library_raises_loudly(monkeypatch, tmp_path):
         assert "Build it" in str(e)
     else:
         raise AssertionError("a missing kernel library must not be silently ignored")
+
+
+def test_jitter_variant_builds_and_is_selected_by_env(monkeypatch):
+    """The timing-perturbation build (-DPKB_JITTER) is a second library with the same entry points; PKB_JITTER=1 loads it."""
+    import ctypes
+
+    from parallelkernelbench_b200 import _native as nv
+    from parallelkernelbench_b200 import build
+
+    path = build.build_jitter()
+    assert path.exists() and path.name == "libpkb200_cuda_jitter.so"
+    lib = ctypes.CDLL(str(path))
+    for sym in ("pkb_coll_reduce", "pkb_coll_allreduce_ll", "pkb_tp_ag_gemm", "pkb_moe_dispatch", "pkb_flash_attn_fwd"):
+        assert hasattr(lib, sym), sym
+    seen = []
+    monkeypatch.setenv("PKB_JITTER", "1")
+    monkeypatch.setattr(nv, "_cuda", None)
+    monkeypatch.setattr(nv, "_load", lambda p, what: seen.append(p.name) or lib)
+    nv.cuda_lib()
+    assert seen == ["libpkb200_cuda_jitter.so"]
+    monkeypatch.setattr(nv, "_cuda", None)

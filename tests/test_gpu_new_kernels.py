@@ -144,3 +144,20 @@ def test_fsdp_llama_resumes_from_sharded_checkpoint():
            "--master-port", "29699", os.path.join(root, "tests/mp/llama_worker.py"), "--resume-check"]
     r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout and "-> same" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_collectives_and_tp_mlp_under_the_timing_perturbation_build():
+    """Random pauses around every signal and wait (PKB_JITTER=1 loads the -DPKB_JITTER library): results must not change."""
+    import subprocess
+    import sys
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "parallelkernelbench_b200/_lib/libpkb200_cuda_jitter.so")):
+        pytest.skip("build it with: python -m parallelkernelbench_b200.build --jitter")
+    for i, script in enumerate(("tests/mp/collectives_worker.py", "tests/mp/tp_mlp_worker.py", "tests/mp/moe_worker.py")):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+               "--master-port", str(29660 + i), os.path.join(root, script)]
+        r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, "PKB_JITTER": "1"})
+        assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, script + r.stdout[-3000:] + r.stderr[-3000:]
