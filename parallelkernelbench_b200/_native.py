@@ -53,8 +53,13 @@ def cuda_lib():
     global _cuda
     with _lock:
         if _cuda is None:
-            # PKB_JITTER=1 selects the timing-perturbation build (random pauses around signals and waits)
-            name = "libpkb200_cuda_jitter.so" if os.environ.get("PKB_JITTER") == "1" else "libpkb200_cuda.so"
+            # debug variants: PKB_JITTER=1 -> random pauses around signals and waits; PKB_DEBUG_BOUNDS=1 -> checked
+            # symmetric-heap bases (violations recorded in the status block, the access redirected to a scratch line)
+            name = "libpkb200_cuda.so"
+            if os.environ.get("PKB_JITTER") == "1":
+                name = "libpkb200_cuda_jitter.so"
+            elif os.environ.get("PKB_DEBUG_BOUNDS") == "1":
+                name = "libpkb200_cuda_bounds.so"
             lib = _load(_LIB_DIR / name, "CUDA kernel library")
             lib.pkb_last_error.restype = ctypes.c_char_p
             _cuda = lib

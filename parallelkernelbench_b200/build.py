@@ -12,7 +12,7 @@ There is no JIT at run time: ranks load the prebuilt objects with ctypes, which 
 reference's per-rank ``load_inline`` cache juggling (reference: utils/cuda_helpers.py:14-47,
 scripts/worker.py:49-55).
 
-Usage: ``python -m parallelkernelbench_b200.build [--force] [--verbose] [--ptxas-info] [--jitter]``
+Usage: ``python -m parallelkernelbench_b200.build [--force] [--verbose] [--ptxas-info] [--jitter] [--debug-bounds]``
 """
 from __future__ import annotations
 
@@ -31,7 +31,11 @@ OUT_DIR = PKG / "_lib"
 OBJ_DIR = PKG.parent / "build" / "obj"
 
 CUDA_LIB = OUT_DIR / "libpkb200_cuda.so"
-CUDA_LIB_JITTER = OUT_DIR / "libpkb200_cuda_jitter.so"   # -DPKB_JITTER: random pauses around signals and waits (PKB_JITTER=1 loads it)
+# debug variants of the CUDA library: same sources, one extra define, selected at load time by an environment variable
+#   jitter: -DPKB_JITTER        random pauses around system-scope signals and waits      (PKB_JITTER=1)
+#   bounds: -DPKB_DEBUG_BOUNDS  checked bases of symmetric-heap accesses, recorded not trapped (PKB_DEBUG_BOUNDS=1)
+VARIANTS = {"jitter": "PKB_JITTER", "bounds": "PKB_DEBUG_BOUNDS"}
+CUDA_LIB_JITTER = OUT_DIR / "libpkb200_cuda_jitter.so"
 HOST_LIB = OUT_DIR / "libpkb200_host.so"
 
 NVCC_FLAGS = [
@@ -115,33 +119,42 @@ def build_all(force: bool = False, verbose: bool = False, ptxas_info: bool = Fal
     return {"cuda": CUDA_LIB, "host": HOST_LIB}
 
 
-def build_jitter(force: bool = False, verbose: bool = False) -> Path:
-    """The timing-perturbation variant of the CUDA library (same sources, ``-DPKB_JITTER``)."""
+def build_variant(variant: str, force: bool = False, verbose: bool = False) -> Path:
+    """A debug variant of the CUDA library (see ``VARIANTS``): ``_lib/libpkb200_cuda_<variant>.so``."""
+    define = VARIANTS[variant]
+    out = OUT_DIR / f"libpkb200_cuda_{variant}.so"
     OUT_DIR.mkdir(parents=True, exist_ok=True)
-    obj_dir = OBJ_DIR.parent / "obj_jitter"
+    obj_dir = OBJ_DIR.parent / f"obj_{variant}"
     obj_dir.mkdir(parents=True, exist_ok=True)
     hdr_mtime = _headers_mtime()
     jobs = [(s, obj_dir / (s.stem + "_cu.o")) for s in cuda_sources()]
     with cf.ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
-        for f in [ex.submit(_compile_one, s, o, force, verbose, False, hdr_mtime, ("PKB_JITTER",)) for s, o in jobs]:
+        for f in [ex.submit(_compile_one, s, o, force, verbose, False, hdr_mtime, (define,)) for s, o in jobs]:
             f.result()
     objs = [str(o) for _, o in jobs]
     newest = max(Path(o).stat().st_mtime for o in objs)
-    if force or not CUDA_LIB_JITTER.exists() or CUDA_LIB_JITTER.stat().st_mtime < newest:
-        _run([_nvcc(), "-shared", "-o", str(CUDA_LIB_JITTER), *objs, "-lcudart_static", "-ldl", "-lrt", "-lpthread"], verbose)
-    return CUDA_LIB_JITTER
+    if force or not out.exists() or out.stat().st_mtime < newest:
+        _run([_nvcc(), "-shared", "-o", str(out), *objs, "-lcudart_static", "-ldl", "-lrt", "-lpthread"], verbose)
+    return out
+
+
+def build_jitter(force: bool = False, verbose: bool = False) -> Path:
+    return build_variant("jitter", force, verbose)
 
 
 def main(argv: list[str] | None = None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--jitter", action="store_true", help="also build libpkb200_cuda_jitter.so (random pauses around signals and waits)")
+    ap.add_argument("--debug-bounds", action="store_true", help="also build libpkb200_cuda_bounds.so (checked symmetric-heap bases)")
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--ptxas-info", action="store_true", help="print registers / spills / shared memory per kernel")
     args = ap.parse_args(argv)
     libs = build_all(force=args.force or args.ptxas_info, verbose=args.verbose, ptxas_info=args.ptxas_info)
     if args.jitter:
-        libs["cuda_jitter"] = build_jitter(force=args.force, verbose=args.verbose)
+        libs["cuda_jitter"] = build_variant("jitter", force=args.force, verbose=args.verbose)
+    if args.debug_bounds:
+        libs["cuda_bounds"] = build_variant("bounds", force=args.force, verbose=args.verbose)
     for k, v in libs.items():
         print(f"{k}: {v} ({'ok' if v.exists() else 'missing'})")
     return 0

@@ -43,8 +43,22 @@ struct SymmCtx {
   uint64_t budget_ns;
 };
 
+// Checked build (-DPKB_DEBUG_BOUNDS, `python -m parallelkernelbench_b200.build --debug-bounds`): a rank outside the heap or an
+// offset beyond one rank's slab is recorded in the status block (BOUNDS_VIOLATION with this rank, the bad rank and the
+// offset in 4 KiB units) and the access is redirected to a scratch line at the end of this rank's control space, so
+// nothing outside the heap is touched and nothing traps. Only the base of an access is checked, not the index added to it.
+constexpr uint64_t kSymmBoundsScratch = kSymmCtrlBytes - 4096;
+static_assert(kSymmChannels * kSymmChannelBytes <= kSymmBoundsScratch, "the scratch line overlaps the channel tables");
+
 template <typename T>
 __device__ __forceinline__ T* symm_ptr(const SymmCtx& c, int global_rank, uint64_t off) {
+#ifdef PKB_DEBUG_BOUNDS
+  if (static_cast<unsigned>(global_rank) >= static_cast<unsigned>(c.world) || off >= c.stride) {
+    record_status(c.status, kStatusBoundsViolation, 0, c.rank, static_cast<uint32_t>(global_rank), 0,
+                  static_cast<uint32_t>(off >> 12));
+    return reinterpret_cast<T*>(c.base + (uint64_t)c.rank * c.stride + kSymmBoundsScratch);
+  }
+#endif
   return reinterpret_cast<T*>(c.base + (uint64_t)global_rank * c.stride + off);
 }
 template <typename T>

@@ -39,7 +39,8 @@ def test_jitter_variant_builds_and_is_selected_by_env(monkeypatch):
     from parallelkernelbench_b200 import _native as nv
     from parallelkernelbench_b200 import build
 
-    path = build.build_jitter()
+    assert set(build.VARIANTS) == {"jitter", "bounds"}
+    path = build.build_variant("jitter")
     assert path.exists() and path.name == "libpkb200_cuda_jitter.so"
     lib = ctypes.CDLL(str(path))
     for sym in ("pkb_coll_reduce", "pkb_coll_allreduce_ll", "pkb_tp_ag_gemm", "pkb_moe_dispatch", "pkb_flash_attn_fwd"):
@@ -50,4 +51,9 @@ def test_jitter_variant_builds_and_is_selected_by_env(monkeypatch):
     monkeypatch.setattr(nv, "_load", lambda p, what: seen.append(p.name) or lib)
     nv.cuda_lib()
     assert seen == ["libpkb200_cuda_jitter.so"]
+    monkeypatch.delenv("PKB_JITTER")
+    monkeypatch.setenv("PKB_DEBUG_BOUNDS", "1")
+    monkeypatch.setattr(nv, "_cuda", None)
+    nv.cuda_lib()
+    assert seen[-1] == "libpkb200_cuda_bounds.so"
     monkeypatch.setattr(nv, "_cuda", None)

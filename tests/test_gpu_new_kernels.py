@@ -161,3 +161,19 @@ def test_collectives_and_tp_mlp_under_the_timing_perturbation_build():
                "--master-port", str(29660 + i), os.path.join(root, script)]
         r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, "PKB_JITTER": "1"})
         assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, script + r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_collectives_and_moe_under_the_checked_build_record_no_violation():
+    """PKB_DEBUG_BOUNDS=1 loads the -DPKB_DEBUG_BOUNDS library: correct code must leave the status block clean."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "parallelkernelbench_b200/_lib/libpkb200_cuda_bounds.so")):
+        pytest.skip("build it with: python -m parallelkernelbench_b200.build --debug-bounds")
+    n = 2 if torch.cuda.device_count() >= 2 else 1
+    for i, script in enumerate(("tests/mp/collectives_worker.py", "tests/mp/moe_worker.py")):
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+               "--master-port", str(29664 + i), os.path.join(root, script)]
+        r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, "PKB_DEBUG_BOUNDS": "1"})
+        assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, script + r.stdout[-3000:] + r.stderr[-3000:]
