@@ -20,11 +20,17 @@
 //  tp_gemm_allgather  GEMM -> all-gather along N (column-parallel linear). The TMA-store epilogue stores every output
 //                   tile into the gathered result of every rank at this rank's column block; a closing barrier
 //                   tells each rank that all column blocks have landed.
+//  tp_gemv_allgather  decode-time LM head: logits of this rank's vocabulary block for 1..4 tokens (memory bound: one warp
+//                   per 8 weight rows, 16-byte loads, fp32 accumulation), bias, and the all-gather along the vocabulary
+//                   in the same kernel - each group of 8 logits leaves as one 16-byte `multimem.st` (or one P2P store
+//                   per member) into every rank's result; results alternate between two buffers so that one closing
+//                   barrier per call is enough.
 //
 // Reference behaviour being replaced: all_gather + matmul + silu, matmul + reduce_scatter,
 // reduce_scatter + RMSNorm and matmul + all_reduce as separate NCCL / cuBLAS / elementwise launches
 // (reference: reference/15_combined_sharded_gemms.py:17-31, reference/16_gemm_reducescatter.py:19-22,
-//  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20, reference/14_gemm_allgather.py:17-22).
+//  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20, reference/14_gemm_allgather.py:17-22,
+//  reference/46_gemv_decode.py:13-18).
 #include "pkb/api.h"
 #include "pkb/collectives_api.h"
 #include "pkb/gemm_umma2.cuh"
@@ -274,6 +280,83 @@ tp_gemm_allgather_kernel(const __grid_constant__ CUtensorMap tmap_a,
   gemm_umma2_cta<EPI, false, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1, &out_maps);
   // the same-index blocks of every rank have completed their stores once this barrier passes
   symm_block_barrier(c, 303, 2);
+}
+
+struct TpGemvArgs {
+  SymmCtx ctx;
+  const __nv_bfloat16* h;     // [M, K] activations (the same on every rank)
+  const __nv_bfloat16* w;     // [n_local, K] this rank's rows of the weight
+  const __nv_bfloat16* bias;  // [n_local] or nullptr
+  uint64_t out_off;           // heap offset of the result buffer of this call: [M, gsize * n_local] bf16
+  int K, n_local;
+  long long ldw;              // elements between rows of w
+  int use_mc;
+};
+
+// One warp computes 8 consecutive logits for all M tokens: per 16-byte chunk of K it loads the chunk of the M activation
+// rows once and of 8 weight rows (8 independent loads in flight), accumulates in fp32, reduces across the warp.
+template <int M>
+__global__ void __launch_bounds__(256) tp_gemv_allgather_kernel(const TpGemvArgs a) {
+  const SymmCtx& c = a.ctx;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int groups = a.n_local >> 3;
+  const long long n_total = (long long)c.gsize * a.n_local;
+  for (int grp = blockIdx.x * warps_per_block + (threadIdx.x >> 5); grp < groups; grp += gridDim.x * warps_per_block) {
+    const int n0 = grp << 3;
+    float acc[8][M];
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+    for (int k = lane * 8; k < a.K; k += 256) {
+      float hv[M][8];
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const U4 u = ld_global_nc_v4(a.h + (long long)m * a.K + k);
+        const float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z), f3 = unpack_bf16x2(u.w);
+        hv[m][0] = f0.x; hv[m][1] = f0.y; hv[m][2] = f1.x; hv[m][3] = f1.y;
+        hv[m][4] = f2.x; hv[m][5] = f2.y; hv[m][6] = f3.x; hv[m][7] = f3.y;
+      }
+      U4 wv[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) wv[r] = ld_global_nc_v4(a.w + (long long)(n0 + r) * a.ldw + k);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        const float2 f0 = unpack_bf16x2(wv[r].x), f1 = unpack_bf16x2(wv[r].y), f2 = unpack_bf16x2(wv[r].z),
+                     f3 = unpack_bf16x2(wv[r].w);
+        const float wf[8] = {f0.x, f0.y, f1.x, f1.y, f2.x, f2.y, f3.x, f3.y};
+#pragma unroll
+        for (int m = 0; m < M; ++m)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[r][m] = fmaf(wf[j], hv[m][j], acc[r][m]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r)
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+    if (lane == 0) {
+      float b[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (a.bias != nullptr) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) b[r] = __bfloat162float(a.bias[n0 + r]);
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        U4 o{pack_bf16x2(acc[0][m] + b[0], acc[1][m] + b[1]), pack_bf16x2(acc[2][m] + b[2], acc[3][m] + b[3]),
+             pack_bf16x2(acc[4][m] + b[4], acc[5][m] + b[5]), pack_bf16x2(acc[6][m] + b[6], acc[7][m] + b[7])};
+        const long long eoff = (long long)m * n_total + (long long)c.grank * a.n_local + n0;
+        if (a.use_mc) {
+          multimem_st_v4(symm_mc<__nv_bfloat16>(c, a.out_off) + eoff, o);
+        } else {
+          for (int g = 0; g < c.gsize; ++g) st_global_v4(symm_ptr<__nv_bfloat16>(c, c.members[g], a.out_off) + eoff, o);
+        }
+      }
+    }
+  }
+  // all same-index blocks of all ranks have stored their logits once this barrier passes
+  symm_block_barrier(c, 304, 1);
 }
 
 }  // namespace pkb
@@ -552,6 +635,34 @@ int pkb_tp_gemm_allgather(const pkb_symm_ctx* h, const void* a_mat, long long ld
     default: PKB_GAG(kEpiBiasSilu) break;
   }
 #undef PKB_GAG
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// logits[M, gsize * n_local] (bf16, at heap offset out_off on every rank) = all_gather along the vocabulary of h @ w^T + bias
+// for M in {1, 2, 4} tokens: h [M, K] the same on every rank, w [n_local, K] this rank's rows. K % 8 == 0, n_local % 8 == 0,
+// all pointers 16-byte aligned. Consecutive calls must alternate between two result buffers (there is no entry barrier);
+// the result is valid on this rank when the kernel has finished.
+int pkb_tp_gemv_allgather(const pkb_symm_ctx* h, const void* act, const void* w, long long ldw, const void* bias, int M,
+                          int n_local, int K, unsigned long long out_off, int allow_multicast, void* stream) {
+  if (int rc = symm_ctx_check(h)) return rc;
+  PKB_CHECK_ARG(M == 1 || M == 2 || M == 4, "1, 2 or 4 tokens");
+  PKB_CHECK_ARG(K > 0 && K % 8 == 0 && n_local > 0 && n_local % 8 == 0 && ldw % 8 == 0, "K, n_local, ldw must be multiples of 8");
+  PKB_CHECK_ARG(((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(w) | out_off) & 15) == 0, "16-byte alignment");
+  PKB_CHECK_ARG((((long long)h->gsize * n_local) & 7) == 0, "row pitch of the result must be a multiple of 8");
+  TpGemvArgs a;
+  a.ctx = symm_ctx_from_api(h);
+  a.h = static_cast<const __nv_bfloat16*>(act);
+  a.w = static_cast<const __nv_bfloat16*>(w);
+  a.bias = static_cast<const __nv_bfloat16*>(bias);
+  a.out_off = out_off; a.K = K; a.n_local = n_local; a.ldw = ldw;
+  a.use_mc = (allow_multicast && h->mc_base != 0 && h->gsize == h->world && h->gsize > 1) ? 1 : 0;
+  int grid = sm_count();           // the same on every rank: the closing barrier pairs blocks by index
+  if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (M == 1) tp_gemv_allgather_kernel<1><<<grid, 256, 0, s>>>(a);
+  else if (M == 2) tp_gemv_allgather_kernel<2><<<grid, 256, 0, s>>>(a);
+  else tp_gemv_allgather_kernel<4><<<grid, 256, 0, s>>>(a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -9,6 +9,8 @@
                      (``multimem.st`` through the switch, or one P2P store per member), closed by a barrier.
 ``GemmAllGather``    (a @ w.T) gathered along the output features (column-parallel linear) in one launch: the TMA-store
                      epilogue writes every output tile into the gathered result of every rank.
+``GemvAllGather``    decode-time LM head for 1, 2 or 4 tokens: memory-bound GEMV over this rank's vocabulary block, bias and the
+                     all-gather of the logits in one launch (16-byte ``multimem.st`` / P2P stores, one closing barrier).
 
 All keep their symmetric buffers between calls (steady-state calls allocate nothing), like the
 module-level buffer caches of the reference's example solutions
@@ -154,3 +156,34 @@ class GemmAllGather:
             nv.ptr(bias), epi, ctypes.c_ulonglong(self.out.offset), nv.current_stream()), "pkb_tp_gemm_allgather")
         nv.count_launch()
         return self.out.local
+
+
+class GemvAllGather:
+    """Vocabulary-parallel LM head at decode time (reference: reference/46_gemv_decode.py:13-18).
+
+    Results alternate between two symmetric buffers, so a returned view stays valid until the call after the next one."""
+
+    def __init__(self, group: SymmGroup, tokens: int, n_local: int, multicast: bool = True):
+        if tokens not in (1, 2, 4):
+            raise ValueError("1, 2 or 4 tokens per call (use the GEMM for larger batches)")
+        if n_local % 8 != 0:
+            raise ValueError("n_local must be a multiple of 8")
+        self.group, self.m, self.n_local, self.multicast = group, tokens, n_local, multicast
+        self.out = [group.heap.empty((tokens, group.size * n_local), torch.bfloat16) for _ in range(2)]
+        self.calls = 0
+
+    def __call__(self, h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        if h.shape[0] != self.m or h.dtype != torch.bfloat16 or not h.is_contiguous():
+            raise ValueError("h must be contiguous bf16 [tokens, K]")
+        K = h.shape[1]
+        if w.shape != (self.n_local, K) or w.stride(1) != 1 or w.dtype != torch.bfloat16 or K % 8 or w.stride(0) % 8:
+            raise ValueError("w must be bf16 [n_local, K] with K and its row pitch multiples of 8")
+        if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != self.n_local or not bias.is_contiguous()):
+            raise ValueError("bias must be contiguous bf16 [n_local]")
+        buf = self.out[self.calls & 1]
+        self.calls += 1
+        nv.check(nv.cuda_lib().pkb_tp_gemv_allgather(self.group.ref, nv.ptr(h), nv.ptr(w), nv.c_ll(w.stride(0)), nv.ptr(bias), self.m,
+                                                     self.n_local, K, ctypes.c_ulonglong(buf.offset), 1 if self.multicast else 0,
+                                                     nv.current_stream()), "pkb_tp_gemv_allgather")
+        nv.count_launch()
+        return buf.local

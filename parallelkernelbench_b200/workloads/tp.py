@@ -404,6 +404,16 @@ def _gemv_ref(rc, h, w, b):
 
 
 def _gemv_ours(rc, h, w, b):
+    import os
+
+    if (os.environ.get("PKB_FUSED_GEMV_AG") == "1" and rc.dist.is_cuda and h.dtype == torch.bfloat16 and h.shape[0] in (1, 2, 4)
+            and w.shape[0] % 8 == 0 and w.shape[1] % 8 == 0):
+        from ..ops.tp import GemvAllGather
+
+        key = ("gemv_ag", h.shape[0], w.shape[0])
+        if key not in rc.cache:
+            rc.cache[key] = GemvAllGather(rc.comm.group(), h.shape[0], w.shape[0])
+        return rc.cache[key](h.contiguous(), w.contiguous(), b.contiguous()).clone()
     if rc.dist.is_cuda and h.dtype == torch.bfloat16:
         from ..ops import gemm_bf16
 
@@ -413,7 +423,8 @@ def _gemv_ours(rc, h, w, b):
     return rc.comm.all_gather_cat(y.contiguous(), dim=1) if rc.world > 1 else y
 
 
-register(OpSpec(name="gemv_decode", problem_ids=(46,), group="tp", configs={"default": {"hidden": 1024, "vocab_local": 1024}},
+register(OpSpec(name="gemv_decode", problem_ids=(46,), group="tp",
+                configs={"default": {"hidden": 1024, "vocab_local": 1024}, "llama": {"hidden": 4096, "vocab_local": 16032}},
                 make_inputs=_gemv_inputs, reference=_gemv_ref, ours=_gemv_ours, atol=5e-2, rtol=2e-2,
                 cost=lambda cfg, W: Cost(hbm_bytes=cfg["hidden"] * cfg["vocab_local"] * 2, flops=2.0 * cfg["hidden"] * cfg["vocab_local"])))
 

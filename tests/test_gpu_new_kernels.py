@@ -177,3 +177,11 @@ def test_collectives_and_moe_under_the_checked_build_record_no_violation():
                "--master-port", str(29664 + i), os.path.join(root, script)]
         r = subprocess.run(cmd, cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, "PKB_DEBUG_BOUNDS": "1"})
         assert r.returncode == 0 and "TOTAL_FAILS 0" in r.stdout, script + r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("nproc", [1, 2])
+def test_fused_gemv_allgather_matches_gemv_then_allgather(nproc):
+    if torch.cuda.device_count() < nproc:
+        pytest.skip(f"needs {nproc} GPUs")
+    _all_ops(nproc, 29652 + nproc, "--ops", "gemv_decode", "--config", "default", "--trials", "3", env={"PKB_FUSED_GEMV_AG": "1"})
+    _all_ops(nproc, 29656 + nproc, "--ops", "gemv_decode", "--config", "llama", env={"PKB_FUSED_GEMV_AG": "1"})
