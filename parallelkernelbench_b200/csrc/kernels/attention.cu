@@ -460,7 +460,13 @@ struct Fa2Smem {
   static constexpr int kTotal = kBars + 256;
 };
 
-template <int D>
+// SPEC (speculative single pass, PKB_FA_SPEC=1): from the second KV tile on, a softmax warp whose rows all have a finite
+// offset computes the exponentials with the CURRENT offset in the same pass that finds the tile's row maximum - one read of
+// S from TMEM instead of two - and tells the correction warps "no rescale" up front. Only if some row's maximum has grown by
+// more than the lazy threshold does the warp repeat the pass with the new offset and rescale its own accumulator rows
+// (after the previous P V product has landed). The offset moves under exactly the same rule as in the two-pass form, so
+// the results are bit-identical to it.
+template <int D, bool SPEC = false>
 __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                             const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
                                             const int head, const int batch) {
@@ -669,6 +675,102 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
         if (!ok) return;
         tc_fence_after_sync();
         const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
+        if constexpr (SPEC) {
+          if (cnt > 0 && __all_sync(0xffffffffu, m_run != -INFINITY)) {
+            // exponentials of S with offset `off`, written to shared memory as bf16 P; returns the row sum and, through
+            // `mx_out`, the largest unmasked raw score of the row
+            auto exp_pass = [&](const float off, float& mx_out) {
+              const uint32_t prow = sb + S::kP + t * S::kPBytes + static_cast<uint32_t>(row) * 128u;
+              float sum = 0.f, mxl = -INFINITY;
+#pragma unroll
+              for (int cc = 0; cc < 4; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32(s_row + cc * 32, r);
+                tmem_ld_wait();
+                float pvv[32];
+                if (need_mask) {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const int col = cc * 32 + i;
+                    const bool masked = col >= valid || (d.causal && kp + col > my_pos);
+                    const float sv = __uint_as_float(r[i]);
+                    if (!masked) mxl = fmaxf(mxl, sv);
+                    pvv[i] = masked ? 0.f : fast_exp2(fmaf(sv, scale2, -off));
+                  }
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i) {
+                    const float sv = __uint_as_float(r[i]);
+                    mxl = fmaxf(mxl, sv);
+                    pvv[i] = fast_exp2(fmaf(sv, scale2, -off));
+                  }
+                }
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < 32; ++i) part[i & 3] += pvv[i];
+                sum += (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const int chunk = cc * 4 + g;
+                  const uint32_t atom = (chunk >> 3) * kAtomBytes;
+                  const uint32_t dst = prow + atom + (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16x2(pvv[8 * g], pvv[8 * g + 1])),
+                               "r"(pack_bf16x2(pvv[8 * g + 2], pvv[8 * g + 3])), "r"(pack_bf16x2(pvv[8 * g + 4], pvv[8 * g + 5])),
+                               "r"(pack_bf16x2(pvv[8 * g + 6], pvv[8 * g + 7]))
+                               : "memory");
+                }
+              }
+              mx_out = mxl;
+              return sum;
+            };
+            // the guess "no rescale" goes to the correction warps before the pass
+            ok = mbar_wait(a_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            alpha_s[t * kFaTile + row] = 1.f;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_full(t));
+            ok = mbar_wait(p_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) return;
+            float mxs;
+            float sum = exp_pass(m_run, mxs);
+            mxs *= scale2;
+            const bool grow = mxs > m_run + 8.f;
+            if (!__any_sync(0xffffffffu, grow)) {
+              l_run += sum;
+            } else {
+              // the guess was wrong for some row of this warp: repeat with the new offsets and rescale the accumulator here
+              const float m_new = grow ? mxs : m_run;
+              const float alpha = grow ? fast_exp2(m_run - m_new) : 1.f;
+              float unused;
+              sum = exp_pass(m_new, unused);
+              l_run = l_run * alpha + sum;
+              m_run = m_new;
+              ok = mbar_wait(pv_done(t), (cnt - 1) & 1, abort_flag, p.budget_ns);   // cnt > 0 on this path
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) return;
+              tc_fence_after_sync();
+              const uint32_t o_row = tmem_o(t) + (static_cast<uint32_t>(q4 * 32) << 16);
+#pragma unroll
+              for (int cc = 0; cc < D / 32; ++cc) {
+                uint32_t r[32];
+                tmem_ld_32x32(o_row + cc * 32, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                tmem_st_32x32(o_row + cc * 32, r);
+              }
+              tmem_st_wait();
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(t));
+            ++cnt;
+            return;
+          }
+        }
         float mx = -INFINITY;
 #pragma unroll
         for (int cc = 0; cc < 4; ++cc) {
@@ -842,11 +944,11 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
   }
 }
 
-template <int D>
+template <int D, bool SPEC = false>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
-  fa_fwd2_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+  fa_fwd2_cta<D, SPEC>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 template <int D>
@@ -938,7 +1040,7 @@ fa_fwd_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   fa_fwd_cta<D>(tmap_q, tmap_k, tmap_v, p, qt, hb % a.hq, hb / a.hq);
 }
 
-template <int D>
+template <int D, bool SPEC = false>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd2_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const FaCommArgs a) {
@@ -950,7 +1052,13 @@ fa_fwd2_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int id = blockIdx.x - a.comm_blocks;
   const int qp = pairs - 1 - id % pairs;
   const int hb = id / pairs;
-  fa_fwd2_cta<D>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
+  fa_fwd2_cta<D, SPEC>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
+}
+
+// PKB_FA_SPEC=1 selects the speculative single-pass softmax of the two-tile kernel (off by default).
+static bool fa_use_spec() {
+  static const bool on = [] { const char* e = getenv("PKB_FA_SPEC"); return e != nullptr && e[0] == '1'; }();
+  return on;
 }
 
 // The two-tile form needs both tiles of a pair in one position run; PKB_FA_ONE_TILE=1 forces the one-tile kernel.
@@ -985,11 +1093,17 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   p.trace_capacity = d.trace_capacity;
   const int n_tiles = (d.sq + kFaTile - 1) / kFaTile;
   if (fa_use_pairs(d) && p.trace == nullptr) {
-    auto kern = fa_fwd2_kernel<D>;
     constexpr int smem = Fa2Smem<D>::kTotal;
-    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
-    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+    if (fa_use_spec()) {
+      auto kern = fa_fwd2_kernel<D, true>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+    } else {
+      auto kern = fa_fwd2_kernel<D, false>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+    }
   } else {
     auto kern = fa_fwd_kernel<D>;
     constexpr int smem = FaSmem<D>::kTotal;
@@ -1074,11 +1188,17 @@ static int launch_fa_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, cons
   p.trace = nullptr;
   p.trace_capacity = 0;
   if (fa_use_pairs(d)) {
-    auto kern = fa_fwd2_ring_kernel<D>;
     constexpr int smem = Fa2Smem<D>::kTotal;
-    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     const int grid = comm_blocks + ((a.num_q_tiles + 1) / 2) * d.hq * d.batch;
-    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+    if (fa_use_spec()) {
+      auto kern = fa_fwd2_ring_kernel<D, true>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+    } else {
+      auto kern = fa_fwd2_ring_kernel<D, false>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+    }
   } else {
     auto kern = fa_fwd_ring_kernel<D>;
     constexpr int smem = FaSmem<D>::kTotal;

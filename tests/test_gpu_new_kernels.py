@@ -185,3 +185,25 @@ def test_fused_gemv_allgather_matches_gemv_then_allgather(nproc):
         pytest.skip(f"needs {nproc} GPUs")
     _all_ops(nproc, 29652 + nproc, "--ops", "gemv_decode", "--config", "default", "--trials", "3", env={"PKB_FUSED_GEMV_AG": "1"})
     _all_ops(nproc, 29656 + nproc, "--ops", "gemv_decode", "--config", "llama", env={"PKB_FUSED_GEMV_AG": "1"})
+
+
+def test_speculative_single_pass_softmax_is_bit_identical_to_the_two_pass_form(tmp_path):
+    """PKB_FA_SPEC=1 changes how often S is read from TMEM, not which offsets the exponentials use: outputs must be equal bit
+    for bit, and the ordinary forward tests must pass with it."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    files = {}
+    for name, env in (("two_pass", {}), ("spec", {"PKB_FA_SPEC": "1"})):
+        files[name] = str(tmp_path / f"{name}.pt")
+        r = subprocess.run([sys.executable, os.path.join(root, "tests/mp/fa_variant_worker.py"), files[name]], cwd=root,
+                           capture_output=True, text=True, timeout=600, env={**os.environ, **env})
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    a, b = torch.load(files["two_pass"]), torch.load(files["spec"])
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests/test_gpu_attention.py"), "-x", "-q", "-k",
+                        "matches_reference or zigzag_rank"], cwd=root, capture_output=True, text=True, timeout=900,
+                       env={**os.environ, "PKB_FA_SPEC": "1"})
+    assert r.returncode == 0, r.stdout[-3000:]
