@@ -165,6 +165,8 @@ int encode_tmap_3d(CUtensorMap* out, int dtype, const void* base, uint64_t inner
 }
 
 // A kernel that waits on a flag nobody sets: exercises the bounded-wait path end to end.
+__global__ void stamp_globaltimer_kernel(unsigned long long* out) { *out = globaltimer_ns(); }
+
 __global__ void wait_selftest_kernel(const uint32_t* flag, uint32_t target, uint64_t budget_ns,
                                      uint32_t* status, uint32_t* out_elapsed_us) {
   const uint64_t t0 = globaltimer_ns();
@@ -199,6 +201,15 @@ int pkb_status_clear() {
   if (!dptr) return kApiCudaError;
   int d = current_device();
   for (int i = 0; i < kStatusWords; ++i) g_status_host[d][i] = 0;
+  return kApiOk;
+}
+
+// One thread writes the GPU's nanosecond timer to *out_ns (uint64, device memory) when the stream reaches this point:
+// a device-side clock for cross-checking event timings.
+int pkb_stamp_globaltimer(void* out_ns, void* stream) {
+  PKB_CHECK_ARG(out_ns != nullptr && (reinterpret_cast<uintptr_t>(out_ns) & 7) == 0, "out_ns must be an 8-byte aligned device pointer");
+  stamp_globaltimer_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned long long*>(out_ns));
+  PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
 

@@ -62,6 +62,42 @@ def _clone_args(args: tuple) -> tuple:
     return tuple(c(a) for a in args)
 
 
+class _Stamps:
+    """Two readings of the GPU's nanosecond timer taken by one-thread kernels on the current stream."""
+
+    def __init__(self, lib, device):
+        from .. import _native as nv
+
+        self._lib, self._nv = lib, nv
+        self._buf = torch.zeros(2, dtype=torch.int64, device=device)
+
+    def __call__(self, slot: int) -> None:
+        if self._buf is None:
+            return
+        rc = self._lib.pkb_stamp_globaltimer(self._nv.ptr(self._buf[slot:]), self._nv.current_stream())
+        if rc != 0:
+            self._buf = None
+
+    def elapsed_ms(self):
+        if self._buf is None:
+            return None
+        a, b = (int(v) for v in self._buf.tolist())
+        return (b - a) * 1e-6 if a and b and b >= a else None
+
+
+def _stamper(device):
+    """The device-clock cross-check is optional: without the kernel library (or with an older one) timing still works."""
+    try:
+        from .. import _native as nv
+
+        lib = nv.cuda_lib()
+        if not hasattr(lib, "pkb_stamp_globaltimer"):
+            return None
+        return _Stamps(lib, device)
+    except Exception:
+        return None
+
+
 def measure(fn: Callable[..., Any], args: tuple, warmup: int = 500, iters: int = 100, device: torch.device | None = None,
             use_graph: bool = False, max_rotation_bytes: int = 8 << 30) -> dict:
     device = device or next((a.device for a in args if isinstance(a, torch.Tensor)), torch.device("cpu"))
@@ -99,16 +135,24 @@ def measure(fn: Callable[..., Any], args: tuple, warmup: int = 500, iters: int =
         torch.cuda.synchronize()
     for i in range(warmup):
         call(i)
+    device_clock_ms = None
     if cuda:
         torch.cuda.synchronize()
+        stamps = _stamper(device)
         events = [torch.cuda.Event(enable_timing=True) for _ in range(iters + 1)]
+        if stamps is not None:
+            stamps(0)
         events[0].record()
         for i in range(iters):
             call(i)
             events[i + 1].record()
+        if stamps is not None:
+            stamps(1)
         torch.cuda.synchronize()
         per_iter = [float(events[i].elapsed_time(events[i + 1])) for i in range(iters)]
         total = float(events[0].elapsed_time(events[iters]))
+        if stamps is not None:
+            device_clock_ms = stamps.elapsed_ms()
     else:
         per_iter = []
         t_start = time.perf_counter()
@@ -131,4 +175,7 @@ def measure(fn: Callable[..., Any], args: tuple, warmup: int = 500, iters: int =
         "l2_cache_size_bytes": float(l2),
         "timed_tensor_bytes": float(nbytes),
         "cuda_graph": bool(graphs),
+        # the same interval on the GPU's own nanosecond timer (two one-thread stamp kernels around the loop): a cross-check of
+        # the event timing; the two agree to within the launch gaps of the stamps
+        "device_clock_total_ms": device_clock_ms,
     }
