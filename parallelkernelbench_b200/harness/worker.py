@@ -109,9 +109,27 @@ def run_worker(args) -> int:
         compare.save_output(y, args.logs_dir, ctx.rank)
 
         if args.measure_perf:
+            sampler = None
+            if ctx.is_cuda:
+                # clocks and throttle reasons of this rank's GPU while it is being timed (read-only nvidia-smi query)
+                try:
+                    from ..utils.clocks import ClockSampler
+
+                    sampler = ClockSampler(gpu_index=getattr(ctx, "local_rank", ctx.rank), period_ms=100).start()
+                except Exception:
+                    sampler = None
             with torch.no_grad():
                 perf = timing.measure(lambda *a: impl(run, *a), inputs, warmup=args.warmup, iters=args.iters,
                                       device=ctx.device, use_graph=args.graph)
+            if sampler is not None:
+                try:
+                    sampler.stop()
+                    perf["clocks"] = sampler.summary()
+                except Exception:
+                    perf["clocks"] = None
+            from ..utils import env as _env
+
+            perf["git_sha"] = _env.git_sha()
             if spec.cost is not None:
                 perf.update(estimate(spec.cost(cfg, ctx.world), perf["wall_time_ms"]))
             perf.update({"op": spec.name, "impl": args.impl, "world": ctx.world, "rank": ctx.rank, "config": cfg,
