@@ -1,0 +1,107 @@
+"""Host model of the no-barrier (data + epoch in one store) exchange used by the small all-reduce and all-gather.
+
+The device kernels (`coll_allreduce_ll_kernel`, `coll_allgather_ll_kernel`) keep two slot sets that alternate with the parity
+of a per-rank epoch and never wait for a peer except on the words they are about to read. This model runs the same protocol
+with Python threads as ranks - every (data, epoch) pair is one atomic tuple store, ranks are delayed at random between the
+steps - and checks the claim the kernels rest on: a rank can run at most one call ahead of any peer, so two parities are
+enough and no call ever reads a word of another call."""
+import random
+import threading
+import time
+
+
+class _Rank:
+    def __init__(self, world, cap):
+        self.epoch = 0                                                       # header word, advanced at the end of a call
+        self.slots = [[[(0, 0)] * cap for _ in range(world)] for _ in range(2)]     # [parity][source][unit] = (data, epoch)
+
+
+def _all_reduce_call(ranks, me, values, rng, budget_s=20.0):
+    world, mine = len(ranks), ranks[me]
+    epoch = mine.epoch + 1
+    par = epoch & 1
+    for i, w in enumerate(values):                                           # send: my word into slot [par][me] of everyone
+        for g in range(world):
+            ranks[g].slots[par][me][i] = (w, epoch)
+            if rng.random() < 0.02:
+                time.sleep(0)
+    out = []
+    t0 = time.time()
+    for i in range(len(values)):                                             # receive: poll the pairs of every source
+        acc = 0
+        for g in range(world):
+            while True:
+                w, e = mine.slots[par][g][i]
+                if e == epoch:
+                    break
+                assert e < epoch, f"rank {me} call {epoch}: unit {i} of source {g} carries a FUTURE epoch {e}"
+                assert time.time() - t0 < budget_s, "peer never arrived"
+                time.sleep(0)
+            acc += w
+        out.append(acc)
+    mine.epoch = epoch                                                       # the last block advances the epoch
+    return out
+
+
+def _run(world, calls, cap, seed):
+    ranks = [_Rank(world, cap) for _ in range(world)]
+    master = random.Random(seed)
+    sizes = [master.randint(1, cap) for _ in range(calls)]
+    inputs = [[[master.randint(-1000, 1000) for _ in range(sizes[c])] for c in range(calls)] for _ in range(world)]
+    errors, results = [], [[None] * calls for _ in range(world)]
+
+    def body(r):
+        rng = random.Random(seed * 100 + r)
+        try:
+            for c in range(calls):
+                if rng.random() < 0.3:
+                    time.sleep(rng.random() * 0.002)                         # this rank falls behind for a while
+                results[r][c] = _all_reduce_call(ranks, r, inputs[r][c], rng)
+        except BaseException as e:  # noqa: BLE001
+            errors.append(e)
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    assert not errors, errors[0]
+    for c in range(calls):
+        want = [sum(inputs[r][c][i] for r in range(world)) for i in range(sizes[c])]
+        for r in range(world):
+            assert results[r][c] == want, (r, c)
+
+
+def test_two_parities_suffice_for_any_interleaving():
+    for world, seed in ((2, 1), (4, 2), (8, 3)):
+        _run(world, calls=60, cap=24, seed=seed)
+
+
+def test_one_parity_would_not_be_enough():
+    """The same protocol with a single slot set must be caught by the model (a fast rank overwrites words a slow rank has
+    not read yet): this guards the model itself against being vacuous."""
+    world, cap = 2, 4
+    ranks = [_Rank(world, cap) for _ in range(world)]
+    for r in ranks:
+        r.slots[1] = r.slots[0]                                              # both parities alias one buffer
+    # rank 0 completes call 1 only after rank 1 has sent; then it races ahead into call 2 and overwrites its own slot in
+    # rank 1 before rank 1 has read call 1
+    rng = random.Random(0)
+    done = {}
+
+    def fast():
+        done["a1"] = _all_reduce_call(ranks, 0, [1, 2, 3, 4], rng)
+        for g in range(world):                                               # the send phase of call 2
+            for i in range(4):
+                ranks[g].slots[0][0][i] = (100 + i, 2)
+
+    ranks[1].slots[0][1] = [(10 * (i + 1), 1) for i in range(4)]             # rank 1 has sent call 1 to rank 0 ...
+    ranks[0].slots[0][1] = [(10 * (i + 1), 1) for i in range(4)]
+    fast()
+    # ... but only now reads it: the words of rank 0 already belong to call 2
+    try:
+        _all_reduce_call(ranks, 1, [10, 20, 30, 40], rng, budget_s=0.5)
+    except AssertionError as e:
+        assert "FUTURE epoch" in str(e)
+    else:
+        raise AssertionError("the single-buffer variant must fail")
