@@ -105,3 +105,38 @@ def test_one_parity_would_not_be_enough():
         assert "FUTURE epoch" in str(e)
     else:
         raise AssertionError("the single-buffer variant must fail")
+
+
+def test_two_result_buffers_and_one_closing_barrier_are_enough():
+    """Model of the fused GEMV + all-gather (`tp_gemv_allgather_kernel`): every call stores this rank's block into buffer
+    (call & 1) of every rank and ends with one barrier; the caller reads the buffer only after its own call has ended. A rank
+    that races ahead may already be storing call c+1 (other buffer) while a slow rank still reads call c, but it cannot reach
+    call c+2 before the slow rank has passed the barrier of c+1, i.e. has finished reading c."""
+    world, calls = 4, 80
+    bufs = [[[None] * world for _ in range(2)] for _ in range(world)]        # [rank][parity][source block] = call index
+    barrier = threading.Barrier(world)
+    errors = []
+
+    def body(r):
+        rng = random.Random(r)
+        try:
+            for c in range(calls):
+                for g in range(world):
+                    bufs[g][c & 1][r] = c                                    # my block lands in everyone's buffer of this call
+                    if rng.random() < 0.1:
+                        time.sleep(0)
+                barrier.wait(30)                                             # the kernel's closing barrier
+                if rng.random() < 0.3:
+                    time.sleep(rng.random() * 0.002)                         # the consumer is slow to read
+                got = list(bufs[r][c & 1])
+                assert got == [c] * world, f"rank {r} call {c} read {got}"
+        except BaseException as e:  # noqa: BLE001
+            errors.append(e)
+            barrier.abort()
+
+    threads = [threading.Thread(target=body, args=(r,)) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    assert not errors, errors[0]
