@@ -31,7 +31,10 @@
 // (reference: reference/15_combined_sharded_gemms.py:17-31, reference/16_gemm_reducescatter.py:19-22,
 //  reference/45_reducescatter_fused_rmsnorm.py:23-29, reference/13_gemm_allreduce.py:17-20, reference/14_gemm_allgather.py:17-22,
 //  reference/46_gemv_decode.py:13-18).
+#include <stdlib.h>
+
 #include "pkb/api.h"
+#include "pkb/bulk_copy.cuh"
 #include "pkb/collectives_api.h"
 #include "pkb/gemm_umma2.cuh"
 #include "pkb/host.h"
@@ -49,11 +52,20 @@ struct TpAgArgs {
   uint32_t epoch;
   int local_in_place;      // x_local already is the local slice of the gather buffer
   int comm_ctas;
+  int bulk_push;           // 1: sub-blocks travel as 16 KiB TMA bulk requests through a shared-memory ring (one issuing thread)
 };
 
 __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
   const SymmCtx& c = a.ctx;
   // every rank has entered this call, so every rank has finished reading the previous gather
+  // bulk form: a communication CTA does no GEMM work, so the kernel's dynamic shared memory is free for the copy ring
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ int s_bulk_abort;
+  BulkRing ring;
+  if (a.bulk_push && threadIdx.x == 0) {
+    s_bulk_abort = 0;
+    bulk_ring_init(ring, (smem_u32(smem_raw) + 127u) & ~127u);
+  }
   if (!symm_block_barrier(c, 300, 1)) return;
   const int W = c.gsize;
   const int total_items = W * a.sub_per_shard;
@@ -65,7 +77,15 @@ __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
     if (dest_g < 0) dest_g += W;
     const int dest = c.members[dest_g];
     const int chunk = c.grank * a.sub_per_shard + sb;
-    {
+    if (a.bulk_push) {
+      if (threadIdx.x == 0) {
+        const uint8_t* src = a.x_local + (long long)sb * a.sub_bytes;
+        uint8_t* dst = symm_ptr<uint8_t>(c, dest, a.gather_off) + (long long)chunk * a.sub_bytes;
+        if (!bulk_copy(ring, dst, src, a.sub_bytes, &s_bulk_abort, c.budget_ns))
+          record_status(c.status, kStatusMbarTimeout, 300, c.rank, dest, 3, item);
+        fence_proxy_async_all();
+      }
+    } else {
       const uint8_t* src = a.x_local + (long long)sb * a.sub_bytes;
       uint8_t* dst = symm_ptr<uint8_t>(c, dest, a.gather_off) + (long long)chunk * a.sub_bytes;
       const long long nvec = a.sub_bytes >> 4;
@@ -437,6 +457,9 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");
   a.comm_ctas = comm_ctas;
+  // PKB_TP_BULK_PUSH=1: push with TMA bulk requests instead of 16-byte stores (off by default)
+  static const bool bulk_push = [] { const char* e = getenv("PKB_TP_BULK_PUSH"); return e != nullptr && e[0] == '1'; }();
+  a.bulk_push = (bulk_push && a.sub_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0) ? 1 : 0;
 
   constexpr int smem = kGemm2SmemTotal;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
