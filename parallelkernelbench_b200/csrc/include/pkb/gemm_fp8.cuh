@@ -274,12 +274,15 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) +
                                static_cast<uint32_t>(pb * BN + half * 128);
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t r[16];
-          tmem_ld_32x16(taddr + c * 16, r);
+        for (int c = 0; c < 8; c += 2) {
+          uint32_t r0[16], r1[16];      // two reads in flight per wait
+          tmem_ld_32x16(taddr + c * 16, r0);
+          tmem_ld_32x16(taddr + c * 16 + 16, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(s, __uint_as_float(r[j]), acc[c * 16 + j]);
+          for (int j = 0; j < 16; ++j) acc[c * 16 + j] = fmaf(s, __uint_as_float(r0[j]), acc[c * 16 + j]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[c * 16 + 16 + j] = fmaf(s, __uint_as_float(r1[j]), acc[c * 16 + 16 + j]);
         }
         tc_fence_before_sync();
         __syncwarp();
