@@ -46,9 +46,24 @@ def build_prompt(op: str, hardware: str = "b200_8", nproc: int = 8, feedback: st
              "## Named shape configurations", "\n".join(f"- {k}: {v}" for k, v in spec.configs.items()),
              "## Input factory", _source(spec.make_inputs), "## Reference implementation (PyTorch + process group)",
              _source(spec.reference)]
+    parts += ["## Worked examples (reference next to a solution file that passes the evaluation)", _examples_section(spec.name)]
     if feedback:
         parts += ["## Result of your previous attempt", feedback]
     return "\n\n".join(p for p in parts if p)
+
+
+def _examples_section(current_op: str) -> str:
+    """Reference/solution pairs of a few ops (the pair of the op being asked for is left out: it would be the answer)."""
+    from ..workloads import registry
+    from .examples import EXAMPLES, example_source
+
+    out = []
+    for op in EXAMPLES:
+        if op == current_op:
+            continue
+        spec = registry.get(op)
+        out.append(f"### `{op}`: reference\n{_source(spec.reference)}\n### `{op}`: solution file\n```python\n{example_source(op).rstrip()}\n```")
+    return "\n\n".join(out)
 
 
 def _source(fn) -> str:

@@ -24,3 +24,19 @@ def test_loop_stops_at_first_matching_candidate(tmp_path):
     assert out["solved"] and len(out["attempts"]) == 2
     assert not out["attempts"][0]["all_ok"] and "verdict" in out["attempts"][0]["feedback"]
     assert os.path.isfile(out["attempts"][1]["path"])
+
+
+def test_worked_examples_are_in_the_prompt_and_pass_the_evaluation():
+    """Every example file is a solution that matches its op's reference (2 CPU ranks), and the prompt of another op shows
+    the pairs while the prompt of the same op does not give its own answer away."""
+    from parallelkernelbench_b200.harness import launch
+    from parallelkernelbench_b200.kernelgen import build_prompt
+    from parallelkernelbench_b200.kernelgen.examples import EXAMPLES, example_path
+
+    p = build_prompt("allgather")
+    assert "Worked examples" in p and "rc.comm.all_reduce(x)" in p and "all_to_all" in p
+    assert "allreduce_symmetric_heap" not in build_prompt("allreduce") and "Example solution for the op `allreduce`" not in build_prompt("allreduce")
+    for op in EXAMPLES:
+        s = launch.eval_op(op, 2, trials=1, backend="gloo", dtype="float32", config="small", solution=str(example_path(op)),
+                           timeout_s=300)
+        assert s["all_ok"], (op, s["trials"][-1].get("result"))
