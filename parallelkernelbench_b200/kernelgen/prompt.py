@@ -35,7 +35,36 @@ CONTRACT = textwrap.dedent("""\
     the fewest bytes over NVLink.""")
 
 
-def build_prompt(op: str, hardware: str = "b200_8", nproc: int = 8, feedback: str | None = None) -> str:
+PRECISION_NOTES = {
+    "bfloat16": "Inputs and outputs are bf16. Accumulate matrix products, reductions and normalisation statistics in fp32 and "
+                "round once at the end; a sum over ranks must not depend on the order in which peers arrive.",
+    "float32": "Inputs and outputs are fp32 (the CPU plumbing configuration): keep every reduction in fp32.",
+}
+
+
+def select_ops(selector: str) -> list[str]:
+    """``"all"``, one op name or reference problem number, or a comma-separated / bracketed list of them
+    (``"13"``, ``"allreduce,13"``, ``"[1, 8, 13]"``) -> op names in registry order, without duplicates
+    (reference: kernelgen/generate_kernel.py:203-232 takes ``--problem all | [a,b] | id``)."""
+    from ..workloads import registry
+
+    sel = selector.strip()
+    if sel == "all":
+        return [s.name for s in registry.all_ops()]
+    names = []
+    for item in sel.strip("[]").split(","):
+        item = item.strip()
+        if item:
+            name = registry.get(item).name
+            if name not in names:
+                names.append(name)
+    if not names:
+        raise ValueError(f"no op selected by {selector!r}")
+    return names
+
+
+def build_prompt(op: str, hardware: str = "b200_8", nproc: int = 8, feedback: str | None = None,
+                 precision: str | None = None) -> str:
     from ..workloads import registry
 
     spec = registry.get(op)
@@ -43,6 +72,7 @@ def build_prompt(op: str, hardware: str = "b200_8", nproc: int = 8, feedback: st
              + (f" (reference problems {', '.join(map(str, spec.problem_ids))})" if spec.problem_ids else ""),
              spec.doc or "", "## Hardware", HARDWARE_PROFILES[hardware],
              "## Contract", CONTRACT.format(op=spec.name, nproc=nproc, atol=spec.atol, rtol=spec.rtol),
+             "## Precision", PRECISION_NOTES.get(precision or "", ""),
              "## Named shape configurations", "\n".join(f"- {k}: {v}" for k, v in spec.configs.items()),
              "## Input factory", _source(spec.make_inputs), "## Reference implementation (PyTorch + process group)",
              _source(spec.reference)]

@@ -40,3 +40,16 @@ def test_worked_examples_are_in_the_prompt_and_pass_the_evaluation():
         s = launch.eval_op(op, 2, trials=1, backend="gloo", dtype="float32", config="small", solution=str(example_path(op)),
                            timeout_s=300)
         assert s["all_ok"], (op, s["trials"][-1].get("result"))
+
+
+def test_prompt_cli_selects_ops_by_name_number_list_and_all(tmp_path):
+    from parallelkernelbench_b200.kernelgen.__main__ import main
+    from parallelkernelbench_b200.kernelgen.prompt import build_prompt, select_ops
+    from parallelkernelbench_b200.workloads import registry
+
+    assert select_ops("13") == ["gemm_allreduce"] and select_ops("[1, allreduce, 8]") == ["allreduce", "alltoall"]
+    assert len(select_ops("all")) == len(registry.all_ops())
+    assert "fp32 and round once" in build_prompt("allreduce", precision="bfloat16").replace("\n", " ")
+    assert main(["prompt", "--op", "1,13", "--out-dir", str(tmp_path)]) == 0
+    assert sorted(p.name for p in tmp_path.iterdir()) == ["prompt_allreduce.md", "prompt_gemm_allreduce.md"]
+    assert "def solution(rc, *inputs)" in (tmp_path / "prompt_allreduce.md").read_text()
