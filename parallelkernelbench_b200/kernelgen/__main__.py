@@ -1,11 +1,12 @@
-"""python -m parallelkernelbench_b200.kernelgen prompt --op OP|13|all|[a,b] [--out-dir DIR] | replay --op OP --candidates DIR"""
+"""python -m parallelkernelbench_b200.kernelgen prompt --op OP|13|all|[a,b] [--out-dir DIR] | replay --op OP --candidates DIR |
+generate --op OP --command "CMD" (CMD reads the prompt on stdin and prints a candidate)"""
 import argparse
 import json
 import sys
 
 import os
 
-from . import ReplayProposer, build_prompt, optimise
+from . import CommandProposer, ReplayProposer, build_prompt, optimise
 from .prompt import select_ops
 
 
@@ -26,6 +27,15 @@ def main(argv=None) -> int:
     r.add_argument("--backend", default=None)
     r.add_argument("--dtype", default="bfloat16")
     r.add_argument("--config", default="default")
+    g = sub.add_parser("generate", help="run the loop with a command that reads the prompt on stdin and prints a candidate")
+    g.add_argument("--op", required=True)
+    g.add_argument("--command", required=True, help="e.g. 'python my_model_runner.py' (prompt on stdin, reply on stdout)")
+    g.add_argument("--workdir", default="logs/kernelgen")
+    g.add_argument("--nproc", type=int, default=2)
+    g.add_argument("--max-iters", type=int, default=4)
+    g.add_argument("--backend", default=None)
+    g.add_argument("--dtype", default="bfloat16")
+    g.add_argument("--config", default="default")
     a = ap.parse_args(argv)
     if a.cmd == "prompt":
         ops = select_ops(a.op)
@@ -43,6 +53,14 @@ def main(argv=None) -> int:
                     print(f"\n<!-- ===== {op} ===== -->")
                 print(text)
         return 0
+    if a.cmd == "generate":
+        rc = 0
+        for op in select_ops(a.op):
+            out = optimise(op, CommandProposer(a.command, log_dir=os.path.join(a.workdir, f"{op}_exchanges")), a.workdir,
+                           nproc=a.nproc, max_iters=a.max_iters, backend=a.backend, dtype=a.dtype, config=a.config)
+            print(json.dumps(out, indent=1))
+            rc = rc or (0 if out["solved"] else 1)
+        return rc
     out = optimise(a.op, ReplayProposer(a.candidates), a.workdir, nproc=a.nproc, backend=a.backend, dtype=a.dtype, config=a.config)
     print(json.dumps(out, indent=1))
     return 0 if out["solved"] else 1

@@ -53,3 +53,28 @@ def test_prompt_cli_selects_ops_by_name_number_list_and_all(tmp_path):
     assert main(["prompt", "--op", "1,13", "--out-dir", str(tmp_path)]) == 0
     assert sorted(p.name for p in tmp_path.iterdir()) == ["prompt_allreduce.md", "prompt_gemm_allreduce.md"]
     assert "def solution(rc, *inputs)" in (tmp_path / "prompt_allreduce.md").read_text()
+
+
+def test_command_proposer_extracts_code_and_loop_records_the_run(tmp_path):
+    """A stand-in "model" (a script that prints prose with a fenced block) drives the loop through CommandProposer."""
+    import json
+    import sys
+
+    from parallelkernelbench_b200.kernelgen import CommandProposer, extract_code, optimise
+
+    assert extract_code("text\n```python\nx = 1\n```\nmore\n```python\ny = 2\n```") == "x = 1\n"
+    assert extract_code("```\nz = 3\n```") == "z = 3\n" and extract_code("w = 4") == "w = 4\n"
+    model = tmp_path / "model.py"
+    model.write_text("import sys\nprompt = sys.stdin.read()\nassert 'def solution(rc, *inputs)' in prompt\n"
+                     "print('Here is my answer:\\n```python\\ndef solution(rc, x):\\n    return rc.comm.all_reduce(x)\\n```')\n")
+    work = tmp_path / "work"
+    out = optimise("allreduce", CommandProposer([sys.executable, str(model)], log_dir=str(work / "ex")), str(work), nproc=2, max_iters=2,
+                   backend="gloo", dtype="float32", config="small", timeout_s=300)
+    assert out["solved"] and len(out["attempts"]) == 1
+    rec = json.loads((work / "allreduce_run.json").read_text())
+    assert rec["solved"] and rec["op"] == "allreduce"
+    ex = json.loads((work / "ex" / "exchange_0.json").read_text())
+    assert "Here is my answer" in ex["reply"] and ex["returncode"] == 0
+    failing = CommandProposer([sys.executable, "-c", "import sys; sys.exit(3)"])
+    out = optimise("allreduce", failing, str(tmp_path / "w2"), nproc=2, max_iters=2, backend="gloo", dtype="float32", config="small")
+    assert not out["solved"] and out["attempts"] == []
