@@ -14,6 +14,7 @@ EXAMPLES = {
     "allreduce": "allreduce_symmetric_heap.py",
     "alltoall": "alltoall_symmetric_heap.py",
     "gemm_allreduce": "gemm_allreduce_two_kernels.py",
+    "tp_rmsnorm": "tp_rmsnorm_own_kernel.py",
 }
 
 

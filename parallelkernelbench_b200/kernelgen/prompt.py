@@ -28,6 +28,10 @@ CONTRACT = textwrap.dedent("""\
     Kernels of this package: ops.gemm_bf16 (a @ w.T on tcgen05), ops.gemm_bf16_kn, ops.gemm_bf16_tn, ops.rmsnorm,
     ops.rope, ops.fp8_quantize_1x128 / fp8_dequantize_1x128, ops.attention.flash_attn_fwd / flash_attn_bwd /
     RingAttention, ops.tp.AllGatherGemm / GemmReduceScatterRMSNorm, ops.moe.MoEExchange / grouped_gemm.
+    Your own CUDA kernel: utils.cuda_ext.compile_cuda_module(source_text, name) builds it for sm_100a (the package's device
+    headers pkb/ptx.cuh - mbarrier, TMA, tcgen05, bounded waits - and pkb/symm.cuh - symmetric-heap view, cross-GPU barriers -
+    are on the include path) and returns a ctypes library; call its extern "C" functions with tensor.data_ptr() and
+    torch.cuda.current_stream().cuda_stream. Every device-side wait must be bounded; never trap or spin without a limit.
     The file is evaluated with
         python -m parallelkernelbench_b200.harness.launch eval --op {op} --nproc {nproc} --solution your_file.py --measure-perf
     which compares every rank's output with the reference within atol={atol}, rtol={rtol} over seeded trials and reports

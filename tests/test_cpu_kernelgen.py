@@ -36,6 +36,12 @@ def test_worked_examples_are_in_the_prompt_and_pass_the_evaluation():
     p = build_prompt("allgather")
     assert "Worked examples" in p and "rc.comm.all_reduce(x)" in p and "all_to_all" in p
     assert "allreduce_symmetric_heap" not in build_prompt("allreduce") and "Example solution for the op `allreduce`" not in build_prompt("allreduce")
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("example_own_kernel", example_path("tp_rmsnorm"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    assert hasattr(mod._kernels(), "ex_row_scale")            # the example's CUDA source builds for sm_100a without a GPU
     for op in EXAMPLES:
         s = launch.eval_op(op, 2, trials=1, backend="gloo", dtype="float32", config="small", solution=str(example_path(op)),
                            timeout_s=300)
