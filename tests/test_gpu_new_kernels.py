@@ -207,3 +207,12 @@ def test_speculative_single_pass_softmax_is_bit_identical_to_the_two_pass_form(t
                         "matches_reference or zigzag_rank"], cwd=root, capture_output=True, text=True, timeout=900,
                        env={**os.environ, "PKB_FA_SPEC": "1"})
     assert r.returncode == 0, r.stdout[-3000:]
+
+
+def test_own_kernel_example_solution_matches_on_gpu():
+    """The worked example that compiles its own CUDA kernels at first use, evaluated like any candidate file."""
+    from parallelkernelbench_b200.harness import launch
+    from parallelkernelbench_b200.kernelgen.examples import example_path
+
+    s = launch.eval_op("tp_rmsnorm", 1, trials=1, solution=str(example_path("tp_rmsnorm")), timeout_s=600)
+    assert s["all_ok"], s["trials"][-1]
