@@ -265,19 +265,27 @@ def cmd_sweep(a) -> int:
                     pass
     rc = 0
     for op in ops:
+        solution = None
+        if a.solutions_dir:
+            # a directory of candidate files named after the ops (<op>.py): ops without a file are left out
+            solution = os.path.join(a.solutions_dir, f"{registry.get(op).name}.py")
+            if not os.path.isfile(solution):
+                print(f"skip {op} (no {solution})")
+                continue
         for w in worlds:
             if (op, w, a.config) in done:
                 print(f"skip {op} w={w} (already in {ledger})")
                 continue
             s = eval_op(op, w, trials=a.trials, measure_perf=a.measure_perf, config=a.config, backend=a.backend,
-                        dtype=a.dtype, warmup=a.warmup, iters=a.iters, timeout_s=a.timeout)
+                        dtype=a.dtype, warmup=a.warmup, iters=a.iters, timeout_s=a.timeout, solution=solution)
             last = s["trials"][-1] if s["trials"] else {}
             cell = {"op": op, "world": w, "config": a.config, "all_ok": s["all_ok"], "git_sha": s["git_sha"],
                     "result": last.get("result"), "speedup": last.get("speedup"),
                     "ref_ms": (last.get("reference_perf") or {}).get("wall_time_ms_max"),
                     "ours_ms": (last.get("ours_perf") or {}).get("wall_time_ms_max"),
                     "pct_of_roofline": (last.get("ours_perf") or {}).get("pct_of_roofline"),
-                    "limiter": (last.get("ours_perf") or {}).get("limiter"), "time": time.time()}
+                    "limiter": (last.get("ours_perf") or {}).get("limiter"), "time": time.time(),
+                    "solution": solution}
             with open(ledger, "a") as fh:
                 fh.write(json.dumps(cell) + "\n")
             rc = rc or (0 if s["all_ok"] else 1)
@@ -355,6 +363,7 @@ def main(argv=None) -> int:
     sp.add_argument("--ledger", default=None)
     sp.add_argument("--resume", action="store_true")
     sp.add_argument("--any-sha", action="store_true", help="with --resume: accept cells recorded at another commit")
+    sp.add_argument("--solutions-dir", default=None, help="evaluate DIR/<op>.py instead of the built-in implementation; ops without a file are skipped")
     sp.set_defaults(fn=cmd_sweep)
     sp = sub.add_parser("report")
     sp.add_argument("--ledger", default=None)

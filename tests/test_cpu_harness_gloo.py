@@ -118,3 +118,12 @@ def test_list_sweep_resume_inspect_and_perf_diff(tmp_path):
     assert r.returncode == 0 and "verdict: match" in r.stdout
     r, _ = _launch("perf-diff", "--op", "allreduce")
     assert r.returncode == 0 and "speed" in r.stdout.lower()
+    sol_dir = tmp_path / "solutions"
+    sol_dir.mkdir()
+    (sol_dir / "allreduce.py").write_text("def solution(rc, x):\n    return rc.comm.all_reduce(x)\n")
+    ledger2 = str(tmp_path / "results_candidates.jsonl")
+    r, _ = _launch("sweep", "--ops", "allreduce,allgather", "--worlds", "2", "--config", "small", "--backend", "gloo", "--dtype", "float32",
+                   "--trials", "1", "--ledger", ledger2, "--solutions-dir", str(sol_dir))
+    assert r.returncode == 0 and "skip allgather (no " in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
+    cells2 = [json.loads(ln) for ln in open(ledger2)]
+    assert len(cells2) == 1 and cells2[0]["op"] == "allreduce" and cells2[0]["all_ok"] and cells2[0]["solution"].endswith("allreduce.py")
