@@ -5,7 +5,7 @@
 Each case allocates a few hundred MB at most (inputs larger than L2 where DRAM figures matter),
 launches the kernel a handful of times and exits, so a capture of one launch ends by itself.
 Cases: gemm_pair, gemm_single, tp_mlp, fa_fwd, fa_fwd_d64, fa_bwd, grouped_gemm, grouped_gemm_fp8, rmsnorm, allreduce,
-fsdp_adamw, moe_exchange, gsplat, delta_scan.
+fsdp_adamw, moe_exchange, gsplat, delta_scan, llama_step.
 """
 from __future__ import annotations
 
@@ -187,6 +187,24 @@ def case_delta_scan(iters):
     v, decay, beta = torch.randn(BH, T, V, device="cuda"), torch.rand(BH, T, K, device="cuda") * 0.1 + 0.9, torch.rand(BH, T, device="cuda")
     for _ in range(iters):
         delta_rule_scan(q, k, v, decay, beta)
+
+
+def case_llama_step(iters):
+    """One decoder layer at Llama-8B width (hidden 4096, ffn 14336, 32/8 heads) with a 16k vocabulary, sequence 4096: the
+    launch list of a full training step (gather, forward, backward, fp8 gradient exchange, AdamW) at about 5 GB."""
+    from ..models.llama import FSDPLlama, LlamaConfig
+    from ..parallel import init_context
+
+    ctx = init_context()
+    cfg = LlamaConfig(layers=1, vocab=16384)
+    model = FSDPLlama(ctx, cfg, impl="ours")
+    g = torch.Generator(device=ctx.device).manual_seed(5)
+    tok = torch.randint(0, cfg.vocab, (cfg.seq,), device=ctx.device, generator=g)
+    tgt = torch.randint(0, cfg.vocab, (cfg.seq,), device=ctx.device, generator=g)
+    for _ in range(iters):
+        model.step(tok, tgt)
+    torch.cuda.synchronize()
+    ctx.finalize()
 
 
 def main(argv=None) -> int:
