@@ -110,8 +110,9 @@ def run_worker(args) -> int:
 
         if args.measure_perf:
             sampler = None
-            if ctx.is_cuda:
-                # clocks and throttle reasons of this rank's GPU while it is being timed (read-only nvidia-smi query)
+            if ctx.is_cuda and getattr(ctx, "local_rank", ctx.rank) == 0:
+                # clocks and throttle reasons of the first GPU while it is being timed (read-only nvidia-smi query; one sampler per
+                # job, not one per rank, so the query itself stays out of the measurement)
                 try:
                     from ..utils.clocks import ClockSampler
 
