@@ -214,3 +214,32 @@ def test_fsdp_llama_sharded_checkpoint_round_trip_on_cpu():
     assert la[0] == lb0 and la[1] == lc1 and a.steps == c.steps == 2
     assert torch.equal(a.units[1].master, c.units[1].master) and torch.equal(a.head_master, c.head_master)
     assert torch.equal(a.embed.m, c.embed.m)
+
+
+def test_push_combine_index_plan_reproduces_the_direct_sum():
+    """Index logic of the MoE way home when the down GEMM's epilogue pushes rows: the dispatch delivers (sender, assignment
+    index) with every row, the expert rank stores output row r at row `assignment index` of the sender's buffer, and the
+    sender sums gates[t, j] * home[t * k + j]. Emulated with plain tensors for W ranks against the direct per-token sum."""
+    torch.manual_seed(5)
+    W, T, k, E, H = 3, 10, 2, 6, 4
+    el = E // W
+    f = lambda e, x: x * (e + 1) + 0.5 * e                                   # "expert e" as a cheap function of the row  # noqa: E731
+    xs = [torch.randn(T, H) for _ in range(W)]
+    idx = [torch.stack([torch.randperm(E)[:k] for _ in range(T)]) for _ in range(W)]
+    gates = [torch.rand(T, k) for _ in range(W)]
+    # dispatch: every rank appends its rows to the receive buffer of the expert's owner, expert-major, with the metadata
+    recv = [[[] for _ in range(el)] for _ in range(W)]
+    for s in range(W):
+        for i in range(T * k):
+            t, e = i // k, int(idx[s].view(-1)[i])
+            recv[e // el][e % el].append((xs[s][t], s, i))
+    home = [torch.full((T * k, H), float("nan")) for _ in range(W)]
+    for r in range(W):                                                       # grouped GEMM with the row-scatter epilogue
+        for le in range(el):
+            for row, src, i in recv[r][le]:
+                home[src][i] = f(r * el + le, row)
+    for s in range(W):                                                       # local combine
+        out = (gates[s].view(-1, 1) * home[s]).view(T, k, H).sum(1)
+        want = torch.stack([sum(gates[s][t, j] * f(int(idx[s][t, j]), xs[s][t]) for j in range(k)) for t in range(T)])
+        torch.testing.assert_close(out, want)
+        assert not torch.isnan(home[s]).any()                                # every assignment came home exactly once
