@@ -7,6 +7,7 @@ sizes, list the registry, and inspect stored results.
     python -m parallelkernelbench_b200.harness.launch eval  --op plumbing --nproc 2 --backend gloo --atol 1e-5 --rtol 1e-5
     python -m parallelkernelbench_b200.harness.launch sweep --ops allreduce,allgather --worlds 1,2,4,8 --resume
     python -m parallelkernelbench_b200.harness.launch report --format markdown      # the sweep ledger as a table
+    python -m parallelkernelbench_b200.harness.launch headline --nproc 8            # the headline configurations, timed
     python -m parallelkernelbench_b200.harness.launch inspect --op allreduce
     python -m parallelkernelbench_b200.harness.launch perf-diff --op allreduce
 
@@ -292,6 +293,43 @@ def cmd_sweep(a) -> int:
     return rc
 
 
+# The configurations the published comparison is made on: (label, op, named config). The FSDP Llama step is an engine, not
+# an op of the registry; its worker prints the same kind of line (see the hint printed at the end).
+HEADLINE = (("1 plumbing AR->AG->RS", "plumbing", "default"),
+            ("2 TP MLP block", "tp_mlp", "default"),
+            ("3 EP MoE 256 experts top-8", "moe_layer", "deepseek"),
+            ("4 CP ring attention fwd+bwd 131072 zigzag", "ring_attention_fwd_bwd", "cp131k"))
+
+
+def cmd_headline(a) -> int:
+    """Evaluate and time the headline configurations at one world size and print them as a markdown table; every cell also
+    goes to the ledger, so `report` can fold several world sizes into one table later."""
+    ledger = a.ledger or os.path.join(LOGS_ROOT, "headline.jsonl")
+    os.makedirs(os.path.dirname(ledger) or ".", exist_ok=True)
+    only = {x.strip() for x in a.only.split(",")} if a.only else None
+    rows, rc = [], 0
+    for label, op, config in HEADLINE:
+        if only and label.split()[0] not in only:
+            continue
+        s = eval_op(op, a.nproc, trials=1, measure_perf=True, config=config, backend=a.backend, dtype=a.dtype, warmup=a.warmup,
+                    iters=a.iters, timeout_s=a.timeout)
+        last = s["trials"][-1] if s["trials"] else {}
+        cell = {"op": op, "world": a.nproc, "config": config, "all_ok": s["all_ok"], "git_sha": s["git_sha"], "label": label,
+                "result": last.get("result"), "speedup": last.get("speedup"),
+                "ref_ms": (last.get("reference_perf") or {}).get("wall_time_ms_max"),
+                "ours_ms": (last.get("ours_perf") or {}).get("wall_time_ms_max"),
+                "pct_of_roofline": (last.get("ours_perf") or {}).get("pct_of_roofline"),
+                "limiter": (last.get("ours_perf") or {}).get("limiter"), "time": time.time()}
+        with open(ledger, "a") as fh:
+            fh.write(json.dumps(cell) + "\n")
+        rows.append(cell)
+        rc = rc or (0 if s["all_ok"] else 1)
+    sys.stdout.write(report.ledger_table(rows, "markdown"))
+    print("5 FSDP Llama step: python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 "
+          "tests/mp/llama_worker.py --full")
+    return rc
+
+
 def cmd_report(a) -> int:
     """Print the sweep ledger as a markdown table or CSV."""
     ledger = a.ledger or os.path.join(LOGS_ROOT, "results.jsonl")
@@ -365,6 +403,16 @@ def main(argv=None) -> int:
     sp.add_argument("--any-sha", action="store_true", help="with --resume: accept cells recorded at another commit")
     sp.add_argument("--solutions-dir", default=None, help="evaluate DIR/<op>.py instead of the built-in implementation; ops without a file are skipped")
     sp.set_defaults(fn=cmd_sweep)
+    sp = sub.add_parser("headline")
+    sp.add_argument("--nproc", "--nproc-per-node", dest="nproc", type=int, default=1)
+    sp.add_argument("--only", default=None, help="comma-separated configuration numbers, e.g. 2,3")
+    sp.add_argument("--dtype", default="bfloat16")
+    sp.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
+    sp.add_argument("--warmup", type=int, default=500)
+    sp.add_argument("--iters", type=int, default=100)
+    sp.add_argument("--timeout", type=float, default=3600.0)
+    sp.add_argument("--ledger", default=None)
+    sp.set_defaults(fn=cmd_headline)
     sp = sub.add_parser("report")
     sp.add_argument("--ledger", default=None)
     sp.add_argument("--format", default="markdown", choices=["markdown", "csv"])

@@ -127,3 +127,13 @@ def test_list_sweep_resume_inspect_and_perf_diff(tmp_path):
     assert r.returncode == 0 and "skip allgather (no " in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]
     cells2 = [json.loads(ln) for ln in open(ledger2)]
     assert len(cells2) == 1 and cells2[0]["op"] == "allreduce" and cells2[0]["all_ok"] and cells2[0]["solution"].endswith("allreduce.py")
+
+
+def test_headline_verb_runs_the_plumbing_configuration_on_cpu(tmp_path):
+    ledger = str(tmp_path / "headline.jsonl")
+    r, _ = _launch("headline", "--only", "1", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--warmup", "2", "--iters", "3",
+                   "--ledger", ledger)
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "| plumbing | default | 2 | match |" in r.stdout and "1 of 1 cells match" in r.stdout and "llama_worker.py --full" in r.stdout
+    cell = json.loads(open(ledger).readline())
+    assert cell["label"].startswith("1 ") and cell["ours_ms"] > 0
