@@ -14,9 +14,27 @@ import shutil
 import subprocess
 
 
-def clean_shared_segments(prefix: str = "pkb200_") -> list[str]:
+def _owner_alive(path: str, prefix: str) -> bool:
+    """Segments are named ``<prefix><pid of the creating rank>_<port>``: the owner is alive if that process exists."""
+    try:
+        pid = int(os.path.basename(path)[len(prefix):].split("_")[0])
+    except ValueError:
+        return False                      # not our naming scheme any more: a leftover of an older version
+    try:
+        os.kill(pid, 0)                   # signal 0: existence check only
+    except ProcessLookupError:
+        return False
+    except PermissionError:
+        return True
+    return True
+
+
+def clean_shared_segments(prefix: str = "pkb200_", directory: str = "/dev/shm") -> list[str]:
+    """Remove shared-memory segments whose creating process is gone (a job that runs next to this one keeps its heap)."""
     removed = []
-    for p in glob.glob(f"/dev/shm/{prefix}*"):
+    for p in glob.glob(os.path.join(directory, f"{prefix}*")):
+        if _owner_alive(p, prefix):
+            continue
         try:
             os.unlink(p)
             removed.append(p)

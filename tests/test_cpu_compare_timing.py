@@ -94,3 +94,21 @@ def test_clock_csv_summary(tmp_path):
                  "0, 1365, 1965, 985.0, 0x4, Not Active, Not Active, Not Active, Active\n")
     s = clocks.summarize_clock_rows(clocks.parse_clock_csv(str(p)))
     assert s["sm_max_mhz"] == 1965 and 1350 <= s["sm_mhz"] <= 1365 and s["reasons"] == ["sw_power_cap"]
+
+
+def test_hygiene_removes_only_segments_of_dead_owners(tmp_path):
+    import os
+    import subprocess
+    import sys
+
+    from parallelkernelbench_b200.harness import hygiene
+
+    child = subprocess.Popen([sys.executable, "-c", "pass"])
+    child.wait()                                                     # a pid that no longer exists
+    mine, dead, odd = tmp_path / f"pkb200_{os.getpid()}_29500", tmp_path / f"pkb200_{child.pid}_29501", tmp_path / "pkb200_legacy"
+    for f in (mine, dead, odd):
+        f.write_bytes(b"x")
+    removed = hygiene.clean_shared_segments(directory=str(tmp_path))
+    assert sorted(os.path.basename(p) for p in removed) == sorted([dead.name, odd.name])
+    assert mine.exists() and not dead.exists()
+    assert set(hygiene.gpu_health()) >= {"ok", "gpus", "detail"}
