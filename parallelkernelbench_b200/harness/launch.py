@@ -220,8 +220,13 @@ def cmd_run(a) -> int:
 
     job = run_job(registry.get(a.op).name, a.impl, a.nproc, trial=a.trial, config=a.config,
                   overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, measure_perf=a.measure_perf,
-                  warmup=a.warmup, iters=a.iters, graph=a.graph, profile=a.profile, timeout_s=a.timeout)
+                  warmup=a.warmup, iters=a.iters, graph=a.graph, profile=a.profile, timeout_s=a.timeout,
+                  extra_worker_args=["--determinism", str(a.determinism)] if a.determinism > 0 else None)
     ok = job["returncode"] == 0 and job["artifact_count"] == a.nproc
+    if a.determinism > 0:
+        for line in job["stdout"].splitlines():
+            if "determinism:" in line:
+                print(line)
     if ok:
         perf = report.summarize_perf(job["job_dir"])
         _keep(job, a.nproc)
@@ -381,6 +386,8 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="verb", required=True)
     sub.add_parser("list").set_defaults(fn=cmd_list)
     sp = sub.add_parser("run"); _common(sp, need_impl=True); sp.set_defaults(fn=cmd_run)
+    sp.add_argument("--determinism", type=int, default=0, metavar="N",
+                    help="repeat the run N times on identical inputs and require bit-identical outputs (exit 1 otherwise)")
     sp = sub.add_parser("eval"); _common(sp)
     sp.add_argument("--trials", type=int, default=5)
     sp.add_argument("--solution", default=None, help="evaluate this file's solution(rc, *inputs) instead of the built-in implementation")

@@ -39,6 +39,8 @@ def parse_args(argv=None):
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays of the op")
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--determinism", type=int, default=0, metavar="N",
+                    help="run the implementation N more times on identical inputs and require bit-identical outputs (a cheap race detector)")
     ap.add_argument("--fail-rank", type=int, default=-1, help="test hook: this rank raises before the first collective")
     ap.add_argument("--exit-rank", type=int, default=-1, help="test hook: this rank exits non-zero before the first collective")
     return ap.parse_args(argv)
@@ -59,6 +61,25 @@ def load_solution(path: str):
     if not callable(fn):
         raise AttributeError(f"{path} does not define a callable `solution(rc, *inputs)`")
     return fn
+
+
+def _bit_identical(a, b) -> bool:
+    """Recursive bitwise comparison of outputs (tensors, tuples / lists, dicts, plain values); NaNs compare by their bits."""
+    import torch
+
+    if isinstance(a, torch.Tensor):
+        if not isinstance(b, torch.Tensor) or a.shape != b.shape or a.dtype != b.dtype:
+            return False
+        if a.numel() == 0:
+            return True
+        ab, bb = a.detach().contiguous().cpu(), b.detach().contiguous().cpu()
+        return bool(torch.equal(ab.view(torch.uint8).reshape(-1) if ab.dtype != torch.bool else ab,
+                                bb.view(torch.uint8).reshape(-1) if bb.dtype != torch.bool else bb))
+    if isinstance(a, (tuple, list)):
+        return isinstance(b, (tuple, list)) and len(a) == len(b) and all(_bit_identical(x, y) for x, y in zip(a, b))
+    if isinstance(a, dict):
+        return isinstance(b, dict) and a.keys() == b.keys() and all(_bit_identical(a[k], b[k]) for k in a)
+    return a == b
 
 
 def run_worker(args) -> int:
@@ -107,6 +128,23 @@ def run_worker(args) -> int:
                 nv.raise_on_status(sync=False)
         ctx.barrier()
         compare.save_output(y, args.logs_dir, ctx.rank)
+
+        if args.determinism > 0:
+            # same seeded inputs, same implementation, N more runs: any differing bit is a race (or an atomic-order dependence)
+            differing = 0
+            for _ in range(args.determinism):
+                again_inputs = spec.make_inputs(run, cfg) if spec.mutates_inputs else inputs
+                with torch.no_grad():
+                    y2 = impl(run, *again_inputs)
+                if ctx.is_cuda:
+                    torch.cuda.synchronize()
+                differing += 0 if _bit_identical(y, y2) else 1
+                ctx.barrier()
+            with open(os.path.join(args.logs_dir, f"rank_{ctx.rank}_determinism.json"), "w") as fh:
+                json.dump({"runs": args.determinism, "differing": differing}, fh)
+            print(f"[Rank {ctx.rank}] determinism: {args.determinism - differing}/{args.determinism} repeat runs bit-identical", flush=True)
+            if differing:
+                rc = 4
 
         if args.measure_perf:
             sampler = None

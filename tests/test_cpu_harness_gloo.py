@@ -137,3 +137,22 @@ def test_headline_verb_runs_the_plumbing_configuration_on_cpu(tmp_path):
     assert "| plumbing | default | 2 | match |" in r.stdout and "1 of 1 cells match" in r.stdout and "llama_worker.py --full" in r.stdout
     cell = json.loads(open(ledger).readline())
     assert cell["label"].startswith("1 ") and cell["ours_ms"] > 0
+
+
+def test_run_with_determinism_check_on_cpu():
+    r, _ = _launch("run", "--op", "allreduce", "--impl", "ours", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--config", "small",
+                   "--determinism", "3")
+    assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
+    assert "determinism: 3/3 repeat runs bit-identical" in r.stdout
+
+
+def test_bit_identical_helper_sees_single_bit_and_structure_differences():
+    import torch
+
+    from parallelkernelbench_b200.harness.worker import _bit_identical
+
+    a = torch.tensor([1.0, float("nan"), -0.0])
+    assert _bit_identical(a, a.clone()) and _bit_identical((a, {"k": a}), (a.clone(), {"k": a.clone()}))
+    assert not _bit_identical(a, torch.tensor([1.0, float("nan"), 0.0]))          # -0.0 against +0.0: equal values, other bits
+    assert not _bit_identical(a, a.double()) and not _bit_identical((a,), (a, a)) and not _bit_identical({"k": a}, {"j": a})
+    assert _bit_identical(torch.empty(0), torch.empty(0)) and _bit_identical(3, 3) and not _bit_identical(3, 4)
