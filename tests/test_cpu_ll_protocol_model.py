@@ -140,3 +140,32 @@ def test_two_result_buffers_and_one_closing_barrier_are_enough():
     for t in threads:
         t.join(120)
     assert not errors, errors[0]
+
+
+def test_native_stress_of_the_exchange_protocol_with_real_threads(tmp_path):
+    """The C++ form of the model above (relaxed 64-bit atomics for the {data, epoch} pairs, one thread per rank), also under
+    ThreadSanitizer when the toolchain has it; the single-slot-set variant must fail."""
+    import os
+    import shutil
+    import subprocess
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        import pytest
+
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "parallelkernelbench_b200", "csrc", "hosttests", "ll_protocol_stress.cpp")
+    exe = str(tmp_path / "ll_stress")
+    subprocess.run([gxx, "-O2", "-std=c++17", "-pthread", src, "-o", exe], check=True, capture_output=True)
+    for args in (("4", "1500", "64"), ("8", "600", "32")):
+        r = subprocess.run([exe, *args], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and "OK" in r.stdout, r.stdout + r.stderr
+    # with one slot set a rank that runs ahead overwrites unread words: a timing matter, so allow a few attempts
+    assert any(subprocess.run([exe, "2", "3000", "16", "single"], capture_output=True, text=True, timeout=120).returncode == 1
+               for _ in range(4))
+    tsan = str(tmp_path / "ll_stress_tsan")
+    built = subprocess.run([gxx, "-O1", "-g", "-std=c++17", "-pthread", "-fsanitize=thread", src, "-o", tsan], capture_output=True)
+    if built.returncode == 0:
+        r = subprocess.run([tsan, "4", "300", "32"], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and "ThreadSanitizer" not in r.stderr, r.stdout + r.stderr[-2000:]
