@@ -169,3 +169,31 @@ def test_native_stress_of_the_exchange_protocol_with_real_threads(tmp_path):
     if built.returncode == 0:
         r = subprocess.run([tsan, "4", "300", "32"], capture_output=True, text=True, timeout=300)
         assert r.returncode == 0 and "ThreadSanitizer" not in r.stderr, r.stdout + r.stderr[-2000:]
+
+
+def test_native_model_of_the_grid_wide_barrier(tmp_path):
+    """Threads as blocks of several ranks run the grid-wide cross-rank barrier with the device code's memory orders; payloads
+    are plain stores read by another block index of another rank, so ThreadSanitizer checks the happens-before chain. The
+    per-block-index barrier in its place must be caught."""
+    import os
+    import shutil
+    import subprocess
+
+    gxx = shutil.which("g++")
+    if gxx is None:
+        import pytest
+
+        pytest.skip("no g++")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = os.path.join(root, "parallelkernelbench_b200", "csrc", "hosttests", "grid_barrier_stress.cpp")
+    exe = str(tmp_path / "gb")
+    subprocess.run([gxx, "-O2", "-std=c++17", "-pthread", src, "-o", exe], check=True, capture_output=True)
+    for args in (("4", "6", "1500"), ("2", "12", "1500")):
+        r = subprocess.run([exe, *args], capture_output=True, text=True, timeout=180)
+        assert r.returncode == 0 and "OK" in r.stdout, r.stdout + r.stderr
+    assert any(subprocess.run([exe, "4", "6", "3000", "blockonly"], capture_output=True, text=True, timeout=180).returncode == 1
+               for _ in range(4))
+    tsan = str(tmp_path / "gb_tsan")
+    if subprocess.run([gxx, "-O1", "-g", "-std=c++17", "-pthread", "-fsanitize=thread", src, "-o", tsan], capture_output=True).returncode == 0:
+        r = subprocess.run([tsan, "3", "4", "300"], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0 and "ThreadSanitizer" not in r.stderr, r.stdout + r.stderr[-2000:]
