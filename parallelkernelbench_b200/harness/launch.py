@@ -255,7 +255,7 @@ def cmd_sweep(a) -> int:
     """ops x world sizes; one JSON line per cell appended to the ledger, finished cells skipped with --resume."""
     from ..workloads import registry
 
-    ops = [s.name for s in registry.all_ops() if s.ours is not None] if a.ops == "all" else a.ops.split(",")
+    ops = [s.name for s in registry.all_ops() if s.ours is not None and not s.explicit_only] if a.ops == "all" else a.ops.split(",")
     worlds = [int(w) for w in a.worlds.split(",")]
     ledger = a.ledger or os.path.join(LOGS_ROOT, "results.jsonl")
     os.makedirs(os.path.dirname(ledger), exist_ok=True)
@@ -298,12 +298,12 @@ def cmd_sweep(a) -> int:
     return rc
 
 
-# The configurations the published comparison is made on: (label, op, named config). The FSDP Llama step is an engine, not
-# an op of the registry; its worker prints the same kind of line (see the hint printed at the end).
+# The configurations the published comparison is made on: (label, op, named config).
 HEADLINE = (("1 plumbing AR->AG->RS", "plumbing", "default"),
             ("2 TP MLP block", "tp_mlp", "default"),
             ("3 EP MoE 256 experts top-8", "moe_layer", "deepseek"),
-            ("4 CP ring attention fwd+bwd 131072 zigzag", "ring_attention_fwd_bwd", "cp131k"))
+            ("4 CP ring attention fwd+bwd 131072 zigzag", "ring_attention_fwd_bwd", "cp131k"),
+            ("5 FSDP Llama-8B training step", "fsdp_llama_step", "llama8b"))
 
 
 def cmd_headline(a) -> int:
@@ -330,8 +330,6 @@ def cmd_headline(a) -> int:
         rows.append(cell)
         rc = rc or (0 if s["all_ok"] else 1)
     sys.stdout.write(report.ledger_table(rows, "markdown"))
-    print("5 FSDP Llama step: python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 "
-          "tests/mp/llama_worker.py --full")
     return rc
 
 

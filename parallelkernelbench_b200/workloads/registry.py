@@ -76,6 +76,7 @@ class OpSpec:
     doc: str = ""
     mutates_inputs: bool = False            # inputs must be re-created for every timed call
     heap_gib: Callable[[dict, int], float] | None = None   # symmetric-heap size this op needs (config, world) -> GiB
+    explicit_only: bool = False             # engine-sized workload: part of "all" selections only when named
 
     def config(self, name: str = "default", overrides: dict | None = None) -> dict:
         if name not in self.configs:
@@ -86,7 +87,7 @@ class OpSpec:
 
 
 _REGISTRY: dict[str, OpSpec] = {}
-_MODULES = ["collectives", "tp", "quant", "optim", "moe", "ulysses", "attention", "wild"]
+_MODULES = ["collectives", "tp", "quant", "optim", "moe", "ulysses", "attention", "wild", "llama"]
 _loaded = False
 
 

@@ -36,7 +36,7 @@ def main() -> int:
         if name in skip:
             continue
         spec = registry.get(name)
-        if spec.ours is None or (spec.ours_needs_cuda and not ctx.is_cuda):
+        if spec.ours is None or (spec.ours_needs_cuda and not ctx.is_cuda) or (spec.explicit_only and args.ops == "all"):
             continue
         cfg_name = args.config if args.config in spec.configs else "default"
         for trial in range(args.trials):

@@ -134,7 +134,7 @@ def test_headline_verb_runs_the_plumbing_configuration_on_cpu(tmp_path):
     r, _ = _launch("headline", "--only", "1", "--nproc", "2", "--backend", "gloo", "--dtype", "float32", "--warmup", "2", "--iters", "3",
                    "--ledger", ledger)
     assert r.returncode == 0, r.stdout[-1500:] + r.stderr[-1500:]
-    assert "| plumbing | default | 2 | match |" in r.stdout and "1 of 1 cells match" in r.stdout and "llama_worker.py --full" in r.stdout
+    assert "| plumbing | default | 2 | match |" in r.stdout and "1 of 1 cells match" in r.stdout
     cell = json.loads(open(ledger).readline())
     assert cell["label"].startswith("1 ") and cell["ours_ms"] > 0
 
@@ -156,3 +156,25 @@ def test_bit_identical_helper_sees_single_bit_and_structure_differences():
     assert not _bit_identical(a, torch.tensor([1.0, float("nan"), 0.0]))          # -0.0 against +0.0: equal values, other bits
     assert not _bit_identical(a, a.double()) and not _bit_identical((a,), (a, a)) and not _bit_identical({"k": a}, {"j": a})
     assert _bit_identical(torch.empty(0), torch.empty(0)) and _bit_identical(3, 3) and not _bit_identical(3, 4)
+
+
+def test_fsdp_llama_step_is_an_explicit_only_op_whose_reference_runs_on_cpu():
+    """The engine-sized workload is in the registry (so `eval`, `headline` and the prompt tooling reach it) but stays out of
+    "all" selections; its PyTorch implementation trains one step on a CPU rank and the loss is near ln(vocab)."""
+    import math
+
+    import torch
+
+    from parallelkernelbench_b200.harness import launch
+    from parallelkernelbench_b200.workloads import registry
+
+    spec = registry.get("fsdp_llama_step")
+    assert spec.explicit_only and spec.ours_needs_cuda and "llama8b" in spec.configs
+    assert [h for h in launch.HEADLINE if h[1] == "fsdp_llama_step"] == [("5 FSDP Llama-8B training step", "fsdp_llama_step", "llama8b")]
+    job = launch.run_job("fsdp_llama_step", "reference", 1, backend="gloo", dtype="bfloat16", config="small", timeout_s=300)
+    assert job["returncode"] == 0 and job["artifact_count"] == 1, job["stderr"][-1500:]
+    loss = torch.load(os.path.join(job["job_dir"], "rank_0.pt"))
+    loss = loss["output_0"] if isinstance(loss, dict) else loss
+    assert abs(float(loss.reshape(-1)[0]) - math.log(1024)) < 0.5
+    c = spec.cost(spec.configs["llama8b"], 8)
+    assert 1.5e14 < c.flops < 3e14 and c.nvlink_bytes > 1e10

@@ -216,3 +216,11 @@ def test_own_kernel_example_solution_matches_on_gpu():
 
     s = launch.eval_op("tp_rmsnorm", 1, trials=1, solution=str(example_path("tp_rmsnorm")), timeout_s=600)
     assert s["all_ok"], s["trials"][-1]
+
+
+def test_fsdp_llama_step_through_the_harness():
+    """The engine as a registry op: ours against the PyTorch + NCCL implementation of the same engine, first step's loss."""
+    from parallelkernelbench_b200.harness import launch
+
+    s = launch.eval_op("fsdp_llama_step", 1, trials=1, config="default", timeout_s=900)
+    assert s["all_ok"], s["trials"][-1]
