@@ -43,8 +43,8 @@ def test_worked_examples_are_in_the_prompt_and_pass_the_evaluation():
     spec.loader.exec_module(mod)
     assert hasattr(mod._kernels(), "ex_row_scale")            # the example's CUDA source builds for sm_100a without a GPU
     for op in EXAMPLES:
-        if op == "allreduce":        # the same one-line solution is evaluated by the loop tests of this file
-            continue
+        if op in ("allreduce", "gemm_allreduce"):    # the one-line solution is evaluated by the loop tests of this file; the
+            continue                                  # GEMM example takes its PyTorch branch on CPU ranks (nothing of its own to check)
         s = launch.eval_op(op, 2, trials=1, backend="gloo", dtype="float32", config="small", solution=str(example_path(op)),
                            timeout_s=300)
         assert s["all_ok"], (op, s["trials"][-1].get("result"))
