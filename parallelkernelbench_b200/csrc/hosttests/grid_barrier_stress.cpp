@@ -43,6 +43,7 @@ int main(int argc, char** argv) {
   auto wait_ge = [&](std::atomic<uint32_t>& w, uint32_t target) {
     const auto t0 = std::chrono::steady_clock::now();
     while ((int32_t)(w.load(std::memory_order_acquire) - target) < 0) {
+      if (failures.load(std::memory_order_relaxed)) return false;      // another block already failed: do not wait for it
       if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(30)) return false;
       std::this_thread::yield();
     }

@@ -52,6 +52,7 @@ int main(int argc, char** argv) {
           uint64_t v;
           while ((uint32_t)((v = slot(me, parity, g, i).load(std::memory_order_relaxed)) >> 32) != epoch) {
             if ((uint32_t)(v >> 32) > epoch) { future.fetch_add(1); failures.fetch_add(1); return; }   // a word of a later call
+            if (failures.load(std::memory_order_relaxed)) return;                        // another rank already failed
             if (std::chrono::steady_clock::now() - t0 > std::chrono::seconds(20)) { timeouts.fetch_add(1); failures.fetch_add(1); return; }
             std::this_thread::yield();
           }
