@@ -179,6 +179,9 @@ def run_worker(args) -> int:
                   f"(min {perf['min_time_ms']:.4f}, {perf['iterations']} iters after {perf['warmup_iterations']} warm-up)",
                   flush=True)
 
+        if getattr(ctx, "_heap", None) is not None and hasattr(ctx._heap, "check_guards"):
+            ctx._heap.check_guards()      # PKB_HEAP_GUARD=1: a write outside a symmetric allocation fails the job here
+
         if args.profile and ctx.is_cuda:
             from torch.profiler import ProfilerActivity, profile
 

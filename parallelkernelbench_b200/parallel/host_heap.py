@@ -77,12 +77,42 @@ class HostHeap:
             self._next_channel += 1
         return self._groups[key]
 
-    def alloc_bytes(self, nbytes: int) -> int:
+    def _raw_alloc(self, nbytes: int) -> int:
         off = (self._top + 63) // 64 * 64
         if off + nbytes > self.nbytes:
             raise MemoryError("host heap exhausted")
         self._top = off + nbytes
         return off
+
+    def alloc_bytes(self, nbytes: int) -> int:
+        from . import guards
+
+        if not guards.enabled():
+            return self._raw_alloc(nbytes)
+        if getattr(self, "_guards", None) is None:
+            base = nv.host_lib().pkbh_heap_local(self.handle)
+
+            def fill(off, n):
+                ctypes.memset(base + off, guards.PATTERN, n)
+
+            def first_bad(off, n):
+                raw = ctypes.string_at(base + off, n)
+                if raw == bytes([guards.PATTERN]) * n:
+                    return -1
+                return next(i for i, b in enumerate(raw) if b != guards.PATTERN)
+
+            self._guards = guards.GuardBook(fill, first_bad, align=64)
+        return self._guards.allocate(self._raw_alloc, nbytes)
+
+    def check_guards(self, raise_on_violation: bool = True) -> list[dict]:
+        """Allocations of this rank's heap whose guard bands were overwritten (empty without ``PKB_HEAP_GUARD=1``)."""
+        from . import guards
+
+        book = getattr(self, "_guards", None)
+        bad = book.check() if book is not None else []
+        if bad and raise_on_violation:
+            raise guards.GuardViolation(bad)
+        return bad
 
     # fault injection (host side only)
     def drop_signals(self, count: int) -> None:

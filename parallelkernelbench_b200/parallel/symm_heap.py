@@ -198,13 +198,45 @@ class SymmetricHeap:
         raw = torch.as_tensor(_RawCudaBuffer(ptr, nbytes, self), device=self.ctx.device)
         return raw.view(dtype)[:n].view(*shape) if n > 0 else torch.empty(shape, dtype=dtype, device=self.ctx.device)
 
-    def alloc_bytes(self, nbytes: int) -> int:
+    def _raw_alloc(self, nbytes: int) -> int:
         off = (self._top + _ALIGN - 1) // _ALIGN * _ALIGN
         if off + nbytes > self.nbytes:
             raise MemoryError(f"symmetric heap exhausted: need {nbytes} bytes at {off}, heap has {self.nbytes} "
                               f"(set PKB_HEAP_GIB)")
         self._top = off + nbytes
         return off
+
+    def alloc_bytes(self, nbytes: int) -> int:
+        from . import guards
+
+        if not guards.enabled():
+            return self._raw_alloc(nbytes)
+        if getattr(self, "_guards", None) is None:
+            local = self.base + self.rank * self.stride
+
+            def fill(off, n):
+                self._view(local + off, (n,), torch.uint8).fill_(guards.PATTERN)
+
+            def first_bad(off, n):
+                bad = (self._view(local + off, (n,), torch.uint8) != guards.PATTERN).nonzero()
+                return int(bad[0]) if bad.numel() else -1
+
+            self._guards = guards.GuardBook(fill, first_bad, align=_ALIGN)
+        return self._guards.allocate(self._raw_alloc, nbytes)
+
+    def check_guards(self, raise_on_violation: bool = True) -> list[dict]:
+        """Allocations of this rank's heap whose guard bands were overwritten (empty without ``PKB_HEAP_GUARD=1``).
+        Synchronises the device."""
+        from . import guards
+
+        book = getattr(self, "_guards", None)
+        if book is None:
+            return []
+        torch.cuda.synchronize()
+        bad = book.check()
+        if bad and raise_on_violation:
+            raise guards.GuardViolation(bad)
+        return bad
 
     def empty(self, shape, dtype=torch.bfloat16) -> SymmTensor:
         shape = tuple(int(s) for s in (shape if isinstance(shape, (tuple, list, torch.Size)) else (shape,)))

@@ -138,3 +138,45 @@ def _late_rank_body(name, rank, world, q):
 def test_late_rank_inside_budget_still_completes():
     out = _run(_late_rank_body, 2)
     assert out == {0: 3.0, 1: 3.0}
+
+
+def test_guard_bands_catch_single_byte_overruns_and_underruns(monkeypatch):
+    import ctypes
+    import os
+
+    import pytest
+
+    from parallelkernelbench_b200 import _native as nv
+    from parallelkernelbench_b200.parallel import guards
+    from parallelkernelbench_b200.parallel.host_heap import HostHeap
+
+    monkeypatch.setenv("PKB_HEAP_GUARD", "1")
+    heap = HostHeap.create(nbytes=4 << 20, name=f"/pkb200_{os.getpid()}_guardtest", rank=0, world=1)
+    try:
+        a, b = heap.alloc_bytes(100), heap.alloc_bytes(4096)
+        assert a % 64 == 0 and b % 64 == 0 and b >= a + 100 + guards.GUARD_BYTES
+        assert heap.check_guards() == []
+        base = nv.host_lib().pkbh_heap_local(heap.handle)
+        ctypes.memset(base + a, 0x11, 100)                              # the allocation itself may be written freely
+        assert heap.check_guards() == []
+        ctypes.memset(base + a + 100, 0x22, 1)                          # one byte past the end of the first allocation
+        ctypes.memset(base + b - 3, 0x33, 2)                            # bytes 3 and 2 before the second one
+        with pytest.raises(guards.GuardViolation, match="1 byte\\(s\\) after"):
+            heap.check_guards()
+        bad = heap.check_guards(raise_on_violation=False)
+        assert {(v["offset"], v["side"], v["distance"]) for v in bad} == {(a, "after", 1), (b, "before", 2)}
+    finally:
+        heap.close()
+
+
+def test_collectives_run_clean_under_guard_bands():
+    """The plumbing sequence (all-reduce, all-gather, reduce-scatter) on two CPU ranks with every heap allocation guarded."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "run", "--op", "plumbing", "--impl", "ours", "--nproc", "2",
+                        "--backend", "gloo", "--dtype", "float32"], cwd=root, capture_output=True, text=True, timeout=300,
+                       env={**os.environ, "PKB_HEAP_GUARD": "1"})
+    assert r.returncode == 0 and "dry run ok" in r.stdout, r.stdout[-1500:] + r.stderr[-1500:]

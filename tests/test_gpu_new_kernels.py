@@ -224,3 +224,16 @@ def test_fsdp_llama_step_through_the_harness():
 
     s = launch.eval_op("fsdp_llama_step", 1, trials=1, config="default", timeout_s=900)
     assert s["all_ok"], s["trials"][-1]
+
+
+@pytest.mark.parametrize("op", ["allreduce", "alltoall", "tp_mlp", "moe_layer"])
+def test_ops_leave_the_guard_bands_of_the_symmetric_heap_intact(op):
+    """PKB_HEAP_GUARD=1 brackets every symmetric allocation with pattern-filled bands; the worker checks them after the run."""
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    n = 2 if torch.cuda.device_count() >= 2 else 1
+    r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "run", "--op", op, "--impl", "ours", "--nproc", str(n),
+                        "--config", "small"], cwd=root, capture_output=True, text=True, timeout=600, env={**os.environ, "PKB_HEAP_GUARD": "1"})
+    assert r.returncode == 0 and "dry run ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
