@@ -464,7 +464,8 @@ struct Fa2Smem {
 // offset computes the exponentials with the CURRENT offset in the same pass that finds the tile's row maximum - one read of
 // S from TMEM instead of two - and tells the correction warps "no rescale" up front. Only if some row's maximum has grown by
 // more than the lazy threshold does the warp repeat the pass with the new offset and rescale its own accumulator rows
-// (after the previous P V product has landed). The offset moves under exactly the same rule as in the two-pass form, so
+// (after the previous P V product has landed). The pass reads S in 16-column pieces through a two-buffer software pipeline,
+// so the TMEM read of the next piece overlaps the arithmetic on the current one. The offset moves under exactly the same rule as in the two-pass form, so
 // the results are bit-identical to it.
 template <int D, bool SPEC = false>
 __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
@@ -682,16 +683,15 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
             auto exp_pass = [&](const float off, float& mx_out) {
               const uint32_t prow = sb + S::kP + t * S::kPBytes + static_cast<uint32_t>(row) * 128u;
               float sum = 0.f, mxl = -INFINITY;
-#pragma unroll
-              for (int cc = 0; cc < 4; ++cc) {
-                uint32_t r[32];
-                tmem_ld_32x32(s_row + cc * 32, r);
-                tmem_ld_wait();
-                float pvv[32];
+              float part[4] = {0.f, 0.f, 0.f, 0.f};
+              // 16 columns: exponentials, running maximum, partial sums in the same order as the two-pass form (four
+              // interleaved partials per 32 columns, folded after the second half), two 16-byte chunks of P
+              auto half = [&](const uint32_t (&r)[16], const int c16) {
+                float pvv[16];
                 if (need_mask) {
 #pragma unroll
-                  for (int i = 0; i < 32; ++i) {
-                    const int col = cc * 32 + i;
+                  for (int i = 0; i < 16; ++i) {
+                    const int col = c16 * 16 + i;
                     const bool masked = col >= valid || (d.causal && kp + col > my_pos);
                     const float sv = __uint_as_float(r[i]);
                     if (!masked) mxl = fmaxf(mxl, sv);
@@ -699,19 +699,19 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
                   }
                 } else {
 #pragma unroll
-                  for (int i = 0; i < 32; ++i) {
+                  for (int i = 0; i < 16; ++i) {
                     const float sv = __uint_as_float(r[i]);
                     mxl = fmaxf(mxl, sv);
                     pvv[i] = fast_exp2(fmaf(sv, scale2, -off));
                   }
                 }
-                float part[4] = {0.f, 0.f, 0.f, 0.f};
+                if ((c16 & 1) == 0) part[0] = part[1] = part[2] = part[3] = 0.f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) part[i & 3] += pvv[i];
-                sum += (part[0] + part[1]) + (part[2] + part[3]);
+                for (int i = 0; i < 16; ++i) part[i & 3] += pvv[i];
+                if (c16 & 1) sum += (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                  const int chunk = cc * 4 + g;
+                for (int g = 0; g < 2; ++g) {
+                  const int chunk = c16 * 2 + g;
                   const uint32_t atom = (chunk >> 3) * kAtomBytes;
                   const uint32_t dst = prow + atom + (static_cast<uint32_t>((chunk & 7) ^ (row & 7)) << 4);
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pack_bf16x2(pvv[8 * g], pvv[8 * g + 1])),
@@ -719,6 +719,21 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
                                "r"(pack_bf16x2(pvv[8 * g + 6], pvv[8 * g + 7]))
                                : "memory");
                 }
+              };
+              // software pipeline over eight 16-column reads with two register buffers: the read of the next piece is in
+              // flight while the current one is processed (tcgen05.wait::ld waits for every outstanding read, so the next
+              // read is issued right after a wait and before the arithmetic on the piece that wait delivered)
+              uint32_t ra[16], rb[16];
+              tmem_ld_32x16(s_row, ra);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 8; c += 2) {
+                tmem_ld_32x16(s_row + (c + 1) * 16, rb);
+                half(ra, c);
+                tmem_ld_wait();
+                if (c + 2 < 8) tmem_ld_32x16(s_row + (c + 2) * 16, ra);
+                half(rb, c + 1);
+                if (c + 2 < 8) tmem_ld_wait();
               }
               mx_out = mxl;
               return sum;
