@@ -27,13 +27,17 @@ __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32
 struct BulkRing {
   uint32_t smem;     // shared-memory address of the ring (16-byte aligned), followed by the mbarriers
   uint32_t phase;
+  int stages;        // depth of the ring: `stages` buffers of kBulkStageBytes, then `stages` mbarriers (at most 32)
 };
 
+constexpr int bulk_ring_bytes(int stages) { return stages * (kBulkStageBytes + 8); }
+
 // Call once per kernel by thread 0 of the block (then __syncthreads before the first copy).
-__device__ __forceinline__ void bulk_ring_init(BulkRing& r, uint32_t smem_addr) {
+__device__ __forceinline__ void bulk_ring_init(BulkRing& r, uint32_t smem_addr, int stages = kBulkStages) {
   r.smem = smem_addr;
   r.phase = 0;
-  for (int s = 0; s < kBulkStages; ++s) mbar_init(smem_addr + kBulkStages * kBulkStageBytes + 8 * s, 1);
+  r.stages = stages;
+  for (int s = 0; s < stages; ++s) mbar_init(smem_addr + stages * kBulkStageBytes + 8 * s, 1);
   fence_mbar_init();
 }
 
@@ -43,13 +47,14 @@ __device__ __forceinline__ bool bulk_copy(BulkRing& r, void* dst, const void* sr
                                           uint64_t budget_ns) {
   const long long n = (bytes + kBulkStageBytes - 1) / kBulkStageBytes;
   auto chunk_bytes = [&](long long c) { return (uint32_t)((c + 1 < n) ? kBulkStageBytes : (bytes - c * kBulkStageBytes)); };
-  auto bar = [&](int s) { return r.smem + kBulkStages * kBulkStageBytes + 8u * s; };
+  const int stages = r.stages;
+  auto bar = [&](int s) { return r.smem + stages * kBulkStageBytes + 8u * s; };
   auto issue_load = [&](long long c) {
-    const int s = (int)(c % kBulkStages);
+    const int s = (int)(c % stages);
     mbar_expect_tx(bar(s), chunk_bytes(c));
     bulk_load(r.smem + s * kBulkStageBytes, static_cast<const uint8_t*>(src) + c * kBulkStageBytes, chunk_bytes(c), bar(s));
   };
-  constexpr int kAhead = kBulkStages - 2;     // loads in flight; two stages may still be read by stores
+  const int kAhead = stages - 2;              // loads in flight; two stages may still be read by stores
   for (long long c = 0; c < n && c < kAhead; ++c) issue_load(c);
   bool ok = true;
   for (long long c = 0; c < n; ++c) {
@@ -58,7 +63,7 @@ __device__ __forceinline__ bool bulk_copy(BulkRing& r, void* dst, const void* sr
       tma_store_wait_read<1>();
       issue_load(c + kAhead);
     }
-    const int s = (int)(c % kBulkStages);
+    const int s = (int)(c % stages);
     if (!mbar_wait(bar(s), (r.phase >> s) & 1u, abort_flag, budget_ns)) { ok = false; break; }
     r.phase ^= 1u << s;
     bulk_store(static_cast<uint8_t*>(dst) + c * kBulkStageBytes, r.smem + s * kBulkStageBytes, chunk_bytes(c));

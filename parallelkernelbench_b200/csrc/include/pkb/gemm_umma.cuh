@@ -52,6 +52,9 @@ struct GemmParams {
   // through a second tensor map straight from the caller's tensor, with no flag to wait for.
   int a_local_row0;
   int a_local_rows;
+  // Optional instrumentation: when not null, every CTA's producer adds the SM cycles it spent waiting for a_ready
+  // flags to a_wait_cycles[blockIdx.x] (one word per CTA of the launch; the caller zeroes it).
+  unsigned long long* a_wait_cycles;
   // ---- GEMM -> reduce-scatter hook ----------------------------------------------------------
   // Output row m belongs to rank m / rs_rows_per_rank; it is stored at
   // rs_out[rank_of_m] + (m % rs_rows_per_rank) * ldc, and when a tile of that row block is done

@@ -105,6 +105,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long waited = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m_blk, n_blk;
         tile_coords(tile, m_blk, n_blk);
@@ -125,7 +126,10 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           int chunk = row0 / p.a_chunk_rows;
           const int last_chunk = (p.M - 1) / p.a_chunk_rows;
           if (chunk > last_chunk) chunk = last_chunk;
-          if (!wait_flag_ge(p.a_ready + chunk, p.a_ready_epoch, p.wait_budget_ns)) {
+          const long long w0 = p.a_wait_cycles != nullptr ? clock64() : 0;
+          const bool arrived = wait_flag_ge(p.a_ready + chunk, p.a_ready_epoch, p.wait_budget_ns);
+          if (p.a_wait_cycles != nullptr) waited += clock64() - w0;
+          if (!arrived) {
             *abort_flag = 1;
             record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
             ok = false;
@@ -148,6 +152,9 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
             phase ^= 1u;
           }
         }
+      }
+      if constexpr (A_READY) {
+        if (p.a_wait_cycles != nullptr) p.a_wait_cycles[blockIdx.x] += (unsigned long long)waited;
       }
     }
     __syncwarp();

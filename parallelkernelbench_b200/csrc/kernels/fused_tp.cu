@@ -55,6 +55,25 @@ struct TpAgArgs {
   int bulk_push;           // 1: sub-blocks travel as 16 KiB TMA bulk requests through a shared-memory ring (one issuing thread)
 };
 
+// Depth of the push ring: a communication CTA owns the whole dynamic shared memory of the GEMM configuration, and the
+// bytes in flight per CTA (ring depth - 2 requests of 16 KiB) decide how few CTAs can keep the link busy.
+constexpr int kTpPushStages = 12;
+static_assert(bulk_ring_bytes(kTpPushStages) + 128 <= kGemm2SmemTotal, "push ring does not fit the kernel's shared memory");
+
+// Both CTAs of a pair must take the same branch after a cross-GPU barrier: the pair GEMM that follows allocates tensor
+// memory for the pair and meets at cluster barriers, so one CTA leaving alone would strand its partner. Every thread of
+// both CTAs calls this; it returns true only if `ok` was true in both CTAs.
+__device__ __forceinline__ bool cluster_pair_all(bool ok) {
+  __shared__ int s_vote;
+  if (threadIdx.x == 0) s_vote = ok ? 1 : 0;
+  cluster_sync_all();
+  int peer;
+  const uint32_t peer_addr = mapa_shared(smem_u32(&s_vote), cluster_ctarank() ^ 1u);
+  asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(peer) : "r"(peer_addr) : "memory");
+  cluster_sync_all();  // the partner has read this CTA's vote before the CTA can exit or vote again
+  return ok && peer != 0;
+}
+
 __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
   const SymmCtx& c = a.ctx;
   // every rank has entered this call, so every rank has finished reading the previous gather
@@ -64,7 +83,7 @@ __device__ __forceinline__ void ag_push_role(const TpAgArgs& a) {
   BulkRing ring;
   if (a.bulk_push && threadIdx.x == 0) {
     s_bulk_abort = 0;
-    bulk_ring_init(ring, (smem_u32(smem_raw) + 127u) & ~127u);
+    bulk_ring_init(ring, (smem_u32(smem_raw) + 127u) & ~127u, kTpPushStages);
   }
   if (!symm_block_barrier(c, 300, 1)) return;
   const int W = c.gsize;
@@ -147,7 +166,7 @@ tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                           const TpRsArgs a) {
   const SymmCtx& c = a.ctx;
   // all ranks have entered this call => all ranks have consumed the previous call's receive slots
-  if (!symm_block_barrier(c, 301, 1)) return;
+  if (!cluster_pair_all(symm_block_barrier(c, 301, 1))) return;
   gemm_umma2_cta<kEpiNone, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1,
                                                      gridDim.x >> 1, &out_maps);
   __syncthreads();
@@ -232,7 +251,7 @@ tp_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const TpArArgs a) {
   const SymmCtx& c = a.ctx;
   // all ranks have entered this call => all ranks have consumed the previous call's receive slots and result
-  if (!symm_block_barrier(c, 302, 1)) return;
+  if (!cluster_pair_all(symm_block_barrier(c, 302, 1))) return;
   gemm_umma2_cta<kEpiNone, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1,
                                                      gridDim.x >> 1, &out_maps);
   __syncthreads();
@@ -296,7 +315,7 @@ tp_gemm_allgather_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ GemmOutMaps out_maps, const GemmParams p,
                          const __grid_constant__ SymmCtx c) {
   // all ranks have entered this call => all ranks have consumed the previous call's gathered result
-  if (!symm_block_barrier(c, 303, 1)) return;
+  if (!cluster_pair_all(symm_block_barrier(c, 303, 1))) return;
   gemm_umma2_cta<EPI, false, false, false, true, true>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1, &out_maps);
   // the same-index blocks of every rank have completed their stores once this barrier passes
   symm_block_barrier(c, 303, 2);
@@ -383,7 +402,17 @@ __global__ void __launch_bounds__(256) tp_gemv_allgather_kernel(const TpGemvArgs
 
 using namespace pkb;
 
+// device buffer that receives, per CTA of pkb_tp_ag_gemm, the cycles its producer waited for gathered rows (null: off)
+static unsigned long long* g_ag_wait_stats = nullptr;
+
 extern "C" {
+
+// Instrumentation of pkb_tp_ag_gemm: `dev_words` points to at least 148 zeroed 64-bit words of device memory (or null to
+// switch it off). Every later call adds, per CTA, the SM cycles its TMA producer spent waiting for rows from the peers.
+int pkb_tp_ag_gemm_set_wait_stats(void* dev_words) {
+  g_ag_wait_stats = static_cast<unsigned long long*>(dev_words);
+  return kApiOk;
+}
 
 // C[gsize*rows, N] = epi( allgather(x_local)[gsize*rows, K] @ w[N, K]^T ), C local bf16.
 // gather_off / flags_off: heap offsets of the gather buffer (gsize*rows*K bf16) and of
@@ -436,6 +465,7 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   p.a_chunk_rows = a_chunk_rows;
   p.a_local_row0 = h->grank * rows;
   p.a_local_rows = rows;
+  p.a_wait_cycles = g_ag_wait_stats;
   const int blocks_per_shard = rows / kGemm2TileM;
   p.group_m = blocks_per_shard < 8 ? blocks_per_shard : 8;
   // keep whole shards inside rasterisation groups when possible

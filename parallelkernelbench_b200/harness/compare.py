@@ -66,8 +66,9 @@ def _compare_leaf(a: Any, b: Any, path: str, atol: float, rtol: float, errors: l
         mx = float(diff[finite].max()) if finite.any() else 0.0
         stats["max_abs_diff"] = max(stats.get("max_abs_diff", 0.0), mx)
         stats["mean_abs_diff"] = max(stats.get("mean_abs_diff", 0.0), float(diff[finite].mean()) if finite.any() else 0.0)
-        if not torch.allclose(af, bf, atol=atol, rtol=rtol, equal_nan=True):
-            bad = int((~torch.isclose(af, bf, atol=atol, rtol=rtol, equal_nan=True)).sum())
+        # NaN never matches, not even NaN (torch.allclose without equal_nan, as the reference's gate: run_local.py:523-525)
+        if not torch.allclose(af, bf, atol=atol, rtol=rtol):
+            bad = int((~torch.isclose(af, bf, atol=atol, rtol=rtol)).sum())
             errors.append(f"{path}: {bad}/{a.numel()} elements differ (max abs diff {mx:.4g}, atol {atol}, rtol {rtol})")
             return False
         return True
@@ -101,6 +102,46 @@ def compare_objects(a: Any, b: Any, atol: float = 1e-2, rtol: float = 1e-2) -> d
     stats: dict = {}
     ok = _compare_leaf(a, b, "out", atol, rtol, errors, stats)
     return {"ok": ok, "errors": errors[:16], **stats}
+
+
+STRICT_ATOL = STRICT_RTOL = 1e-2        # the gate of the reference harness (reference: run_local.py:523-525)
+
+
+def accuracy_gate(ref: Any, cand: Any, atol: float, rtol: float, oracle=None) -> dict:
+    """One implementation's output against the reference's, for gates that may be looser than 1e-2 / 1e-2.
+
+    ``strict``: the candidate is within 1e-2 / 1e-2 of the reference - the reference harness's own criterion.
+    ``oracle``: it is not, but it is within the op's gate AND ``oracle()`` (the reference code on the same inputs widened
+    to fp32; called only when needed) shows the candidate at most twice as far from the fp32 result as the low-precision
+    reference is, in max and in mean absolute error. A candidate that merely fits the loose gate fails.
+    ``op_override_unverified``: no fp32 run is possible for the op, the op gate alone decided.
+    Returns the comparison dict plus ``gate`` (and ``oracle_err`` when the fp32 run was used)."""
+    strict = compare_objects(ref, cand, STRICT_ATOL, STRICT_RTOL)
+    if strict["ok"]:
+        return dict(strict, gate="strict")
+    if atol <= STRICT_ATOL and rtol <= STRICT_RTOL:
+        return dict(compare_objects(ref, cand, atol, rtol), gate="op")
+    res = dict(compare_objects(ref, cand, atol, rtol), gate="op_override_unverified")
+    if not res["ok"] or oracle is None:
+        return res
+    try:
+        exact = oracle()
+    except Exception as e:          # the reference code cannot run in fp32 for this op
+        return dict(res, oracle_err=f"unavailable: {type(e).__name__}: {e}"[:200])
+    if exact is None:
+        return res
+    e_ref = compare_objects(exact, ref, float("inf"), 0.0)
+    e_cand = compare_objects(exact, cand, float("inf"), 0.0)
+    if not (e_ref["ok"] and e_cand["ok"]):
+        return dict(res, oracle_err="unusable: " + "; ".join((e_ref["errors"] + e_cand["errors"])[:2]))
+    errs = {"ref_max": e_ref.get("max_abs_diff", 0.0), "ours_max": e_cand.get("max_abs_diff", 0.0),
+            "ref_mean": e_ref.get("mean_abs_diff", 0.0), "ours_mean": e_cand.get("mean_abs_diff", 0.0)}
+    earned = errs["ours_max"] <= 2.0 * errs["ref_max"] + 1e-3 and errs["ours_mean"] <= 2.0 * errs["ref_mean"] + 1e-4
+    res.update(gate="oracle", oracle_err=errs)
+    if not earned:
+        res["ok"] = False
+        res["errors"] = [f"within the op gate but further from the fp32 result than twice the reference's own error: {errs}"] + res["errors"]
+    return res
 
 
 def compare_dirs(ref_dir: str, cand_dir: str, atol: float = 1e-2, rtol: float = 1e-2, expected_ranks: int | None = None) -> dict:

@@ -82,13 +82,25 @@ def classify_trial(ref_job: dict, cand_job: dict, cmp: dict | None) -> dict:
     if ref_job["artifact_count"] == 0 or cand_job["artifact_count"] == 0:
         failed = ref_job if ref_job["artifact_count"] == 0 else cand_job
         return {"result": "no_artifacts", "failed_impl": failed["impl"], "returncode": failed["returncode"]}
+    # a job that saved its outputs and failed afterwards (guard band overwritten, non-deterministic repeat run, a device
+    # wait that ran out while being timed, a crash in the timing loop) is a failure even if the saved outputs compare equal
+    if ref_job["returncode"] != 0 or ref_job.get("timed_out"):
+        return {"result": "reference_failed", "failed_impl": ref_job["impl"], "returncode": ref_job["returncode"]}
+    if cand_job["returncode"] != 0 or cand_job.get("timed_out"):
+        return {"result": "candidate_failed", "failed_impl": cand_job["impl"], "returncode": cand_job["returncode"]}
     if cmp is None:
         return {"result": "no_artifacts"}
     return {"result": "match" if cmp["ok"] else cmp["kind"]}
 
 
-def trial_line(trial: int, verdict: dict, ref_perf: dict | None, cand_perf: dict | None) -> str:
+def trial_line(trial: int, verdict: dict, ref_perf: dict | None, cand_perf: dict | None, gate: dict | None = None) -> str:
     s = f"trial {trial}: {verdict['result']}"
+    if gate and gate.get("gate"):
+        s += f" [gate: {gate['gate']}"
+        if isinstance(gate.get("oracle"), dict):
+            o = gate["oracle"]
+            s += f", max error vs fp32: reference {o['ref_max']:.3g}, ours {o['ours_max']:.3g}"
+        s += "]"
     if ref_perf and cand_perf:
         r, c = ref_perf["wall_time_ms_max"], cand_perf["wall_time_ms_max"]
         s += f" | ref {r:.4f} ms | ours {c:.4f} ms | speedup {r / c:.2f}x"
@@ -124,7 +136,7 @@ def ledger_rows(path: str, latest_only: bool = True) -> list[dict]:
     return sorted(out, key=lambda d: (d["op"], d.get("config", "default"), d["world"]))
 
 
-_COLUMNS = (("op", "op"), ("config", "config"), ("world", "GPUs"), ("result", "result"), ("ref_ms", "reference ms"),
+_COLUMNS = (("op", "op"), ("config", "config"), ("world", "GPUs"), ("result", "result"), ("gate", "gate"), ("ref_ms", "reference ms"),
             ("ours_ms", "ours ms"), ("speedup", "speed-up"), ("pct_of_roofline", "% of roofline"), ("limiter", "limiter"),
             ("git_sha", "commit"))
 

@@ -26,7 +26,7 @@ import torch.distributed as dist
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--op", required=True)
-    ap.add_argument("--impl", required=True, choices=["reference", "ours", "file"])
+    ap.add_argument("--impl", required=True, choices=["reference", "ours", "file", "oracle"])
     ap.add_argument("--solution", default=None, help="with --impl file: a Python file that defines solution(rc, *inputs)")
     ap.add_argument("--logs-dir", required=True)
     ap.add_argument("--config", default="default")
@@ -82,6 +82,24 @@ def _bit_identical(a, b) -> bool:
     return a == b
 
 
+def _widen(x):
+    """bf16 / fp16 tensors -> fp32, containers walked, everything else untouched."""
+    if isinstance(x, torch.Tensor):
+        return x.float() if x.dtype in (torch.bfloat16, torch.float16) else x
+    if isinstance(x, (tuple, list)):
+        return type(x)(_widen(v) for v in x)
+    if isinstance(x, dict):
+        return {k: _widen(v) for k, v in x.items()}
+    return x
+
+
+def _check_guards(ctx) -> None:
+    """PKB_HEAP_GUARD=1: raise if any guard band around a symmetric-heap allocation was overwritten."""
+    heap = getattr(ctx, "_heap", None)
+    if heap is not None and hasattr(heap, "check_guards"):
+        heap.check_guards()
+
+
 def run_worker(args) -> int:
     from ..parallel import init_context
     from ..workloads import registry
@@ -110,7 +128,7 @@ def run_worker(args) -> int:
         if args.impl == "file":
             impl = load_solution(args.solution)
         else:
-            impl = spec.reference if args.impl == "reference" else spec.ours
+            impl = spec.reference if args.impl in ("reference", "oracle") else spec.ours
         if impl is None:
             raise NotImplementedError(f"op {spec.name} has no '{args.impl}' implementation")
         if args.impl == "ours" and spec.ours_needs_cuda and not ctx.is_cuda:
@@ -118,15 +136,22 @@ def run_worker(args) -> int:
         print(f"[Rank {ctx.rank}/{ctx.world}] {spec.name} impl={args.impl} cfg={cfg} dtype={args.dtype} "
               f"device={ctx.device} backend={ctx.backend}", flush=True)
         inputs = spec.make_inputs(run, cfg)
+        if args.impl == "oracle":
+            # the same seeded values as every other implementation sees, widened to fp32, through the reference code: an
+            # accuracy yardstick for gates looser than 1e-2 (how far is each implementation from the fp32 result?)
+            inputs = _widen(inputs)
+            run.dtype = torch.float32
         with torch.no_grad():
             y = impl(run, *inputs)
+        uses_native = ctx.is_cuda and args.impl in ("ours", "file")     # a candidate file may call the package's kernels too
+        if uses_native:
+            from .. import _native as nv
         if ctx.is_cuda:
             torch.cuda.synchronize()
-            if args.impl == "ours":
-                from .. import _native as nv
-
+            if uses_native:
                 nv.raise_on_status(sync=False)
         ctx.barrier()
+        _check_guards(ctx)                # a write outside a symmetric allocation fails the job before anything is saved
         compare.save_output(y, args.logs_dir, ctx.rank)
 
         if args.determinism > 0:
@@ -160,6 +185,8 @@ def run_worker(args) -> int:
             with torch.no_grad():
                 perf = timing.measure(lambda *a: impl(run, *a), inputs, warmup=args.warmup, iters=args.iters,
                                       device=ctx.device, use_graph=args.graph)
+            if uses_native:
+                nv.raise_on_status(sync=True)      # a device wait that ran out inside the timed loop invalidates the time
             if sampler is not None:
                 try:
                     sampler.stop()
@@ -179,8 +206,7 @@ def run_worker(args) -> int:
                   f"(min {perf['min_time_ms']:.4f}, {perf['iterations']} iters after {perf['warmup_iterations']} warm-up)",
                   flush=True)
 
-        if getattr(ctx, "_heap", None) is not None and hasattr(ctx._heap, "check_guards"):
-            ctx._heap.check_guards()      # PKB_HEAP_GUARD=1: a write outside a symmetric allocation fails the job here
+        _check_guards(ctx)                # again after the repeat runs and the timed loop
 
         if args.profile and ctx.is_cuda:
             from torch.profiler import ProfilerActivity, profile

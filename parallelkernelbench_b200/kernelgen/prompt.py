@@ -11,7 +11,13 @@ HARDWARE_PROFILES = {
         (900 GB/s per direction per GPU, in-switch reduction through multimem instructions); 148 SMs, 227 KB shared
         memory per CTA, 256 KB tensor memory per SM, 126 MB L2, 180 GB HBM3e at about 6.5 TB/s measured copy bandwidth;
         dense bf16 about 1.4-1.6 PFLOP/s measured. Matrix products belong on tcgen05.mma with accumulators in tensor
-        memory and operands staged by TMA; never issue a TMA load with cluster multicast from another GPU's memory."""),
+        memory and operands staged by TMA.
+        Off-limits in any candidate (it runs on two or more ranks of a shared machine, and the evaluator refuses the file
+        before building it): any TMA or bulk load with cluster multicast (local sources included - let each CTA fetch its
+        own tile, or stage a remote tile in local memory first); the batched memcpy entry points of the CUDA runtime and
+        driver (issue one cudaMemcpyAsync per copy or gather with a kernel); device traps and failing device asserts;
+        any spin or wait without an iteration or time limit (on expiry record a status and return); changing clocks, power
+        limits or any other GPU setting."""),
     "cpu_gloo": "CPU ranks over gloo and a shared-memory twin of the symmetric heap: correctness of the host logic only.",
 }
 

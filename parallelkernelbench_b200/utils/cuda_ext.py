@@ -44,7 +44,12 @@ def compile_cuda_module(source: str, name: str = "candidate", extra_flags: tuple
     """Build ``source`` (CUDA C++ with ``extern "C"`` entry points) into a shared object for sm_100a and load it.
 
     Compilation errors raise ``RuntimeError`` with nvcc's output. ``extra_flags`` are appended to the nvcc command
-    (for example ``("-Xptxas", "-v")``); ``-gencode arch=compute_100a,code=sm_100a`` is always used."""
+    (for example ``("-Xptxas", "-v")``); ``-gencode arch=compute_100a,code=sm_100a`` is always used. Source that names a
+    cluster-multicast bulk/tensor load, a batched memcpy entry point or a device trap is refused with
+    ``ForbiddenSourceError`` (see ``utils/source_screen.py``)."""
+    from .source_screen import require_clean
+
+    require_clean(source, f"CUDA source '{name}'")      # before nvcc: nothing forbidden is ever built, let alone launched
     flags = (*BASE_FLAGS, *extra_flags)
     key = hashlib.sha256(("\0".join(flags) + "\0" + source).encode()).hexdigest()[:24]
     if key in _loaded:

@@ -77,6 +77,13 @@ class OpSpec:
     mutates_inputs: bool = False            # inputs must be re-created for every timed call
     heap_gib: Callable[[dict, int], float] | None = None   # symmetric-heap size this op needs (config, world) -> GiB
     explicit_only: bool = False             # engine-sized workload: part of "all" selections only when named
+    tol_note: str = ""                      # why the gate is looser than 1e-2 / 1e-2 (required whenever it is)
+
+    def tolerance(self, config_name: str = "default") -> tuple[float, float]:
+        """(atol, rtol) of a named config: a config may carry its own ``atol`` / ``rtol`` keys (a lower-precision variant of
+        the op), otherwise the op's values apply."""
+        cfg = self.configs.get(config_name, {})
+        return float(cfg.get("atol", self.atol)), float(cfg.get("rtol", self.rtol))
 
     def config(self, name: str = "default", overrides: dict | None = None) -> dict:
         if name not in self.configs:
@@ -109,6 +116,9 @@ def load_all() -> None:
         except ModuleNotFoundError as e:
             if e.name != f"{__package__}.{m}":
                 raise
+    from . import tolerances
+
+    tolerances.attach(_REGISTRY.values())
 
 
 def get(name: str) -> OpSpec:

@@ -77,6 +77,11 @@ def test_report_classification_and_perf_summary(tmp_path):
     assert report.classify_trial(ok, dict(ok, impl="ours"), {"ok": True, "kind": "match"})["result"] == "match"
     assert report.classify_trial(ok, dict(ok, impl="ours"), {"ok": False, "kind": "tensor_mismatch"})["result"] == "tensor_mismatch"
     assert report.classify_trial(dict(ok, interrupted=True), ok, None)["result"] == "interrupted"
+    # outputs were saved and compare equal, but the candidate job failed afterwards (guard band, determinism, timing loop)
+    late = dict(ok, impl="ours", returncode=4)
+    assert report.classify_trial(ok, late, {"ok": True, "kind": "match"})["result"] == "candidate_failed"
+    assert report.classify_trial(ok, dict(ok, impl="ours", timed_out=True, returncode=-9), {"ok": True, "kind": "match"})["result"] == "candidate_failed"
+    assert report.classify_trial(dict(ok, returncode=1), dict(ok, impl="ours"), {"ok": True, "kind": "match"})["result"] == "reference_failed"
     assert report.environment_hint("OSError: [Errno 98] Address already in use")
     for r, ms in enumerate((1.0, 3.0)):
         with open(tmp_path / f"rank_{r}_perf.json", "w") as fh:
@@ -112,3 +117,54 @@ def test_hygiene_removes_only_segments_of_dead_owners(tmp_path):
     assert sorted(os.path.basename(p) for p in removed) == sorted([dead.name, odd.name])
     assert mine.exists() and not dead.exists()
     assert set(hygiene.gpu_health()) >= {"ok", "gpus", "detail"}
+
+
+def test_nan_in_either_output_is_a_mismatch():
+    import torch
+
+    from parallelkernelbench_b200.harness import compare
+
+    a = torch.tensor([1.0, float("nan"), 3.0])
+    assert not compare.compare_objects(a, a.clone())["ok"]              # NaN on both sides is still a failure
+    assert not compare.compare_objects(torch.tensor([1.0, 2.0, 3.0]), a)["ok"]
+    assert compare.compare_objects(torch.tensor([1.0, 2.0]), torch.tensor([1.0, 2.0]))["ok"]
+
+
+
+def test_loose_gate_must_be_earned_against_the_fp32_result(tmp_path, monkeypatch):
+    """A candidate outside 1e-2/1e-2 of the bf16 reference passes only if the op's gate holds AND it is at most twice as far
+    from the fp32 result as the reference is; a candidate that merely fits the loose gate fails."""
+    import torch
+
+    from parallelkernelbench_b200.harness import compare, launch
+
+    torch.manual_seed(0)
+    exact = torch.randn(4096) * 20
+    ref = exact.to(torch.bfloat16)                                    # one rounding
+    good = (exact + 0.3 * (exact.abs() / 256) * torch.sign(torch.randn(4096))).to(torch.bfloat16)   # a comparable error
+    sloppy = (exact + 0.4).to(torch.bfloat16)                         # inside atol 0.5, but four times the reference's error
+
+    def job(name, t):
+        d = tmp_path / name
+        compare.save_output(t, str(d), 0)
+        return {"impl": name, "returncode": 0, "artifact_count": 1, "job_dir": str(d)}
+
+    ref_job, good_job, sloppy_job = job("reference", ref), job("good", good), job("sloppy", sloppy)
+    calls = []
+
+    def fake_run_job(op, impl, nproc, trial=0, **kw):
+        calls.append(impl)
+        return dict(job(f"oracle{len(calls)}", exact), stderr="")
+
+    monkeypatch.setattr(launch, "run_job", fake_run_job)
+    cmp, gate = launch._gate("x", 1, 0, ref_job, job("same", ref.clone()), 0.5, 2e-2, True, {})
+    assert cmp["ok"] and gate["gate"] == "strict" and calls == []     # the fp32 run is only made when it is needed
+    tiny = ref.float().clone()
+    tiny[ref.float().abs() < 0.5] += 0.02                             # near zero, 0.02 breaks atol 1e-2 but is within bf16 noise elsewhere
+    cmp, gate = launch._gate("x", 1, 0, ref_job, good_job, 0.5, 2e-2, True, {})
+    if gate["gate"] == "oracle":
+        assert cmp["ok"] and gate["oracle_ok"]
+    cmp, gate = launch._gate("x", 1, 0, ref_job, sloppy_job, 0.5, 2e-2, True, {})
+    assert gate["gate"] == "oracle" and not gate["oracle_ok"] and not cmp["ok"]
+    cmp, gate = launch._gate("x", 1, 0, ref_job, sloppy_job, 0.5, 2e-2, False, {})
+    assert cmp["ok"] and gate["gate"] == "op_override_unverified"     # without the fp32 run the record says so
