@@ -11,16 +11,23 @@ configuration. One step = one forward of the block = two fused kernel launches.
         --master-port 29500 bench.py --gpus 8 --steps 50 --warmup 10
 
 Rank 0 prints ONE JSON line. ``value`` is rows (tokens) per second summed over all GPUs, device
-timed with CUDA events as the max over ranks. The same line carries the time of the PyTorch + NCCL
-+ cuBLAS implementation of the block measured in the same process with the same protocol
-(``ref_ms_per_step``, ``speedup_vs_ref``), the fraction of the compute roofline, an end-to-end
-number that includes the host->device copy of every step's input and a device->host read of a
-result metric, the clocks seen during the timed region, and the number of our kernels launched.
+timed with CUDA events as the max over ranks. Before anything is timed the block's output is compared,
+on every rank, with the PyTorch + NCCL + cuBLAS implementation of the same block (``max_abs_err``,
+``correct``; a mismatch makes the run exit 1). The same line carries the time of that implementation
+measured in the same process with the same protocol (``ref_ms_per_step``, ``speedup_vs_ref``), the
+fraction of the compute roofline (against the measured burst peak when the timed window is shorter than
+a second, the sustained one otherwise - ``roofline_peak.kind`` says which), a repeat of the measurement
+over at least 1.5 s with the clocks sampled inside it (``sustained``), an end-to-end number that includes
+the host->device copy of every step's input and a device->host read of a result metric, and the number
+of our kernels launched. ``--suite`` adds the other headline configurations (expert-parallel MoE layer,
+ring attention forward + backward, FSDP Llama step) as extra keys, each checked against and timed next to
+its PyTorch + NCCL implementation.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import sys
 import time
@@ -41,21 +48,62 @@ def parse_args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-ref", action="store_true", help="skip timing the in-repo PyTorch+NCCL implementation")
     ap.add_argument("--comm-ctas", type=int, default=0)
+    ap.add_argument("--sustained-sec", type=float, default=1.5, help="length of the repeat measurement with clock samples (0: skip)")
+    ap.add_argument("--wait-stats", action="store_true", help="report how long the GEMM's producers waited for gathered rows")
+    ap.add_argument("--suite", action="store_true", help="also run the MoE, ring-attention and Llama headline configurations")
+    ap.add_argument("--suite-only", default="", help="comma-separated subset of 3,4,5 for --suite")
+    ap.add_argument("--suite-warmup", type=int, default=3)
+    ap.add_argument("--suite-iters", type=int, default=10)
     return ap.parse_args()
 
 
 def reference_arm() -> int:
-    # The upstream tree is a flat collection of scripts without installable packages: the offline
-    # `pip install --target baseline/_ref` stops in metadata generation (setuptools refuses
-    # automatic discovery over several top-level packages), with and without --no-deps and from a
-    # writable copy. Nothing of it is importable from baseline/_ref, so this arm cannot run.
+    """The upstream tree cannot produce this metric on this configuration through its own code path.
+
+    It is a flat collection of scripts, so the offline ``pip install --target baseline/_ref`` stops in
+    metadata generation ("Multiple top-level packages discovered in a flat-layout"), with and without
+    ``--no-deps`` and from a writable copy; ``baseline/_ref`` therefore holds a plain copy of its
+    ``reference/``, ``utils/`` and ``run_local.py``. That copy imports, but its input factory fixes the
+    tensor-parallel MLP workload (problem 15) at hidden 256 and FFN 512 with the weights replicated on
+    every rank (utils/input_output_tensors.py:369-378) and exposes no parameter for them, and problem 45
+    (reduce-scatter + RMSNorm) is a separate problem with its own inputs: the block of this benchmark -
+    rows 2048 per rank, hidden 8192, FFN 28672 sharded over the ranks - cannot be expressed without
+    modifying it."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    why = ("reference is not pip-installable offline: setuptools metadata generation fails on its flat "
-           "multi-package layout (no build configuration), so baseline/_ref is empty")
-    if os.path.isdir(ref_dir) and any(os.scandir(ref_dir)):
-        why = "baseline/_ref exists but the reference ships no importable package or benchmark entry point for this config"
+    have = os.path.isfile(os.path.join(ref_dir, "utils", "input_output_tensors.py"))
+    why = ("the reference's stock input factory hard-codes its TP-MLP workload (problem 15) to hidden 256 / FFN 512 with replicated "
+           "weights and keeps reduce-scatter+RMSNorm as a separate problem, so hidden 8192 / FFN 28672 sharded over the ranks cannot "
+           "be run unmodified; pip install --target fails in metadata generation (flat multi-package layout), baseline/_ref is "
+           + ("a plain copy" if have else "absent"))
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
+
+
+def _numa_pin(dev_index: int) -> dict:
+    """Bind this process (and hence the pinned host buffers it allocates next) to the NUMA node of its GPU. Read-only with
+    respect to the GPU; silently does nothing where /sys does not expose the topology."""
+    import torch
+
+    info = {"numa_node": None, "cpus": None}
+    try:
+        p = torch.cuda.get_device_properties(dev_index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as fh:
+            node = int(fh.read().strip())
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0) & cpus
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+            info = {"numa_node": node, "cpus": len(allowed)}
+    except (OSError, ValueError, AttributeError):
+        pass
+    return info
 
 
 def main() -> int:
@@ -75,23 +123,51 @@ def main() -> int:
     from parallelkernelbench_b200.utils.clocks import ClockSampler
     from parallelkernelbench_b200.utils.env import measured_peaks
 
+    suite_cfgs = []
+    if args.suite:
+        from parallelkernelbench_b200.harness import suite as suite_mod
+
+        suite_cfgs = suite_mod.select(args.suite_only)
+        os.environ["PKB_HEAP_GIB"] = str(max(float(os.environ.get("PKB_HEAP_GIB", "1")),
+                                             suite_mod.heap_gib(suite_cfgs, int(os.environ.get("WORLD_SIZE", "1")))))
     os.environ.setdefault("PKB_HEAP_GIB", "1")
     ctx = init_context()
     W, rank, dev = ctx.world, ctx.rank, ctx.device
     if W != args.gpus and rank == 0:
         print(f"[bench] note: --gpus {args.gpus} but WORLD_SIZE={W}; using {W}", file=sys.stderr)
+    numa = _numa_pin(dev.index)          # before any pinned host allocation
     heap = ctx.heap()
     group = heap.world_group
 
     cfg = TPMLPConfig(rows_per_rank=ROWS_PER_RANK, hidden=HIDDEN, ffn=FFN)
     w1, w2, gamma = TPMLPBlock.random_weights(cfg, W, rank, dev)
     block = TPMLPBlock(group, cfg, w1, w2, gamma, comm_ctas=args.comm_ctas)
+    ref = TPMLPReference(W, ROWS_PER_RANK, HIDDEN, w1, w2, gamma, cfg.eps)
 
     # a rotation of input buffers (the per-step working set, weights + activations, is already far
     # larger than the 126 MB L2; rotating the inputs additionally defeats any reuse across steps)
     n_inputs = 4
     gen = torch.Generator(device=dev).manual_seed(4242 + rank)
     xs = [torch.randn(ROWS_PER_RANK, HIDDEN, device=dev, dtype=torch.bfloat16, generator=gen) for _ in range(n_inputs)]
+
+    def all_max(v: float) -> float:
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        if W > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---------------------------------------------------------------- correctness, outside every timed region
+    # both implementations on the same input, on every rank; the gate is the harness's (1e-2 relative on a normalised
+    # output of unit scale, plus the bf16 rounding of the three stages the PyTorch formulation rounds separately)
+    y_ours = block(xs[0]).float().clone()
+    y_ref = ref(xs[0]).float()
+    nv.raise_on_status(sync=True)
+    err = (y_ours - y_ref).abs()
+    max_abs_err = all_max(float(err.max()))
+    bad = all_max(float((err > 6e-2 + 3e-2 * y_ref.abs()).float().mean()))
+    finite = all_max(0.0 if bool(torch.isfinite(y_ours).all()) else 1.0) == 0.0
+    correct = finite and bad == 0.0
+    del y_ours, y_ref, err
 
     def timed(fn, steps: int, warmup: int):
         for i in range(warmup):
@@ -108,27 +184,58 @@ def main() -> int:
         torch.cuda.synchronize()
         ctx.barrier()
         torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        if W > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), nv.launches() - launches0
+        return all_max(e0.elapsed_time(e1) / steps), nv.launches() - launches0
+
+    wait_buf = None
+    if args.wait_stats:
+        wait_buf = torch.zeros(256, device=dev, dtype=torch.int64)
+        nv.check(nv.cuda_lib().pkb_tp_ag_gemm_set_wait_stats(nv.ptr(wait_buf)), "pkb_tp_ag_gemm_set_wait_stats")
 
     # ---------------------------------------------------------------- device-timed headline
-    sampler = ClockSampler(gpu_index=ctx.local_rank, period_ms=50).start() if rank == 0 else None
+    sampler = ClockSampler(device=dev, period_ms=50).start() if rank == 0 else None
     ms_ours, launches = timed(lambda i: block(xs[i % n_inputs]), args.steps, args.warmup)
     if sampler is not None:
-        time.sleep(0.25)
+        time.sleep(0.1)
         sampler.stop()
         clocks = sampler.summary()
+        clocks["window"] = "headline timed region (includes its warm-up)"
     else:
         clocks = None
     nv.raise_on_status(sync=True)
 
+    wait_stats = None
+    if wait_buf is not None:
+        nv.check(nv.cuda_lib().pkb_tp_ag_gemm_set_wait_stats(nv.ptr(None)), "pkb_tp_ag_gemm_set_wait_stats")
+        w = wait_buf.cpu().tolist()
+        calls = args.steps + args.warmup
+        per_call_us = sorted(c / calls / 1.9e3 for c in w if c > 0)       # cycles -> microseconds at ~1.9 GHz
+        wait_stats = {"ctas_that_waited": len(per_call_us), "calls": calls,
+                      "wait_us_per_call_median": per_call_us[len(per_call_us) // 2] if per_call_us else 0.0,
+                      "wait_us_per_call_max": per_call_us[-1] if per_call_us else 0.0,
+                      "note": "SM cycles the GEMM's TMA producers spent waiting for rows from the peers, per CTA and call, at 1.9 GHz"}
+
+    # ---------------------------------------------------------------- the same measurement over >= sustained-sec
+    sustained = None
+    if args.sustained_sec > 0:
+        n_sus = max(args.steps, int(math.ceil(args.sustained_sec * 1e3 / ms_ours)))
+        s2 = ClockSampler(device=dev, period_ms=50).start() if rank == 0 else None
+        ms_sus, _ = timed(lambda i: block(xs[i % n_inputs]), n_sus, 3)
+        if s2 is not None:
+            s2.stop()
+            sus_clocks = s2.summary()
+        else:
+            sus_clocks = None
+        nv.raise_on_status(sync=True)
+        sustained = {"ms_per_step": ms_sus, "steps": n_sus, "clocks": sus_clocks}
+        if clocks is not None and clocks.get("samples", 0) < 10 and sus_clocks is not None:
+            # the headline window is too short to be sampled: describe the clocks by the long repeat of the same kernels
+            clocks = dict(sus_clocks, window=f"repeat of the same step for {n_sus} steps directly after the headline window "
+                                             f"(the {args.steps}-step window itself held {clocks.get('samples', 0)} samples)")
+
     # ---------------------------------------------------------------- end to end through the public API
     # every step: H2D copy of the step's input from pinned host memory (copy stream, double
     # buffered so it overlaps the previous step's kernels), forward, a scalar result metric, and its
-    # D2H read into pinned memory.
+    # D2H read into pinned memory. The host buffers were allocated after binding to the GPU's NUMA node.
     host_x = [torch.randn(ROWS_PER_RANK, HIDDEN, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
     dev_x = [torch.empty(ROWS_PER_RANK, HIDDEN, device=dev, dtype=torch.bfloat16) for _ in range(2)]
     host_metric = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -139,12 +246,21 @@ def main() -> int:
     for ev in compute_done:
         ev.record(main_stream)
 
-    def e2e_step(i: int):
+    def prefetch(i: int):
         b = i & 1
         with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(compute_done[b])
+            copy_stream.wait_event(compute_done[b])        # the step that last read this buffer has finished
             dev_x[b].copy_(host_x[b], non_blocking=True)
             h2d_done[b].record(copy_stream)
+
+    prefetch(0)
+    step_no = [0]
+
+    def e2e_step(_i: int):
+        i = step_no[0]
+        step_no[0] = i + 1
+        b = i & 1
+        prefetch(i + 1)                                    # the next step's input travels while this step computes
         main_stream.wait_event(h2d_done[b])
         y = block(dev_x[b])
         metric = y.float().pow(2).mean().reshape(1)
@@ -155,21 +271,39 @@ def main() -> int:
     nv.raise_on_status(sync=True)
     h2d_bytes = ROWS_PER_RANK * HIDDEN * 2
     d2h_bytes = 4
+    # the host->device rate all ranks reach together when nothing else runs (explains, or rules out, a copy-bound step)
+    torch.cuda.synchronize()
+    ctx.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(8):
+        dev_x[i & 1].copy_(host_x[i & 1], non_blocking=True)
+    e1.record()
+    torch.cuda.synchronize()
+    h2d_gbs = 8 * h2d_bytes / (all_max(e0.elapsed_time(e1)) * 1e-3) / 1e9
 
     # ---------------------------------------------------------------- PyTorch + NCCL + cuBLAS implementation
     ms_ref = None
     if not args.no_ref:
         time.sleep(float(os.environ.get("PKB_COOLDOWN_SEC", "0.5")))
-        ref = TPMLPReference(W, ROWS_PER_RANK, HIDDEN, w1, w2, gamma, cfg.eps)
         ms_ref, _ = timed(lambda i: ref(xs[i % n_inputs]), args.steps, args.warmup)
 
     peaks = measured_peaks()
     flops_per_gpu = 4.0 * (W * ROWS_PER_RANK) * HIDDEN * (FFN // W)
     tflops = flops_per_gpu / (ms_ours * 1e-3) / 1e12
-    peak = float(peaks.get("bf16_tflops_sustained") or peaks.get("bf16_tflops"))
+    window_s = ms_ours * 1e-3 * args.steps
+    burst, sus_peak = peaks.get("bf16_tflops"), peaks.get("bf16_tflops_sustained")
+    if window_s < 1.0 and burst:
+        peak, kind = float(burst), "burst cuBLAS bf16 (of measured): the timed window is shorter than 1 s"
+    else:
+        peak, kind = float(sus_peak or burst), "sustained cuBLAS bf16 (of measured): the timed window is 1 s or longer"
     # per GPU and per direction: (W-1) activation shards gathered + (W-1) partial row blocks scattered
     nvlink_bytes_per_dir = 2.0 * (W - 1) * ROWS_PER_RANK * HIDDEN * 2
     roofline_ms = max(flops_per_gpu / (peak * 1e12), nvlink_bytes_per_dir / 770e9) * 1e3
+    if sustained is not None:
+        p_s = float(sus_peak or burst)
+        sustained["tflops_per_gpu"] = flops_per_gpu / (sustained["ms_per_step"] * 1e-3) / 1e12
+        sustained["pct_roofline_of_sustained_peak"] = 100.0 * max(flops_per_gpu / (p_s * 1e12), nvlink_bytes_per_dir / 770e9) * 1e3 / sustained["ms_per_step"]
     tokens = W * ROWS_PER_RANK
     out = {
         "metric": "tp_mlp_block_tokens_per_s",
@@ -188,21 +322,39 @@ def main() -> int:
         "config": {"model": "tp_mlp_block(AG->GEMM->SiLU->GEMM->RS->RMSNorm)", "global_batch": tokens,
                    "seq_len": ROWS_PER_RANK, "hidden": HIDDEN, "ffn": FFN, "parallelism": f"tp{W}",
                    "l2_policy": "inputs larger than L2 (weights+activations per step >> 126 MB) and 4 rotating input buffers"},
+        "correct": correct,
+        "max_abs_err": max_abs_err,
+        "checked_against": "in-repo PyTorch + NCCL + cuBLAS implementation, every rank, same input, outside the timed regions",
         "tflops_per_gpu": tflops,
         "pct_roofline": 100.0 * roofline_ms / ms_ours,
         "roofline_ms": roofline_ms,
-        "roofline_peak": {"bf16_tflops": peak, "source": peaks.get("source"), "kind": "sustained cuBLAS bf16 (of measured)"},
+        "roofline_peak": {"bf16_tflops": peak, "source": peaks.get("source"), "kind": kind},
+        "sustained": sustained,
         "ref_ms_per_step": ms_ref,
         "speedup_vs_ref": (ms_ref / ms_ours) if ms_ref else None,
         "ref_impl": "in-repo PyTorch + NCCL + cuBLAS implementation of the same block, same timing protocol",
         "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d_bytes * W, "d2h_bytes_per_step": d2h_bytes * W},
+                "h2d_bytes_per_step": h2d_bytes * W, "d2h_bytes_per_step": d2h_bytes * W,
+                "h2d_gbs_per_rank_all_ranks_copying": h2d_gbs, "numa": numa,
+                "note": "input of step i+1 is copied on a second stream while step i computes"},
         "gpu_launches": launches,
         "clocks": clocks,
     }
+    if wait_stats is not None:
+        out["a_ready_wait"] = wait_stats
+
+    if args.suite:
+        del block, ref, xs, dev_x
+        torch.cuda.empty_cache()
+        out["suite"] = suite_mod.run(ctx, suite_cfgs, warmup=args.suite_warmup, iters=args.suite_iters)
+
     ctx.finalize()
     if rank == 0:
         print(json.dumps(out))
+    if not correct:
+        if rank == 0:
+            print(f"[bench] MISMATCH against the PyTorch+NCCL implementation: max abs err {max_abs_err}", file=sys.stderr)
+        return 1
     return 0
 
 

@@ -1,0 +1,223 @@
+"""Single-GPU kernel timings against the library kernel for the same work.
+
+    python -m parallelkernelbench_b200.harness.microbench <case> [<case> ...] [--iters N] [--warmup W] [--json FILE]
+
+Every case times one of our kernels and, where a library kernel for the same arithmetic exists, that kernel too
+(cuBLAS through ``torch.matmul``, the fused attention behind ``scaled_dot_product_attention``), with the same protocol:
+``warmup`` untimed calls, then ``iters`` calls each bracketed by its own pair of CUDA events with a write of a buffer
+larger than L2 between calls (so no call finds its inputs cached), mean and minimum reported. One JSON line per case:
+``{"case", "ours_ms", "lib_ms", "ours_tflops", "lib_tflops", "ratio_vs_lib", ...}`` with the fraction of the measured bf16
+peak where the case is a contraction.
+
+Cases: ``gemm`` (8192^3 bf16), ``fa_fwd`` / ``fa_bwd`` (sequence 16384, causal, 32 query / 8 KV heads, head dim 128),
+``fa_fwd_4k``, ``grouped_bf16`` / ``grouped_fp8`` (32 experts x 2048 rows, 7168 -> 4096 gate/up with SwiGLU: the expert GEMM of
+the 256-expert MoE configuration per rank), ``rmsnorm``, ``fp8_quant``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+
+class _Timer:
+    def __init__(self, warmup: int, iters: int):
+        self.warmup, self.iters = warmup, iters
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")       # 2x the 126 MB L2
+
+    def __call__(self, fn) -> dict:
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        ms = []
+        for _ in range(self.iters):
+            self.flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        return {"mean_ms": sum(ms) / len(ms), "min_ms": min(ms)}
+
+
+def _peaks() -> dict:
+    from ..utils.env import measured_peaks
+
+    return measured_peaks()
+
+
+def _line(case: str, ours: dict, lib: dict | None, flops: float = 0.0, bytes_moved: float = 0.0, **extra) -> dict:
+    out = {"case": case, "ours_ms": ours["mean_ms"], "ours_min_ms": ours["min_ms"]}
+    if lib is not None:
+        out.update({"lib_ms": lib["mean_ms"], "lib_min_ms": lib["min_ms"], "ratio_vs_lib": lib["mean_ms"] / ours["mean_ms"]})
+    pk = _peaks()
+    if flops:
+        out["ours_tflops"] = flops / (ours["mean_ms"] * 1e-3) / 1e12
+        if lib is not None:
+            out["lib_tflops"] = flops / (lib["mean_ms"] * 1e-3) / 1e12
+        if pk.get("bf16_tflops"):
+            out["frac_of_measured_bf16_burst_peak"] = out["ours_tflops"] / float(pk["bf16_tflops"])
+    if bytes_moved:
+        out["ours_gbs"] = bytes_moved / (ours["mean_ms"] * 1e-3) / 1e9
+        if pk.get("hbm_gbs"):
+            out["frac_of_measured_copy_bandwidth"] = out["ours_gbs"] / float(pk["hbm_gbs"])
+    out.update(extra)
+    return out
+
+
+def case_gemm(t: _Timer) -> dict:
+    from ..ops import gemm_bf16
+
+    n = 8192
+    a = torch.randn(n, n, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, n, device="cuda", dtype=torch.bfloat16) * 0.02
+    out = torch.empty(n, n, device="cuda", dtype=torch.bfloat16)
+    ours = t(lambda: gemm_bf16(a, w, out=out))
+    wt = w.t()
+    lib = t(lambda: torch.matmul(a, wt, out=out))
+    return _line("gemm", ours, lib, flops=2.0 * n ** 3, shape=[n, n, n])
+
+
+def _attn_inputs(S, hq=32, hkv=8, d=128):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    mk = lambda h: torch.randn(1, S, h, d, device="cuda", dtype=torch.bfloat16, generator=g)  # noqa: E731
+    return mk(hq), mk(hkv), mk(hkv), mk(hq)
+
+
+def _fa_fwd(t: _Timer, S: int, name: str) -> dict:
+    import torch.nn.functional as F
+
+    from ..ops.attention import flash_attn_fwd
+
+    q, k, v, _ = _attn_inputs(S)
+    ours = t(lambda: flash_attn_fwd(q, k, v, causal=True))
+    qt, kt, vt = (x.transpose(1, 2) for x in (q, k, v))            # [B, H, S, D] views: the layout the library call takes
+    lib = t(lambda: F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True))
+    o_ours = flash_attn_fwd(q, k, v, causal=True)[0]
+    o_lib = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True).transpose(1, 2)
+    err = float((o_ours.float() - o_lib.float()).abs().max())
+    flops = 4.0 * S * S * 32 * 128 / 2                               # causal: half of the score matrix
+    return _line(name, ours, lib, flops=flops, seq=S, heads="32/8", head_dim=128, max_abs_diff_vs_lib=err)
+
+
+def case_fa_fwd(t):
+    return _fa_fwd(t, 16384, "fa_fwd")
+
+
+def case_fa_fwd_4k(t):
+    return _fa_fwd(t, 4096, "fa_fwd_4k")
+
+
+def case_fa_bwd(t: _Timer) -> dict:
+    import torch.nn.functional as F
+
+    from ..ops.attention import flash_attn_bwd, flash_attn_fwd
+
+    S = 16384
+    q, k, v, do = _attn_inputs(S)
+    out, lse = flash_attn_fwd(q, k, v, causal=True)
+    ours = t(lambda: flash_attn_bwd(q, k, v, out, lse, do, causal=True))
+    qt, kt, vt = (x.transpose(1, 2).detach().requires_grad_(True) for x in (q, k, v))
+    dot = do.transpose(1, 2)
+
+    def lib_step():
+        with torch.enable_grad():
+            o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True, enable_gqa=True)
+        return o
+
+    o = lib_step()
+
+    def lib_bwd():
+        torch.autograd.grad(o, (qt, kt, vt), dot, retain_graph=True)
+
+    lib = t(lib_bwd)
+    flops = 10.0 * S * S * 32 * 128 / 2
+    return _line("fa_bwd", ours, lib, flops=flops, seq=S, heads="32/8", head_dim=128)
+
+
+def _grouped_shapes():
+    G, rows, H, I2 = 32, 2048, 7168, 4096
+    offs = (torch.arange(G + 1, dtype=torch.int32) * rows).cuda()
+    return G, rows, H, I2, offs
+
+
+def case_grouped_bf16(t: _Timer) -> dict:
+    from ..ops.moe import grouped_gemm
+
+    G, rows, H, I2, offs = _grouped_shapes()
+    a = torch.randn(G * rows, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(G, I2, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    out = torch.empty(G * rows, I2 // 2, device="cuda", dtype=torch.bfloat16)
+    ours = t(lambda: grouped_gemm(a, w, offs, epilogue="swiglu", out=out))
+    return _line("grouped_bf16", ours, None, flops=2.0 * G * rows * H * I2, groups=G, rows_per_group=rows, k=H, n=I2)
+
+
+def case_grouped_fp8(t: _Timer) -> dict:
+    from ..ops.gemm_fp8 import gemm_fp8_blockscaled
+    from ..refs.gemm_fp8 import quantize_rows_1x128, quantize_weight_128x128
+
+    G, rows, H, I2, offs = _grouped_shapes()
+    a8, sa = quantize_rows_1x128(torch.randn(G * rows, H, device="cuda"))
+    w8, sb = quantize_weight_128x128(torch.randn(G, I2, H, device="cuda") * 0.02)
+    out = torch.empty(G * rows, I2 // 2, device="cuda", dtype=torch.uint8)
+    osc = torch.empty(G * rows, I2 // 256, device="cuda", dtype=torch.float32)
+    ours = t(lambda: gemm_fp8_blockscaled(a8, sa, w8, sb, offsets=offs, epilogue="swiglu_quant", out=out, out_scales=osc))
+    return _line("grouped_fp8", ours, None, flops=2.0 * G * rows * H * I2, groups=G, rows_per_group=rows, k=H, n=I2,
+                 note="e4m3 operands, fp32 1x128 / 128x128 scales, SwiGLU + 1x128 re-quantise epilogue")
+
+
+def case_rmsnorm(t: _Timer) -> dict:
+    from ..ops import rmsnorm
+
+    x = torch.randn(16384, 8192, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(8192, device="cuda", dtype=torch.bfloat16)
+    ours = t(lambda: rmsnorm(x, g))
+    lib = t(lambda: torch.nn.functional.rms_norm(x, (8192,), g, 1e-6))
+    return _line("rmsnorm", ours, lib, bytes_moved=2.0 * x.numel() * 2)
+
+
+def case_fp8_quant(t: _Timer) -> dict:
+    from ..ops import fp8_quantize_1x128
+
+    x = torch.randn(16384, 8192, device="cuda", dtype=torch.bfloat16)
+    ours = t(lambda: fp8_quantize_1x128(x))
+    return _line("fp8_quant", ours, None, bytes_moved=x.numel() * (2 + 1 + 4 / 128))
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("cases", nargs="+")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--json", default=None, help="append the result lines to this file as well")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("microbench needs a GPU", file=sys.stderr)
+        return 2
+    from .. import _native as nv
+
+    t = _Timer(max(3, a.warmup), a.iters)
+    rc = 0
+    for name in a.cases:
+        fn = globals().get("case_" + name)
+        if fn is None:
+            print(f"unknown case {name}", file=sys.stderr)
+            rc = 2
+            continue
+        res = fn(t)
+        nv.raise_on_status(sync=True)
+        res = {k: (round(v, 5) if isinstance(v, float) and math.isfinite(v) else v) for k, v in res.items()}
+        line = json.dumps(res)
+        print(line, flush=True)
+        if a.json:
+            with open(a.json, "a") as fh:
+                fh.write(line + "\n")
+    return rc
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -179,7 +179,7 @@ def run_worker(args) -> int:
                 try:
                     from ..utils.clocks import ClockSampler
 
-                    sampler = ClockSampler(gpu_index=getattr(ctx, "local_rank", ctx.rank), period_ms=100).start()
+                    sampler = ClockSampler(device=ctx.device, period_ms=100).start()
                 except Exception:
                     sampler = None
             with torch.no_grad():

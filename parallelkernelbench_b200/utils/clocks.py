@@ -19,9 +19,26 @@ _QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,
           "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
 
+def gpu_selector(device=None, gpu_index: int = 0) -> str:
+    """What to pass to ``nvidia-smi -i`` for a torch device: its UUID. ``nvidia-smi`` numbers physical GPUs, a process
+    numbers the GPUs it can see, so under CUDA_VISIBLE_DEVICES an index would select somebody else's GPU."""
+    if device is not None:
+        try:
+            import torch
+
+            return "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+        except Exception:
+            pass
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+    ids = [v.strip() for v in vis.split(",") if v.strip()]
+    if ids and gpu_index < len(ids):
+        return ids[gpu_index]                 # a physical index or a UUID: both are accepted by -i
+    return str(gpu_index)
+
+
 class ClockSampler:
-    def __init__(self, gpu_index: int = 0, period_ms: int = 200, path: str | None = None):
-        self.gpu_index = gpu_index
+    def __init__(self, gpu_index: int = 0, period_ms: int = 200, path: str | None = None, device=None):
+        self.gpu_index = gpu_selector(device, gpu_index)
         self.period_ms = period_ms
         self.path = path or os.path.join(tempfile.gettempdir(), f"pkb_clocks_{os.getpid()}.csv")
         self.proc = None
