@@ -26,7 +26,10 @@ extern "C" {
 // library routine that allocates.
 //
 // * The first call on a device looks up the device address of that array (once per device, with
-//   that device current). Make this first call before any stream capture begins.
+//   that device current). With lazy module loading that lookup can also be what makes the driver
+//   load the library's device code and back the array with memory, so "allocates nothing" holds
+//   from the second call on each device: make the first call during warm-up, before the region in
+//   which allocation is forbidden and before any stream capture begins.
 // * Every call uses the same array. Two calls whose kernels may overlap on the GPU (different
 //   streams, or different host threads without ordering) race on it: serialise them.
 // * Nothing in the array has to start at zero; each call overwrites the entries it reads.

@@ -38,7 +38,10 @@ def test_noalloc_cross_entropy_matches_existing_entry_point_twice():
 
     lib = nv.cuda_lib()
     g = torch.Generator(device="cuda").manual_seed(2024)
-    for rows, vocab, dtype in ((777, 4096, torch.bfloat16), (33, 1000, torch.float32)):
+    # 5000 x 257: more rows than the kernel's grid has blocks (its row loop strides) and an odd vocabulary;
+    # 65536 x 8: exactly the capacity of the scratch array
+    for rows, vocab, dtype in ((777, 4096, torch.bfloat16), (33, 1000, torch.float32), (5000, 257, torch.float32),
+                               (65536, 8, torch.bfloat16)):
         logits = (torch.randn(rows, vocab, device="cuda", generator=g) * 3).to(dtype)
         target = torch.randint(0, vocab, (rows,), device="cuda", generator=g)
         got = _noalloc(lib, logits, target)
