@@ -959,6 +959,408 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
   }
 }
 
+// ================================================================================================
+// Two Q tiles per CTA, P kept in tensor memory.
+// The S = Q K^T and O += P V products of a 128 x 128 x 128 step each read 64 KiB of operands from shared memory in the
+// 512 cycles they take, which is the whole shared-memory bandwidth of the SM: with P also written to and read from shared
+// memory the tensor core cannot be kept busy. Here the softmax thread of a row reads its 128 scores with ONE round of
+// tcgen05.ld (the row stays in registers, so S is read once, not twice), and writes the bf16 probabilities back into the
+// first 64 columns of the same TMEM buffer with tcgen05.st; the P V product takes its A operand from there
+// (tcgen05.mma with A in tensor memory). Shared memory then only feeds K, V and Q, and the 64 KiB that P occupied hold a
+// second stage of K and V, so the loads of tile j+1 run under the products of tile j.
+//   warp 0       TMA producer: Q0, Q1 once; K and V through two-stage rings
+//   warp 1       MMA issuer, per KV tile j:  O_0 += P_0(j-1) V(j-1);  S_0 = Q_0 K(j)^T;  O_1 += P_1(j-1) V(j-1);  S_1 = Q_1 K(j)^T
+//                (S_t(j) overwrites P_t(j-1); products of one thread execute in issue order, so no extra wait is needed)
+//   warps 4-7    softmax of tile 0, warps 8-11 softmax of tile 1 (thread = row; more registers via setmaxnreg)
+//   warps 12-15  correction: scale O_t in TMEM by alpha when a row's offset moved (rare: the offset follows the maximum lazily)
+// ================================================================================================
+template <int D>
+struct Fa3Smem {
+  static constexpr int kTileBytes = kFaTile * D * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kQ = 0;                               // two tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;             // kStages tiles
+  static constexpr int kV = kK + kStages * kTileBytes;       // kStages tiles
+  static constexpr int kAlpha = kV + kStages * kTileBytes;   // [2][128] fp32
+  static constexpr int kBars = kAlpha + 2 * kFaTile * 4;
+  static constexpr int kTotal = kBars + 512;
+};
+
+// register budgets per warpgroup after the prologue (the kernel is compiled for 128 per thread: 512 x 128 = the whole file)
+constexpr int kFa3RegsIo = 80, kFa3RegsSoftmax = 168, kFa3RegsCorr = 80;
+static_assert(128 * kFa3RegsIo + 256 * kFa3RegsSoftmax + 128 * kFa3RegsCorr <= 65536, "register budgets exceed the register file");
+
+template <int D>
+__device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                            const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
+                                            const int head, const int batch) {
+  using S = Fa3Smem<D>;
+  constexpr int kAtoms = D / 64;
+  constexpr int kAtomBytes = kFaTile * 128;
+  constexpr int kStages = S::kStages;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = smem_u32(smem);
+  const pkb_attn_desc& d = p.d;
+
+  const uint32_t bar0 = sb + S::kBars;
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
+  auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
+  auto a_full = [&](int t) { return bar0 + 8u * (13 + t); };
+  auto a_empty = [&](int t) { return bar0 + 8u * (15 + t); };
+  auto o_scaled = [&](int t) { return bar0 + 8u * (17 + t); };
+  auto pv_done = [&](int t) { return bar0 + 8u * (19 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 22);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* alpha_s = reinterpret_cast<float*>(smem + S::kAlpha);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_head = head / (d.hq / d.hkv);
+  const int n_q_tiles = (d.sq + kFaTile - 1) / kFaTile;
+  const int qt0 = q_pair * 2;
+  const bool has1 = qt0 + 1 < n_q_tiles;
+  const int q_row0 = qt0 * kFaTile;
+  const int q_seg = q_row0 / d.q_seg_rows;
+  const int q_pos0 = d.q_seg_pos[q_seg] + (q_row0 - q_seg * d.q_seg_rows);   // both tiles lie in one segment
+  const int q_pos_last0 = q_pos0 + kFaTile - 1;
+  const int q_pos_last = q_pos_last0 + (has1 ? kFaTile : 0);
+  const int q_tok0 = batch * d.sq + q_row0;
+  const int kv_tok_base = batch * d.skv;
+  auto need0 = [&](int kp) { return !(d.causal && kp > q_pos_last0); };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if ((sb & 1023u) != 0) {
+      *abort_flag = 1;
+      record_status(p.status, kStatusBadArgument, 603, 0, 0, 1, 0);
+    }
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), 4);
+      mbar_init(a_full(t), 4); mbar_init(a_empty(t), 4);
+      mbar_init(o_scaled(t), 4); mbar_init(pv_done(t), 1);
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  auto tmem_s = [&](int t) { return tmem_base + t * 128; };      // S_t: 128 fp32 columns; P_t (bf16 pairs) reuses the first 64
+  auto tmem_o = [&](int t) { return tmem_base + 256 + t * D; };
+  const bool bad = *abort_flag != 0;
+
+  if (warp < 4) {
+    warpgroup_reg_dec<kFa3RegsIo>();
+    if (bad) {
+      // common exit
+    } else if (warp == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      if (lane == 0) {
+        mbar_expect_tx(q_full, (has1 ? 2 : 1) * S::kTileBytes);
+        for (int t = 0; t < (has1 ? 2 : 1); ++t)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kQ + t * S::kTileBytes + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0 + t * kFaTile);
+        bool ok = true;
+        int last_seg = -1;
+        for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
+          if (!ok) return;
+          const int st = j % kStages;
+          const uint32_t ph = (j / kStages) & 1;
+          if (seg != last_seg) {
+            last_seg = seg;
+            if (d.kv_seg_ready != nullptr && d.kv_seg_flag[seg] >= 0) {
+              if (!wait_flag_ge(d.kv_seg_ready + d.kv_seg_flag[seg], d.ready_epoch, p.budget_ns)) {
+                *abort_flag = 1;
+                record_status(p.status, kStatusPeerTimeout, 603, 0, seg, 10, j);
+                ok = false;
+                return;
+              }
+              fence_proxy_async_all();
+            }
+          }
+          if (!mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          mbar_expect_tx(k_full(st), S::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kK + st * S::kTileBytes + a * kAtomBytes, &tmap_k, k_full(st), a * 64, kv_head, kv_tok_base + row);
+          if (!mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          mbar_expect_tx(v_full(st), S::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kV + st * S::kTileBytes + a * kAtomBytes, &tmap_v, v_full(st), a * 64, kv_head, kv_tok_base + row);
+        });
+        if (!ok) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 11, 0);
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer ------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = make_idesc(kFaTile, kFaTile, 1, 1, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc(kFaTile, D, 1, 1, 0, 1);
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.budget_ns);
+        int pv[2] = {0, 0};         // P V products issued per tile
+        auto issue_s = [&](int t, int st) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+            umma_f16_ss(tmem_s(t), make_smem_desc_sw128_kmajor(sb + S::kQ + t * S::kTileBytes + off),
+                        make_smem_desc_sw128_kmajor(sb + S::kK + st * S::kTileBytes + off), idesc_s, k != 0);
+          }
+          umma_commit(s_full(t));
+        };
+        // O_t += P_t V: A = P_t from tensor memory (16 bf16 of K per step = 8 columns), B = V tile, MN-major
+        auto issue_pv = [&](int t, int st) {
+          if (!mbar_wait(p_full(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
+          if (!mbar_wait(o_scaled(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < kFaTile / 16; ++k) {
+            const uint64_t dv = make_smem_desc_sw128_mnmajor(sb + S::kV + st * S::kTileBytes + k * 2048, kAtomBytes);
+            umma_f16_ts(tmem_o(t), tmem_s(t) + k * 8, dv, idesc_o, (k != 0) || (pv[t] != 0));
+          }
+          umma_commit(pv_done(t));
+          ++pv[t];
+          return true;
+        };
+        int prev_kp = 0, prev_st = 0;
+        const int n = for_each_kv_tile(d, q_pos_last, [&](int j, int /*row*/, int kp, int /*valid*/, int /*seg*/) {
+          if (!ok) return;
+          const int st = j % kStages;
+          if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (j == 0) {
+            if (need0(kp)) issue_s(0, st);
+            if (has1) issue_s(1, st);
+            umma_commit(k_empty(st));
+            prev_kp = kp; prev_st = st;
+            return;
+          }
+          if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
+          if (need0(kp)) issue_s(0, st);
+          if (has1) {
+            if (!issue_pv(1, prev_st)) { ok = false; return; }
+            issue_s(1, st);
+          }
+          umma_commit(v_empty(prev_st));
+          umma_commit(k_empty(st));
+          prev_kp = kp; prev_st = st;
+        });
+        if (ok && n > 0) {
+          ok = mbar_wait(v_full(prev_st), ((n - 1) / kStages) & 1, abort_flag, p.budget_ns);
+          if (ok && need0(prev_kp)) ok = issue_pv(0, prev_st);
+          if (ok && has1) ok = issue_pv(1, prev_st);
+        }
+        if (!ok) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 20, 0);
+      }
+      __syncwarp();
+    }
+  } else if (warp < 12) {
+    warpgroup_reg_inc<kFa3RegsSoftmax>();
+    // ------------------------------ softmax of tile t (thread = row) ------------------------------
+    const int t = (warp >= 8) ? 1 : 0;
+    if (!bad && (t == 0 || has1)) {
+      const int q4 = warp & 3;
+      const int row = q4 * 32 + lane;
+      const int my_pos = q_pos0 + t * kFaTile + row;
+      const int tile_row0 = q_row0 + t * kFaTile;
+      const float scale2 = d.scale * kLog2e;
+      float m_run = -INFINITY, l_run = 0.f;
+      bool ok = true;
+      int cnt = 0;
+      const uint32_t s_row = tmem_s(t) + (static_cast<uint32_t>(q4 * 32) << 16);
+      for_each_kv_tile(d, q_pos_last, [&](int /*j*/, int /*rowbuf*/, int kp, int valid, int /*seg*/) {
+        if (!ok) return;
+        if (t == 0 && !need0(kp)) return;
+        const uint32_t ph = cnt & 1;
+        ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after_sync();
+        // the whole row of scores in registers: four reads in flight, one wait
+        uint32_t r[128];
+        {
+          uint32_t (&r0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+          uint32_t (&r1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+          uint32_t (&r2)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[64]);
+          uint32_t (&r3)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[96]);
+          tmem_ld_32x32(s_row, r0);
+          tmem_ld_32x32(s_row + 32, r1);
+          tmem_ld_32x32(s_row + 64, r2);
+          tmem_ld_32x32(s_row + 96, r3);
+          tmem_ld_wait();
+        }
+        const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i)
+            if (i >= valid || (d.causal && kp + i > my_pos)) r[i] = 0xff800000u;    // -inf: exp2 gives 0
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
+        // the offset follows the row maximum lazily: it moves only when the maximum has grown by more than 8 (a factor
+        // 256 in the exponentials, harmless in fp32 sums and bf16 P), which makes rescaling the accumulator rare
+        const float m_new = (mx > m_run + 8.f) ? mx : m_run;
+        const bool dead = m_new == -INFINITY;
+        const float alpha = (dead || m_new == m_run) ? 1.f : fast_exp2(m_run - m_new);
+        const float neg_m = dead ? 0.f : -m_new;
+        ok = mbar_wait(a_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        alpha_s[t * kFaTile + row] = alpha;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_full(t));
+        // exponentials in place, then packed to bf16 pairs in the first 64 registers
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const float e = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, neg_m));
+          sum4[i & 3] += e;
+          r[i] = __float_as_uint(e);
+        }
+        uint32_t w[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        {
+          const uint32_t (&w0)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[0]);
+          const uint32_t (&w1)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[32]);
+          tmem_st_32x32(s_row, w0);
+          tmem_st_32x32(s_row + 32, w1);
+          tmem_st_wait();
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(t));
+        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m_run = m_new;
+        ++cnt;
+      });
+      // epilogue: O_t / l -> bf16
+      const bool row_ok = tile_row0 + row < d.sq;
+      if (ok && cnt > 0) {
+        ok = mbar_wait(pv_done(t), (cnt - 1) & 1, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        if (cnt > 0) tc_fence_after_sync();
+        const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+        if (p.lse != nullptr && row_ok)
+          p.lse[(static_cast<long long>(batch) * d.hq + head) * d.sq + tile_row0 + row] =
+              (l_run > 0.f) ? (m_run + log2f(l_run)) * kLn2 : -INFINITY;
+        __nv_bfloat16* dst = p.out + (static_cast<long long>(q_tok0 + t * kFaTile + row) * d.hq + head) * D;
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t o[32];
+          if (cnt > 0) {
+            tmem_ld_32x32(tmem_o(t) + (static_cast<uint32_t>(q4 * 32) << 16) + cc * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              U4 u{pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv)};
+              st_global_v4(dst + cc * 32 + i, u);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 30 + t, 0);
+      }
+    }
+  } else {
+    warpgroup_reg_dec<kFa3RegsCorr>();
+    // ------------------------------ correction (thread = row, both tiles) ------------------------------
+    if (!bad) {
+      const int q4 = warp & 3;
+      const int row = q4 * 32 + lane;
+      const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+      int cnt[2] = {0, 0};
+      bool ok = true;
+      for_each_kv_tile(d, q_pos_last, [&](int /*j*/, int /*rowbuf*/, int kp, int /*valid*/, int /*seg*/) {
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (t == 0 ? !need0(kp) : !has1) continue;
+          const uint32_t ph = cnt[t] & 1;
+          ok = mbar_wait(a_full(t), ph, abort_flag, p.budget_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          const float alpha = alpha_s[t * kFaTile + row];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(a_empty(t));
+          if (cnt[t] > 0) {
+            // the accumulator may only be touched once the previous P V product has landed in it
+            ok = mbar_wait(pv_done(t), (cnt[t] - 1) & 1, abort_flag, p.budget_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (__any_sync(0xffffffffu, alpha != 1.f)) {
+              tc_fence_after_sync();
+#pragma unroll
+              for (int cc = 0; cc < D / 32; ++cc) {
+                uint32_t o[32];
+                tmem_ld_32x32(tmem_o(t) + lane_off + cc * 32, o);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                tmem_st_32x32(tmem_o(t) + lane_off + cc * 32, o);
+              }
+              tmem_st_wait();
+              tc_fence_before_sync();
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(o_scaled(t));
+          ++cnt[t];
+        }
+      });
+      if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 40, 0);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
 template <int D, bool SPEC = false>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -1070,6 +1472,27 @@ fa_fwd2_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   fa_fwd2_cta<D, SPEC>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
 }
 
+template <int D>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_fwd3_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const FaParams p, const FaCommArgs a) {
+  if ((int)blockIdx.x < a.comm_blocks) {
+    fa_push_role(a);
+    return;
+  }
+  const int pairs = (a.num_q_tiles + 1) / 2;
+  const int id = blockIdx.x - a.comm_blocks;
+  const int qp = pairs - 1 - id % pairs;
+  const int hb = id / pairs;
+  fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
+}
+
+// PKB_FA_V3=1 selects the two-tile kernel that keeps P in tensor memory (off until it has been validated and timed).
+static bool fa_use_v3() {
+  static const bool on = [] { const char* e = getenv("PKB_FA_V3"); return e != nullptr && e[0] == '1'; }();
+  return on;
+}
+
 // PKB_FA_SPEC=1 selects the speculative single-pass softmax of the two-tile kernel (off by default).
 static bool fa_use_spec() {
   static const bool on = [] { const char* e = getenv("PKB_FA_SPEC"); return e != nullptr && e[0] == '1'; }();
@@ -1107,7 +1530,13 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   p.trace = reinterpret_cast<long long*>(d.trace);
   p.trace_capacity = d.trace_capacity;
   const int n_tiles = (d.sq + kFaTile - 1) / kFaTile;
-  if (fa_use_pairs(d) && p.trace == nullptr) {
+  if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v3()) {
+    constexpr int smem = Fa3Smem<D>::kTotal;
+    dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
+    auto kern = fa_fwd3_kernel<D>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+  } else if (fa_use_pairs(d) && p.trace == nullptr) {
     constexpr int smem = Fa2Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     if (fa_use_spec()) {
@@ -1202,7 +1631,13 @@ static int launch_fa_ring(const pkb_attn_desc* desc, const pkb_symm_ctx* h, cons
   p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
   p.trace = nullptr;
   p.trace_capacity = 0;
-  if (fa_use_pairs(d)) {
+  if (fa_use_pairs(d) && fa_use_v3()) {
+    constexpr int smem = Fa3Smem<D>::kTotal;
+    const int grid = comm_blocks + ((a.num_q_tiles + 1) / 2) * d.hq * d.batch;
+    auto kern = fa_fwd3_ring_kernel<D>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p, a);
+  } else if (fa_use_pairs(d)) {
     constexpr int smem = Fa2Smem<D>::kTotal;
     const int grid = comm_blocks + ((a.num_q_tiles + 1) / 2) * d.hq * d.batch;
     if (fa_use_spec()) {

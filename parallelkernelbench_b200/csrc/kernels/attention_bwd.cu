@@ -39,6 +39,12 @@ struct FaBwdParams {
   float* dq;            // [batch * sq, hq, D] fp32, zero-initialised by the caller
   float* dk;            // [batch * skv, hkv, D] fp32
   float* dv;            // [batch * skv, hkv, D] fp32
+  // Context-parallel form: when seg_scatter != 0 the dK / dV rows of KV segment s are ADDED (fp32 vector reductions) into
+  // dk_seg[s] / dv_seg[s], which point at row 0 of that segment inside the accumulator of the rank that owns the rows -
+  // peer memory for remote segments, so the partial sums go home from the epilogue instead of through a reduce-scatter.
+  int seg_scatter;
+  float* dk_seg[16];
+  float* dv_seg[16];
   uint32_t* status;
   uint64_t budget_ns;
 };
@@ -124,13 +130,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   const int batch = blockIdx.z;
 
   // which KV tile: heavy tiles (early positions see the most queries under a causal mask) come first in launch order
-  int kv_row0 = 0, kv_pos0 = 0, kv_valid = 0;
+  int kv_row0 = 0, kv_pos0 = 0, kv_valid = 0, kv_seg = 0, kv_row_in_seg = 0;
   {
     int t = blockIdx.x;
     bool found = false;
     for (int seg = 0; seg < d.num_kv_segs && !found; ++seg) {
       const int nt = (d.kv_seg_len[seg] + kFbTile - 1) / kFbTile;
       if (t < nt) {
+        kv_seg = seg;
+        kv_row_in_seg = t * kFbTile;
         kv_row0 = d.kv_seg_row0[seg] + t * kFbTile;
         kv_pos0 = d.kv_seg_pos0[seg] + t * kFbTile;
         kv_valid = min(kFbTile, d.kv_seg_len[seg] - t * kFbTile);
@@ -399,9 +407,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     }
     if (ok) {
       // rows of dV / dK are the KV rows of this tile
-      const bool row_ok = row < kv_valid;
+      const bool row_ok = row < kv_valid && !(p.seg_scatter && n_steps == 0);   // nothing to add for a tile no query saw
       float* dvp = p.dv + ((static_cast<long long>(kv_tok0) + row) * d.hkv + kv_head) * D + col0;
       float* dkp = p.dk + ((static_cast<long long>(kv_tok0) + row) * d.hkv + kv_head) * D + col0;
+      if (p.seg_scatter) {
+        const long long off = (static_cast<long long>(kv_row_in_seg + row) * d.hkv + kv_head) * D + col0;
+        dvp = p.dv_seg[kv_seg] + off;
+        dkp = p.dk_seg[kv_seg] + off;
+      }
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
         uint32_t rv[32], rk[32];
@@ -413,7 +426,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 #pragma unroll
           for (int i = 0; i < 32; ++i) { rv[i] = 0u; rk[i] = 0u; }
         }
-        if (row_ok) {
+        if (row_ok && p.seg_scatter) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            red_add_v4_f32(dvp + c * 32 + i, __uint_as_float(rv[i]), __uint_as_float(rv[i + 1]), __uint_as_float(rv[i + 2]),
+                           __uint_as_float(rv[i + 3]));
+            red_add_v4_f32(dkp + c * 32 + i, __uint_as_float(rk[i]), __uint_as_float(rk[i + 1]), __uint_as_float(rk[i + 2]),
+                           __uint_as_float(rk[i + 3]));
+          }
+        } else if (row_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
             st_global_v4(dvp + c * 32 + i, U4{rv[i], rv[i + 1], rv[i + 2], rv[i + 3]});
@@ -421,6 +442,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           }
         }
       }
+      // remote additions must have been performed before this rank tells its peers (the barrier launch that follows) that it is done
+      if (p.seg_scatter) __threadfence_system();
     } else if (lane == 0 && !bad) {
       record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 40, 0);
     }
@@ -441,7 +464,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
 template <int D>
 static int launch_fa_bwd(const pkb_attn_desc& d, const void* q, const void* k, const void* v, const void* o, const void* dout,
-                         const void* lse, void* delta, void* lse2, void* dq, void* dk, void* dv, cudaStream_t stream) {
+                         const void* lse, void* delta, void* lse2, void* dq, void* dk, void* dv, cudaStream_t stream,
+                         const unsigned long long* dk_seg = nullptr, const unsigned long long* dv_seg = nullptr) {
   CUtensorMap tq, tk, tv, tdo;
   int rc = encode_tmap_3d(&tq, kTmapBf16, q, D, d.hq, (uint64_t)d.batch * d.sq, (uint64_t)D * 2, (uint64_t)d.hq * D * 2, 64, 1,
                           kFbTile, kSwizzle128);
@@ -469,6 +493,11 @@ static int launch_fa_bwd(const pkb_attn_desc& d, const void* q, const void* k, c
   p.dq = static_cast<float*>(dq);
   p.dk = static_cast<float*>(dk);
   p.dv = static_cast<float*>(dv);
+  p.seg_scatter = (dk_seg != nullptr && dv_seg != nullptr) ? 1 : 0;
+  for (int sg = 0; sg < 16; ++sg) {
+    p.dk_seg[sg] = p.seg_scatter && sg < d.num_kv_segs ? reinterpret_cast<float*>(dk_seg[sg]) : nullptr;
+    p.dv_seg[sg] = p.seg_scatter && sg < d.num_kv_segs ? reinterpret_cast<float*>(dv_seg[sg]) : nullptr;
+  }
   p.status = status_block_device_ptr();
   p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
   auto kern = fa_bwd_kernel<D>;
@@ -504,3 +533,29 @@ extern "C" int pkb_flash_attn_bwd(const pkb_attn_desc* desc, const void* q, cons
   if (d.head_dim == 128) return launch_fa_bwd<128>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, dk, dv, s);
   return launch_fa_bwd<64>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, dk, dv, s);
 }
+
+// Context-parallel backward: like pkb_flash_attn_bwd, but the dK / dV rows of KV segment s are added into the fp32 buffers at
+// addresses dk_seg[s] / dv_seg[s] ([kv_seg_len[s], hkv, d] each, row 0 of the segment first), which may be peers' symmetric
+// memory. The caller zero-fills every accumulator and makes all ranks meet (a barrier launch) before this call, and makes
+// them meet again after it before anyone reads its accumulator. dq as in pkb_flash_attn_bwd.
+extern "C" int pkb_flash_attn_bwd_scatter(const pkb_attn_desc* desc, const void* q, const void* k, const void* v, const void* o,
+                                          const void* dout, const void* lse, void* delta_scratch, void* lse2_scratch, void* dq,
+                                          const unsigned long long* dk_seg, const unsigned long long* dv_seg, void* stream) {
+  PKB_CHECK_ARG(desc != nullptr && dk_seg != nullptr && dv_seg != nullptr, "null descriptor or destination table");
+  const pkb_attn_desc& d = *desc;
+  PKB_CHECK_ARG(d.head_dim == 64 || d.head_dim == 128, "head_dim must be 64 or 128");
+  PKB_CHECK_ARG(d.hq % d.hkv == 0 && d.batch == 1 && d.sq >= 1 && d.skv >= 1, "bad attention shape (one sequence)");
+  PKB_CHECK_ARG(d.num_q_segs >= 1 && d.num_q_segs <= 16 && d.num_kv_segs >= 1 && d.num_kv_segs <= 16, "1..16 segments");
+  PKB_CHECK_ARG(d.q_seg_rows % kFbTile == 0 || d.num_q_segs == 1, "q segments must be multiples of 128 rows");
+  PKB_CHECK_ARG(d.q_seg_rows >= 1, "q_seg_rows must be positive");
+  for (int s = 0; s < d.num_kv_segs; ++s) {
+    PKB_CHECK_ARG(d.kv_seg_row0[s] >= 0 && d.kv_seg_len[s] >= 0 && d.kv_seg_row0[s] + d.kv_seg_len[s] <= d.skv,
+                  "kv segment outside the buffer");
+    PKB_CHECK_ARG(dk_seg[s] != 0 && dv_seg[s] != 0 && ((dk_seg[s] | dv_seg[s]) & 15) == 0, "segment destinations must be 16-byte aligned");
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (d.head_dim == 128)
+    return launch_fa_bwd<128>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, nullptr, nullptr, s, dk_seg, dv_seg);
+  return launch_fa_bwd<64>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, nullptr, nullptr, s, dk_seg, dv_seg);
+}
+

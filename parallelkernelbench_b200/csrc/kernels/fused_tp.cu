@@ -480,16 +480,18 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   a.sub_per_shard = rows / a_chunk_rows;
   a.epoch = epoch;
   a.local_in_place = (x_local == g_local + (long long)h->grank * rows * K * 2) ? 1 : 0;
-  // pushing (W-1) copies of the shard must keep pace with the GEMM that consumes them. Measured at 8 ranks
-  // (2048 x 8192 rows per rank, ms per TP-MLP block): 8 CTAs 2.24, 16 CTAs 1.95, 24 CTAs 2.03, 32 CTAs 2.13
-  if (comm_ctas <= 0) comm_ctas = W >= 8 ? 16 : (W > 1 ? 8 : 2);
+  // The shard travels as 16 KiB TMA bulk requests through a shared-memory ring, one issuing thread per communication CTA
+  // (PKB_TP_BULK_PUSH=0 selects the older form: 16-byte loads and stores by all threads of the CTA). With thread copies
+  // the rate is bound by the loads a CTA can keep in flight, so many CTAs are needed and the step time follows their
+  // number (8 ranks, 2048 x 8192 rows per rank, ms per TP-MLP block: 8 CTAs 2.24, 16 CTAs 1.95, 24 CTAs 2.03); a bulk ring
+  // keeps 160 KiB in flight per CTA, so a few CTAs fill the link and the rest of the SMs stay with the GEMM.
+  static const bool bulk_off = [] { const char* e = getenv("PKB_TP_BULK_PUSH"); return e != nullptr && e[0] == '0'; }();
+  a.bulk_push = (!bulk_off && a.sub_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0) ? 1 : 0;
+  if (comm_ctas <= 0) comm_ctas = a.bulk_push ? (W > 1 ? 8 : 2) : (W >= 8 ? 16 : (W > 1 ? 8 : 2));
   comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
   const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");
   a.comm_ctas = comm_ctas;
-  // PKB_TP_BULK_PUSH=1: push with TMA bulk requests instead of 16-byte stores (off by default)
-  static const bool bulk_push = [] { const char* e = getenv("PKB_TP_BULK_PUSH"); return e != nullptr && e[0] == '1'; }();
-  a.bulk_push = (bulk_push && a.sub_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0) ? 1 : 0;
 
   constexpr int smem = kGemm2SmemTotal;
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -21,7 +21,8 @@ from .roofline import estimate
 
 # label -> (op, named config)
 CONFIGS = {
-    "3": ("moe_layer", "deepseek"),
+    "3": ("moe_layer", "deepseek"),                      # fp8 dispatch, bf16 experts
+    "3f": ("moe_layer", "deepseek_fp8_experts"),         # fp8 dispatch feeding block-scaled fp8 expert GEMMs
     "4": ("ring_attention_fwd_bwd", "cp131k"),
     "5": ("fsdp_llama_step", "llama8b"),
 }
@@ -65,6 +66,8 @@ def run_one(ctx, op: str, cfg_name: str, warmup: int = 3, iters: int = 10, time_
     row: dict = {"op": op, "config": cfg_name, "world": ctx.world, "warmup": warmup, "iters": iters}
     rc_ref = registry.RunCtx(ctx, spec.name, trial=0, dtype=torch.bfloat16)
     rc_ours = registry.RunCtx(ctx, spec.name, trial=0, dtype=torch.bfloat16)
+    heap = ctx.heap()
+    mark = heap.mark()             # symmetric buffers of this configuration are handed back when it is done
     try:
         with torch.no_grad():
             in_ref = spec.make_inputs(rc_ref, cfg)
@@ -102,7 +105,10 @@ def run_one(ctx, op: str, cfg_name: str, warmup: int = 3, iters: int = 10, time_
         rc_ours.cache.clear()
         gc.collect()
         if ctx.is_cuda:
+            torch.cuda.synchronize()
             torch.cuda.empty_cache()
+        ctx.barrier()              # no rank may reuse the space while a peer's kernels can still write into it
+        heap.release(mark)
     return row
 
 

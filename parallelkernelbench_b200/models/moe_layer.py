@@ -37,7 +37,7 @@ class MoEConfig:
     fp8_dispatch: bool = True
     fp8_experts: bool = False
     push_combine: bool = False      # the down GEMM's epilogue stores each output row in its token owner's memory
-    fused_router: bool = False      # softmax + top-k + histogram in one kernel instead of PyTorch ops + histogram kernel
+    fused_router: bool = True       # softmax + top-k + histogram in one kernel (up to 256 experts) instead of PyTorch ops + histogram kernel
     weight_std: float = 0.02
 
 
@@ -49,7 +49,7 @@ class EPMoELayer:
         self.w_router, self.router_bias = w_router.contiguous(), router_bias
         self.router_bias_f32 = None if router_bias is None else router_bias.float().contiguous()
         if cfg.fused_router and cfg.num_experts > 256:
-            raise ValueError("the fused router handles at most 256 experts")
+            cfg.fused_router = False             # the one-warp-per-token router kernel holds at most 256 experts in registers
         self.w_gate_up = interleave_gate_up(w_gate, w_up)
         self.w_down = w_down.contiguous()
         self.ex = MoEExchange(group, cfg.num_experts, cfg.hidden, cfg.tokens_per_rank, cfg.top_k, cfg.capacity_factor,

@@ -98,6 +98,7 @@ class RingAttention:
         self.flags = heap.empty((max(W * self.segs, 4),), torch.int32)
         self.flags.local.zero_()
         self.calls = 0
+        self._fwd_kv = None        # (data_ptr, version) of the K and V the gather buffers currently hold
 
     def positions(self, rank_in_group: int) -> list[int]:
         if self.layout == "zigzag":
@@ -145,27 +146,42 @@ class RingAttention:
             ctypes.c_ulonglong(self.flags.offset), self.segs, self.seg_rows, self.comm_blocks, nv.ptr(out), nv.ptr(lse),
             nv.current_stream()), "pkb_flash_attn_fwd_ring")
         nv.count_launch()
+        self._fwd_kv = (k.data_ptr(), v.data_ptr(), k._version, v._version)
         return out, lse
 
     __call__ = forward
 
     def backward(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor,
-                 causal: bool = True, scale: float | None = None):
-        """Gradients of :meth:`forward`. K and V of the whole group are gathered (one launch each), the backward kernel
-        walks them by segment with this rank's query positions - dQ is complete locally, dK/dV partials for every KV
-        row come out in fp32 - and one reduce-scatter per tensor sends the partial sums to the owners of the rows.
-        Returns ``(dq, dk, dv)`` in fp32 for this rank's rows."""
+                 causal: bool = True, scale: float | None = None, fused: bool | None = None):
+        """Gradients of :meth:`forward`. Returns ``(dq, dk, dv)`` in fp32 for this rank's rows.
+
+        Fused form (default on GPUs; ``PKB_RING_BWD_UNFUSED=1`` or ``fused=False`` selects the other): K and V of the whole
+        group are read from the gather buffers the forward call filled (nothing is gathered again when ``k`` / ``v`` are the
+        tensors of the last forward call), and the backward kernel adds the dK / dV rows of every KV segment straight into
+        the fp32 accumulator of the rank that owns the segment - ``red.global.add.v4.f32`` over peer pointers from its
+        epilogue. Two barrier launches bracket it (accumulators zeroed everywhere before, all additions landed after). Per
+        rank (W-1)/W of one fp32 dK + dV cross NVLink once, and no whole-sequence partial buffer is written or re-read
+        (reference behaviour: a ring of send/recv steps around per-block gradients, reference/57_ring_attention_backward_dp.py:72-121).
+
+        Unfused form: all-gather of K and V, single-GPU backward into fp32 partials for every row of the sequence, one
+        reduce-scatter per tensor."""
+        import os
+
         from . import collectives as C
 
         W, r = self.W, self.group.rank_in_group
+        if fused is None:
+            fused = os.environ.get("PKB_RING_BWD_UNFUSED") != "1"
+        q_segments = [(self.seg_rows, pos) for pos in self.positions(r)]
+        kv_segments = [(src * self.rows + sgi * self.seg_rows, pos, self.seg_rows) for src in range(W)
+                       for sgi, pos in enumerate(self.positions(src))]
+        if W > 1 and fused and q.is_cuda and q.dtype == torch.bfloat16:
+            return self._backward_fused(q, k, v, out, lse, dout, causal, scale, q_segments, kv_segments)
         if W > 1:
             kg = C.all_gather(k.contiguous(), self.group).view(W * self.rows, self.hkv, self.D)
             vg = C.all_gather(v.contiguous(), self.group).view(W * self.rows, self.hkv, self.D)
         else:
             kg, vg = k, v
-        q_segments = [(self.seg_rows, pos) for pos in self.positions(r)]
-        kv_segments = [(src * self.rows + sgi * self.seg_rows, pos, self.seg_rows) for src in range(W)
-                       for sgi, pos in enumerate(self.positions(src))]
         dk_buf = dv_buf = None
         if W > 1:      # partial sums for every KV row of the group live in the heap: the reduce-scatter reads them in place
             heap = self.group.heap
@@ -177,6 +193,50 @@ class RingAttention:
         if W > 1:
             return dq, C.reduce_scatter(dkf, self.group), C.reduce_scatter(dvf, self.group)
         return dq, dkf, dvf
+
+    def _backward_fused(self, q, k, v, out, lse, dout, causal, scale, q_segments, kv_segments):
+        from . import collectives as C
+
+        W, r = self.W, self.group.rank_in_group
+        heap = self.group.heap
+        same_kv = self._fwd_kv == (k.data_ptr(), v.data_ptr(), k._version, v._version)
+        if not same_kv:
+            # K / V are not what the last forward call gathered: gather them into the same buffers
+            C.all_gather(k.contiguous(), self.group, out=self.k_gather.local.view(W, self.rows, self.hkv, self.D))
+            C.all_gather(v.contiguous(), self.group, out=self.v_gather.local.view(W, self.rows, self.hkv, self.D))
+        kg, vg = self.k_gather.local, self.v_gather.local
+        shape = (self.rows, self.hkv, self.D)
+        dk_acc = heap.named(("ring_dk_acc", self.group.channel, shape), shape, torch.float32)
+        dv_acc = heap.named(("ring_dv_acc", self.group.channel, shape), shape, torch.float32)
+        dk_acc.local.zero_()
+        dv_acc.local.zero_()
+        C.barrier(self.group)                                  # every accumulator is zero before any rank adds to it
+        d = AttnDesc()
+        d.batch, d.sq, d.skv, d.hq, d.hkv, d.head_dim = 1, self.rows, W * self.rows, self.hq, self.hkv, self.D
+        d.causal = 1 if causal else 0
+        d.scale = float(scale if scale is not None else 1.0 / math.sqrt(self.D))
+        d.q_seg_rows, d.num_q_segs = q_segments[0][0], len(q_segments)
+        for i, (_, pos) in enumerate(q_segments):
+            d.q_seg_pos[i] = pos
+        d.num_kv_segs = len(kv_segments)
+        seg_bytes = self.seg_rows * self.hkv * self.D * 4
+        dk_ptrs, dv_ptrs = (ctypes.c_ulonglong * 16)(), (ctypes.c_ulonglong * 16)()
+        for i, (row0, pos0, ln) in enumerate(kv_segments):
+            d.kv_seg_row0[i], d.kv_seg_pos0[i], d.kv_seg_len[i] = row0, pos0, ln
+            src, sgi = divmod(i, self.segs)                   # kv_segments is rank-major, segment-minor
+            owner = self.group.members[src]
+            dk_ptrs[i] = (heap.base + owner * heap.stride + dk_acc.offset) + sgi * seg_bytes
+            dv_ptrs[i] = (heap.base + owner * heap.stride + dv_acc.offset) + sgi * seg_bytes
+        qc, oc, doc = (t.contiguous() for t in (q, out, dout))
+        lsec = lse.reshape(1, self.hq, self.rows).float().contiguous()
+        delta, lse2 = torch.empty_like(lsec), torch.empty_like(lsec)
+        dq = torch.zeros((self.rows, self.hq, self.D), dtype=torch.float32, device=q.device)
+        nv.check(nv.cuda_lib().pkb_flash_attn_bwd_scatter(ctypes.byref(d), nv.ptr(qc), nv.ptr(kg), nv.ptr(vg), nv.ptr(oc), nv.ptr(doc),
+                                                          nv.ptr(lsec), nv.ptr(delta), nv.ptr(lse2), nv.ptr(dq), dk_ptrs, dv_ptrs,
+                                                          nv.current_stream()), "pkb_flash_attn_bwd_scatter")
+        nv.count_launch(2)
+        C.barrier(self.group)                                  # all ranks' additions into this rank's rows have landed
+        return dq, dk_acc.local, dv_acc.local
 
 
 def flash_attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, lse: torch.Tensor, dout: torch.Tensor, *,

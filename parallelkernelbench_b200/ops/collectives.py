@@ -65,6 +65,24 @@ def _ll_slots(group: SymmGroup, nbytes: int):
     return buf, cap_units
 
 
+def all_reduce_(x: torch.Tensor, group: SymmGroup, max_blocks: int = 0) -> torch.Tensor:
+    """In-place sum all-reduce of a tensor that lives in the symmetric heap (bf16 / fp32, whole-job group with a multicast
+    mapping): every rank reduces its slice through the switch (``multimem.ld_reduce``) and writes the sums back to the
+    same addresses on all ranks (``multimem.st``). No staging copy, no result buffer, no copy out - the message crosses
+    HBM once for the read and once for the write, like NCCL's in-place form on registered buffers
+    (reference: kernelgen/solutions_new_allreduce_parallelkittens.py:64-66 reduces in place the same way)."""
+    off = group.heap.contains(x)
+    if off is None or off % 16 != 0 or not x.is_contiguous():
+        raise ValueError("all_reduce_ needs a contiguous, 16-byte aligned tensor allocated from the symmetric heap")
+    if not (group.heap.mc_base != 0 and group.is_whole_heap and x.dtype in (torch.bfloat16, torch.float32)):
+        raise RuntimeError("in-place all-reduce needs the multicast mapping, the whole-job group and bf16/fp32 data")
+    nv.check(_lib().pkb_coll_allreduce_nvls(group.ref, _DT[x.dtype], nv.ptr(x), nv.c_ll(x.numel()), ctypes.c_ulonglong(off),
+                                            ctypes.c_ulonglong(off), nv.ptr(None), 1, max_blocks, nv.current_stream()),
+             "pkb_coll_allreduce_nvls")
+    nv.count_launch()
+    return x
+
+
 def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Tensor | None = None,
                algo: str = "auto", scale: float = 1.0, max_blocks: int = 0) -> torch.Tensor:
     x = _check(x)

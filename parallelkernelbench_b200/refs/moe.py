@@ -19,6 +19,25 @@ def fp8_round_trip_1x128(x: torch.Tensor) -> torch.Tensor:
     return ((xb / s).to(torch.float8_e4m3fn).float() * s).reshape(x.shape).to(x.dtype)
 
 
+# e4m3 round trip of expert weights, keyed by the weight tensors: weights are quantised once when a model is loaded, so a
+# timed loop over this reference must not pay for it on every call
+_W8_CACHE: dict = {}
+
+
+def _fp8_expert_weights(w_gate, w_up, w_down):
+    from .gemm_fp8 import dequantize_weight_128x128, quantize_weight_128x128
+
+    key = (w_gate.data_ptr(), w_up.data_ptr(), w_down.data_ptr(), w_gate._version, w_up._version, w_down._version)
+    if key not in _W8_CACHE:
+        if len(_W8_CACHE) > 8:
+            _W8_CACHE.clear()
+        gu = torch.stack([w_gate, w_up], dim=-2).reshape(w_gate.shape[0], 2 * w_gate.shape[1], w_gate.shape[2])
+        gu = dequantize_weight_128x128(*quantize_weight_128x128(gu)).to(w_gate.dtype)
+        _W8_CACHE[key] = (gu[:, 0::2].contiguous(), gu[:, 1::2].contiguous(),
+                          dequantize_weight_128x128(*quantize_weight_128x128(w_down)).to(w_down.dtype))
+    return _W8_CACHE[key]
+
+
 def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: int, top_k: int, group=None,
                   fp8_dispatch: bool = False, gates_idx=None, fp8_experts: bool = False):
     """``w_gate``/``w_up``: [E_local, I, H], ``w_down``: [E_local, H, I]. Returns [T, H].
@@ -37,12 +56,7 @@ def moe_reference(x, w_router, router_bias, w_gate, w_up, w_down, num_experts: i
     else:
         gates, idx = gates_idx
     if fp8_experts:
-        from .gemm_fp8 import dequantize_weight_128x128, quantize_weight_128x128
-
-        gu = torch.stack([w_gate, w_up], dim=-2).reshape(w_gate.shape[0], 2 * w_gate.shape[1], w_gate.shape[2])
-        gu = dequantize_weight_128x128(*quantize_weight_128x128(gu)).to(w_gate.dtype)
-        w_gate, w_up = gu[:, 0::2], gu[:, 1::2]
-        w_down = dequantize_weight_128x128(*quantize_weight_128x128(w_down)).to(w_down.dtype)
+        w_gate, w_up, w_down = _fp8_expert_weights(w_gate, w_up, w_down)
     flat_e = idx.reshape(-1).long()
     order = torch.argsort(flat_e, stable=True)
     tok = (order // top_k)

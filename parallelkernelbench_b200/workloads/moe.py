@@ -195,7 +195,7 @@ def _moe_ours(rc, x, w_router, b_router, wg, wu, wd, E, k, members, fp8, lora):
     if key not in rc.cache:
         cfg = MoEConfig(hidden=x.shape[1], inter=wg.shape[1], num_experts=E, top_k=k, tokens_per_rank=x.shape[0],
                         capacity_factor=float(len(members)) if x.shape[0] * k <= 8192 else 2.0, fp8_dispatch=fp8 >= 1,
-                        fp8_experts=fp8 >= 2, fused_router=os.environ.get("PKB_FUSED_ROUTER") == "1" and E <= 256,
+                        fp8_experts=fp8 >= 2, fused_router=os.environ.get("PKB_FUSED_ROUTER", "1") != "0" and E <= 256,
                         push_combine=os.environ.get("PKB_PUSH_COMBINE") == "1")
         rc.cache[key] = EPMoELayer(rc.comm.group(members), rc.comm, cfg, w_router, wg, wu, wd, router_bias=b_router)
     return rc.cache[key](x)

@@ -169,11 +169,13 @@ def _gar_ours(rc, a, b):
             and K % 8 == 0 and N % 8 == 0):
         from ..ops.tp import GemmAllReduce
 
-        key = ("gemm_ar", M, N, b.data_ptr())
+        key = ("gemm_ar", M, N)                   # one set of symmetric buffers per shape; the K-major weight per weight tensor
         if key not in rc.cache:
-            rc.cache[key] = (GemmAllReduce(rc.comm.group(), M // W, N), b.t().contiguous())
-        op, w = rc.cache[key]
-        return op(a.contiguous(), w).clone()
+            rc.cache[key] = GemmAllReduce(rc.comm.group(), M // W, N)
+        wkey = ("gemm_ar_w", b.data_ptr(), b._version)
+        if wkey not in rc.cache:
+            rc.cache[wkey] = b.t().contiguous()
+        return rc.cache[key](a.contiguous(), rc.cache[wkey]).clone()
     return rc.comm.all_reduce(_mm(rc, a, b))
 
 
@@ -205,11 +207,13 @@ def _gag_ours(rc, a, b):
     if os.environ.get("PKB_FUSED_GEMM_AG") == "1" and rc.dist.is_cuda and a.dtype == torch.bfloat16 and nl % 64 == 0 and K % 8 == 0:
         from ..ops.tp import GemmAllGather
 
-        key = ("gemm_ag", M, nl, b.data_ptr())
+        key = ("gemm_ag", M, nl)
         if key not in rc.cache:
-            rc.cache[key] = (GemmAllGather(rc.comm.group(), M, nl), b.t().contiguous())
-        op, w = rc.cache[key]
-        return op(a.contiguous(), w).clone()
+            rc.cache[key] = GemmAllGather(rc.comm.group(), M, nl)
+        wkey = ("gemm_ag_w", b.data_ptr(), b._version)
+        if wkey not in rc.cache:
+            rc.cache[wkey] = b.t().contiguous()
+        return rc.cache[key](a.contiguous(), rc.cache[wkey]).clone()
     return rc.comm.all_gather_cat(_mm(rc, a, b), dim=1) if rc.world > 1 else _mm(rc, a, b)
 
 

@@ -139,6 +139,18 @@ def main() -> int:
     same = all(torch.equal(C.all_reduce(x, g, algo="twoshot"), first) for _ in range(20))
     report("all_reduce twoshot determinism x20", same)
 
+    if heap.mc_base and W > 1:
+        # in-place form on a heap-resident tensor: the sums replace the inputs on every rank
+        for dtype, n in ((torch.bfloat16, 1 << 20), (torch.float32, 123456 // 4 * 4)):
+            xs = heap.named(("inplace_x", str(dtype)), (n,), dtype)
+            xs.local.copy_(torch.randn(n, device=dev, generator=torch.Generator(device=dev).manual_seed(50 + r)).to(dtype))
+            ref = xs.local.clone(); dist.all_reduce(ref)
+            torch.cuda.synchronize(); dist.barrier()
+            y = C.all_reduce_(xs.local, g)
+            torch.cuda.synchronize()
+            report(f"all_reduce_ in place {dtype}", torch.allclose(y.float(), ref.float(), atol=2e-2, rtol=2e-2) and y.data_ptr() == xs.local.data_ptr(),
+                   f"maxerr={(y.float() - ref.float()).abs().max().item():.3g}")
+
     # quick timing vs NCCL (device time, max over ranks)
     def timeit(fn, n=30, warm=10):
         for _ in range(warm):
@@ -162,8 +174,27 @@ def main() -> int:
                 continue
             t = timeit(lambda: C.all_reduce(x, g, algo=algo, out=y))
             line += f" {algo}={t * 1e3:.1f}us"
+        if heap.mc_base and W > 1:
+            xs = heap.named(("perf_inplace", nbytes), (nbytes // 2,), torch.bfloat16)
+            xs.local.zero_()
+            t = timeit(lambda: C.all_reduce_(xs.local, g))
+            line += f" nvls_inplace={t * 1e3:.1f}us (bus {2 * (W - 1) / W * nbytes / t / 1e6:.0f} GB/s; nccl bus {2 * (W - 1) / W * nbytes / t_nccl / 1e6:.0f} GB/s)"
         if r == 0:
             print(line, flush=True)
+
+    for nbytes in (1 << 24, 1 << 27):
+        # reduce-scatter and all-to-all of `nbytes` per rank: time and bytes received per rank and direction
+        x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16).view(W, -1)
+        yr = torch.empty(nbytes // 2 // W, device=dev, dtype=torch.bfloat16)
+        t_nccl = timeit(lambda: dist.reduce_scatter_tensor(yr, x.view(-1)))
+        t_ours = timeit(lambda: C.reduce_scatter(x.view(W * (x.shape[1] // 8), 8), g))
+        ya = torch.empty_like(x)
+        t_nccl_a = timeit(lambda: dist.all_to_all_single(ya.view(-1), x.view(-1)))
+        t_ours_a = timeit(lambda: C.all_to_all(x, g, out=ya))
+        if r == 0:
+            per_dir = (W - 1) / W * nbytes
+            print(f"PERF reduce_scatter {nbytes}B nccl={t_nccl * 1e3:.1f}us ours={t_ours * 1e3:.1f}us ({per_dir / t_ours / 1e6:.0f} GB/s per direction)", flush=True)
+            print(f"PERF all_to_all {nbytes}B nccl={t_nccl_a * 1e3:.1f}us ours={t_ours_a * 1e3:.1f}us ({per_dir / t_ours_a / 1e6:.0f} GB/s per direction)", flush=True)
 
     for nbytes in (1 << 20, 1 << 24, 1 << 27):
         x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
