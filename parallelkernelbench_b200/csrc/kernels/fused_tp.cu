@@ -146,6 +146,32 @@ tp_ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                 &tmap_a_local);
 }
 
+// Sum of the partial slots of one output row, kept in registers. Thread t owns the 16-byte chunks t, t + T, t + 2T, ... of
+// the row (T = threads of the CTA), at most kRowChunks of them; for every chunk the loads of ALL slots are issued before the
+// first addition, so a thread has up to kGemmMaxWorld independent 16-byte loads in flight instead of one (the slots were
+// written by peers over NVLink and are read once, from HBM: this phase is bound by loads in flight, not by arithmetic).
+// The slots are added in rank order in fp32, so the result does not depend on arrival order.
+constexpr int kRowChunks = 8;   // rows of up to 8 * 8 * 192 = 12288 elements stay in registers
+
+__device__ __forceinline__ void sum_slots_chunk(const __nv_bfloat16* p0, long long slot_stride, int gsize, float scale, float (&v)[8]) {
+  U4 u[kGemmMaxWorld];
+#pragma unroll
+  for (int g = 0; g < kGemmMaxWorld; ++g)
+    if (g < gsize) u[g] = ld_global_relaxed_v4(p0 + g * slot_stride);   // peers wrote these rows: read them coherently
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+#pragma unroll
+  for (int g = 0; g < kGemmMaxWorld; ++g) {
+    if (g < gsize) {
+      const float2 f0 = unpack_bf16x2(u[g].x), f1 = unpack_bf16x2(u[g].y), f2 = unpack_bf16x2(u[g].z), f3 = unpack_bf16x2(u[g].w);
+      v[0] += f0.x; v[1] += f0.y; v[2] += f1.x; v[3] += f1.y;
+      v[4] += f2.x; v[5] += f2.y; v[6] += f3.x; v[7] += f3.y;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] *= scale;
+}
+
 struct TpRsArgs {
   SymmCtx ctx;
   uint64_t recv_off;     // heap offset of the receive slots [gsize][rows_per_rank, N] bf16
@@ -192,22 +218,53 @@ tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!s_ok) return;
       waited_blk = blk;
     }
+    const __nv_bfloat16* row_slots = slots + (long long)row * a.N;
+    __nv_bfloat16* yrow = a.out + (long long)row * a.N;
+    if (a.N <= kRowChunks * 8 * nthreads) {
+      // the row stays in registers between the sum and the normalisation
+      float vals[kRowChunks][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int ch = 0; ch < kRowChunks; ++ch) {
+        const int i = (ch * nthreads + (int)threadIdx.x) * 8;
+        if (i < a.N) {
+          sum_slots_chunk(row_slots + i, slot_stride, c.gsize, a.scale, vals[ch]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) ss += vals[ch][j] * vals[ch][j];
+        }
+      }
+      ss = warp_sum(ss);
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+      __syncthreads();
+      float total = 0.f;
+      for (int w = 0; w < (nthreads >> 5); ++w) total += red[w];
+      const float rstd = rsqrtf(total / (float)a.N + a.eps);
+#pragma unroll
+      for (int ch = 0; ch < kRowChunks; ++ch) {
+        const int i = (ch * nthreads + (int)threadIdx.x) * 8;
+        if (i < a.N) {
+          const U4 g = ld_global_v4(a.gamma + i);
+          const float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+          U4 o;
+          o.x = pack_bf16x2(vals[ch][0] * rstd * g0.x, vals[ch][1] * rstd * g0.y);
+          o.y = pack_bf16x2(vals[ch][2] * rstd * g1.x, vals[ch][3] * rstd * g1.y);
+          o.z = pack_bf16x2(vals[ch][4] * rstd * g2.x, vals[ch][5] * rstd * g2.y);
+          o.w = pack_bf16x2(vals[ch][6] * rstd * g3.x, vals[ch][7] * rstd * g3.y);
+          st_global_v4(yrow + i, o);
+        }
+      }
+      __syncthreads();        // red[] is reused by the next row
+      continue;
+    }
+    // rows too long for registers: fp32 row buffer in shared memory
     float ss = 0.f;
     for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int g = 0; g < c.gsize; ++g) {
-        // peers wrote these rows with plain stores followed by a release; read them coherently
-        U4 u = ld_global_relaxed_v4(slots + g * slot_stride + (long long)row * a.N + i);
-        float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
-               f3 = unpack_bf16x2(u.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
+      float v[8];
+      sum_slots_chunk(row_slots + i, slot_stride, c.gsize, a.scale, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        acc[j] *= a.scale;
-        rowbuf[i + j] = acc[j];
-        ss += acc[j] * acc[j];
+        rowbuf[i + j] = v[j];
+        ss += v[j] * v[j];
       }
     }
     ss = warp_sum(ss);
@@ -216,7 +273,6 @@ tp_gemm_rs_rmsnorm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     float total = 0.f;
     for (int w = 0; w < (nthreads >> 5); ++w) total += red[w];
     const float rstd = rsqrtf(total / (float)a.N + a.eps);
-    __nv_bfloat16* yrow = a.out + (long long)row * a.N;
     for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
       U4 g = ld_global_v4(a.gamma + i);
       float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z),
@@ -276,20 +332,13 @@ tp_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_a,
       waited_blk = blk;
     }
     for (int i = threadIdx.x * 8; i < a.N; i += nthreads * 8) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int g = 0; g < c.gsize; ++g) {
-        // peers wrote these rows with TMA stores followed by a release; read them coherently
-        U4 u = ld_global_relaxed_v4(slots + g * slot_stride + (long long)row * a.N + i);
-        float2 f0 = unpack_bf16x2(u.x), f1 = unpack_bf16x2(u.y), f2 = unpack_bf16x2(u.z),
-               f3 = unpack_bf16x2(u.w);
-        acc[0] += f0.x; acc[1] += f0.y; acc[2] += f1.x; acc[3] += f1.y;
-        acc[4] += f2.x; acc[5] += f2.y; acc[6] += f3.x; acc[7] += f3.y;
-      }
+      float acc[8];
+      sum_slots_chunk(slots + (long long)row * a.N + i, slot_stride, c.gsize, a.scale, acc);
       U4 o;
-      o.x = pack_bf16x2(acc[0] * a.scale, acc[1] * a.scale);
-      o.y = pack_bf16x2(acc[2] * a.scale, acc[3] * a.scale);
-      o.z = pack_bf16x2(acc[4] * a.scale, acc[5] * a.scale);
-      o.w = pack_bf16x2(acc[6] * a.scale, acc[7] * a.scale);
+      o.x = pack_bf16x2(acc[0], acc[1]);
+      o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]);
+      o.w = pack_bf16x2(acc[6], acc[7]);
       const long long eoff = (my_row0 + row) * a.N + i;
       if (a.use_mc) {
         multimem_st_v4(symm_mc<__nv_bfloat16>(c, a.out_off) + eoff, o);

@@ -10,6 +10,8 @@
 namespace pkb {
 
 constexpr int kNormThreads = 256;
+constexpr int kNormRowChunks = 4;   // bf16 rows of up to 4 * 8 * 256 = 8192 elements stay in registers between the two passes
+constexpr int kNormMaxSrc = 8;      // ... when at most this many source buffers are summed
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
   v = warp_sum(v);
@@ -23,14 +25,68 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // Row lives in dynamic shared memory as fp32 between the two passes.
-template <bool SRC_F32>
-__global__ void __launch_bounds__(kNormThreads)
+// MAXSRC: upper bound of nsrc the register path is compiled for (1: plain RMSNorm, more CTAs per SM; kNormMaxSrc: sums)
+template <bool SRC_F32, int MAXSRC>
+__global__ void __launch_bounds__(kNormThreads, MAXSRC == 1 ? 4 : 2)
 sum_rmsnorm_kernel(const void* __restrict__ src, long long src_stride, int nsrc,
                    const __nv_bfloat16* __restrict__ gamma, __nv_bfloat16* __restrict__ y, int rows,
                    int cols, float scale, float eps) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    __nv_bfloat16* yrow = y + (long long)row * cols;
+    if constexpr (!SRC_F32) {
+      if (cols <= kNormRowChunks * 8 * kNormThreads && nsrc <= MAXSRC) {
+        // bf16 sources, row short enough for registers: thread t owns the 16-byte chunks t, t + 256, ...; the loads of all
+        // sources of a chunk are issued before the first addition (memory bound: what counts is loads in flight)
+        const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(src) + (long long)row * cols;
+        float vals[kNormRowChunks][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) {
+          const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+          if (i < cols) {
+            U4 u[MAXSRC];
+#pragma unroll
+            for (int sidx = 0; sidx < MAXSRC; ++sidx)
+              if (sidx < nsrc) u[sidx] = ld_global_nc_v4(base + (long long)sidx * src_stride + i);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vals[ch][j] = 0.f;
+#pragma unroll
+            for (int sidx = 0; sidx < MAXSRC; ++sidx) {
+              if (sidx < nsrc) {
+                const float2 f0 = unpack_bf16x2(u[sidx].x), f1 = unpack_bf16x2(u[sidx].y), f2 = unpack_bf16x2(u[sidx].z),
+                             f3 = unpack_bf16x2(u[sidx].w);
+                vals[ch][0] += f0.x; vals[ch][1] += f0.y; vals[ch][2] += f1.x; vals[ch][3] += f1.y;
+                vals[ch][4] += f2.x; vals[ch][5] += f2.y; vals[ch][6] += f3.x; vals[ch][7] += f3.y;
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              vals[ch][j] *= scale;
+              ss += vals[ch][j] * vals[ch][j];
+            }
+          }
+        }
+        const float total = block_sum(ss, red);
+        const float rstd = rsqrtf(total / (float)cols + eps);
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) {
+          const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+          if (i < cols) {
+            const U4 g = ld_global_v4(gamma + i);
+            const float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+            U4 o;
+            o.x = pack_bf16x2(vals[ch][0] * rstd * g0.x, vals[ch][1] * rstd * g0.y);
+            o.y = pack_bf16x2(vals[ch][2] * rstd * g1.x, vals[ch][3] * rstd * g1.y);
+            o.z = pack_bf16x2(vals[ch][4] * rstd * g2.x, vals[ch][5] * rstd * g2.y);
+            o.w = pack_bf16x2(vals[ch][6] * rstd * g3.x, vals[ch][7] * rstd * g3.y);
+            st_global_v4(yrow + i, o);
+          }
+        }
+        continue;
+      }
+    }
     float ss = 0.f;
     if constexpr (SRC_F32) {
       const float* base = static_cast<const float*>(src) + (long long)row * cols;
@@ -66,7 +122,6 @@ sum_rmsnorm_kernel(const void* __restrict__ src, long long src_stride, int nsrc,
     }
     const float total = block_sum(ss, red);
     const float rstd = rsqrtf(total / (float)cols + eps);
-    __nv_bfloat16* yrow = y + (long long)row * cols;
     for (int i = threadIdx.x * 8; i < cols; i += kNormThreads * 8) {
       U4 g = ld_global_v4(gamma + i);
       float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z),
@@ -87,24 +142,22 @@ static int launch_sum_rmsnorm(const void* src, long long src_stride, int nsrc, i
                               float eps, cudaStream_t stream) {
   PKB_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0, "cols must be a positive multiple of 8");
   PKB_CHECK_ARG(nsrc >= 1, "need at least one source");
-  const int smem = cols * (int)sizeof(float);
+  const bool in_regs = !src_is_f32 && cols <= kNormRowChunks * 8 * kNormThreads && nsrc <= kNormMaxSrc;
+  const int smem = in_regs ? 0 : cols * (int)sizeof(float);
   PKB_CHECK_ARG(smem <= 200 * 1024, "row too long for the shared-memory row buffer");
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  if (src_is_f32) {
-    auto k = sum_rmsnorm_kernel<true>;
-    if (smem > 48 * 1024)
-      PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<grid, kNormThreads, smem, stream>>>(src, src_stride, nsrc,
-                                            static_cast<const __nv_bfloat16*>(gamma),
-                                            static_cast<__nv_bfloat16*>(y), rows, cols, scale, eps);
-  } else {
-    auto k = sum_rmsnorm_kernel<false>;
-    if (smem > 48 * 1024)
-      PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    k<<<grid, kNormThreads, smem, stream>>>(src, src_stride, nsrc,
-                                            static_cast<const __nv_bfloat16*>(gamma),
-                                            static_cast<__nv_bfloat16*>(y), rows, cols, scale, eps);
+#define PKB_NORM_LAUNCH(F32, MS)                                                                        \
+  {                                                                                                    \
+    auto k = sum_rmsnorm_kernel<F32, MS>;                                                              \
+    if (smem > 48 * 1024)                                                                              \
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));      \
+    k<<<grid, kNormThreads, smem, stream>>>(src, src_stride, nsrc, static_cast<const __nv_bfloat16*>(gamma), \
+                                            static_cast<__nv_bfloat16*>(y), rows, cols, scale, eps);   \
   }
+  if (src_is_f32) PKB_NORM_LAUNCH(true, 1)
+  else if (nsrc == 1) PKB_NORM_LAUNCH(false, 1)
+  else PKB_NORM_LAUNCH(false, kNormMaxSrc)
+#undef PKB_NORM_LAUNCH
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

@@ -251,6 +251,21 @@ def _pad_to(flat, mult):
 _HYP = (1e-3, 0.9, 0.999, 1e-8)
 
 
+def _fused_step(rc, part):
+    """The one-launch reduce-scatter -> Adam -> all-gather step for shards of ``part`` elements (GPU, bf16, part % 8 == 0), or
+    None where it does not apply. ``PKB_UNFUSED_OPTIM=1`` keeps the three-launch form."""
+    import os
+
+    if not rc.dist.is_cuda or rc.dtype != torch.bfloat16 or part % 8 or rc.world < 2 or os.environ.get("PKB_UNFUSED_OPTIM") == "1":
+        return None
+    key = ("zero_adam", part)
+    if key not in rc.cache:
+        from ..ops.optim import ZeroAdamStep
+
+        rc.cache[key] = ZeroAdamStep(rc.comm.group(), part)
+    return rc.cache[key]
+
+
 # ---- 40: DDP ---------------------------------------------------------------------------------------
 def _ddp_inputs(rc, cfg):
     x, y, shapes = _mlp_data(rc, cfg)
@@ -292,7 +307,20 @@ def _ddp_ours(rc, x, y, params, ms, vs, lr, b1, b2, eps, step):
     flat, fm, fv = state[0], state[1], state[2]
     g = mlp_grads(rc, x, y, *_split(flat, params))
     n = flat.numel()
-    if W > 1:
+    fused = _fused_step(rc, (n + 8 * W - 1) // (8 * W) * 8) if W > 1 else None
+    if fused is not None:
+        # one launch: in-switch sum of this rank's gradient slice, Adam in registers, the new parameters stored on every rank;
+        # the moments of the other shards come with a second small gather
+        part = fused.part
+        fused.grad_buffer.zero_()
+        fused.grad_buffer[:n].copy_(g)
+        sl = slice(rc.rank * part, (rc.rank + 1) * part)
+        pad = lambda t: F.pad(t, (0, W * part - n))[sl].contiguous()  # noqa: E731
+        ps, ms_, vs_ = pad(flat), pad(fm), pad(fv)
+        p = fused.step(ps, ms_, vs_, lr=lr, beta1=b1, beta2=b2, eps=eps, step=step, grad_scale=1.0 / W)[:n].clone()
+        mv = rc.comm.all_gather(torch.stack([ms_, vs_]))                # [W, 2, part]
+        m, v = (mv[:, i].reshape(-1)[:n] for i in range(2))
+    elif W > 1:
         # all-reduce = reduce-scatter + all-gather: update the shard between the two halves
         gs = rc.comm.reduce_scatter(_pad_to(g, W).contiguous(), scale=1.0 / W)
         sh = gs.numel()
@@ -360,8 +388,16 @@ def _zero_ours(rc, x, y, params, m_part, v_part, lr, b1, b2, eps, step):
         flat = rc.comm.broadcast(flat.contiguous(), src=0)
     g = mlp_grads(rc, x, y, *_split(flat, params))
     part = m_part.numel()
-    gp = F.pad(g, (0, W * part - g.numel()))
     fp = F.pad(flat, (0, W * part - flat.numel()))
+    fused = _fused_step(rc, part) if W > 1 else None
+    if fused is not None:
+        # reduce-scatter of the gradient, Adam on the shard and all-gather of the new parameters in one launch
+        fused.grad_buffer.zero_()
+        fused.grad_buffer[:g.numel()].copy_(g)
+        ps, m, v = fp[r * part:(r + 1) * part].contiguous(), m_part.clone(), v_part.clone()
+        full = fused.step(ps, m, v, lr=lr, beta1=b1, beta2=b2, eps=eps, step=step, grad_scale=1.0 / W)
+        return {"params": full[:flat.numel()].clone(), "m": m, "v": v}
+    gp = F.pad(g, (0, W * part - g.numel()))
     gs = rc.comm.reduce_scatter(gp.contiguous(), scale=1.0 / W) if W > 1 else gp
     p, m, v = _adam_ours(rc, fp[r * part:(r + 1) * part], m_part, v_part, gs, lr, b1, b2, eps, step)
     full = rc.comm.all_gather(p.contiguous()).reshape(-1) if W > 1 else p
@@ -396,6 +432,11 @@ def _fa_ref(rc, g, w, m, v, lr, b1, b2, eps, step):
 
 
 def _fa_ours(rc, g, w, m, v, lr, b1, b2, eps, step):
+    fused = _fused_step(rc, w.numel())
+    if fused is not None:
+        # Adam on the local shard and the all-gather of the result in one launch (no reduction: the gradient is local)
+        fused.grad_buffer[:g.numel()].copy_(g)
+        return fused.step(w.clone(), m.clone(), v.clone(), lr=lr, beta1=b1, beta2=b2, eps=eps, step=step, reduce=False).clone()
     p, _, _ = _adam_ours(rc, w, m, v, g, lr, b1, b2, eps, step)
     return rc.comm.all_gather(p.contiguous()).reshape(-1) if rc.world > 1 else p
 
@@ -441,6 +482,14 @@ def _fsdp_ours(rc, x, y, shard, shapes, m, v, lr, b1, b2, eps, wd, step):
     n = sum(math.prod(s) for s in shapes)
     like = [torch.empty(s) for s in shapes]
     g = mlp_grads(rc, x, y, *_split(full[:n], like))
+    fused = _fused_step(rc, shard.numel()) if W > 1 else None
+    if fused is not None:
+        # gradient reduce-scatter and AdamW on the shard in one launch (the parameters are gathered by the next step)
+        fused.grad_buffer.zero_()
+        fused.grad_buffer[:n].copy_(g)
+        ps, mn, vn = shard.clone(), m.clone(), v.clone()
+        fused.step(ps, mn, vn, lr=lr, beta1=b1, beta2=b2, eps=eps, step=step, weight_decay=wd, grad_scale=1.0 / W, gather=False)
+        return ps, mn, vn
     gp = F.pad(g, (0, full.numel() - n))
     gs = rc.comm.reduce_scatter(gp.contiguous(), scale=1.0 / W) if W > 1 else gp
     if rc.dist.is_cuda:

@@ -45,6 +45,17 @@ def _q19_ref(rc, x, block):
 
 
 def _q19_ours(rc, x, block):
+    import os
+
+    if rc.dist.is_cuda and rc.world > 1 and x.dtype == torch.bfloat16 and os.environ.get("PKB_UNFUSED_PUSH") != "1":
+        # quantise and gather in one launch: payload and scales go from the quantising thread to every rank's gathered buffers
+        from ..ops.fused_push import Fp8QuantAllGather
+
+        key = ("q19", tuple(x.shape))
+        if key not in rc.cache:
+            rc.cache[key] = Fp8QuantAllGather(rc.comm.group(), tuple(x.shape))
+        y, s = rc.cache[key](x)
+        return y.clone(), s.clone()
     y, s = _quant(rc, x)
     if rc.world == 1:
         return y.unsqueeze(0), s.unsqueeze(0)

@@ -317,6 +317,19 @@ def _rope_ref(rc, q, k, cos, sin):
 
 
 def _rope_ours(rc, q, k, cos, sin):
+    import os
+
+    if (rc.dist.is_cuda and rc.world > 1 and q.dtype == torch.bfloat16 and q.shape[-1] % 16 == 0
+            and os.environ.get("PKB_UNFUSED_PUSH") != "1"):
+        # rotate and gather in one launch: every rotated 16-byte piece is stored into the gathered q / k of all ranks
+        from ..ops.fused_push import RopeAllGather
+
+        b, t, hq, d = q.shape
+        key = ("rope_ag", tuple(q.shape), tuple(k.shape))
+        if key not in rc.cache:
+            rc.cache[key] = RopeAllGather(rc.comm.group(), b, t, hq, k.shape[2], d)
+        qg, kg = rc.cache[key](q, k, cos, sin)
+        return qg.clone(), kg.clone()
     if rc.dist.is_cuda:
         from ..ops import rope
 

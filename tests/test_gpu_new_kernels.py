@@ -235,3 +235,66 @@ def test_ops_leave_the_guard_bands_of_the_symmetric_heap_intact(op):
     r = subprocess.run([sys.executable, "-m", "parallelkernelbench_b200.harness.launch", "run", "--op", op, "--impl", "ours", "--nproc", str(n),
                         "--config", "small"], cwd=root, capture_output=True, text=True, timeout=600, env={**os.environ, "PKB_HEAP_GUARD": "1"})
     assert r.returncode == 0 and "dry run ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("state_dtype", [torch.bfloat16, torch.float32])
+def test_fused_zero_adam_step_matches_the_formula_on_one_rank(state_dtype):
+    """One rank: the reduction and the gather degenerate to local moves, the arithmetic is the whole of it."""
+    from parallelkernelbench_b200.ops.optim import ZeroAdamStep
+    from parallelkernelbench_b200.parallel import init_context
+
+    os.environ.setdefault("PKB_HEAP_GIB", "0.25")
+    ctx = init_context()
+    try:
+        part = 8 * 1000 + 8
+        g = torch.Generator(device="cuda").manual_seed(3)
+        op = ZeroAdamStep(ctx.heap().world_group, part)
+        grad = torch.randn(part, device="cuda", generator=g).to(torch.bfloat16)
+        p0 = (torch.randn(part, device="cuda", generator=g) * 0.2).to(state_dtype)
+        m0 = (torch.randn(part, device="cuda", generator=g) * 0.01).to(state_dtype)
+        v0 = (torch.rand(part, device="cuda", generator=g) * 0.01).to(state_dtype)
+        lr, b1, b2, eps, wd, step, gs = 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, 0.5
+        op.grad_buffer.copy_(grad)
+        p, m, v = p0.clone(), m0.clone(), v0.clone()
+        full = op.step(p, m, v, lr=lr, beta1=b1, beta2=b2, eps=eps, step=step, weight_decay=wd, grad_scale=gs)
+        gf = grad.float() * gs
+        m_ref = b1 * m0.float() + (1 - b1) * gf
+        v_ref = b2 * v0.float() + (1 - b2) * gf * gf
+        upd = (m_ref / (1 - b1 ** step)) / ((v_ref / (1 - b2 ** step)).sqrt() + eps)
+        p_ref = p0.float() - lr * upd - lr * wd * p0.float()
+        tol = dict(atol=1e-5, rtol=1e-5) if state_dtype == torch.float32 else dict(atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(p.float(), p_ref, **tol)
+        torch.testing.assert_close(m.float(), m_ref, **tol)
+        torch.testing.assert_close(v.float(), v_ref, **tol)
+        torch.testing.assert_close(full.float(), p_ref, atol=1e-2, rtol=1e-2)      # the gathered copy is bf16
+    finally:
+        ctx.finalize()
+
+
+def test_fused_quantise_and_rope_pushes_match_their_two_step_forms_on_one_rank():
+    """One rank: the gather is a local store, what is checked is the arithmetic and the layout of the gathered buffers."""
+    from parallelkernelbench_b200.ops import fp8_quantize_1x128, rope
+    from parallelkernelbench_b200.ops.fused_push import Fp8QuantAllGather, RopeAllGather
+    from parallelkernelbench_b200.parallel import init_context
+
+    os.environ.setdefault("PKB_HEAP_GIB", "0.25")
+    ctx = init_context()
+    try:
+        group = ctx.heap().world_group
+        g = torch.Generator(device="cuda").manual_seed(9)
+        x = (torch.randn(37, 384, device="cuda", generator=g) * torch.rand(37, 1, device="cuda", generator=g) * 5).to(torch.bfloat16)
+        x[3] = 0                                                     # an all-zero block keeps scale 1
+        y, s = Fp8QuantAllGather(group, tuple(x.shape))(x)
+        y_ref, s_ref = fp8_quantize_1x128(x)
+        assert torch.equal(y[0], y_ref) and torch.equal(s[0], s_ref)
+
+        b, t, hq, hk, d = 2, 24, 4, 2, 64
+        q = torch.randn(b, t, hq, d, device="cuda", generator=g).to(torch.bfloat16)
+        k = torch.randn(b, t, hk, d, device="cuda", generator=g).to(torch.bfloat16)
+        ang = torch.rand(b, t, d, device="cuda", generator=g) * 6.28
+        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        qg, kg = RopeAllGather(group, b, t, hq, hk, d)(q, k, cos, sin)
+        torch.testing.assert_close(qg, rope(q, cos, sin), atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(kg, rope(k, cos, sin), atol=1e-2, rtol=1e-2)
+    finally:
+        ctx.finalize()
