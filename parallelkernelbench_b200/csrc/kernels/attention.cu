@@ -1361,6 +1361,405 @@ fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
+// ================================================================================================
+// Two Q tiles per CTA, P in tensor memory, TWO threads per row.
+// With one thread per row a softmax step costs its warp at least 128 ex2 x 8 cycles of the special-function pipe plus the
+// TMEM read and the maximum, about 1500 cycles, while the other Q tile's two products cover only 1024: the chain
+// S product -> softmax -> P V product -> next S product (S and P share TMEM columns) sets the pace, not a pipe. Here a row
+// is split between two threads of two warps that sit on the same TMEM lane quadrant (columns 0-63 and 64-127): each reads 64
+// scores, the two exchange their maxima through shared memory and an mbarrier (a bounded wait), each computes 64 exponentials
+// and stores its 32 packed columns of P. Row sums stay per half until the end. There is no correction warpgroup: the offset
+// of the exponentials follows the maximum lazily, so a rescale is rare, and when a row does need one the two threads of the
+// row scale their halves of the accumulator themselves once the previous P V product has landed.
+//   warp 0        TMA producer (Q0, Q1 once; K, V through two-stage rings)      warp 1   MMA issuer (as above)
+//   warps 4-7 / 8-11     softmax of tile 0, column half 0 / 1
+//   warps 12-15 / 16-19  softmax of tile 1, column half 0 / 1
+// ================================================================================================
+constexpr int kFa4Threads = 640;
+constexpr int kFa4RegsIo = 56, kFa4RegsSoftmax = 104;   // compiled for 96 per thread (640 x 96 = 61440 registers at launch)
+static_assert(128 * kFa4RegsIo + 512 * kFa4RegsSoftmax <= 640 * 96, "register budgets exceed the register file");
+
+template <int D>
+struct Fa4Smem {
+  static constexpr int kTileBytes = kFaTile * D * 2;
+  static constexpr int kStages = 2;
+  static constexpr int kQ = 0;                               // two tiles
+  static constexpr int kK = kQ + 2 * kTileBytes;
+  static constexpr int kV = kK + kStages * kTileBytes;
+  static constexpr int kXch = kV + kStages * kTileBytes;     // [parity][tile][half][128] fp32: maxima / row sums of the halves
+  static constexpr int kBars = kXch + 2 * 2 * 2 * kFaTile * 4;
+  static constexpr int kTotal = kBars + 512;
+};
+
+template <int D, bool POLY>
+__device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
+                                            const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
+                                            const int head, const int batch) {
+  using S = Fa4Smem<D>;
+  constexpr int kAtoms = D / 64;
+  constexpr int kAtomBytes = kFaTile * 128;
+  constexpr int kStages = S::kStages;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const uint32_t sb = smem_u32(smem);
+  const pkb_attn_desc& d = p.d;
+
+  const uint32_t bar0 = sb + S::kBars;
+  const uint32_t q_full = bar0;
+  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
+  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
+  auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
+  auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
+  auto pv_done = [&](int t) { return bar0 + 8u * (13 + t); };
+  auto x_bar = [&](int t, int q) { return bar0 + 8u * (15 + t * 4 + q); };   // the two warps of (tile, lane quadrant) meet here
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 24);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  float* xch = reinterpret_cast<float*>(smem + S::kXch);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_head = head / (d.hq / d.hkv);
+  const int n_q_tiles = (d.sq + kFaTile - 1) / kFaTile;
+  const int qt0 = q_pair * 2;
+  const bool has1 = qt0 + 1 < n_q_tiles;
+  const int q_row0 = qt0 * kFaTile;
+  const int q_seg = q_row0 / d.q_seg_rows;
+  const int q_pos0 = d.q_seg_pos[q_seg] + (q_row0 - q_seg * d.q_seg_rows);   // both tiles lie in one segment
+  const int q_pos_last0 = q_pos0 + kFaTile - 1;
+  const int q_pos_last = q_pos_last0 + (has1 ? kFaTile : 0);
+  const int q_tok0 = batch * d.sq + q_row0;
+  const int kv_tok_base = batch * d.skv;
+  auto need0 = [&](int kp) { return !(d.causal && kp > q_pos_last0); };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    if ((sb & 1023u) != 0) {
+      *abort_flag = 1;
+      record_status(p.status, kStatusBadArgument, 604, 0, 0, 1, 0);
+    }
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), 8);          // lane 0 of the eight softmax warps of the tile
+      mbar_init(pv_done(t), 1);
+      for (int q = 0; q < 4; ++q) mbar_init(x_bar(t, q), 2);   // lane 0 of the warp of either column half
+    }
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  auto tmem_s = [&](int t) { return tmem_base + t * 128; };      // S_t: 128 fp32 columns; P_t (bf16 pairs) reuses the first 64
+  auto tmem_o = [&](int t) { return tmem_base + 256 + t * D; };
+  const bool bad = *abort_flag != 0;
+
+  if (warp < 4) {
+    warpgroup_reg_dec<kFa4RegsIo>();
+    if (bad) {
+      // common exit
+    } else if (warp == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      if (lane == 0) {
+        mbar_expect_tx(q_full, (has1 ? 2 : 1) * S::kTileBytes);
+        for (int t = 0; t < (has1 ? 2 : 1); ++t)
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kQ + t * S::kTileBytes + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0 + t * kFaTile);
+        bool ok = true;
+        int last_seg = -1;
+        for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
+          if (!ok) return;
+          const int st = j % kStages;
+          const uint32_t ph = (j / kStages) & 1;
+          if (seg != last_seg) {
+            last_seg = seg;
+            if (d.kv_seg_ready != nullptr && d.kv_seg_flag[seg] >= 0) {
+              if (!wait_flag_ge(d.kv_seg_ready + d.kv_seg_flag[seg], d.ready_epoch, p.budget_ns)) {
+                *abort_flag = 1;
+                record_status(p.status, kStatusPeerTimeout, 604, 0, seg, 10, j);
+                ok = false;
+                return;
+              }
+              fence_proxy_async_all();
+            }
+          }
+          if (!mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          mbar_expect_tx(k_full(st), S::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kK + st * S::kTileBytes + a * kAtomBytes, &tmap_k, k_full(st), a * 64, kv_head, kv_tok_base + row);
+          if (!mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          mbar_expect_tx(v_full(st), S::kTileBytes);
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d(sb + S::kV + st * S::kTileBytes + a * kAtomBytes, &tmap_v, v_full(st), a * 64, kv_head, kv_tok_base + row);
+        });
+        if (!ok) record_status(p.status, kStatusMbarTimeout, 604, 0, 0, 11, 0);
+      }
+      __syncwarp();
+    } else if (warp == 1) {
+      // ------------------------------ MMA issuer ------------------------------
+      if (lane == 0) {
+        constexpr uint32_t idesc_s = make_idesc(kFaTile, kFaTile, 1, 1, 0, 0);
+        constexpr uint32_t idesc_o = make_idesc(kFaTile, D, 1, 1, 0, 1);
+        bool ok = mbar_wait(q_full, 0, abort_flag, p.budget_ns);
+        int pv[2] = {0, 0};
+        auto issue_s = [&](int t, int st) {
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
+            umma_f16_ss(tmem_s(t), make_smem_desc_sw128_kmajor(sb + S::kQ + t * S::kTileBytes + off),
+                        make_smem_desc_sw128_kmajor(sb + S::kK + st * S::kTileBytes + off), idesc_s, k != 0);
+          }
+          umma_commit(s_full(t));
+        };
+        // O_t += P_t V: A = P_t from tensor memory (16 bf16 of K per step = 8 columns), B = V tile, MN-major. P_t is complete -
+        // and, if rows had to be rescaled, O_t already scaled - when all eight softmax warps of the tile have arrived.
+        auto issue_pv = [&](int t, int st) {
+          if (!mbar_wait(p_full(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int k = 0; k < kFaTile / 16; ++k) {
+            const uint64_t dv = make_smem_desc_sw128_mnmajor(sb + S::kV + st * S::kTileBytes + k * 2048, kAtomBytes);
+            umma_f16_ts(tmem_o(t), tmem_s(t) + k * 8, dv, idesc_o, (k != 0) || (pv[t] != 0));
+          }
+          umma_commit(pv_done(t));
+          ++pv[t];
+          return true;
+        };
+        int prev_kp = 0, prev_st = 0;
+        const int n = for_each_kv_tile(d, q_pos_last, [&](int j, int /*row*/, int kp, int /*valid*/, int /*seg*/) {
+          if (!ok) return;
+          const int st = j % kStages;
+          if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (j == 0) {
+            if (need0(kp)) issue_s(0, st);
+            if (has1) issue_s(1, st);
+            umma_commit(k_empty(st));
+            prev_kp = kp; prev_st = st;
+            return;
+          }
+          if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
+          if (need0(kp)) issue_s(0, st);
+          if (has1) {
+            if (!issue_pv(1, prev_st)) { ok = false; return; }
+            issue_s(1, st);
+          }
+          umma_commit(v_empty(prev_st));
+          umma_commit(k_empty(st));
+          prev_kp = kp; prev_st = st;
+        });
+        if (ok && n > 0) {
+          ok = mbar_wait(v_full(prev_st), ((n - 1) / kStages) & 1, abort_flag, p.budget_ns);
+          if (ok && need0(prev_kp)) ok = issue_pv(0, prev_st);
+          if (ok && has1) ok = issue_pv(1, prev_st);
+        }
+        if (!ok) record_status(p.status, kStatusMbarTimeout, 604, 0, 0, 20, 0);
+      }
+      __syncwarp();
+    }
+  } else {
+    warpgroup_reg_inc<kFa4RegsSoftmax>();
+    // ------------------------------ softmax: tile t, column half `half`, thread = row ------------------------------
+    const int wg = (warp >> 2) - 1;            // 0..3
+    const int t = wg >> 1;
+    const int half = wg & 1;
+    if (!bad && (t == 0 || has1)) {
+      const int q4 = warp & 3;
+      const int row = q4 * 32 + lane;
+      const uint32_t xb = x_bar(t, q4);
+      uint32_t xph = 0;
+      // bounded meeting of the two warps that share this tile's rows (an mbarrier, not bar.sync, so that a failed wait
+      // elsewhere can never leave a warp parked at a barrier its partner will not reach)
+      auto meet = [&]() {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xb);
+        bool got = mbar_wait(xb, xph, abort_flag, p.budget_ns);
+        got = __all_sync(0xffffffffu, got);
+        xph ^= 1u;
+        return got;
+      };
+      const int my_pos = q_pos0 + t * kFaTile + row;
+      const int tile_row0 = q_row0 + t * kFaTile;
+      const float scale2 = d.scale * kLog2e;
+      float m_run = -INFINITY, l_run = 0.f;      // l_run: sum over this thread's 64 columns only
+      bool ok = true;
+      int cnt = 0;
+      const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
+      const uint32_t s_cols = tmem_s(t) + lane_off + half * 64;     // this thread's 64 score columns
+      const uint32_t p_cols = tmem_s(t) + lane_off + half * 32;     // ... and where its 32 packed P columns go
+      const uint32_t o_cols = tmem_o(t) + lane_off + half * (D / 2);
+      for_each_kv_tile(d, q_pos_last, [&](int /*j*/, int /*rowbuf*/, int kp, int valid, int /*seg*/) {
+        if (!ok) return;
+        if (t == 0 && !need0(kp)) return;
+        const uint32_t ph = cnt & 1;
+        ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return;
+        tc_fence_after_sync();
+        uint32_t r[64];
+        {
+          uint32_t (&r0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
+          uint32_t (&r1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
+          tmem_ld_32x32(s_cols, r0);
+          tmem_ld_32x32(s_cols + 32, r1);
+          tmem_ld_wait();
+        }
+        const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int col = half * 64 + i;
+            if (col >= valid || (d.causal && kp + col > my_pos)) r[i] = 0xff800000u;    // -inf: exp2 gives 0
+          }
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int i = 0; i < 64; i += 8) {        // three-input maxima: half the issue slots of a chain of two-input ones
+          mx4[0] = max3(mx4[0], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+          mx4[1] = max3(mx4[1], __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+          mx4[2] = max3(mx4[2], __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+          mx4[3] = max3(mx4[3], __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // exchange with the thread that holds the other half of the row (it has finished READING its scores by then, so the
+        // P columns that overlap its score columns may be written after this point)
+        float* slot = xch + ((ph * 2 + t) * 2) * kFaTile;
+        slot[half * kFaTile + row] = mx;
+        ok = meet();
+        if (!ok) return;
+        mx = fmaxf(mx, slot[(half ^ 1) * kFaTile + row]) * scale2;
+        // the offset follows the row maximum lazily: it moves only when the maximum has grown by more than 8
+        const float m_new = (mx > m_run + 8.f) ? mx : m_run;
+        const bool dead = m_new == -INFINITY;
+        const float alpha = (dead || m_new == m_run) ? 1.f : fast_exp2(m_run - m_new);
+        const float neg_m = dead ? 0.f : -m_new;
+        if (cnt > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // rare: rows of this warp moved their offset - scale this thread's half of the accumulator row once the previous
+          // P V product has landed (the next one is not issued before this warp has arrived on p_full)
+          ok = mbar_wait(pv_done(t), (cnt - 1) & 1, abort_flag, p.budget_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) return;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int cc = 0; cc < D / 2 / 16; ++cc) {
+            uint32_t o[16];
+            tmem_ld_32x16(o_cols + cc * 16, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x16(o_cols + cc * 16, o);
+          }
+          tmem_st_wait();
+        }
+        // exponentials: scale / subtract and the row sum as packed fp32 pairs; every fourth pair of an unmasked tile takes the
+        // polynomial on the FMA pipe instead of the special-function unit (masked tiles need the exact zero of ex2(-inf))
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t w[32];
+        const bool poly_ok = POLY && !need_mask && !dead;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x0, x1;
+          fma2_bcast(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), scale2, neg_m);
+          float e0, e1;
+          if (POLY && (i & 3) == 3 && poly_ok) {
+            e0 = poly_exp2(x0);
+            e1 = poly_exp2(x1);
+          } else {
+            e0 = fast_exp2(x0);
+            e1 = fast_exp2(x1);
+          }
+          if (i & 1) add2_acc(sum4[2], sum4[3], e0, e1);
+          else add2_acc(sum4[0], sum4[1], e0, e1);
+          w[i] = pack_bf16x2(e0, e1);
+        }
+        tmem_st_32x32(p_cols, w);
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(t));
+        l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+        m_run = m_new;
+        ++cnt;
+      });
+      // epilogue: the two halves add their row sums, then each normalises and stores its half of the output row
+      float* slot = xch + ((cnt & 1) * 2 + t) * 2 * kFaTile;
+      slot[half * kFaTile + row] = l_run;
+      if (ok) ok = meet();
+      const float l_tot = ok ? l_run + slot[(half ^ 1) * kFaTile + row] : 0.f;
+      const bool row_ok = tile_row0 + row < d.sq;
+      if (ok && cnt > 0) {
+        ok = mbar_wait(pv_done(t), (cnt - 1) & 1, abort_flag, p.budget_ns);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        if (cnt > 0) tc_fence_after_sync();
+        const float inv = l_tot > 0.f ? 1.0f / l_tot : 0.f;
+        if (p.lse != nullptr && row_ok && half == 0)
+          p.lse[(static_cast<long long>(batch) * d.hq + head) * d.sq + tile_row0 + row] =
+              (l_tot > 0.f) ? (m_run + log2f(l_tot)) * kLn2 : -INFINITY;
+        __nv_bfloat16* dst = p.out + (static_cast<long long>(q_tok0 + t * kFaTile + row) * d.hq + head) * D + half * (D / 2);
+#pragma unroll
+        for (int cc = 0; cc < D / 2 / 32; ++cc) {
+          uint32_t o[32];
+          if (cnt > 0) {
+            tmem_ld_32x32(o_cols + cc * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (row_ok) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              U4 u{pack_bf16x2(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv),
+                   pack_bf16x2(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv)};
+              st_global_v4(dst + cc * 32 + i, u);
+            }
+          }
+        }
+      } else if (lane == 0) {
+        record_status(p.status, kStatusMbarTimeout, 604, 0, 0, 30 + t, 0);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, bool POLY>
+__global__ void __launch_bounds__(kFa4Threads, 1)
+fa_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  fa_fwd4_cta<D, POLY>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
 template <int D, bool SPEC = false>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -1487,9 +1886,16 @@ fa_fwd3_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
 }
 
-// PKB_FA_V3=1 selects the two-tile kernel that keeps P in tensor memory (off until it has been validated and timed).
+// The two-tile kernel that keeps P in tensor memory is the default (880 against 670 TFLOP/s at S = 16384 causal, 32 / 8 heads,
+// d = 128); PKB_FA_V3=0 selects the older form with P in shared memory.
 static bool fa_use_v3() {
-  static const bool on = [] { const char* e = getenv("PKB_FA_V3"); return e != nullptr && e[0] == '1'; }();
+  static const bool on = [] { const char* e = getenv("PKB_FA_V3"); return !(e != nullptr && e[0] == '0'); }();
+  return on;
+}
+
+// PKB_FA_V4=1 selects the P-in-TMEM kernel with two threads per row.
+static bool fa_use_v4() {
+  static const bool on = [] { const char* e = getenv("PKB_FA_V4"); return e != nullptr && e[0] == '1'; }();
   return on;
 }
 
@@ -1530,7 +1936,21 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   p.trace = reinterpret_cast<long long*>(d.trace);
   p.trace_capacity = d.trace_capacity;
   const int n_tiles = (d.sq + kFaTile - 1) / kFaTile;
-  if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v3()) {
+  if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v4()) {
+    constexpr int smem = Fa4Smem<D>::kTotal;
+    dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
+    // PKB_FA_POLY=0: all exponentials on the special-function unit
+    static const bool poly = [] { const char* e = getenv("PKB_FA_POLY"); return !(e != nullptr && e[0] == '0'); }();
+    if (poly) {
+      auto kern = fa_fwd4_kernel<D, true>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFa4Threads, smem, stream>>>(tq, tk, tv, p);
+    } else {
+      auto kern = fa_fwd4_kernel<D, false>;
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      kern<<<grid, kFa4Threads, smem, stream>>>(tq, tk, tv, p);
+    }
+  } else if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v3()) {
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     auto kern = fa_fwd3_kernel<D>;

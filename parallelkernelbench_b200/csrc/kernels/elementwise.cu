@@ -59,9 +59,10 @@ __global__ void fp8_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ 
     float s = amax / 448.0f;
     if (pow2_scales && s > 0.f) s = exp2f(ceilf(log2f(s)));  // power-of-two scale (exact to undo)
     if (s == 0.f) s = 1.0f;
-    const float inv = 1.0f / s;
-    __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
-    __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+    // a true division, not a multiplication by the reciprocal: the quotient decides the e4m3 code at rounding boundaries,
+    // and x / s is what the PyTorch formulation computes (the kernel is memory bound, the divisions are free)
+    __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[0], s), __fdiv_rn(v[1], s)), __NV_SATFINITE, __NV_E4M3);
+    __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2], s), __fdiv_rn(v[3], s)), __NV_SATFINITE, __NV_E4M3);
     reinterpret_cast<uint32_t*>(y + b * 128)[lane] = (uint32_t)lo | ((uint32_t)hi << 16);
     if (lane == 0) scales[b] = s;
   }

@@ -199,12 +199,14 @@ def _gag_ref(rc, a, b):
 
 
 def _gag_ours(rc, a, b):
-    """Two launches (tcgen05 GEMM, symmetric-heap all-gather), or the single fused kernel when PKB_FUSED_GEMM_AG=1 and
-    the shapes fit it (local N a multiple of 64, K a multiple of 8)."""
+    """The single fused kernel (the GEMM's TMA-store epilogue writes every tile into the gathered result of every rank) when the
+    shapes fit it (local N a multiple of 64, K a multiple of 8); PKB_FUSED_GEMM_AG=0 selects the two-launch form (tcgen05 GEMM,
+    then the symmetric-heap all-gather). Measured on 2 GPUs at 4096 x 8192 x 1024: 0.112 ms fused, 0.146 ms two launches,
+    0.193 ms cuBLAS + NCCL."""
     import os
 
     (M, K), nl = a.shape, b.shape[1]
-    if os.environ.get("PKB_FUSED_GEMM_AG") == "1" and rc.dist.is_cuda and a.dtype == torch.bfloat16 and nl % 64 == 0 and K % 8 == 0:
+    if os.environ.get("PKB_FUSED_GEMM_AG", "1") != "0" and rc.dist.is_cuda and a.dtype == torch.bfloat16 and nl % 64 == 0 and K % 8 == 0:
         from ..ops.tp import GemmAllGather
 
         key = ("gemm_ag", M, nl)

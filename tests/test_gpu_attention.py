@@ -119,7 +119,7 @@ def test_flash_attention_backward_zigzag_segments():
         assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), f"{name}: {err}"
 
 
-@pytest.mark.parametrize("variant", ["PKB_FA_V3"])
+@pytest.mark.parametrize("variant", ["PKB_FA_V3=0", "PKB_FA_V4=1", "PKB_FA_V4=1,PKB_FA_POLY=0"])
 def test_forward_variants_pass_the_same_checks(variant):
     """The forward kernel variants are selected by an environment variable that is read once per process, so the forward
     checks of this file are repeated in a child process with the variable set."""
@@ -127,9 +127,10 @@ def test_forward_variants_pass_the_same_checks(variant):
     import subprocess
     import sys
 
-    if os.environ.get(variant) == "1":
+    extra = dict(item.split("=") for item in variant.split(","))
+    if all(os.environ.get(k) == v for k, v in extra.items()):
         pytest.skip("already running under the variant")
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-x", "-q", "-k", "matches_reference or zigzag_rank"],
-                       cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, variant: "1"})
+                       cwd=root, capture_output=True, text=True, timeout=900, env={**os.environ, **extra})
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1500:]
