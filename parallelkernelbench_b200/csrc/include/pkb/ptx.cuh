@@ -506,6 +506,13 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);
   return __bfloat1622float2(v);
 }
+// x / s rounded to nearest, given inv = 1 / s rounded to nearest: q0 = x * inv is within an ulp, the residual x - q0 * s is
+// exact in an FMA, and one correction step lands on the correctly rounded quotient (x and s normal, no overflow).
+__device__ __forceinline__ float div_rn_by(float x, float s, float inv) {
+  const float q0 = x * inv;
+  const float r = fmaf(-q0, s, x);
+  return fmaf(r, inv, q0);
+}
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

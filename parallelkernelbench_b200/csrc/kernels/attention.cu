@@ -986,11 +986,18 @@ struct Fa3Smem {
   static constexpr int kTotal = kBars + 512;
 };
 
+// Softmax arithmetic variant of the P-in-TMEM kernel used by default (see fa_fwd3_cta). Measured at S = 16384 causal, 32 / 8
+// heads, d = 128: 0 (scalar) 876 TFLOP/s, 1 (packed pairs, three-input maxima) 916, 2 (polynomial for a quarter of the
+// exponentials) 644, 3 (both) 676 - the polynomial costs more issue slots than the special-function unit it relieves.
+constexpr int kFa3DefaultOpt = 1;
+
 // register budgets per warpgroup after the prologue (the kernel is compiled for 128 per thread: 512 x 128 = the whole file)
 constexpr int kFa3RegsIo = 80, kFa3RegsSoftmax = 168, kFa3RegsCorr = 80;
 static_assert(128 * kFa3RegsIo + 256 * kFa3RegsSoftmax + 128 * kFa3RegsCorr <= 65536, "register budgets exceed the register file");
 
-template <int D>
+// OPT bit 0: three-input maxima and packed fp32 pairs for scale / subtract and the row sum; bit 1: every fourth pair of
+// exponentials of an unmasked tile on the FMA pipe (polynomial) instead of the special-function unit.
+template <int D, int OPT>
 __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                             const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
                                             const int head, const int batch) {
@@ -1215,8 +1222,18 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
             if (i >= valid || (d.causal && kp + i > my_pos)) r[i] = 0xff800000u;    // -inf: exp2 gives 0
         }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        if constexpr (OPT & 1) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+          for (int i = 0; i < 128; i += 8) {
+            mx4[0] = max3(mx4[0], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+            mx4[1] = max3(mx4[1], __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+            mx4[2] = max3(mx4[2], __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+            mx4[3] = max3(mx4[3], __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+        }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
         // the offset follows the row maximum lazily: it moves only when the maximum has grown by more than 8 (a factor
         // 256 in the exponentials, harmless in fp32 sums and bf16 P), which makes rescaling the accumulator rare
@@ -1232,15 +1249,45 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         if (lane == 0) mbar_arrive(a_full(t));
         // exponentials in place, then packed to bf16 pairs in the first 64 registers
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const float e = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, neg_m));
-          sum4[i & 3] += e;
-          r[i] = __float_as_uint(e);
-        }
         uint32_t w[64];
+        if constexpr (OPT != 0) {
+          const bool poly_ok = (OPT & 2) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
 #pragma unroll
-        for (int i = 0; i < 64; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+          for (int i = 0; i < 64; ++i) {
+            float x0, x1;
+            if constexpr (OPT & 1) {
+              fma2_bcast(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), scale2, neg_m);
+            } else {
+              x0 = fmaf(__uint_as_float(r[2 * i]), scale2, neg_m);
+              x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale2, neg_m);
+            }
+            float e0, e1;
+            if ((OPT & 2) && (i & 3) == 3 && poly_ok) {
+              e0 = poly_exp2(x0);
+              e1 = poly_exp2(x1);
+            } else {
+              e0 = fast_exp2(x0);
+              e1 = fast_exp2(x1);
+            }
+            if constexpr (OPT & 1) {
+              if (i & 1) add2_acc(sum4[2], sum4[3], e0, e1);
+              else add2_acc(sum4[0], sum4[1], e0, e1);
+            } else {
+              sum4[(2 * i) & 3] += e0;
+              sum4[(2 * i + 1) & 3] += e1;
+            }
+            w[i] = pack_bf16x2(e0, e1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            const float e = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, neg_m));
+            sum4[i & 3] += e;
+            r[i] = __float_as_uint(e);
+          }
+#pragma unroll
+          for (int i = 0; i < 64; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        }
         {
           const uint32_t (&w0)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[0]);
           const uint32_t (&w1)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[32]);
@@ -1354,11 +1401,11 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
   }
 }
 
-template <int D>
+template <int D, int OPT>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
-  fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+  fa_fwd3_cta<D, OPT>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // ================================================================================================
@@ -1883,7 +1930,7 @@ fa_fwd3_ring_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int id = blockIdx.x - a.comm_blocks;
   const int qp = pairs - 1 - id % pairs;
   const int hb = id / pairs;
-  fa_fwd3_cta<D>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
+  fa_fwd3_cta<D, kFa3DefaultOpt>(tmap_q, tmap_k, tmap_v, p, qp, hb % a.hq, hb / a.hq);
 }
 
 // The two-tile kernel that keeps P in tensor memory is the default (880 against 670 TFLOP/s at S = 16384 causal, 32 / 8 heads,
@@ -1953,9 +2000,21 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   } else if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v3()) {
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
-    auto kern = fa_fwd3_kernel<D>;
-    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
+    // PKB_FA_OPT=0..3 selects the softmax arithmetic variant (bit 0: packed pairs and three-input maxima, bit 1: polynomial)
+    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : kFa3DefaultOpt; }();
+#define PKB_FA3(O)                                                                                   \
+    {                                                                                                \
+      auto kern = fa_fwd3_kernel<D, O>;                                                              \
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+      kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);                                       \
+    }
+    switch (opt) {
+      case 1: PKB_FA3(1) break;
+      case 2: PKB_FA3(2) break;
+      case 3: PKB_FA3(3) break;
+      default: PKB_FA3(0) break;
+    }
+#undef PKB_FA3
   } else if (fa_use_pairs(d) && p.trace == nullptr) {
     constexpr int smem = Fa2Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);

@@ -71,12 +71,13 @@ __global__ void __launch_bounds__(256) fp8_quant_allgather_kernel(const QuantAgA
     if (t >= nthr) continue;
     float s = amax / 448.0f;
     if (s == 0.f) s = 1.0f;
+    const float inv = __frcp_rn(s);
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      // true divisions (x / s decides the code at rounding boundaries, as in the PyTorch formulation)
-      const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * j], s), __fdiv_rn(v[4 * j + 1], s)), __NV_SATFINITE, __NV_E4M3);
-      const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * j + 2], s), __fdiv_rn(v[4 * j + 3], s)), __NV_SATFINITE, __NV_E4M3);
+      // correctly rounded x / s (the quotient decides the code at rounding boundaries, as in the PyTorch formulation)
+      const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[4 * j], s, inv), div_rn_by(v[4 * j + 1], s, inv)), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[4 * j + 2], s, inv), div_rn_by(v[4 * j + 3], s, inv)), __NV_SATFINITE, __NV_E4M3);
       o[j] = (uint32_t)lo | ((uint32_t)hi << 16);
     }
     push_v4(c, a.use_mc, a.payload_off, (long long)c.grank * a.n + (t << 4), U4{o[0], o[1], o[2], o[3]});
