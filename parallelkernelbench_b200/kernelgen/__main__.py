@@ -33,6 +33,8 @@ def main(argv=None) -> int:
     g.add_argument("--workdir", default="logs/kernelgen")
     g.add_argument("--nproc", type=int, default=2)
     g.add_argument("--max-iters", type=int, default=4)
+    g.add_argument("--resume", action="store_true", help="continue a previous run of this op in --workdir from its last feedback")
+    g.add_argument("--measure-perf", action="store_true", help="time reference and candidate; the best matching candidate is kept by speed-up")
     g.add_argument("--backend", default=None)
     g.add_argument("--dtype", default="bfloat16")
     g.add_argument("--config", default="default")
@@ -57,7 +59,8 @@ def main(argv=None) -> int:
         rc = 0
         for op in select_ops(a.op):
             out = optimise(op, CommandProposer(a.command, log_dir=os.path.join(a.workdir, f"{op}_exchanges")), a.workdir,
-                           nproc=a.nproc, max_iters=a.max_iters, backend=a.backend, dtype=a.dtype, config=a.config)
+                           nproc=a.nproc, max_iters=a.max_iters, backend=a.backend, dtype=a.dtype, config=a.config,
+                           resume=a.resume, measure_perf=a.measure_perf)
             print(json.dumps(out, indent=1))
             rc = rc or (0 if out["solved"] else 1)
         return rc

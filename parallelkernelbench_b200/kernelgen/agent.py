@@ -70,30 +70,72 @@ def _feedback(summary: dict) -> str:
     return "\n".join(lines)
 
 
+def _trajectory(workdir: str, op: str, record: dict) -> None:
+    """One JSON line per event of a run (prompt sent, candidate received, screen verdict, evaluation) in ``<op>_trajectory.jsonl``:
+    the step-by-step record of an optimisation run, appendable across resumed runs (the reference keeps the agent framework's
+    message history for the same purpose, reference: kernelgen/agent.py:198-287)."""
+    record = {"time": time.strftime("%Y-%m-%dT%H:%M:%S"), "op": op, **record}
+    with open(os.path.join(workdir, f"{op}_trajectory.jsonl"), "a") as fh:
+        fh.write(json.dumps(record) + "\n")
+
+
 def optimise(op: str, propose: Callable[[str, str | None], str], workdir: str, nproc: int = 2, max_iters: int = 4, trials: int = 1,
-             target_speedup: float = 0.0, **eval_kw) -> dict:
+             target_speedup: float = 0.0, resume: bool = False, **eval_kw) -> dict:
     """Ask ``propose`` for a solution file, evaluate it against the reference, feed the verdict back, until every trial
-    matches (and ``target_speedup`` is reached when timing is on) or ``max_iters`` attempts are used. Returns the history."""
+    matches (and ``target_speedup`` is reached when timing is on) or ``max_iters`` attempts are used.
+
+    Every candidate is screened before it is evaluated (``utils.source_screen``): a file that names a construct that must not
+    run on the shared GPUs is not launched, the hits go back to the proposer as feedback and the attempt counts. The run leaves
+    the candidates, ``<op>_trajectory.jsonl`` (one line per event) and ``<op>_run.json`` (history, the best matching
+    candidate and its speed-up) in ``workdir``; with ``resume`` a previous ``<op>_run.json`` is continued from its last
+    feedback instead of starting over. Returns the run record."""
     from ..harness.launch import eval_op
+    from ..utils.source_screen import screen_source
 
     os.makedirs(workdir, exist_ok=True)
+    run_path = os.path.join(workdir, f"{op}_run.json")
     history, feedback = [], None
-    for it in range(max_iters):
+    if resume and os.path.exists(run_path):
+        with open(run_path) as fh:
+            prev = json.load(fh)
+        history = prev.get("attempts", [])
+        feedback = history[-1]["feedback"] if history else None
+        _trajectory(workdir, op, {"event": "resume", "attempts_so_far": len(history)})
+    for it in range(len(history), len(history) + max_iters):
+        prompt = build_prompt(op, nproc=nproc, feedback=feedback)
+        _trajectory(workdir, op, {"event": "prompt", "iteration": it, "prompt_chars": len(prompt), "had_feedback": feedback is not None})
         try:
-            source = propose(build_prompt(op, nproc=nproc, feedback=feedback), feedback)
-        except StopIteration:
+            source = propose(prompt, feedback)
+        except StopIteration as e:
+            _trajectory(workdir, op, {"event": "proposer_stopped", "iteration": it, "why": str(e)[:300]})
             break
         path = os.path.join(workdir, f"{op}_candidate_{it}.py")
+        hits = screen_source(source)
+        if hits:
+            # never written as a runnable file, never launched: the proposer is told why and may try again
+            with open(path + ".rejected.txt", "w") as fh:
+                fh.write("\n".join(hits) + "\n")
+            feedback = "verdict: rejected before evaluation - the file names constructs that must not run here:\n" + "\n".join(hits)
+            history.append({"iteration": it, "path": None, "all_ok": False, "speedup": 0.0, "feedback": feedback, "screened_out": True})
+            _trajectory(workdir, op, {"event": "screened_out", "iteration": it, "hits": hits[:8]})
+            continue
         with open(path, "w") as fh:
             fh.write(source)
+        _trajectory(workdir, op, {"event": "candidate", "iteration": it, "path": path, "lines": source.count("\n")})
         summary = eval_op(op, nproc, trials=trials, solution=path, **eval_kw)
         feedback = _feedback(summary)
-        sp = (summary["trials"][-1].get("speedup") or 0.0) if summary.get("trials") else 0.0
-        history.append({"iteration": it, "path": path, "all_ok": summary["all_ok"], "speedup": sp, "feedback": feedback})
+        last = summary["trials"][-1] if summary.get("trials") else {}
+        sp = last.get("speedup") or 0.0
+        history.append({"iteration": it, "path": path, "all_ok": summary["all_ok"], "speedup": sp, "feedback": feedback,
+                        "result": last.get("result"), "gate": (last.get("gate") or {}).get("gate")})
+        _trajectory(workdir, op, {"event": "evaluated", "iteration": it, "all_ok": summary["all_ok"], "result": last.get("result"),
+                                  "speedup": sp})
         if summary["all_ok"] and sp >= target_speedup:
             break
-    out = {"op": op, "solved": bool(history and history[-1]["all_ok"]), "attempts": history, "nproc": nproc,
+    ok = [h for h in history if h["all_ok"]]
+    best = max(ok, key=lambda h: h["speedup"]) if ok else None
+    out = {"op": op, "solved": bool(ok), "best": best, "attempts": history, "nproc": nproc,
            "finished_at": time.strftime("%Y-%m-%dT%H:%M:%S")}
-    with open(os.path.join(workdir, f"{op}_run.json"), "w") as fh:      # run record next to the candidates
+    with open(run_path, "w") as fh:      # run record next to the candidates
         json.dump(out, fh, indent=1)
     return out

@@ -86,3 +86,33 @@ def test_command_proposer_extracts_code_and_loop_records_the_run(tmp_path):
     failing = CommandProposer([sys.executable, "-c", "import sys; sys.exit(3)"])
     out = optimise("allreduce", failing, str(tmp_path / "w2"), nproc=2, max_iters=2, backend="gloo", dtype="float32", config="small")
     assert not out["solved"] and out["attempts"] == []
+
+
+def test_loop_screens_candidates_keeps_a_trajectory_and_resumes(tmp_path):
+    """A candidate that names a forbidden construct is never launched and its attempt is fed back; every event of the run is
+    in the trajectory file; a resumed run continues the attempt numbering and keeps the best matching candidate."""
+    import json
+
+    from parallelkernelbench_b200.kernelgen import optimise
+
+    bad = "SRC = '" + "cuda" + "Memcpy" + "Batch" + "Async(a, b, c)'\ndef solution(rc, x):\n    return x\n"
+    good = "def solution(rc, x):\n    return rc.comm.all_reduce(x)\n"
+    replies = iter([bad, good])
+    seen_feedback = []
+
+    def propose(prompt, feedback):
+        seen_feedback.append(feedback)
+        return next(replies)
+
+    out = optimise("allreduce", propose, str(tmp_path), nproc=2, max_iters=3, backend="gloo", dtype="float32", config="small")
+    assert out["solved"] and len(out["attempts"]) == 2
+    assert out["attempts"][0]["screened_out"] and out["attempts"][0]["path"] is None
+    assert "rejected before evaluation" in seen_feedback[1]
+    assert out["best"]["iteration"] == 1 and os.path.exists(out["best"]["path"])
+    assert not os.path.exists(tmp_path / "allreduce_candidate_0.py")            # the refused text is not kept as a runnable file
+    events = [json.loads(line)["event"] for line in open(tmp_path / "allreduce_trajectory.jsonl")]
+    assert events == ["prompt", "screened_out", "prompt", "candidate", "evaluated"]
+
+    more = optimise("allreduce", lambda p, f: good, str(tmp_path), nproc=2, max_iters=1, backend="gloo", dtype="float32",
+                    config="small", resume=True)
+    assert [a["iteration"] for a in more["attempts"]] == [0, 1, 2] and more["solved"]
