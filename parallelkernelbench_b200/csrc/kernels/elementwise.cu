@@ -44,18 +44,46 @@ __global__ void rope_kernel(const T* __restrict__ x, const T* __restrict__ cs, c
 // y = sat(x / s). One warp handles one block: 4 elements per lane.
 // ================================================================================================
 template <typename T>
-__global__ void fp8_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, float* __restrict__ scales,
-                                 long long nblocks, int pow2_scales) {
-  const int lane = threadIdx.x & 31;
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long b = warp; b < nblocks; b += nwarps) {
-    const T* p = x + b * 128 + lane * 4;
-    float v[4];
+__device__ __forceinline__ void load16(const T* p, float (&v)[16]);
+template <>
+__device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[16]) {
+  const U4 u0 = ld_global_nc_v4(p), u1 = ld_global_nc_v4(p + 8);
+  const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = (float)p[j];
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
-    amax = warp_max(amax);
+  for (int j = 0; j < 8; ++j) {
+    const float2 f = unpack_bf16x2(w[j]);
+    v[2 * j] = f.x; v[2 * j + 1] = f.y;
+  }
+}
+template <>
+__device__ __forceinline__ void load16<float>(const float* p, float (&v)[16]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const U4 u = ld_global_nc_v4(p + 4 * q);
+    v[4 * q] = __uint_as_float(u.x); v[4 * q + 1] = __uint_as_float(u.y);
+    v[4 * q + 2] = __uint_as_float(u.z); v[4 * q + 3] = __uint_as_float(u.w);
+  }
+}
+
+// A thread owns 16 consecutive elements (32 or 64 bytes in, one 16-byte store out); the 8 lanes of a 128-element block share
+// its maximum through three shuffles. Memory bound: what counts is bytes in flight per thread, not arithmetic.
+template <typename T>
+__global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ y, float* __restrict__ scales,
+                                                        long long nblocks, int pow2_scales) {
+  const long long nthr = nblocks * 8;
+  for (long long t0 = (long long)blockIdx.x * blockDim.x; t0 < nthr; t0 += (long long)gridDim.x * blockDim.x) {
+    const long long t = t0 + threadIdx.x;      // nthr is a multiple of 8: a group of 8 lanes is active or idle as a whole
+    float v[16];
+    float amax = 0.f;
+    if (t < nthr) {
+      load16<T>(x + (t << 4), v);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    }
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    if (t >= nthr) continue;
     float s = amax / 448.0f;
     if (pow2_scales && s > 0.f) s = exp2f(ceilf(log2f(s)));  // power-of-two scale (exact to undo)
     if (s == 0.f) s = 1.0f;
@@ -63,10 +91,15 @@ __global__ void fp8_quant_kernel(const T* __restrict__ x, uint8_t* __restrict__ 
     // x / s is what the PyTorch formulation computes. One reciprocal per block, then per element a product, its residual
     // and one correction (three FMA-pipe instructions instead of a division each).
     const float inv = __frcp_rn(s);
-    __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[0], s, inv), div_rn_by(v[1], s, inv)), __NV_SATFINITE, __NV_E4M3);
-    __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[2], s, inv), div_rn_by(v[3], s, inv)), __NV_SATFINITE, __NV_E4M3);
-    reinterpret_cast<uint32_t*>(y + b * 128)[lane] = (uint32_t)lo | ((uint32_t)hi << 16);
-    if (lane == 0) scales[b] = s;
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[4 * j], s, inv), div_rn_by(v[4 * j + 1], s, inv)), __NV_SATFINITE, __NV_E4M3);
+      const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(div_rn_by(v[4 * j + 2], s, inv), div_rn_by(v[4 * j + 3], s, inv)), __NV_SATFINITE, __NV_E4M3);
+      o[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+    }
+    st_global_v4(y + (t << 4), U4{o[0], o[1], o[2], o[3]});
+    if ((t & 7) == 0) scales[t >> 3] = s;
   }
 }
 
@@ -300,7 +333,8 @@ int pkb_fp8_quant_1x128(const void* x, void* y, void* scales, long long n, int d
   if (n == 0) return kApiOk;
   const long long nb = n / 128;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = grid_1d(nb * 32, 256);
+  PKB_CHECK_ARG(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0, "input and payload must be 16-byte aligned");
+  const int grid = grid_1d(nb * 8, 256);
   if (dtype == 0)
     fp8_quant_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), static_cast<uint8_t*>(y),
                                                         static_cast<float*>(scales), nb, pow2_scales);
