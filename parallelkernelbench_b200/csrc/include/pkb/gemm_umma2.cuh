@@ -28,7 +28,11 @@ struct alignas(64) GemmOutMaps {
 
 // BCAST (with TMA_STORE): every output tile is stored into the result of EVERY rank (maps m[0 .. world)), at column
 // p.bcast_col0 + its own column: the all-gather along N of a column-parallel GEMM happens in the epilogue.
-template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false, bool BCAST = false>
+// A_MN / B_MN: the operand is given MN-major ([K, M] resp. [K, N] row-major, the layouts of dX = dY W and dW = dY^T X): a CTA's
+// 128 rows (columns) of it arrive as two 64 x 64 boxes (one 128-byte-swizzle atom each, 8 KiB apart) and are described to the
+// tensor core as MN-major; 16 along K is then 16 shared-memory rows = 2048 bytes.
+template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false, bool BCAST = false, bool A_MN = false,
+          bool B_MN = false>
 __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const int pair,
                                                const int num_pairs,
@@ -36,6 +40,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
                                                const CUtensorMap* tmap_a_local = nullptr) {
   static_assert(!(TMA_STORE && OUT_F32), "the TMA-store epilogue writes bf16");
   static_assert(!BCAST || (TMA_STORE && !RS_SCATTER), "the broadcast epilogue is a TMA-store epilogue");
+  static_assert(!(A_MN && A_READY), "the gathered-A hook loads A K-major");
   constexpr int kStages = kGemm2Stages;
   constexpr int BN = kGemm2TileN;
   constexpr uint32_t kTmemCols = 512;
@@ -145,8 +150,18 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           }
           if (leader) mbar_expect_tx(full_bar(stage), 2 * kGemm2StageBytes);
           const uint32_t sa = smem_base + stage * kGemm2StageBytes;
-          tma_load_2d_pair(sa, map_a, full_bar(stage), kb * kGemmBlockK, a_row);
-          tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0);
+          if constexpr (A_MN) {
+            tma_load_2d_pair(sa, map_a, full_bar(stage), a_row, kb * kGemmBlockK);
+            tma_load_2d_pair(sa + 8192, map_a, full_bar(stage), a_row + 64, kb * kGemmBlockK);
+          } else {
+            tma_load_2d_pair(sa, map_a, full_bar(stage), kb * kGemmBlockK, a_row);
+          }
+          if constexpr (B_MN) {
+            tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), col0, kb * kGemmBlockK);
+            tma_load_2d_pair(sa + kGemm2ABytes + 8192, &tmap_b, full_bar(stage), col0 + 64, kb * kGemmBlockK);
+          } else {
+            tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -161,7 +176,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
     if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc(kGemm2TileM, BN, 1, 1);
+      constexpr uint32_t idesc = make_idesc(kGemm2TileM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -182,11 +197,12 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           }
           tc_fence_after_sync();
           const uint32_t sa = smem_base + stage * kGemm2StageBytes;
-          const uint64_t da = make_smem_desc_sw128_kmajor(sa);
-          const uint64_t db = make_smem_desc_sw128_kmajor(sa + kGemm2ABytes);
+          const uint64_t da = A_MN ? make_smem_desc_sw128_mnmajor(sa, 8192u) : make_smem_desc_sw128_kmajor(sa);
+          const uint64_t db = B_MN ? make_smem_desc_sw128_mnmajor(sa + kGemm2ABytes, 8192u)
+                                   : make_smem_desc_sw128_kmajor(sa + kGemm2ABytes);
 #pragma unroll
-          for (int k = 0; k < kGemmBlockK / 16; ++k)
-            umma_f16_ss_pair(tmem_d, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          for (int k = 0; k < kGemmBlockK / 16; ++k)   // 16 along K: +32 bytes inside a K-major row, +2048 bytes MN-major
+            umma_f16_ss_pair(tmem_d, da + (A_MN ? 128u : 2u) * k, db + (B_MN ? 128u : 2u) * k, idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit_pair(empty_bar(stage), 0x3);
           if (++stage == kStages) {
             stage = 0;
@@ -411,6 +427,14 @@ gemm_umma2_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   gemm_umma2_cta<EPI, OUT_F32, A_READY, RS_SCATTER>(tmap_a, tmap_b, p, blockIdx.x >> 1,
                                                     gridDim.x >> 1);
+}
+
+// MN-major operands (see gemm_umma2_cta), register epilogue (bf16 or fp32 output)
+template <int EPI, bool OUT_F32, bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_umma2_mn_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                     const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma2_cta<EPI, OUT_F32, false, false, false, false, A_MN, B_MN>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1);
 }
 
 // bf16 output through the TMA-store epilogue

@@ -1,4 +1,6 @@
 // Host launchers of the tcgen05 GEMM (kernel template in pkb/gemm_umma.cuh).
+#include <cstdlib>
+
 #include "pkb/api.h"
 #include "pkb/gemm_umma2.cuh"
 #include "pkb/host.h"
@@ -79,6 +81,25 @@ static int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, 
   }
   set_last_error("unknown epilogue");
   return kApiBadArgument;
+}
+
+// The backward layouts on CTA pairs: PKB_GEMM_PAIR_MN=0 keeps the one-CTA-per-tile kernels.
+static bool pair_mn_enabled() {
+  static const bool on = [] { const char* e = getenv("PKB_GEMM_PAIR_MN"); return !(e != nullptr && e[0] == '0'); }();
+  return on;
+}
+
+template <int EPI, bool OUT_F32, bool A_MN, bool B_MN>
+static int launch_pair_mn(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int M, int N, cudaStream_t stream) {
+  auto kern = gemm_umma2_mn_kernel<EPI, OUT_F32, A_MN, B_MN>;
+  PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemm2SmemTotal));
+  p.group_m = 8;
+  const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int ctas = sm_count() & ~1;
+  if (ctas > 2 * tiles) ctas = 2 * tiles;
+  kern<<<ctas, kGemmThreads, kGemm2SmemTotal, stream>>>(ta, tb, p);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
 }
 
 }  // namespace pkb
@@ -295,6 +316,12 @@ extern "C" int pkb_gemm_bf16_bkn(const void* a, long long lda, const void* b, lo
   int ctas = sm_count();
   if (ctas > tiles) ctas = tiles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair_mn_enabled() && M >= 256 && N >= 256) {
+    // large problems: 256 x 256 tiles on CTA pairs (every operand byte crosses L2 -> shared memory once per pair)
+    if (epilogue == kEpiSilu)
+      return out_f32 ? launch_pair_mn<kEpiSilu, true, false, true>(ta, tb, p, M, N, s) : launch_pair_mn<kEpiSilu, false, false, true>(ta, tb, p, M, N, s);
+    return out_f32 ? launch_pair_mn<kEpiNone, true, false, true>(ta, tb, p, M, N, s) : launch_pair_mn<kEpiNone, false, false, true>(ta, tb, p, M, N, s);
+  }
   constexpr int smem = GemmSmem<128>::kTotal;
 #define PKB_BKN(EPI, F32)                                                                          \
   {                                                                                                \
@@ -329,6 +356,8 @@ extern "C" int pkb_gemm_bf16_tn(const void* a, long long lda, const void* b, lon
   int ctas = sm_count();
   if (ctas > tiles) ctas = tiles;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (pair_mn_enabled() && M >= 256 && N >= 256)
+    return out_f32 ? launch_pair_mn<kEpiNone, true, true, true>(ta, tb, p, M, N, s) : launch_pair_mn<kEpiNone, false, true, true>(ta, tb, p, M, N, s);
   constexpr int smem = GemmSmem<256>::kTotal;
   if (out_f32) {
     auto kern = gemm_umma_tn_kernel<256, true>;

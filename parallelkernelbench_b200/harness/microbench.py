@@ -9,7 +9,7 @@ larger than L2 between calls (so no call finds its inputs cached), mean and mini
 ``{"case", "ours_ms", "lib_ms", "ours_tflops", "lib_tflops", "ratio_vs_lib", ...}`` with the fraction of the measured bf16
 peak where the case is a contraction.
 
-Cases: ``gemm`` (8192^3 bf16), ``fa_fwd`` / ``fa_bwd`` (sequence 16384, causal, 32 query / 8 KV heads, head dim 128),
+Cases: ``gemm`` (8192^3 bf16), ``gemm_bwd`` (dX and dW of a 4096 x 4096 x 14336 linear layer), ``fa_fwd`` / ``fa_bwd`` (sequence 16384, causal, 32 query / 8 KV heads, head dim 128),
 ``fa_fwd_4k``, ``grouped_bf16`` / ``grouped_fp8`` (32 experts x 2048 rows, 7168 -> 4096 gate/up with SwiGLU: the expert GEMM of
 the 256-expert MoE configuration per rank), ``rmsnorm``, ``fp8_quant``.
 """
@@ -80,6 +80,27 @@ def case_gemm(t: _Timer) -> dict:
     wt = w.t()
     lib = t(lambda: torch.matmul(a, wt, out=out))
     return _line("gemm", ours, lib, flops=2.0 * n ** 3, shape=[n, n, n])
+
+
+def case_gemm_bwd(t: _Timer) -> dict:
+    """The two backward layouts of a linear layer at Llama-8B MLP size: dX = dY @ W (B given [K, N]) and dW = dY^T @ X."""
+    from ..ops import gemm_bf16_kn, gemm_bf16_tn
+
+    tokens, n_in, n_out = 4096, 4096, 14336
+    dy = torch.randn(tokens, n_out, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n_out, n_in, device="cuda", dtype=torch.bfloat16) * 0.02
+    x = torch.randn(tokens, n_in, device="cuda", dtype=torch.bfloat16)
+    dx = torch.empty(tokens, n_in, device="cuda", dtype=torch.bfloat16)
+    dw = torch.empty(n_out, n_in, device="cuda", dtype=torch.float32)
+    ours_dx = t(lambda: gemm_bf16_kn(dy, w, out=dx))
+    lib_dx = t(lambda: torch.matmul(dy, w, out=dx))
+    ours_dw = t(lambda: gemm_bf16_tn(dy, x, out=dw))
+    dwb = torch.empty(n_out, n_in, device="cuda", dtype=torch.bfloat16)
+    lib_dw = t(lambda: torch.matmul(dy.t(), x, out=dwb))
+    fl = 2.0 * tokens * n_in * n_out
+    out = _line("gemm_bwd_dx", ours_dx, lib_dx, flops=fl, shape=[tokens, n_in, n_out])
+    out["dw"] = _line("gemm_bwd_dw", ours_dw, lib_dw, flops=fl, note="ours writes fp32, the library call bf16")
+    return out
 
 
 def _attn_inputs(S, hq=32, hkv=8, d=128):

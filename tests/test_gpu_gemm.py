@@ -88,7 +88,7 @@ def test_large_k_accumulation():
     torch.testing.assert_close(out.float(), _ref(a, w), atol=3e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (300, 200, 136)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 384, 512), (300, 200, 136), (520, 712, 328), (4096, 4096, 1024)])
 def test_gemm_with_row_major_kn_weight(M, N, K):
     from parallelkernelbench_b200.ops.gemm import gemm_bf16_kn
 
@@ -98,7 +98,7 @@ def test_gemm_with_row_major_kn_weight(M, N, K):
     torch.testing.assert_close(out.float(), a.float() @ b.float(), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 512, 1000), (4096, 1024, 4096)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (384, 512, 1000), (4096, 1024, 4096), (264, 648, 200)])
 def test_gemm_transposed_a_for_weight_gradients(M, N, K):
     from parallelkernelbench_b200.ops import gemm_bf16_tn
 
