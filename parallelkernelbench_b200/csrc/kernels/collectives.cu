@@ -652,6 +652,92 @@ coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
 }
 
 // ================================================================================================
+// NVLS push all-gather: every rank reads its own shard once and stores it through the multicast mapping, the switch
+// replicates each 16-byte store into the gathered buffer of every rank. A sender's link carries its shard once (a pull
+// all-gather serves it W-1 times), stores are posted (no round trip to hide), and the local loads come from HBM.
+// NVLS reduce-scatter: every rank reads the sum of its slice over all ranks with multimem.ld_reduce (the switch adds) and
+// writes it to its local output - the first half of the NVLS all-reduce on its own.
+// ================================================================================================
+struct NvlsAgArgs {
+  const void* src;         // this rank's shard, `bytes` bytes (16-byte aligned, any device memory)
+  long long bytes;         // multiple of 16
+  uint64_t gather_off;     // heap offset of the gathered buffer [gsize][bytes]
+  void* out;               // optional local output that receives a copy of the gathered buffer (null: caller reads the heap)
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_allgather_nvls_kernel(const SymmCtx c, const NvlsAgArgs a) {
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  GridCopier cp;
+  cp.init(bulk_smem, &s_abort, c.budget_ns);
+  // all ranks have entered: the previous gathered result has been consumed everywhere
+  if (!symm_grid_barrier(c, 206, 1)) return;
+  const long long nvec = a.bytes >> 4;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const uint8_t* src = static_cast<const uint8_t*>(a.src);
+  uint8_t* dst = symm_mc<uint8_t>(c, a.gather_off) + (long long)c.grank * a.bytes;
+  long long i = tid;
+  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {   // four local loads in flight per thread, then four posted stores
+    const U4 v0 = ld_global_nc_v4(src + (i << 4)), v1 = ld_global_nc_v4(src + ((i + nthreads) << 4));
+    const U4 v2 = ld_global_nc_v4(src + ((i + 2 * nthreads) << 4)), v3 = ld_global_nc_v4(src + ((i + 3 * nthreads) << 4));
+    multimem_st_v4(dst + (i << 4), v0);
+    multimem_st_v4(dst + ((i + nthreads) << 4), v1);
+    multimem_st_v4(dst + ((i + 2 * nthreads) << 4), v2);
+    multimem_st_v4(dst + ((i + 3 * nthreads) << 4), v3);
+  }
+  for (; i < nvec; i += nthreads) multimem_st_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
+  // every block of every rank has issued its stores once this barrier passes
+  if (!symm_grid_barrier(c, 206, 2)) return;
+  if (a.out != nullptr) {
+    cp.proxy_fence();
+    cp.copy(a.out, symm_local<uint8_t>(c, a.gather_off), a.bytes * c.gsize);
+  }
+}
+
+struct NvlsRsArgs {
+  const void* src;       // this rank's full input [gsize * n] (staged into the heap unless it already lives there)
+  long long n;           // elements per slice
+  uint64_t stage_off;
+  void* out;             // local output, n elements
+  int src_in_heap;
+};
+
+template <int DT>
+__global__ void __launch_bounds__(kCollThreads)
+coll_reduce_scatter_nvls_kernel(const SymmCtx c, const NvlsRsArgs a) {
+  using P = Pack<DT>;
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  GridCopier cp;
+  cp.init(bulk_smem, &s_abort, c.budget_ns);
+  if (!a.src_in_heap) cp.copy(symm_local<uint8_t>(c, a.stage_off), a.src, a.n * c.gsize * P::kElem);
+  cp.proxy_fence();
+  if (!symm_grid_barrier(c, 207, 1)) return;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long nvec = a.n / P::kN;                       // the host checks that n is a multiple of the vector width
+  const uint8_t* mc = symm_mc<uint8_t>(c, a.stage_off) + (long long)c.grank * a.n * P::kElem;
+  uint8_t* out = static_cast<uint8_t*>(a.out);
+  auto ldr = [&](long long i) {
+    if constexpr (DT == kCollBf16) return multimem_ld_reduce_bf16x8(mc + (i << 4));
+    else return multimem_ld_reduce_f32x4(mc + (i << 4));
+  };
+  long long i = tid;
+  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
+    const U4 r0 = ldr(i), r1 = ldr(i + nthreads), r2 = ldr(i + 2 * nthreads), r3 = ldr(i + 3 * nthreads);
+    st_global_v4(out + (i << 4), r0);
+    st_global_v4(out + ((i + nthreads) << 4), r1);
+    st_global_v4(out + ((i + 2 * nthreads) << 4), r2);
+    st_global_v4(out + ((i + 3 * nthreads) << 4), r3);
+  }
+  for (; i < nvec; i += nthreads) st_global_v4(out + (i << 4), ldr(i));
+  // nobody may overwrite its staged input (the next call) while a peer still reads it through the switch
+  symm_grid_barrier(c, 207, 2);
+}
+
+// ================================================================================================
 // all-to-all-v: rows of row_bytes; send_counts/send_offsets (in rows, int64, device) per destination
 // ================================================================================================
 struct A2AVArgs {
@@ -906,6 +992,38 @@ int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, l
   if (dtype == kCollBf16) launch_with_ring(coll_allreduce_nvls_kernel<kCollBf16>, grid, s, c, a);
   else if (dtype == kCollF32) launch_with_ring(coll_allreduce_nvls_kernel<kCollF32>, grid, s, c, a);
   else { set_last_error("NVLS all-reduce supports bf16 and fp32"); return kApiUnsupported; }
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// Gathered buffer [gsize][bytes] at heap offset gather_off on every rank (and a local copy in `out` when it is not null);
+// bytes % 16 == 0, src 16-byte aligned; needs the multicast mapping and the whole-job group.
+int pkb_coll_allgather_nvls(const pkb_symm_ctx* h, const void* src, long long bytes, unsigned long long gather_off, void* out,
+                            int max_blocks, void* stream) {
+  if (int rc = symm_ctx_check(h)) return rc;
+  PKB_CHECK_ARG(h->mc_base != 0 && h->gsize == h->world, "NVLS all-gather needs the multicast mapping and the whole-job group");
+  PKB_CHECK_ARG(bytes > 0 && bytes % 16 == 0 && (gather_off & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                (reinterpret_cast<uintptr_t>(out) & 15) == 0, "16-byte alignment and a size that is a multiple of 16");
+  NvlsAgArgs a{src, bytes, gather_off, out};
+  launch_with_ring(coll_allgather_nvls_kernel, grid_for(bytes, max_blocks), static_cast<cudaStream_t>(stream), symm_ctx_from_api(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// out[n] = sum over ranks of slice grank of every rank's [gsize * n] input (bf16 or fp32, n a multiple of 8 resp. 4).
+int pkb_coll_reduce_scatter_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n, unsigned long long stage_off,
+                                 void* out, int src_in_heap, int max_blocks, void* stream) {
+  if (int rc = symm_ctx_check(h)) return rc;
+  PKB_CHECK_ARG(h->mc_base != 0 && h->gsize == h->world, "NVLS reduce-scatter needs the multicast mapping and the whole-job group");
+  PKB_CHECK_ARG(dtype == kCollBf16 || dtype == kCollF32, "NVLS reduce-scatter supports bf16 and fp32");
+  PKB_CHECK_ARG(n > 0 && n % (dtype == kCollBf16 ? 8 : 4) == 0, "slice length must be a multiple of 16 bytes");
+  PKB_CHECK_ARG((stage_off & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0, "16-byte alignment");
+  NvlsRsArgs a{src, n, stage_off, out, src_in_heap};
+  const int grid = grid_for(n * elem_size(dtype), max_blocks);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  SymmCtx c = symm_ctx_from_api(h);
+  if (dtype == kCollBf16) launch_with_ring(coll_reduce_scatter_nvls_kernel<kCollBf16>, grid, s, c, a);
+  else launch_with_ring(coll_reduce_scatter_nvls_kernel<kCollF32>, grid, s, c, a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

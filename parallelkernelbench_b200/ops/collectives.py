@@ -137,9 +137,15 @@ def all_reduce(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Te
     return out
 
 
+def _nvls_ok(group: SymmGroup) -> bool:
+    return group.heap.mc_base != 0 and group.is_whole_heap and group.size > 1
+
+
 def reduce_scatter(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torch.Tensor | None = None,
-                   scale: float = 1.0) -> torch.Tensor:
-    """``x`` is ``[W * n, ...]``; rank g receives the reduction of chunk g."""
+                   scale: float = 1.0, algo: str = "auto") -> torch.Tensor:
+    """``x`` is ``[W * n, ...]``; rank g receives the reduction of chunk g. ``algo``: ``"pull"`` (peer loads), ``"nvls"``
+    (the switch adds: ``multimem.ld_reduce`` of this rank's slice; bf16 / fp32 sums on the whole-job group) or ``"auto"``
+    (NVLS for slices of ``tuning.reduce_scatter_nvls_min`` bytes and more)."""
     x = _check(x)
     W = group.size
     if x.shape[0] % W != 0:
@@ -147,6 +153,17 @@ def reduce_scatter(x: torch.Tensor, group: SymmGroup, op: str = "sum", out: torc
     n = x.numel() // W
     if out is None:
         out = torch.empty((x.shape[0] // W, *x.shape[1:]), dtype=x.dtype, device=x.device)
+    nvls_fit = (_nvls_ok(group) and op == "sum" and scale == 1.0 and x.dtype in (torch.bfloat16, torch.float32)
+                and (n * x.element_size()) % 16 == 0 and out.is_contiguous() and out.data_ptr() % 16 == 0)
+    if algo == "nvls" and not nvls_fit:
+        raise RuntimeError("NVLS reduce-scatter needs multicast, the whole-job group, a bf16/fp32 sum and 16-byte slices")
+    if algo == "nvls" or (algo == "auto" and nvls_fit and n * x.element_size() >= tuning.reduce_scatter_nvls_min(W)):
+        off, stage_bytes = _stage(group, "rs_in", x)
+        nv.check(_lib().pkb_coll_reduce_scatter_nvls(group.ref, _DT[x.dtype], nv.ptr(x), nv.c_ll(n), ctypes.c_ulonglong(off),
+                                                     nv.ptr(out), 0 if stage_bytes else 1, 0, nv.current_stream()),
+                 "pkb_coll_reduce_scatter_nvls")
+        nv.count_launch()
+        return out
     off, stage_bytes = _stage(group, "rs_in", x)
     nv.check(_lib().pkb_coll_reduce(group.ref, _DT[x.dtype], _OP[op], nv.ptr(x),
                                     nv.c_ll(x.numel() if stage_bytes else 0), ctypes.c_ulonglong(off),
@@ -179,13 +196,28 @@ def _gather_call(group, x, mask, in_base, member_stride, seg_bytes, out, out_str
     nv.count_launch()
 
 
-def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Returns ``[W, *x.shape]`` (member order)."""
+def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None, algo: str = "auto") -> torch.Tensor:
+    """Returns ``[W, *x.shape]`` (member order). ``algo``: ``"pull"`` (peer loads / TMA-bulk requests), ``"nvls"`` (every rank
+    stores its shard once through the multicast mapping and the switch replicates it) or ``"auto"`` (NVLS for shards of
+    ``tuning.all_gather_nvls_min`` bytes and more on the whole-job group)."""
     x = _check(x)
     W = group.size
     if out is None:
         out = torch.empty((W, *x.shape), dtype=x.dtype, device=x.device)
     nb = x.numel() * x.element_size()
+    nvls_fit = _nvls_ok(group) and nb % 16 == 0 and x.data_ptr() % 16 == 0 and out.is_contiguous() and out.data_ptr() % 16 == 0
+    if algo == "nvls" and not nvls_fit:
+        raise RuntimeError("NVLS all-gather needs multicast, the whole-job group and 16-byte aligned shards")
+    if algo == "nvls" or (algo == "auto" and nvls_fit and nb >= tuning.all_gather_nvls_min(W)):
+        goff = group.heap.contains(out)
+        direct = goff is not None and goff % 16 == 0          # the caller's result already lives in the heap: no copy out
+        if not direct:
+            cap = 1 << max(12, (W * nb - 1).bit_length())
+            goff = group.heap.named(("ag_nvls", group.channel), (cap,), torch.uint8).offset
+        nv.check(_lib().pkb_coll_allgather_nvls(group.ref, nv.ptr(x), nv.c_ll(nb), ctypes.c_ulonglong(goff),
+                                                nv.ptr(None if direct else out), 0, nv.current_stream()), "pkb_coll_allgather_nvls")
+        nv.count_launch()
+        return out
     if W > 1 and 0 < nb <= tuning.all_gather_ll_max(W) and nb % 4 == 0 and x.data_ptr() % 4 == 0 and out.is_contiguous():
         buf, cap_units = _ll_slots(group, nb)
         nv.check(_lib().pkb_coll_allgather_ll(group.ref, nv.ptr(x), nv.c_ll(nb // 4), ctypes.c_ulonglong(buf.offset), nv.c_ll(cap_units),

@@ -48,6 +48,21 @@ def all_gather_ll_max(world: int, table: dict | None = None) -> int:
     return int(_row("all_gather", world, table)["ll_max_bytes"])
 
 
+_NVLS_OFF = 1 << 62
+
+
+def all_gather_nvls_min(world: int, table: dict | None = None) -> int:
+    """Shard size in bytes from which the all-gather stores through the multicast mapping instead of pulling from the peers
+    (``nvls_min_bytes`` of the table's ``all_gather`` row; absent = never)."""
+    return int(_row("all_gather", world, table).get("nvls_min_bytes", _NVLS_OFF))
+
+
+def reduce_scatter_nvls_min(world: int, table: dict | None = None) -> int:
+    """Slice size in bytes from which the reduce-scatter lets the switch add (``multimem.ld_reduce``) instead of reading the
+    peers' slices one by one (``nvls_min_bytes`` of the table's ``reduce_scatter`` row; absent = never)."""
+    return int(_row("reduce_scatter", world, table).get("nvls_min_bytes", _NVLS_OFF))
+
+
 def thresholds_from_timings(timings: dict[str, dict[int, float]]) -> dict:
     """One table row from measured times: ``timings[algo][nbytes] = microseconds``.
 

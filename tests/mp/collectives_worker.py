@@ -151,6 +151,18 @@ def main() -> int:
             report(f"all_reduce_ in place {dtype}", torch.allclose(y.float(), ref.float(), atol=2e-2, rtol=2e-2) and y.data_ptr() == xs.local.data_ptr(),
                    f"maxerr={(y.float() - ref.float()).abs().max().item():.3g}")
 
+    if heap.mc_base and W > 1:
+        # the switch-side forms of all-gather and reduce-scatter against NCCL
+        xa = torch.randn(3 * 4096 + 8, device=dev, dtype=torch.bfloat16, generator=torch.Generator(device=dev).manual_seed(70 + r))
+        ref = torch.empty(W * xa.numel(), device=dev, dtype=torch.bfloat16); dist.all_gather_into_tensor(ref, xa)
+        report("all_gather nvls", torch.equal(C.all_gather(xa, g, algo="nvls").view(-1), ref))
+        for dtype in (torch.bfloat16, torch.float32):
+            xr = torch.randn(W * 2048, 8, device=dev, generator=torch.Generator(device=dev).manual_seed(80 + r)).to(dtype)
+            ref = torch.empty(2048, 8, device=dev, dtype=dtype); dist.reduce_scatter_tensor(ref, xr)
+            got = C.reduce_scatter(xr, g, algo="nvls")
+            report(f"reduce_scatter nvls {dtype}", torch.allclose(got.float(), ref.float(), atol=2e-2, rtol=2e-2),
+                   f"maxerr={(got.float() - ref.float()).abs().max().item():.3g}")
+
     # quick timing vs NCCL (device time, max over ranks)
     def timeit(fn, n=30, warm=10):
         for _ in range(warm):
@@ -187,13 +199,15 @@ def main() -> int:
         x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16).view(W, -1)
         yr = torch.empty(nbytes // 2 // W, device=dev, dtype=torch.bfloat16)
         t_nccl = timeit(lambda: dist.reduce_scatter_tensor(yr, x.view(-1)))
-        t_ours = timeit(lambda: C.reduce_scatter(x.view(W * (x.shape[1] // 8), 8), g))
+        t_ours = timeit(lambda: C.reduce_scatter(x.view(W * (x.shape[1] // 8), 8), g, algo="pull"))
+        t_nvls = timeit(lambda: C.reduce_scatter(x.view(W * (x.shape[1] // 8), 8), g, algo="nvls")) if heap.mc_base and W > 1 else float("nan")
         ya = torch.empty_like(x)
         t_nccl_a = timeit(lambda: dist.all_to_all_single(ya.view(-1), x.view(-1)))
         t_ours_a = timeit(lambda: C.all_to_all(x, g, out=ya))
         if r == 0:
             per_dir = (W - 1) / W * nbytes
-            print(f"PERF reduce_scatter {nbytes}B nccl={t_nccl * 1e3:.1f}us ours={t_ours * 1e3:.1f}us ({per_dir / t_ours / 1e6:.0f} GB/s per direction)", flush=True)
+            print(f"PERF reduce_scatter {nbytes}B nccl={t_nccl * 1e3:.1f}us pull={t_ours * 1e3:.1f}us ({per_dir / t_ours / 1e6:.0f} GB/s per direction) "
+                  f"nvls={t_nvls * 1e3:.1f}us ({per_dir / t_nvls / 1e6:.0f} GB/s)", flush=True)
             print(f"PERF all_to_all {nbytes}B nccl={t_nccl_a * 1e3:.1f}us ours={t_ours_a * 1e3:.1f}us ({per_dir / t_ours_a / 1e6:.0f} GB/s per direction)", flush=True)
 
     for nbytes in (1 << 20, 1 << 24, 1 << 27):
@@ -201,10 +215,17 @@ def main() -> int:
         yn = torch.empty(W * (nbytes // 2), device=dev, dtype=torch.bfloat16)
         yo = torch.empty(W, nbytes // 2, device=dev, dtype=torch.bfloat16)
         t_nccl = timeit(lambda: dist.all_gather_into_tensor(yn, x))
-        t_ours = timeit(lambda: C.all_gather(x, g, out=yo))
+        t_ours = timeit(lambda: C.all_gather(x, g, out=yo, algo="pull"))
+        line = (f"PERF all_gather {nbytes}B/rank nccl={t_nccl * 1e3:.1f}us pull={t_ours * 1e3:.1f}us "
+                f"({(W - 1) * nbytes / t_ours / 1e6:.0f} GB/s in per rank)")
+        if heap.mc_base and W > 1:
+            t_nvls = timeit(lambda: C.all_gather(x, g, out=yo, algo="nvls"))
+            yh = heap.named(("perf_ag_out", nbytes), (W, nbytes // 2), torch.bfloat16)
+            t_nvls_h = timeit(lambda: C.all_gather(x, g, out=yh.local, algo="nvls"))
+            line += (f" nvls={t_nvls * 1e3:.1f}us ({(W - 1) * nbytes / t_nvls / 1e6:.0f} GB/s) "
+                     f"nvls_into_heap={t_nvls_h * 1e3:.1f}us ({(W - 1) * nbytes / t_nvls_h / 1e6:.0f} GB/s)")
         if r == 0:
-            print(f"PERF all_gather {nbytes}B/rank nccl={t_nccl * 1e3:.1f}us ours={t_ours * 1e3:.1f}us "
-                  f"({(W - 1) * nbytes / t_ours / 1e6:.0f} GB/s in per rank)", flush=True)
+            print(line, flush=True)
 
     # the same comparison with both sides replayed from a CUDA graph (launch overhead of either host path removed),
     # inputs and outputs living in the symmetric heap so that no staging copy is involved
