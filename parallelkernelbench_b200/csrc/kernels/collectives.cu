@@ -637,12 +637,12 @@ coll_allreduce_nvls_kernel(const SymmCtx c, const TwoShotArgs a) {
     else return multimem_ld_reduce_f32x4(symm_mc<uint8_t>(c, a.stage_off) + (i << 4));
   };
   long long i = v0 + tid;
-  for (; i + 3 * nthreads < v1; i += 4 * nthreads) {   // four in-switch reductions in flight per thread
-    const U4 r0 = ldr(i), r1 = ldr(i + nthreads), r2 = ldr(i + 2 * nthreads), r3 = ldr(i + 3 * nthreads);
-    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), r0);
-    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + nthreads) << 4), r1);
-    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + 2 * nthreads) << 4), r2);
-    multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + 3 * nthreads) << 4), r3);
+  for (; i + 7 * nthreads < v1; i += 8 * nthreads) {   // eight in-switch reductions in flight per thread
+    U4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ldr(i + u * nthreads);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + ((i + u * nthreads) << 4), v[u]);
   }
   for (; i < v1; i += nthreads) multimem_st_v4(symm_mc<uint8_t>(c, a.result_off) + (i << 4), ldr(i));
   if (!symm_grid_barrier(c, 203, 2)) return;
@@ -679,13 +679,12 @@ coll_allgather_nvls_kernel(const SymmCtx c, const NvlsAgArgs a) {
   const uint8_t* src = static_cast<const uint8_t*>(a.src);
   uint8_t* dst = symm_mc<uint8_t>(c, a.gather_off) + (long long)c.grank * a.bytes;
   long long i = tid;
-  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {   // four local loads in flight per thread, then four posted stores
-    const U4 v0 = ld_global_nc_v4(src + (i << 4)), v1 = ld_global_nc_v4(src + ((i + nthreads) << 4));
-    const U4 v2 = ld_global_nc_v4(src + ((i + 2 * nthreads) << 4)), v3 = ld_global_nc_v4(src + ((i + 3 * nthreads) << 4));
-    multimem_st_v4(dst + (i << 4), v0);
-    multimem_st_v4(dst + ((i + nthreads) << 4), v1);
-    multimem_st_v4(dst + ((i + 2 * nthreads) << 4), v2);
-    multimem_st_v4(dst + ((i + 3 * nthreads) << 4), v3);
+  for (; i + 7 * nthreads < nvec; i += 8 * nthreads) {   // eight local loads in flight per thread, then eight posted stores
+    U4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ld_global_nc_v4(src + ((i + u * nthreads) << 4));
+#pragma unroll
+    for (int u = 0; u < 8; ++u) multimem_st_v4(dst + ((i + u * nthreads) << 4), v[u]);
   }
   for (; i < nvec; i += nthreads) multimem_st_v4(dst + (i << 4), ld_global_nc_v4(src + (i << 4)));
   // every block of every rank has issued its stores once this barrier passes
@@ -725,12 +724,12 @@ coll_reduce_scatter_nvls_kernel(const SymmCtx c, const NvlsRsArgs a) {
     else return multimem_ld_reduce_f32x4(mc + (i << 4));
   };
   long long i = tid;
-  for (; i + 3 * nthreads < nvec; i += 4 * nthreads) {
-    const U4 r0 = ldr(i), r1 = ldr(i + nthreads), r2 = ldr(i + 2 * nthreads), r3 = ldr(i + 3 * nthreads);
-    st_global_v4(out + (i << 4), r0);
-    st_global_v4(out + ((i + nthreads) << 4), r1);
-    st_global_v4(out + ((i + 2 * nthreads) << 4), r2);
-    st_global_v4(out + ((i + 3 * nthreads) << 4), r3);
+  for (; i + 7 * nthreads < nvec; i += 8 * nthreads) {   // eight in-switch reductions in flight per thread (a round trip through the switch each)
+    U4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) v[u] = ldr(i + u * nthreads);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) st_global_v4(out + ((i + u * nthreads) << 4), v[u]);
   }
   for (; i < nvec; i += nthreads) st_global_v4(out + (i << 4), ldr(i));
   // nobody may overwrite its staged input (the next call) while a peer still reads it through the switch

@@ -16,6 +16,8 @@
 
 namespace pkb {
 
+constexpr float kInv448 = 1.0f / 448.0f;
+
 // ================================================================================================
 // RoPE (rotate-half): x is [tokens, heads, dim]; cos/sin are [tokens, dim] (the two halves of a row
 // of cos/sin normally repeat). out[.., :d/2] = x1*cos1 - x2*sin1 ; out[.., d/2:] = x2*cos2 + x1*sin2
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x,
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     if (t >= nthr) continue;
-    float s = amax / 448.0f;
+    float s = amax * kInv448;   // amax / 448 the way PyTorch evaluates a tensor divided by a Python scalar on the GPU: times the rounded reciprocal
     if (pow2_scales && s > 0.f) s = exp2f(ceilf(log2f(s)));  // power-of-two scale (exact to undo)
     if (s == 0.f) s = 1.0f;
     // the correctly rounded quotient x / s, not x * (1 / s): the quotient decides the e4m3 code at rounding boundaries, and

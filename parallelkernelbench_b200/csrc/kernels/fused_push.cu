@@ -19,6 +19,8 @@
 
 namespace pkb {
 
+constexpr float kInv448 = 1.0f / 448.0f;
+
 __device__ __forceinline__ void multimem_st_f32(void* mc_ptr, float v) {
   asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(mc_ptr), "f"(v) : "memory");
 }
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(256) fp8_quant_allgather_kernel(const QuantAgA
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     if (t >= nthr) continue;
-    float s = amax / 448.0f;
+    float s = amax * kInv448;   // amax / 448 the way PyTorch evaluates a tensor divided by a Python scalar on the GPU: times the rounded reciprocal
     if (s == 0.f) s = 1.0f;
     const float inv = __frcp_rn(s);
     uint32_t o[4];

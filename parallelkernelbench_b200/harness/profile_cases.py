@@ -5,7 +5,7 @@
 Each case allocates a few hundred MB at most (inputs larger than L2 where DRAM figures matter),
 launches the kernel a handful of times and exits, so a capture of one launch ends by itself.
 Cases: gemm_pair, gemm_single, tp_mlp, fa_fwd, fa_fwd_d64, fa_bwd, grouped_gemm, grouped_gemm_fp8, rmsnorm, allreduce,
-fsdp_adamw, moe_exchange, gsplat, delta_scan, llama_step.
+fsdp_adamw, moe_exchange, gsplat, delta_scan, llama_step, llama_step_8l.
 """
 from __future__ import annotations
 
@@ -197,6 +197,24 @@ def case_llama_step(iters):
 
     ctx = init_context()
     cfg = LlamaConfig(layers=1, vocab=16384)
+    model = FSDPLlama(ctx, cfg, impl="ours")
+    g = torch.Generator(device=ctx.device).manual_seed(5)
+    tok = torch.randint(0, cfg.vocab, (cfg.seq,), device=ctx.device, generator=g)
+    tgt = torch.randint(0, cfg.vocab, (cfg.seq,), device=ctx.device, generator=g)
+    for _ in range(iters):
+        model.step(tok, tgt)
+    torch.cuda.synchronize()
+    ctx.finalize()
+
+
+def case_llama_step_8l(iters):
+    """Eight decoder layers at Llama-8B width with the full 128256 vocabulary, sequence 4096: the launch list of a training step
+    with the per-layer work and the vocabulary-sized head in realistic proportion (about 30 GB on the device)."""
+    from ..models.llama import FSDPLlama, LlamaConfig
+    from ..parallel import init_context
+
+    ctx = init_context()
+    cfg = LlamaConfig(layers=8)
     model = FSDPLlama(ctx, cfg, impl="ours")
     g = torch.Generator(device=ctx.device).manual_seed(5)
     tok = torch.randint(0, cfg.vocab, (cfg.seq,), device=ctx.device, generator=g)

@@ -17,6 +17,7 @@ from parallelkernelbench_b200.parallel import init_context  # noqa: E402
 
 
 def main() -> int:
+    os.environ.setdefault("PKB_HEAP_GIB", "4")       # the bandwidth lines keep several 128 MiB x W buffers in the heap
     ctx = init_context()
     heap = ctx.heap()
     g = heap.world_group

@@ -28,10 +28,11 @@ def test_fp8_quant_dequant_round_trip(dtype):
     xb = x.float().view(64, 8, 128)
     s_ref = xb.abs().amax(-1) / 448.0
     s_ref = torch.where(s_ref == 0, torch.ones_like(s_ref), s_ref)
-    torch.testing.assert_close(s, s_ref, rtol=1e-6, atol=0)
+    # scales and payload bytes equal PyTorch's evaluation of the same formula on the GPU bit for bit: the scale is amax times the
+    # rounded reciprocal of 448 (how a tensor divided by a Python scalar is computed there), the quotient is correctly rounded
+    assert torch.equal(s, s_ref)
     y_ref = (xb / s_ref.unsqueeze(-1)).to(torch.float8_e4m3fn).view(64, 1024)
-    assert (y.view(torch.float8_e4m3fn).float() - y_ref.float()).abs().max() <= 32.0   # at most one fp8 ulp at the top
-    assert (y.view(torch.float8_e4m3fn).float() != y_ref.float()).float().mean() < 0.01
+    assert torch.equal(y.view(torch.uint8), y_ref.view(torch.uint8))
     back = fp8_dequantize_1x128(y, s, torch.float32)
     torch.testing.assert_close(back, x.float(), atol=2e-3, rtol=0.07)   # e4m3: 3 mantissa bits, subnormals near zero
     y2, s2 = fp8_quantize_1x128(x, pow2_scales=True)
