@@ -30,6 +30,11 @@ int pkb_coll_gather(const pkb_symm_ctx* h, const void* src, long long stage_byte
                     unsigned long long stage_off, unsigned int src_mask, long long in_base,
                     long long in_member_stride, long long seg_bytes, void* out, long long out_stride,
                     int active, int max_blocks, void* stream);
+// All-to-all of gsize chunks of chunk_bytes as a push with the TMA unit (bulk loads of local memory, bulk stores into the
+// receivers' [gsize, chunk_bytes] buffer at heap offset recv_off). out: local result, or null when the receive buffer itself
+// is the result (it then has to be free on every member when the call starts).
+int pkb_coll_all_to_all_push(const pkb_symm_ctx* h, const void* src, long long chunk_bytes, unsigned long long recv_off,
+                             void* out, int max_blocks, void* stream);
 // Latency-optimised all-reduce (bf16 / fp32, at most cap_units 4-byte words): data and an epoch word travel in one
 // 8-byte store, no barrier. ll_off: header (16 bytes, zero at first use) + 2 * gsize * cap_units * 8 bytes in the heap.
 int pkb_coll_allreduce_ll(const pkb_symm_ctx* h, int dtype, int op, const void* src, long long n, unsigned long long ll_off,

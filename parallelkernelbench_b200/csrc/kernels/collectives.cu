@@ -372,6 +372,65 @@ coll_a2a_perm_kernel(const SymmCtx c, const A2APermArgs a) {
 }
 
 // ================================================================================================
+// all-to-all as a push: every block moves one slice of each outgoing chunk with the TMA unit, local memory -> shared-memory
+// ring -> the receiver's buffer (cp.async.bulk loads of this GPU's memory, cp.async.bulk stores into the peer's). Stores over
+// NVLink are posted, so the sender never waits a round trip, and the input needs no staging copy. The project's example
+// all-to-all is built the same way from TMA loads and TMA stores into the destination device
+// (reference: kernelgen/solutions_new_alltoall_parallelkittens.py:36-122).
+// Slice b of a chunk is written by block b of the sender and copied out by block b of the receiver, so barriers between
+// same-index blocks are enough: one before the first store (the receiver has finished reading its buffer in its previous
+// call) and one after the last.
+// ================================================================================================
+struct A2APushArgs {
+  const void* src;      // [gsize, chunk] local input, any device memory
+  long long chunk;      // bytes per destination (multiple of 16)
+  uint64_t recv_off;    // heap offset of the [gsize, chunk] receive buffer of every member
+  void* out;            // local output; null when the receive buffer is the output
+};
+
+__global__ void __launch_bounds__(kCollThreads)
+coll_a2a_push_kernel(const SymmCtx c, const A2APushArgs a) {
+  extern __shared__ __align__(128) uint8_t bulk_smem[];
+  __shared__ int s_abort;
+  BulkRing ring;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    bulk_ring_init(ring, smem_u32(bulk_smem));
+  }
+  __syncthreads();
+  if (!symm_block_barrier(c, 211, 1)) return;
+  long long per = (a.chunk + gridDim.x - 1) / gridDim.x;
+  per = (per + 1023) & ~1023ll;
+  const long long b0 = per * blockIdx.x;
+  const long long nb = b0 >= a.chunk ? 0 : (b0 + per <= a.chunk ? per : a.chunk - b0);
+  const uint8_t* src = static_cast<const uint8_t*>(a.src);
+  uint8_t* out = static_cast<uint8_t*>(a.out);
+  if (threadIdx.x == 0 && nb > 0) {
+    bool ok = true;
+    for (int k = 0; k < c.gsize && ok; ++k) {
+      const int g = (c.grank + k) % c.gsize;      // every member starts with its own chunk, then a different peer each
+      uint8_t* to = (g == c.grank && out) ? out + (long long)g * a.chunk
+                                          : symm_ptr<uint8_t>(c, c.members[g], a.recv_off) + (long long)c.grank * a.chunk;
+      ok = bulk_copy(ring, to + b0, src + (long long)g * a.chunk + b0, nb, &s_abort, c.budget_ns);
+    }
+    fence_proxy_async_all();                      // the bulk stores are ordered before the release in the barrier
+    if (!ok) record_status(c.status, kStatusMbarTimeout, 211, c.rank, c.rank, 3, 0);
+  }
+  if (!symm_block_barrier(c, 211, 2)) return;
+  if (out && threadIdx.x == 0 && nb > 0) {
+    fence_proxy_async_all();                      // the peers' stores are visible to the bulk loads below
+    const uint8_t* recv = symm_local<uint8_t>(c, a.recv_off);
+    for (int g = 0; g < c.gsize; ++g) {
+      if (g == c.grank) continue;
+      if (!bulk_copy(ring, out + (long long)g * a.chunk + b0, recv + (long long)g * a.chunk + b0, nb, &s_abort, c.budget_ns)) {
+        record_status(c.status, kStatusMbarTimeout, 211, c.rank, c.rank, 4, 0);
+        break;
+      }
+    }
+  }
+}
+
+// ================================================================================================
 // latency-optimised all-reduce for small messages: every 4 bytes of data travel with a 4-byte epoch word in ONE 8-byte
 // store straight into the receiver's slot for this sender, and the receiver polls the words it is about to reduce.
 // There is no barrier at all: the cost is one kernel launch plus one one-way NVLink store. Two slots alternate by the
@@ -903,6 +962,19 @@ int pkb_coll_a2a_permute(const pkb_symm_ctx* h, const void* src, long long stage
   const long long moved = extents[0] * extents[1] * extents[2] * inner_bytes * h->gsize;
   const int grid = grid_for(moved > stage_bytes ? moved : stage_bytes, max_blocks);
   coll_a2a_perm_kernel<<<grid, kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+int pkb_coll_all_to_all_push(const pkb_symm_ctx* h, const void* src, long long chunk_bytes, unsigned long long recv_off,
+                             void* out, int max_blocks, void* stream) {
+  if (int rc = symm_ctx_check(h)) return rc;
+  PKB_CHECK_ARG(chunk_bytes > 0 && (chunk_bytes & 15) == 0, "chunk_bytes must be a positive multiple of 16");
+  PKB_CHECK_ARG((((uintptr_t)src | (uintptr_t)out | recv_off) & 15) == 0, "buffers must be 16-byte aligned");
+  A2APushArgs a{src, chunk_bytes, recv_off, out};
+  // one ring thread per block: blocks beyond the point where each holds a few ring-fulls only add barrier traffic
+  int grid = grid_for(chunk_bytes / 8, max_blocks);
+  launch_with_ring(coll_a2a_push_kernel, grid, static_cast<cudaStream_t>(stream), symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }

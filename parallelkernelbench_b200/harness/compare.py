@@ -17,13 +17,18 @@ from typing import Any
 
 import torch
 
+from ..utils.ragged import Ragged
+
 _RANK_FILE = re.compile(r"^rank_(\d+)\.pt$")
 
 
 def normalize_output(y: Any) -> Any:
-    """Tensor stays a tensor, tuple/list becomes ``{'output_i': ...}``, dicts are walked; all on CPU."""
+    """Tensor stays a tensor, a ``Ragged`` result is cut to its valid length, tuple/list becomes ``{'output_i': ...}``, dicts
+    are walked; all on CPU."""
     if isinstance(y, torch.Tensor):
         return y.detach().to("cpu")
+    if isinstance(y, Ragged):                        # device-side length: trimmed here, outside any timed region
+        return y.trimmed().detach().to("cpu")
     if isinstance(y, (tuple, list)):
         return {f"output_{i}": normalize_output(v) for i, v in enumerate(y)}
     if isinstance(y, dict):

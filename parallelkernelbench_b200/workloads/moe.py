@@ -15,6 +15,7 @@ import torch.distributed as dist
 
 from ..harness.roofline import Cost
 from ..refs.moe import moe_reference
+from ..utils.ragged import Ragged, compact_padded, permute_segments_padded
 from .registry import OpSpec, RunCtx, register
 
 
@@ -80,8 +81,7 @@ def _a2av_ref(rc, x, counts, cap):
 
 def _a2av_ours(rc, x, counts, cap):
     out, _recv, total = rc.comm.all_to_all_v(x.contiguous(), counts, cap)
-    n = int(total.item())                                   # only to trim the result for the comparison
-    return {"rows": out[:n], "count": total.reshape(1).to(torch.int64)}
+    return {"rows": Ragged(out, total), "count": total.reshape(1).to(torch.int64)}    # the length never leaves the device
 
 
 register(OpSpec(name="alltoall_v", problem_ids=(27,), group="moe", configs={"default": {"rows": 1024, "cols": 1024}, "small": {"rows": 64, "cols": 8}},

@@ -15,6 +15,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from ..harness.roofline import Cost
+from ..utils.ragged import Ragged, compact_padded, permute_segments_padded
 from .registry import OpSpec, RunCtx, register
 
 
@@ -62,10 +63,10 @@ register(OpSpec(name="ulysses_all_to_all", problem_ids=(33,), group="ulysses",
 # ---- 35: variable-size all-gather -----------------------------------------------------------------
 def _p35_inputs(rc: RunCtx, cfg):
     rows = cfg["m"] - (rc.rank * cfg.get("shrink", 0))          # ranks may hold different numbers of rows
-    return (rc.randn(max(rows, 1), cfg["n"]), 0)
+    return (rc.randn(max(rows, 1), cfg["n"]), 0, cfg["m"])      # the last entry: an upper bound of the rows of any rank
 
 
-def _p35_ref(rc, x, gather_dim):
+def _p35_ref(rc, x, gather_dim, cap=None):
     W = rc.world
     if W == 1:
         return x.contiguous()
@@ -83,25 +84,20 @@ def _p35_ref(rc, x, gather_dim):
     return torch.cat(parts, dim=gather_dim).contiguous()
 
 
-def _p35_ours(rc, x, gather_dim):
-    """The row counts travel as device data next to the payload (padded to a common capacity given by the config),
-    so no size exchange has to come back to the host before the payload moves."""
+def _p35_ours(rc, x, gather_dim, cap):
+    """The row counts travel as device data next to the payload (padded to the capacity ``cap`` that the configuration
+    gives), and the valid rows are brought together by a gather through computed indices, so no size comes back to the host:
+    the result is a ``Ragged`` buffer whose length stays on the device."""
     W = rc.world
     if W == 1:
         return x.contiguous()
     xm = x.movedim(gather_dim, 0).contiguous()
-    cap = rc.cache.get("agv_cap")
-    if cap is None:
-        capt = rc.comm.all_reduce(torch.tensor([xm.shape[0]], dtype=torch.int64, device=x.device), op="max")
-        cap = rc.cache["agv_cap"] = int(capt.item())            # once per job; later calls reuse it
-    padded = torch.zeros((cap + 1, *xm.shape[1:]), dtype=x.dtype, device=x.device)
+    padded = torch.zeros((cap, *xm.shape[1:]), dtype=x.dtype, device=x.device)
     padded[:xm.shape[0]] = xm
-    hdr = torch.tensor([xm.shape[0]], dtype=torch.int64, device=x.device)
+    hdr = torch.tensor([xm.shape[0]], dtype=torch.int64, device=x.device)      # host-known shape -> device, no read-back
     counts = rc.comm.all_gather(hdr).view(-1)
-    allp = rc.comm.all_gather(padded)[:, :cap]
-    keep = (torch.arange(cap, device=x.device)[None, :] < counts[:, None]).reshape(-1)
-    out = allp.reshape(W * cap, *xm.shape[1:])[keep]
-    return out.movedim(0, gather_dim).contiguous()
+    rows, total = compact_padded(rc.comm.all_gather(padded), counts)
+    return Ragged(rows.movedim(0, gather_dim), total, dim=gather_dim)
 
 
 register(OpSpec(name="ulysses_all_gather_variable", problem_ids=(35,), group="ulysses",

@@ -15,6 +15,7 @@ import torch.distributed as dist
 import torch.nn.functional as F
 
 from ..harness.roofline import Cost
+from ..utils.ragged import Ragged, compact_padded, permute_segments_padded
 from .registry import OpSpec, RunCtx, register
 from .ulysses import _a2a_ref
 
@@ -664,9 +665,9 @@ def _se_ours(rc, idx, value):
     packed = torch.cat([idx[perm].view(-1, 1).view(torch.uint8).view(idx.numel(), 8), vb], 1).contiguous()
     cap = idx.numel() * W
     out, _recv, total = rc.comm.all_to_all_v(packed, counts, cap)
-    n = int(total.item())                                                  # only to trim the result for the comparison
-    out = out[:n]
-    return {"idx": out[:, :8].contiguous().view(torch.int64).view(-1), "value": out[:, 8:].contiguous().view(value.dtype).view(n, -1)}
+    # the number of received rows stays on the device: both results are capacity buffers with a device-side length
+    return {"idx": Ragged(out[:, :8].contiguous().view(torch.int64).view(-1), total),
+            "value": Ragged(out[:, 8:].contiguous().view(value.dtype).view(cap, -1), total)}
 
 
 register(OpSpec(name="gnn_sparse_embedding_route", problem_ids=(67,), group="wild",
@@ -719,10 +720,10 @@ register(OpSpec(name="gnn_sparse_feature_fetch_projection", problem_ids=(68,), g
 # ---- 69: rank of the positive among gathered negatives -----------------------------------------------
 def _ns_inputs(rc: RunCtx, cfg):
     n = cfg["pos"] + rc.rank % 3
-    return (rc.randn(n), rc.randn(n, cfg["neg"], salt=1))
+    return (rc.randn(n), rc.randn(n, cfg["neg"], salt=1), cfg["pos"] + 2)      # last: an upper bound of the rows of any rank
 
 
-def _ns_ref(rc, pos, neg):
+def _ns_ref(rc, pos, neg, cap=None):
     W = rc.world
     if W > 1:
         sizes = torch.zeros(W, dtype=torch.int64, device=pos.device)
@@ -741,22 +742,20 @@ def _ns_ref(rc, pos, neg):
     return torch.nonzero(order == 0)[:, 1] + 1
 
 
-def _ns_ours(rc, pos, neg):
+def _ns_ours(rc, pos, neg, cap):
     """Rank = 1 + number of negatives that beat the positive: counted where the rows live, only the ranks (8 bytes per
-    row instead of the whole score matrix) are gathered, with the row counts carried on the device."""
+    row instead of the whole score matrix) are gathered, with the row counts carried on the device; the result is a
+    capacity buffer with a device-side length."""
     W = rc.world
     local = 1 + (torch.sigmoid(neg.float()) > torch.sigmoid(pos.float()).view(-1, 1)).sum(1)
     if W == 1:
         return local
-    cap = rc.cache.get("ns_cap")
-    if cap is None:
-        cap = rc.cache["ns_cap"] = int(rc.comm.all_reduce(torch.tensor([pos.shape[0]], dtype=torch.int64, device=pos.device), op="max").item())
     padded = torch.zeros(cap + 1, dtype=torch.int64, device=pos.device)
     padded[:local.numel()] = local
     padded[cap] = local.numel()
     allr = rc.comm.all_gather(padded)                                      # [W, cap + 1]
-    keep = torch.arange(cap, device=pos.device)[None, :] < allr[:, cap:cap + 1]
-    return allr[:, :cap][keep]
+    rows, total = compact_padded(allr[:, :cap], allr[:, cap])
+    return Ragged(rows, total)
 
 
 register(OpSpec(name="gnn_negative_scoring", problem_ids=(69,), group="wild",
@@ -792,15 +791,15 @@ def _kjt(rc, lengths, values, key_splits, B, ours):
     ks = torch.tensor(key_splits, device=dev)
     len_counts = ks * B                                                    # lengths sent to each destination
     feat_sum = lengths.view(-1, B).sum(1)                                  # values per feature
-    bounds = torch.cumsum(ks, 0)
-    val_counts = torch.stack([feat_sum[int(b - k):int(b)].sum() for b, k in zip(bounds.tolist(), key_splits)])
+    ends = [sum(key_splits[:d + 1]) for d in range(W)]                     # host integers: the key split is a Python list
+    val_counts = torch.stack([feat_sum[e - k:e].sum() for e, k in zip(ends, key_splits)])
     if W > 1:
         if ours:
             # capacities are upper bounds that every rank computes alike (lengths are at most 20 per entry)
             ksm, nf = max(key_splits), sum(key_splits)
             rl, _, tl = rc.comm.all_to_all_v(lengths.view(-1, 1).contiguous(), len_counts, ksm * B * W, max_send_rows=nf * B)
             rv, _, tv = rc.comm.all_to_all_v(values.view(-1, 1).contiguous(), val_counts, 20 * ksm * B * W, max_send_rows=20 * nf * B)
-            rl, rv = rl.view(-1)[:key_splits[r] * B * W], rv.view(-1)[:int(tv.item())]
+            rl, rv = rl.view(-1)[:key_splits[r] * B * W], rv.view(-1)             # rv: capacity buffer, tv values valid
         else:
             rl, _ = _a2av_ref(lengths, len_counts)
             rv, _ = _a2av_ref(values, val_counts)
@@ -810,7 +809,8 @@ def _kjt(rc, lengths, values, key_splits, B, ours):
     # received order is (source rank, feature); the consumer wants (feature, source rank)
     recat = torch.tensor([f + s * local for f in range(local) for s in range(W)], device=dev)
     l2 = rl.view(W * local, B)
-    return {"lengths": l2[recat].reshape(-1), "values": _segment_permute(rv, l2.sum(1), recat),
+    values_out = permute_segments_padded(rv, l2.sum(1), recat) if (ours and W > 1) else _segment_permute(rv, l2.sum(1), recat)
+    return {"lengths": l2[recat].reshape(-1), "values": values_out,
             "stride": torch.tensor(B * W, device=dev)}
 
 
@@ -1501,7 +1501,7 @@ def _sort_inputs(rc: RunCtx, cfg):
     if rc.trial % 4 == 3 and rc.rank % 2 == 1:
         n = 0
     vals = rc.randint(-50, 50, (n,)).to(rc.dtype) - rc.rank * max(1, n)
-    return (vals,)
+    return (vals, max(cfg["n_local"], 1) * rc.world)               # last: an upper bound of the global element count
 
 
 def _target_counts(sizes: torch.Tensor, r: int, W: int) -> torch.Tensor:
@@ -1516,7 +1516,7 @@ def _target_counts(sizes: torch.Tensor, r: int, W: int) -> torch.Tensor:
     return (torch.minimum(t_end, my_end) - torch.maximum(t_start, my_start)).clamp(min=0)
 
 
-def _sample_sort(rc, x, ours):
+def _sample_sort(rc, x, cap, ours):
     W, r = rc.world, rc.rank
     s = x.float().sort().values
     if W == 1:
@@ -1540,21 +1540,23 @@ def _sample_sort(rc, x, ours):
     split = alls[sidx]
     bounds = torch.searchsorted(s, split, right=True)
     counts = torch.diff(torch.cat([torch.zeros(1, dtype=torch.long, device=dev), bounds, torch.tensor([n], device=dev)]))
-    cap = rc.cache.get("sort_cap")
-    if cap is None:
-        tot = rc.comm.all_reduce(torch.tensor([n], dtype=torch.int64, device=dev)) if ours else _allreduce_ref(torch.tensor([n], dtype=torch.int64, device=dev))
-        cap = rc.cache["sort_cap"] = max(int(tot.item()), 1)
     got, total = a2av(s, counts, cap)
-    m = (got[:int(total.item())] if total is not None else got).sort().values
-    sizes = gather1(torch.tensor([m.numel()], dtype=torch.int64, device=dev)).reshape(-1)
-    out, total = a2av(m, _target_counts(sizes, r, W), cap)
-    out = out[:int(total.item())] if total is not None else out
-    return out.to(x.dtype)
+    if not ours:
+        m = got.sort().values
+        sizes = gather1(torch.tensor([m.numel()], dtype=torch.int64, device=dev)).reshape(-1)
+        out, _ = a2av(m, _target_counts(sizes, r, W), cap)
+        return out.to(x.dtype)
+    # ours: the received count never comes back to the host. The capacity buffer is sorted whole with +inf behind the
+    # valid part, and the second exchange sends the first ``total`` rows of it (its send counts add up to ``total``).
+    m = torch.where(torch.arange(cap, device=dev) < total, got, torch.full_like(got, float("inf"))).sort().values
+    sizes = gather1(total.reshape(1).to(torch.int64)).reshape(-1)
+    out, _, total2 = rc.comm.all_to_all_v(m.view(-1, 1).contiguous(), _target_counts(sizes, r, W), cap)
+    return Ragged(out.view(-1).to(x.dtype), total2)
 
 
 register(OpSpec(name="distributed_sample_sort", problem_ids=(85,), group="wild",
                 configs={"default": {"n_local": 128}, "small": {"n_local": 16}, "large": {"n_local": 1 << 20}},
-                make_inputs=_sort_inputs, reference=lambda rc, x: _sample_sort(rc, x, False), ours=lambda rc, x: _sample_sort(rc, x, True),
+                make_inputs=_sort_inputs, reference=lambda rc, x, cap: _sample_sort(rc, x, cap, False), ours=lambda rc, x, cap: _sample_sort(rc, x, cap, True),
                 atol=0, rtol=0))
 
 
