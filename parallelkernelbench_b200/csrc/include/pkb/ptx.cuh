@@ -101,6 +101,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same test with a suspend-time hint: the thread may sleep in hardware for up to `hint_ns` and is woken as soon as the
+// phase completes, so a waiting warp polls (and takes issue slots from the warps that compute) far less often.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Default budget of a device-side wait. Generous for production kernels (a healthy wait is
 // microseconds); tests that exercise the time-out path pass a few milliseconds instead.
 constexpr uint64_t kDefaultWaitBudgetNs = 4000000000ull;
@@ -113,15 +129,17 @@ __device__ __forceinline__ long long budget_cycles(uint64_t budget_ns) {
   return static_cast<long long>(budget_ns) * 2;
 }
 
+constexpr uint32_t kMbarSuspendHintNs = 4000;
+
 // Bounded mbarrier wait. `abort_flag` lives in shared memory and is shared by all roles of the
-// CTA: the first role whose budget expires raises it, every other wait sees it within ~1k polls.
+// CTA: the first role whose budget expires raises it, every other wait sees it within 64 polls (a poll sleeps up to kMbarSuspendHintNs).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           uint64_t budget_ns = kDefaultWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ffu) == 0u) {
+  while (!mbar_try_wait_hint(bar, parity, kMbarSuspendHintNs)) {
+    if ((++spins & 0x3fu) == 0u) {
       if (*abort_flag) return false;
       const long long now = clock64();
       if (t0 == 0) {

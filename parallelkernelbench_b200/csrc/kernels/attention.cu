@@ -997,7 +997,9 @@ static_assert(128 * kFa3RegsIo + 256 * kFa3RegsSoftmax + 128 * kFa3RegsCorr <= 6
 
 // OPT bit 0: three-input maxima and packed fp32 pairs for scale / subtract and the row sum; bit 1: every fourth pair of
 // exponentials of an unmasked tile on the FMA pipe (polynomial) instead of the special-function unit.
-template <int D, int OPT>
+// TRACE: CTA (0,0,0) records clock64 at the hand-over points of every role (see fa_trace) - a separate instantiation, so the
+// production kernel carries none of it.
+template <int D, int OPT, bool TRACE = false>
 __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                             const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
                                             const int head, const int batch) {
@@ -1153,6 +1155,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           if (!ok) return;
           const int st = j % kStages;
           if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace(p, 0, 0, j);
           if (j == 0) {
             if (need0(kp)) issue_s(0, st);
             if (has1) issue_s(1, st);
@@ -1161,11 +1164,16 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
             return;
           }
           if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace(p, 0, 1, j);
           if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace(p, 0, 2, j);
           if (need0(kp)) issue_s(0, st);
+          if constexpr (TRACE) fa_trace(p, 0, 3, j);
           if (has1) {
             if (!issue_pv(1, prev_st)) { ok = false; return; }
+            if constexpr (TRACE) fa_trace(p, 0, 4, j);
             issue_s(1, st);
+            if constexpr (TRACE) fa_trace(p, 0, 5, j);
           }
           umma_commit(v_empty(prev_st));
           umma_commit(k_empty(st));
@@ -1201,6 +1209,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 0, cnt); }
         tc_fence_after_sync();
         // the whole row of scores in registers: four reads in flight, one wait
         uint32_t r[128];
@@ -1215,6 +1224,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           tmem_ld_32x32(s_row + 96, r3);
           tmem_ld_wait();
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 1, cnt); }
         const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
         if (need_mask) {
 #pragma unroll
@@ -1241,12 +1251,14 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         const bool dead = m_new == -INFINITY;
         const float alpha = (dead || m_new == m_run) ? 1.f : fast_exp2(m_run - m_new);
         const float neg_m = dead ? 0.f : -m_new;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 2, cnt); }
         ok = mbar_wait(a_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
         alpha_s[t * kFaTile + row] = alpha;
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(t));
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 3, cnt); }
         // exponentials in place, then packed to bf16 pairs in the first 64 registers
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t w[64];
@@ -1288,6 +1300,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
 #pragma unroll
           for (int i = 0; i < 64; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 4, cnt); }
         {
           const uint32_t (&w0)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[0]);
           const uint32_t (&w1)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[32]);
@@ -1298,6 +1311,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(t));
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 5, cnt); }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;
         ++cnt;
@@ -1356,6 +1370,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           ok = mbar_wait(a_full(t), ph, abort_flag, p.budget_ns);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 3, 2 * t, cnt[t]); }
           const float alpha = alpha_s[t * kFaTile + row];
           __syncwarp();
           if (lane == 0) mbar_arrive(a_empty(t));
@@ -1381,6 +1396,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(o_scaled(t));
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 3, 2 * t + 1, cnt[t]); }
           ++cnt[t];
         }
       });
@@ -1401,11 +1417,11 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
   }
 }
 
-template <int D, int OPT>
+template <int D, int OPT, bool TRACE = false>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd3_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
-  fa_fwd3_cta<D, OPT>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+  fa_fwd3_cta<D, OPT, TRACE>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // ================================================================================================
@@ -1997,6 +2013,12 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
       PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
       kern<<<grid, kFa4Threads, smem, stream>>>(tq, tk, tv, p);
     }
+  } else if (fa_use_pairs(d) && p.trace != nullptr && fa_use_v3()) {
+    constexpr int smem = Fa3Smem<D>::kTotal;
+    dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
+    auto kern = fa_fwd3_kernel<D, kFa3DefaultOpt, true>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kFaThreads, smem, stream>>>(tq, tk, tv, p);
   } else if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v3()) {
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);

@@ -133,6 +133,41 @@ def case_fa_fwd_4k(t):
     return _fa_fwd(t, 4096, "fa_fwd_4k")
 
 
+def case_fa_trace(t: _Timer) -> dict:
+    """Device-side timeline of the attention forward's longest CTA: the roles stamp ``clock64`` at every hand-over, and the
+    medians of the intervals between consecutive stamps (over the unmasked KV tiles) say which hand-over the chain waits on.
+    Roles: 0 MMA issuer, 1 / 2 softmax of Q tile 0 / 1 (first warp), 3 correction. Cycles of the SM clock."""
+    from ..ops.attention import flash_attn_fwd
+
+    q, k, v, _ = _attn_inputs(16384)
+    flash_attn_fwd(q, k, v, causal=True)
+    trace = torch.zeros(4 + 4 * 8192, dtype=torch.int64, device="cuda")
+    flash_attn_fwd(q, k, v, causal=True, trace=trace)
+    torch.cuda.synchronize()
+    n = min(int(trace[0]), 8192)
+    rec = trace[4:4 + 4 * n].view(n, 4).cpu().tolist()
+    by_role: dict[int, dict[int, dict[int, int]]] = {}
+    for role, ev, tile, clk in rec:
+        by_role.setdefault(role, {}).setdefault(tile, {})[ev] = clk
+    out: dict = {"case": "fa_trace", "records": n}
+    for role, tiles in sorted(by_role.items()):
+        idx = sorted(tiles)
+        steady = [i for i in idx if 8 <= i < 100 and i + 1 in tiles]
+        evs = sorted({e for i in steady for e in tiles[i]})
+        med = lambda xs: sorted(xs)[len(xs) // 2] if xs else None  # noqa: E731
+        row = {"period": med([tiles[i + 1][evs[0]] - tiles[i][evs[0]] for i in steady if evs and evs[0] in tiles[i] and evs[0] in tiles[i + 1]])}
+        for a, b in zip(evs, evs[1:]):
+            row[f"e{a}->e{b}"] = med([tiles[i][b] - tiles[i][a] for i in steady if a in tiles[i] and b in tiles[i]])
+        if evs:
+            row[f"e{evs[-1]}->next e{evs[0]}"] = med([tiles[i + 1][evs[0]] - tiles[i][evs[-1]] for i in steady if evs[-1] in tiles[i] and evs[0] in tiles[i + 1]])
+        out[f"role{role}"] = row
+    # offset between the two softmax roles at the same tile index (are the Q tiles half a period apart?)
+    if 1 in by_role and 2 in by_role:
+        offs = [by_role[2][i][0] - by_role[1][i][0] for i in by_role[1] if 8 <= i < 100 and i in by_role[2] and 0 in by_role[1][i] and 0 in by_role[2][i]]
+        out["softmax1_minus_softmax0_at_s_ready"] = sorted(offs)[len(offs) // 2] if offs else None
+    return out
+
+
 def case_fa_bwd(t: _Timer) -> dict:
     import torch.nn.functional as F
 

@@ -228,8 +228,11 @@ def all_gather(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = Non
     return out
 
 
-def all_to_all(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None) -> torch.Tensor:
-    """``x`` is ``[W, ...]``; ``out[g] = x_of_member_g[my index]``."""
+def all_to_all(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = None, algo: str = "auto") -> torch.Tensor:
+    """``x`` is ``[W, ...]``; ``out[g] = x_of_member_g[my index]``. ``algo``: ``"pull"`` (stage the input in the heap, receivers
+    read their chunks from the peers), ``"push"`` (TMA bulk loads of the local input, TMA bulk stores into the receivers'
+    buffers; no staging copy, and no copy out when ``out`` lives in the symmetric heap at the same offset on every member) or
+    ``"auto"`` (push for chunks of ``tuning.all_to_all_push_min`` bytes and more)."""
     x = _check(x)
     W = group.size
     if x.shape[0] != W:
@@ -237,6 +240,21 @@ def all_to_all(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = Non
     if out is None:
         out = torch.empty_like(x)
     chunk = x[0].numel() * x.element_size()
+    push_fit = W > 1 and chunk % 16 == 0 and x.data_ptr() % 16 == 0 and out.is_contiguous() and out.data_ptr() % 16 == 0
+    if algo == "push" and not push_fit:
+        raise RuntimeError("the push all-to-all needs more than one member and 16-byte aligned chunks")
+    goff = group.heap.contains(out) if push_fit else None
+    direct = goff is not None and goff % 16 == 0              # the senders store straight into the caller's result
+    # with a result outside the heap the push pays a local copy out of the receive buffer, so it takes over later
+    push_min = tuning.all_to_all_push_min(W, direct=direct)
+    if algo == "push" or (algo == "auto" and push_fit and chunk >= push_min):
+        if not direct:
+            cap = 1 << max(12, (W * chunk - 1).bit_length())
+            goff = group.heap.named(("a2a_push", group.channel), (cap,), torch.uint8).offset
+        nv.check(_lib().pkb_coll_all_to_all_push(group.ref, nv.ptr(x), nv.c_ll(chunk), ctypes.c_ulonglong(goff),
+                                                 nv.ptr(None if direct else out), 0, nv.current_stream()), "pkb_coll_all_to_all_push")
+        nv.count_launch()
+        return out
     _gather_call(group, x, (1 << W) - 1, 0, chunk, chunk, out, chunk, True, "a2a_in")
     return out
 

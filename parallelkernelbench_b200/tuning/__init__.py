@@ -63,6 +63,14 @@ def reduce_scatter_nvls_min(world: int, table: dict | None = None) -> int:
     return int(_row("reduce_scatter", world, table).get("nvls_min_bytes", _NVLS_OFF))
 
 
+def all_to_all_push_min(world: int, table: dict | None = None, direct: bool = False) -> int:
+    """Chunk size in bytes (per destination) from which the all-to-all pushes with TMA bulk stores into the receivers instead of
+    staging its input and letting the receivers pull: ``push_min_bytes`` of the table's ``all_to_all`` row, or
+    ``push_direct_min_bytes`` when the result lives in the symmetric heap and needs no copy out (absent = never)."""
+    row = _row("all_to_all", world, table)
+    return int(row.get("push_direct_min_bytes" if direct else "push_min_bytes", _NVLS_OFF))
+
+
 def thresholds_from_timings(timings: dict[str, dict[int, float]]) -> dict:
     """One table row from measured times: ``timings[algo][nbytes] = microseconds``.
 

@@ -90,6 +90,21 @@ def main() -> int:
     ref = torch.empty_like(x)
     dist.all_to_all_single(ref, x)
     report("all_to_all", torch.equal(C.all_to_all(x, g), ref))
+    if W > 1:
+        # push form (TMA bulk stores into the receivers): odd chunk sizes, a chunk smaller than one ring stage, a result
+        # that lives in the symmetric heap (no copy out), and back-to-back calls that reuse the receive buffer
+        for n_el in (8, 1000, 40 * 1024 + 8, (1 << 20) + 24):
+            x = torch.randn(W, n_el, device=dev, dtype=torch.bfloat16, generator=gen)
+            ref = torch.empty_like(x)
+            dist.all_to_all_single(ref, x)
+            ok = torch.equal(C.all_to_all(x, g, algo="push"), ref)
+            yh = heap.named(("a2a_push_out", n_el), (W, n_el), torch.bfloat16)
+            C.all_to_all(x, g, out=yh.local, algo="push")
+            ok &= torch.equal(yh.local, ref)
+            x2 = x + 1
+            dist.all_to_all_single(ref, x2)
+            ok &= torch.equal(C.all_to_all(x2, g, algo="push"), ref)
+            report(f"all_to_all push {n_el} elements per chunk", ok)
     # broadcast / scatter / gather / reduce
     x = torch.randn(3000, device=dev, generator=gen)
     ref = x.clone(); dist.broadcast(ref, src=W - 1)
@@ -204,12 +219,18 @@ def main() -> int:
         t_nvls = timeit(lambda: C.reduce_scatter(x.view(W * (x.shape[1] // 8), 8), g, algo="nvls")) if heap.mc_base and W > 1 else float("nan")
         ya = torch.empty_like(x)
         t_nccl_a = timeit(lambda: dist.all_to_all_single(ya.view(-1), x.view(-1)))
-        t_ours_a = timeit(lambda: C.all_to_all(x, g, out=ya))
+        t_ours_a = timeit(lambda: C.all_to_all(x, g, out=ya, algo="pull"))
+        t_push_a = t_push_h = float("nan")
+        if W > 1:
+            t_push_a = timeit(lambda: C.all_to_all(x, g, out=ya, algo="push"))
+            yah = heap.named(("perf_a2a_out", nbytes), tuple(x.shape), torch.bfloat16)
+            t_push_h = timeit(lambda: C.all_to_all(x, g, out=yah.local, algo="push"))
         if r == 0:
             per_dir = (W - 1) / W * nbytes
             print(f"PERF reduce_scatter {nbytes}B nccl={t_nccl * 1e3:.1f}us pull={t_ours * 1e3:.1f}us ({per_dir / t_ours / 1e6:.0f} GB/s per direction) "
                   f"nvls={t_nvls * 1e3:.1f}us ({per_dir / t_nvls / 1e6:.0f} GB/s)", flush=True)
-            print(f"PERF all_to_all {nbytes}B nccl={t_nccl_a * 1e3:.1f}us ours={t_ours_a * 1e3:.1f}us ({per_dir / t_ours_a / 1e6:.0f} GB/s per direction)", flush=True)
+            print(f"PERF all_to_all {nbytes}B nccl={t_nccl_a * 1e3:.1f}us pull={t_ours_a * 1e3:.1f}us ({per_dir / t_ours_a / 1e6:.0f} GB/s per direction) "
+                  f"push={t_push_a * 1e3:.1f}us ({per_dir / t_push_a / 1e6:.0f} GB/s) push_into_heap={t_push_h * 1e3:.1f}us ({per_dir / t_push_h / 1e6:.0f} GB/s)", flush=True)
 
     for nbytes in (1 << 20, 1 << 24, 1 << 27):
         x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
