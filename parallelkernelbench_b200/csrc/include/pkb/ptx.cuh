@@ -245,6 +245,46 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Predicated forms for an issuing WARP: all 32 lanes walk the issue loop together and `lead` (non-zero in one lane, see
+// elect_one) selects the lane whose instruction takes effect. With the loop wrapped in `if (lane == 0)` instead, the code
+// runs under a divergent branch, the compiler cannot keep descriptors and addresses in uniform registers, and every
+// tcgen05 instruction is preceded by register-to-uniform-register moves whose latency, not the tensor pipe, then sets the
+// pace of a kernel that issues a product every 64 cycles.
+__device__ __forceinline__ void umma_f16_ss_p(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_ts_p(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(lead)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_p(uint32_t bar, uint32_t lead) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(bar), "r"(lead)
+      : "memory");
+}
 // fp8 (e4m3/e5m2) operands, fp32 accumulate.
 __device__ __forceinline__ void umma_f8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                            uint32_t idesc, uint32_t accumulate) {
@@ -366,6 +406,22 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128_mnmajor(uint32_t smem_a
   d |= static_cast<uint64_t>(1024u >> 4) << 32;                            // stride byte offset
   d |= static_cast<uint64_t>(1) << 46;
   d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// The two words of the 128-byte-swizzle descriptors above, for issue loops that must stay short: the high word is a constant,
+// and stepping the start address by `bytes` adds bytes >> 4 to the low word (the address field holds (addr & 0x3FFFF) >> 4 and
+// cannot carry into the next field while the operand stays inside the 256 KiB window). One thread issues every product of a
+// CTA; if it rebuilds a descriptor from the address for each product its own instruction latency, not the tensor pipe, sets
+// the pace (measured: 115 cycles per 128 x 128 x 16 product against 65 with the words prepared).
+constexpr uint32_t kSmemDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t smem_desc_lo_kmajor(uint32_t smem_addr) { return (smem_addr & 0x3FFFFu) >> 4; }
+__device__ __forceinline__ uint32_t smem_desc_lo_mnmajor(uint32_t smem_addr, uint32_t atom_stride_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((atom_stride_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t smem_desc_join(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kSmemDescHiSw128));
   return d;
 }
 
@@ -519,6 +575,12 @@ __device__ __forceinline__ void multimem_red_add_u32(uint32_t* mc_ptr, uint32_t 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+// The same packing for non-negative finite inputs on the integer pipe: add half an ulp of bf16 to each word and take the upper
+// halves with one byte permute (round to nearest, ties away from zero). cvt.rn.bf16x2.f32 executes on the special-function
+// pipe, which a softmax already saturates with its exponentials; this form leaves that pipe to them.
+__device__ __forceinline__ uint32_t pack_bf16x2_alu(float lo, float hi) {
+  return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
 }
 __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
   __nv_bfloat162 v = *reinterpret_cast<__nv_bfloat162*>(&u);

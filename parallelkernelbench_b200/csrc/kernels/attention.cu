@@ -62,6 +62,17 @@ __device__ __forceinline__ void fa_trace(const FaParams& p, int role, int event,
   }
 }
 
+// Trace of the P-in-TMEM kernel: a plain store into the slot of (role, tile, event) - no atomic, nothing to wait for, so the
+// stamps do not stretch the chain they measure. Layout after the four header words: [4 roles][kFaTraceTiles][8 events].
+constexpr int kFaTraceTiles = 160;
+__device__ __forceinline__ void fa_trace_slot(const FaParams& p, int role, int event, int tile) {
+  if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0 || tile >= kFaTraceTiles) return;
+  if (p.trace_capacity * 4 < 4 * kFaTraceTiles * 8) return;
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  p.trace[4 + (role * kFaTraceTiles + tile) * 8 + event] = t;
+}
+
 template <int D>
 struct FaSmem {
   static constexpr int kTileBytes = kFaTile * D * 2;       // Q, K, V tile
@@ -981,8 +992,8 @@ struct Fa3Smem {
   static constexpr int kQ = 0;                               // two tiles
   static constexpr int kK = kQ + 2 * kTileBytes;             // kStages tiles
   static constexpr int kV = kK + kStages * kTileBytes;       // kStages tiles
-  static constexpr int kAlpha = kV + kStages * kTileBytes;   // [2][128] fp32
-  static constexpr int kBars = kAlpha + 2 * kFaTile * 4;
+  static constexpr int kAlpha = kV + kStages * kTileBytes;   // [2 tiles][2 step parities][128] fp32
+  static constexpr int kBars = kAlpha + 2 * 2 * kFaTile * 4;
   static constexpr int kTotal = kBars + 512;
 };
 
@@ -996,7 +1007,10 @@ constexpr int kFa3RegsIo = 80, kFa3RegsSoftmax = 168, kFa3RegsCorr = 80;
 static_assert(128 * kFa3RegsIo + 256 * kFa3RegsSoftmax + 128 * kFa3RegsCorr <= 65536, "register budgets exceed the register file");
 
 // OPT bit 0: three-input maxima and packed fp32 pairs for scale / subtract and the row sum; bit 1: every fourth pair of
-// exponentials of an unmasked tile on the FMA pipe (polynomial) instead of the special-function unit.
+// exponentials of an unmasked tile on the FMA pipe (polynomial) instead of the special-function unit; bit 2: P packed to
+// bf16 on the integer pipe (pack_bf16x2_alu) - the conversion instruction shares the special-function pipe with the
+// exponentials, and the trace of a softmax step showed that pipe saturated: (128 ex2 + 64 conversions) x 8 cycles = the
+// 1540 cycles the exponential loop took.
 // TRACE: CTA (0,0,0) records clock64 at the hand-over points of every role (see fa_trace) - a separate instantiation, so the
 // production kernel carries none of it.
 template <int D, int OPT, bool TRACE = false>
@@ -1018,9 +1032,8 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
   auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
   auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
   auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
-  auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
+  auto p_full = [&](int t, int half) { return bar0 + 8u * (11 + t + 4 * half); };   // 11, 12 first half; 15, 16 second half
   auto a_full = [&](int t) { return bar0 + 8u * (13 + t); };
-  auto a_empty = [&](int t) { return bar0 + 8u * (15 + t); };
   auto o_scaled = [&](int t) { return bar0 + 8u * (17 + t); };
   auto pv_done = [&](int t) { return bar0 + 8u * (19 + t); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 22);
@@ -1054,8 +1067,8 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), 4);
-      mbar_init(a_full(t), 4); mbar_init(a_empty(t), 4);
+      mbar_init(p_full(t, 0), 4); mbar_init(p_full(t, 1), 4);
+      mbar_init(a_full(t), 4);
       mbar_init(o_scaled(t), 4); mbar_init(pv_done(t), 1);
     }
     fence_mbar_init();
@@ -1121,32 +1134,46 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
       __syncwarp();
     } else if (warp == 1) {
       // ------------------------------ MMA issuer ------------------------------
-      if (lane == 0) {
+      // The whole warp walks the loop and waits on the barriers; one elected lane's tcgen05 instructions take effect
+      // (see umma_f16_ss_p): addresses and descriptors then live in uniform registers.
+      {
+        const uint32_t lead = elect_one() ? 1u : 0u;
         constexpr uint32_t idesc_s = make_idesc(kFaTile, kFaTile, 1, 1, 0, 0);
         constexpr uint32_t idesc_o = make_idesc(kFaTile, D, 1, 1, 0, 1);
         bool ok = mbar_wait(q_full, 0, abort_flag, p.budget_ns);
         int pv[2] = {0, 0};         // P V products issued per tile
+        const uint32_t q_lo0 = smem_desc_lo_kmajor(sb + S::kQ);
+        const uint32_t k_lo0 = smem_desc_lo_kmajor(sb + S::kK);
+        const uint32_t v_lo0 = smem_desc_lo_mnmajor(sb + S::kV, kAtomBytes);
+        const uint32_t tmem_s0 = tmem_base, tmem_o0 = tmem_base + 256;
         auto issue_s = [&](int t, int st) {
           tc_fence_after_sync();
+          const uint32_t ql = q_lo0 + t * (S::kTileBytes >> 4), kl = k_lo0 + st * (S::kTileBytes >> 4), ds = tmem_s0 + t * 128;
 #pragma unroll
           for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-            umma_f16_ss(tmem_s(t), make_smem_desc_sw128_kmajor(sb + S::kQ + t * S::kTileBytes + off),
-                        make_smem_desc_sw128_kmajor(sb + S::kK + st * S::kTileBytes + off), idesc_s, k != 0);
+            const uint32_t off = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
+            umma_f16_ss_p(ds, smem_desc_join(ql + off), smem_desc_join(kl + off), idesc_s, k != 0, lead);
           }
-          umma_commit(s_full(t));
+          umma_commit_p(s_full(t), lead);
         };
         // O_t += P_t V: A = P_t from tensor memory (16 bf16 of K per step = 8 columns), B = V tile, MN-major
         auto issue_pv = [&](int t, int st) {
-          if (!mbar_wait(p_full(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
-          if (!mbar_wait(o_scaled(t), pv[t] & 1, abort_flag, p.budget_ns)) return false;
-          tc_fence_after_sync();
+          // P arrives in two halves of 64 keys: the product over the first half runs while the softmax threads still
+          // compute the exponentials of the second
+          const uint32_t ph = pv[t] & 1;
+          const uint32_t vl = v_lo0 + st * (S::kTileBytes >> 4), ds = tmem_s0 + t * 128, dout = tmem_o0 + t * D;
+          const uint32_t acc0 = pv[t] != 0;
+          if (!mbar_wait(o_scaled(t), ph, abort_flag, p.budget_ns)) return false;
 #pragma unroll
-          for (int k = 0; k < kFaTile / 16; ++k) {
-            const uint64_t dv = make_smem_desc_sw128_mnmajor(sb + S::kV + st * S::kTileBytes + k * 2048, kAtomBytes);
-            umma_f16_ts(tmem_o(t), tmem_s(t) + k * 8, dv, idesc_o, (k != 0) || (pv[t] != 0));
+          for (int half = 0; half < 2; ++half) {
+            if (!mbar_wait(p_full(t, half), ph, abort_flag, p.budget_ns)) return false;
+            if constexpr (TRACE) { if (t == 0 && half == 0 && lane == 0) fa_trace_slot(p, 0, 7, pv[0] + 1); }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int k = half * 4; k < half * 4 + 4; ++k)
+              umma_f16_ts_p(dout, ds + k * 8, smem_desc_join(vl + k * (2048 >> 4)), idesc_o, k != 0 ? 1u : acc0, lead);
           }
-          umma_commit(pv_done(t));
+          umma_commit_p(pv_done(t), lead);
           ++pv[t];
           return true;
         };
@@ -1155,28 +1182,29 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           if (!ok) return;
           const int st = j % kStages;
           if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
-          if constexpr (TRACE) fa_trace(p, 0, 0, j);
+          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 0, j); }
           if (j == 0) {
             if (need0(kp)) issue_s(0, st);
             if (has1) issue_s(1, st);
-            umma_commit(k_empty(st));
+            umma_commit_p(k_empty(st), lead);
             prev_kp = kp; prev_st = st;
             return;
           }
           if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
-          if constexpr (TRACE) fa_trace(p, 0, 1, j);
+          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 1, j); }
           if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
-          if constexpr (TRACE) fa_trace(p, 0, 2, j);
+          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 2, j); }
           if (need0(kp)) issue_s(0, st);
-          if constexpr (TRACE) fa_trace(p, 0, 3, j);
+          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 3, j); }
           if (has1) {
             if (!issue_pv(1, prev_st)) { ok = false; return; }
-            if constexpr (TRACE) fa_trace(p, 0, 4, j);
+            if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 4, j); }
             issue_s(1, st);
-            if constexpr (TRACE) fa_trace(p, 0, 5, j);
+            if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 5, j); }
           }
-          umma_commit(v_empty(prev_st));
-          umma_commit(k_empty(st));
+          umma_commit_p(v_empty(prev_st), lead);
+          umma_commit_p(k_empty(st), lead);
+          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 6, j); }
           prev_kp = kp; prev_st = st;
         });
         if (ok && n > 0) {
@@ -1184,7 +1212,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           if (ok && need0(prev_kp)) ok = issue_pv(0, prev_st);
           if (ok && has1) ok = issue_pv(1, prev_st);
         }
-        if (!ok) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 20, 0);
+        if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 20, 0);
       }
       __syncwarp();
     }
@@ -1209,41 +1237,37 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 0, cnt); }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 0, cnt); }
         tc_fence_after_sync();
-        // the whole row of scores in registers: four reads in flight, one wait
+        // the whole row of scores in registers, read in four chunks of 32 columns: the read of the next chunk is in flight
+        // while the maximum of the current one is taken (masking first where the tile crosses the diagonal or the end)
         uint32_t r[128];
-        {
-          uint32_t (&r0)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[0]);
-          uint32_t (&r1)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[32]);
-          uint32_t (&r2)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[64]);
-          uint32_t (&r3)[32] = *reinterpret_cast<uint32_t (*)[32]>(&r[96]);
-          tmem_ld_32x32(s_row, r0);
-          tmem_ld_32x32(s_row + 32, r1);
-          tmem_ld_32x32(s_row + 64, r2);
-          tmem_ld_32x32(s_row + 96, r3);
-          tmem_ld_wait();
-        }
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 1, cnt); }
         const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 128; ++i)
-            if (i >= valid || (d.causal && kp + i > my_pos)) r[i] = 0xff800000u;    // -inf: exp2 gives 0
-        }
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        if constexpr (OPT & 1) {
+        tmem_ld_32x32(s_row, *reinterpret_cast<uint32_t (*)[32]>(&r[0]));
 #pragma unroll
-          for (int i = 0; i < 128; i += 8) {
-            mx4[0] = max3(mx4[0], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-            mx4[1] = max3(mx4[1], __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-            mx4[2] = max3(mx4[2], __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-            mx4[3] = max3(mx4[3], __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+        for (int c = 0; c < 4; ++c) {
+          tmem_ld_wait();
+          if (c < 3) tmem_ld_32x32(s_row + (c + 1) * 32, *reinterpret_cast<uint32_t (*)[32]>(&r[(c + 1) * 32]));
+          if (need_mask) {
+#pragma unroll
+            for (int i = c * 32; i < c * 32 + 32; ++i)
+              if (i >= valid || (d.causal && kp + i > my_pos)) r[i] = 0xff800000u;    // -inf: exp2 gives 0
           }
-        } else {
+          if constexpr (OPT & 1) {
 #pragma unroll
-          for (int i = 0; i < 128; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+            for (int i = c * 32; i < c * 32 + 32; i += 8) {
+              mx4[0] = max3(mx4[0], __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+              mx4[1] = max3(mx4[1], __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+              mx4[2] = max3(mx4[2], __uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+              mx4[3] = max3(mx4[3], __uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+            }
+          } else {
+#pragma unroll
+            for (int i = c * 32; i < c * 32 + 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(r[i]));
+          }
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 1, cnt); }
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale2;
         // the offset follows the row maximum lazily: it moves only when the maximum has grown by more than 8 (a factor
         // 256 in the exponentials, harmless in fp32 sums and bf16 P), which makes rescaling the accumulator rare
@@ -1251,21 +1275,22 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         const bool dead = m_new == -INFINITY;
         const float alpha = (dead || m_new == m_run) ? 1.f : fast_exp2(m_run - m_new);
         const float neg_m = dead ? 0.f : -m_new;
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 2, cnt); }
-        ok = mbar_wait(a_empty(t), ph ^ 1u, abort_flag, p.budget_ns);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) return;
-        alpha_s[t * kFaTile + row] = alpha;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 2, cnt); }
+        // one alpha slot per step parity: the slot is rewritten two steps later, and the scores of step j+2 only exist
+        // after the P V product of step j, which waited for the correction warp's o_scaled arrival (it read the slot first)
+        alpha_s[(t * 2 + ph) * kFaTile + row] = alpha;
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(t));
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 3, cnt); }
-        // exponentials in place, then packed to bf16 pairs in the first 64 registers
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 3, cnt); }
+        // exponentials, packed to bf16 pairs, written over the first 64 score columns and published in two halves of 64 keys
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t w[64];
-        if constexpr (OPT != 0) {
-          const bool poly_ok = (OPT & 2) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
+        const bool poly_ok = (OPT & 2) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[32];
+#pragma unroll
+          for (int ii = 0; ii < 32; ++ii) {
+            const int i = half * 32 + ii;
             float x0, x1;
             if constexpr (OPT & 1) {
               fma2_bcast(x0, x1, __uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]), scale2, neg_m);
@@ -1288,30 +1313,16 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
               sum4[(2 * i) & 3] += e0;
               sum4[(2 * i + 1) & 3] += e1;
             }
-            w[i] = pack_bf16x2(e0, e1);
+            w[ii] = (OPT & 4) ? pack_bf16x2_alu(e0, e1) : pack_bf16x2(e0, e1);
           }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 128; ++i) {
-            const float e = fast_exp2(fmaf(__uint_as_float(r[i]), scale2, neg_m));
-            sum4[i & 3] += e;
-            r[i] = __float_as_uint(e);
-          }
-#pragma unroll
-          for (int i = 0; i < 64; ++i) w[i] = pack_bf16x2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-        }
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 4, cnt); }
-        {
-          const uint32_t (&w0)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[0]);
-          const uint32_t (&w1)[32] = *reinterpret_cast<const uint32_t (*)[32]>(&w[32]);
-          tmem_st_32x32(s_row, w0);
-          tmem_st_32x32(s_row + 32, w1);
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 4 + 2 * half, cnt); }
+          tmem_st_32x32(s_row + half * 32, w);
           tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(p_full(t, half));
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 5 + 2 * half, cnt); }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(p_full(t));
-        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 1 + t, 5, cnt); }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;
         ++cnt;
@@ -1370,10 +1381,8 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           ok = mbar_wait(a_full(t), ph, abort_flag, p.budget_ns);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
-          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 3, 2 * t, cnt[t]); }
-          const float alpha = alpha_s[t * kFaTile + row];
-          __syncwarp();
-          if (lane == 0) mbar_arrive(a_empty(t));
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 3, 2 * t, cnt[t]); }
+          const float alpha = alpha_s[(t * 2 + ph) * kFaTile + row];
           if (cnt[t] > 0) {
             // the accumulator may only be touched once the previous P V product has landed in it
             ok = mbar_wait(pv_done(t), (cnt[t] - 1) & 1, abort_flag, p.budget_ns);
@@ -1396,7 +1405,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(o_scaled(t));
-          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace(p, 3, 2 * t + 1, cnt[t]); }
+          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 3, 2 * t + 1, cnt[t]); }
           ++cnt[t];
         }
       });
@@ -1454,7 +1463,7 @@ struct Fa4Smem {
   static constexpr int kTotal = kBars + 512;
 };
 
-template <int D, bool POLY>
+template <int D, bool POLY, bool TRACE = false>
 __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUtensorMap& tmap_k,
                                             const CUtensorMap& tmap_v, const FaParams& p, const int q_pair,
                                             const int head, const int batch) {
@@ -1608,6 +1617,7 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
           if (!ok) return;
           const int st = j % kStages;
           if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace_slot(p, 0, 0, j);
           if (j == 0) {
             if (need0(kp)) issue_s(0, st);
             if (has1) issue_s(1, st);
@@ -1616,11 +1626,16 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
             return;
           }
           if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace_slot(p, 0, 1, j);
           if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
+          if constexpr (TRACE) fa_trace_slot(p, 0, 2, j);
           if (need0(kp)) issue_s(0, st);
+          if constexpr (TRACE) fa_trace_slot(p, 0, 3, j);
           if (has1) {
             if (!issue_pv(1, prev_st)) { ok = false; return; }
+            if constexpr (TRACE) fa_trace_slot(p, 0, 4, j);
             issue_s(1, st);
+            if constexpr (TRACE) fa_trace_slot(p, 0, 5, j);
           }
           umma_commit(v_empty(prev_st));
           umma_commit(k_empty(st));
@@ -1673,6 +1688,7 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
         ok = mbar_wait(s_full(t), ph, abort_flag, p.budget_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 0, cnt); }
         tc_fence_after_sync();
         uint32_t r[64];
         {
@@ -1682,6 +1698,7 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
           tmem_ld_32x32(s_cols + 32, r1);
           tmem_ld_wait();
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 1, cnt); }
         const bool need_mask = (d.causal && kp + kFaTile - 1 > my_pos) || valid < kFaTile;
         if (need_mask) {
 #pragma unroll
@@ -1703,8 +1720,10 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
         // P columns that overlap its score columns may be written after this point)
         float* slot = xch + ((ph * 2 + t) * 2) * kFaTile;
         slot[half * kFaTile + row] = mx;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 2, cnt); }
         ok = meet();
         if (!ok) return;
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 3, cnt); }
         mx = fmaxf(mx, slot[(half ^ 1) * kFaTile + row]) * scale2;
         // the offset follows the row maximum lazily: it moves only when the maximum has grown by more than 8
         const float m_new = (mx > m_run + 8.f) ? mx : m_run;
@@ -1750,11 +1769,13 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
           else add2_acc(sum4[0], sum4[1], e0, e1);
           w[i] = pack_bf16x2(e0, e1);
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 4, cnt); }
         tmem_st_32x32(p_cols, w);
         tmem_st_wait();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_full(t));
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0 && half == 0) fa_trace_slot(p, 1 + t, 5, cnt); }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;
         ++cnt;
@@ -1816,11 +1837,11 @@ __device__ __forceinline__ void fa_fwd4_cta(const CUtensorMap& tmap_q, const CUt
   }
 }
 
-template <int D, bool POLY>
+template <int D, bool POLY, bool TRACE = false>
 __global__ void __launch_bounds__(kFa4Threads, 1)
 fa_fwd4_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
-  fa_fwd4_cta<D, POLY>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
+  fa_fwd4_cta<D, POLY, TRACE>(tmap_q, tmap_k, tmap_v, p, gridDim.x - 1 - blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 template <int D, bool SPEC = false>
@@ -1999,7 +2020,13 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
   p.trace = reinterpret_cast<long long*>(d.trace);
   p.trace_capacity = d.trace_capacity;
   const int n_tiles = (d.sq + kFaTile - 1) / kFaTile;
-  if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v4()) {
+  if (fa_use_pairs(d) && p.trace != nullptr && fa_use_v4()) {
+    constexpr int smem = Fa4Smem<D>::kTotal;
+    dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
+    auto kern = fa_fwd4_kernel<D, false, true>;
+    PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, kFa4Threads, smem, stream>>>(tq, tk, tv, p);
+  } else if (fa_use_pairs(d) && p.trace == nullptr && fa_use_v4()) {
     constexpr int smem = Fa4Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     // PKB_FA_POLY=0: all exponentials on the special-function unit
@@ -2023,7 +2050,7 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     // PKB_FA_OPT=0..3 selects the softmax arithmetic variant (bit 0: packed pairs and three-input maxima, bit 1: polynomial)
-    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '3') ? e[0] - '0' : kFa3DefaultOpt; }();
+    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '7') ? e[0] - '0' : kFa3DefaultOpt; }();
 #define PKB_FA3(O)                                                                                   \
     {                                                                                                \
       auto kern = fa_fwd3_kernel<D, O>;                                                              \
@@ -2034,6 +2061,8 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
       case 1: PKB_FA3(1) break;
       case 2: PKB_FA3(2) break;
       case 3: PKB_FA3(3) break;
+      case 5: PKB_FA3(5) break;
+      case 7: PKB_FA3(7) break;
       default: PKB_FA3(0) break;
     }
 #undef PKB_FA3

@@ -133,6 +133,29 @@ def case_fa_fwd_4k(t):
     return _fa_fwd(t, 4096, "fa_fwd_4k")
 
 
+def case_umma_rate(t: _Timer) -> dict:
+    """SM cycles per ``tcgen05.mma`` (M = 128, K = 16, bf16) by operand form, one issuing thread, 512 products in a row; with
+    one CTA alone on the GPU and with one CTA on every SM. Nominal: 64 cycles at N = 128, 32 at N = 64, 128 at N = 256."""
+    import ctypes
+
+    from .. import _native as nv
+
+    forms = {0: "ss_n128", 1: "ss_n64", 2: "ss_n256", 3: "ts_bmn_n128", 4: "ss_bmn_n128", 5: "ts_n128", 6: "ts_bmn_n64",
+             7: "ss_n128_two_accumulators"}
+    out: dict = {"case": "umma_rate", "mmas": 512}
+    for ctas in (1, 148):
+        res = {}
+        for form, name in forms.items():
+            buf = torch.zeros(ctas, dtype=torch.int64, device="cuda")
+            for _ in range(2):
+                nv.check(nv.cuda_lib().pkb_umma_rate(form, 512, ctas, nv.ptr(buf), nv.current_stream()), "pkb_umma_rate")
+            torch.cuda.synchronize()
+            nv.raise_on_status(sync=True)
+            res[name] = round(float(buf.double().median()) / 512, 1)
+        out[f"cycles_per_mma_{ctas}cta"] = res
+    return out
+
+
 def case_fa_trace(t: _Timer) -> dict:
     """Device-side timeline of the attention forward's longest CTA: the roles stamp ``clock64`` at every hand-over, and the
     medians of the intervals between consecutive stamps (over the unmasked KV tiles) say which hand-over the chain waits on.
@@ -141,19 +164,27 @@ def case_fa_trace(t: _Timer) -> dict:
 
     q, k, v, _ = _attn_inputs(16384)
     flash_attn_fwd(q, k, v, causal=True)
-    trace = torch.zeros(4 + 4 * 8192, dtype=torch.int64, device="cuda")
+    tiles_cap = 160                                                     # kFaTraceTiles of the kernel
+    trace = torch.zeros(4 + 4 * tiles_cap * 8, dtype=torch.int64, device="cuda")
     flash_attn_fwd(q, k, v, causal=True, trace=trace)
     torch.cuda.synchronize()
-    n = min(int(trace[0]), 8192)
-    rec = trace[4:4 + 4 * n].view(n, 4).cpu().tolist()
+    slots = trace[4:].view(4, tiles_cap, 8).cpu().tolist()
     by_role: dict[int, dict[int, dict[int, int]]] = {}
-    for role, ev, tile, clk in rec:
-        by_role.setdefault(role, {}).setdefault(tile, {})[ev] = clk
+    n = 0
+    for role in range(4):
+        for tile in range(tiles_cap):
+            for ev in range(8):
+                if slots[role][tile][ev]:
+                    by_role.setdefault(role, {}).setdefault(tile, {})[ev] = slots[role][tile][ev]
+                    n += 1
     out: dict = {"case": "fa_trace", "records": n}
     for role, tiles in sorted(by_role.items()):
         idx = sorted(tiles)
         steady = [i for i in idx if 8 <= i < 100 and i + 1 in tiles]
         evs = sorted({e for i in steady for e in tiles[i]})
+        if steady:                                                     # order the events by their time inside a step
+            ref = steady[len(steady) // 2]
+            evs = sorted((e for e in evs if e in tiles[ref]), key=lambda e: tiles[ref][e])
         med = lambda xs: sorted(xs)[len(xs) // 2] if xs else None  # noqa: E731
         row = {"period": med([tiles[i + 1][evs[0]] - tiles[i][evs[0]] for i in steady if evs and evs[0] in tiles[i] and evs[0] in tiles[i + 1]])}
         for a, b in zip(evs, evs[1:]):
@@ -165,6 +196,15 @@ def case_fa_trace(t: _Timer) -> dict:
     if 1 in by_role and 2 in by_role:
         offs = [by_role[2][i][0] - by_role[1][i][0] for i in by_role[1] if 8 <= i < 100 and i in by_role[2] and 0 in by_role[1][i] and 0 in by_role[2][i]]
         out["softmax1_minus_softmax0_at_s_ready"] = sorted(offs)[len(offs) // 2] if offs else None
+    # hand-overs between roles: P written -> P V issued (the issuer handles tile j's P V in its iteration j + 1), and
+    # S issued -> S seen complete by the softmax warp
+    def cross(ra, ea, rb, eb, shift):
+        xs = [by_role[rb][i + shift][eb] - by_role[ra][i][ea] for i in by_role.get(ra, {})
+              if 8 <= i < 100 and ea in by_role[ra][i] and (i + shift) in by_role.get(rb, {}) and eb in by_role[rb][i + shift]]
+        return sorted(xs)[len(xs) // 2] if xs else None
+    last = max(by_role.get(1, {}).get(10, {0: 0}))                   # the last softmax event: all of P is published
+    out["handover"] = {"p0_written->pv0_issued": cross(1, last, 0, 2, 1), "s0_issued->s0_seen": cross(0, 3, 1, 0, 0),
+                       "p1_written->pv1_issued": cross(2, last, 0, 4, 1), "s1_issued->s1_seen": cross(0, 5, 2, 0, 0)}
     return out
 
 
