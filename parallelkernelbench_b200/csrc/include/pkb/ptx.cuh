@@ -84,6 +84,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// predicated forms for a producer WARP whose lanes walk the loop together (see umma_f16_ss_p)
+__device__ __forceinline__ void mbar_expect_tx_p(uint32_t bar, uint32_t bytes, uint32_t lead) {
+  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %2, 0;\n\t@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}\n" ::"r"(bar),
+               "r"(bytes), "r"(lead)
+               : "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -153,6 +159,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// The same wait for a warp whose lanes walk a loop together: one lane polls (32 lanes testing the same barrier are 32
+// barrier operations), the result is shared by a vote. `lead` is non-zero in exactly one lane.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns,
+                                               uint32_t lead) {
+  bool ok = true;
+  if (lead) ok = mbar_wait(bar, parity, abort_flag, budget_ns);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ----------------------------------------------------------------------------------------------
 // TMA: tiled bulk tensor copies. Loads complete on an mbarrier of this CTA; stores use bulk groups.
 // The innermost coordinate times the element size must be a multiple of 16 bytes.
@@ -167,6 +182,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
       " [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_p(uint32_t smem_dst, const CUtensorMap* desc, uint32_t bar, int32_t c0, int32_t c1,
+                                              int32_t c2, uint32_t lead) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\tsetp.ne.b32 q, %6, 0;\n\t"
+      "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];\n\t}\n"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(desc)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(lead)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* desc,

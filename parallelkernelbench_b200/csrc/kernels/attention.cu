@@ -65,12 +65,12 @@ __device__ __forceinline__ void fa_trace(const FaParams& p, int role, int event,
 // Trace of the P-in-TMEM kernel: a plain store into the slot of (role, tile, event) - no atomic, nothing to wait for, so the
 // stamps do not stretch the chain they measure. Layout after the four header words: [4 roles][kFaTraceTiles][8 events].
 constexpr int kFaTraceTiles = 160;
-__device__ __forceinline__ void fa_trace_slot(const FaParams& p, int role, int event, int tile) {
+__device__ __forceinline__ void fa_trace_slot(const FaParams& p, int role, int event, int tile, bool flag = false) {
   if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0 || tile >= kFaTraceTiles) return;
   if (p.trace_capacity * 4 < 4 * kFaTraceTiles * 8) return;
   long long t;
   asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
-  p.trace[4 + (role * kFaTraceTiles + tile) * 8 + event] = t;
+  p.trace[4 + (role * kFaTraceTiles + tile) * 8 + event] = t | (flag ? (1ll << 62) : 0ll);   // bit 62: a caller-defined flag
 }
 
 template <int D>
@@ -988,14 +988,16 @@ __device__ __forceinline__ void fa_fwd2_cta(const CUtensorMap& tmap_q, const CUt
 template <int D>
 struct Fa3Smem {
   static constexpr int kTileBytes = kFaTile * D * 2;
-  static constexpr int kStages = 2;
+  static constexpr int kStagesK = 3;                         // K(j+1) is wanted earlier than V(j+1): one stage more
+  static constexpr int kStagesV = 2;
   static constexpr int kQ = 0;                               // two tiles
-  static constexpr int kK = kQ + 2 * kTileBytes;             // kStages tiles
-  static constexpr int kV = kK + kStages * kTileBytes;       // kStages tiles
-  static constexpr int kAlpha = kV + kStages * kTileBytes;   // [2 tiles][2 step parities][128] fp32
+  static constexpr int kK = kQ + 2 * kTileBytes;
+  static constexpr int kV = kK + kStagesK * kTileBytes;
+  static constexpr int kAlpha = kV + kStagesV * kTileBytes;  // [2 tiles][2 step parities][128] fp32
   static constexpr int kBars = kAlpha + 2 * 2 * kFaTile * 4;
   static constexpr int kTotal = kBars + 512;
 };
+static_assert(Fa3Smem<128>::kTotal <= 232448, "shared-memory plan exceeds the 227 KiB a CTA may use");
 
 // Softmax arithmetic variant of the P-in-TMEM kernel used by default (see fa_fwd3_cta). Measured at S = 16384 causal, 32 / 8
 // heads, d = 128: 0 (scalar) 876 TFLOP/s, 1 (packed pairs, three-input maxima) 916, 2 (polynomial for a quarter of the
@@ -1020,23 +1022,25 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
   using S = Fa3Smem<D>;
   constexpr int kAtoms = D / 64;
   constexpr int kAtomBytes = kFaTile * 128;
-  constexpr int kStages = S::kStages;
+  constexpr int kStagesK = S::kStagesK, kStagesV = S::kStagesV;
   extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sb = smem_u32(smem);
   const pkb_attn_desc& d = p.d;
 
   const uint32_t bar0 = sb + S::kBars;
   const uint32_t q_full = bar0;
-  auto k_full = [&](int s) { return bar0 + 8u * (1 + s); };
-  auto k_empty = [&](int s) { return bar0 + 8u * (3 + s); };
-  auto v_full = [&](int s) { return bar0 + 8u * (5 + s); };
+  // kv_full(j % 3): K of tile j and V of tile j-1 arrive together (the issuing warp needs both for step j and every barrier
+  // operation it executes sits on the chain between two products). Three of them, because the producer can be two steps ahead.
+  auto kv_full = [&](int s) { return bar0 + 8u * (1 + s); };
+  auto k_empty = [&](int s) { return bar0 + 8u * (4 + s); };
   auto v_empty = [&](int s) { return bar0 + 8u * (7 + s); };
   auto s_full = [&](int t) { return bar0 + 8u * (9 + t); };
-  auto p_full = [&](int t, int half) { return bar0 + 8u * (11 + t + 4 * half); };   // 11, 12 first half; 15, 16 second half
+  // p_full(t): P of the step is in tensor memory (four softmax warps) AND the accumulator has been rescaled where a row's
+  // offset moved (four correction warps): one wait for the issuing warp before the P V product
+  auto p_full = [&](int t) { return bar0 + 8u * (11 + t); };
   auto a_full = [&](int t) { return bar0 + 8u * (13 + t); };
-  auto o_scaled = [&](int t) { return bar0 + 8u * (17 + t); };
-  auto pv_done = [&](int t) { return bar0 + 8u * (19 + t); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 22);
+  auto pv_done = [&](int t) { return bar0 + 8u * (15 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + S::kBars + 8 * 18);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   float* alpha_s = reinterpret_cast<float*>(smem + S::kAlpha);
 
@@ -1062,14 +1066,13 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
       record_status(p.status, kStatusBadArgument, 603, 0, 0, 1, 0);
     }
     mbar_init(q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_full(s), 1); mbar_init(v_empty(s), 1);
-    }
+    for (int s = 0; s < kStagesK; ++s) { mbar_init(kv_full(s), 1); mbar_init(k_empty(s), 1); }
+    for (int s = 0; s < kStagesV; ++s) mbar_init(v_empty(s), 1);
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t, 0), 4); mbar_init(p_full(t, 1), 4);
+      mbar_init(p_full(t), 8);
       mbar_init(a_full(t), 4);
-      mbar_init(o_scaled(t), 4); mbar_init(pv_done(t), 1);
+      mbar_init(pv_done(t), 1);
     }
     fence_mbar_init();
     tma_prefetch_desc(&tmap_q);
@@ -1094,42 +1097,58 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
       // common exit
     } else if (warp == 0) {
       // ------------------------------ TMA producer ------------------------------
-      if (lane == 0) {
-        mbar_expect_tx(q_full, (has1 ? 2 : 1) * S::kTileBytes);
+      // warp-uniform loop, one elected lane's copies take effect (see umma_f16_ss_p)
+      {
+        const uint32_t lead = elect_one() ? 1u : 0u;
+        mbar_expect_tx_p(q_full, (has1 ? 2 : 1) * S::kTileBytes, lead);
         for (int t = 0; t < (has1 ? 2 : 1); ++t)
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
-            tma_load_3d(sb + S::kQ + t * S::kTileBytes + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0 + t * kFaTile);
+            tma_load_3d_p(sb + S::kQ + t * S::kTileBytes + a * kAtomBytes, &tmap_q, q_full, a * 64, head, q_tok0 + t * kFaTile, lead);
         bool ok = true;
         int last_seg = -1;
-        for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
+        // step j's barrier carries K(j) and V(j-1): the K slot was freed at the end of step j-3, the V slot at the end of
+        // step j-2, so both are requested about two steps before the issuing warp asks for them
+        auto load_v = [&](int j, int row, uint32_t bar) {
+          const int sv = j % kStagesV;
+          if (!mbar_wait(v_empty(sv), ((j / kStagesV) & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+#pragma unroll
+          for (int a = 0; a < kAtoms; ++a)
+            tma_load_3d_p(sb + S::kV + sv * S::kTileBytes + a * kAtomBytes, &tmap_v, bar, a * 64, kv_head, kv_tok_base + row, lead);
+        };
+        int prev_row = 0;
+        const int n = for_each_kv_tile(d, q_pos_last, [&](int j, int row, int /*kp*/, int /*valid*/, int seg) {
           if (!ok) return;
-          const int st = j % kStages;
-          const uint32_t ph = (j / kStages) & 1;
+          const int sk = j % kStagesK;
           if (seg != last_seg) {
             last_seg = seg;
             if (d.kv_seg_ready != nullptr && d.kv_seg_flag[seg] >= 0) {
               if (!wait_flag_ge(d.kv_seg_ready + d.kv_seg_flag[seg], d.ready_epoch, p.budget_ns)) {
                 *abort_flag = 1;
-                record_status(p.status, kStatusPeerTimeout, 603, 0, seg, 10, j);
+                if (lane == 0) record_status(p.status, kStatusPeerTimeout, 603, 0, seg, 10, j);
                 ok = false;
                 return;
               }
               fence_proxy_async_all();
             }
           }
-          if (!mbar_wait(k_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
-          mbar_expect_tx(k_full(st), S::kTileBytes);
+          if (!mbar_wait(k_empty(sk), ((j / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          mbar_expect_tx_p(kv_full(sk), (j > 0 ? 2 : 1) * S::kTileBytes, lead);
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
-            tma_load_3d(sb + S::kK + st * S::kTileBytes + a * kAtomBytes, &tmap_k, k_full(st), a * 64, kv_head, kv_tok_base + row);
-          if (!mbar_wait(v_empty(st), ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
-          mbar_expect_tx(v_full(st), S::kTileBytes);
-#pragma unroll
-          for (int a = 0; a < kAtoms; ++a)
-            tma_load_3d(sb + S::kV + st * S::kTileBytes + a * kAtomBytes, &tmap_v, v_full(st), a * 64, kv_head, kv_tok_base + row);
+            tma_load_3d_p(sb + S::kK + sk * S::kTileBytes + a * kAtomBytes, &tmap_k, kv_full(sk), a * 64, kv_head, kv_tok_base + row, lead);
+          if (j > 0) load_v(j - 1, prev_row, kv_full(sk));
+          prev_row = row;
         });
-        if (!ok) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 11, 0);
+        if (ok && n > 0) {                     // the last V tile alone, on the barrier step n would have used
+          if (mbar_wait(k_empty(n % kStagesK), ((n / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns)) {
+            mbar_expect_tx_p(kv_full(n % kStagesK), S::kTileBytes, lead);
+            load_v(n - 1, prev_row, kv_full(n % kStagesK));
+          } else {
+            ok = false;
+          }
+        }
+        if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 603, 0, 0, 11, 0);
       }
       __syncwarp();
     } else if (warp == 1) {
@@ -1146,7 +1165,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         const uint32_t k_lo0 = smem_desc_lo_kmajor(sb + S::kK);
         const uint32_t v_lo0 = smem_desc_lo_mnmajor(sb + S::kV, kAtomBytes);
         const uint32_t tmem_s0 = tmem_base, tmem_o0 = tmem_base + 256;
-        auto issue_s = [&](int t, int st) {
+        auto issue_s = [&](int t, int st) {            // st: K stage
           tc_fence_after_sync();
           const uint32_t ql = q_lo0 + t * (S::kTileBytes >> 4), kl = k_lo0 + st * (S::kTileBytes >> 4), ds = tmem_s0 + t * 128;
 #pragma unroll
@@ -1158,40 +1177,33 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         };
         // O_t += P_t V: A = P_t from tensor memory (16 bf16 of K per step = 8 columns), B = V tile, MN-major
         auto issue_pv = [&](int t, int st) {
-          // P arrives in two halves of 64 keys: the product over the first half runs while the softmax threads still
-          // compute the exponentials of the second
           const uint32_t ph = pv[t] & 1;
           const uint32_t vl = v_lo0 + st * (S::kTileBytes >> 4), ds = tmem_s0 + t * 128, dout = tmem_o0 + t * D;
           const uint32_t acc0 = pv[t] != 0;
-          if (!mbar_wait(o_scaled(t), ph, abort_flag, p.budget_ns)) return false;
+          if (!mbar_wait(p_full(t), ph, abort_flag, p.budget_ns)) return false;
+          if constexpr (TRACE) { if (t == 0 && lane == 0) fa_trace_slot(p, 0, 7, pv[0] + 1); }
+          tc_fence_after_sync();
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            if (!mbar_wait(p_full(t, half), ph, abort_flag, p.budget_ns)) return false;
-            if constexpr (TRACE) { if (t == 0 && half == 0 && lane == 0) fa_trace_slot(p, 0, 7, pv[0] + 1); }
-            tc_fence_after_sync();
-#pragma unroll
-            for (int k = half * 4; k < half * 4 + 4; ++k)
-              umma_f16_ts_p(dout, ds + k * 8, smem_desc_join(vl + k * (2048 >> 4)), idesc_o, k != 0 ? 1u : acc0, lead);
-          }
+          for (int k = 0; k < kFaTile / 16; ++k)
+            umma_f16_ts_p(dout, ds + k * 8, smem_desc_join(vl + k * (2048 >> 4)), idesc_o, k != 0 ? 1u : acc0, lead);
           umma_commit_p(pv_done(t), lead);
           ++pv[t];
           return true;
         };
-        int prev_kp = 0, prev_st = 0;
+        int prev_kp = 0, prev_st = 0;                   // prev_st: V stage of the previous tile
         const int n = for_each_kv_tile(d, q_pos_last, [&](int j, int /*row*/, int kp, int /*valid*/, int /*seg*/) {
           if (!ok) return;
-          const int st = j % kStages;
-          if (!mbar_wait(k_full(st), (j / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
+          const int st = j % kStagesK;
+          if constexpr (TRACE) { if (lane == 0 && j > 0) fa_trace_slot(p, 0, 6, j - 1); }
+          if (!mbar_wait(kv_full(st), (j / kStagesK) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
           if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 0, j); }
           if (j == 0) {
             if (need0(kp)) issue_s(0, st);
             if (has1) issue_s(1, st);
             umma_commit_p(k_empty(st), lead);
-            prev_kp = kp; prev_st = st;
+            prev_kp = kp; prev_st = j % kStagesV;
             return;
           }
-          if (!mbar_wait(v_full(prev_st), ((j - 1) / kStages) & 1, abort_flag, p.budget_ns)) { ok = false; return; }
-          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 1, j); }
           if (need0(prev_kp) && !issue_pv(0, prev_st)) { ok = false; return; }
           if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 2, j); }
           if (need0(kp)) issue_s(0, st);
@@ -1204,11 +1216,11 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           }
           umma_commit_p(v_empty(prev_st), lead);
           umma_commit_p(k_empty(st), lead);
-          if constexpr (TRACE) { if (lane == 0) fa_trace_slot(p, 0, 6, j); }
-          prev_kp = kp; prev_st = st;
+          prev_kp = kp; prev_st = j % kStagesV;
         });
         if (ok && n > 0) {
-          ok = mbar_wait(v_full(prev_st), ((n - 1) / kStages) & 1, abort_flag, p.budget_ns);
+          ok = mbar_wait(kv_full(n % kStagesK), (n / kStagesK) & 1, abort_flag, p.budget_ns);
+          umma_commit_p(k_empty(n % kStagesK), lead);          // no K tile was read in this step; the commit keeps the ring's phases in step
           if (ok && need0(prev_kp)) ok = issue_pv(0, prev_st);
           if (ok && has1) ok = issue_pv(1, prev_st);
         }
@@ -1277,12 +1289,13 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         const float neg_m = dead ? 0.f : -m_new;
         if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 2, cnt); }
         // one alpha slot per step parity: the slot is rewritten two steps later, and the scores of step j+2 only exist
-        // after the P V product of step j, which waited for the correction warp's o_scaled arrival (it read the slot first)
+        // after the P V product of step j, which waited for the correction warp's arrival on p_full (it read the slot first)
         alpha_s[(t * 2 + ph) * kFaTile + row] = alpha;
         __syncwarp();
         if (lane == 0) mbar_arrive(a_full(t));
         if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 3, cnt); }
-        // exponentials, packed to bf16 pairs, written over the first 64 score columns and published in two halves of 64 keys
+        // exponentials, packed to bf16 pairs and written over the first 64 score columns, 64 keys at a time (the packed words
+        // of one half are stored while the next half is computed, and fewer registers are live than with the whole row)
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         const bool poly_ok = (OPT & 2) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
 #pragma unroll
@@ -1315,14 +1328,14 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
             }
             w[ii] = (OPT & 4) ? pack_bf16x2_alu(e0, e1) : pack_bf16x2(e0, e1);
           }
-          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 4 + 2 * half, cnt); }
           tmem_st_32x32(s_row + half * 32, w);
-          tmem_st_wait();
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(p_full(t, half));
-          if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 5 + 2 * half, cnt); }
         }
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 4, cnt); }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(t));
+        if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 1 + t, 5, cnt); }
         l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
         m_run = m_new;
         ++cnt;
@@ -1404,7 +1417,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
             }
           }
           __syncwarp();
-          if (lane == 0) mbar_arrive(o_scaled(t));
+          if (lane == 0) mbar_arrive(p_full(t));
           if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 3, 2 * t + 1, cnt[t]); }
           ++cnt[t];
         }

@@ -170,14 +170,17 @@ def case_fa_trace(t: _Timer) -> dict:
     torch.cuda.synchronize()
     slots = trace[4:].view(4, tiles_cap, 8).cpu().tolist()
     by_role: dict[int, dict[int, dict[int, int]]] = {}
+    flagged: dict = {}                                                  # stamps whose flag bit is set, tiles 8..99
     n = 0
     for role in range(4):
         for tile in range(tiles_cap):
             for ev in range(8):
                 if slots[role][tile][ev]:
-                    by_role.setdefault(role, {}).setdefault(tile, {})[ev] = slots[role][tile][ev]
+                    by_role.setdefault(role, {}).setdefault(tile, {})[ev] = slots[role][tile][ev] & ((1 << 62) - 1)
+                    if slots[role][tile][ev] >> 62 and 8 <= tile < 100:
+                        flagged[(role, ev)] = flagged.get((role, ev), 0) + 1
                     n += 1
-    out: dict = {"case": "fa_trace", "records": n}
+    out: dict = {"case": "fa_trace", "records": n, "flagged_of_92": {f"role{r}_e{e}": c for (r, e), c in sorted(flagged.items())}}
     for role, tiles in sorted(by_role.items()):
         idx = sorted(tiles)
         steady = [i for i in idx if 8 <= i < 100 and i + 1 in tiles]
