@@ -166,7 +166,9 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // warp-uniform loop: one elected lane's copies take effect (see umma_f16_ss_p)
+    {
+      const uint32_t lead = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -175,14 +177,14 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
         tile_coords(tile, row0, row_end, n_blk, b_row0);
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, stage, 11, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, stage, 11, tile);
             ok = false;
             break;
           }
-          mbar_expect_tx(full_bar(stage), S::kStageBytes);
+          mbar_expect_tx_p(full_bar(stage), S::kStageBytes, lead);
           const uint32_t sa = smem_base + stage * S::kStageBytes;
-          tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kFp8BlockK, row0);
-          tma_load_2d(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kFp8BlockK, b_row0);
+          tma_load_2d_p(sa, &tmap_a, full_bar(stage), kb * kFp8BlockK, row0, lead);
+          tma_load_2d_p(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kFp8BlockK, b_row0, lead);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -193,8 +195,11 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane's tcgen05 instructions take effect (see umma_f16_ss_p)
+    {
+      const uint32_t lead = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc = make_idesc(kFp8BlockM, BN, 0, 0);  // e4m3 x e4m3, fp32 accumulate
+      const uint32_t a_lo0 = smem_desc_lo_kmajor(smem_base), b_lo0 = smem_desc_lo_kmajor(smem_base + S::kABytes);
       int stage = 0;
       uint32_t phase = 0;
       int pb = 0;
@@ -203,27 +208,23 @@ __device__ __forceinline__ void gemm_fp8_cta(const CUtensorMap& tmap_a, const CU
       for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(pempty_bar(pb), pb_phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, pb, 20, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, pb, 20, tile);
             ok = false;
             break;
           }
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, stage, 21, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, 0, stage, 21, tile);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * S::kStageBytes;
-          const uint64_t da = make_smem_desc_sw128_kmajor(sa);
-          const uint64_t db = make_smem_desc_sw128_kmajor(sa + S::kABytes);
+          const uint32_t a_lo = a_lo0 + stage * (S::kStageBytes >> 4), b_lo = b_lo0 + stage * (S::kStageBytes >> 4);
           const uint32_t tmem_d = tmem_base + pb * BN;
 #pragma unroll
-          for (int k = 0; k < kFp8BlockK / 32; ++k) {
-            // 32 e4m3 = 32 bytes along K inside the swizzled row: +2 in the (addr >> 4) field
-            umma_f8_ss(tmem_d, da + 2u * k, db + 2u * k, idesc, k != 0 ? 1u : 0u);
-          }
-          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
-          umma_commit(pfull_bar(pb));     // partial sum of this K block complete
+          for (int k = 0; k < kFp8BlockK / 32; ++k)   // 32 e4m3 = 32 bytes along K inside the swizzled row: +2 in the address field
+            umma_f8_ss_p(tmem_d, smem_desc_join(a_lo + 2u * k), smem_desc_join(b_lo + 2u * k), idesc, k != 0 ? 1u : 0u, lead);
+          umma_commit_p(empty_bar(stage), lead);  // stage reusable once these MMAs have read it
+          umma_commit_p(pfull_bar(pb), lead);     // partial sum of this K block complete
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;

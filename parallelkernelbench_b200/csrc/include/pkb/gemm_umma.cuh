@@ -195,7 +195,9 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    {
+      // warp-uniform loop: one elected lane's copies take effect (see umma_f16_ss_p)
+      const uint32_t lead = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -206,7 +208,7 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
           const int chunk = row0 / p.a_chunk_rows;
           if (!wait_flag_ge(p.a_ready + chunk, p.a_ready_epoch, p.wait_budget_ns)) {
             *abort_flag = 1;
-            record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
+            if (lane == 0) record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
             ok = false;
             break;
           }
@@ -216,26 +218,26 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
         }
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 11, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 11, tile);
             ok = false;
             break;
           }
-          mbar_expect_tx(full_bar(stage), S::kStageBytes);
+          mbar_expect_tx_p(full_bar(stage), S::kStageBytes, lead);
           const uint32_t sa = smem_base + stage * S::kStageBytes;
           if constexpr (A_MN) {
 #pragma unroll
             for (int j = 0; j < kGemmBlockM / 64; ++j)
-              tma_load_2d(sa + j * 8192, &tmap_a, full_bar(stage), row0 + j * 64, kb * kGemmBlockK);
+              tma_load_2d_p(sa + j * 8192, &tmap_a, full_bar(stage), row0 + j * 64, kb * kGemmBlockK, lead);
           } else {
-            tma_load_2d(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0);
+            tma_load_2d_p(sa, &tmap_a, full_bar(stage), kb * kGemmBlockK, row0, lead);
           }
           if constexpr (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sa + S::kABytes + j * 8192, &tmap_b, full_bar(stage), b_row0 + j * 64,
-                          kb * kGemmBlockK);
+              tma_load_2d_p(sa + S::kABytes + j * 8192, &tmap_b, full_bar(stage), b_row0 + j * 64,
+                          kb * kGemmBlockK, lead);
           } else {
-            tma_load_2d(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, b_row0);
+            tma_load_2d_p(sa + S::kABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, b_row0, lead);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -247,8 +249,14 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // warp-uniform loop, one elected lane's tcgen05 instructions take effect (see umma_f16_ss_p)
+    {
+      const uint32_t lead = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc = make_idesc(kGemmBlockM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // low descriptor words of stage 0; a stage adds kStageBytes >> 4, a K step of 16 adds 2 (K-major: 32 bytes inside the
+      // swizzled row) or 128 (MN-major: 16 rows of 128 bytes)
+      const uint32_t a_lo0 = A_MN ? smem_desc_lo_mnmajor(smem_base, 8192u) : smem_desc_lo_kmajor(smem_base);
+      const uint32_t b_lo0 = B_MN ? smem_desc_lo_mnmajor(smem_base + S::kABytes, 8192u) : smem_desc_lo_kmajor(smem_base + S::kABytes);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -256,37 +264,31 @@ __device__ __forceinline__ void gemm_umma_cta(const CUtensorMap& tmap_a, const C
       bool ok = true;
       for (int tile = cta; tile < num_tiles && ok; tile += num_ctas) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-          record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
+          if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 21, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 21, tile);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * S::kStageBytes;
-          const uint64_t da = A_MN ? make_smem_desc_sw128_mnmajor(sa, 8192u) : make_smem_desc_sw128_kmajor(sa);
-          const uint64_t db = B_MN ? make_smem_desc_sw128_mnmajor(sa + S::kABytes, 8192u)
-                                   : make_smem_desc_sw128_kmajor(sa + S::kABytes);
+          const uint32_t a_lo = a_lo0 + stage * (S::kStageBytes >> 4), b_lo = b_lo0 + stage * (S::kStageBytes >> 4);
 #pragma unroll
-          for (int k = 0; k < kGemmBlockK / 16; ++k) {
-            // K-major: 16 bf16 = 32 bytes along K inside the swizzled row: +2 in the (addr >> 4)
-            // field. MN-major: 16 K rows of 128 bytes: +128.
-            umma_f16_ss(tmem_d, da + (A_MN ? 128u : 2u) * k, db + (B_MN ? 128u : 2u) * k, idesc,
-                        (kb | k) != 0 ? 1u : 0u);
-          }
-          umma_commit(empty_bar(stage));  // smem stage reusable once these MMAs have read it
+          for (int k = 0; k < kGemmBlockK / 16; ++k)
+            umma_f16_ss_p(tmem_d, smem_desc_join(a_lo + (A_MN ? 128u : 2u) * k), smem_desc_join(b_lo + (B_MN ? 128u : 2u) * k), idesc,
+                          (kb | k) != 0 ? 1u : 0u, lead);
+          umma_commit_p(empty_bar(stage), lead);  // smem stage reusable once these MMAs have read it
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit(tfull_bar(acc));  // accumulator complete
+        umma_commit_p(tfull_bar(acc), lead);  // accumulator complete
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;

@@ -106,7 +106,9 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------------------
-    if (lane == 0) {
+    {
+      // warp-uniform loop: one elected lane's copies take effect (see umma_f16_ss_p)
+      const uint32_t lead = elect_one() ? 1u : 0u;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -136,7 +138,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           if (p.a_wait_cycles != nullptr) waited += clock64() - w0;
           if (!arrived) {
             *abort_flag = 1;
-            record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
+            if (lane == 0) record_status(p.status, kStatusPeerTimeout, p.kernel_id, p.rank, chunk, 10, tile);
             ok = false;
             break;
           }
@@ -144,23 +146,23 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
         }
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 11, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 11, tile);
             ok = false;
             break;
           }
-          if (leader) mbar_expect_tx(full_bar(stage), 2 * kGemm2StageBytes);
+          mbar_expect_tx_p(full_bar(stage), 2 * kGemm2StageBytes, leader ? lead : 0u);
           const uint32_t sa = smem_base + stage * kGemm2StageBytes;
           if constexpr (A_MN) {
-            tma_load_2d_pair(sa, map_a, full_bar(stage), a_row, kb * kGemmBlockK);
-            tma_load_2d_pair(sa + 8192, map_a, full_bar(stage), a_row + 64, kb * kGemmBlockK);
+            tma_load_2d_pair_p(sa, map_a, full_bar(stage), a_row, kb * kGemmBlockK, lead);
+            tma_load_2d_pair_p(sa + 8192, map_a, full_bar(stage), a_row + 64, kb * kGemmBlockK, lead);
           } else {
-            tma_load_2d_pair(sa, map_a, full_bar(stage), kb * kGemmBlockK, a_row);
+            tma_load_2d_pair_p(sa, map_a, full_bar(stage), kb * kGemmBlockK, a_row, lead);
           }
           if constexpr (B_MN) {
-            tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), col0, kb * kGemmBlockK);
-            tma_load_2d_pair(sa + kGemm2ABytes + 8192, &tmap_b, full_bar(stage), col0 + 64, kb * kGemmBlockK);
+            tma_load_2d_pair_p(sa + kGemm2ABytes, &tmap_b, full_bar(stage), col0, kb * kGemmBlockK, lead);
+            tma_load_2d_pair_p(sa + kGemm2ABytes + 8192, &tmap_b, full_bar(stage), col0 + 64, kb * kGemmBlockK, lead);
           } else {
-            tma_load_2d_pair(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0);
+            tma_load_2d_pair_p(sa + kGemm2ABytes, &tmap_b, full_bar(stage), kb * kGemmBlockK, col0, lead);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -169,14 +171,21 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
         }
       }
       if constexpr (A_READY) {
-        if (p.a_wait_cycles != nullptr) p.a_wait_cycles[blockIdx.x] += (unsigned long long)waited;
+        if (p.a_wait_cycles != nullptr && lane == 0) p.a_wait_cycles[blockIdx.x] += (unsigned long long)waited;
       }
     }
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ------------------------------
-    if (leader && lane == 0) {
+    // The whole warp walks the loop and waits on the barriers; one elected lane's tcgen05 instructions take effect. Under
+    // `if (lane == 0)` the loop would run in divergent code, where addresses and descriptors cannot live in uniform
+    // registers and every tcgen05 instruction drags register-to-uniform moves behind it (see umma_f16_ss_p).
+    if (leader) {
+      const uint32_t lead = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc = make_idesc(kGemm2TileM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      // low descriptor words of stage 0; a stage adds kGemm2StageBytes >> 4, a K step of 16 adds 2 (K-major) or 128 (MN-major)
+      const uint32_t a_lo0 = A_MN ? smem_desc_lo_mnmajor(smem_base, 8192u) : smem_desc_lo_kmajor(smem_base);
+      const uint32_t b_lo0 = B_MN ? smem_desc_lo_mnmajor(smem_base + kGemm2ABytes, 8192u) : smem_desc_lo_kmajor(smem_base + kGemm2ABytes);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -184,33 +193,31 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.wait_budget_ns)) {
-          record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
+          if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, acc, 20, tile);
           break;
         }
         tc_fence_after_sync();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.wait_budget_ns)) {
-            record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 21, tile);
+            if (lane == 0) record_status(p.status, kStatusMbarTimeout, p.kernel_id, p.rank, stage, 21, tile);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_base + stage * kGemm2StageBytes;
-          const uint64_t da = A_MN ? make_smem_desc_sw128_mnmajor(sa, 8192u) : make_smem_desc_sw128_kmajor(sa);
-          const uint64_t db = B_MN ? make_smem_desc_sw128_mnmajor(sa + kGemm2ABytes, 8192u)
-                                   : make_smem_desc_sw128_kmajor(sa + kGemm2ABytes);
+          const uint32_t a_lo = a_lo0 + stage * (kGemm2StageBytes >> 4), b_lo = b_lo0 + stage * (kGemm2StageBytes >> 4);
 #pragma unroll
-          for (int k = 0; k < kGemmBlockK / 16; ++k)   // 16 along K: +32 bytes inside a K-major row, +2048 bytes MN-major
-            umma_f16_ss_pair(tmem_d, da + (A_MN ? 128u : 2u) * k, db + (B_MN ? 128u : 2u) * k, idesc, (kb | k) != 0 ? 1u : 0u);
-          umma_commit_pair(empty_bar(stage), 0x3);
+          for (int k = 0; k < kGemmBlockK / 16; ++k)
+            umma_f16_ss_pair_p(tmem_d, smem_desc_join(a_lo + (A_MN ? 128u : 2u) * k), smem_desc_join(b_lo + (B_MN ? 128u : 2u) * k), idesc,
+                               (kb | k) != 0 ? 1u : 0u, lead);
+          umma_commit_pair_p(empty_bar(stage), 0x3, lead);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (!ok) break;
-        umma_commit_pair(tfull_bar(acc), 0x3);
+        umma_commit_pair_p(tfull_bar(acc), 0x3, lead);
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1u;

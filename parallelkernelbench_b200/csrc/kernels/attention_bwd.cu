@@ -223,12 +223,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   if (bad || n_steps == 0) {
     // nothing to accumulate for this tile: its dK / dV rows keep the zeros the caller put there
   } else if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(kv_full, 2 * S::kTileBytes);
+    // producer: the whole warp walks the loop, one elected lane's copies take effect. Under `if (lane == 0)` the loop would
+    // run in divergent code, where addresses cannot live in uniform registers (see umma_f16_ss_p).
+    {
+      const uint32_t lead = elect_one() ? 1u : 0u;
+      mbar_expect_tx_p(kv_full, 2 * S::kTileBytes, lead);
 #pragma unroll
       for (int a = 0; a < kAtoms; ++a) {
-        tma_load_3d(sb + S::kK + a * kAtomBytes, &tmap_k, kv_full, a * 64, kv_head, kv_tok0);
-        tma_load_3d(sb + S::kV + a * kAtomBytes, &tmap_v, kv_full, a * 64, kv_head, kv_tok0);
+        tma_load_3d_p(sb + S::kK + a * kAtomBytes, &tmap_k, kv_full, a * 64, kv_head, kv_tok0, lead);
+        tma_load_3d_p(sb + S::kV + a * kAtomBytes, &tmap_v, kv_full, a * 64, kv_head, kv_tok0, lead);
       }
       bool ok = true;
       for (int step = 0; step < n_steps && ok; ++step) {
@@ -236,21 +239,31 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         step_coords(step, head, qt);
         if (!mbar_wait(qdo_empty, (step & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; break; }
         const int q_tok0 = batch * d.sq + qt * kFbTile;
-        mbar_expect_tx(qdo_full, 2 * S::kTileBytes);
+        mbar_expect_tx_p(qdo_full, 2 * S::kTileBytes, lead);
 #pragma unroll
         for (int a = 0; a < kAtoms; ++a) {
-          tma_load_3d(sb + S::kQ + a * kAtomBytes, &tmap_q, qdo_full, a * 64, head, q_tok0);
-          tma_load_3d(sb + S::kDO + a * kAtomBytes, &tmap_do, qdo_full, a * 64, head, q_tok0);
+          tma_load_3d_p(sb + S::kQ + a * kAtomBytes, &tmap_q, qdo_full, a * 64, head, q_tok0, lead);
+          tma_load_3d_p(sb + S::kDO + a * kAtomBytes, &tmap_do, qdo_full, a * 64, head, q_tok0, lead);
         }
       }
-      if (!ok) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 11, 0);
+      if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 11, 0);
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
+    // issuer: warp-uniform loop with prepared descriptor words; one elected lane's tcgen05 instructions take effect
+    {
+      const uint32_t lead = elect_one() ? 1u : 0u;
       constexpr uint32_t idesc_s = make_idesc(kFbTile, kFbTile, 1, 1, 0, 0);   // S, dP: both operands K-major
       constexpr uint32_t idesc_acc = make_idesc(kFbTile, D, 1, 1, 1, 1);       // dV, dK: A and B MN-major
       constexpr uint32_t idesc_dq = make_idesc(kFbTile, D, 1, 1, 0, 1);        // dQ: A K-major, B MN-major
+      // K-major views step 16 along K by 32 bytes inside a 64-column atom (atoms kAtomBytes apart); MN-major views step 16
+      // along K by 16 rows of 128 bytes
+      const uint32_t q_k = smem_desc_lo_kmajor(sb + S::kQ), k_k = smem_desc_lo_kmajor(sb + S::kK);
+      const uint32_t do_k = smem_desc_lo_kmajor(sb + S::kDO), v_k = smem_desc_lo_kmajor(sb + S::kV);
+      const uint32_t ds_k = smem_desc_lo_kmajor(sb + S::kDS);
+      const uint32_t k_mn = smem_desc_lo_mnmajor(sb + S::kK, kAtomBytes), p_mn = smem_desc_lo_mnmajor(sb + S::kP, kAtomBytes);
+      const uint32_t do_mn = smem_desc_lo_mnmajor(sb + S::kDO, kAtomBytes), ds_mn = smem_desc_lo_mnmajor(sb + S::kDS, kAtomBytes);
+      const uint32_t q_mn = smem_desc_lo_mnmajor(sb + S::kQ, kAtomBytes);
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.budget_ns);
       for (int step = 0; step < n_steps && ok; ++step) {
         const uint32_t ph = step & 1;
@@ -261,45 +274,39 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kQ + off), make_smem_desc_sw128_kmajor(sb + S::kK + off),
-                      idesc_s, k != 0);
+          const uint32_t off = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
+          umma_f16_ss_p(tmem_s, smem_desc_join(q_k + off), smem_desc_join(k_k + off), idesc_s, k != 0, lead);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          umma_f16_ss(tmem_dp, make_smem_desc_sw128_kmajor(sb + S::kDO + off), make_smem_desc_sw128_kmajor(sb + S::kV + off),
-                      idesc_s, k != 0);
+          const uint32_t off = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
+          umma_f16_ss_p(tmem_dp, smem_desc_join(do_k + off), smem_desc_join(v_k + off), idesc_s, k != 0, lead);
         }
-        umma_commit(sdp_full);
+        umma_commit_p(sdp_full, lead);
         if (!mbar_wait(pds_full, ph, abort_flag, p.budget_ns)) { ok = false; break; }
         tc_fence_after_sync();
         // dQ partial = dS K_j  (K dimension = the 128 kv rows)
 #pragma unroll
         for (int k = 0; k < kFbTile / 16; ++k) {
-          const uint32_t aoff = (k >> 2) * kAtomBytes + (k & 3) * 32;
-          const uint64_t b_k = make_smem_desc_sw128_mnmajor(sb + S::kK + k * 2048, kAtomBytes);
-          umma_f16_ss(tmem_s, make_smem_desc_sw128_kmajor(sb + S::kDS + aoff), b_k, idesc_dq, k != 0);
+          const uint32_t aoff = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
+          umma_f16_ss_p(tmem_s, smem_desc_join(ds_k + aoff), smem_desc_join(k_mn + k * (2048 >> 4)), idesc_dq, k != 0, lead);
         }
-        umma_commit(dq_full);      // the drain of dQ overlaps the two accumulating products below
+        umma_commit_p(dq_full, lead);      // the drain of dQ overlaps the two accumulating products below
         // dV += P^T dO ; dK += dS^T Q   (K dimension = the 128 q rows, 16 per instruction = 2048 bytes of a [row][128 B] atom)
+        const uint32_t acc0 = step != 0;
 #pragma unroll
-        for (int k = 0; k < kFbTile / 16; ++k) {
-          const uint64_t a_p = make_smem_desc_sw128_mnmajor(sb + S::kP + k * 2048, kAtomBytes);
-          const uint64_t b_do = make_smem_desc_sw128_mnmajor(sb + S::kDO + k * 2048, kAtomBytes);
-          umma_f16_ss(tmem_dv, a_p, b_do, idesc_acc, (step != 0) || (k != 0));
-        }
+        for (int k = 0; k < kFbTile / 16; ++k)
+          umma_f16_ss_p(tmem_dv, smem_desc_join(p_mn + k * (2048 >> 4)), smem_desc_join(do_mn + k * (2048 >> 4)), idesc_acc,
+                        k != 0 ? 1u : acc0, lead);
 #pragma unroll
-        for (int k = 0; k < kFbTile / 16; ++k) {
-          const uint64_t a_ds = make_smem_desc_sw128_mnmajor(sb + S::kDS + k * 2048, kAtomBytes);
-          const uint64_t b_q = make_smem_desc_sw128_mnmajor(sb + S::kQ + k * 2048, kAtomBytes);
-          umma_f16_ss(tmem_dk, a_ds, b_q, idesc_acc, (step != 0) || (k != 0));
-        }
-        umma_commit(qdo_empty);
-        umma_commit(pds_empty);
+        for (int k = 0; k < kFbTile / 16; ++k)
+          umma_f16_ss_p(tmem_dk, smem_desc_join(ds_mn + k * (2048 >> 4)), smem_desc_join(q_mn + k * (2048 >> 4)), idesc_acc,
+                        k != 0 ? 1u : acc0, lead);
+        umma_commit_p(qdo_empty, lead);
+        umma_commit_p(pds_empty, lead);
       }
-      if (ok) umma_commit(acc_full);
-      else record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 20, 0);
+      if (ok) umma_commit_p(acc_full, lead);
+      else if (lane == 0) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 20, 0);
     }
     __syncwarp();
   } else if (warp < 4) {
