@@ -221,6 +221,12 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* desc, uint32_t s
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+// Adds `bytes` of fp32 from shared memory into global memory (16-byte aligned on both sides, a multiple of 16 bytes): one
+// request to the TMA unit instead of bytes / 16 vector reductions issued by threads. Joins the thread's bulk group.
+__device__ __forceinline__ void bulk_reduce_add_f32(void* gdst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src), "r"(bytes)
+               : "memory");
+}
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");

@@ -47,7 +47,18 @@ struct FaBwdParams {
   float* dv_seg[16];
   uint32_t* status;
   uint64_t budget_ns;
+  long long* trace;     // optional: CTA (0,0,0) stamps clock64 at its hand-overs (see fb_trace)
 };
+
+// Device-side trace: a plain store into the slot of (role, step, event); roles 0 issuing warp, 1 P / dS warps (first warp),
+// 2 dQ drain warps (first warp). Layout: [3 roles][kFbTraceSteps][8 events] int64.
+constexpr int kFbTraceSteps = 160;
+__device__ __forceinline__ void fb_trace(const FaBwdParams& p, int role, int event, int step) {
+  if (p.trace == nullptr || blockIdx.x != 0 || blockIdx.y != 0 || blockIdx.z != 0 || step >= kFbTraceSteps) return;
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  p.trace[(role * kFbTraceSteps + step) * 8 + event] = t;
+}
 
 template <int D>
 struct FbSmem {
@@ -59,8 +70,14 @@ struct FbSmem {
   static constexpr int kDO = kQ + kTileBytes;
   static constexpr int kP = kDO + kTileBytes;
   static constexpr int kDS = kP + kPBytes;
-  static constexpr int kBars = kDS + kPBytes;
+  // dQ staging: half of a step's fp32 partial at a time ([128 rows][D / 2] with a row pitch of D * 2 + 16 bytes, which is
+  // conflict-free for threads that each write their own row). A buffer of its own, so that the reductions of step s run
+  // under the products and the P / dS computation of step s+1.
+  static constexpr int kDqPitch = D * 2 + 16;
+  static constexpr int kDqStage = kDS + kPBytes;
+  static constexpr int kBars = kDqStage + kFbTile * kDqPitch;
   static constexpr int kTotal = kBars + 256;
+  static_assert(kTotal <= 232448, "shared-memory plan exceeds the 227 KiB a CTA may use");
 };
 
 // delta[b,h,s] = sum_d dO * O ; lse2 = lse * log2(e). One warp per (token, head).
@@ -98,7 +115,7 @@ __device__ __forceinline__ int fb_q_pos(const pkb_attn_desc& d, int row) {
   return d.q_seg_pos[seg] + (row - seg * d.q_seg_rows);
 }
 
-template <int D>
+template <int D, bool TRACE = false>
 __global__ void __launch_bounds__(kFbThreads, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -267,10 +284,11 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.budget_ns);
       for (int step = 0; step < n_steps && ok; ++step) {
         const uint32_t ph = step & 1;
-        if (!mbar_wait(qdo_full, ph, abort_flag, p.budget_ns) || !mbar_wait(dq_empty, ph ^ 1u, abort_flag, p.budget_ns)) {
-          ok = false;
-          break;
-        }
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 0, step); }
+        if (!mbar_wait(qdo_full, ph, abort_flag, p.budget_ns)) { ok = false; break; }
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 1, step); }
+        if (!mbar_wait(dq_empty, ph ^ 1u, abort_flag, p.budget_ns)) { ok = false; break; }
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 2, step); }
         tc_fence_after_sync();
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
@@ -283,16 +301,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           umma_f16_ss_p(tmem_dp, smem_desc_join(do_k + off), smem_desc_join(v_k + off), idesc_s, k != 0, lead);
         }
         umma_commit_p(sdp_full, lead);
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 3, step); }
         if (!mbar_wait(pds_full, ph, abort_flag, p.budget_ns)) { ok = false; break; }
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 4, step); }
         tc_fence_after_sync();
-        // dQ partial = dS K_j  (K dimension = the 128 kv rows)
-#pragma unroll
-        for (int k = 0; k < kFbTile / 16; ++k) {
-          const uint32_t aoff = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
-          umma_f16_ss_p(tmem_s, smem_desc_join(ds_k + aoff), smem_desc_join(k_mn + k * (2048 >> 4)), idesc_dq, k != 0, lead);
-        }
-        umma_commit_p(dq_full, lead);      // the drain of dQ overlaps the two accumulating products below
         // dV += P^T dO ; dK += dS^T Q   (K dimension = the 128 q rows, 16 per instruction = 2048 bytes of a [row][128 B] atom)
+        // These are the last readers of the Q and dO tiles, so they go first: the load of the next step's Q and dO (one
+        // buffer each - shared memory is full) then runs under the dQ product and its drain instead of after them.
         const uint32_t acc0 = step != 0;
 #pragma unroll
         for (int k = 0; k < kFbTile / 16; ++k)
@@ -303,7 +318,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
           umma_f16_ss_p(tmem_dk, smem_desc_join(ds_mn + k * (2048 >> 4)), smem_desc_join(q_mn + k * (2048 >> 4)), idesc_acc,
                         k != 0 ? 1u : acc0, lead);
         umma_commit_p(qdo_empty, lead);
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 5, step); }
+        // dQ partial = dS K_j  (K dimension = the 128 kv rows), into the columns that held S
+#pragma unroll
+        for (int k = 0; k < kFbTile / 16; ++k) {
+          const uint32_t aoff = ((k >> 2) * kAtomBytes + (k & 3) * 32) >> 4;
+          umma_f16_ss_p(tmem_s, smem_desc_join(ds_k + aoff), smem_desc_join(k_mn + k * (2048 >> 4)), idesc_dq, k != 0, lead);
+        }
+        umma_commit_p(dq_full, lead);
         umma_commit_p(pds_empty, lead);
+        if constexpr (TRACE) { if (lane == 0) fb_trace(p, 0, 6, step); }
       }
       if (ok) umma_commit_p(acc_full, lead);
       else if (lane == 0) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 20, 0);
@@ -329,10 +353,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
       const float lse2 = row_ok ? p.lse2[sidx] : 0.f;
       const float delta = row_ok ? p.delta[sidx] : 0.f;
       const bool row_dead = !row_ok || lse2 == -INFINITY;
+      const bool need_mask = row_dead || kv_valid < kFbTile || (d.causal && kv_pos0 + kFbTile - 1 > my_pos);
+      if constexpr (TRACE) { if (warp == 4 && lane == 0) fb_trace(p, 1, 0, step); }
       ok = mbar_wait(sdp_full, ph, abort_flag, p.budget_ns);
+      if constexpr (TRACE) { if (warp == 4 && lane == 0) fb_trace(p, 1, 1, step); }
       if (ok && step > 0) ok = mbar_wait(pds_empty, ph ^ 1u, abort_flag, p.budget_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if constexpr (TRACE) { if (warp == 4 && lane == 0) fb_trace(p, 1, 2, step); }
       tc_fence_after_sync();
       const uint32_t lane_off = static_cast<uint32_t>(q4 * 32) << 16;
       const uint32_t prow = sb + S::kP + static_cast<uint32_t>(row) * 128u;
@@ -345,13 +373,22 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tmem_ld_32x32(tmem_dp + lane_off + c * 32, rd);
         tmem_ld_wait();
         float pv[32], dsv[32];
+        if (!need_mask) {                 // the whole row of this tile is visible: no per-element tests
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 32 + i;
-          const bool masked = row_dead || col >= kv_valid || (d.causal && kv_pos0 + col > my_pos);
-          const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[i]), scale2, -lse2));
-          pv[i] = pe;
-          dsv[i] = pe * (__uint_as_float(rd[i]) - delta) * d.scale;
+          for (int i = 0; i < 32; ++i) {
+            const float pe = fast_exp2(fmaf(__uint_as_float(rs[i]), scale2, -lse2));
+            pv[i] = pe;
+            dsv[i] = pe * (__uint_as_float(rd[i]) - delta) * d.scale;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            const bool masked = row_dead || col >= kv_valid || (d.causal && kv_pos0 + col > my_pos);
+            const float pe = masked ? 0.f : fast_exp2(fmaf(__uint_as_float(rs[i]), scale2, -lse2));
+            pv[i] = pe;
+            dsv[i] = pe * (__uint_as_float(rd[i]) - delta) * d.scale;
+          }
         }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -368,10 +405,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                        : "memory");
         }
       }
+      if constexpr (TRACE) { if (warp == 4 && lane == 0) fb_trace(p, 1, 3, step); }
       tc_fence_before_sync();
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
+      if constexpr (TRACE) { if (warp == 4 && lane == 0) fb_trace(p, 1, 4, step); }
     }
     if (!ok && lane == 0) record_status(p.status, kStatusMbarTimeout, 650, 0, 0, 30, 0);
   } else {
@@ -385,28 +424,49 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     for (int step = 0; step < n_steps && ok; ++step) {
       int head, qt;
       step_coords(step, head, qt);
+      if constexpr (TRACE) { if (warp == 12 && lane == 0) fb_trace(p, 2, 0, step); }
       ok = mbar_wait(dq_full, step & 1, abort_flag, p.budget_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      if constexpr (TRACE) { if (warp == 12 && lane == 0) fb_trace(p, 2, 1, step); }
       tc_fence_after_sync();
       const int q_row = qt * kFbTile + row;
       float* dst = p.dq + ((static_cast<long long>(batch) * d.sq + q_row) * d.hq + head) * D + col0;
+      // The partial goes to the fp32 dQ in global memory as two bulk reductions per row (one per half of the head dimension,
+      // staged in shared memory) instead of 32 vector reductions per thread, which took 4100 of a step's 11000 cycles and sat
+      // between two steps' products. Tensor memory is released as soon as both halves have been read: the second half waits
+      // in registers while the TMA unit reads the first out of the staging buffer.
+      const uint32_t stage_row = sb + S::kDqStage + static_cast<uint32_t>(row) * S::kDqPitch;
+      constexpr int HC = DH / 2;             // columns per half
+      auto stage_half = [&](const uint32_t (&r)[HC]) {
 #pragma unroll
-      for (int c = 0; c < DH / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_s + lane_off + col0 + c * 32, r);
-        tmem_ld_wait();
-        if (q_row < d.sq) {
+        for (int i = 0; i < HC; i += 4)
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + i * 4), "r"(r[i]), "r"(r[i + 1]), "r"(r[i + 2]), "r"(r[i + 3])
+                       : "memory");
+        fence_proxy_async_smem();            // this thread's row is visible to the TMA unit
+        return 0;
+      };
+      uint32_t r0[HC], r1[HC];
 #pragma unroll
-          for (int i = 0; i < 32; i += 4)
-            red_add_v4_f32(dst + c * 32 + i, __uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]),
-                           __uint_as_float(r[i + 3]));
-        }
-      }
+      for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tmem_s + lane_off + c * 32, *reinterpret_cast<uint32_t (*)[32]>(&r0[c * 32]));
+      tmem_ld_wait();
+      tma_store_wait_read<0>();              // the previous step's second half has left the staging buffer
+      stage_half(r0);
+#pragma unroll
+      for (int c = 0; c < HC / 32; ++c) tmem_ld_32x32(tmem_s + lane_off + HC + c * 32, *reinterpret_cast<uint32_t (*)[32]>(&r1[c * 32]));
+      tmem_ld_wait();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(dq_empty);
+      if (q_row < d.sq) bulk_reduce_add_f32(dst, stage_row, HC * 4);
+      tma_store_commit();
+      tma_store_wait_read<0>();
+      stage_half(r1);
+      if (q_row < d.sq) bulk_reduce_add_f32(dst + HC, stage_row, HC * 4);
+      tma_store_commit();
+      if constexpr (TRACE) { if (warp == 12 && lane == 0) fb_trace(p, 2, 2, step); }
     }
+    tma_store_wait_all<0>();               // every bulk reduction of this thread has been performed
     if (ok && n_steps > 0) {
       ok = mbar_wait(acc_full, 0, abort_flag, p.budget_ns);
       ok = __all_sync(0xffffffffu, ok);
@@ -469,6 +529,9 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
   }
 }
 
+// Trace buffer of the next backward launches (device memory, 3 * kFbTraceSteps * 8 int64, zeroed by the caller); null = off.
+static long long* g_fb_trace = nullptr;
+
 template <int D>
 static int launch_fa_bwd(const pkb_attn_desc& d, const void* q, const void* k, const void* v, const void* o, const void* dout,
                          const void* lse, void* delta, void* lse2, void* dq, void* dk, void* dv, cudaStream_t stream,
@@ -506,8 +569,9 @@ static int launch_fa_bwd(const pkb_attn_desc& d, const void* q, const void* k, c
     p.dv_seg[sg] = p.seg_scatter && sg < d.num_kv_segs ? reinterpret_cast<float*>(dv_seg[sg]) : nullptr;
   }
   p.status = status_block_device_ptr();
+  p.trace = g_fb_trace;
   p.budget_ns = d.budget_ns ? d.budget_ns : kDefaultWaitBudgetNs;
-  auto kern = fa_bwd_kernel<D>;
+  auto kern = g_fb_trace != nullptr ? fa_bwd_kernel<D, true> : fa_bwd_kernel<D, false>;
   constexpr int smem = FbSmem<D>::kTotal;
   PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   int kv_tiles = 0;
@@ -566,3 +630,7 @@ extern "C" int pkb_flash_attn_bwd_scatter(const pkb_attn_desc* desc, const void*
   return launch_fa_bwd<64>(d, q, k, v, o, dout, lse, delta_scratch, lse2_scratch, dq, nullptr, nullptr, s, dk_seg, dv_seg);
 }
 
+extern "C" int pkb_flash_attn_bwd_set_trace(void* dev_words) {
+  pkb::g_fb_trace = static_cast<long long*>(dev_words);
+  return pkb::kApiOk;
+}

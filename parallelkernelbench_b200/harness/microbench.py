@@ -211,6 +211,44 @@ def case_fa_trace(t: _Timer) -> dict:
     return out
 
 
+def case_fa_bwd_trace(t: _Timer) -> dict:
+    """Device-side timeline of the attention backward's heaviest CTA (the first KV tile, which every query tile sees): medians
+    of the intervals between consecutive stamps of each role over the steady steps, in SM cycles. Roles: 0 issuing warp
+    (0 step start, 1 Q/dO landed, 2 dQ drained, 3 S and dP issued, 4 P and dS in shared memory, 5 dV and dK issued, 6 dQ issued),
+    1 P / dS warps (0 start, 1 S and dP complete, 2 previous P/dS consumed, 3 computed, 4 published), 2 dQ drain warps
+    (0 start, 1 dQ complete, 2 drained)."""
+    from .. import _native as nv
+    from ..ops.attention import flash_attn_bwd, flash_attn_fwd
+
+    q, k, v, do = _attn_inputs(16384)
+    out, lse = flash_attn_fwd(q, k, v, causal=True)
+    flash_attn_bwd(q, k, v, out, lse, do, causal=True)
+    steps_cap = 160
+    trace = torch.zeros(3 * steps_cap * 8, dtype=torch.int64, device="cuda")
+    nv.check(nv.cuda_lib().pkb_flash_attn_bwd_set_trace(nv.ptr(trace)), "pkb_flash_attn_bwd_set_trace")
+    try:
+        flash_attn_bwd(q, k, v, out, lse, do, causal=True)
+        torch.cuda.synchronize()
+    finally:
+        nv.check(nv.cuda_lib().pkb_flash_attn_bwd_set_trace(None), "pkb_flash_attn_bwd_set_trace")
+    slots = trace.view(3, steps_cap, 8).cpu().tolist()
+    res: dict = {"case": "fa_bwd_trace"}
+    med = lambda xs: sorted(xs)[len(xs) // 2] if xs else None  # noqa: E731
+    for role in range(3):
+        steps = {i: {e: c for e, c in enumerate(slots[role][i]) if c} for i in range(steps_cap)}
+        steady = [i for i in range(8, 100) if steps[i] and steps.get(i + 1)]
+        if not steady:
+            continue
+        ref = steady[len(steady) // 2]
+        evs = sorted(steps[ref], key=lambda e: steps[ref][e])
+        row = {"period": med([steps[i + 1][evs[0]] - steps[i][evs[0]] for i in steady if evs[0] in steps[i] and evs[0] in steps[i + 1]])}
+        for a, b in zip(evs, evs[1:]):
+            row[f"e{a}->e{b}"] = med([steps[i][b] - steps[i][a] for i in steady if a in steps[i] and b in steps[i]])
+        row[f"e{evs[-1]}->next e{evs[0]}"] = med([steps[i + 1][evs[0]] - steps[i][evs[-1]] for i in steady if evs[-1] in steps[i] and evs[0] in steps[i + 1]])
+        res[f"role{role}"] = row
+    return res
+
+
 def case_fa_bwd(t: _Timer) -> dict:
     import torch.nn.functional as F
 
