@@ -674,6 +674,35 @@ __device__ __forceinline__ float poly_exp2(float x) {
   const float pl = fmaf(fmaf(fmaf(0.077119089663028717f, f, 0.227564394474029541f), f, 0.695146143436431884f), f, 1.0f);
   return __int_as_float(__float_as_int(pl) + (__float_as_int(xr) << 23));
 }
+// Two 2^x at once on the FMA and integer pipes, packed fp32 arithmetic for the range reduction and the polynomial (see
+// poly_exp2 for the method): 2 clamps, 6 packed operations and 2 integer multiply-adds per pair, against 2 special-function
+// instructions of about 12 pipe cycles each.
+__device__ __forceinline__ void poly_exp2_x2(float& e0, float& e1, float x0, float x1) {
+  x0 = fmaxf(x0, -126.f);
+  x1 = fmaxf(x1, -126.f);
+  uint32_t p0, p1, r0, r1;
+  asm("{\n\t.reg .b64 x, xr, n, f, p, magic, nmagic, mone, c1, c2, c3, one;\n\t"
+      "mov.b64 x, {%4, %5};\n\t"
+      "mov.b64 magic, {0f4B400000, 0f4B400000};\n\t"      // 1.5 * 2^23
+      "mov.b64 nmagic, {0fCB400000, 0fCB400000};\n\t"
+      "mov.b64 mone, {0fBF800000, 0fBF800000};\n\t"
+      "mov.b64 one, {0f3F800000, 0f3F800000};\n\t"
+      "mov.b64 c3, {0f3D9DF09D, 0f3D9DF09D};\n\t"         // 0.0771190897
+      "mov.b64 c2, {0f3E6906A4, 0f3E6906A4};\n\t"         // 0.2275643945
+      "mov.b64 c1, {0f3F31F519, 0f3F31F519};\n\t"         // 0.6951461434
+      "add.rm.ftz.f32x2 xr, x, magic;\n\t"                 // low mantissa bits of xr = floor(x)
+      "add.rn.ftz.f32x2 n, xr, nmagic;\n\t"                // floor(x) as a float
+      "fma.rn.ftz.f32x2 f, n, mone, x;\n\t"                // fraction in [0, 1)
+      "fma.rn.ftz.f32x2 p, c3, f, c2;\n\t"
+      "fma.rn.ftz.f32x2 p, p, f, c1;\n\t"
+      "fma.rn.ftz.f32x2 p, p, f, one;\n\t"
+      "mov.b64 {%0, %1}, p;\n\t"
+      "mov.b64 {%2, %3}, xr;\n\t}"
+      : "=r"(p0), "=r"(p1), "=r"(r0), "=r"(r1)
+      : "f"(x0), "f"(x1));
+  e0 = __uint_as_float(p0 + (r0 << 23));                  // the integer part goes into the exponent field
+  e1 = __uint_as_float(p1 + (r1 << 23));
+}
 // Packed fp32 arithmetic of sm_100 (two lanes per instruction) and the three-input maximum: they halve the issue slots of the
 // scale / subtract, row-sum and row-maximum steps of a softmax.
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -687,6 +716,13 @@ __device__ __forceinline__ void fma2_bcast(float& d0, float& d1, float a0, float
       "fma.rn.ftz.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
       : "=f"(d0), "=f"(d1)
       : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+// (d0, d1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void mul2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.ftz.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d0), "=f"(d1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 // (d0, d1) += (a0, a1)
 __device__ __forceinline__ void add2_acc(float& d0, float& d1, float a0, float a1) {

@@ -1009,7 +1009,8 @@ constexpr int kFa3RegsIo = 80, kFa3RegsSoftmax = 168, kFa3RegsCorr = 80;
 static_assert(128 * kFa3RegsIo + 256 * kFa3RegsSoftmax + 128 * kFa3RegsCorr <= 65536, "register budgets exceed the register file");
 
 // OPT bit 0: three-input maxima and packed fp32 pairs for scale / subtract and the row sum; bit 1: every fourth pair of
-// exponentials of an unmasked tile on the FMA pipe (polynomial) instead of the special-function unit; bit 2: P packed to
+// exponentials of an unmasked tile on the FMA pipe (packed polynomial, poly_exp2_x2) instead of the special-function unit,
+// bit 3: every second pair; bit 2: P packed to
 // bf16 on the integer pipe (pack_bf16x2_alu) - the conversion instruction shares the special-function pipe with the
 // exponentials, and the trace of a softmax step showed that pipe saturated: (128 ex2 + 64 conversions) x 8 cycles = the
 // 1540 cycles the exponential loop took.
@@ -1297,7 +1298,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         // exponentials, packed to bf16 pairs and written over the first 64 score columns, 64 keys at a time (the packed words
         // of one half are stored while the next half is computed, and fewer registers are live than with the whole row)
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-        const bool poly_ok = (OPT & 2) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
+        const bool poly_ok = (OPT & 10) && !need_mask && !dead;      // masked tiles need the exact zero of ex2(-inf)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           uint32_t w[32];
@@ -1312,9 +1313,8 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
               x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale2, neg_m);
             }
             float e0, e1;
-            if ((OPT & 2) && (i & 3) == 3 && poly_ok) {
-              e0 = poly_exp2(x0);
-              e1 = poly_exp2(x1);
+            if ((((OPT & 2) && (i & 3) == 3) || ((OPT & 8) && (i & 1) == 1)) && poly_ok) {
+              poly_exp2_x2(e0, e1, x0, x1);
             } else {
               e0 = fast_exp2(x0);
               e1 = fast_exp2(x1);
@@ -2063,7 +2063,7 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     // PKB_FA_OPT=0..3 selects the softmax arithmetic variant (bit 0: packed pairs and three-input maxima, bit 1: polynomial)
-    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '7') ? e[0] - '0' : kFa3DefaultOpt; }();
+    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '9') ? e[0] - '0' : kFa3DefaultOpt; }();
 #define PKB_FA3(O)                                                                                   \
     {                                                                                                \
       auto kern = fa_fwd3_kernel<D, O>;                                                              \
@@ -2076,6 +2076,7 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
       case 3: PKB_FA3(3) break;
       case 5: PKB_FA3(5) break;
       case 7: PKB_FA3(7) break;
+      case 9: PKB_FA3(9) break;
       default: PKB_FA3(0) break;
     }
 #undef PKB_FA3

@@ -373,12 +373,16 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         tmem_ld_32x32(tmem_dp + lane_off + c * 32, rd);
         tmem_ld_wait();
         float pv[32], dsv[32];
-        if (!need_mask) {                 // the whole row of this tile is visible: no per-element tests
+        if (!need_mask) {                 // the whole row of this tile is visible: no per-element tests, packed fp32 pairs
+          const float neg_lse2 = -lse2, neg_ds = -delta * d.scale;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float pe = fast_exp2(fmaf(__uint_as_float(rs[i]), scale2, -lse2));
-            pv[i] = pe;
-            dsv[i] = pe * (__uint_as_float(rd[i]) - delta) * d.scale;
+          for (int i = 0; i < 32; i += 2) {
+            float x0, x1, t0, t1;
+            fma2_bcast(x0, x1, __uint_as_float(rs[i]), __uint_as_float(rs[i + 1]), scale2, neg_lse2);
+            fma2_bcast(t0, t1, __uint_as_float(rd[i]), __uint_as_float(rd[i + 1]), d.scale, neg_ds);   // (dP - delta) * scale
+            pv[i] = fast_exp2(x0);
+            pv[i + 1] = fast_exp2(x1);
+            mul2(dsv[i], dsv[i + 1], pv[i], pv[i + 1], t0, t1);
           }
         } else {
 #pragma unroll

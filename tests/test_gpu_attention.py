@@ -119,7 +119,7 @@ def test_flash_attention_backward_zigzag_segments():
         assert err <= 2e-2 * max(ref.abs().max().item(), 1.0), f"{name}: {err}"
 
 
-@pytest.mark.parametrize("variant", ["PKB_FA_V3=0", "PKB_FA_V4=1", "PKB_FA_V4=1,PKB_FA_POLY=0", "PKB_FA_OPT=1", "PKB_FA_OPT=7"])
+@pytest.mark.parametrize("variant", ["PKB_FA_V3=0", "PKB_FA_V4=1", "PKB_FA_V4=1,PKB_FA_POLY=0", "PKB_FA_OPT=3", "PKB_FA_OPT=5", "PKB_FA_OPT=9"])
 def test_forward_variants_pass_the_same_checks(variant):
     """The forward kernel variants are selected by an environment variable that is read once per process, so the forward
     checks of this file are repeated in a child process with the variable set."""
