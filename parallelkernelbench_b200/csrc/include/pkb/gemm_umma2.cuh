@@ -31,8 +31,11 @@ struct alignas(64) GemmOutMaps {
 // A_MN / B_MN: the operand is given MN-major ([K, M] resp. [K, N] row-major, the layouts of dX = dY W and dW = dY^T X): a CTA's
 // 128 rows (columns) of it arrive as two 64 x 64 boxes (one 128-byte-swizzle atom each, 8 KiB apart) and are described to the
 // tensor core as MN-major; 16 along K is then 16 shared-memory rows = 2048 bytes.
+// GROUPED: A is a stack of row groups (p.grp_offsets, device memory) and group e multiplies with rows [e * N, (e + 1) * N) of B
+// (one weight matrix per group, e.g. the experts of a MoE layer): tiles are (group, 256-row block of the group, n block), rows
+// of a tile beyond the group's end are computed and not stored. Register epilogue only.
 template <int EPI, bool OUT_F32, bool A_READY, bool RS_SCATTER, bool TMA_STORE = false, bool BCAST = false, bool A_MN = false,
-          bool B_MN = false>
+          bool B_MN = false, bool GROUPED = false>
 __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
                                                const GemmParams& p, const int pair,
                                                const int num_pairs,
@@ -41,6 +44,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
   static_assert(!(TMA_STORE && OUT_F32), "the TMA-store epilogue writes bf16");
   static_assert(!BCAST || (TMA_STORE && !RS_SCATTER), "the broadcast epilogue is a TMA-store epilogue");
   static_assert(!(A_MN && A_READY), "the gathered-A hook loads A K-major");
+  static_assert(!GROUPED || (!TMA_STORE && !RS_SCATTER && !A_READY && !A_MN && !B_MN && !OUT_F32), "the grouped form is K-major, bf16, register epilogue");
   constexpr int kStages = kGemm2Stages;
   constexpr int BN = kGemm2TileN;
   constexpr uint32_t kTmemCols = 512;
@@ -65,8 +69,35 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
 
   const int num_m = (p.M + kGemm2TileM - 1) / kGemm2TileM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
   const int num_k = (p.K + kGemmBlockK - 1) / kGemmBlockK;
+  // grouped form: prefix sums of the groups' 256-row tile counts, built once per CTA from the device-side offsets
+  __shared__ int s_tile_prefix[GROUPED ? kGemmMaxGroups + 1 : 1];
+  if constexpr (GROUPED) {
+    for (int e = threadIdx.x; e < p.grp_count; e += blockDim.x) {
+      const int cnt = p.grp_offsets[e + 1] - p.grp_offsets[e];
+      s_tile_prefix[e + 1] = (cnt + kGemm2TileM - 1) / kGemm2TileM;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      s_tile_prefix[0] = 0;
+      for (int e = 0; e < p.grp_count; ++e) s_tile_prefix[e + 1] += s_tile_prefix[e];
+    }
+    __syncthreads();
+  }
+  const int num_tiles = GROUPED ? s_tile_prefix[p.grp_count] * num_n : num_m * num_n;
+  // grouped: tile -> first row of the pair's 256-row block, the group's row limit, first row of B, n block (n fastest)
+  auto tile_rows = [&](int tile, int& row0, int& row_end, int& b_row0, int& n_blk) {
+    const int mi = tile / num_n;
+    n_blk = tile - mi * num_n;
+    int lo = 0, hi = p.grp_count;  // find e with prefix[e] <= mi < prefix[e+1]
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (s_tile_prefix[mid] <= mi) lo = mid; else hi = mid;
+    }
+    row0 = p.grp_offsets[lo] + (mi - s_tile_prefix[lo]) * kGemm2TileM;
+    row_end = p.grp_offsets[lo + 1];
+    b_row0 = lo * p.N + n_blk * BN;
+  };
   const int group_m = p.group_m > 0 ? p.group_m : 8;
 
   auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
@@ -114,10 +145,11 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
       bool ok = true;
       long long waited = 0;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        int m_blk, n_blk;
-        tile_coords(tile, m_blk, n_blk);
-        const int row0 = m_blk * kGemm2TileM + (int)cta_rank * 128;
-        const int col0 = n_blk * BN + (int)cta_rank * 128;
+        int m_blk = 0, n_blk = 0, g_row0 = 0, g_row_end = 0, g_b_row0 = 0;
+        if constexpr (GROUPED) tile_rows(tile, g_row0, g_row_end, g_b_row0, n_blk);
+        else tile_coords(tile, m_blk, n_blk);
+        const int row0 = (GROUPED ? g_row0 : m_blk * kGemm2TileM) + (int)cta_rank * 128;
+        const int col0 = (GROUPED ? g_b_row0 : n_blk * BN) + (int)cta_rank * 128;   // this CTA's 128 rows of B
         const CUtensorMap* map_a = &tmap_a;
         int a_row = row0;
         bool a_is_local = false;
@@ -233,8 +265,9 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
     const uint32_t leader_tempty0 = mapa_shared(tempty_bar(0), 0);
     const uint32_t leader_tempty1 = mapa_shared(tempty_bar(1), 0);
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
-      int m_blk, n_blk;
-      tile_coords(tile, m_blk, n_blk);
+      int m_blk = 0, n_blk = 0, g_row0 = 0, g_row_end = 0, g_b_row0 = 0;
+      if constexpr (GROUPED) tile_rows(tile, g_row0, g_row_end, g_b_row0, n_blk);
+      else tile_coords(tile, m_blk, n_blk);
       bool ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.wait_budget_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
@@ -243,7 +276,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
         break;
       }
       tc_fence_after_sync();
-      const int row_blk0 = m_blk * kGemm2TileM + (int)cta_rank * 128;
+      const int row_blk0 = (GROUPED ? g_row0 : m_blk * kGemm2TileM) + (int)cta_rank * 128;
       const int row = row_blk0 + q * 32 + lane;
       const int n0 = n_blk * BN;
       uint8_t* out_row;
@@ -332,7 +365,7 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
           }
         }
       } else {
-      const bool row_ok = row < p.M;
+      const bool row_ok = row < (GROUPED ? g_row_end : p.M);
   #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -354,7 +387,20 @@ __device__ __forceinline__ void gemm_umma2_cta(const CUtensorMap& tmap_a, const 
   #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = silu_f(v[j]);
             }
-            if constexpr (OUT_F32) {
+            if constexpr (EPI == kEpiSwiGLU) {
+              // accumulator columns come in (gate, up) pairs: 32 of them give 16 outputs at column col0 / 2
+              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out_row) + (col0 >> 1);
+              float h[16];
+  #pragma unroll
+              for (int j = 0; j < 16; ++j) h[j] = silu_f(v[2 * j]) * v[2 * j + 1];
+              if (col0 + 32 <= p.N && (p.ldc & 7) == 0) {
+                st_global_v4(o, U4{pack_bf16x2(h[0], h[1]), pack_bf16x2(h[2], h[3]), pack_bf16x2(h[4], h[5]), pack_bf16x2(h[6], h[7])});
+                st_global_v4(o + 8, U4{pack_bf16x2(h[8], h[9]), pack_bf16x2(h[10], h[11]), pack_bf16x2(h[12], h[13]), pack_bf16x2(h[14], h[15])});
+              } else {
+                for (int j = 0; j < 16; ++j)
+                  if (col0 + 2 * j + 1 < p.N) o[j] = __float2bfloat16_rn(h[j]);
+              }
+            } else if constexpr (OUT_F32) {
               float* o = reinterpret_cast<float*>(out_row) + col0;
               if (col0 + 32 <= p.N && (p.ldc & 3) == 0) {
   #pragma unroll
@@ -442,6 +488,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_umma2_mn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   gemm_umma2_cta<EPI, OUT_F32, false, false, false, false, A_MN, B_MN>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1);
+}
+
+// grouped form (see gemm_umma2_cta): one weight matrix per row group, register epilogue
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_umma2_grouped_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  gemm_umma2_cta<EPI, false, false, false, false, false, false, false, true>(tmap_a, tmap_b, p, blockIdx.x >> 1, gridDim.x >> 1);
 }
 
 // bf16 output through the TMA-store epilogue

@@ -105,21 +105,42 @@ __global__ void __launch_bounds__(256) fp8_quant_kernel(const T* __restrict__ x,
   }
 }
 
+// A thread owns 16 consecutive e4m3 values (one 16-byte load, 32 or 64 bytes out as 16-byte stores); 8 threads share a block's
+// scale. `valid_rows` (device, may be null): rows at and beyond *valid_rows of a [rows, blocks_per_row * 128] buffer are left
+// alone - a receive buffer sized for the worst case is only dequantised as far as it was filled.
 template <typename T>
-__global__ void fp8_dequant_kernel(const uint8_t* __restrict__ y, const float* __restrict__ scales,
-                                   T* __restrict__ x, long long nblocks) {
-  const int lane = threadIdx.x & 31;
-  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long b = warp; b < nblocks; b += nwarps) {
-    const uint32_t packed = reinterpret_cast<const uint32_t*>(y + b * 128)[lane];
-    const float s = scales[b];
-    __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed & 0xffffu), __NV_E4M3);
-    __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(packed >> 16), __NV_E4M3);
-    float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
-    float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
-    T* o = x + b * 128 + lane * 4;
-    o[0] = (T)(f0.x * s); o[1] = (T)(f0.y * s); o[2] = (T)(f1.x * s); o[3] = (T)(f1.y * s);
+__global__ void __launch_bounds__(256) fp8_dequant_kernel(const uint8_t* __restrict__ y, const float* __restrict__ scales,
+                                                          T* __restrict__ x, long long nblocks, const int* __restrict__ valid_rows,
+                                                          long long blocks_per_row) {
+  long long nb = nblocks;
+  if (valid_rows != nullptr) {
+    const long long lim = (long long)(*valid_rows) * blocks_per_row;
+    if (lim < nb) nb = lim;
+  }
+  const long long nthr = nb * 8;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < nthr; t += (long long)gridDim.x * blockDim.x) {
+    const U4 u = ld_global_nc_v4(y + (t << 4));
+    const float sc = scales[t >> 3];
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+    float v[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] & 0xffffu), __NV_E4M3);
+      __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[j] >> 16), __NV_E4M3);
+      const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
+      const float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+      v[4 * j] = f0.x * sc; v[4 * j + 1] = f0.y * sc; v[4 * j + 2] = f1.x * sc; v[4 * j + 3] = f1.y * sc;
+    }
+    T* o = x + (t << 4);
+    if constexpr (sizeof(T) == 2) {
+      st_global_v4(o, U4{pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7])});
+      st_global_v4(o + 8, U4{pack_bf16x2(v[8], v[9]), pack_bf16x2(v[10], v[11]), pack_bf16x2(v[12], v[13]), pack_bf16x2(v[14], v[15])});
+    } else {
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        st_global_v4(o + 4 * q, U4{__float_as_uint(v[4 * q]), __float_as_uint(v[4 * q + 1]), __float_as_uint(v[4 * q + 2]),
+                                   __float_as_uint(v[4 * q + 3])});
+    }
   }
 }
 
@@ -347,20 +368,33 @@ int pkb_fp8_quant_1x128(const void* x, void* y, void* scales, long long n, int d
   return kApiOk;
 }
 
-int pkb_fp8_dequant_1x128(const void* y, const void* scales, void* x, long long n, int dtype, void* stream) {
+static int launch_fp8_dequant(const void* y, const void* scales, void* x, long long n, int dtype, const int* valid_rows,
+                              long long blocks_per_row, void* stream) {
   PKB_CHECK_ARG(n % 128 == 0, "element count must be a multiple of 128");
+  PKB_CHECK_ARG((((uintptr_t)y | (uintptr_t)x) & 15) == 0, "buffers must be 16-byte aligned");
   if (n == 0) return kApiOk;
   const long long nb = n / 128;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = grid_1d(nb * 32, 256);
+  const int grid = grid_1d(nb * 8, 256);
   if (dtype == 0)
     fp8_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(y), static_cast<const float*>(scales),
-                                                          static_cast<__nv_bfloat16*>(x), nb);
+                                                          static_cast<__nv_bfloat16*>(x), nb, valid_rows, blocks_per_row);
   else
     fp8_dequant_kernel<float><<<grid, 256, 0, s>>>(static_cast<const uint8_t*>(y), static_cast<const float*>(scales),
-                                                  static_cast<float*>(x), nb);
+                                                  static_cast<float*>(x), nb, valid_rows, blocks_per_row);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
+}
+
+int pkb_fp8_dequant_1x128(const void* y, const void* scales, void* x, long long n, int dtype, void* stream) {
+  return launch_fp8_dequant(y, scales, x, n, dtype, nullptr, 0, stream);
+}
+
+// The same for a [rows, cols] buffer of which only the first *valid_rows rows (an int32 in device memory) hold data.
+int pkb_fp8_dequant_1x128_rows(const void* y, const void* scales, void* x, long long rows, long long cols, int dtype,
+                               const void* valid_rows, void* stream) {
+  PKB_CHECK_ARG(cols % 128 == 0 && valid_rows != nullptr, "cols must be a multiple of 128 and valid_rows given");
+  return launch_fp8_dequant(y, scales, x, rows * cols, dtype, static_cast<const int*>(valid_rows), cols / 128, stream);
 }
 
 int pkb_adam(void* p, void* m, void* v, const void* g, void* p_bf16, long long n, int grad_dtype, float lr,

@@ -219,8 +219,30 @@ extern "C" int pkb_gemm_bf16_grouped(const void* a, long long lda, const void* b
   p.world = 1;
   p.grp_offsets = static_cast<const int*>(offsets);
   p.grp_count = groups;
-  const int ctas = sm_count();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // CTA pairs (256 x 256 tiles over two SMs, half of the B traffic per SM) when the shape allows; PKB_GROUPED_PAIR=0 keeps
+  // the one-CTA-per-tile kernel
+  static const bool pair_on = [] { const char* e = getenv("PKB_GROUPED_PAIR"); return !(e != nullptr && e[0] == '0'); }();
+  if (pair_on && block_n == 256 && N % 256 == 0 && K % kGemmBlockK == 0 && sm_count() >= 2) {
+    CUtensorMap tb2;
+    rc = encode_tmap_2d(&tb2, kTmapBf16, b, (uint64_t)K, (uint64_t)groups * N, (uint64_t)ldb * 2, kGemmBlockK, 128, kSwizzle128);
+    if (rc) return rc;
+    p.kernel_id = 107;
+    const int num_ctas = sm_count() & ~1;
+#define PKB_GROUPED_PAIR_LAUNCH(EPI)                                                                             \
+    {                                                                                                             \
+      auto kern = gemm_umma2_grouped_kernel<EPI>;                                                                 \
+      PKB_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemm2SmemTotal));   \
+      kern<<<num_ctas, kGemmThreads, kGemm2SmemTotal, s>>>(ta, tb2, p);                                           \
+    }
+    if (epilogue == kEpiNone) PKB_GROUPED_PAIR_LAUNCH(kEpiNone)
+    else if (epilogue == kEpiSilu) PKB_GROUPED_PAIR_LAUNCH(kEpiSilu)
+    else PKB_GROUPED_PAIR_LAUNCH(kEpiSwiGLU)
+#undef PKB_GROUPED_PAIR_LAUNCH
+    PKB_CHECK_CUDA(cudaGetLastError());
+    return kApiOk;
+  }
+  const int ctas = sm_count();
 #define PKB_GROUPED(BN, EPI)                                                                        \
   {                                                                                                 \
     auto kern = gemm_umma_grouped_kernel<BN, EPI>;                                                  \

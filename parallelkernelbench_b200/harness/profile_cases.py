@@ -4,7 +4,7 @@
 
 Each case allocates a few hundred MB at most (inputs larger than L2 where DRAM figures matter),
 launches the kernel a handful of times and exits, so a capture of one launch ends by itself.
-Cases: gemm_pair, gemm_single, tp_mlp, fa_fwd, fa_fwd_d64, fa_bwd, grouped_gemm, grouped_gemm_fp8, rmsnorm, allreduce,
+Cases: gemm_pair, gemm_single, tp_mlp, moe_layer, fa_fwd, fa_fwd_d64, fa_bwd, grouped_gemm, grouped_gemm_fp8, rmsnorm, allreduce,
 fsdp_adamw, moe_exchange, gsplat, delta_scan, llama_step, llama_step_8l.
 """
 from __future__ import annotations
@@ -153,6 +153,34 @@ def case_moe_exchange(iters):
     wg = torch.randn(32, 512, 2048, device=dev, dtype=torch.bfloat16) * 0.02
     wu = torch.randn(32, 512, 2048, device=dev, dtype=torch.bfloat16) * 0.02
     wd = torch.randn(32, 2048, 512, device=dev, dtype=torch.bfloat16) * 0.02
+    comm = Comm(ctx)
+    layer = EPMoELayer(comm.group(), comm, cfg, w_router, wg, wu, wd)
+    x = torch.randn(cfg.tokens_per_rank, cfg.hidden, device=dev, dtype=torch.bfloat16)
+    for _ in range(iters):
+        layer(x)
+    torch.cuda.synchronize()
+    ctx.finalize()
+
+
+def case_moe_layer(iters):
+    """The whole expert-parallel layer at one rank with the per-rank work of the 8-rank headline configuration: 8192 tokens x
+    7168, 32 local experts, top-8 (65536 expert rows of 2048 per expert), fp8 dispatch, bf16 experts; PKB_MOE_FP8_EXPERTS=1
+    selects the block-scaled fp8 experts."""
+    import os
+
+    from ..models.moe_layer import EPMoELayer, MoEConfig
+    from ..parallel import init_context
+    from ..parallel.comm import Comm
+
+    ctx = init_context()
+    dev = ctx.device
+    E, H, I = 32, 7168, 2048
+    cfg = MoEConfig(hidden=H, inter=I, num_experts=E, top_k=8, tokens_per_rank=8192, fp8_dispatch=True,
+                    fp8_experts=os.environ.get("PKB_MOE_FP8_EXPERTS") == "1")
+    w_router = torch.randn(E, H, device=dev, dtype=torch.bfloat16) * 0.02
+    wg = torch.randn(E, I, H, device=dev, dtype=torch.bfloat16) * 0.02
+    wu = torch.randn(E, I, H, device=dev, dtype=torch.bfloat16) * 0.02
+    wd = torch.randn(E, H, I, device=dev, dtype=torch.bfloat16) * 0.02
     comm = Comm(ctx)
     layer = EPMoELayer(comm.group(), comm, cfg, w_router, wg, wu, wd)
     x = torch.randn(cfg.tokens_per_rank, cfg.hidden, device=dev, dtype=torch.bfloat16)

@@ -49,11 +49,22 @@ def fp8_quantize_1x128(x: torch.Tensor, pow2_scales: bool = False):
     return y, s
 
 
-def fp8_dequantize_1x128(y: torch.Tensor, s: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+def fp8_dequantize_1x128(y: torch.Tensor, s: torch.Tensor, dtype: torch.dtype = torch.bfloat16,
+                         valid_rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``y`` e4m3 bytes with one fp32 scale per 128 values. ``valid_rows`` (an int32 device scalar, for 2-D ``y``): only that
+    many leading rows hold data - the rest of the result is left unwritten (a receive buffer sized for the worst case is
+    dequantised as far as it was filled, without the count coming to the host)."""
     yc = y.contiguous().view(torch.uint8)
     out = torch.empty(yc.shape, dtype=dtype, device=y.device)
-    nv.check(nv.cuda_lib().pkb_fp8_dequant_1x128(nv.ptr(yc), nv.ptr(s.contiguous()), nv.ptr(out), nv.c_ll(yc.numel()),
-                                                 _DT[dtype], nv.current_stream()), "pkb_fp8_dequant_1x128")
+    if valid_rows is not None:
+        if yc.dim() != 2 or valid_rows.dtype != torch.int32:
+            raise ValueError("valid_rows needs a 2-D input and an int32 device scalar")
+        nv.check(nv.cuda_lib().pkb_fp8_dequant_1x128_rows(nv.ptr(yc), nv.ptr(s.contiguous()), nv.ptr(out), nv.c_ll(yc.shape[0]),
+                                                          nv.c_ll(yc.shape[1]), _DT[dtype], nv.ptr(valid_rows), nv.current_stream()),
+                 "pkb_fp8_dequant_1x128_rows")
+    else:
+        nv.check(nv.cuda_lib().pkb_fp8_dequant_1x128(nv.ptr(yc), nv.ptr(s.contiguous()), nv.ptr(out), nv.c_ll(yc.numel()),
+                                                     _DT[dtype], nv.current_stream()), "pkb_fp8_dequant_1x128")
     nv.count_launch()
     return out
 

@@ -175,7 +175,8 @@ class MoEExchange:
             s = self.recv_scales.local.view(torch.float32)[:, :nblk]
             if s.shape[1] * 4 != self.scale_bytes:
                 s = s.contiguous()
-            return fp8_dequantize_1x128(self.recv_payload.local, s, torch.bfloat16)
+            # only the rows that arrived (offsets[-1], on the device) are converted: the buffer has capacity_factor x the mean
+            return fp8_dequantize_1x128(self.recv_payload.local, s, torch.bfloat16, valid_rows=self.offsets[self.El:self.El + 1])
         return self.recv_payload.local.view(torch.bfloat16)
 
     def home_ptrs(self) -> list[int]:

@@ -172,3 +172,16 @@ def test_clip_grad_norm_kernels_match_torch(dtype):
         torch.testing.assert_close(norm, total, rtol=2e-3, atol=1e-3)
         for got, r in zip(mine, ref):
             torch.testing.assert_close(got.float(), r * coef, rtol=2e-2 if dtype == torch.bfloat16 else 1e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_fp8_dequant_stops_at_the_device_side_row_count():
+    from parallelkernelbench_b200.ops import fp8_dequantize_1x128, fp8_quantize_1x128
+
+    x = torch.randn(96, 512, device="cuda", dtype=torch.bfloat16)
+    y, s = fp8_quantize_1x128(x)
+    full = fp8_dequantize_1x128(y, s, torch.bfloat16)
+    valid = torch.tensor([37], dtype=torch.int32, device="cuda")
+    part = fp8_dequantize_1x128(y, s, torch.bfloat16, valid_rows=valid)
+    assert torch.equal(part[:37], full[:37])
+    assert torch.allclose(full.float(), x.float(), atol=0.3, rtol=0.07)

@@ -106,3 +106,43 @@ def test_gemm_transposed_a_for_weight_gradients(M, N, K):
     b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) * 0.1
     out = gemm_bf16_tn(a, b, out_dtype=torch.float32)
     torch.testing.assert_close(out, a.float().t() @ b.float(), atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("epilogue", ["none", "swiglu"])
+@pytest.mark.parametrize("pair", ["1", "0"])
+def test_grouped_gemm_uneven_groups(epilogue, pair):
+    """Ragged GEMM (one weight matrix per row group) with an empty group, groups that end inside a 256-row tile and rows behind
+    the last group, on the CTA-pair kernel and on the one-CTA-per-tile kernel (selected by a variable read once per process,
+    hence the child process), against per-group fp32 products."""
+    import os
+    import subprocess
+    import sys
+
+    if os.environ.get("PKB_TEST_GROUPED_CHILD") != "1":
+        root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+        r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-x", "-q", "-k",
+                            f"test_grouped_gemm_uneven_groups and {epilogue} and {pair}"], cwd=root, capture_output=True, text=True,
+                           timeout=600, env={**os.environ, "PKB_TEST_GROUPED_CHILD": "1", "PKB_GROUPED_PAIR": pair})
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-1500:]
+        return
+    from parallelkernelbench_b200.ops.moe import grouped_gemm
+
+    torch.manual_seed(3)
+    counts = [300, 0, 513, 128, 77, 256]
+    G, N, K = len(counts), 512, 320
+    rows = sum(counts) + 40                                  # rows behind the last group are never touched
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    a = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(G, N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+    n_out = N // 2 if epilogue == "swiglu" else N
+    out = torch.full((rows, n_out), 7.0, device="cuda", dtype=torch.bfloat16)
+    grouped_gemm(a, w, off, epilogue=epilogue, out=out)
+    torch.cuda.synchronize()
+    lo = 0
+    for e, c in enumerate(counts):
+        acc = a[lo:lo + c].float() @ w[e].float().t()
+        ref = torch.nn.functional.silu(acc[:, 0::2]) * acc[:, 1::2] if epilogue == "swiglu" else acc
+        assert torch.allclose(out[lo:lo + c].float(), ref, atol=2e-2, rtol=2e-2), (e, (out[lo:lo + c].float() - ref).abs().max())
+        lo += c
+    assert bool((out[lo:] == 7.0).all())                     # untouched
