@@ -33,6 +33,68 @@ sum_rmsnorm_kernel(const void* __restrict__ src, long long src_stride, int nsrc,
                    int cols, float scale, float eps) {
   extern __shared__ float rowbuf[];
   __shared__ float red[32];
+  if constexpr (!SRC_F32 && MAXSRC == 1) {
+    if (cols <= kNormRowChunks * 8 * kNormThreads && nsrc == 1) {
+      // plain RMSNorm of a row that fits in registers: the loads of the CTA's NEXT row are issued before the reduction of
+      // the current one, so a CTA always has a row in flight (two block-wide synchronisations per row otherwise leave the
+      // memory system idle: 4.2 TB/s without the prefetch)
+      const __nv_bfloat16* s0 = static_cast<const __nv_bfloat16*>(src);
+      U4 cur[kNormRowChunks];
+      int row = blockIdx.x;
+      if (row < rows) {
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) {
+          const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+          if (i < cols) cur[ch] = ld_global_nc_v4(s0 + (long long)row * cols + i);
+        }
+      }
+      for (; row < rows; row += gridDim.x) {
+        const int nrow = row + (int)gridDim.x;
+        U4 nxt[kNormRowChunks];
+        if (nrow < rows) {
+#pragma unroll
+          for (int ch = 0; ch < kNormRowChunks; ++ch) {
+            const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+            if (i < cols) nxt[ch] = ld_global_nc_v4(s0 + (long long)nrow * cols + i);
+          }
+        }
+        float vals[kNormRowChunks][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) {
+          const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+          if (i < cols) {
+            const float2 f0 = unpack_bf16x2(cur[ch].x), f1 = unpack_bf16x2(cur[ch].y), f2 = unpack_bf16x2(cur[ch].z),
+                         f3 = unpack_bf16x2(cur[ch].w);
+            vals[ch][0] = f0.x * scale; vals[ch][1] = f0.y * scale; vals[ch][2] = f1.x * scale; vals[ch][3] = f1.y * scale;
+            vals[ch][4] = f2.x * scale; vals[ch][5] = f2.y * scale; vals[ch][6] = f3.x * scale; vals[ch][7] = f3.y * scale;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss += vals[ch][j] * vals[ch][j];
+          }
+        }
+        const float total = block_sum(ss, red);
+        const float rstd = rsqrtf(total / (float)cols + eps);
+        __nv_bfloat16* yrow = y + (long long)row * cols;
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) {
+          const int i = (ch * kNormThreads + (int)threadIdx.x) * 8;
+          if (i < cols) {
+            const U4 g = ld_global_v4(gamma + i);
+            const float2 g0 = unpack_bf16x2(g.x), g1 = unpack_bf16x2(g.y), g2 = unpack_bf16x2(g.z), g3 = unpack_bf16x2(g.w);
+            U4 o;
+            o.x = pack_bf16x2(vals[ch][0] * rstd * g0.x, vals[ch][1] * rstd * g0.y);
+            o.y = pack_bf16x2(vals[ch][2] * rstd * g1.x, vals[ch][3] * rstd * g1.y);
+            o.z = pack_bf16x2(vals[ch][4] * rstd * g2.x, vals[ch][5] * rstd * g2.y);
+            o.w = pack_bf16x2(vals[ch][6] * rstd * g3.x, vals[ch][7] * rstd * g3.y);
+            st_global_v4(yrow + i, o);
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < kNormRowChunks; ++ch) cur[ch] = nxt[ch];
+      }
+      return;
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     __nv_bfloat16* yrow = y + (long long)row * cols;
     if constexpr (!SRC_F32) {
