@@ -2063,7 +2063,7 @@ static int launch_fa(const pkb_attn_desc* desc, const void* q, const void* k, co
     constexpr int smem = Fa3Smem<D>::kTotal;
     dim3 grid((n_tiles + 1) / 2, d.hq, d.batch);
     // PKB_FA_OPT=0..3 selects the softmax arithmetic variant (bit 0: packed pairs and three-input maxima, bit 1: polynomial)
-    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '9') ? e[0] - '0' : kFa3DefaultOpt; }();
+    static const int opt = [] { const char* e = getenv("PKB_FA_OPT"); return (e != nullptr && e[0] >= '0' && e[0] <= '9') ? atoi(e) : kFa3DefaultOpt; }();
 #define PKB_FA3(O)                                                                                   \
     {                                                                                                \
       auto kern = fa_fwd3_kernel<D, O>;                                                              \

@@ -149,7 +149,11 @@ struct MoeDispatchArgs {
   uint64_t recv_meta_off;   // 0, or heap offset of int2 [capacity]: (sender's index in the group, assignment index) per row
 };
 
-__global__ void __launch_bounds__(256) moe_dispatch_kernel(const SymmCtx c, const MoeDispatchArgs a) {
+// 512 threads per block, two blocks per SM: the cross-GPU block barrier caps the grid at kSymmMaxBlocks blocks, so the warps
+// that keep copies in flight have to come from the block size.
+constexpr int kMoeXchgThreads = 512;
+
+__global__ void __launch_bounds__(kMoeXchgThreads, 2) moe_dispatch_kernel(const SymmCtx c, const MoeDispatchArgs a) {
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -169,7 +173,13 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const SymmCtx c, cons
     const int dest = c.members[e / a.experts_per_rank];
     const uint8_t* src = a.payload + t * a.payload_bytes;
     uint8_t* dst = symm_ptr<uint8_t>(c, dest, a.recv_payload_off) + (long long)slot * a.payload_bytes;
-    for (int b = lane * 16; b < a.payload_bytes; b += 32 * 16) st_global_v4(dst + b, ld_global_v4(src + b));
+    // four 16-byte loads in flight per lane before the first store
+    int b = lane * 16;
+    for (; b + 3 * 512 < a.payload_bytes; b += 4 * 512) {
+      const U4 u0 = ld_global_v4(src + b), u1 = ld_global_v4(src + b + 512), u2 = ld_global_v4(src + b + 1024), u3 = ld_global_v4(src + b + 1536);
+      st_global_v4(dst + b, u0); st_global_v4(dst + b + 512, u1); st_global_v4(dst + b + 1024, u2); st_global_v4(dst + b + 1536, u3);
+    }
+    for (; b < a.payload_bytes; b += 512) st_global_v4(dst + b, ld_global_v4(src + b));
     if (a.scales != nullptr) {
       const uint8_t* ss = a.scales + t * a.scale_bytes;
       uint8_t* sd = symm_ptr<uint8_t>(c, dest, a.recv_scale_off) + (long long)slot * a.scale_bytes;
@@ -196,7 +206,7 @@ struct MoeCombineArgs {
 };
 
 template <int MAXK>
-__global__ void __launch_bounds__(256) moe_combine_kernel(const SymmCtx c, const MoeCombineArgs a) {
+__global__ void __launch_bounds__(kMoeXchgThreads, 2) moe_combine_kernel(const SymmCtx c, const MoeCombineArgs a) {
   // every rank's expert outputs are complete once all ranks have entered this kernel
   if (!symm_block_barrier(c, 501, 1)) return;
   const int lane = threadIdx.x & 31;
@@ -305,7 +315,7 @@ int pkb_moe_dispatch_meta(const pkb_symm_ctx* h, const void* payload, const void
   PKB_CHECK_ARG((recv_meta_off & 7) == 0, "heap offsets misaligned");
   int grid = sm_count() * 2;   // fixed: the same on every rank, the barrier pairs blocks by index
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
-  moe_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
+  moe_dispatch_kernel<<<grid, kMoeXchgThreads, 0, static_cast<cudaStream_t>(stream)>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
@@ -331,9 +341,9 @@ int pkb_moe_combine_from(const pkb_symm_ctx* h, unsigned long long y_off, const 
   int grid = sm_count() * 2;
   if (grid > kSymmMaxBlocks) grid = kSymmMaxBlocks;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (top_k <= 2) moe_combine_kernel<2><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
-  else if (top_k <= 4) moe_combine_kernel<4><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
-  else moe_combine_kernel<8><<<grid, 256, 0, s>>>(symm_ctx_from_api(h), a);
+  if (top_k <= 2) moe_combine_kernel<2><<<grid, kMoeXchgThreads, 0, s>>>(symm_ctx_from_api(h), a);
+  else if (top_k <= 4) moe_combine_kernel<4><<<grid, kMoeXchgThreads, 0, s>>>(symm_ctx_from_api(h), a);
+  else moe_combine_kernel<8><<<grid, kMoeXchgThreads, 0, s>>>(symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;
 }
