@@ -31,6 +31,9 @@ CONTRACT = textwrap.dedent("""\
     rank maps: all_reduce(x, op="sum", scale=1.0), all_gather(x) -> [W, ...], reduce_scatter(x), all_to_all(x[W, ...]),
     all_to_all_v(rows, counts, capacity), all_to_all_permute(x, scatter_dim, gather_dim), row_gather(shard, ids),
     broadcast / reduce / scatter / gather, barrier(); rc.comm.heap allocates tensors that peers can address.
+    A result whose length is only known on the device may be returned as utils.ragged.Ragged(buffer, count[, dim]) - a capacity
+    buffer and a device-side count, trimmed by the harness when it stores the output - so that no size has to come back to the
+    host inside the timed call (never call .item() / .tolist() on the hot path).
     Kernels of this package: ops.gemm_bf16 (a @ w.T on tcgen05), ops.gemm_bf16_kn, ops.gemm_bf16_tn, ops.rmsnorm,
     ops.rope, ops.fp8_quantize_1x128 / fp8_dequantize_1x128, ops.attention.flash_attn_fwd / flash_attn_bwd /
     RingAttention, ops.tp.AllGatherGemm / GemmReduceScatterRMSNorm, ops.moe.MoEExchange / grouped_gemm.
