@@ -48,6 +48,9 @@ int pkb_coll_allreduce_twoshot(const pkb_symm_ctx* h, int dtype, int op, const v
 // NVLS push all-gather / NVLS reduce-scatter (see collectives.cu); both need the multicast mapping and the whole-job group.
 int pkb_coll_allgather_nvls(const pkb_symm_ctx* h, const void* src, long long bytes, unsigned long long gather_off, void* out,
                             int max_blocks, void* stream);
+// Broadcast of member `root`'s bytes through the switch (multimem.st by the root only) into heap offset bcast_off of every rank.
+int pkb_coll_broadcast_nvls(const pkb_symm_ctx* h, const void* src, long long bytes, int root, unsigned long long bcast_off, void* out,
+                            int max_blocks, void* stream);
 int pkb_coll_reduce_scatter_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n, unsigned long long stage_off,
                                  void* out, int src_in_heap, int max_blocks, void* stream);
 int pkb_coll_allreduce_nvls(const pkb_symm_ctx* h, int dtype, const void* src, long long n,

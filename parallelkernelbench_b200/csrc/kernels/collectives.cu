@@ -722,6 +722,7 @@ struct NvlsAgArgs {
   long long bytes;         // multiple of 16
   uint64_t gather_off;     // heap offset of the gathered buffer [gsize][bytes]
   void* out;               // optional local output that receives a copy of the gathered buffer (null: caller reads the heap)
+  int root;                // -1: all-gather (member g stores slot g); >= 0: broadcast - only member `root` stores, into slot 0
 };
 
 __global__ void __launch_bounds__(kCollThreads)
@@ -736,8 +737,8 @@ coll_allgather_nvls_kernel(const SymmCtx c, const NvlsAgArgs a) {
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const uint8_t* src = static_cast<const uint8_t*>(a.src);
-  uint8_t* dst = symm_mc<uint8_t>(c, a.gather_off) + (long long)c.grank * a.bytes;
-  long long i = tid;
+  uint8_t* dst = symm_mc<uint8_t>(c, a.gather_off) + (a.root < 0 ? (long long)c.grank * a.bytes : 0ll);
+  long long i = (a.root < 0 || a.root == c.grank) ? tid : nvec;      // broadcast: only the root has something to store
   for (; i + 7 * nthreads < nvec; i += 8 * nthreads) {   // eight local loads in flight per thread, then eight posted stores
     U4 v[8];
 #pragma unroll
@@ -750,7 +751,7 @@ coll_allgather_nvls_kernel(const SymmCtx c, const NvlsAgArgs a) {
   if (!symm_grid_barrier(c, 206, 2)) return;
   if (a.out != nullptr) {
     cp.proxy_fence();
-    cp.copy(a.out, symm_local<uint8_t>(c, a.gather_off), a.bytes * c.gsize);
+    cp.copy(a.out, symm_local<uint8_t>(c, a.gather_off), a.root < 0 ? a.bytes * c.gsize : a.bytes);
   }
 }
 
@@ -1075,7 +1076,22 @@ int pkb_coll_allgather_nvls(const pkb_symm_ctx* h, const void* src, long long by
   PKB_CHECK_ARG(h->mc_base != 0 && h->gsize == h->world, "NVLS all-gather needs the multicast mapping and the whole-job group");
   PKB_CHECK_ARG(bytes > 0 && bytes % 16 == 0 && (gather_off & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
                 (reinterpret_cast<uintptr_t>(out) & 15) == 0, "16-byte alignment and a size that is a multiple of 16");
-  NvlsAgArgs a{src, bytes, gather_off, out};
+  NvlsAgArgs a{src, bytes, gather_off, out, -1};
+  launch_with_ring(coll_allgather_nvls_kernel, grid_for(bytes, max_blocks), static_cast<cudaStream_t>(stream), symm_ctx_from_api(h), a);
+  PKB_CHECK_CUDA(cudaGetLastError());
+  return kApiOk;
+}
+
+// Broadcast through the switch: member `root` stores its `bytes` once through the multicast mapping and they land in the buffer
+// at heap offset bcast_off of every rank (and in `out` when it is not null). Same constraints as the all-gather above.
+int pkb_coll_broadcast_nvls(const pkb_symm_ctx* h, const void* src, long long bytes, int root, unsigned long long bcast_off, void* out,
+                            int max_blocks, void* stream) {
+  if (int rc = symm_ctx_check(h)) return rc;
+  PKB_CHECK_ARG(h->mc_base != 0 && h->gsize == h->world, "NVLS broadcast needs the multicast mapping and the whole-job group");
+  PKB_CHECK_ARG(root >= 0 && root < h->gsize, "root out of range");
+  PKB_CHECK_ARG(bytes > 0 && bytes % 16 == 0 && (bcast_off & 15) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0 &&
+                (reinterpret_cast<uintptr_t>(out) & 15) == 0, "16-byte alignment and a size that is a multiple of 16");
+  NvlsAgArgs a{src, bytes, bcast_off, out, root};
   launch_with_ring(coll_allgather_nvls_kernel, grid_for(bytes, max_blocks), static_cast<cudaStream_t>(stream), symm_ctx_from_api(h), a);
   PKB_CHECK_CUDA(cudaGetLastError());
   return kApiOk;

@@ -259,10 +259,23 @@ def all_to_all(x: torch.Tensor, group: SymmGroup, out: torch.Tensor | None = Non
     return out
 
 
-def broadcast(x: torch.Tensor, group: SymmGroup, src: int = 0) -> torch.Tensor:
+def broadcast(x: torch.Tensor, group: SymmGroup, src: int = 0, algo: str = "auto") -> torch.Tensor:
+    """Every member receives member ``src``'s tensor. ``algo``: ``"pull"`` (stage at the root, the others read it), ``"nvls"`` (the
+    root stores once through the multicast mapping and the switch replicates it) or ``"auto"`` (NVLS from
+    ``tuning.broadcast_nvls_min`` bytes on the whole-job group)."""
     x = _check(x)
     out = torch.empty_like(x)
     nb = x.numel() * x.element_size()
+    nvls_fit = _nvls_ok(group) and nb % 16 == 0 and x.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+    if algo == "nvls" and not nvls_fit:
+        raise RuntimeError("NVLS broadcast needs multicast, the whole-job group and a 16-byte aligned tensor")
+    if algo == "nvls" or (algo == "auto" and nvls_fit and nb >= tuning.broadcast_nvls_min(group.size)):
+        cap = 1 << max(12, (nb - 1).bit_length())
+        boff = group.heap.named(("bc_nvls", group.channel), (cap,), torch.uint8).offset
+        nv.check(_lib().pkb_coll_broadcast_nvls(group.ref, nv.ptr(x), nv.c_ll(nb), int(src), ctypes.c_ulonglong(boff), nv.ptr(out), 0,
+                                                nv.current_stream()), "pkb_coll_broadcast_nvls")
+        nv.count_launch()
+        return out
     _gather_call(group, x, 1 << src, 0, 0, nb, out, nb, True, "bc_in")
     return out
 

@@ -63,6 +63,12 @@ def reduce_scatter_nvls_min(world: int, table: dict | None = None) -> int:
     return int(_row("reduce_scatter", world, table).get("nvls_min_bytes", _NVLS_OFF))
 
 
+def broadcast_nvls_min(world: int, table: dict | None = None) -> int:
+    """Message size in bytes from which a broadcast on the whole-job group is stored through the multicast mapping by its root
+    (``nvls_min_bytes`` of the table's ``broadcast`` row; absent = never)."""
+    return int(_row("broadcast", world, table).get("nvls_min_bytes", _NVLS_OFF))
+
+
 def all_to_all_push_min(world: int, table: dict | None = None, direct: bool = False) -> int:
     """Chunk size in bytes (per destination) from which the all-to-all pushes with TMA bulk stores into the receivers instead of
     staging its input and letting the receivers pull: ``push_min_bytes`` of the table's ``all_to_all`` row, or

@@ -109,6 +109,12 @@ def main() -> int:
     x = torch.randn(3000, device=dev, generator=gen)
     ref = x.clone(); dist.broadcast(ref, src=W - 1)
     report("broadcast", torch.equal(C.broadcast(x, g, src=W - 1), ref))
+    if heap.mc_base and W > 1:
+        xb = torch.randn(1 << 18, device=dev, generator=gen) + r
+        refb = xb.clone(); dist.broadcast(refb, src=1)
+        okb = torch.equal(C.broadcast(xb, g, src=1, algo="nvls"), refb)
+        okb &= torch.equal(C.broadcast(xb + 1, g, src=0, algo="nvls"), (lambda t: (dist.broadcast(t, src=0), t)[1])((xb + 1).clone()))
+        report("broadcast through the switch (multimem.st by the root)", okb)
     x = torch.randn(W, 129, device=dev, generator=gen)
     ref = torch.empty(129, device=dev)
     dist.scatter(ref, list(x.unbind(0)) if r == 0 else None, src=0)
@@ -231,6 +237,15 @@ def main() -> int:
                   f"nvls={t_nvls * 1e3:.1f}us ({per_dir / t_nvls / 1e6:.0f} GB/s)", flush=True)
             print(f"PERF all_to_all {nbytes}B nccl={t_nccl_a * 1e3:.1f}us pull={t_ours_a * 1e3:.1f}us ({per_dir / t_ours_a / 1e6:.0f} GB/s per direction) "
                   f"push={t_push_a * 1e3:.1f}us ({per_dir / t_push_a / 1e6:.0f} GB/s) push_into_heap={t_push_h * 1e3:.1f}us ({per_dir / t_push_h / 1e6:.0f} GB/s)", flush=True)
+
+    if heap.mc_base and W > 1:
+        for nbytes in (1 << 20, 1 << 27):
+            xb = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
+            t_nccl = timeit(lambda: dist.broadcast(xb, src=0))
+            t_pull = timeit(lambda: C.broadcast(xb, g, src=0, algo="pull"))
+            t_nvls = timeit(lambda: C.broadcast(xb, g, src=0, algo="nvls"))
+            if r == 0:
+                print(f"PERF broadcast {nbytes}B nccl={t_nccl * 1e3:.1f}us pull={t_pull * 1e3:.1f}us nvls={t_nvls * 1e3:.1f}us", flush=True)
 
     for nbytes in (1 << 20, 1 << 24, 1 << 27):
         x = torch.randn(nbytes // 2, device=dev, dtype=torch.bfloat16)
