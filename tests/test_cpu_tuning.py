@@ -42,3 +42,18 @@ def test_thresholds_from_timings_finds_the_crossovers():
     assert row == {"ll_max_bytes": 65536, "oneshot_max_bytes": 16777216, "large": "twoshot"}
     t["nvls"][134217728] = 200.0
     assert tuning.thresholds_from_timings(t)["large"] == "nvls"
+
+
+def test_push_and_in_switch_thresholds_come_from_the_table():
+    """All-gather / reduce-scatter / broadcast in-switch thresholds and the all-to-all push thresholds are table rows too: absent
+    rows mean "never", the all-to-all has a separate (lower) threshold for results that already live in the symmetric heap."""
+    t = {"version": 1, "all_gather": {"4": {"ll_max_bytes": 1024, "nvls_min_bytes": 4096}}, "reduce_scatter": {"8": {"nvls_min_bytes": 8192}},
+         "broadcast": {"default": {"nvls_min_bytes": 2048}},
+         "all_to_all": {"default": {"push_min_bytes": 1 << 23, "push_direct_min_bytes": 1 << 20}}}
+    assert tuning.all_gather_nvls_min(4, t) == 4096 and tuning.all_gather_nvls_min(2, t) > 1 << 60
+    assert tuning.reduce_scatter_nvls_min(8, t) == 8192 and tuning.reduce_scatter_nvls_min(4, t) > 1 << 60
+    assert tuning.broadcast_nvls_min(3, t) == 2048
+    assert tuning.all_to_all_push_min(4, t) == 1 << 23 and tuning.all_to_all_push_min(4, t, direct=True) == 1 << 20
+    # the committed table parses and keeps the orderings the kernels rely on
+    assert tuning.all_to_all_push_min(4, direct=True) <= tuning.all_to_all_push_min(4)
+    assert tuning.all_gather_nvls_min(8) >= tuning.all_gather_ll_max(8)
