@@ -159,6 +159,30 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return true;
 }
 
+// The same bounded wait for roles that are NOT on a kernel's critical path (a producer that runs steps ahead, a warp that only
+// reacts to rare events): between two tests the warp sleeps `sleep_ns`, so it takes far fewer issue slots from the warps of
+// its scheduler that compute, at the price of waking up to `sleep_ns` late.
+__device__ __forceinline__ bool mbar_wait_backoff(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns,
+                                                  uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    __nanosleep(sleep_ns);
+    if ((++spins & 0x3fu) == 0u) {
+      if (*abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > budget_cycles(budget_ns)) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // The same wait for a warp whose lanes walk a loop together: one lane polls (32 lanes testing the same barrier are 32
 // barrier operations), the result is shared by a vote. `lead` is non-zero in exactly one lane.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t budget_ns,

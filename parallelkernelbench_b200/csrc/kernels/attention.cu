@@ -1112,7 +1112,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         // step j-2, so both are requested about two steps before the issuing warp asks for them
         auto load_v = [&](int j, int row, uint32_t bar) {
           const int sv = j % kStagesV;
-          if (!mbar_wait(v_empty(sv), ((j / kStagesV) & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (!mbar_wait_backoff(v_empty(sv), ((j / kStagesV) & 1) ^ 1u, abort_flag, p.budget_ns, 256)) { ok = false; return; }
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
             tma_load_3d_p(sb + S::kV + sv * S::kTileBytes + a * kAtomBytes, &tmap_v, bar, a * 64, kv_head, kv_tok_base + row, lead);
@@ -1133,7 +1133,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
               fence_proxy_async_all();
             }
           }
-          if (!mbar_wait(k_empty(sk), ((j / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns)) { ok = false; return; }
+          if (!mbar_wait_backoff(k_empty(sk), ((j / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns, 256)) { ok = false; return; }
           mbar_expect_tx_p(kv_full(sk), (j > 0 ? 2 : 1) * S::kTileBytes, lead);
 #pragma unroll
           for (int a = 0; a < kAtoms; ++a)
@@ -1142,7 +1142,7 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
           prev_row = row;
         });
         if (ok && n > 0) {                     // the last V tile alone, on the barrier step n would have used
-          if (mbar_wait(k_empty(n % kStagesK), ((n / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns)) {
+          if (mbar_wait_backoff(k_empty(n % kStagesK), ((n / kStagesK) & 1) ^ 1u, abort_flag, p.budget_ns, 256)) {
             mbar_expect_tx_p(kv_full(n % kStagesK), S::kTileBytes, lead);
             load_v(n - 1, prev_row, kv_full(n % kStagesK));
           } else {
@@ -1391,7 +1391,8 @@ __device__ __forceinline__ void fa_fwd3_cta(const CUtensorMap& tmap_q, const CUt
         for (int t = 0; t < 2 && ok; ++t) {
           if (t == 0 ? !need0(kp) : !has1) continue;
           const uint32_t ph = cnt[t] & 1;
-          ok = mbar_wait(a_full(t), ph, abort_flag, p.budget_ns);
+          // the rescale factors arrive long before the step's P: this warp may wake a little late and polls sparingly
+          ok = mbar_wait_backoff(a_full(t), ph, abort_flag, p.budget_ns, 128);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           if constexpr (TRACE) { if (q4 == 0 && lane == 0) fa_trace_slot(p, 3, 2 * t, cnt[t]); }
