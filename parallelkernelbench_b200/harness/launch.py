@@ -5,6 +5,8 @@ sizes, list the registry, and inspect stored results.
     python -m parallelkernelbench_b200.harness.launch run   --op allreduce --impl ours --nproc 2
     python -m parallelkernelbench_b200.harness.launch eval  --op tp_mlp --nproc 8 --measure-perf
     python -m parallelkernelbench_b200.harness.launch eval  --op plumbing --nproc 2 --backend gloo --atol 1e-5 --rtol 1e-5
+    python -m parallelkernelbench_b200.harness.launch remote-worker --spool /shared/pkb_spool                    # on the GPU box
+    python -m parallelkernelbench_b200.harness.launch eval  --op allreduce --nproc 8 --remote-spool /shared/pkb_spool   # anywhere
     python -m parallelkernelbench_b200.harness.launch sweep --ops allreduce,allgather --worlds 1,2,4,8 --resume
     python -m parallelkernelbench_b200.harness.launch report --format markdown      # the sweep ledger as a table
     python -m parallelkernelbench_b200.harness.launch headline --nproc 8            # the headline configurations, timed
@@ -169,7 +171,7 @@ STRICT_ATOL, STRICT_RTOL = compare.STRICT_ATOL, compare.STRICT_RTOL
 
 
 def _gate(spec_name: str, nproc: int, trial: int, ref_job: dict, cand_job: dict, atol: float, rtol: float, use_oracle: bool,
-          job_kw: dict) -> tuple[dict | None, dict]:
+          job_kw: dict, runner=None) -> tuple[dict | None, dict]:
     """Decide one trial. Returns (comparison used for the verdict, record of how the gate was applied).
 
     1. candidate within 1e-2 / 1e-2 of the reference (the reference harness's own gate): pass, ``gate = "strict"``.
@@ -192,7 +194,7 @@ def _gate(spec_name: str, nproc: int, trial: int, ref_job: dict, cand_job: dict,
     if not cmp["ok"] or not use_oracle:
         return cmp, info
     kw = {k: v for k, v in job_kw.items() if k in ("config", "overrides", "dtype", "backend", "timeout_s", "pg_timeout_s")}
-    oracle_job = run_job(spec_name, "oracle", nproc, trial=trial, **kw)
+    oracle_job = (runner or run_job)(spec_name, "oracle", nproc, trial=trial, **kw)
     if oracle_job["returncode"] != 0 or oracle_job["artifact_count"] < nproc:
         tail = [ln for ln in (oracle_job.get("stderr") or "").strip().splitlines() if ln.strip()]
         info["oracle"] = "unavailable" + (f": {tail[-1][:200]}" if tail else "")
@@ -220,9 +222,12 @@ def _gate(spec_name: str, nproc: int, trial: int, ref_job: dict, cand_job: dict,
 
 
 def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rtol: float | None = None, measure_perf=False,
-            cooldown: float | None = None, solution: str | None = None, oracle: bool = True, **job_kw) -> dict:
+            cooldown: float | None = None, solution: str | None = None, oracle: bool = True, runner=None, **job_kw) -> dict:
+    """``runner``: a callable with the signature and result of ``run_job`` that executes the jobs somewhere else
+    (``harness.remote.RemoteRunner.run_job``); comparison, gate and classification stay here."""
     from ..workloads import registry
 
+    run = runner or run_job
     spec = registry.get(op)
     op_atol, op_rtol = spec.tolerance(job_kw.get("config", "default"))
     atol = op_atol if atol is None else atol
@@ -231,11 +236,11 @@ def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rto
     results, all_ok, interrupted, env_failed = [], True, False, False
     for t in range(trials):
         hygiene.between_jobs()
-        ref_job = run_job(spec.name, "reference", nproc, trial=t, measure_perf=measure_perf, **job_kw)
+        ref_job = run(spec.name, "reference", nproc, trial=t, measure_perf=measure_perf, **job_kw)
         time.sleep(cooldown)
-        cand_job = run_job(spec.name, "file" if solution else "ours", nproc, trial=t, measure_perf=measure_perf,
-                           solution=solution, **job_kw)
-        cmp, gate = _gate(spec.name, nproc, t, ref_job, cand_job, atol, rtol, oracle, job_kw)
+        cand_job = run(spec.name, "file" if solution else "ours", nproc, trial=t, measure_perf=measure_perf,
+                       solution=solution, **job_kw)
+        cmp, gate = _gate(spec.name, nproc, t, ref_job, cand_job, atol, rtol, oracle, job_kw, runner=runner)
         verdict = report.classify_trial(ref_job, cand_job, cmp)
         ref_perf = report.summarize_perf(ref_job["job_dir"]) if measure_perf else None
         cand_perf = report.summarize_perf(cand_job["job_dir"]) if measure_perf else None
@@ -264,7 +269,7 @@ def eval_op(op: str, nproc: int, trials: int = 5, atol: float | None = None, rto
             all_ok = False
             entry["early_stop"] = True
             break
-    summary = {"version": 1, "backend": "local", "mode": "eval", "op": spec.name, "problem_ids": list(spec.problem_ids),
+    summary = {"version": 1, "backend": "remote" if runner is not None else "local", "mode": "eval", "op": spec.name, "problem_ids": list(spec.problem_ids),
                "all_ok": all_ok, "interrupted": interrupted, "harness_environment_failed": env_failed,
                "trials": results, "nproc_per_node": nproc, "atol": atol, "rtol": rtol, "git_sha": env.git_sha()}
     print("all trials match" if all_ok else "mismatch", flush=True)
@@ -317,12 +322,24 @@ def cmd_run(a) -> int:
 def cmd_eval(a) -> int:
     from ..workloads import registry
 
+    runner = None
+    if a.remote_spool:
+        from . import remote
+
+        runner = remote.make_runner(a.remote_spool, ssh=a.remote_ssh, wait_s=a.remote_wait).run_job
     s = eval_op(a.op, a.nproc, trials=a.trials, atol=a.atol, rtol=a.rtol, measure_perf=a.measure_perf, config=a.config,
                 overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
-                graph=a.graph, profile=a.profile, timeout_s=a.timeout, solution=a.solution)
+                graph=a.graph, profile=a.profile, timeout_s=a.timeout, solution=a.solution, runner=runner)
     if s["interrupted"]:
         return 130
     return 0 if s["all_ok"] else 1
+
+
+def cmd_remote_worker(a) -> int:
+    from . import remote
+
+    remote.serve(a.spool, once=a.once, poll_s=a.poll)
+    return 0
 
 
 def cmd_sweep(a) -> int:
@@ -466,7 +483,15 @@ def main(argv=None) -> int:
     sp.add_argument("--solution", default=None, help="evaluate this file's solution(rc, *inputs) instead of the built-in implementation")
     sp.add_argument("--atol", type=float, default=None)
     sp.add_argument("--rtol", type=float, default=None)
+    sp.add_argument("--remote-spool", default=None, help="run the jobs through the queue in this spool directory (see harness/remote.py)")
+    sp.add_argument("--remote-ssh", default=None, metavar="USER@HOST", help="the spool directory lives on this host (SFTP)")
+    sp.add_argument("--remote-wait", type=float, default=3600.0, help="seconds to wait for one remote job")
     sp.set_defaults(fn=cmd_eval)
+    sp = sub.add_parser("remote-worker", help="serve the job queue of a spool directory on this machine")
+    sp.add_argument("--spool", required=True)
+    sp.add_argument("--once", action="store_true", help="serve at most one job, or return at once when the queue is empty")
+    sp.add_argument("--poll", type=float, default=0.5)
+    sp.set_defaults(fn=cmd_remote_worker)
     sp = sub.add_parser("sweep")
     sp.add_argument("--ops", default="all")
     sp.add_argument("--worlds", default="1,2,4,8")
