@@ -11,7 +11,8 @@ peak where the case is a contraction.
 
 Cases: ``gemm`` (8192^3 bf16), ``gemm_bwd`` (dX and dW of a 4096 x 4096 x 14336 linear layer), ``fa_fwd`` / ``fa_bwd`` (sequence 16384, causal, 32 query / 8 KV heads, head dim 128),
 ``fa_fwd_4k``, ``grouped_bf16`` / ``grouped_fp8`` (32 experts x 2048 rows, 7168 -> 4096 gate/up with SwiGLU: the expert GEMM of
-the 256-expert MoE configuration per rank), ``rmsnorm``, ``fp8_quant``.
+the 256-expert MoE configuration per rank), ``rmsnorm``, ``fp8_quant``, ``kalman`` and ``sinkhorn`` (fp64 block Kalman step and
+Sinkhorn-Knopp normalisation, each on a 256 MiB operand, against the library-op forms of the same formulas).
 """
 from __future__ import annotations
 
@@ -323,6 +324,52 @@ def case_fp8_quant(t: _Timer) -> dict:
     x = torch.randn(16384, 8192, device="cuda", dtype=torch.bfloat16)
     ours = t(lambda: fp8_quantize_1x128(x))
     return _line("fp8_quant", ours, None, bytes_moved=x.numel() * (2 + 1 + 4 / 128))
+
+
+def case_kalman(t: _Timer) -> dict:
+    """Block Kalman-filter step in fp64, 32 blocks of 1024 x 1024 (a 256 MiB covariance, twice the L2): our three launches
+    (P read twice, written once) against the same formulas as library products (reference/63_deepmd_kalman_filter_optimizer.py)."""
+    from ..ops.wild import kalman_block_step
+
+    nb, n, lam = 32, 1024, 0.98
+    H = torch.randn(nb, n, 1, dtype=torch.float64, device="cuda") * 0.01
+    w = torch.randn(nb, n, 1, dtype=torch.float64, device="cuda")
+    P = torch.eye(n, dtype=torch.float64, device="cuda").repeat(nb, 1, 1) + 0.01 * torch.randn(nb, n, n, dtype=torch.float64, device="cuda")
+    err = torch.randn(1, dtype=torch.float64, device="cuda")
+
+    def lib_step():
+        K = torch.bmm(P, H)
+        A = 1.0 / (lam + torch.bmm(H.transpose(1, 2), K)).sum().reshape(1)
+        return w + A * err * K, (1.0 / lam) * (P - A * torch.bmm(K, K.transpose(1, 2)))
+
+    ours = t(lambda: kalman_block_step(H, err, w, P, lam))
+    lib = t(lib_step)
+    return _line("kalman", ours, lib, bytes_moved=3.0 * P.numel() * 8)
+
+
+def case_sinkhorn(t: _Timer) -> dict:
+    """Sinkhorn-Knopp, 4096 samples x 16384 prototypes fp32 (256 MiB), three iterations: our scale-vector form (nine passes
+    over the logits: one for the mass, two per iteration, one read and one write for the result) against the matrix-rewriting
+    form of reference/80_dinov2_distributed_sinkhorn_knopp.py."""
+    from ..ops.wild import sinkhorn_knopp
+
+    B, Pn, temp, iters = 4096, 16384, 0.07, 3
+    x = torch.randn(B, Pn, device="cuda") * 0.01
+
+    def lib_form():
+        q = torch.exp(x / temp).T.contiguous()
+        q /= q.sum()
+        for _ in range(iters):
+            q /= q.sum(dim=1, keepdim=True)
+            q /= Pn
+            q /= q.sum(dim=0, keepdim=True)
+            q /= B
+        q *= B
+        return q.T.contiguous()
+
+    ours = t(lambda: sinkhorn_knopp(x, temp, iters))
+    lib = t(lib_form)
+    return _line("sinkhorn", ours, lib, bytes_moved=(3.0 + 2 * iters) * x.numel() * 4)
 
 
 def main(argv=None) -> int:

@@ -392,6 +392,13 @@ def _kalman_inputs(rc: RunCtx, cfg):
 def _kalman(rc, H, err, w, P, lam, nue, ours):
     """All blocks batched (the project loops over them); the scalar and the weights cross ranks."""
     W = rc.world
+    if ours and rc.dist.is_cuda and P.dtype == torch.float64:
+        from ..ops.wild import kalman_block_step
+
+        w_new, P_new = kalman_block_step(H, err, w, P, lam, all_reduce=rc.comm.all_reduce if W > 1 else None)
+        allw = rc.comm.all_gather(w_new) if W > 1 else w_new.unsqueeze(0)
+        lam_next = torch.tensor(nue * lam + 1 - nue, dtype=torch.float64, device=H.device)
+        return {"weights": allw.reshape(-1, w.shape[1], 1), "P": P_new, "lambda": lam_next}
     K = torch.bmm(P, H)                                                   # [nb, n, 1]
     tmp = (lam + torch.bmm(H.transpose(1, 2), K)).sum().reshape(1)
     if W > 1:
@@ -1320,6 +1327,10 @@ def _sk_ours(rc, t, temp, iters):
     of which is two matrix-vector passes over exp(t/temp) and one small all-reduce; the result is written once."""
     W = rc.world
     ar = (lambda x: rc.comm.all_reduce(x)) if W > 1 else (lambda x: x)
+    if rc.dist.is_cuda:
+        from ..ops.wild import sinkhorn_knopp
+
+        return sinkhorn_knopp(t, temp, iters, all_reduce=ar if W > 1 else None)   # the exponentials are never stored either
     E = torch.exp(t.float() / temp)                                           # [B, P]
     B, P = E.shape
     head = ar(torch.stack([torch.tensor(float(B), device=t.device), E.sum()]))   # batch size and mass in one exchange
