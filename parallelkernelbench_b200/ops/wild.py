@@ -131,3 +131,60 @@ def sinkhorn_knopp(t: torch.Tensor, temp: float, iters: int, all_reduce=None) ->
              "pkb_sinkhorn_scale")
     nv.count_launch()
     return out
+
+
+KNN_MAX_CANDIDATES = 4096
+
+
+def knn_topk_local(sim: torch.Tensor, labels: torch.Tensor, k: int, classes: int | None = None):
+    """The ``k`` most similar training rows per query (reference: reference/79_dinov2_distributed_knn.py:7-14).
+    ``sim`` [R, N] fp32, ``labels`` int64 with N entries. With ``classes`` the similarities [R, k] and the class votes
+    [R, classes] come back (the single-rank result); without, (similarity, label) pairs [R, k, 2] for the exchange."""
+    R, N = sim.shape
+    if sim.dtype != torch.float32 or labels.dtype != torch.int64 or labels.numel() != N or N > KNN_MAX_CANDIDATES:
+        raise ValueError("fp32 similarities [R, N <= 4096] and N int64 labels expected")
+    sc, lc = sim.contiguous(), labels.reshape(-1).contiguous()
+    pairs = sims = votes = None
+    if classes is None:
+        pairs = torch.empty((R, k, 2), dtype=torch.float32, device=sim.device)
+    else:
+        sims = torch.empty((R, k), dtype=torch.float32, device=sim.device)
+        votes = torch.empty((R, classes), dtype=torch.float32, device=sim.device)
+    nv.check(nv.cuda_lib().pkb_knn_topk(nv.ptr(sc), nv.ptr(lc), nv.c_ll(R), nv.c_ll(N), nv.c_ll(0), 1, N, 1, k, classes or 0,
+                                        nv.ptr(pairs) if pairs is not None else None, nv.ptr(sims) if sims is not None else None,
+                                        nv.ptr(votes) if votes is not None else None, nv.current_stream()), "pkb_knn_topk")
+    nv.count_launch()
+    return pairs if classes is None else (sims, votes)
+
+
+def knn_merge_votes(lists: torch.Tensor, k: int, classes: int):
+    """Merge the candidate lists of all ranks (reference: reference/79_dinov2_distributed_knn.py:43-65): ``lists``
+    [W, Q, k', 2] fp32 pairs as the exchange delivered them. Returns the ``k`` best similarities [Q, k] and the votes [Q, classes]."""
+    W, Q, kk, two = lists.shape
+    if lists.dtype != torch.float32 or two != 2 or W * kk > KNN_MAX_CANDIDATES:
+        raise ValueError("fp32 pairs [W, Q, k, 2] with W * k <= 4096 expected")
+    lc = lists.contiguous()
+    sims = torch.empty((Q, k), dtype=torch.float32, device=lists.device)
+    votes = torch.empty((Q, classes), dtype=torch.float32, device=lists.device)
+    nv.check(nv.cuda_lib().pkb_knn_topk(nv.ptr(lc), None, nv.c_ll(Q), nv.c_ll(kk * 2), nv.c_ll(Q * kk * 2), W, kk, 2, k, classes, None,
+                                        nv.ptr(sims), nv.ptr(votes), nv.current_stream()), "pkb_knn_topk")
+    nv.count_launch()
+    return sims, votes
+
+
+def mask_iou_suppress(logits: torch.Tensor, last: torch.Tensor, threshold: float, reverse: bool = False) -> torch.Tensor:
+    """Which of the ``n`` masks are suppressed by an overlapping mask that was occluded less recently
+    (reference: reference/81_sam3_allgather_iou_suppression.py:30-48). ``logits`` [n, H, W] fp32 (a mask is ``logits > 0``),
+    ``last`` int64 [n]. Returns a bool vector [n]. The masks are packed to one bit per pixel; the pairwise pass counts bits."""
+    n = logits.shape[0]
+    hw = logits[0].numel()
+    if logits.dtype != torch.float32 or last.dtype != torch.int64 or last.numel() != n or hw % 32 != 0:
+        raise ValueError("fp32 logits [n, H, W] with H * W a multiple of 32 and n int64 occlusion indices expected")
+    lc, lastc = logits.contiguous(), last.contiguous()
+    bits = torch.empty((n, hw // 32), dtype=torch.int32, device=logits.device)
+    area = torch.empty(n, dtype=torch.int32, device=logits.device)
+    sup = torch.zeros(n, dtype=torch.int32, device=logits.device)
+    nv.check(nv.cuda_lib().pkb_mask_iou_suppress(nv.ptr(lc), nv.ptr(lastc), nv.ptr(bits), nv.ptr(area), nv.ptr(sup), n, hw,
+                                                 ctypes.c_double(threshold), int(bool(reverse)), nv.current_stream()), "pkb_mask_iou_suppress")
+    nv.count_launch(2 if n > 1 else 1)
+    return sup.bool()

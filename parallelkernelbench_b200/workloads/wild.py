@@ -1281,6 +1281,17 @@ def _knn_ours(rc, test, train_t, labels, k, classes):
         sim = gemm_bf16_kn(allq.contiguous(), train_t.contiguous(), out_dtype=torch.float32)
     else:
         sim = allq.float() @ train_t.float()
+    if rc.dist.is_cuda and sim.shape[1] <= 4096 and W * k <= 4096 and classes <= 4096:
+        from ..ops.wild import knn_merge_votes, knn_topk_local
+
+        # one block per query sorts its candidates in shared memory; the k best leave as (similarity, label) pairs in the
+        # layout of the exchange, and the merge on the owner writes similarities and votes from the same kernel
+        if W == 1:
+            s1, v1 = knn_topk_local(sim.float(), labels, k, classes)
+            return {"sims": s1, "votes": v1}
+        got = rc.comm.all_to_all(knn_topk_local(sim.float(), labels, k).view(W, Q, k, 2))
+        s1, v1 = knn_merge_votes(got, k, classes)
+        return {"sims": s1, "votes": v1}
     sims, idx = sim.topk(k, dim=1)
     lab = labels.expand(sims.shape[0], -1).gather(1, idx)
     if W > 1:
@@ -1377,6 +1388,11 @@ def _sam(rc, masks, scores, counts, last, thr, ours):
         return torch.cat([allp[s, :counts[s]] for s in range(W)])
     mg, sg = gv(masks), gv(scores)
     n = mg.shape[0]
+    if ours and rc.dist.is_cuda and mg[0].numel() % 32 == 0:
+        from ..ops.wild import mask_iou_suppress
+
+        sup = mask_iou_suppress(mg, last, thr)                     # bit-packed masks, one block per pair
+        return {"masks": torch.where(sup.view(n, 1, 1), torch.full_like(mg, -10.0), mg), "scores": sg, "suppressed": sup}
     b = (mg > 0).flatten(1).float()
     inter = b @ b.t()
     area = b.sum(1)

@@ -62,3 +62,57 @@ def test_sinkhorn_knopp_matches_the_matrix_rewriting_form(B, P):
     out2 = sinkhorn_knopp(t, temp, iters, all_reduce=lambda x: x * 2)
     torch.testing.assert_close(out2.double(), rewrite(2), atol=1e-9, rtol=1e-4)
     assert torch.equal(out, sinkhorn_knopp(t, temp, iters))               # fixed summation orders: bit-reproducible
+
+
+@pytest.mark.parametrize("R,N,k,classes", [(32, 2048, 200, 1000), (5, 300, 7, 10), (3, 4096, 4096, 50), (2, 2, 1, 3)])
+def test_knn_topk_matches_library_topk_and_votes(R, N, k, classes):
+    from parallelkernelbench_b200.ops.wild import knn_merge_votes, knn_topk_local
+
+    g = torch.Generator(device="cuda").manual_seed(R * N + k)
+    sim = torch.randn(R, N, device="cuda", generator=g)
+    labels = torch.randint(0, classes, (1, N), device="cuda", generator=g)
+    top, idx = sim.topk(k, dim=1)
+    lab = labels.expand(R, -1).gather(1, idx)
+    votes = torch.zeros(R, classes, device="cuda").scatter_add_(1, lab, torch.ones_like(top)) / k
+    s1, v1 = knn_topk_local(sim, labels, k, classes)
+    assert torch.equal(s1, top)                                       # a selection: the values are the inputs themselves
+    torch.testing.assert_close(v1, votes, atol=1e-6, rtol=1e-6)
+    pairs = knn_topk_local(sim, labels, k)
+    assert torch.equal(pairs[..., 0], top) and torch.equal(pairs[..., 1].long().sort(1).values, lab.sort(1).values)
+    # merge of W candidate lists, laid out [W, Q, k, 2] as the exchange delivers them
+    W, kk = 4, min(k, 4096 // 4)
+    lists = torch.stack([torch.randn(R, kk, device="cuda", generator=g), torch.randint(0, classes, (R, kk), device="cuda", generator=g).float()], -1)
+    lists = torch.stack([lists + 0.001 * s for s in range(W)])        # [W, R, kk, 2]; labels shifted too, rounded again below
+    lists[..., 1] = lists[..., 1].round().clamp(0, classes - 1)
+    s_all = lists[..., 0].permute(1, 0, 2).reshape(R, W * kk)
+    l_all = lists[..., 1].permute(1, 0, 2).reshape(R, W * kk).long()
+    km = min(k, W * kk)
+    top2, ti = s_all.topk(km, dim=1)
+    lab2 = l_all.gather(1, ti)
+    votes2 = torch.zeros(R, classes, device="cuda").scatter_add_(1, lab2, torch.ones_like(top2)) / km
+    s2, v2 = knn_merge_votes(lists, km, classes)
+    assert torch.equal(s2, top2)
+    torch.testing.assert_close(v2, votes2, atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("n,H,W", [(9, 256, 256), (5, 8, 8), (1, 8, 4), (24, 64, 32)])
+def test_mask_iou_suppression_matches_the_matrix_form(n, H, W):
+    from parallelkernelbench_b200.ops.wild import mask_iou_suppress
+
+    g = torch.Generator(device="cuda").manual_seed(n * H + W)
+    base = torch.randn(-(-n // 3), H, W, device="cuda", generator=g)
+    masks = base.repeat_interleave(3, 0)[:n].clone()
+    masks = masks + 0.35 * torch.randn(masks.shape, device="cuda", generator=g)      # groups of three heavily overlapping masks
+    last = torch.randint(-1, 4, (n,), device="cuda", generator=g)
+    for thr in (0.7, 0.4):
+        for reverse in (False, True):
+            b = (masks > 0).flatten(1).float()
+            inter = b @ b.t()
+            area = b.sum(1)
+            iou = inter / (area[:, None] + area[None, :] - inter).clamp_min(1.0)
+            over = torch.triu(iou >= thr, diagonal=1)
+            li, lj = last.view(n, 1), last.view(1, n)
+            cmp = torch.lt if reverse else torch.gt
+            want = (over & cmp(li, lj) & (lj > -1)).any(1) | (over & cmp(lj, li) & (li > -1)).any(0)
+            got = mask_iou_suppress(masks, last, thr, reverse)
+            assert torch.equal(got, want), (thr, reverse, got.tolist(), want.tolist())
