@@ -188,3 +188,19 @@ def mask_iou_suppress(logits: torch.Tensor, last: torch.Tensor, threshold: float
                                                  ctypes.c_double(threshold), int(bool(reverse)), nv.current_stream()), "pkb_mask_iou_suppress")
     nv.count_launch(2 if n > 1 else 1)
     return sup.bool()
+
+
+def siglip_loss_from_products(prod: torch.Tensor, scale: float, bias: float, diag_offset: int) -> torch.Tensor:
+    """Sigmoid contrastive loss of this rank's images against all text blocks (reference: reference/58_openclip_contrastive_loss.py):
+    ``prod`` [B, N] fp32 are the raw image-text products, the matching text of image ``i`` is column ``diag_offset + i``.
+    Returns ``-sum logsigmoid(label * (scale * prod + bias)) / B`` as a 0-dim tensor; one pass over ``prod``."""
+    B, N = prod.shape
+    if prod.dtype != torch.float32 or not prod.is_cuda:
+        raise TypeError("fp32 CUDA products expected")
+    pc = prod.contiguous()
+    blocks = min(B, 592)
+    partial = torch.empty(blocks, dtype=torch.float32, device=prod.device)
+    nv.check(nv.cuda_lib().pkb_siglip_loss_partials(nv.ptr(pc), nv.ptr(partial), B, N, diag_offset, ctypes.c_double(scale), ctypes.c_double(bias),
+                                                    blocks, nv.current_stream()), "pkb_siglip_loss_partials")
+    nv.count_launch()
+    return partial.sum()

@@ -81,6 +81,10 @@ def _siglip_ours(rc, img, txt, scale, bias):
     W, r = rc.world, rc.rank
     B = img.shape[0]
     allt = rc.comm.all_gather(txt.contiguous()).reshape(W * B, -1) if W > 1 else txt
+    if rc.dist.is_cuda:
+        from ..ops.wild import siglip_loss_from_products
+
+        return siglip_loss_from_products(_mm_nt(rc, img, allt, out_f32=True), scale, bias, r * B)   # the whole epilogue in one pass
     logits = _mm_nt(rc, img, allt, out_f32=True) * scale + bias
     sign = -torch.ones_like(logits)
     idx = torch.arange(B, device=img.device)

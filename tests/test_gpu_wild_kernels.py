@@ -116,3 +116,22 @@ def test_mask_iou_suppression_matches_the_matrix_form(n, H, W):
             want = (over & cmp(li, lj) & (lj > -1)).any(1) | (over & cmp(lj, li) & (li > -1)).any(0)
             got = mask_iou_suppress(masks, last, thr, reverse)
             assert torch.equal(got, want), (thr, reverse, got.tolist(), want.tolist())
+
+
+@pytest.mark.parametrize("B,W,r", [(128, 4, 2), (8, 1, 0), (700, 2, 1), (3, 3, 0)])
+def test_siglip_loss_epilogue_matches_logsigmoid_sum(B, W, r):
+    import torch.nn.functional as F
+
+    from parallelkernelbench_b200.ops.wild import siglip_loss_from_products
+
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + W)
+    prod = torch.randn(B, W * B, device="cuda", generator=g) * 0.6
+    scale, bias = 10.0, -10.0
+    logits = (scale * prod.double() + bias)
+    sign = -torch.ones_like(logits)
+    idx = torch.arange(B, device="cuda")
+    sign[idx, r * B + idx] = 1.0
+    want = -F.logsigmoid(sign * logits).sum() / B
+    got = siglip_loss_from_products(prod, scale, bias, r * B)
+    torch.testing.assert_close(got.double(), want, atol=1e-5, rtol=2e-5)
+    assert torch.equal(got, siglip_loss_from_products(prod, scale, bias, r * B))
