@@ -78,3 +78,56 @@ def test_fused_tp_objects_validate_shapes_before_touching_the_heap():
         GemvAllGather(None, 3, 64)
     with pytest.raises(ValueError, match="multiple of 8"):
         GemvAllGather(None, 1, 12)
+
+
+def test_small_kernel_entry_points_reject_bad_arguments_before_any_launch():
+    """The argument checks of the native entry points return an error code (and a message) before anything is launched,
+    so they run on a machine without a GPU; host memory stands in for the tensors."""
+    import ctypes
+
+    from parallelkernelbench_b200 import _native as nv
+
+    lib = nv.cuda_lib()
+    buf = torch.zeros(64, dtype=torch.float64)
+    p, dbl, ll = nv.ptr(buf), ctypes.c_double, nv.c_ll
+    calls = {
+        "kalman_gain: no blocks": lambda: lib.pkb_kalman_gain(p, p, p, p, ll(0), 4, dbl(0.98), None),
+        "kalman_gain: null tensor": lambda: lib.pkb_kalman_gain(None, p, p, p, ll(1), 4, dbl(0.98), None),
+        "kalman_update: lambda zero": lambda: lib.pkb_kalman_update(p, p, p, p, p, p, p, ll(1), 4, dbl(0.0), None),
+        "sinkhorn_rowdot: temperature": lambda: lib.pkb_sinkhorn_rowdot(p, p, p, 4, 4, dbl(0.0), None),
+        "sinkhorn_coldot: more splits than rows": lambda: lib.pkb_sinkhorn_coldot(p, p, p, 4, 4, 5, dbl(0.07), None),
+        "sinkhorn_coldot: an empty split": lambda: lib.pkb_sinkhorn_coldot(p, p, p, 10, 4, 8, dbl(0.07), None),
+        "sinkhorn_scale: null tensor": lambda: lib.pkb_sinkhorn_scale(None, p, p, p, 4, 4, dbl(0.07), None),
+        "knn_topk: dense without labels": lambda: lib.pkb_knn_topk(p, None, ll(1), ll(8), ll(0), 1, 8, 1, 2, 0, p, None, None, None),
+        "knn_topk: too many candidates": lambda: lib.pkb_knn_topk(p, p, ll(1), ll(8192), ll(0), 1, 8192, 1, 2, 0, p, None, None, None),
+        "knn_topk: k beyond the candidates": lambda: lib.pkb_knn_topk(p, p, ll(1), ll(8), ll(0), 1, 8, 1, 9, 0, p, None, None, None),
+        "knn_topk: no output": lambda: lib.pkb_knn_topk(p, p, ll(1), ll(8), ll(0), 1, 8, 1, 2, 0, None, None, None, None),
+        "knn_topk: votes without classes": lambda: lib.pkb_knn_topk(p, p, ll(1), ll(8), ll(0), 1, 8, 1, 2, 0, None, p, p, None),
+        "mask_iou: pixels not a multiple of 32": lambda: lib.pkb_mask_iou_suppress(p, p, p, p, p, 2, 33, dbl(0.7), 0, None),
+        "siglip: matching pairs outside the matrix": lambda: lib.pkb_siglip_loss_partials(p, p, 4, 4, 1, dbl(10.0), dbl(-10.0), 4, None),
+        "siglip: more blocks than rows": lambda: lib.pkb_siglip_loss_partials(p, p, 4, 8, 0, dbl(10.0), dbl(-10.0), 5, None),
+    }
+    for what, call in calls.items():
+        rc = call()
+        msg = lib.pkb_last_error()
+        assert rc != 0 and b"bad argument" in msg, (what, rc, msg)
+
+
+def test_small_kernel_wrappers_reject_malformed_tensors():
+    from parallelkernelbench_b200.ops import wild
+
+    with pytest.raises(TypeError):
+        wild.kalman_block_step(torch.zeros(1, 4, 1), torch.zeros(1), torch.zeros(1, 4, 1), torch.zeros(1, 4, 4), 0.98)     # fp32, CPU
+    with pytest.raises(TypeError):
+        wild.sinkhorn_knopp(torch.zeros(4, 4), 0.07, 3)
+    with pytest.raises(ValueError):
+        wild.knn_topk_local(torch.zeros(2, 8), torch.zeros(7, dtype=torch.int64), 2)
+    with pytest.raises(ValueError):
+        wild.knn_topk_local(torch.zeros(2, 5000), torch.zeros(5000, dtype=torch.int64), 2)
+    with pytest.raises(ValueError):
+        wild.knn_merge_votes(torch.zeros(4, 2, 2000, 2), 5, 10)
+    with pytest.raises(ValueError):
+        wild.mask_iou_suppress(torch.zeros(2, 3, 11), torch.zeros(2, dtype=torch.int64), 0.7)
+    with pytest.raises(TypeError):
+        wild.siglip_loss_from_products(torch.zeros(4, 4), 10.0, -10.0, 0)
+    assert wild._sk_splits(1024) == (32, 32) and wild._sk_splits(10) == (10, 1) and wild._sk_splits(40) == (20, 2) and wild._sk_splits(1) == (1, 1)
