@@ -536,7 +536,11 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   // keeps 160 KiB in flight per CTA, so a few CTAs fill the link and the rest of the SMs stay with the GEMM.
   static const bool bulk_off = [] { const char* e = getenv("PKB_TP_BULK_PUSH"); return e != nullptr && e[0] == '0'; }();
   a.bulk_push = (!bulk_off && a.sub_bytes % 16 == 0 && (reinterpret_cast<uintptr_t>(x_local) & 15) == 0) ? 1 : 0;
-  if (comm_ctas <= 0) comm_ctas = a.bulk_push ? (W > 1 ? 8 : 2) : (W >= 8 ? 16 : (W > 1 ? 8 : 2));
+  // Number of communication CTAs: a bulk-push CTA sustains about 36 GB/s (measured at 4 ranks: 4 CTAs made the GEMM's
+  // producers wait 169 us per call for 96 MiB of remote rows, 8 CTAs 2 us), and the GEMM consumes one remote shard per
+  // 1/W of its run time, so the rate the push needs grows with W while the shard size stays: 8 CTAs cover a 32 MiB shard in
+  // 115 us, which is enough up to 4 ranks (175 us per shard of GEMM time) and not at 8 ranks (87 us), where 16 are used.
+  if (comm_ctas <= 0) comm_ctas = a.bulk_push ? (W >= 8 ? 16 : (W > 4 ? 12 : (W > 1 ? 8 : 2))) : (W >= 8 ? 16 : (W > 1 ? 8 : 2));
   comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
   const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");
