@@ -86,7 +86,8 @@ class LocalTransport:
 
 class SshTransport:
     """The spool lives on another host, reached by SFTP (paramiko; key-based login as configured for ``ssh``). Only the four
-    operations of ``LocalTransport`` are needed. Not exercised by the test-suite (it needs an SSH server)."""
+    operations of ``LocalTransport`` are needed. The test-suite runs this class against a stand-in SFTP client; a real
+    connection needs an SSH server."""
 
     def __init__(self, target: str, root: str, port: int = 22):
         import paramiko

@@ -51,3 +51,106 @@ def test_candidate_is_screened_before_it_is_sent(tmp_path, monkeypatch):
     job = runner.run_job("allreduce", "file", 2, solution=str(cand), backend="gloo")
     assert job["returncode"] == 2 and "rejected" in job["stderr"]
     assert os.listdir(os.path.join(spool, "incoming")) == []            # nothing was submitted
+
+
+class _FakeSftp:
+    """The subset of paramiko's SFTP client the transport uses, mapped onto a local directory that plays the remote host."""
+
+    def __init__(self, host_root):
+        self.host_root = host_root
+
+    def _l(self, path):
+        return os.path.join(self.host_root, path.lstrip("/"))
+
+    def stat(self, path):
+        return os.stat(self._l(path))
+
+    def mkdir(self, path):
+        os.mkdir(self._l(path))
+
+    def open(self, path, mode="r"):
+        return open(self._l(path), mode + "b")
+
+    def posix_rename(self, src, dst):
+        os.replace(self._l(src), self._l(dst))
+
+    def listdir_attr(self, path):
+        out = []
+        for name in os.listdir(self._l(path)):
+            st = os.stat(os.path.join(self._l(path), name))
+            out.append(type("Attr", (), {"filename": name, "st_mode": st.st_mode})())
+        return out
+
+    def get(self, remote, local):
+        import shutil
+
+        shutil.copyfile(self._l(remote), local)
+
+    def remove(self, path):
+        os.remove(self._l(path))
+
+    def rmdir(self, path):
+        os.rmdir(self._l(path))
+
+
+class _FakeFile:
+    def __init__(self, fh):
+        self.fh = fh
+
+    def write(self, data):
+        self.fh.write(data.encode("utf-8") if isinstance(data, str) else data)
+
+    def read(self):
+        return self.fh.read()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.fh.close()
+
+
+def test_sftp_transport_against_a_fake_sftp_client(tmp_path, monkeypatch):
+    """The SSH transport's own logic (remote mkdir -p, atomic put, recursive fetch and removal) over a stand-in SFTP client."""
+    import paramiko
+
+    host_root = tmp_path / "remote_host"
+    host_root.mkdir()
+    sftp = _FakeSftp(str(host_root))
+    real_open = sftp.open
+    sftp.open = lambda path, mode="r": _FakeFile(real_open(path, mode))
+    seen = {}
+
+    class FakeClient:
+        def load_system_host_keys(self):
+            seen["host_keys"] = True
+
+        def set_missing_host_key_policy(self, policy):
+            seen["policy"] = type(policy).__name__
+
+        def connect(self, host, port=22, username=None):
+            seen["connect"] = (host, port, username)
+
+        def open_sftp(self):
+            return sftp
+
+    monkeypatch.setattr(paramiko, "SSHClient", FakeClient)
+    monkeypatch.setattr(launch, "LOGS_ROOT", str(tmp_path / "logs"))
+    tr = remote.SshTransport("bench@gpubox", "/scratch/spool", port=2222)
+    assert seen == {"host_keys": True, "policy": "RejectPolicy", "connect": ("gpubox", 2222, "bench")}     # unknown hosts are refused
+    spool_on_host = str(host_root / "scratch" / "spool")
+    assert sorted(os.listdir(spool_on_host)) == ["done", "incoming", "running"]
+    tr.put_text_atomic("incoming/j1.json", json.dumps({"op": "no_such_op", "impl": "ours", "nproc": 1, "backend": "gloo", "timeout_s": 60}))
+    assert os.listdir(os.path.join(spool_on_host, "incoming")) == ["j1.json"]                              # no temporary name left behind
+    assert remote.serve(spool_on_host, once=True, log=lambda *_: None) == 1                               # the worker runs on the "host"
+    res = json.loads(tr.get_text("done/j1/result.json"))
+    assert res["returncode"] != 0 and res["job_id"] == "j1"
+    os.makedirs(os.path.join(spool_on_host, "done", "j1", "artifacts", "traces"), exist_ok=True)
+    for rel in ("rank_0.pt", "traces/rank_0.json"):
+        with open(os.path.join(spool_on_host, "done", "j1", "artifacts", rel), "w") as fh:
+            fh.write("x")
+    got = tr.fetch_tree("done/j1/artifacts", str(tmp_path / "fetched"))
+    assert got == ["rank_0.pt", "traces/rank_0.json"] and os.path.exists(tmp_path / "fetched" / "traces" / "rank_0.json")
+    assert tr.get_text("done/missing/result.json") is None
+    tr.remove_tree("done/j1")
+    assert os.listdir(os.path.join(spool_on_host, "done")) == []
