@@ -294,11 +294,29 @@ def cmd_list(_args) -> int:
     return 0
 
 
+def _overrides(a) -> dict:
+    """``--set key=value`` pairs plus the reference launcher's two size knobs: ``--m`` / ``--n`` set the keys ``m`` / ``n`` of
+    the op's config where it has them (reference: run_local.py:517-518; ops whose sizes have other names say so)."""
+    from ..workloads import registry
+
+    out = registry.parse_overrides(a.set)
+    cfg = registry.get(a.op).configs.get(a.config, {})
+    for key in ("m", "n"):
+        val = getattr(a, key, None)
+        if val is None:
+            continue
+        if key in cfg:
+            out.setdefault(key, val)
+        else:
+            print(f"note: --{key} ignored: config {a.config!r} of {registry.get(a.op).name} has no key {key!r} (keys: {', '.join(sorted(cfg))})")
+    return out
+
+
 def cmd_run(a) -> int:
     from ..workloads import registry
 
     job = run_job(registry.get(a.op).name, a.impl, a.nproc, trial=a.trial, config=a.config,
-                  overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, measure_perf=a.measure_perf,
+                  overrides=_overrides(a), dtype=a.dtype, backend=a.backend, measure_perf=a.measure_perf,
                   warmup=a.warmup, iters=a.iters, graph=a.graph, profile=a.profile, timeout_s=a.timeout,
                   extra_worker_args=["--determinism", str(a.determinism)] if a.determinism > 0 else None)
     ok = job["returncode"] == 0 and job["artifact_count"] == a.nproc
@@ -328,7 +346,7 @@ def cmd_eval(a) -> int:
 
         runner = remote.make_runner(a.remote_spool, ssh=a.remote_ssh, wait_s=a.remote_wait).run_job
     s = eval_op(a.op, a.nproc, trials=a.trials, atol=a.atol, rtol=a.rtol, measure_perf=a.measure_perf, config=a.config,
-                overrides=registry.parse_overrides(a.set), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
+                overrides=_overrides(a), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
                 graph=a.graph, profile=a.profile, timeout_s=a.timeout, solution=a.solution, runner=runner)
     if s["interrupted"]:
         return 130
@@ -452,12 +470,14 @@ def cmd_perf_diff(a) -> int:
 
 
 def _common(sp, need_impl=False):
-    sp.add_argument("--op", required=True)
+    sp.add_argument("--op", "--problem", dest="op", required=True, help="op name or the reference's problem number")
     if need_impl:
         sp.add_argument("--impl", default="ours", choices=["reference", "ours", "oracle"])
-    sp.add_argument("--nproc", "--nproc-per-node", dest="nproc", type=int, default=1)
+    sp.add_argument("--nproc", "--nproc-per-node", "--num-gpus", dest="nproc", type=int, default=1)
     sp.add_argument("--config", default="default")
     sp.add_argument("--set", action="append", default=[])
+    sp.add_argument("--m", type=int, default=None, help="shorthand for --set m=M on ops whose config has that key")
+    sp.add_argument("--n", type=int, default=None, help="shorthand for --set n=N on ops whose config has that key")
     sp.add_argument("--dtype", default="bfloat16")
     sp.add_argument("--backend", default=None, choices=[None, "nccl", "gloo"])
     sp.add_argument("--measure-perf", action="store_true")
@@ -472,6 +492,7 @@ def _common(sp, need_impl=False):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="parallelkernelbench_b200.harness.launch", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--logs-dir", default=None, help="base directory of job directories, kept artifacts and ledgers (default: PKB_LOGS_DIR or <repo>/logs)")
     sub = ap.add_subparsers(dest="verb", required=True)
     sp = sub.add_parser("list"); sp.set_defaults(fn=cmd_list)
     sp.add_argument("--tolerances", action="store_true", help="list the ops compared with a gate looser than 1e-2 / 1e-2, and why")
@@ -534,6 +555,9 @@ def main(argv=None) -> int:
         sp.add_argument("--max-print", type=int, default=8)
         sp.set_defaults(fn=fn)
     args = ap.parse_args(argv)
+    if args.logs_dir:
+        global LOGS_ROOT
+        LOGS_ROOT = os.path.abspath(args.logs_dir)
     try:
         return args.fn(args)
     except KeyboardInterrupt:

@@ -178,3 +178,27 @@ def test_fsdp_llama_step_is_an_explicit_only_op_whose_reference_runs_on_cpu():
     assert abs(float(loss.reshape(-1)[0]) - math.log(1024)) < 0.5
     c = spec.cost(spec.configs["llama8b"], 8)
     assert 1.5e14 < c.flops < 3e14 and c.nvlink_bytes > 1e10
+
+
+def test_reference_style_flags_are_accepted(tmp_path, capsys, monkeypatch):
+    """--problem / --num-gpus / --m / --n / --logs-dir: the spelling of the reference's launcher maps onto op, nproc, config
+    overrides and the log root."""
+    from parallelkernelbench_b200.harness import launch
+
+    monkeypatch.setattr(launch, "LOGS_ROOT", launch.LOGS_ROOT)          # restored after the test: --logs-dir rebinds it
+    logs = tmp_path / "my_logs"
+    rc = launch.main(["--logs-dir", str(logs), "run", "--problem", "1", "--num-gpus", "1", "--backend", "gloo", "--dtype", "float32",
+                      "--config", "small", "--m", "4", "--n", "32"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "dry run ok" in out
+    kept = logs / "op_allreduce" / "w1" / "ours" / "trial_0"
+    assert (kept / "rank_0.pt").exists()
+    import torch
+
+    y = torch.load(kept / "rank_0.pt")
+    shape = tuple((y["output"] if isinstance(y, dict) and "output" in y else y).shape) if not isinstance(y, (list, tuple)) else None
+    assert shape is None or shape == (4, 32), shape                       # the size knobs reached the input factory
+    rc = launch.main(["--logs-dir", str(logs), "run", "--problem", "80", "--num-gpus", "1", "--backend", "gloo", "--dtype", "float32",
+                      "--config", "small", "--m", "4"])
+    out = capsys.readouterr().out
+    assert rc == 0 and "--m ignored" in out and "prototypes" in out
