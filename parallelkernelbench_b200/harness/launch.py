@@ -340,6 +340,11 @@ def cmd_run(a) -> int:
 def cmd_eval(a) -> int:
     from ..workloads import registry
 
+    if a.solutions_dir and not a.solution:
+        a.solution = os.path.join(a.solutions_dir, f"{registry.get(a.op).name}.py")     # the naming rule of ``sweep --solutions-dir``
+        if not os.path.isfile(a.solution):
+            print(f"no candidate file {a.solution}")
+            return 2
     runner = None
     if a.remote_spool:
         from . import remote
@@ -502,6 +507,7 @@ def main(argv=None) -> int:
     sp = sub.add_parser("eval"); _common(sp)
     sp.add_argument("--trials", type=int, default=5)
     sp.add_argument("--solution", default=None, help="evaluate this file's solution(rc, *inputs) instead of the built-in implementation")
+    sp.add_argument("--solutions-dir", default=None, help="evaluate DIR/<op>.py (used when --solution is not given)")
     sp.add_argument("--atol", type=float, default=None)
     sp.add_argument("--rtol", type=float, default=None)
     sp.add_argument("--remote-spool", default=None, help="run the jobs through the queue in this spool directory (see harness/remote.py)")
