@@ -1,12 +1,13 @@
 """python -m parallelkernelbench_b200.kernelgen prompt --op OP|13|all|[a,b] [--out-dir DIR] | replay --op OP --candidates DIR |
-generate --op OP --command "CMD" (CMD reads the prompt on stdin and prints a candidate)"""
+generate --op OP --command "CMD" (CMD reads the prompt on stdin and prints a candidate) |
+generate --op OP --endpoint http://host:8000/v1 --model NAME (a chat-completions endpoint; key from $PKB_KERNELGEN_API_KEY)"""
 import argparse
 import json
 import sys
 
 import os
 
-from . import CommandProposer, ReplayProposer, build_prompt, optimise
+from . import CommandProposer, HttpProposer, ReplayProposer, build_prompt, optimise
 from .prompt import select_ops
 
 
@@ -29,7 +30,11 @@ def main(argv=None) -> int:
     r.add_argument("--config", default="default")
     g = sub.add_parser("generate", help="run the loop with a command that reads the prompt on stdin and prints a candidate")
     g.add_argument("--op", required=True)
-    g.add_argument("--command", required=True, help="e.g. 'python my_model_runner.py' (prompt on stdin, reply on stdout)")
+    g.add_argument("--command", default=None, help="e.g. 'python my_model_runner.py' (prompt on stdin, reply on stdout)")
+    g.add_argument("--endpoint", default=None, help="base URL of a chat-completions endpoint, e.g. http://127.0.0.1:8000/v1")
+    g.add_argument("--model", default=None, help="model name sent to --endpoint")
+    g.add_argument("--api-key-env", default="PKB_KERNELGEN_API_KEY", help="environment variable holding the endpoint's key, if it needs one")
+    g.add_argument("--max-tokens", type=int, default=16384)
     g.add_argument("--workdir", default="logs/kernelgen")
     g.add_argument("--nproc", type=int, default=2)
     g.add_argument("--max-iters", type=int, default=4)
@@ -57,8 +62,13 @@ def main(argv=None) -> int:
         return 0
     if a.cmd == "generate":
         rc = 0
+        if bool(a.command) == bool(a.endpoint) or (a.endpoint and not a.model):
+            ap.error("generate needs exactly one of --command or --endpoint (the latter with --model)")
         for op in select_ops(a.op):
-            out = optimise(op, CommandProposer(a.command, log_dir=os.path.join(a.workdir, f"{op}_exchanges")), a.workdir,
+            log_dir = os.path.join(a.workdir, f"{op}_exchanges")
+            proposer = (CommandProposer(a.command, log_dir=log_dir) if a.command else
+                        HttpProposer(a.endpoint, a.model, api_key_env=a.api_key_env, max_tokens=a.max_tokens, log_dir=log_dir))
+            out = optimise(op, proposer, a.workdir,
                            nproc=a.nproc, max_iters=a.max_iters, backend=a.backend, dtype=a.dtype, config=a.config,
                            resume=a.resume, measure_perf=a.measure_perf)
             print(json.dumps(out, indent=1))

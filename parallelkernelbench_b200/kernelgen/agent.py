@@ -57,6 +57,48 @@ class CommandProposer:
         return extract_code(res.stdout)
 
 
+class HttpProposer:
+    """Asks a chat-completions endpoint for the next candidate: ``POST <base_url>/chat/completions`` with the usual
+    ``{"model", "messages", "max_tokens", "temperature"}`` body, the reply read from ``choices[0].message.content``. That is
+    the wire format of the hosted providers the reference talks to through their SDKs (reference:
+    kernelgen/generate_kernel.py:390-488) and of model servers one can run next to the GPUs, so no SDK is needed; the key,
+    if the endpoint wants one, comes from the environment variable named by ``api_key_env``. Feedback from the previous
+    attempt is already part of the prompt text."""
+
+    SYSTEM = ("You write one Python file that defines solution(rc, *inputs) for the distributed GPU workload described by the "
+              "user. Reply with a single fenced python block and nothing that needs to be executed outside it.")
+
+    def __init__(self, base_url: str, model: str, api_key_env: str | None = "PKB_KERNELGEN_API_KEY", max_tokens: int = 16384,
+                 temperature: float = 0.2, timeout_s: float = 900.0, log_dir: str | None = None):
+        self.url = base_url.rstrip("/") + "/chat/completions"
+        self.model, self.api_key_env, self.max_tokens, self.temperature = model, api_key_env, max_tokens, temperature
+        self.timeout_s, self.log_dir, self.calls = timeout_s, log_dir, 0
+
+    def __call__(self, prompt: str, feedback: str | None) -> str:
+        import requests
+
+        headers = {"Content-Type": "application/json"}
+        key = os.environ.get(self.api_key_env or "", "")
+        if key:
+            headers["Authorization"] = f"Bearer {key}"
+        body = {"model": self.model, "max_tokens": self.max_tokens, "temperature": self.temperature,
+                "messages": [{"role": "system", "content": self.SYSTEM}, {"role": "user", "content": prompt}]}
+        try:
+            resp = requests.post(self.url, headers=headers, json=body, timeout=self.timeout_s)
+            status, text = resp.status_code, resp.text
+            reply = resp.json()["choices"][0]["message"]["content"] if status == 200 else ""
+        except (requests.RequestException, ValueError, KeyError, IndexError, TypeError) as e:
+            status, text, reply = -1, f"{type(e).__name__}: {e}", ""
+        if self.log_dir:
+            os.makedirs(self.log_dir, exist_ok=True)
+            with open(os.path.join(self.log_dir, f"exchange_{self.calls}.json"), "w") as fh:     # the key is never written
+                json.dump({"url": self.url, "model": self.model, "status": status, "prompt": prompt, "reply": reply or text[-4000:]}, fh)
+        self.calls += 1
+        if not (reply or "").strip():
+            raise StopIteration(f"endpoint gave no usable reply (status {status}): {text[-300:]}")
+        return extract_code(reply)
+
+
 def _feedback(summary: dict) -> str:
     t = summary["trials"][-1] if summary.get("trials") else {}
     lines = [f"verdict: {t.get('result', 'no result')}"]

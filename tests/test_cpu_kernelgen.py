@@ -116,3 +116,56 @@ def test_loop_screens_candidates_keeps_a_trajectory_and_resumes(tmp_path):
     more = optimise("allreduce", lambda p, f: good, str(tmp_path), nproc=2, max_iters=1, backend="gloo", dtype="float32",
                     config="small", resume=True)
     assert [a["iteration"] for a in more["attempts"]] == [0, 1, 2] and more["solved"]
+
+
+def test_http_proposer_talks_to_a_chat_completions_endpoint(tmp_path, monkeypatch):
+    """A local HTTP server stands in for the model endpoint: first reply wrong, second right (prose around a fenced block);
+    the key goes out as a bearer token and is not written to the exchange log."""
+    import json
+    import threading
+    from http.server import BaseHTTPRequestHandler, HTTPServer
+
+    from parallelkernelbench_b200.kernelgen import HttpProposer, optimise
+
+    replies = ["Here you go:\n```python\ndef solution(rc, x):\n    return x * 2\n```\n",
+               "Fixed, the sum was missing.\n```python\ndef solution(rc, x):\n    return rc.comm.all_reduce(x)\n```\nDone."]
+    seen = []
+
+    class Handler(BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            seen.append({"path": self.path, "auth": self.headers.get("Authorization"), "model": body["model"],
+                         "roles": [m["role"] for m in body["messages"]], "user": body["messages"][-1]["content"]})
+            if len(seen) > len(replies):
+                self.send_response(500)
+                self.end_headers()
+                return
+            out = json.dumps({"choices": [{"message": {"role": "assistant", "content": replies[len(seen) - 1]}}]}).encode()
+            self.send_response(200)
+            self.send_header("Content-Type", "application/json")
+            self.send_header("Content-Length", str(len(out)))
+            self.end_headers()
+            self.wfile.write(out)
+
+        def log_message(self, *a):
+            pass
+
+    srv = HTTPServer(("127.0.0.1", 0), Handler)
+    th = threading.Thread(target=srv.serve_forever, daemon=True)
+    th.start()
+    monkeypatch.setenv("PKB_KERNELGEN_API_KEY", "sk-test-123")
+    try:
+        prop = HttpProposer(f"http://127.0.0.1:{srv.server_port}/v1", "local-model", log_dir=str(tmp_path / "ex"), timeout_s=30)
+        out = optimise("allreduce", prop, str(tmp_path / "work"), nproc=2, max_iters=3, backend="gloo", dtype="float32", config="small",
+                       timeout_s=300)
+        assert out["solved"] and len(out["attempts"]) == 2
+        assert [s["path"] for s in seen] == ["/v1/chat/completions"] * 2 and seen[0]["auth"] == "Bearer sk-test-123"
+        assert seen[0]["model"] == "local-model" and seen[0]["roles"] == ["system", "user"]
+        assert "Result of your previous attempt" in seen[1]["user"] and "Result of your previous attempt" not in seen[0]["user"]
+        logged = (tmp_path / "ex" / "exchange_0.json").read_text()
+        assert "sk-test-123" not in logged and "def solution" in logged
+        # an endpoint that fails ends the run instead of raising
+        out2 = optimise("allgather", prop, str(tmp_path / "work2"), nproc=2, max_iters=2, backend="gloo", dtype="float32", config="small")
+        assert not out2["solved"] and out2["attempts"] == []
+    finally:
+        srv.shutdown()
