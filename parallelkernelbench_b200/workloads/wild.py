@@ -427,7 +427,8 @@ def _allreduce_ref(t):
 register(OpSpec(name="kalman_filter_step", problem_ids=(63,), group="wild",
                 configs={"default": {"blocks": 8, "block": 1024}, "small": {"blocks": 2, "block": 16}},
                 make_inputs=_kalman_inputs, reference=lambda rc, *a: _kalman(rc, *a, ours=False), ours=lambda rc, *a: _kalman(rc, *a, ours=True),
-                atol=1e-9, rtol=1e-9))
+                atol=1e-9, rtol=1e-9,
+                cost=lambda cfg, W: Cost(hbm_bytes=3.0 * cfg["blocks"] * cfg["block"] ** 2 * 8)))   # P read twice, written once
 
 
 # =================================================================================================
@@ -1361,7 +1362,9 @@ def _sk_ours(rc, t, temp, iters):
 
 register(OpSpec(name="sinkhorn_knopp", problem_ids=(80,), group="wild",
                 configs={"default": {"batch": 1024, "prototypes": 16384}, "small": {"batch": 8, "prototypes": 32}},
-                make_inputs=_sk_inputs, reference=_sk_ref, ours=_sk_ours, atol=1e-7, rtol=1e-3))
+                make_inputs=_sk_inputs, reference=_sk_ref, ours=_sk_ours, atol=1e-7, rtol=1e-3,
+                # one pass for the mass, two per iteration (three iterations), one read and one write for the result
+                cost=lambda cfg, W: Cost(hbm_bytes=9.0 * cfg["batch"] * cfg["prototypes"] * 4, nvlink_bytes=3.0 * cfg["prototypes"] * 4 * (W - 1))))
 
 
 # =================================================================================================
