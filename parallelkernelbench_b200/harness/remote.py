@@ -239,8 +239,17 @@ def _serve_one(spool: str, job_id: str, payload: dict) -> dict:
 
 def serve(spool: str, once: bool = False, poll_s: float = 0.5, stop: threading.Event | None = None, log=print) -> int:
     """Queue worker: claim jobs from ``<spool>/incoming`` in name order, run them here, publish results. Returns the number of
-    jobs served (``once``: return after the first job or when the queue is empty)."""
+    jobs served (``once``: return after the first job or when the queue is empty). On start a worker also takes back jobs that
+    a previous worker of this spool had claimed and not finished (left in ``running/`` by a crash or a kill): they go back to
+    ``incoming/`` and run again, so a client waiting for them is not stranded."""
     LocalTransport(spool)                                               # creates the three directories
+    for n in sorted(os.listdir(os.path.join(spool, "running"))):
+        if n.endswith(".json") and not os.path.exists(os.path.join(spool, "done", n[:-5], "result.json")):
+            try:
+                os.replace(os.path.join(spool, "running", n), os.path.join(spool, "incoming", n))
+                log(f"[remote-worker] re-queued unfinished job {n[:-5]}")
+            except OSError:
+                pass
     served = 0
     while not (stop is not None and stop.is_set()):
         claimed = _claim(spool)
@@ -253,6 +262,16 @@ def serve(spool: str, once: bool = False, poll_s: float = 0.5, stop: threading.E
         log(f"[remote-worker] {job_id}: {payload.get('op')} / {payload.get('impl')} / nproc {payload.get('nproc')} / trial {payload.get('trial')}")
         res = _serve_one(spool, job_id, payload)
         log(f"[remote-worker] {job_id}: rc={res.get('returncode')} artifacts={res.get('artifact_count')}")
+        try:
+            # leftovers of a job that died (shared-memory segments whose owner is gone) must not meet the next job
+            # (reference: run_together/worker.py cleans up between jobs on the GPU side as well)
+            from . import hygiene
+
+            removed = hygiene.between_jobs().get("removed_segments") or []
+            if removed:
+                log(f"[remote-worker] removed {len(removed)} stale shared-memory segment(s)")
+        except Exception as e:                                          # hygiene is best effort
+            log(f"[remote-worker] hygiene failed: {type(e).__name__}: {e}")
         served += 1
         if once:
             break

@@ -154,3 +154,15 @@ def test_sftp_transport_against_a_fake_sftp_client(tmp_path, monkeypatch):
     assert tr.get_text("done/missing/result.json") is None
     tr.remove_tree("done/j1")
     assert os.listdir(os.path.join(spool_on_host, "done")) == []
+
+
+def test_a_restarted_worker_requeues_what_its_predecessor_left_unfinished(tmp_path, monkeypatch):
+    monkeypatch.setattr(launch, "LOGS_ROOT", str(tmp_path / "logs"))
+    spool = str(tmp_path / "spool")
+    tr = remote.LocalTransport(spool)
+    tr.put_text_atomic("running/orphan.json", json.dumps({"op": "no_such_op", "impl": "ours", "nproc": 1, "backend": "gloo", "timeout_s": 60}))
+    lines = []
+    assert remote.serve(spool, once=True, log=lines.append) == 1
+    assert any("re-queued unfinished job orphan" in ln for ln in lines)
+    assert json.loads(tr.get_text("done/orphan/result.json"))["job_id"] == "orphan"
+    assert os.listdir(os.path.join(spool, "running")) == []
