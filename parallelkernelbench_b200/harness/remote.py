@@ -27,6 +27,7 @@ import os
 import posixpath
 import secrets
 import shutil
+import socket
 import stat
 import tempfile
 import threading
@@ -175,6 +176,11 @@ def _claim(spool: str) -> tuple[str, dict] | None:
         except OSError:
             continue                                   # another worker was faster
         try:
+            with open(dst + ".owner", "w", encoding="utf-8") as fh:
+                fh.write(f"{socket.gethostname()} {os.getpid()}")
+        except OSError:
+            pass
+        try:
             with open(dst, encoding="utf-8") as fh:
                 return n[:-5], json.load(fh)
         except (OSError, ValueError) as e:
@@ -230,24 +236,50 @@ def _serve_one(spool: str, job_id: str, payload: dict) -> dict:
     with open(tmp, "w", encoding="utf-8") as fh:
         json.dump(result, fh)
     os.replace(tmp, os.path.join(out_dir, "result.json"))               # written last: its presence means "complete"
-    try:
-        os.remove(os.path.join(spool, "running", job_id + ".json"))
-    except OSError:
-        pass
+    for leftover in (job_id + ".json", job_id + ".json.owner"):
+        try:
+            os.remove(os.path.join(spool, "running", leftover))
+        except OSError:
+            pass
     return result
+
+
+def _owner_gone(owner_file: str) -> bool:
+    """True if the worker that claimed a job ran on this host and no longer exists (or left no record). A claim by a worker on
+    another host is left alone: this process cannot tell whether that worker is alive."""
+    try:
+        with open(owner_file, encoding="utf-8") as fh:
+            host, pid = fh.read().split()
+    except (OSError, ValueError):
+        return True
+    if host != socket.gethostname():
+        return False
+    try:
+        os.kill(int(pid), 0)
+    except ProcessLookupError:
+        return True
+    except (PermissionError, ValueError):
+        return False
+    return int(pid) == os.getpid()          # a claim by this very process from an earlier serve() call that was stopped
 
 
 def serve(spool: str, once: bool = False, poll_s: float = 0.5, stop: threading.Event | None = None, log=print) -> int:
     """Queue worker: claim jobs from ``<spool>/incoming`` in name order, run them here, publish results. Returns the number of
     jobs served (``once``: return after the first job or when the queue is empty). On start a worker also takes back jobs that
-    a previous worker of this spool had claimed and not finished (left in ``running/`` by a crash or a kill): they go back to
-    ``incoming/`` and run again, so a client waiting for them is not stranded."""
+    a worker on this host had claimed and not finished before it died (left in ``running/`` by a crash or a kill; the claim
+    records host and pid): they go back to ``incoming/`` and run again, so a client waiting for them is not stranded. Claims of
+    live workers, and of workers on other hosts, are left alone, so several workers can serve one spool."""
     LocalTransport(spool)                                               # creates the three directories
     for n in sorted(os.listdir(os.path.join(spool, "running"))):
-        if n.endswith(".json") and not os.path.exists(os.path.join(spool, "done", n[:-5], "result.json")):
+        path = os.path.join(spool, "running", n)
+        if n.endswith(".json") and not os.path.exists(os.path.join(spool, "done", n[:-5], "result.json")) and _owner_gone(path + ".owner"):
             try:
-                os.replace(os.path.join(spool, "running", n), os.path.join(spool, "incoming", n))
+                os.replace(path, os.path.join(spool, "incoming", n))
                 log(f"[remote-worker] re-queued unfinished job {n[:-5]}")
+            except OSError:
+                pass
+            try:
+                os.remove(path + ".owner")
             except OSError:
                 pass
     served = 0

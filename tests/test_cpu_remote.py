@@ -166,3 +166,21 @@ def test_a_restarted_worker_requeues_what_its_predecessor_left_unfinished(tmp_pa
     assert any("re-queued unfinished job orphan" in ln for ln in lines)
     assert json.loads(tr.get_text("done/orphan/result.json"))["job_id"] == "orphan"
     assert os.listdir(os.path.join(spool, "running")) == []
+
+
+def test_claims_of_live_or_foreign_workers_are_left_alone(tmp_path, monkeypatch):
+    import socket
+
+    monkeypatch.setattr(launch, "LOGS_ROOT", str(tmp_path / "logs"))
+    spool = str(tmp_path / "spool")
+    tr = remote.LocalTransport(spool)
+    payload = json.dumps({"op": "no_such_op", "impl": "ours", "nproc": 1, "backend": "gloo", "timeout_s": 60})
+    tr.put_text_atomic("running/live.json", payload)
+    tr.put_text_atomic("running/live.json.owner", f"{socket.gethostname()} {os.getppid()}")       # a process that exists
+    tr.put_text_atomic("running/elsewhere.json", payload)
+    tr.put_text_atomic("running/elsewhere.json.owner", "some-other-host 1")
+    tr.put_text_atomic("running/dead.json", payload)
+    tr.put_text_atomic("running/dead.json.owner", f"{socket.gethostname()} 2147483646")           # no such pid
+    assert remote.serve(spool, once=True, log=lambda *_: None) == 1
+    assert sorted(n for n in os.listdir(os.path.join(spool, "running")) if n.endswith(".json")) == ["elsewhere.json", "live.json"]
+    assert os.path.exists(os.path.join(spool, "done", "dead", "result.json"))
