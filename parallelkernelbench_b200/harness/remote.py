@@ -270,6 +270,13 @@ def serve(spool: str, once: bool = False, poll_s: float = 0.5, stop: threading.E
     records host and pid): they go back to ``incoming/`` and run again, so a client waiting for them is not stranded. Claims of
     live workers, and of workers on other hosts, are left alone, so several workers can serve one spool."""
     LocalTransport(spool)                                               # creates the three directories
+    try:
+        from . import hygiene
+
+        health = hygiene.gpu_health()                                   # read-only device listing, as the reference's worker does
+        log(f"[remote-worker] GPUs visible: {health['gpus']}" + ("" if health["ok"] else f" ({health['detail']})"))
+    except Exception as e:
+        log(f"[remote-worker] GPU listing failed: {type(e).__name__}: {e}")
     for n in sorted(os.listdir(os.path.join(spool, "running"))):
         path = os.path.join(spool, "running", n)
         if n.endswith(".json") and not os.path.exists(os.path.join(spool, "done", n[:-5], "result.json")) and _owner_gone(path + ".owner"):
