@@ -20,6 +20,7 @@ def main(argv=None) -> int:
     p.add_argument("--nproc", type=int, default=8)
     p.add_argument("--precision", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--out-dir", default=None, help="write prompt_<op>.md per selected op instead of printing")
+    p.add_argument("--prompts", default=None, help="TOML file whose entries replace the packaged templates (kernelgen/prompts.toml)")
     r = sub.add_parser("replay", help="run the loop over recorded candidate files")
     r.add_argument("--op", required=True)
     r.add_argument("--candidates", required=True)
@@ -36,6 +37,8 @@ def main(argv=None) -> int:
     g.add_argument("--api-key-env", default="PKB_KERNELGEN_API_KEY", help="environment variable holding the endpoint's key, if it needs one")
     g.add_argument("--max-tokens", type=int, default=16384)
     g.add_argument("--workdir", default="logs/kernelgen")
+    g.add_argument("--prompts", default=None, help="TOML file whose entries replace the packaged templates")
+    g.add_argument("--hardware", default="b200_8", help="hardware profile of the templates to quote")
     g.add_argument("--nproc", type=int, default=2)
     g.add_argument("--max-iters", type=int, default=4)
     g.add_argument("--resume", action="store_true", help="continue a previous run of this op in --workdir from its last feedback")
@@ -49,7 +52,7 @@ def main(argv=None) -> int:
         if a.out_dir:
             os.makedirs(a.out_dir, exist_ok=True)
         for op in ops:
-            text = build_prompt(op, a.hardware, a.nproc, precision=a.precision)
+            text = build_prompt(op, a.hardware, a.nproc, precision=a.precision, templates=a.prompts)
             if a.out_dir:
                 path = os.path.join(a.out_dir, f"prompt_{op}.md")
                 with open(path, "w") as fh:
@@ -70,7 +73,7 @@ def main(argv=None) -> int:
                         HttpProposer(a.endpoint, a.model, api_key_env=a.api_key_env, max_tokens=a.max_tokens, log_dir=log_dir))
             out = optimise(op, proposer, a.workdir,
                            nproc=a.nproc, max_iters=a.max_iters, backend=a.backend, dtype=a.dtype, config=a.config,
-                           resume=a.resume, measure_perf=a.measure_perf)
+                           resume=a.resume, measure_perf=a.measure_perf, templates=a.prompts, hardware=a.hardware)
             print(json.dumps(out, indent=1))
             rc = rc or (0 if out["solved"] else 1)
         return rc

@@ -122,7 +122,7 @@ def _trajectory(workdir: str, op: str, record: dict) -> None:
 
 
 def optimise(op: str, propose: Callable[[str, str | None], str], workdir: str, nproc: int = 2, max_iters: int = 4, trials: int = 1,
-             target_speedup: float = 0.0, resume: bool = False, **eval_kw) -> dict:
+             target_speedup: float = 0.0, resume: bool = False, templates: str | None = None, hardware: str = "b200_8", **eval_kw) -> dict:
     """Ask ``propose`` for a solution file, evaluate it against the reference, feed the verdict back, until every trial
     matches (and ``target_speedup`` is reached when timing is on) or ``max_iters`` attempts are used.
 
@@ -130,7 +130,8 @@ def optimise(op: str, propose: Callable[[str, str | None], str], workdir: str, n
     run on the shared GPUs is not launched, the hits go back to the proposer as feedback and the attempt counts. The run leaves
     the candidates, ``<op>_trajectory.jsonl`` (one line per event) and ``<op>_run.json`` (history, the best matching
     candidate and its speed-up) in ``workdir``; with ``resume`` a previous ``<op>_run.json`` is continued from its last
-    feedback instead of starting over. Returns the run record."""
+    feedback instead of starting over. ``templates`` / ``hardware``: a TOML file laid over the packaged prompt templates and
+    the hardware profile to quote from them. Returns the run record."""
     from ..harness.launch import eval_op
     from ..utils.source_screen import screen_source
 
@@ -144,7 +145,7 @@ def optimise(op: str, propose: Callable[[str, str | None], str], workdir: str, n
         feedback = history[-1]["feedback"] if history else None
         _trajectory(workdir, op, {"event": "resume", "attempts_so_far": len(history)})
     for it in range(len(history), len(history) + max_iters):
-        prompt = build_prompt(op, nproc=nproc, feedback=feedback)
+        prompt = build_prompt(op, hardware=hardware, nproc=nproc, feedback=feedback, templates=templates)
         _trajectory(workdir, op, {"event": "prompt", "iteration": it, "prompt_chars": len(prompt), "had_feedback": feedback is not None})
         try:
             source = propose(prompt, feedback)

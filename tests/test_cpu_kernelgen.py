@@ -169,3 +169,21 @@ def test_http_proposer_talks_to_a_chat_completions_endpoint(tmp_path, monkeypatc
         assert not out2["solved"] and out2["attempts"] == []
     finally:
         srv.shutdown()
+
+
+def test_prompt_templates_come_from_toml_and_can_be_overridden(tmp_path):
+    from parallelkernelbench_b200.kernelgen import build_prompt
+    from parallelkernelbench_b200.kernelgen.__main__ import main
+    from parallelkernelbench_b200.kernelgen.prompt import load_templates
+
+    base = load_templates()
+    assert {"contract", "hardware", "precision"} <= set(base) and "b200_8" in base["hardware"] and "{op}" in base["contract"]
+    extra = tmp_path / "mine.toml"
+    extra.write_text("[hardware]\nlab_2 = '''two GPUs of the lab machine, NVLink bridge'''\n[precision]\nbfloat16 = '''keep sums in fp32 (site rule)'''\n")
+    p = build_prompt("allreduce", hardware="lab_2", nproc=2, precision="bfloat16", templates=str(extra))
+    assert "two GPUs of the lab machine" in p and "site rule" in p and "def solution(rc, *inputs)" in p        # contract kept
+    assert "lab_2" not in load_templates()["hardware"]                                                       # the packaged file is untouched
+    out_dir = tmp_path / "prompts"
+    assert main(["prompt", "--op", "[1, 13]", "--hardware", "lab_2", "--nproc", "2", "--prompts", str(extra), "--out-dir", str(out_dir)]) == 0
+    assert sorted(f.name for f in out_dir.iterdir()) == ["prompt_allreduce.md", "prompt_gemm_allreduce.md"]
+    assert "two GPUs of the lab machine" in (out_dir / "prompt_gemm_allreduce.md").read_text()
