@@ -20,7 +20,7 @@ def main(argv=None) -> int:
     p.add_argument("--nproc", type=int, default=8)
     p.add_argument("--precision", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--out-dir", default=None, help="write prompt_<op>.md per selected op instead of printing")
-    p.add_argument("--prompts", default=None, help="TOML file whose entries replace the packaged templates (kernelgen/prompts.toml)")
+    p.add_argument("--prompts", default=None, help="TOML file whose entries replace the packaged templates (kernelgen/templates.toml)")
     r = sub.add_parser("replay", help="run the loop over recorded candidate files")
     r.add_argument("--op", required=True)
     r.add_argument("--candidates", required=True)

@@ -7,12 +7,12 @@ import os
 import textwrap
 import tomllib
 
-_TEMPLATE_FILE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "prompts.toml")
+_TEMPLATE_FILE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "templates.toml")
 
 
 def load_templates(path: str | None = None) -> dict:
     """The prompt templates (``contract``, ``[hardware]`` profiles, ``[precision]`` notes) from the packaged
-    ``prompts.toml``, with the entries of ``path`` - a file of the same layout - laid over them (reference:
+    ``templates.toml``, with the entries of ``path`` - a file of the same layout - laid over them (reference:
     kernelgen/prompts.toml keeps its templates in TOML for the same reason: they are edited far more often than code)."""
     with open(_TEMPLATE_FILE, "rb") as fh:
         base = tomllib.load(fh)
