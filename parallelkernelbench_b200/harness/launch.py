@@ -1,6 +1,7 @@
 """Launcher CLI: run one implementation, evaluate ours against the reference, sweep ops x world
 sizes, list the registry, and inspect stored results.
 
+    python -m parallelkernelbench_b200.harness.launch doctor                        # what is installed, built and visible
     python -m parallelkernelbench_b200.harness.launch list
     python -m parallelkernelbench_b200.harness.launch run   --op allreduce --impl ours --nproc 2
     python -m parallelkernelbench_b200.harness.launch eval  --op tp_mlp --nproc 8 --measure-perf
@@ -358,6 +359,73 @@ def cmd_eval(a) -> int:
     return 0 if s["all_ok"] else 1
 
 
+def doctor() -> dict:
+    """What a first run needs, checked without launching anything on a GPU: interpreter and torch versions, the compiler, the
+    in-tree native libraries and a few entry points each must export, the devices ``nvidia-smi -L`` lists (read-only),
+    room in /dev/shm for the CPU twin of the symmetric heap, and which roofline denominators are in use. The reference
+    prints hints of this kind only after a job has failed (reference: utils/run_utils.py:126-139)."""
+    import platform
+    import shutil as _sh
+
+    import torch
+
+    from .. import _native as nv
+    from ..utils import env as _env
+
+    out: dict = {"python": platform.python_version(), "torch": torch.__version__, "torch_cuda": torch.version.cuda,
+                 "nccl_backend": bool(torch.distributed.is_available() and torch.distributed.is_nccl_available()),
+                 "gloo_backend": bool(torch.distributed.is_available() and torch.distributed.is_gloo_available()),
+                 "nvcc": os.environ.get("NVCC") or _sh.which("nvcc"), "git_sha": _env.git_sha()}
+    libs = {}
+    for what, avail, loader, symbols in (
+            ("cuda", nv.cuda_lib_available, nv.cuda_lib, ("pkb_gemm_bf16_pair", "pkb_flash_attn_fwd", "pkb_coll_allreduce_nvls", "pkb_tp_ag_gemm", "pkb_heap_create")),
+            ("host", nv.host_lib_available, nv.host_lib, ("pkbh_ctrl_bytes",))):
+        rec = {"built": bool(avail()), "loads": False, "missing_symbols": []}
+        if rec["built"]:
+            try:
+                lib = loader()
+                rec["loads"] = True
+                rec["missing_symbols"] = [s for s in symbols if not hasattr(lib, s)]
+            except Exception as e:
+                rec["error"] = f"{type(e).__name__}: {e}"[:300]
+        libs[what] = rec
+    out["native_libraries"] = libs
+    out["gpus"] = hygiene.gpu_health()
+    try:
+        st = os.statvfs("/dev/shm")
+        out["dev_shm_free_mib"] = st.f_bavail * st.f_frsize >> 20
+    except OSError:
+        out["dev_shm_free_mib"] = None
+    pk = _env.measured_peaks()
+    out["roofline_peaks"] = {k: pk.get(k) for k in ("source", "hbm_gbs", "bf16_tflops", "bf16_tflops_sustained")}
+    problems = []
+    if not libs["cuda"]["built"] or not libs["host"]["built"]:
+        problems.append("native libraries are not built: run `python -m parallelkernelbench_b200.build` (needs nvcc)")
+    for what, rec in libs.items():
+        if rec["built"] and (not rec["loads"] or rec["missing_symbols"]):
+            problems.append(f"the {what} library is stale or broken: rebuild with `python -m parallelkernelbench_b200.build --force`")
+    if not out["nvcc"]:
+        problems.append("nvcc not found (set $NVCC or put CUDA >= 12.8 on PATH): needed to build, not to run")
+    if not out["gpus"]["ok"]:
+        problems.append("no GPU visible: only the CPU / gloo configurations (`--backend gloo`) can run here")
+    if out["dev_shm_free_mib"] is not None and out["dev_shm_free_mib"] < 256:
+        problems.append("/dev/shm has less than 256 MiB free: the CPU twin of the symmetric heap may not fit")
+    out["problems"] = problems
+    return out
+
+
+def cmd_doctor(a) -> int:
+    d = doctor()
+    if a.json:
+        print(json.dumps(d, indent=1))
+    else:
+        for k, v in d.items():
+            if k != "problems":
+                print(f"{k}: {v}")
+        print("problems: none" if not d["problems"] else "problems:\n  - " + "\n  - ".join(d["problems"]))
+    return 0 if not [p for p in d["problems"] if "not built" in p or "stale or broken" in p] else 1
+
+
 def cmd_remote_worker(a) -> int:
     from . import remote
 
@@ -514,6 +582,9 @@ def main(argv=None) -> int:
     sp.add_argument("--remote-ssh", default=None, metavar="USER@HOST", help="the spool directory lives on this host (SFTP)")
     sp.add_argument("--remote-wait", type=float, default=3600.0, help="seconds to wait for one remote job")
     sp.set_defaults(fn=cmd_eval)
+    sp = sub.add_parser("doctor", help="check interpreter, compiler, native libraries, visible GPUs and /dev/shm without launching anything")
+    sp.add_argument("--json", action="store_true")
+    sp.set_defaults(fn=cmd_doctor)
     sp = sub.add_parser("remote-worker", help="serve the job queue of a spool directory on this machine")
     sp.add_argument("--spool", required=True)
     sp.add_argument("--once", action="store_true", help="serve at most one job, or return at once when the queue is empty")

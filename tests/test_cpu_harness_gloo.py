@@ -202,3 +202,19 @@ def test_reference_style_flags_are_accepted(tmp_path, capsys, monkeypatch):
                       "--config", "small", "--m", "4"])
     out = capsys.readouterr().out
     assert rc == 0 and "--m ignored" in out and "prototypes" in out
+
+
+def test_doctor_reports_the_environment_without_launching_anything(capsys):
+    from parallelkernelbench_b200.harness import launch
+
+    d = launch.doctor()
+    assert d["native_libraries"]["cuda"] == {"built": True, "loads": True, "missing_symbols": []}
+    assert d["native_libraries"]["host"]["loads"] and d["gloo_backend"] and d["roofline_peaks"]["hbm_gbs"] > 1000
+    assert isinstance(d["problems"], list) and not any("not built" in p or "stale" in p for p in d["problems"])
+    assert launch.main(["doctor"]) == 0
+    out = capsys.readouterr().out
+    assert "native_libraries" in out and "problems" in out
+    assert launch.main(["doctor", "--json"]) == 0
+    import json
+
+    assert json.loads(capsys.readouterr().out)["python"]
