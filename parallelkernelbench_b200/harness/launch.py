@@ -338,6 +338,21 @@ def cmd_run(a) -> int:
     return 130 if job["interrupted"] else 1
 
 
+def _remote_runner(a):
+    """``run_job`` of a remote queue when ``--remote-spool`` was given, else None (jobs run on this machine)."""
+    if not getattr(a, "remote_spool", None):
+        return None
+    from . import remote
+
+    return remote.make_runner(a.remote_spool, ssh=a.remote_ssh, wait_s=a.remote_wait).run_job
+
+
+def _remote_args(sp) -> None:
+    sp.add_argument("--remote-spool", default=None, help="run the jobs through the queue in this spool directory (see harness/remote.py)")
+    sp.add_argument("--remote-ssh", default=None, metavar="USER@HOST", help="the spool directory lives on this host (SFTP)")
+    sp.add_argument("--remote-wait", type=float, default=3600.0, help="seconds to wait for one remote job")
+
+
 def cmd_eval(a) -> int:
     from ..workloads import registry
 
@@ -346,11 +361,7 @@ def cmd_eval(a) -> int:
         if not os.path.isfile(a.solution):
             print(f"no candidate file {a.solution}")
             return 2
-    runner = None
-    if a.remote_spool:
-        from . import remote
-
-        runner = remote.make_runner(a.remote_spool, ssh=a.remote_ssh, wait_s=a.remote_wait).run_job
+    runner = _remote_runner(a)
     s = eval_op(a.op, a.nproc, trials=a.trials, atol=a.atol, rtol=a.rtol, measure_perf=a.measure_perf, config=a.config,
                 overrides=_overrides(a), dtype=a.dtype, backend=a.backend, warmup=a.warmup, iters=a.iters,
                 graph=a.graph, profile=a.profile, timeout_s=a.timeout, solution=a.solution, runner=runner)
@@ -452,6 +463,7 @@ def cmd_sweep(a) -> int:
                 except ValueError:
                     pass
     rc = 0
+    runner = _remote_runner(a)
     for op in ops:
         solution = None
         if a.solutions_dir:
@@ -465,7 +477,7 @@ def cmd_sweep(a) -> int:
                 print(f"skip {op} w={w} (already in {ledger})")
                 continue
             s = eval_op(op, w, trials=a.trials, measure_perf=a.measure_perf, config=a.config, backend=a.backend,
-                        dtype=a.dtype, warmup=a.warmup, iters=a.iters, timeout_s=a.timeout, solution=solution)
+                        dtype=a.dtype, warmup=a.warmup, iters=a.iters, timeout_s=a.timeout, solution=solution, runner=runner)
             last = s["trials"][-1] if s["trials"] else {}
             cell = {"op": op, "world": w, "config": a.config, "all_ok": s["all_ok"], "git_sha": s["git_sha"],
                     "result": last.get("result"), "speedup": last.get("speedup"),
@@ -578,9 +590,7 @@ def main(argv=None) -> int:
     sp.add_argument("--solutions-dir", default=None, help="evaluate DIR/<op>.py (used when --solution is not given)")
     sp.add_argument("--atol", type=float, default=None)
     sp.add_argument("--rtol", type=float, default=None)
-    sp.add_argument("--remote-spool", default=None, help="run the jobs through the queue in this spool directory (see harness/remote.py)")
-    sp.add_argument("--remote-ssh", default=None, metavar="USER@HOST", help="the spool directory lives on this host (SFTP)")
-    sp.add_argument("--remote-wait", type=float, default=3600.0, help="seconds to wait for one remote job")
+    _remote_args(sp)
     sp.set_defaults(fn=cmd_eval)
     sp = sub.add_parser("doctor", help="check interpreter, compiler, native libraries, visible GPUs and /dev/shm without launching anything")
     sp.add_argument("--json", action="store_true")
@@ -605,6 +615,7 @@ def main(argv=None) -> int:
     sp.add_argument("--resume", action="store_true")
     sp.add_argument("--any-sha", action="store_true", help="with --resume: accept cells recorded at another commit")
     sp.add_argument("--solutions-dir", default=None, help="evaluate DIR/<op>.py instead of the built-in implementation; ops without a file are skipped")
+    _remote_args(sp)
     sp.set_defaults(fn=cmd_sweep)
     sp = sub.add_parser("headline")
     sp.add_argument("--nproc", "--nproc-per-node", dest="nproc", type=int, default=1)
