@@ -123,6 +123,9 @@ def main() -> int:
     from parallelkernelbench_b200.utils.clocks import ClockSampler
     from parallelkernelbench_b200.utils.env import measured_peaks
 
+    if not torch.cuda.is_available():
+        print("bench.py needs a CUDA device (B200): no GPU is visible to this process", file=sys.stderr)
+        return 2
     suite_cfgs = []
     if args.suite:
         from parallelkernelbench_b200.harness import suite as suite_mod
