@@ -57,3 +57,15 @@ def test_jitter_variant_builds_and_is_selected_by_env(monkeypatch):
     nv.cuda_lib()
     assert seen[-1] == "libpkb200_cuda_bounds.so"
     monkeypatch.setattr(nv, "_cuda", None)
+
+
+def test_example_script_compiles_and_declines_politely_without_a_gpu():
+    import subprocess
+
+    path = os.path.join(ROOT, "examples", "tp_mlp_block.py")
+    compile(open(path).read(), path, "exec")
+    import torch
+
+    if not torch.cuda.is_available():
+        r = subprocess.run([sys.executable, path], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 2 and "needs CUDA" in r.stderr
