@@ -1312,7 +1312,10 @@ def _knn_ours(rc, test, train_t, labels, k, classes):
 register(OpSpec(name="distributed_knn", problem_ids=(79,), group="wild",
                 configs={"default": {"queries": 32, "train": 2048, "d": 384, "k": 200, "classes": 1000},
                          "small": {"queries": 4, "train": 64, "d": 16, "k": 5, "classes": 10}},
-                make_inputs=_knn_inputs, reference=_knn_ref, ours=_knn_ours, atol=2e-2, rtol=2e-2))
+                make_inputs=_knn_inputs, reference=_knn_ref, ours=_knn_ours, atol=2e-2, rtol=2e-2,
+                # similarity GEMM of all ranks' queries against the local shard; queries gathered, candidate lists exchanged
+                cost=lambda cfg, W: Cost(flops=2.0 * W * cfg["queries"] * cfg["train"] * cfg["d"],
+                                         nvlink_bytes=(W - 1) * cfg["queries"] * (cfg["d"] * 2 + min(cfg["k"], cfg["train"]) * 8))))
 
 
 # =================================================================================================
@@ -1415,7 +1418,9 @@ def _sam(rc, masks, scores, counts, last, thr, ours):
 register(OpSpec(name="mask_iou_suppression", problem_ids=(81,), group="wild",
                 configs={"default": {"h": 256, "w": 256}, "small": {"h": 8, "w": 8}},
                 make_inputs=_sam_inputs, reference=lambda rc, *a: _sam(rc, *a, ours=False), ours=lambda rc, *a: _sam(rc, *a, ours=True),
-                atol=1e-5, rtol=1e-5))
+                atol=1e-5, rtol=1e-5,
+                # about two masks per rank: gathered as fp32, read once for packing and once for the output, written once
+                cost=lambda cfg, W: Cost(hbm_bytes=3.0 * 2 * W * cfg["h"] * cfg["w"] * 4, nvlink_bytes=2.0 * (W - 1) * cfg["h"] * cfg["w"] * 4)))
 
 
 # =================================================================================================
