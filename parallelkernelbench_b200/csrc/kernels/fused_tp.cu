@@ -463,6 +463,14 @@ int pkb_tp_ag_gemm_set_wait_stats(void* dev_words) {
   return kApiOk;
 }
 
+// Default number of communication CTAs of the all-gather -> GEMM kernel for a group of `world` ranks (bulk_push: the TMA bulk
+// ring; otherwise the thread-copy push). Exposed so that the rule can be checked without a GPU.
+extern "C" int pkb_tp_default_comm_ctas(int world, int bulk_push) {
+  if (world <= 1) return 2;
+  if (bulk_push) return world >= 8 ? 16 : (world > 4 ? 12 : 8);
+  return world >= 8 ? 16 : 8;
+}
+
 // C[gsize*rows, N] = epi( allgather(x_local)[gsize*rows, K] @ w[N, K]^T ), C local bf16.
 // gather_off / flags_off: heap offsets of the gather buffer (gsize*rows*K bf16) and of
 // gsize * (rows / a_chunk_rows) uint32 flags. `epoch` must grow by one on every call (same value
@@ -540,7 +548,7 @@ int pkb_tp_ag_gemm(const pkb_symm_ctx* h, const void* x_local, int rows, int K,
   // producers wait 169 us per call for 96 MiB of remote rows, 8 CTAs 2 us), and the GEMM consumes one remote shard per
   // 1/W of its run time, so the rate the push needs grows with W while the shard size stays: 8 CTAs cover a 32 MiB shard in
   // 115 us, which is enough up to 4 ranks (175 us per shard of GEMM time) and not at 8 ranks (87 us), where 16 are used.
-  if (comm_ctas <= 0) comm_ctas = a.bulk_push ? (W >= 8 ? 16 : (W > 4 ? 12 : (W > 1 ? 8 : 2))) : (W >= 8 ? 16 : (W > 1 ? 8 : 2));
+  if (comm_ctas <= 0) comm_ctas = pkb_tp_default_comm_ctas(W, a.bulk_push);
   comm_ctas = (comm_ctas + 1) & ~1;  // whole clusters
   const int sms = sm_count() & ~1;
   PKB_CHECK_ARG(comm_ctas < sms && comm_ctas <= kSymmMaxBlocks, "too many communication CTAs");

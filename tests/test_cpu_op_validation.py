@@ -131,3 +131,14 @@ def test_small_kernel_wrappers_reject_malformed_tensors():
     with pytest.raises(TypeError):
         wild.siglip_loss_from_products(torch.zeros(4, 4), 10.0, -10.0, 0)
     assert wild._sk_splits(1024) == (32, 32) and wild._sk_splits(10) == (10, 1) and wild._sk_splits(40) == (20, 2) and wild._sk_splits(1) == (1, 1)
+
+
+def test_default_number_of_push_ctas_follows_the_rank_count():
+    """A bulk-push CTA sustains a fixed rate while the GEMM consumes one remote shard per 1/W of its run time, so the default
+    grows with the group; it stays a multiple of the 8 sub-blocks of a shard from 8 ranks on."""
+    from parallelkernelbench_b200 import _native as nv
+
+    f = nv.cuda_lib().pkb_tp_default_comm_ctas
+    assert [f(w, 1) for w in (1, 2, 4, 6, 8)] == [2, 8, 8, 12, 16]
+    assert [f(w, 0) for w in (1, 2, 4, 8)] == [2, 8, 8, 16]
+    assert all(f(w, b) % 2 == 0 for w in range(1, 9) for b in (0, 1))          # whole CTA pairs
