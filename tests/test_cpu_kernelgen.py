@@ -187,3 +187,16 @@ def test_prompt_templates_come_from_toml_and_can_be_overridden(tmp_path):
     assert main(["prompt", "--op", "[1, 13]", "--hardware", "lab_2", "--nproc", "2", "--prompts", str(extra), "--out-dir", str(out_dir)]) == 0
     assert sorted(f.name for f in out_dir.iterdir()) == ["prompt_allreduce.md", "prompt_gemm_allreduce.md"]
     assert "two GPUs of the lab machine" in (out_dir / "prompt_gemm_allreduce.md").read_text()
+
+
+def test_generate_wants_exactly_one_source_of_candidates():
+    import pytest
+
+    from parallelkernelbench_b200.kernelgen.__main__ import main
+
+    for argv in (["generate", "--op", "allreduce"],
+                 ["generate", "--op", "allreduce", "--command", "cat", "--endpoint", "http://127.0.0.1:1/v1", "--model", "m"],
+                 ["generate", "--op", "allreduce", "--endpoint", "http://127.0.0.1:1/v1"]):
+        with pytest.raises(SystemExit) as e:
+            main(argv)
+        assert e.value.code == 2
