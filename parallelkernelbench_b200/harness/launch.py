@@ -287,6 +287,12 @@ def cmd_list(_args) -> int:
             if s.atol > compare.STRICT_ATOL or s.rtol > compare.STRICT_RTOL:
                 print(f"{s.name:36s} atol={s.atol:<6g} rtol={s.rtol:<6g} {s.tol_note}")
         return 0
+    if getattr(_args, "json", False):
+        # machine-readable registry: what tooling around the harness (sweeps, dashboards, generators) starts from
+        print(json.dumps([{"op": s.name, "group": s.group, "problem_ids": list(s.problem_ids), "configs": s.configs, "atol": s.atol, "rtol": s.rtol,
+                           "has_ours": s.ours is not None, "needs_cuda": s.ours_needs_cuda, "explicit_only": s.explicit_only,
+                           "has_cost_model": s.cost is not None} for s in registry.all_ops()], indent=1))
+        return 0
     for s in registry.all_ops():
         impl = "ours+ref" if s.ours is not None else "ref only"
         print(f"{s.name:32s} group={s.group:12s} problems={','.join(map(str, s.problem_ids)) or '-':12s} {impl:8s} configs={','.join(s.configs)}")
@@ -581,6 +587,7 @@ def main(argv=None) -> int:
     sub = ap.add_subparsers(dest="verb", required=True)
     sp = sub.add_parser("list"); sp.set_defaults(fn=cmd_list)
     sp.add_argument("--tolerances", action="store_true", help="list the ops compared with a gate looser than 1e-2 / 1e-2, and why")
+    sp.add_argument("--json", action="store_true", help="the registry as JSON (op, group, problem ids, configs, tolerances)")
     sp = sub.add_parser("run"); _common(sp, need_impl=True); sp.set_defaults(fn=cmd_run)
     sp.add_argument("--determinism", type=int, default=0, metavar="N",
                     help="repeat the run N times on identical inputs and require bit-identical outputs (exit 1 otherwise)")

@@ -218,3 +218,15 @@ def test_doctor_reports_the_environment_without_launching_anything(capsys):
     import json
 
     assert json.loads(capsys.readouterr().out)["python"]
+
+
+def test_list_as_json_covers_every_reference_problem(capsys):
+    import json
+
+    from parallelkernelbench_b200.harness import launch
+
+    assert launch.main(["list", "--json"]) == 0
+    ops = json.loads(capsys.readouterr().out)
+    covered = {p for o in ops for p in o["problem_ids"]}
+    assert covered >= set(range(1, 88)) and all(o["has_ours"] for o in ops if o["problem_ids"])
+    assert {"default"} <= set(ops[0]["configs"])
