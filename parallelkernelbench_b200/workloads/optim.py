@@ -233,6 +233,19 @@ def _mlp_dims(cfg, W):
     return n_total, max(16, min(cfg["n"], 256)), max(32, min(cfg["n"] // 2, 512)), max(8, min(cfg["n"] // 4, 256))
 
 
+def _mlp_param_count(cfg, W) -> int:
+    _, d_in, hid, d_out = _mlp_dims(cfg, W)
+    return hid * d_in + hid + d_out * hid + d_out
+
+
+def _step_cost(cfg, W, broadcasts: int = 0) -> Cost:
+    """Communication and memory floor of one data-parallel optimiser step on the two-layer MLP: the gradient crosses the links
+    once reduced ((W-1)/W of it per rank) and the new parameters once gathered; parameters, two moments and the gradient are
+    read and the first three written, in bf16."""
+    n = _mlp_param_count(cfg, W)
+    return Cost(nvlink_bytes=(2.0 + broadcasts) * n * 2 * (W - 1) / max(W, 1), hbm_bytes=7.0 * n * 2 / max(W, 1))
+
+
 def _mlp_data(rc, cfg, salt=0):
     n_total, d_in, hid, d_out = _mlp_dims(cfg, rc.world)
     chunk = n_total // rc.world
@@ -335,7 +348,7 @@ def _ddp_ours(rc, x, y, params, ms, vs, lr, b1, b2, eps, step):
 
 _MLP_CFG = {"default": {"m": 1024, "n": 1024}, "small": {"m": 32, "n": 64}}
 register(OpSpec(name="ddp_step", problem_ids=(40,), group="optim", configs=_MLP_CFG, make_inputs=_ddp_inputs, reference=_ddp_ref,
-                ours=_ddp_ours, atol=2e-2, rtol=2e-2))
+                ours=_ddp_ours, atol=2e-2, rtol=2e-2, cost=lambda cfg, W: _step_cost(cfg, W, broadcasts=3)))
 
 
 # ---- 41 / 42: ZeRO-1 / ZeRO-2 (optimizer state sharded; grads all-reduced vs reduce-scattered) --------
@@ -405,9 +418,9 @@ def _zero_ours(rc, x, y, params, m_part, v_part, lr, b1, b2, eps, step):
 
 
 register(OpSpec(name="zero1_step", problem_ids=(41,), group="optim", configs=_MLP_CFG, make_inputs=_zero_inputs, reference=_zero_ref(1),
-                ours=_zero_ours, atol=2e-2, rtol=2e-2))
+                ours=_zero_ours, atol=2e-2, rtol=2e-2, cost=_step_cost))
 register(OpSpec(name="zero2_step", problem_ids=(42,), group="optim", configs=_MLP_CFG, make_inputs=_zero_inputs, reference=_zero_ref(2),
-                ours=_zero_ours, atol=2e-2, rtol=2e-2))
+                ours=_zero_ours, atol=2e-2, rtol=2e-2, cost=_step_cost))
 
 
 # ---- 43: Adam on the shard, then all-gather of the updated parameters ---------------------------------
@@ -499,4 +512,4 @@ def _fsdp_ours(rc, x, y, shard, shapes, m, v, lr, b1, b2, eps, wd, step):
 
 
 register(OpSpec(name="fsdp_step", problem_ids=(47,), group="optim", configs=_MLP_CFG, make_inputs=_fsdp_inputs, reference=_fsdp_ref,
-                ours=_fsdp_ours, atol=2e-2, rtol=2e-2))
+                ours=_fsdp_ours, atol=2e-2, rtol=2e-2, cost=_step_cost))
