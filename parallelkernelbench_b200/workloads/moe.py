@@ -85,7 +85,8 @@ def _a2av_ours(rc, x, counts, cap):
 
 
 register(OpSpec(name="alltoall_v", problem_ids=(27,), group="moe", configs={"default": {"rows": 1024, "cols": 1024}, "small": {"rows": 64, "cols": 8}},
-                make_inputs=_a2av_inputs, reference=_a2av_ref, ours=_a2av_ours, atol=0, rtol=0))
+                make_inputs=_a2av_inputs, reference=_a2av_ref, ours=_a2av_ours, atol=0, rtol=0,
+                cost=lambda cfg, W: Cost(nvlink_bytes=cfg["rows"] * cfg["cols"] * 2.0 * (W - 1) / max(W, 1))))   # rows leave once
 
 
 # ---- 30: all-reduce of three small LoRA gradients ----------------------------------------------------

@@ -346,7 +346,10 @@ def _rope_ours(rc, q, k, cos, sin):
 
 register(OpSpec(name="rope_allgather", problem_ids=(17,), group="tp",
                 configs={"default": {"b": 16, "t": 16, "heads": 8, "d": 64}, "long": {"b": 1, "t": 32768, "heads": 32, "d": 128}},
-                make_inputs=_rope_inputs, reference=_rope_ref, ours=_rope_ours, atol=3e-2, rtol=2e-2))
+                make_inputs=_rope_inputs, reference=_rope_ref, ours=_rope_ours, atol=3e-2, rtol=2e-2,
+                # q and k of this rank's t / W positions go to every peer; every rank reads its shard and writes the gathered q, k
+                cost=lambda cfg, W: Cost(nvlink_bytes=2.0 * cfg["b"] * max(1, cfg["t"] // W) * cfg["heads"] * cfg["d"] * 2 * (W - 1),
+                                         hbm_bytes=2.0 * cfg["b"] * max(1, cfg["t"] // W) * cfg["heads"] * cfg["d"] * 2 * (1 + W))))
 
 
 # ---- 18: RMSNorm over a TP-sharded hidden dimension ---------------------------------------------
